@@ -1,0 +1,51 @@
+// Host emulation of the GPU decode GEMV: runs the very same unit functions the kernel runs
+// (csrc/gemv_units.h) over weights in the device layout, so the bit manipulation of every
+// fast-path block type is verifiable without a GPU.
+#include "gemv_units.h"
+
+#include <vector>
+
+using namespace rlz;
+
+namespace {
+template <int QT>
+void emu_rows(const uint8_t* W, int64_t stride, const ActView& a, float* y, int64_t n, int k, int batch) {
+  const int upr = dev_units_per_row(QT, k);
+  for (int64_t r = 0; r < n; ++r) {
+    for (int b = 0; b < batch; ++b) {
+      ActView ab{a.q + (int64_t)b * k, a.d + (int64_t)b * (k >> 5), a.s + (int64_t)b * (k >> 4), k};
+      // 32 lanes, each striding over units, then a tree reduction like the warp shuffle
+      float lane[32];
+      for (int l = 0; l < 32; ++l) { float acc = 0.f; for (int u = l; u < upr; u += 32) unit_dot<QT, 1>(W + r * stride, u, ab, &acc); lane[l] = acc; }
+      for (int off = 16; off > 0; off >>= 1) for (int l = 0; l < off; ++l) lane[l] += lane[l + off];
+      y[(int64_t)b * n + r] = lane[0];
+    }
+  }
+}
+}  // namespace
+
+extern "C" {
+
+int64_t rlz_dev_row_bytes(int qtype, int64_t k) { return dev_row_bytes(qtype, k); }
+
+// y[batch, n] = W_dev[n, k] x[batch, k] with int8 activations, exactly as the GPU fast path computes it.
+int rlz_emu_gemv(int qtype, const void* W, int64_t stride, const float* x, float* y, int64_t n, int k, int batch) {
+  if (k % 32) return -1;
+  std::vector<int8_t> q((size_t)batch * k); std::vector<float> d((size_t)batch * (k / 32)), s((size_t)batch * (k / 16));
+  for (int b = 0; b < batch; ++b)
+    for (int i = 0; i < k / 32; ++i)
+      quantize_act_block32(x + (int64_t)b * k + 32 * i, q.data() + (int64_t)b * k + 32 * i, d.data() + (int64_t)b * (k / 32) + i,
+                           s.data() + (int64_t)b * (k / 16) + 2 * i);
+  ActView a{q.data(), d.data(), s.data(), k};
+  const uint8_t* w = (const uint8_t*)W;
+  switch (qtype) {
+    case QT_Q4_K: emu_rows<QT_Q4_K>(w, stride, a, y, n, k, batch); return 0;
+    case QT_Q5_K: emu_rows<QT_Q5_K>(w, stride, a, y, n, k, batch); return 0;
+    case QT_Q6_K: emu_rows<QT_Q6_K>(w, stride, a, y, n, k, batch); return 0;
+    case QT_Q8_0: emu_rows<QT_Q8_0>(w, stride, a, y, n, k, batch); return 0;
+    case QT_Q4_0: emu_rows<QT_Q4_0>(w, stride, a, y, n, k, batch); return 0;
+    default: return -2;
+  }
+}
+
+}  // extern "C"

@@ -1,0 +1,291 @@
+// Flash-decode GQA attention over a paged bf16 KV cache, one new token per sequence, with the
+// work that surrounds it in a decode layer fused in:
+//   * per-head RMSNorm of q/k (QK-norm models), RoPE (NORM / NEOX, partial rotary) on q and k
+//   * append of the new k/v row to the paged cache
+//   * split-K over the context (grid.y) with the log-sum-exp merge done by the last CTA to
+//     finish for a (sequence, kv-head group), so there is no separate reduce launch.
+//
+// Cache layout: k_cache / v_cache = bf16 [num_pages, n_kv_heads, PAGE, head_dim]; a
+// sequence's pages are listed in page_table[b, :].  Positions are read from device memory so
+// the launch is replayable inside a CUDA graph; positions[b] < 0 marks an empty batch slot.
+//
+// Replaces the reference's rope*/kv_cache_scatter*/incremental_attention*/multi_warp_attention*/
+// flash_decoding_chunk+reduce kernels (src/cuda/executor/kv_scatter.rs:15-388,
+// src/cuda/executor/flash_decoding_graphed.rs:14-209, src/cuda/executor/batch.rs:18-400).
+#include "common.cuh"
+#include <cuda_bf16.h>
+#include <math.h>
+
+namespace rlz {
+
+constexpr int ATT_PAGE = 16;
+constexpr int ATT_THREADS = 128;
+constexpr int ATT_TB = 4;            // tokens per half-warp per iteration
+
+struct AttnDecodeParams {
+  const float* qkv;        // [B, ld_qkv]: q heads | k heads | v heads (after bias)
+  float* out;              // [B, ld_out]: attention output, head-major
+  __nv_bfloat16* k_cache;
+  __nv_bfloat16* v_cache;
+  const int32_t* positions;   // [B]
+  const int32_t* page_table;  // [B, max_pages]
+  const float* q_norm_w;   // [head_dim] or null
+  const float* k_norm_w;   // [head_dim] or null
+  float* partial;          // scratch [B, H, splits, head_dim + 2]
+  int32_t* counters;       // scratch [B, n_kv_heads * head_groups], zero before first use
+  int64_t ld_qkv, ld_out;
+  int32_t n_heads, n_kv_heads, head_dim, max_pages;
+  int32_t rope_dim, rope_type, splits, batch;
+  int32_t q_off, k_off, v_off, _pad;   // element offsets of the q / k / v sections in a qkv row
+  float rope_theta, eps, scale, _padf;
+};
+
+__device__ __forceinline__ void rope_inplace(float* v, int d_rot, int rope_type, int pos, float theta, int tid, int nthreads) {
+  const int half = d_rot >> 1;
+  for (int i = tid; i < half; i += nthreads) {
+    const float freq = powf(theta, -2.f * (float)i / (float)d_rot);
+    float sn, cs;
+    sincosf((float)pos * freq, &sn, &cs);
+    const int i0 = rope_type == 2 ? i : 2 * i, i1 = rope_type == 2 ? i + half : 2 * i + 1;
+    const float a = v[i0], b = v[i1];
+    v[i0] = a * cs - b * sn;
+    v[i1] = a * sn + b * cs;
+  }
+}
+
+template <int GT>
+__global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_constant__ AttnDecodeParams p) {
+  const int G = p.n_heads / p.n_kv_heads;
+  const int hgroups = (G + GT - 1) / GT;
+  const int kvh = blockIdx.x / hgroups, hg = blockIdx.x - kvh * hgroups;
+  const int split = blockIdx.y, b = blockIdx.z;
+  const int d = p.head_dim;
+  const int g0 = hg * GT, gn = min(GT, G - g0);          // query heads [g0, g0+gn) of this kv head
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int l16 = lane & 15, hw = tid >> 4;              // half-warp id 0..7
+
+  __shared__ float q_s[GT][128];
+  __shared__ float k_s[128], v_s[128];
+  __shared__ float part_s[ATT_THREADS / 16][GT][128 + 2];
+  __shared__ int last_flag;
+
+  pdl_launch_dependents();
+  pdl_wait();
+
+  const int pos = p.positions[b];
+  if (pos < 0) return;
+  const int seq_len = pos + 1;
+  int chunk = (seq_len + p.splits - 1) / p.splits;
+  chunk = (chunk + ATT_PAGE - 1) / ATT_PAGE * ATT_PAGE;
+  const int start = split * chunk, end = min(seq_len, start + chunk);
+  const bool owner = start <= pos && pos < end;
+
+  // ---- stage q (this head group), and k/v of the new token ---------------------------------
+  const float* row = p.qkv + (int64_t)b * p.ld_qkv;
+  for (int i = tid; i < gn * d; i += ATT_THREADS) {
+    const int g = i / d, j = i - g * d;
+    q_s[g][j] = row[p.q_off + (kvh * G + g0 + g) * d + j];
+  }
+  if (owner) {
+    for (int j = tid; j < d; j += ATT_THREADS) {
+      k_s[j] = row[p.k_off + kvh * d + j];
+      v_s[j] = row[p.v_off + kvh * d + j];
+    }
+  }
+  __syncthreads();
+  if (p.q_norm_w) {      // per-head RMSNorm, one warp per head
+    for (int g = warp; g < gn + (owner ? 1 : 0); g += ATT_THREADS / 32) {
+      float* v = g < gn ? q_s[g] : k_s;
+      const float* w = g < gn ? p.q_norm_w : p.k_norm_w;
+      float ss = 0.f;
+      for (int j = lane; j < d; j += 32) ss += v[j] * v[j];
+      ss = warp_sum(ss);
+      const float r = rsqrtf(ss / (float)d + p.eps);
+      for (int j = lane; j < d; j += 32) v[j] = v[j] * r * w[j];
+    }
+    __syncthreads();
+  }
+  if (p.rope_dim > 0) {
+    for (int g = 0; g < gn; ++g) rope_inplace(q_s[g], p.rope_dim, p.rope_type, pos, p.rope_theta, tid, ATT_THREADS);
+    if (owner) rope_inplace(k_s, p.rope_dim, p.rope_type, pos, p.rope_theta, tid, ATT_THREADS);
+    __syncthreads();
+  }
+  const int32_t* pt = p.page_table + (int64_t)b * p.max_pages;
+  if (owner && hg == 0) {   // append the new row to the cache (one head group does it)
+    const int page = pt[pos / ATT_PAGE], slot = pos % ATT_PAGE;
+    const int64_t off = (((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE + slot) * d;
+    for (int j = tid; j < d; j += ATT_THREADS) {
+      p.k_cache[off + j] = __float2bfloat16_rn(k_s[j]);
+      p.v_cache[off + j] = __float2bfloat16_rn(v_s[j]);
+    }
+  }
+  __syncthreads();
+
+  // ---- per-lane query slice: 8 dims, pre-scaled so that exp2 can be used ---------------------
+  const int j0 = l16 * 8;
+  const bool lane_ok = j0 < d;
+  const float qscale = p.scale * 1.4426950408889634f;
+  float q[GT][8], acc[GT][8], m[GT], l[GT];
+#pragma unroll
+  for (int g = 0; g < GT; ++g) {
+    m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { acc[g][j] = 0.f; q[g][j] = (g < gn && lane_ok) ? q_s[g][j0 + j] * qscale : 0.f; }
+  }
+
+  // the owner CTA of a non-zero head group reads the new row from shared memory instead of the
+  // cache (another CTA is writing it), everyone else reads the cache only
+  // shuffles stay inside a half-warp (all 16 lanes share base / validity), so each half uses its own mask
+  const unsigned hmask = 0xFFFFu << (lane & 16);
+  const int iters = (max(0, end - start) + (ATT_THREADS / 16) * ATT_TB - 1) / ((ATT_THREADS / 16) * ATT_TB);
+  for (int it = 0; it < iters; ++it) {
+    const int base = start + (it * (ATT_THREADS / 16) + hw) * ATT_TB;
+    const bool any = base < end;
+    const int page = any ? pt[base / ATT_PAGE] : 0, slot = base % ATT_PAGE;
+    const int64_t off = (((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE + slot) * d + j0;
+    uint4 kr[ATT_TB], vr[ATT_TB];
+#pragma unroll
+    for (int t = 0; t < ATT_TB; ++t) {
+      const bool ok = lane_ok && base + t < end && !(hg != 0 && base + t == pos);
+      kr[t] = ok ? *(const uint4*)(p.k_cache + off + (int64_t)t * d) : make_uint4(0, 0, 0, 0);
+      vr[t] = ok ? *(const uint4*)(p.v_cache + off + (int64_t)t * d) : make_uint4(0, 0, 0, 0);
+    }
+    float kf[ATT_TB][8], vf[ATT_TB][8];
+#pragma unroll
+    for (int t = 0; t < ATT_TB; ++t) {
+      const uint32_t kw[4] = {kr[t].x, kr[t].y, kr[t].z, kr[t].w}, vw[4] = {vr[t].x, vr[t].y, vr[t].z, vr[t].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        kf[t][2 * j] = __uint_as_float(kw[j] << 16); kf[t][2 * j + 1] = __uint_as_float(kw[j] & 0xFFFF0000u);
+        vf[t][2 * j] = __uint_as_float(vw[j] << 16); vf[t][2 * j + 1] = __uint_as_float(vw[j] & 0xFFFF0000u);
+      }
+      if (hg != 0 && base + t == pos && lane_ok) {   // new row straight from shared memory (bf16-rounded like the cache)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          kf[t][j] = __bfloat162float(__float2bfloat16_rn(k_s[j0 + j]));
+          vf[t][j] = __bfloat162float(__float2bfloat16_rn(v_s[j0 + j]));
+        }
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+      float s[ATT_TB];
+#pragma unroll
+      for (int t = 0; t < ATT_TB; ++t) {
+        float x = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x += q[g][j] * kf[t][j];
+        x += __shfl_xor_sync(hmask, x, 8);
+        x += __shfl_xor_sync(hmask, x, 4);
+        x += __shfl_xor_sync(hmask, x, 2);
+        x += __shfl_xor_sync(hmask, x, 1);
+        s[t] = base + t < end ? x : -INFINITY;
+      }
+      float mn = m[g];
+#pragma unroll
+      for (int t = 0; t < ATT_TB; ++t) mn = fmaxf(mn, s[t]);
+      if (mn == -INFINITY) continue;           // nothing valid seen yet by this stream
+      const float corr = exp2f(m[g] - mn);     // m = -inf on the first valid pass -> 0
+      l[g] *= corr;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[g][j] *= corr;
+#pragma unroll
+      for (int t = 0; t < ATT_TB; ++t) {
+        const float pr = exp2f(s[t] - mn);
+        l[g] += pr;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[g][j] += pr * vf[t][j];
+      }
+      m[g] = mn;
+    }
+  }
+
+  // ---- combine the 8 half-warp streams of this CTA -------------------------------------------
+#pragma unroll
+  for (int g = 0; g < GT; ++g) {
+    if (g < gn) {
+      if (lane_ok) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) part_s[hw][g][j0 + j] = acc[g][j];
+      }
+      if (l16 == 0) { part_s[hw][g][128] = m[g]; part_s[hw][g][129] = l[g]; }
+    }
+  }
+  __syncthreads();
+  const int S = p.splits;
+  for (int i = tid; i < gn * d; i += ATT_THREADS) {
+    const int g = i / d, j = i - g * d;
+    float mm = -INFINITY;
+    for (int w = 0; w < ATT_THREADS / 16; ++w) mm = fmaxf(mm, part_s[w][g][128]);
+    float a = 0.f, ll = 0.f;
+    for (int w = 0; w < ATT_THREADS / 16; ++w) {
+      const float mw = part_s[w][g][128];
+      const float c = mw == -INFINITY ? 0.f : exp2f(mw - mm);
+      a += c * part_s[w][g][j]; ll += c * part_s[w][g][129];
+    }
+    float* dst = p.partial + (((int64_t)b * p.n_heads + kvh * G + g0 + g) * S + split) * (d + 2);
+    dst[j] = a;
+    if (j == 0) { dst[d] = mm; dst[d + 1] = ll; }
+  }
+
+  // ---- last CTA of this (sequence, kv head, head group) merges the splits ----------------------
+  __threadfence();
+  __syncthreads();
+  int32_t* ctr = p.counters + (int64_t)b * (p.n_kv_heads * hgroups) + blockIdx.x;
+  if (tid == 0) {
+    const int ticket = atomicAdd(ctr, 1);
+    last_flag = ticket == S - 1;
+    if (last_flag) *ctr = 0;       // self-cleaning for the next launch
+  }
+  __syncthreads();
+  if (!last_flag) return;
+  __threadfence();
+  for (int i = tid; i < gn * d; i += ATT_THREADS) {
+    const int g = i / d, j = i - g * d;
+    const float* src = p.partial + ((int64_t)b * p.n_heads + kvh * G + g0 + g) * S * (d + 2);
+    float mm = -INFINITY;
+    for (int s = 0; s < S; ++s) mm = fmaxf(mm, __ldcg(src + (int64_t)s * (d + 2) + d));
+    float a = 0.f, ll = 0.f;
+    for (int s = 0; s < S; ++s) {
+      const float ms = __ldcg(src + (int64_t)s * (d + 2) + d);
+      const float c = ms == -INFINITY ? 0.f : exp2f(ms - mm);
+      a += c * __ldcg(src + (int64_t)s * (d + 2) + j);
+      ll += c * __ldcg(src + (int64_t)s * (d + 2) + d + 1);
+    }
+    p.out[(int64_t)b * p.ld_out + (kvh * G + g0 + g) * d + j] = a / ll;
+  }
+}
+
+}  // namespace rlz
+
+extern "C" {
+
+// scratch sizes for a launch configuration (floats / ints)
+long long rlz_attn_decode_partial_floats(int batch, int n_heads, int splits, int head_dim) {
+  return (long long)batch * n_heads * splits * (head_dim + 2);
+}
+long long rlz_attn_decode_counter_ints(int batch, int n_heads) { return (long long)batch * n_heads; }
+
+int rlz_attn_decode(const rlz::AttnDecodeParams* pp, void* stream) {
+  using namespace rlz;
+  const AttnDecodeParams& p = *pp;
+  if (p.head_dim % 8 || p.head_dim > 128 || p.head_dim < 8) return -1;
+  if (p.n_heads % p.n_kv_heads || p.splits < 1 || p.batch < 1) return -2;
+  if (p.rope_dim > p.head_dim || (p.rope_dim & 1)) return -3;
+  if (((uintptr_t)p.k_cache & 15) || ((uintptr_t)p.v_cache & 15)) return -4;
+  const int G = p.n_heads / p.n_kv_heads;
+  const int GT = G == 1 ? 1 : G == 2 ? 2 : G == 8 ? 8 : 4;
+  const int hgroups = (G + GT - 1) / GT;
+  dim3 grid(p.n_kv_heads * hgroups, p.splits, p.batch), block(ATT_THREADS);
+  cudaError_t e;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (GT) {
+    case 1: e = launch(attn_decode_kernel<1>, grid, block, 0, st, p); break;
+    case 2: e = launch(attn_decode_kernel<2>, grid, block, 0, st, p); break;
+    case 8: e = launch(attn_decode_kernel<8>, grid, block, 0, st, p); break;
+    default: e = launch(attn_decode_kernel<4>, grid, block, 0, st, p); break;
+  }
+  return (int)e;
+}
+
+}  // extern "C"

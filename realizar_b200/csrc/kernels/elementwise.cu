@@ -1,0 +1,207 @@
+// Small bandwidth-bound kernels: embedding lookup (any block type), RMSNorm / LayerNorm with an
+// optional fused residual add, standalone RoPE, bias / residual add, activations, and the
+// paged KV append used by prefill.  On the decode path most of this work is fused into the
+// GEMV and attention kernels; these standalone forms serve prefill, tests and tracing.
+//
+// Replaces the reference's rmsnorm*/layernorm*/fused_residual_rmsnorm, rope*/batched_rope*,
+// residual_add/batched_bias_broadcast_add, silu/gelu/fused_swiglu and scatter_packed_kv kernels
+// (src/cuda/executor/layer_norm_gpu.rs:8-877, src/cuda/executor/residual.rs:16-416,
+// src/cuda/executor/silu.rs:13-255, src/cuda/executor/layers/cublas_prefill/attention.rs:191-290).
+#include "common.cuh"
+#include "../quant_blocks.h"
+#include <cuda_bf16.h>
+
+namespace rlz {
+
+// out[t, :] = dequant(table[tokens[t], :]) (+ pos_table[positions[t], :]).  One CTA per token.
+__global__ void embed_kernel(const uint8_t* table, int qtype, int64_t row_bytes, int hidden, const int32_t* tokens,
+                             const float* pos_table, const int32_t* positions, float* out, int64_t ld_out, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int tok = tokens[t];
+  float* o = out + (int64_t)t * ld_out;
+  if (tok < 0 || tok >= vocab) { for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = 0.f; return; }
+  const uint8_t* row = table + (int64_t)tok * row_bytes;
+  const int be = qtype_block_elems(qtype), bb = qtype_block_bytes(qtype);
+  if (be == 1) {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      float v;
+      if (qtype == QT_F32) v = ((const float*)row)[i];
+      else { const uint16_t h = ((const uint16_t*)row)[i]; v = qtype == QT_F16 ? half_bits_to_float(h) : bf16_bits_to_float(h); }
+      o[i] = v;
+    }
+  } else {
+    for (int blk = threadIdx.x; blk < hidden / be; blk += blockDim.x) {
+      float tmp[256];
+      dequant_block(qtype, row + (int64_t)blk * bb, tmp);
+      for (int j = 0; j < be; ++j) o[blk * be + j] = tmp[j];
+    }
+  }
+  if (pos_table) {
+    __syncthreads();
+    const float* pr = pos_table + (int64_t)positions[t] * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] += pr[i];
+  }
+}
+
+// y = norm(x (+ residual)) * w (+ b); when `sum_out` is given the pre-norm sum is stored too.
+__global__ void norm_kernel(const float* x, const float* residual, const float* w, const float* b, float* y, float* sum_out,
+                            int n, int64_t ld, int norm_type, float eps) {
+  __shared__ float red[40];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t off = (int64_t)blockIdx.x * ld;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = x[off + i];
+    if (residual) v += residual[off + i];
+    if (sum_out) sum_out[off + i] = v;
+    s += norm_type == NORM_LAYER ? v : v * v;
+  }
+  s = block_sum(s, red);
+  float mean = 0.f, rstd;
+  if (norm_type == NORM_LAYER) {
+    mean = s / (float)n;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      float v = x[off + i]; if (residual) v += residual[off + i];
+      ss += (v - mean) * (v - mean);
+    }
+    ss = block_sum(ss, red);
+    rstd = rsqrtf(ss / (float)n + eps);
+  } else {
+    rstd = rsqrtf(s / (float)n + eps);
+  }
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = x[off + i]; if (residual) v += residual[off + i];
+    v = (v - mean) * rstd;
+    if (w) v *= w[i];
+    if (b) v += b[i];
+    y[off + i] = v;
+  }
+}
+
+// per-head RMSNorm (QK-norm): x [T, heads, d] in place
+__global__ void head_rmsnorm_kernel(float* x, const float* w, int heads, int d, int64_t ld, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int h = warp; h < heads; h += nw) {
+    float* v = x + (int64_t)t * ld + (int64_t)h * d;
+    float ss = 0.f;
+    for (int j = lane; j < d; j += 32) ss += v[j] * v[j];
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / (float)d + eps);
+    for (int j = lane; j < d; j += 32) v[j] = v[j] * r * w[j];
+  }
+}
+
+// RoPE in place on x [T, heads, d]: rotates the first rope_dim dims of each head.
+__global__ void rope_kernel(float* x, const int32_t* positions, int heads, int d, int64_t ld, int rope_dim, int rope_type, float theta) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, half = rope_dim >> 1;
+  const int pos = positions[t];
+  if (pos < 0) return;
+  for (int idx = threadIdx.x; idx < heads * half; idx += blockDim.x) {
+    const int h = idx / half, i = idx - h * half;
+    const float freq = powf(theta, -2.f * (float)i / (float)rope_dim);
+    float sn, cs; sincosf((float)pos * freq, &sn, &cs);
+    float* v = x + (int64_t)t * ld + (int64_t)h * d;
+    const int i0 = rope_type == 2 ? i : 2 * i, i1 = rope_type == 2 ? i + half : 2 * i + 1;
+    const float a = v[i0], bb = v[i1];
+    v[i0] = a * cs - bb * sn; v[i1] = a * sn + bb * cs;
+  }
+}
+
+// y[r, c] = act(a[r, c] + bias[c]) (* gate-mul b[r, c]) (+ residual[r, c])
+__global__ void elementwise_kernel(const float* a, const float* b, const float* bias, const float* residual, float* y,
+                                   int64_t rows, int cols, int64_t ld_a, int64_t ld_b, int64_t ld_y, int act, int mul) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t total = rows * cols;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / cols; const int c = (int)(idx - r * cols);
+    float v = a[r * ld_a + c];
+    if (bias) v += bias[c];
+    if (act == ACT_GELU) v = gelu_tanh(v); else if (act == ACT_SILU) v = silu(v);
+    if (mul) v *= b[r * ld_b + c];
+    if (residual) v += residual[r * ld_y + c];
+    y[r * ld_y + c] = v;
+  }
+}
+
+// Append T rows of k / v ([T, n_kv_heads, d] f32, row stride ld) to the paged bf16 cache.
+__global__ void kv_append_kernel(const float* k, const float* v, int64_t ld, __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
+                                 const int32_t* positions, const int32_t* page_rows, int n_kv_heads, int d, int page) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  if (pos < 0) return;
+  const int pg = page_rows[t];                     // physical page holding position `pos`
+  const int slot = pos % page;
+  for (int idx = threadIdx.x; idx < n_kv_heads * d; idx += blockDim.x) {
+    const int h = idx / d, j = idx - h * d;
+    const int64_t off = (((int64_t)pg * n_kv_heads + h) * page + slot) * d + j;
+    k_cache[off] = __float2bfloat16_rn(k[(int64_t)t * ld + idx]);
+    v_cache[off] = __float2bfloat16_rn(v[(int64_t)t * ld + idx]);
+  }
+}
+
+// Feed sampled tokens back as the next step's inputs and advance positions of active slots.
+__global__ void advance_kernel(int32_t* tokens, const int32_t* sampled, int32_t* positions, int batch) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < batch && positions[b] >= 0) { tokens[b] = sampled[b]; positions[b] += 1; }
+}
+
+}  // namespace rlz
+
+extern "C" {
+using namespace rlz;
+
+int rlz_advance(int32_t* tokens, const int32_t* sampled, int32_t* positions, int batch, void* stream) {
+  return (int)launch(advance_kernel, dim3((batch + 63) / 64), dim3(64), 0, (cudaStream_t)stream, tokens, sampled, positions, batch);
+}
+
+int rlz_embed(const void* table, int qtype, long long row_bytes, int hidden, int vocab, const int32_t* tokens, int n_tokens,
+              const float* pos_table, const int32_t* positions, float* out, long long ld_out, void* stream) {
+  const int be = qtype_block_elems(qtype);
+  if (!be || hidden % be) return -1;
+  return (int)launch(embed_kernel, dim3(n_tokens), dim3(128), 0, (cudaStream_t)stream, (const uint8_t*)table, qtype, (int64_t)row_bytes,
+                     hidden, tokens, pos_table, positions, out, (int64_t)ld_out, vocab);
+}
+
+int rlz_norm(const float* x, const float* residual, const float* w, const float* b, float* y, float* sum_out, int rows, int n,
+             long long ld, int norm_type, float eps, void* stream) {
+  return (int)launch(norm_kernel, dim3(rows), dim3(n >= 2048 ? 512 : 256), 0, (cudaStream_t)stream, x, residual, w, b, y, sum_out, n, (int64_t)ld, norm_type, eps);
+}
+
+int rlz_head_rmsnorm(float* x, const float* w, int rows, int heads, int d, long long ld, float eps, void* stream) {
+  return (int)launch(head_rmsnorm_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, x, w, heads, d, (int64_t)ld, eps);
+}
+
+int rlz_rope(float* x, const int32_t* positions, int rows, int heads, int d, long long ld, int rope_dim, int rope_type, float theta, void* stream) {
+  if (rope_dim <= 0) return 0;
+  if (rope_dim > d || (rope_dim & 1)) return -1;
+  return (int)launch(rope_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, x, positions, heads, d, (int64_t)ld, rope_dim, rope_type, theta);
+}
+
+int rlz_elementwise(const float* a, const float* b, const float* bias, const float* residual, float* y, long long rows, int cols,
+                    long long ld_a, long long ld_b, long long ld_y, int act, int mul, void* stream) {
+  const long long total = rows * cols;
+  int grid = (int)((total + 255) / 256); if (grid > 148 * 8) grid = 148 * 8; if (grid < 1) grid = 1;
+  return (int)launch(elementwise_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, a, b, bias, residual, y, (int64_t)rows, cols,
+                     (int64_t)ld_a, (int64_t)ld_b, (int64_t)ld_y, act, mul);
+}
+
+int rlz_kv_append(const float* k, const float* v, long long ld, void* k_cache, void* v_cache, const int32_t* positions,
+                  const int32_t* page_rows, int n_tokens, int n_kv_heads, int d, int page, void* stream) {
+  return (int)launch(kv_append_kernel, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, k, v, (int64_t)ld, (__nv_bfloat16*)k_cache,
+                     (__nv_bfloat16*)v_cache, positions, page_rows, n_kv_heads, d, page);
+}
+
+}  // extern "C"

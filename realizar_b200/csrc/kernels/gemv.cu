@@ -1,0 +1,316 @@
+// Decode GEMV over block-quantised weights (batch 1..4), with the surrounding element-wise
+// work fused in:
+//   prologue : RMSNorm / LayerNorm of the input vector and its int8 quantisation (per CTA, in
+//              shared memory) - no separate norm or quantise kernels, no activation round trip;
+//   body     : one warp per output row, lanes stride over 16-byte weight units (dp4a);
+//   epilogue : bias, GELU/SiLU, SwiGLU combine of a gate/up pair, second accumulated matrix
+//              (parallel attention+MLP blocks), residual add.
+// One launch covers up to four matrices that share the launch (e.g. Q, K, V or QKV + MLP-up).
+//
+// Replaces the reference's q4k/q5k/q6k/q8_0/q4_0 GEMV families, q8_quantize, the fused
+// rmsnorm/gate-up/swiglu GEMVs, residual_add and bias kernels
+// (src/cuda/executor/q4k_mwv_gemv.rs:7-945, src/cuda/executor/layers/gemv_dispatch.rs:53-309).
+#include "common.cuh"
+#include "../gemv_units.h"
+#include "gemv_params.h"
+
+namespace rlz {
+
+constexpr int GEMV_THREADS = 512;
+
+// ---- input staging ---------------------------------------------------------------------
+// mean / rstd of one input row (block-wide).  LayerNorm uses two passes for accuracy.
+__device__ void row_stats(const GemvX& X, const float* x, float* red, float* mean_out, float* rstd_out) {
+  float mean = 0.f, rstd = 1.f;
+  if (X.norm == NORM_RMS) {
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < X.k; i += blockDim.x * 4) {
+      const float4 v = *(const float4*)(x + i);
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = block_sum(ss, red);
+    rstd = rsqrtf(ss / (float)X.k + X.eps);
+  } else if (X.norm == NORM_LAYER) {
+    float s = 0.f;
+    for (int i = threadIdx.x * 4; i < X.k; i += blockDim.x * 4) {
+      const float4 v = *(const float4*)(x + i);
+      s += v.x + v.y + v.z + v.w;
+    }
+    mean = block_sum(s, red) / (float)X.k;
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < X.k; i += blockDim.x * 4) {
+      const float4 v = *(const float4*)(x + i);
+      const float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+      ss += a * a + b * b + c * c + d * d;
+    }
+    ss = block_sum(ss, red);
+    rstd = rsqrtf(ss / (float)X.k + X.eps);
+  }
+  *mean_out = mean; *rstd_out = rstd;
+}
+
+__device__ __forceinline__ float4 load_normed(const GemvX& X, const float* x, int i, float mean, float rstd) {
+  float4 v = *(const float4*)(x + i);
+  if (X.norm != NORM_NONE) {
+    v.x = (v.x - mean) * rstd; v.y = (v.y - mean) * rstd; v.z = (v.z - mean) * rstd; v.w = (v.w - mean) * rstd;
+    if (X.nw) { const float4 w = __ldg((const float4*)(X.nw + i)); v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w; }
+    if (X.nb) { const float4 b = __ldg((const float4*)(X.nb + i)); v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w; }
+  }
+  return v;
+}
+
+// int8 staging: xq[B][k], xd[B][k/32], xs[B][k/16]
+template <int B>
+__device__ void stage_x_q8(const GemvX& X, int8_t* xq, float* xd, float* xs, float* red) {
+  const int k = X.k;
+#pragma unroll 1
+  for (int b = 0; b < B; ++b) {
+    const float* x = X.x + (int64_t)b * X.ld;
+    float mean, rstd;
+    row_stats(X, x, red, &mean, &rstd);
+    // groups of 8 lanes own one 32-block; the loop bound is warp-uniform so shuffles are safe
+    for (int base = (threadIdx.x & ~31) * 4; base < k; base += blockDim.x * 4) {
+      const int i = base + (threadIdx.x & 31) * 4;
+      const bool ok = i < k;
+      float4 v = ok ? load_normed(X, x, i, mean, rstd) : make_float4(0.f, 0.f, 0.f, 0.f);
+      float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+      const float d = amax / 127.f, inv = amax > 0.f ? 127.f / amax : 0.f;
+      const int q0 = __float2int_rn(v.x * inv), q1 = __float2int_rn(v.y * inv), q2 = __float2int_rn(v.z * inv), q3 = __float2int_rn(v.w * inv);
+      int s = q0 + q1 + q2 + q3;
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      if (ok) {
+        *(uint32_t*)(xq + (int64_t)b * k + i) = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
+        if ((threadIdx.x & 3) == 0) xs[(int64_t)b * (k >> 4) + (i >> 4)] = d * (float)s;
+        if ((threadIdx.x & 7) == 0) xd[(int64_t)b * (k >> 5) + (i >> 5)] = d;
+      }
+    }
+  }
+}
+
+// f32 staging for dense / generic block types: xf[B][k]
+template <int B>
+__device__ void stage_x_f32(const GemvX& X, float* xf, float* red) {
+#pragma unroll 1
+  for (int b = 0; b < B; ++b) {
+    const float* x = X.x + (int64_t)b * X.ld;
+    float mean, rstd;
+    row_stats(X, x, red, &mean, &rstd);
+    for (int i = threadIdx.x * 4; i < X.k; i += blockDim.x * 4)
+      *(float4*)(xf + (int64_t)b * X.k + i) = load_normed(X, x, i, mean, rstd);
+  }
+}
+
+// ---- row loops ---------------------------------------------------------------------------
+template <int QT, int B>
+__device__ __forceinline__ void rows_q8(const GemvSeg& S, int r0, int r1, const ActView& a, float* rowacc, int s) {
+  const int upr = dev_units_per_row(QT, S.k);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int r = r0 + warp; r < r1; r += nw) {
+    const uint8_t* row = S.W + (int64_t)r * S.stride;
+    float acc[B];
+#pragma unroll
+    for (int b = 0; b < B; ++b) acc[b] = 0.f;
+#pragma unroll 4
+    for (int u = lane; u < upr; u += 32) unit_dot<QT, B>(row, u, a, acc);
+#pragma unroll
+    for (int b = 0; b < B; ++b) acc[b] = warp_sum(acc[b]);
+    if (lane == 0) {
+#pragma unroll
+      for (int b = 0; b < B; ++b) rowacc[((r - r0) * 2 + s) * B + b] = acc[b];
+    }
+  }
+}
+
+// generic path: any block type through the plain block decoders, f32 activations
+template <int B>
+__device__ void rows_f32(const GemvSeg& S, int r0, int r1, const float* xf, float* rowacc, int s) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int be = qtype_block_elems(S.qtype), bb = qtype_block_bytes(S.qtype);
+  for (int r = r0 + warp; r < r1; r += nw) {
+    const uint8_t* row = S.W + (int64_t)r * S.stride;
+    float acc[B];
+#pragma unroll
+    for (int b = 0; b < B; ++b) acc[b] = 0.f;
+    if (be == 1) {   // dense rows: 4 elements per lane step
+      for (int i = lane * 4; i < S.k; i += 128) {
+        float w[4];
+        if (S.qtype == QT_F32) { const float4 t = *(const float4*)(row + (int64_t)i * 4); w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w; }
+        else {
+          const uint2 t = *(const uint2*)(row + (int64_t)i * 2);
+          const uint32_t h[4] = {t.x & 0xFFFFu, t.x >> 16, t.y & 0xFFFFu, t.y >> 16};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) w[j] = S.qtype == QT_F16 ? h2f(h[j]) : __uint_as_float(h[j] << 16);
+        }
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+          const float4 xv = *(const float4*)(xf + (int64_t)b * S.k + i);
+          acc[b] += w[0] * xv.x + w[1] * xv.y + w[2] * xv.z + w[3] * xv.w;
+        }
+      }
+    } else {
+      const int nblk = S.k / be;
+      for (int blk = lane; blk < nblk; blk += 32) {
+        float tmp[256];
+        dequant_block(S.qtype, row + (int64_t)blk * bb, tmp);
+        for (int b = 0; b < B; ++b) {
+          const float* xb = xf + (int64_t)b * S.k + (int64_t)blk * be;
+          float t = 0.f;
+          for (int j = 0; j < be; ++j) t += tmp[j] * xb[j];
+          acc[b] += t;
+        }
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < B; ++b) acc[b] = warp_sum(acc[b]);
+    if (lane == 0) {
+#pragma unroll
+      for (int b = 0; b < B; ++b) rowacc[((r - r0) * 2 + s) * B + b] = acc[b];
+    }
+  }
+}
+
+template <int B, bool FAST>
+__global__ void __launch_bounds__(GEMV_THREADS, (FAST && B <= 2 ? 2 : 1)) gemv_kernel(const __grid_constant__ GemvParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  int m = 0;
+  while (m + 1 < p.nmat && (int)blockIdx.x >= p.mat[m + 1].cta_begin) ++m;
+  const GemvMat& M = p.mat[m];
+  const int r0 = ((int)blockIdx.x - M.cta_begin) * M.rows_per_cta;
+  const int r1 = min(M.n, r0 + M.rows_per_cta);
+
+  // pull this CTA's weight slab towards L2 while the previous kernel drains
+  for (int s = 0; s < M.nseg; ++s) {
+    const uint8_t* base = M.seg[s].W + (int64_t)r0 * M.seg[s].stride;
+    const int64_t bytes = (int64_t)max(0, r1 - r0) * M.seg[s].stride;
+    for (int64_t off = (int64_t)threadIdx.x * 128; off < bytes; off += (int64_t)blockDim.x * 128) prefetch_l2(base + off);
+  }
+  pdl_launch_dependents();
+  pdl_wait();
+
+  // shared memory carve-up (sizes fixed by the launcher from max_k / max_rows)
+  const int kq = p.max_k;
+  constexpr bool fast = FAST;
+  int8_t* xq = (int8_t*)smem;
+  float* xd = (float*)(smem + (size_t)B * kq);
+  float* xs = xd + (size_t)B * (kq >> 5);
+  float* xf = (float*)smem;
+  const size_t act_bytes = !FAST ? (size_t)B * kq * 4 : (size_t)B * kq + (size_t)B * (kq >> 5) * 4 + (size_t)B * (kq >> 4) * 4;
+  float* red = (float*)(smem + ((act_bytes + 15) & ~(size_t)15));
+  float* rowacc = red + 40;
+
+  int staged = -1;
+  for (int s = 0; s < M.nseg; ++s) {
+    const GemvSeg& S = M.seg[s];
+    if (S.x_id != staged) {
+      __syncthreads();
+      if constexpr (fast) stage_x_q8<B>(p.xs[S.x_id], xq, xd, xs, red); else stage_x_f32<B>(p.xs[S.x_id], xf, red);
+      staged = S.x_id;
+      __syncthreads();
+    }
+    if constexpr (fast) {
+      const ActView a{xq, xd, xs, S.k};
+      switch (S.qtype) {
+        case QT_Q4_K: rows_q8<QT_Q4_K, B>(S, r0, r1, a, rowacc, s); break;
+        case QT_Q5_K: rows_q8<QT_Q5_K, B>(S, r0, r1, a, rowacc, s); break;
+        case QT_Q6_K: rows_q8<QT_Q6_K, B>(S, r0, r1, a, rowacc, s); break;
+        case QT_Q8_0: rows_q8<QT_Q8_0, B>(S, r0, r1, a, rowacc, s); break;
+        default: rows_q8<QT_Q4_0, B>(S, r0, r1, a, rowacc, s); break;
+      }
+    } else {
+      rows_f32<B>(S, r0, r1, xf, rowacc, s);
+    }
+  }
+  __syncthreads();
+
+  // epilogue
+  for (int idx = threadIdx.x; idx < (r1 - r0) * B; idx += blockDim.x) {
+    const int rl = idx / B, b = idx - rl * B, r = r0 + rl;
+    float v = rowacc[(rl * 2 + 0) * B + b];
+    if (M.nseg == 2) {
+      const float v1 = rowacc[(rl * 2 + 1) * B + b];
+      if (M.combine == COMBINE_ADD) v += v1;
+      else {
+        if (M.bias) v += M.bias[r];
+        if (M.bias2) { const float u = v1 + M.bias2[r]; v = (M.combine == COMBINE_SILU_MUL ? silu(v) : gelu_tanh(v)) * u; }
+        else v = (M.combine == COMBINE_SILU_MUL ? silu(v) : gelu_tanh(v)) * v1;
+      }
+    }
+    if (M.nseg == 1 || M.combine == COMBINE_ADD) {
+      if (M.bias) v += M.bias[r];
+      if (M.bias2) v += M.bias2[r];
+    }
+    if (M.act == ACT_GELU) v = gelu_tanh(v); else if (M.act == ACT_SILU) v = silu(v);
+    if (M.has_residual) v += p.residual[(int64_t)b * p.ld_res + r];
+    p.y[(int64_t)b * p.ldy + M.out_off + r] = v;
+  }
+}
+
+size_t gemv_smem_bytes(const GemvParams& p) {
+  const size_t B = (size_t)p.batch, kq = (size_t)p.max_k;
+  const size_t act = p.any_generic ? B * kq * 4 : B * kq + B * (kq >> 5) * 4 + B * (kq >> 4) * 4;
+  return ((act + 15) & ~(size_t)15) + 40 * 4 + (size_t)p.max_rows * 2 * B * 4;
+}
+
+template <int B, bool FAST>
+cudaError_t launch_gemv_t(const GemvParams& p, int grid, cudaStream_t stream) {
+  const size_t smem = gemv_smem_bytes(p);
+  static bool configured = false;
+  if (smem > 48 * 1024 && !configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<B, FAST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  return launch(gemv_kernel<B, FAST>, dim3(grid), dim3(GEMV_THREADS), smem, stream, p);
+}
+template <int B>
+cudaError_t launch_gemv(const GemvParams& p, int grid, cudaStream_t stream) {
+  return p.any_generic ? launch_gemv_t<B, false>(p, grid, stream) : launch_gemv_t<B, true>(p, grid, stream);
+}
+
+}  // namespace rlz
+
+extern "C" {
+
+// Returns 0 on success, a negative value for invalid parameters, or a positive cudaError_t.
+int rlz_gemv(const rlz::GemvParams* pp, void* stream) {
+  using namespace rlz;
+  GemvParams p = *pp;
+  if (p.nmat < 1 || p.nmat > GEMV_MAX_MATS || p.batch < 1 || p.batch > 4) return -1;
+  int grid = 0, max_rows = 0, max_k = 0, any_generic = 0;
+  for (int m = 0; m < p.nmat; ++m) {
+    GemvMat& M = p.mat[m];
+    if (M.nseg < 1 || M.nseg > 2 || M.n < 1 || M.rows_per_cta < 1) return -2;
+    const bool fast0 = M.seg[0].qtype == QT_Q4_K || M.seg[0].qtype == QT_Q5_K || M.seg[0].qtype == QT_Q6_K || M.seg[0].qtype == QT_Q8_0 || M.seg[0].qtype == QT_Q4_0;
+    for (int s = 0; s < M.nseg; ++s) {
+      const GemvSeg& S = M.seg[s];
+      const bool f = S.qtype == QT_Q4_K || S.qtype == QT_Q5_K || S.qtype == QT_Q6_K || S.qtype == QT_Q8_0 || S.qtype == QT_Q4_0;
+      if (f != fast0) return -3;                        // a matrix is all fast-path or all generic
+      if (!f) any_generic = 1;
+      if (m > 0 && (int)!f != any_generic) return -3;   // and so is a launch
+      if (S.x_id < 0 || S.x_id >= GEMV_MAX_X || p.xs[S.x_id].k != S.k) return -4;
+      if (S.k % 32 || (S.stride & 15) || ((uintptr_t)S.W & 15)) return -5;
+      if (qtype_block_elems(S.qtype) == 0 || S.k % qtype_block_elems(S.qtype)) return -6;
+      if (S.k > max_k) max_k = S.k;
+    }
+    M.cta_begin = grid;
+    grid += (M.n + M.rows_per_cta - 1) / M.rows_per_cta;
+    if (M.rows_per_cta > max_rows) max_rows = M.rows_per_cta;
+  }
+  p.max_k = max_k; p.max_rows = max_rows; p.any_generic = any_generic;
+  if (gemv_smem_bytes(p) > 227 * 1024) return -7;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e;
+  switch (p.batch) {
+    case 1: e = launch_gemv<1>(p, grid, st); break;
+    case 2: e = launch_gemv<2>(p, grid, st); break;
+    case 3: e = launch_gemv<3>(p, grid, st); break;
+    default: e = launch_gemv<4>(p, grid, st); break;
+  }
+  return (int)e;
+}
+
+}  // extern "C"

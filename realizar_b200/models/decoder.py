@@ -1,0 +1,343 @@
+"""GPU decoder: uploads a ``ModelWeights`` to one GPU (optionally a tensor-parallel shard of
+it) and builds the per-step launch plan of the decode kernels.
+
+Launch plan for one decode step of ``batch`` sequences (L layers):
+
+* sequential-residual models (Llama / Qwen2 / Mistral ...), 5 launches per layer:
+  ``gemv[attn_norm -> Q|K|V (+bias)]`` -> ``attn_decode[qk-norm, rope, kv append, flash-decode]``
+  -> ``gemv[o_proj + residual]`` -> ``gemv[ffn_norm -> silu(gate) * up]`` -> ``gemv[down + residual]``
+* parallel-residual models (Phi-2), 3 launches per layer:
+  ``gemv[layernorm -> QKV (+bias) | gelu(fc1 + bias)]`` -> ``attn_decode`` ->
+  ``gemv[o_proj(attn) + fc2(act) + biases + residual]``
+* then ``gemv[output_norm -> lm_head]`` and the token selection kernel.
+
+The reference's equivalent is ``transformer_layer_workspace_inner`` with ~10 launches per layer
+(src/cuda/executor/layers/gemv_dispatch.rs:53-309) and its capability gate that keeps
+LayerNorm / GELU models off the GPU (src/gguf/cuda/loading.rs:250-270); here they run on the
+same kernels.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..ops import (ACT_GELU, ACT_NONE, COMBINE_ADD, COMBINE_GELU_MUL, COMBINE_SILU_MUL, NORM_LAYER, NORM_NONE, NORM_RMS,
+                   DeviceWeight, MatOut, VecIn)
+from ..quant import BLOCK_SPECS, QType, row_bytes
+from .config import ModelConfig
+from .weights import ModelWeights, QTensor
+
+
+def _f32(t: Optional[QTensor], device) -> Optional[torch.Tensor]:
+    """Small tensors (norm weights, biases, position table) as contiguous f32 on the device."""
+    if t is None:
+        return None
+    return torch.from_numpy(np.ascontiguousarray(t.to_f32())).to(device)
+
+
+def shard_rows(t: QTensor, r0: int, r1: int) -> QTensor:
+    """Rows [r0, r1) of a stored matrix (column-parallel shard)."""
+    n, k = t.shape
+    rb = row_bytes(t.qtype, k)
+    data = t.data.reshape(-1)[r0 * rb: r1 * rb]
+    return QTensor(t.qtype, (r1 - r0, k), data)
+
+
+def shard_cols(t: QTensor, k0: int, k1: int):
+    """Columns [k0, k1) of a stored matrix (row-parallel shard).
+
+    Block types cannot be cut inside a block, so the shard keeps every block that overlaps the
+    range and silences the sub-blocks outside it by zeroing their scales (Q4_K / Q5_K: 32-wide,
+    Q6_K: 16-wide sub-blocks).  Returns ``(shard, cover_start)``: the shard multiplies the
+    activation slice ``[cover_start, cover_start + shard.k)`` whose entries outside ``[k0, k1)``
+    must be zero.
+    """
+    n, k = t.shape
+    qt = QType(t.qtype)
+    spec = BLOCK_SPECS[qt]
+    sub = {QType.Q4_K: 32, QType.Q5_K: 32, QType.Q6_K: 16}.get(qt, spec.elems)
+    if k0 % sub or k1 % sub:
+        raise ValueError(f"{qt.name} weights can only be split at multiples of {sub} columns (got {k0}:{k1})")
+    b0, b1 = k0 // spec.elems, -(-k1 // spec.elems)
+    data = t.data if isinstance(t.data, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(t.data))
+    blocks = data.reshape(n, k // spec.elems, spec.nbytes)[:, b0:b1].clone()
+    cover0 = b0 * spec.elems
+    if spec.elems == 256:
+        for bi, blk in ((0, b0), (blocks.shape[1] - 1, b1 - 1)):
+            lo, hi = blk * 256, blk * 256 + 256
+            for j in range(256 // sub):
+                s0 = lo + j * sub
+                if s0 >= k0 and s0 + sub <= k1:
+                    continue
+                if qt == QType.Q6_K:
+                    blocks[:, bi, 192 + j] = 0
+                else:                       # packed 6-bit scale / min of sub-block j
+                    sc = blocks[:, bi, 4:16]
+                    if j < 4:
+                        sc[:, j] &= 0xC0
+                        sc[:, j + 4] &= 0xC0
+                    else:
+                        sc[:, j + 4] = 0
+                        sc[:, j - 4] &= 0x3F
+                        sc[:, j] &= 0x3F
+    out = QTensor(t.qtype, (n, (b1 - b0) * spec.elems), blocks.reshape(-1))
+    return out, cover0
+
+
+@dataclass
+class LayerWeights:
+    attn_norm_w: Optional[torch.Tensor] = None
+    attn_norm_b: Optional[torch.Tensor] = None
+    ffn_norm_w: Optional[torch.Tensor] = None
+    ffn_norm_b: Optional[torch.Tensor] = None
+    q: Optional[DeviceWeight] = None
+    k: Optional[DeviceWeight] = None
+    v: Optional[DeviceWeight] = None
+    q_b: Optional[torch.Tensor] = None
+    k_b: Optional[torch.Tensor] = None
+    v_b: Optional[torch.Tensor] = None
+    o: Optional[DeviceWeight] = None
+    o_b: Optional[torch.Tensor] = None
+    gate: Optional[DeviceWeight] = None
+    up: Optional[DeviceWeight] = None
+    up_b: Optional[torch.Tensor] = None
+    down: Optional[DeviceWeight] = None
+    down_b: Optional[torch.Tensor] = None
+    q_norm_w: Optional[torch.Tensor] = None
+    k_norm_w: Optional[torch.Tensor] = None
+    o_in_off: int = 0          # offset of this rank's attention output inside the o_proj input buffer
+    down_in_off: int = 0       # same for the MLP activation inside the down-proj input buffer
+
+
+class GpuModel:
+    """Weights of one (shard of a) decoder on one GPU."""
+
+    def __init__(self, weights: ModelWeights, device="cuda", tp_rank: int = 0, tp_size: int = 1):
+        cfg = weights.config
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.tp_rank, self.tp_size = tp_rank, tp_size
+        if cfg.num_heads % tp_size or cfg.num_kv_heads % tp_size or cfg.intermediate_dim % tp_size:
+            raise ValueError(f"tensor parallel size {tp_size} must divide heads ({cfg.num_heads}), kv heads "
+                             f"({cfg.num_kv_heads}) and the FFN width ({cfg.intermediate_dim})")
+        self.heads = cfg.num_heads // tp_size
+        self.kv_heads = cfg.num_kv_heads // tp_size
+        self.q_dim, self.kv_dim = self.heads * cfg.head_dim, self.kv_heads * cfg.head_dim
+        self.inter = cfg.intermediate_dim // tp_size
+        # column of the MLP activation inside the qkv|act buffer of parallel-residual models; under TP
+        # the activation slice is surrounded by zero padding because row-parallel shards read whole blocks
+        self.act_col0 = self.q_dim + 2 * self.kv_dim + (256 if tp_size > 1 else 0)
+        dev = self.device
+        up = lambda t: ops.upload_weight(t.data, t.qtype, t.shape[0], t.shape[1], dev)
+
+        emb = weights["token_embd.weight"]
+        self.embed_qtype = int(emb.qtype)
+        self.embed_row_bytes = row_bytes(emb.qtype, cfg.hidden_dim)
+        self.embed_table = emb.torch_bytes(dev).contiguous()
+        pe = weights.get("token_pos_embd.weight")
+        self.pos_table = _f32(pe, dev)
+
+        out_w = weights.output_weight()
+        self.vocab = cfg.vocab_size
+        v_per = -(-self.vocab // tp_size)
+        self.vocab_start = tp_rank * v_per
+        self.vocab_local = max(0, min(self.vocab, self.vocab_start + v_per) - self.vocab_start)
+        self.lm_head = up(shard_rows(out_w, self.vocab_start, self.vocab_start + self.vocab_local) if tp_size > 1 else out_w)
+        ob = weights.get("output.bias")
+        self.lm_head_b = _f32(ob, dev)
+        if self.lm_head_b is not None and tp_size > 1:
+            self.lm_head_b = self.lm_head_b[self.vocab_start: self.vocab_start + self.vocab_local].contiguous()
+        self.out_norm_w = _f32(weights.get("output_norm.weight"), dev)
+        self.out_norm_b = _f32(weights.get("output_norm.bias"), dev)
+
+        self.layers: List[LayerWeights] = []
+        qd, kvd, hd = cfg.q_dim, cfg.kv_dim, cfg.head_dim
+        for l in range(cfg.num_layers):
+            p = f"blk.{l}."
+            L = LayerWeights()
+            g = lambda n: weights.get(p + n)
+            L.attn_norm_w, L.attn_norm_b = _f32(g("attn_norm.weight"), dev), _f32(g("attn_norm.bias"), dev)
+            L.ffn_norm_w, L.ffn_norm_b = _f32(g("ffn_norm.weight"), dev), _f32(g("ffn_norm.bias"), dev)
+            q0, q1 = tp_rank * self.q_dim, (tp_rank + 1) * self.q_dim
+            k0, k1 = tp_rank * self.kv_dim, (tp_rank + 1) * self.kv_dim
+            if g("attn_qkv.weight") is not None:
+                qkv, qkv_b = g("attn_qkv.weight"), _f32(g("attn_qkv.bias"), dev)
+                L.q, L.k, L.v = up(shard_rows(qkv, q0, q1)), up(shard_rows(qkv, qd + k0, qd + k1)), up(shard_rows(qkv, qd + kvd + k0, qd + kvd + k1))
+                if qkv_b is not None:
+                    L.q_b, L.k_b, L.v_b = qkv_b[q0:q1].contiguous(), qkv_b[qd + k0: qd + k1].contiguous(), qkv_b[qd + kvd + k0: qd + kvd + k1].contiguous()
+            else:
+                L.q, L.k, L.v = up(shard_rows(g("attn_q.weight"), q0, q1)), up(shard_rows(g("attn_k.weight"), k0, k1)), up(shard_rows(g("attn_v.weight"), k0, k1))
+                bq, bk, bv = _f32(g("attn_q.bias"), dev), _f32(g("attn_k.bias"), dev), _f32(g("attn_v.bias"), dev)
+                L.q_b = bq[q0:q1].contiguous() if bq is not None else None
+                L.k_b = bk[k0:k1].contiguous() if bk is not None else None
+                L.v_b = bv[k0:k1].contiguous() if bv is not None else None
+            L.q_norm_w, L.k_norm_w = _f32(g("attn_q_norm.weight"), dev), _f32(g("attn_k_norm.weight"), dev)
+            i0, i1 = tp_rank * self.inter, (tp_rank + 1) * self.inter
+            if tp_size > 1:
+                o_sh, o_cover = shard_cols(g("attn_output.weight"), q0, q1)
+                d_sh, d_cover = shard_cols(g("ffn_down.weight"), i0, i1)
+                L.o, L.o_in_off = up(o_sh), q0 - o_cover
+                L.down, L.down_in_off = up(d_sh), i0 - d_cover
+            else:
+                L.o, L.down = up(g("attn_output.weight")), up(g("ffn_down.weight"))
+            L.o_b, L.down_b = _f32(g("attn_output.bias"), dev), _f32(g("ffn_down.bias"), dev)
+            if tp_size > 1 and tp_rank != 0:       # biases of row-parallel layers are added once
+                L.o_b = L.down_b = None
+            if cfg.gated_ffn:
+                L.gate = up(shard_rows(g("ffn_gate.weight"), i0, i1))
+            L.up = up(shard_rows(g("ffn_up.weight"), i0, i1))
+            ub = _f32(g("ffn_up.bias"), dev)
+            L.up_b = ub[i0:i1].contiguous() if ub is not None else None
+            self.layers.append(L)
+
+    def weight_bytes(self) -> int:
+        tot = self.lm_head.nbytes
+        for L in self.layers:
+            for w in (L.q, L.k, L.v, L.o, L.gate, L.up, L.down):
+                if w is not None:
+                    tot += w.nbytes
+        return tot
+
+
+@dataclass
+class StepBuffers:
+    """Static device buffers of a decode step for up to ``max_batch`` sequences."""
+    tokens: torch.Tensor
+    positions: torch.Tensor
+    page_table: torch.Tensor
+    x: torch.Tensor            # residual stream [B, hidden]
+    y1: torch.Tensor           # qkv (+ MLP activation for parallel-residual models)
+    attn_out: torch.Tensor     # o_proj input (padded to the covering blocks under TP)
+    act: torch.Tensor          # down-proj input
+    partial_out: Optional[torch.Tensor]   # row-parallel partial sums awaiting the all-reduce (TP only)
+    logits: torch.Tensor
+    sampled: torch.Tensor
+    temperature: torch.Tensor
+    top_k: torch.Tensor
+    top_p: torch.Tensor
+    min_p: torch.Tensor
+    uniform: torch.Tensor
+    attn_partial: torch.Tensor
+    attn_counters: torch.Tensor
+
+
+class DecodePlan:
+    """The launch sequence of one decode step for a fixed batch size; ``run()`` issues it on
+    the current stream (eagerly or under graph capture)."""
+
+    def __init__(self):
+        self.thunks: List[Callable[[], None]] = []
+        self.keep: list = []
+        self.kernel_launches = 0
+
+    def add_gemv(self, p):
+        self.keep.append(p)
+        self.thunks.append(lambda p=p: ops.gemv_launch(p))
+        self.kernel_launches += 1
+
+    def add_attn(self, p):
+        self.keep.append(p)
+        self.thunks.append(lambda p=p: ops.attn_decode_launch(p))
+        self.kernel_launches += 1
+
+    def add(self, fn, launches=1):
+        self.thunks.append(fn)
+        self.kernel_launches += launches
+
+    def run(self):
+        for t in self.thunks:
+            t()
+
+
+def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, v_cache: torch.Tensor, batch: int, splits: int,
+                      comm=None, greedy_only: bool = False, sm_count: int = 148) -> DecodePlan:
+    """Create the launch plan for ``batch`` sequences (rows 0..batch-1 of the step buffers).
+
+    ``k_cache`` / ``v_cache`` are ``[layers, pages, kv_heads, 16, head_dim]`` bf16.  ``comm`` is the
+    tensor-parallel communicator (``None`` on one GPU); it provides ``all_reduce_sum_(tensor)``.
+    """
+    cfg = model.cfg
+    plan = DecodePlan()
+    H, hd = cfg.hidden_dim, cfg.head_dim
+    qd, kvd, I = model.q_dim, model.kv_dim, model.inter
+    norm_t = NORM_LAYER if cfg.uses_layernorm else NORM_RMS
+    tp = model.tp_size > 1
+    target = 2 * sm_count if batch <= 2 else sm_count
+    chunks = [(c, min(4, batch - c)) for c in range(0, batch, 4)]       # GEMV kernels take <= 4 rows at a time
+    qkv_w = qd + 2 * kvd
+    ld1 = buf.y1.stride(0)
+
+    plan.add(lambda: ops.embed(model.embed_table, model.embed_qtype, model.embed_row_bytes, H, cfg.vocab_size, buf.tokens[:batch], buf.x,
+                               model.pos_table, buf.positions))
+
+    def reduce_into_x(partial_rows):
+        """TP: x += all_reduce(partial).  The residual add is one fused elementwise launch."""
+        comm.all_reduce_sum_(partial_rows)
+        ops.elementwise(partial_rows, residual=buf.x[:batch], out=buf.x[:batch])
+
+    for l, L in enumerate(model.layers):
+        kc, vc = k_cache[l], v_cache[l]
+        for c0, cb in chunks:
+            x = buf.x[c0:]
+            xin = VecIn(x, H, ld=buf.x.stride(0), norm=norm_t, norm_w=L.attn_norm_w, norm_b=L.attn_norm_b, eps=cfg.eps)
+            mats = [MatOut([(L.q, 0)], out_off=0, bias=L.q_b), MatOut([(L.k, 0)], out_off=qd, bias=L.k_b),
+                    MatOut([(L.v, 0)], out_off=qd + kvd, bias=L.v_b)]
+            if cfg.parallel_residual:
+                mats.append(MatOut([(L.up, 0)], out_off=model.act_col0 + L.down_in_off, bias=L.up_b, act=ACT_GELU if cfg.constraints.activation == "gelu" else ops.ACT_SILU))
+            plan.add_gemv(ops.build_gemv_params([xin], mats, buf.y1[c0:], cb, ldy=ld1, target_ctas=target))
+        plan.add_attn(ops.build_attn_decode_params(
+            buf.y1, buf.attn_out[:, L.o_in_off:], kc, vc, buf.positions, buf.page_table, buf.attn_partial, buf.attn_counters,
+            model.heads, model.kv_heads, hd, splits, batch, cfg.rope_dim if cfg.uses_rope else 0, cfg.rope_type, cfg.rope_theta,
+            0, qd, qd + kvd, L.q_norm_w, L.k_norm_w, cfg.eps, ld_qkv=ld1, ld_out=buf.attn_out.stride(0)))
+        if cfg.parallel_residual:
+            for c0, cb in chunks:
+                a_in = VecIn(buf.attn_out[c0:], L.o.k, ld=buf.attn_out.stride(0))
+                m_in = VecIn(buf.y1[c0:, model.act_col0:], L.down.k, ld=ld1)
+                mat = MatOut([(L.o, 0), (L.down, 1)], bias=L.o_b, bias2=L.down_b, combine=COMBINE_ADD, residual=not tp)
+                dst = buf.partial_out if tp else buf.x
+                plan.add_gemv(ops.build_gemv_params([a_in, m_in], [mat], dst[c0:], cb, ldy=dst.stride(0), residual=None if tp else buf.x[c0:],
+                                                    ld_res=buf.x.stride(0), target_ctas=target))
+            if tp:
+                plan.add(lambda: reduce_into_x(buf.partial_out[:batch]), launches=1)
+        else:
+            for c0, cb in chunks:
+                a_in = VecIn(buf.attn_out[c0:], L.o.k, ld=buf.attn_out.stride(0))
+                dst = buf.partial_out if tp else buf.x
+                plan.add_gemv(ops.build_gemv_params([a_in], [MatOut([(L.o, 0)], bias=L.o_b, residual=not tp)], dst[c0:], cb, ldy=dst.stride(0),
+                                                    residual=None if tp else buf.x[c0:], ld_res=buf.x.stride(0), target_ctas=target))
+            if tp:
+                plan.add(lambda: reduce_into_x(buf.partial_out[:batch]), launches=1)
+            for c0, cb in chunks:
+                xin = VecIn(buf.x[c0:], H, ld=buf.x.stride(0), norm=norm_t, norm_w=L.ffn_norm_w, norm_b=L.ffn_norm_b, eps=cfg.eps)
+                if cfg.gated_ffn:
+                    comb = COMBINE_SILU_MUL if cfg.constraints.activation == "silu" else COMBINE_GELU_MUL
+                    mat = MatOut([(L.gate, 0), (L.up, 0)], combine=comb, bias2=L.up_b)
+                else:
+                    mat = MatOut([(L.up, 0)], bias=L.up_b, act=ACT_GELU if cfg.constraints.activation == "gelu" else ops.ACT_SILU)
+                plan.add_gemv(ops.build_gemv_params([xin], [mat], buf.act[c0:, L.down_in_off:], cb, ldy=buf.act.stride(0), target_ctas=target))
+            for c0, cb in chunks:
+                d_in = VecIn(buf.act[c0:], L.down.k, ld=buf.act.stride(0))
+                dst = buf.partial_out if tp else buf.x
+                plan.add_gemv(ops.build_gemv_params([d_in], [MatOut([(L.down, 0)], bias=L.down_b, residual=not tp)], dst[c0:], cb, ldy=dst.stride(0),
+                                                    residual=None if tp else buf.x[c0:], ld_res=buf.x.stride(0), target_ctas=target))
+            if tp:
+                plan.add(lambda: reduce_into_x(buf.partial_out[:batch]), launches=1)
+
+    for c0, cb in chunks:
+        xin = VecIn(buf.x[c0:], H, ld=buf.x.stride(0), norm=norm_t, norm_w=model.out_norm_w, norm_b=model.out_norm_b, eps=cfg.eps)
+        plan.add_gemv(ops.build_gemv_params([xin], [MatOut([(model.lm_head, 0)], bias=model.lm_head_b)], buf.logits[c0:], cb,
+                                            ldy=buf.logits.stride(0), target_ctas=2 * sm_count))
+    if tp:
+        plan.add(lambda: comm.gather_logits_(buf.logits[:batch], model), launches=0)
+    if greedy_only:
+        plan.add(lambda: ops.argmax(buf.logits[:batch], out=buf.sampled, vocab=cfg.vocab_size))
+    else:
+        sp = ops.build_sample_params(buf.logits[:batch], buf.temperature, buf.top_k, buf.top_p, buf.uniform, buf.sampled, buf.min_p,
+                                     vocab=cfg.vocab_size)
+        plan.keep.append(sp)
+        plan.add(lambda: ops.sample_launch(sp))
+    return plan

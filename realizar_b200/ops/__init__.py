@@ -1,0 +1,275 @@
+"""Python entry points of the sm_100a kernels (``librlz_cuda.so``).
+
+Every wrapper launches on the current torch CUDA stream, so calls compose with torch ops and
+can be captured into CUDA graphs.  There is no fallback implementation: if the native library
+is missing on a GPU host the import of :func:`lib` raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import torch
+
+from .._native import cuda_lib
+from ..quant import QType
+from ..quant.device_layout import dev_row_bytes, to_device_layout
+from . import _signatures as S
+from ._signatures import (ACT_GELU, ACT_NONE, ACT_SILU, COMBINE_ADD, COMBINE_GELU_MUL, COMBINE_SILU_MUL, NORM_LAYER,
+                          NORM_NONE, NORM_RMS)
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib():
+    return cuda_lib()
+
+
+def check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    if rc > 0:
+        msg = lib().rlz_cuda_error_string(rc).decode()
+        raise KernelError(f"{what}: CUDA error {rc} ({msg})")
+    raise KernelError(f"{what}: invalid arguments (code {rc})")
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def launch_count() -> int:
+    return int(lib().rlz_launch_count())
+
+
+def set_pdl(on: bool) -> None:
+    lib().rlz_set_pdl(1 if on else 0)
+
+
+# ------------------------------------------------------------------------------ weights ----
+@dataclass
+class DeviceWeight:
+    """A weight matrix resident on the GPU in the device layout of its block type."""
+    data: torch.Tensor      # uint8 [n, stride]
+    qtype: int
+    n: int
+    k: int
+
+    @property
+    def stride(self) -> int:
+        return self.data.stride(0)
+
+    @property
+    def nbytes(self) -> int:
+        return self.data.numel()
+
+    def rows(self, r0: int, r1: int) -> "DeviceWeight":
+        return DeviceWeight(self.data[r0:r1], self.qtype, r1 - r0, self.k)
+
+
+def upload_weight(data, qtype: int, n: int, k: int, device) -> DeviceWeight:
+    """Stored block bytes (numpy or torch uint8, flat) -> device layout on ``device``."""
+    t = data if isinstance(data, torch.Tensor) else torch.from_numpy(data)
+    t = t.to(device, non_blocking=True).reshape(-1)
+    dev = to_device_layout(t, qtype, n, k).contiguous()
+    assert dev.shape == (n, dev_row_bytes(qtype, k)), (dev.shape, n, dev_row_bytes(qtype, k))
+    return DeviceWeight(dev, int(qtype), n, k)
+
+
+# ------------------------------------------------------------------------------ GEMV -------
+@dataclass
+class VecIn:
+    """Input vector(s) ``[batch, k]`` (row stride ``ld``) with an optional fused norm."""
+    x: torch.Tensor
+    k: int
+    ld: Optional[int] = None
+    norm: int = NORM_NONE
+    norm_w: Optional[torch.Tensor] = None
+    norm_b: Optional[torch.Tensor] = None
+    eps: float = 1e-5
+
+
+@dataclass
+class MatOut:
+    """A block of output rows: one or two (weight, input index) pairs and an epilogue."""
+    segs: Sequence[tuple]                  # [(DeviceWeight, x_index), ...]
+    out_off: int = 0
+    bias: Optional[torch.Tensor] = None
+    bias2: Optional[torch.Tensor] = None
+    combine: int = COMBINE_ADD
+    act: int = ACT_NONE
+    residual: bool = False
+    rows_per_cta: int = 0                  # 0 = choose automatically
+
+
+def plan_rows_per_cta(mats: Sequence[MatOut], target_ctas: int) -> List[int]:
+    total = sum(sum(w.nbytes for w, _ in m.segs) for m in mats) or 1
+    out = []
+    for m in mats:
+        n = m.segs[0][0].n
+        share = sum(w.nbytes for w, _ in m.segs) / total
+        ctas = max(1, round(target_ctas * share))
+        rpc = max(1, -(-n // ctas))
+        out.append(min(rpc, 1024))
+    return out
+
+
+def build_gemv_params(xs: Sequence[VecIn], mats: Sequence[MatOut], y: torch.Tensor, batch: int, ldy: Optional[int] = None,
+                      residual: Optional[torch.Tensor] = None, ld_res: Optional[int] = None, target_ctas: int = 296) -> S.GemvParams:
+    """Fill a parameter block.  The caller keeps every referenced tensor alive."""
+    if not (1 <= len(mats) <= S.GEMV_MAX_MATS and 1 <= len(xs) <= S.GEMV_MAX_X):
+        raise ValueError("a GEMV launch takes 1..4 matrices and 1..4 inputs")
+    p = S.GemvParams()
+    auto = plan_rows_per_cta(mats, target_ctas)
+    for i, v in enumerate(xs):
+        X = p.xs[i]
+        X.x, X.nw, X.nb = v.x.data_ptr(), ptr(v.norm_w), ptr(v.norm_b)
+        X.ld = v.ld if v.ld is not None else v.x.stride(0) if v.x.dim() > 1 else v.k
+        X.k, X.norm, X.eps = v.k, v.norm, v.eps
+    for i, m in enumerate(mats):
+        M = p.mat[i]
+        M.nseg = len(m.segs)
+        for s, (w, xi) in enumerate(m.segs):
+            seg = M.seg[s]
+            seg.W, seg.stride, seg.qtype, seg.k, seg.x_id = w.data.data_ptr(), w.stride, w.qtype, w.k, xi
+            if xs[xi].k != w.k:
+                raise ValueError(f"matrix {i} segment {s}: k={w.k} but input {xi} has k={xs[xi].k}")
+        M.bias, M.bias2 = ptr(m.bias), ptr(m.bias2)
+        M.combine, M.act, M.has_residual = m.combine, m.act, 1 if m.residual else 0
+        M.n, M.out_off = m.segs[0][0].n, m.out_off
+        M.rows_per_cta = m.rows_per_cta or auto[i]
+    p.nmat, p.batch = len(mats), batch
+    p.y, p.ldy = y.data_ptr(), ldy if ldy is not None else (y.stride(0) if y.dim() > 1 else y.numel())
+    p.residual = ptr(residual)
+    p.ld_res = ld_res if ld_res is not None else (residual.stride(0) if residual is not None and residual.dim() > 1 else 0)
+    return p
+
+
+def gemv_launch(p: S.GemvParams) -> None:
+    check(lib().rlz_gemv(ctypes.byref(p), stream_ptr()), "gemv")
+
+
+def gemv(w: DeviceWeight, x: torch.Tensor, bias=None, act=ACT_NONE, residual=None, norm=NORM_NONE, norm_w=None, norm_b=None,
+         eps=1e-5) -> torch.Tensor:
+    """``y = act(W norm(x) + bias) + residual`` for ``x`` of shape ``[batch<=4, k]`` (convenience form)."""
+    x2 = x.reshape(-1, w.k).contiguous().float()
+    batch = x2.shape[0]
+    y = torch.empty(batch, w.n, device=x.device, dtype=torch.float32)
+    res = residual.reshape(batch, w.n).contiguous().float() if residual is not None else None
+    p = build_gemv_params([VecIn(x2, w.k, norm=norm, norm_w=norm_w, norm_b=norm_b, eps=eps)],
+                          [MatOut([(w, 0)], bias=bias, act=act, residual=res is not None)], y, batch, residual=res)
+    gemv_launch(p)
+    return y.reshape(*x.shape[:-1], w.n)
+
+
+# ------------------------------------------------------------------------------ attention --
+def attn_decode_scratch(batch: int, n_heads: int, splits: int, head_dim: int, device):
+    partial = torch.empty(int(lib().rlz_attn_decode_partial_floats(batch, n_heads, splits, head_dim)), device=device, dtype=torch.float32)
+    counters = torch.zeros(int(lib().rlz_attn_decode_counter_ints(batch, n_heads)), device=device, dtype=torch.int32)
+    return partial, counters
+
+
+def build_attn_decode_params(qkv, out, k_cache, v_cache, positions, page_table, partial, counters, n_heads, n_kv_heads, head_dim,
+                             splits, batch, rope_dim, rope_type, rope_theta, q_off, k_off, v_off, q_norm_w=None, k_norm_w=None,
+                             eps=1e-6, ld_qkv=None, ld_out=None) -> S.AttnDecodeParams:
+    p = S.AttnDecodeParams()
+    p.qkv, p.out, p.k_cache, p.v_cache = qkv.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr()
+    p.positions, p.page_table = positions.data_ptr(), page_table.data_ptr()
+    p.q_norm_w, p.k_norm_w = ptr(q_norm_w), ptr(k_norm_w)
+    p.partial, p.counters = partial.data_ptr(), counters.data_ptr()
+    p.ld_qkv = ld_qkv if ld_qkv is not None else qkv.stride(0)
+    p.ld_out = ld_out if ld_out is not None else out.stride(0)
+    p.n_heads, p.n_kv_heads, p.head_dim, p.max_pages = n_heads, n_kv_heads, head_dim, page_table.shape[-1]
+    p.rope_dim, p.rope_type, p.splits, p.batch = rope_dim, rope_type, splits, batch
+    p.q_off, p.k_off, p.v_off = q_off, k_off, v_off
+    p.rope_theta, p.eps, p.scale = rope_theta, eps, head_dim ** -0.5
+    return p
+
+
+def attn_decode_launch(p: S.AttnDecodeParams) -> None:
+    check(lib().rlz_attn_decode(ctypes.byref(p), stream_ptr()), "attn_decode")
+
+
+# ------------------------------------------------------------------------------ small ops --
+def embed(table: torch.Tensor, qtype: int, row_bytes: int, hidden: int, vocab: int, tokens: torch.Tensor, out: torch.Tensor,
+          pos_table: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None) -> None:
+    check(lib().rlz_embed(table.data_ptr(), int(qtype), row_bytes, hidden, vocab, tokens.data_ptr(), tokens.numel(), ptr(pos_table),
+                          ptr(positions), out.data_ptr(), out.stride(0), stream_ptr()), "embed")
+
+
+def norm(x: torch.Tensor, w=None, b=None, norm_type=NORM_RMS, eps=1e-5, residual=None, sum_out=None) -> torch.Tensor:
+    x2 = x.reshape(-1, x.shape[-1])
+    y = torch.empty_like(x2)
+    check(lib().rlz_norm(x2.data_ptr(), ptr(residual), ptr(w), ptr(b), y.data_ptr(), ptr(sum_out), x2.shape[0], x2.shape[1], x2.stride(0),
+                         norm_type, eps, stream_ptr()), "norm")
+    return y.reshape(x.shape)
+
+
+def head_rmsnorm_(x: torch.Tensor, w: torch.Tensor, heads: int, d: int, eps: float) -> None:
+    check(lib().rlz_head_rmsnorm(x.data_ptr(), w.data_ptr(), x.shape[0], heads, d, x.stride(0), eps, stream_ptr()), "head_rmsnorm")
+
+
+def rope_(x: torch.Tensor, positions: torch.Tensor, heads: int, d: int, rope_dim: int, rope_type: int, theta: float) -> None:
+    """In-place RoPE on ``x [T, >= heads*d]`` (row stride taken from the tensor)."""
+    check(lib().rlz_rope(x.data_ptr(), positions.data_ptr(), x.shape[0], heads, d, x.stride(0), rope_dim, rope_type, theta, stream_ptr()), "rope")
+
+
+def elementwise(a: torch.Tensor, b=None, bias=None, residual=None, act=ACT_NONE, out=None) -> torch.Tensor:
+    """``act(a + bias) [* b] [+ residual]`` over 2-D views."""
+    a2 = a.reshape(-1, a.shape[-1])
+    y = out if out is not None else torch.empty(a2.shape, device=a.device, dtype=torch.float32)
+    y2 = y.reshape(-1, y.shape[-1])
+    b2 = b.reshape(-1, b.shape[-1]) if b is not None else None
+    check(lib().rlz_elementwise(a2.data_ptr(), ptr(b2), ptr(bias), ptr(residual), y2.data_ptr(), a2.shape[0], a2.shape[1], a2.stride(0),
+                                b2.stride(0) if b2 is not None else 0, y2.stride(0), act, 1 if b is not None else 0, stream_ptr()), "elementwise")
+    return y.reshape(a.shape) if out is None else y
+
+
+def kv_append(k, v, k_cache, v_cache, positions, page_rows, n_kv_heads, d, page=16) -> None:
+    check(lib().rlz_kv_append(k.data_ptr(), v.data_ptr(), k.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(),
+                              page_rows.data_ptr(), k.shape[0], n_kv_heads, d, page, stream_ptr()), "kv_append")
+
+
+def advance_(tokens: torch.Tensor, sampled: torch.Tensor, positions: torch.Tensor) -> None:
+    check(lib().rlz_advance(tokens.data_ptr(), sampled.data_ptr(), positions.data_ptr(), tokens.numel(), stream_ptr()), "advance")
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, out_val: Optional[torch.Tensor] = None, index_offset: int = 0,
+           vocab: Optional[int] = None) -> torch.Tensor:
+    l2 = logits.reshape(-1, logits.shape[-1])
+    if out is None:
+        out = torch.empty(l2.shape[0], device=logits.device, dtype=torch.int32)
+    check(lib().rlz_argmax(l2.data_ptr(), l2.stride(0), vocab or l2.shape[1], l2.shape[0], out.data_ptr(), ptr(out_val), index_offset, stream_ptr()), "argmax")
+    return out
+
+
+def build_sample_params(logits, temperature, top_k, top_p, uniform, out, min_p=None, out_logprob=None, vocab=None) -> S.SampleParams:
+    p = S.SampleParams()
+    l2 = logits.reshape(-1, logits.shape[-1])
+    p.logits, p.ld, p.vocab, p.batch = l2.data_ptr(), l2.stride(0), vocab or l2.shape[1], l2.shape[0]
+    p.temperature, p.top_k, p.top_p, p.min_p = temperature.data_ptr(), top_k.data_ptr(), top_p.data_ptr(), ptr(min_p)
+    p.uniform, p.out, p.out_logprob = uniform.data_ptr(), out.data_ptr(), ptr(out_logprob)
+    return p
+
+
+def sample_launch(p: S.SampleParams) -> None:
+    check(lib().rlz_sample(ctypes.byref(p), stream_ptr()), "sample")
+
+
+def sample(logits, temperature, top_k, top_p, uniform, min_p=None) -> torch.Tensor:
+    out = torch.empty(logits.reshape(-1, logits.shape[-1]).shape[0], device=logits.device, dtype=torch.int32)
+    sample_launch(build_sample_params(logits, temperature, top_k, top_p, uniform, out, min_p))
+    return out
+
+
+def penalties_(logits, history, repetition=None, presence=None, frequency=None) -> None:
+    l2 = logits.reshape(-1, logits.shape[-1])
+    check(lib().rlz_penalties(l2.data_ptr(), l2.stride(0), l2.shape[1], l2.shape[0], history.data_ptr(), history.shape[-1], ptr(repetition),
+                              ptr(presence), ptr(frequency), stream_ptr()), "penalties")

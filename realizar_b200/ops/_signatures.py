@@ -1,0 +1,76 @@
+"""ctypes mirrors of the parameter blocks in ``csrc/kernels`` and the argument types of every
+exported launcher of ``librlz_cuda.so``."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_float, c_int, c_int32, c_int64, c_longlong, c_void_p
+
+GEMV_MAX_MATS = 4
+GEMV_MAX_X = 4
+
+ACT_NONE, ACT_GELU, ACT_SILU = 0, 1, 2
+COMBINE_ADD, COMBINE_SILU_MUL, COMBINE_GELU_MUL = 0, 1, 2
+NORM_NONE, NORM_RMS, NORM_LAYER = 0, 1, 2
+
+
+class GemvSeg(Structure):
+    _fields_ = [("W", c_void_p), ("stride", c_int64), ("qtype", c_int32), ("k", c_int32), ("x_id", c_int32), ("_pad", c_int32)]
+
+
+class GemvMat(Structure):
+    _fields_ = [("seg", GemvSeg * 2), ("bias", c_void_p), ("bias2", c_void_p), ("nseg", c_int32), ("combine", c_int32),
+                ("n", c_int32), ("out_off", c_int32), ("act", c_int32), ("has_residual", c_int32), ("rows_per_cta", c_int32),
+                ("cta_begin", c_int32)]
+
+
+class GemvX(Structure):
+    _fields_ = [("x", c_void_p), ("nw", c_void_p), ("nb", c_void_p), ("ld", c_int64), ("k", c_int32), ("norm", c_int32),
+                ("eps", c_float), ("_pad", c_int32)]
+
+
+class GemvParams(Structure):
+    _fields_ = [("mat", GemvMat * GEMV_MAX_MATS), ("xs", GemvX * GEMV_MAX_X), ("y", c_void_p), ("residual", c_void_p),
+                ("ldy", c_int64), ("ld_res", c_int64), ("nmat", c_int32), ("batch", c_int32), ("max_k", c_int32),
+                ("max_rows", c_int32), ("any_generic", c_int32), ("_pad", c_int32)]
+
+
+class AttnDecodeParams(Structure):
+    _fields_ = [("qkv", c_void_p), ("out", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p), ("positions", c_void_p),
+                ("page_table", c_void_p), ("q_norm_w", c_void_p), ("k_norm_w", c_void_p), ("partial", c_void_p),
+                ("counters", c_void_p), ("ld_qkv", c_int64), ("ld_out", c_int64), ("n_heads", c_int32), ("n_kv_heads", c_int32),
+                ("head_dim", c_int32), ("max_pages", c_int32), ("rope_dim", c_int32), ("rope_type", c_int32), ("splits", c_int32),
+                ("batch", c_int32), ("q_off", c_int32), ("k_off", c_int32), ("v_off", c_int32), ("_pad", c_int32),
+                ("rope_theta", c_float), ("eps", c_float), ("scale", c_float), ("_padf", c_float)]
+
+
+class SampleParams(Structure):
+    _fields_ = [("logits", c_void_p), ("ld", c_int64), ("vocab", c_int32), ("batch", c_int32), ("temperature", c_void_p),
+                ("top_k", c_void_p), ("top_p", c_void_p), ("min_p", c_void_p), ("uniform", c_void_p), ("out", c_void_p),
+                ("out_logprob", c_void_p)]
+
+
+def declare(lib: ctypes.CDLL) -> None:
+    lib.rlz_launch_count.restype = c_longlong
+    lib.rlz_set_pdl.argtypes = [c_int]
+    lib.rlz_device_info.argtypes = [c_int, POINTER(c_int), POINTER(c_longlong)]
+    lib.rlz_cuda_error_string.argtypes = [c_int]
+    lib.rlz_cuda_error_string.restype = ctypes.c_char_p
+    lib.rlz_gemv.argtypes = [POINTER(GemvParams), c_void_p]
+    lib.rlz_attn_decode.argtypes = [POINTER(AttnDecodeParams), c_void_p]
+    lib.rlz_attn_decode_partial_floats.argtypes = [c_int, c_int, c_int, c_int]
+    lib.rlz_attn_decode_partial_floats.restype = c_longlong
+    lib.rlz_attn_decode_counter_ints.argtypes = [c_int, c_int]
+    lib.rlz_attn_decode_counter_ints.restype = c_longlong
+    lib.rlz_embed.argtypes = [c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p]
+    lib.rlz_norm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_int, c_float, c_void_p]
+    lib.rlz_head_rmsnorm.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_float, c_void_p]
+    lib.rlz_rope.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_int, c_int, c_float, c_void_p]
+    lib.rlz_elementwise.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_longlong,
+                                    c_longlong, c_int, c_int, c_void_p]
+    lib.rlz_kv_append.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+    lib.rlz_advance.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+    lib.rlz_argmax.argtypes = [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
+    lib.rlz_sample.argtypes = [POINTER(SampleParams), c_void_p]
+    lib.rlz_penalties.argtypes = [c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+    for name in ("rlz_gemm_kquant", "rlz_attn_prefill", "rlz_flash_decode_static", "rlz_symm_alloc"):
+        pass  # declared by their own modules when present

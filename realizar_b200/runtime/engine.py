@@ -1,0 +1,284 @@
+"""Decode engine: static step buffers, the paged KV cache on the device, CUDA-graph capture of
+the decode step per batch-size bucket, and slot-level sequence management.
+
+One engine instance drives one GPU (one tensor-parallel rank).  The host never touches
+activations: a step consumes ``tokens`` / ``positions`` / ``page_table`` that live on the
+device and produces ``sampled`` token ids there; the streaming loop moves 4-byte ids through
+pinned memory.
+
+Capability parity with the reference's graph-captured decode (indirect position / seq_len
+buffers, per-batch-size graphs; src/cuda/executor/layers/graphed_capture.rs:16-364,
+src/cuda/executor/layers/forward_graphed_decode.rs:18-211) and with its batched decode state
+(src/gguf/cuda/generate_batched_streaming.rs:8-660).
+"""
+from __future__ import annotations
+
+import logging
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..models.decoder import DecodePlan, GpuModel, StepBuffers, build_decode_plan
+from ..models.weights import ModelWeights
+from .paged_kv import PagedKvCache
+
+log = logging.getLogger("realizar_b200.engine")
+
+PAGE = 16
+
+
+@dataclass
+class EngineConfig:
+    max_batch: int = 4
+    max_seq_len: int = 2048
+    num_pages: Optional[int] = None        # default: enough for max_batch full-length sequences
+    cuda_graphs: bool = True
+    pdl: bool = True                       # programmatic dependent launch between kernels
+    attn_splits: int = 0                   # 0 = choose from the SM count
+    greedy_only: bool = False              # compile plans with argmax instead of the sampling kernel
+    batch_buckets: Sequence[int] = ()      # graph buckets; default powers of two up to max_batch
+    seed: int = 0
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    min_p: float = 0.0
+    max_tokens: int = 64
+    stop_token_ids: Sequence[int] = ()
+    seed: Optional[int] = None
+
+
+@dataclass
+class Slot:
+    seq_id: int = -1
+    active: bool = False
+    position: int = -1          # position of the token fed in the next step
+    n_pages: int = 0
+
+
+class DecodeEngine:
+    def __init__(self, weights: ModelWeights, config: Optional[EngineConfig] = None, device="cuda", comm=None,
+                 tp_rank: int = 0, tp_size: int = 1):
+        self.cfg = config or EngineConfig()
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("DecodeEngine runs on a CUDA device; use models.cpu_model.CpuModel on the CPU")
+        self.comm = comm
+        self.model = GpuModel(weights, self.device, tp_rank, tp_size)
+        self.mcfg = self.model.cfg
+        m, c, dev = self.model, self.cfg, self.device
+        props = torch.cuda.get_device_properties(self.device)
+        self.sm_count = props.multi_processor_count
+        B = c.max_batch
+        self.max_pages_per_seq = -(-c.max_seq_len // PAGE)
+        self.num_pages = c.num_pages or B * self.max_pages_per_seq
+        hd = self.mcfg.head_dim
+        # [2 (k,v), layers, pages, kv_heads, PAGE, head_dim] bf16
+        self.kv = torch.zeros(2, self.mcfg.num_layers, self.num_pages, m.kv_heads, PAGE, hd, device=dev, dtype=torch.bfloat16)
+        self.pages = PagedKvCache(self.num_pages, PAGE)
+        self.splits = c.attn_splits or self._choose_splits(B)
+        qkv_w = m.q_dim + 2 * m.kv_dim
+        o_k = max(L.o.k for L in m.layers)
+        d_k = max(L.down.k for L in m.layers)
+        y1_w = (m.act_col0 + d_k + 256) if self.mcfg.parallel_residual else qkv_w
+        z = lambda *s, dt=torch.float32: torch.zeros(*s, device=dev, dtype=dt)
+        part, ctr = ops.attn_decode_scratch(B, m.heads, self.splits, hd, dev)
+        self.buf = StepBuffers(
+            tokens=z(B, dt=torch.int32), positions=torch.full((B,), -1, device=dev, dtype=torch.int32),
+            page_table=z(B, self.max_pages_per_seq, dt=torch.int32), x=z(B, self.mcfg.hidden_dim), y1=z(B, y1_w),
+            attn_out=z(B, o_k), act=z(B, d_k + 256), partial_out=z(B, self.mcfg.hidden_dim) if tp_size > 1 else None,
+            logits=z(B, m.vocab_local if tp_size > 1 else self.mcfg.vocab_size), sampled=z(B, dt=torch.int32),
+            temperature=z(B), top_k=z(B, dt=torch.int32), top_p=torch.ones(B, device=dev), min_p=z(B), uniform=z(B),
+            attn_partial=part, attn_counters=ctr)
+        self.slots = [Slot() for _ in range(B)]
+        self.buckets = sorted(set(c.batch_buckets or [b for b in (1, 2, 4, 8, 16, 32, 64, 128) if b < B] + [B]))
+        self._plans: Dict[int, DecodePlan] = {}
+        self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self._gen = torch.Generator(device=dev).manual_seed(c.seed)
+        # pinned staging for the streaming loop
+        self._h_tokens = torch.zeros(B, dtype=torch.int32).pin_memory()
+        self._h_positions = torch.full((B,), -1, dtype=torch.int32).pin_memory()
+        self._h_sampled = torch.zeros(B, dtype=torch.int32).pin_memory()
+        self._h_table = torch.zeros(B, self.max_pages_per_seq, dtype=torch.int32).pin_memory()
+        self._next_seq = 0
+        self.pdl = c.pdl
+        ops.set_pdl(self.pdl)
+        self.steps_run = 0
+
+    # -- configuration helpers --------------------------------------------------------------
+    def _choose_splits(self, batch: int) -> int:
+        ctas_per_split = self.model.kv_heads * max(1, batch)
+        want = max(1, (2 * self.sm_count) // max(1, ctas_per_split))
+        return int(min(32, want))
+
+    def bucket_for(self, batch: int) -> int:
+        for b in self.buckets:
+            if b >= batch:
+                return b
+        raise ValueError(f"batch {batch} exceeds max_batch {self.cfg.max_batch}")
+
+    # -- plans and graphs -------------------------------------------------------------------
+    def plan(self, bucket: int) -> DecodePlan:
+        if bucket not in self._plans:
+            self._plans[bucket] = build_decode_plan(self.model, self.buf, self.kv[0], self.kv[1], bucket, self.splits, self.comm,
+                                                    self.cfg.greedy_only, self.sm_count)
+        return self._plans[bucket]
+
+    def kernels_per_step(self, bucket: int) -> int:
+        return self.plan(bucket).kernel_launches
+
+    def _capture(self, bucket: int) -> Optional[torch.cuda.CUDAGraph]:
+        plan = self.plan(bucket)
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            plan.run()                      # warm-up outside capture (sets kernel attributes, loads modules)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize(self.device)
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                plan.run()
+            return g
+        except Exception as e:  # pragma: no cover - depends on driver support
+            if self.pdl:
+                log.warning("graph capture with programmatic dependent launch failed (%s); retrying without it", e)
+                self.pdl = False
+                ops.set_pdl(False)
+                torch.cuda.synchronize(self.device)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    plan.run()
+                return g
+            raise
+
+    def run_step(self, batch: int) -> None:
+        """Issue one decode step for slots ``0..batch-1`` on the current stream."""
+        bucket = self.bucket_for(batch)
+        if self.cfg.cuda_graphs:
+            g = self._graphs.get(bucket)
+            if g is None:
+                g = self._graphs[bucket] = self._capture(bucket)
+            g.replay()
+        else:
+            self.plan(bucket).run()
+        self.steps_run += 1
+
+    def advance(self, batch: int) -> None:
+        """Device-side feedback: sampled tokens become the next inputs, positions move on."""
+        ops.advance_(self.buf.tokens[:batch], self.buf.sampled[:batch], self.buf.positions[:batch])
+
+    # -- slots ---------------------------------------------------------------------------------
+    def free_slots(self) -> List[int]:
+        return [i for i, s in enumerate(self.slots) if not s.active]
+
+    def open_slot(self, slot: int, reserve_tokens: int) -> int:
+        """Bind a new sequence to ``slot`` and reserve KV pages for ``reserve_tokens`` tokens."""
+        s = self.slots[slot]
+        if s.active:
+            raise RuntimeError(f"slot {slot} is busy")
+        if reserve_tokens > self.cfg.max_seq_len:
+            raise ValueError(f"sequence of {reserve_tokens} tokens exceeds max_seq_len {self.cfg.max_seq_len}")
+        seq_id = self._next_seq
+        self._next_seq += 1
+        self.pages.add_sequence(seq_id)
+        s.seq_id, s.active, s.position, s.n_pages = seq_id, True, 0, 0
+        self._ensure_pages(slot, reserve_tokens)
+        return seq_id
+
+    def _ensure_pages(self, slot: int, length: int) -> None:
+        s = self.slots[slot]
+        pages = self.pages.reserve(s.seq_id, length)
+        if len(pages) != s.n_pages:
+            row = self._h_table[slot]
+            row[: len(pages)] = torch.tensor(pages, dtype=torch.int32)
+            self.buf.page_table[slot].copy_(row, non_blocking=True)
+            s.n_pages = len(pages)
+
+    def close_slot(self, slot: int) -> None:
+        s = self.slots[slot]
+        if not s.active:
+            return
+        self.pages.free_sequence(s.seq_id)
+        s.active, s.seq_id, s.position, s.n_pages = False, -1, -1, 0
+        self._h_positions[slot] = -1
+        self.buf.positions[slot: slot + 1].fill_(-1)
+
+    def set_sampling(self, slot: int, sp: SamplingParams) -> None:
+        b = self.buf
+        b.temperature[slot] = float(sp.temperature)
+        b.top_k[slot] = int(sp.top_k)
+        b.top_p[slot] = float(sp.top_p)
+        b.min_p[slot] = float(sp.min_p)
+
+    # -- single-token feeding ------------------------------------------------------------------
+    def feed(self, slot_tokens: Dict[int, int]) -> torch.Tensor:
+        """Run one step feeding ``{slot: token}`` at each slot's current position; other slots idle.
+        Returns the pinned host tensor of sampled ids (valid after the implied synchronisation)."""
+        hi = max(slot_tokens) + 1
+        for i in range(hi):
+            s = self.slots[i]
+            if i in slot_tokens and s.active:
+                self._ensure_pages(i, s.position + 1)
+                self._h_tokens[i] = slot_tokens[i]
+                self._h_positions[i] = s.position
+            else:
+                self._h_positions[i] = -1
+        b = self.buf
+        b.tokens[:hi].copy_(self._h_tokens[:hi], non_blocking=True)
+        b.positions[:hi].copy_(self._h_positions[:hi], non_blocking=True)
+        if not self.cfg.greedy_only:
+            b.uniform[:hi].copy_(torch.rand(hi, device=self.device, generator=self._gen))
+        self.run_step(hi)
+        self._h_sampled[:hi].copy_(b.sampled[:hi], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        for i in slot_tokens:
+            if self.slots[i].active:
+                self.slots[i].position += 1
+        return self._h_sampled
+
+    def prefill(self, slot: int, tokens: Sequence[int]) -> int:
+        """Run the prompt through the decode path token by token (serial prefill, as the reference's
+        ``run_prefill`` loop, src/gguf/cuda/generate_2.rs:261-273).  Returns the token sampled after
+        the last prompt token."""
+        out = 0
+        for t in tokens:
+            out = int(self.feed({slot: int(t)})[slot])
+        return out
+
+    # -- convenience ----------------------------------------------------------------------------
+    def generate(self, prompt: Sequence[int], sampling: Optional[SamplingParams] = None, on_token=None) -> List[int]:
+        """Generate for a single prompt in slot 0 (streams through ``on_token`` if given)."""
+        sp = sampling or SamplingParams()
+        free = self.free_slots()
+        if not free:
+            raise RuntimeError("no free slot")
+        slot = free[0]
+        self.open_slot(slot, min(self.cfg.max_seq_len, len(prompt) + sp.max_tokens))
+        try:
+            self.set_sampling(slot, sp)
+            nxt = self.prefill(slot, prompt)
+            out: List[int] = []
+            stop = set(sp.stop_token_ids)
+            for _ in range(sp.max_tokens):
+                out.append(nxt)
+                if on_token is not None:
+                    on_token(nxt)
+                if nxt in stop or self.slots[slot].position >= self.cfg.max_seq_len:
+                    break
+                nxt = int(self.feed({slot: nxt})[slot])
+            return out
+        finally:
+            self.close_slot(slot)
+
+    def logits_of_last_step(self, slot: int = 0) -> torch.Tensor:
+        return self.buf.logits[slot, : self.mcfg.vocab_size].clone()
+
+    def memory_report(self) -> dict:
+        return {"weights_bytes": self.model.weight_bytes(), "kv_bytes": self.kv.numel() * 2, "kv_pages": self.num_pages,
+                "kv_utilization": self.pages.stats().utilization}

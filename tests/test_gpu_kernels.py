@@ -1,0 +1,259 @@
+"""Numerics of the sm_100a kernels against plain PyTorch fp32 references of the same op."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from realizar_b200 import quant
+from realizar_b200.quant import QType
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return float((a - b).abs().max() / (b.abs().max() + 1e-12))
+
+
+def _weight(n, k, qt, seed=0, std=0.02):
+    from realizar_b200 import ops
+    rng = np.random.default_rng(seed)
+    w = (rng.standard_normal((n, k)) * std).astype(np.float32)
+    q = quant.quantize(w, qt)
+    wd = torch.from_numpy(quant.dequantize(q, qt, (n, k)))
+    return ops.upload_weight(q, qt, n, k, "cuda"), wd
+
+
+FAST = [QType.Q4_K, QType.Q5_K, QType.Q6_K, QType.Q8_0, QType.Q4_0]
+GENERIC = [QType.Q4_1, QType.Q5_0, QType.Q5_1, QType.Q2_K, QType.F16, QType.BF16, QType.F32]
+
+
+@pytest.mark.parametrize("qt", FAST + GENERIC)
+@pytest.mark.parametrize("batch", [1, 3])
+def test_gemv_matches_fp32(cuda_device, qt, batch):
+    from realizar_b200 import ops
+    n, k = 300, 1024
+    w, wd = _weight(n, k, qt, seed=int(qt))
+    x = torch.randn(batch, k, device="cuda")
+    y = ops.gemv(w, x)
+    ref = x.cpu() @ wd.T
+    tol = 0.02 if qt in FAST else 2e-3       # int8 activations on the fast path
+    assert _rel(y, ref) < tol, (qt, _rel(y, ref))
+
+
+@pytest.mark.parametrize("n,k", [(37, 256), (2560, 2560), (513, 10240), (1000, 4096)])
+def test_gemv_shapes_q4k(cuda_device, n, k):
+    from realizar_b200 import ops
+    w, wd = _weight(n, k, QType.Q4_K, seed=n)
+    x = torch.randn(1, k, device="cuda")
+    assert _rel(ops.gemv(w, x), x.cpu() @ wd.T) < 0.02
+
+
+@pytest.mark.parametrize("norm", ["rms", "layer"])
+@pytest.mark.parametrize("qt", [QType.Q4_K, QType.Q5_1])
+def test_gemv_fused_norm_bias_act_residual(cuda_device, norm, qt):
+    from realizar_b200 import ops
+    n, k, B = 256, 512, 2
+    w, wd = _weight(n, k, qt, seed=5)
+    x = torch.randn(B, k, device="cuda") * 3 + 0.5
+    g, b = torch.rand(k, device="cuda") + 0.5, torch.randn(k, device="cuda") * 0.1
+    bias, res = torch.randn(n, device="cuda") * 0.1, torch.randn(B, n, device="cuda")
+    y = ops.gemv(w, x, bias=bias, act=ops.ACT_GELU, residual=res, norm=ops.NORM_RMS if norm == "rms" else ops.NORM_LAYER,
+                 norm_w=g, norm_b=b if norm == "layer" else None, eps=1e-5)
+    xc = x.cpu()
+    if norm == "rms":
+        h = xc / torch.sqrt((xc * xc).mean(-1, keepdim=True) + 1e-5) * g.cpu()
+    else:
+        h = torch.nn.functional.layer_norm(xc, (k,), g.cpu(), b.cpu(), 1e-5)
+    ref = torch.nn.functional.gelu(h @ wd.T + bias.cpu(), approximate="tanh") + res.cpu()
+    assert _rel(y, ref) < 0.02
+
+
+def test_gemv_swiglu_pair_and_dual_accumulate(cuda_device):
+    from realizar_b200 import ops
+    from realizar_b200.ops import MatOut, VecIn
+    n, k, k2, B = 384, 512, 768, 2
+    wg, wgd = _weight(n, k, QType.Q4_K, 1)
+    wu, wud = _weight(n, k, QType.Q4_K, 2)
+    x = torch.randn(B, k, device="cuda")
+    y = torch.empty(B, n, device="cuda")
+    p = ops.build_gemv_params([VecIn(x, k)], [MatOut([(wg, 0), (wu, 0)], combine=ops.COMBINE_SILU_MUL)], y, B)
+    ops.gemv_launch(p)
+    ref = torch.nn.functional.silu(x.cpu() @ wgd.T) * (x.cpu() @ wud.T)
+    assert _rel(y, ref) < 0.03
+    # two matrices with different inputs accumulated into the same rows (+ two biases + residual)
+    w2, w2d = _weight(n, k2, QType.Q6_K, 3)
+    x2 = torch.randn(B, k2, device="cuda")
+    b1, b2, res = torch.randn(n, device="cuda"), torch.randn(n, device="cuda"), torch.randn(B, n, device="cuda")
+    y2 = torch.empty(B, n, device="cuda")
+    p = ops.build_gemv_params([VecIn(x, k), VecIn(x2, k2)], [MatOut([(wg, 0), (w2, 1)], bias=b1, bias2=b2, residual=True)], y2, B, residual=res)
+    ops.gemv_launch(p)
+    ref2 = x.cpu() @ wgd.T + x2.cpu() @ w2d.T + b1.cpu() + b2.cpu() + res.cpu()
+    assert _rel(y2, ref2) < 0.02
+
+
+def test_gemv_multi_matrix_launch(cuda_device):
+    from realizar_b200 import ops
+    from realizar_b200.ops import MatOut, VecIn
+    k = 512
+    ws = [_weight(n, k, qt, 10 + i) for i, (n, qt) in enumerate([(128, QType.Q4_K), (64, QType.Q4_K), (64, QType.Q6_K), (200, QType.Q5_K)])]
+    x = torch.randn(1, k, device="cuda")
+    total = sum(w.n for w, _ in ws)
+    y = torch.zeros(1, total, device="cuda")
+    mats, off = [], 0
+    for w, _ in ws:
+        mats.append(MatOut([(w, 0)], out_off=off))
+        off += w.n
+    ops.gemv_launch(ops.build_gemv_params([VecIn(x, k)], mats, y, 1))
+    ref = torch.cat([x.cpu() @ wd.T for _, wd in ws], dim=-1)
+    assert _rel(y, ref) < 0.02
+
+
+def _ref_attention(q, kc, vc, scale):
+    # q [H, d]; kc/vc [T, Hkv, d]
+    H, d = q.shape
+    Hkv = kc.shape[1]
+    g = H // Hkv
+    kk, vv = kc.repeat_interleave(g, dim=1), vc.repeat_interleave(g, dim=1)
+    s = torch.einsum("hd,thd->ht", q, kk) * scale
+    return torch.einsum("ht,thd->hd", s.softmax(-1), vv)
+
+
+@pytest.mark.parametrize("H,Hkv,d,rope_dim,rope_type", [(8, 8, 80, 32, 2), (8, 2, 128, 128, 0), (14, 2, 64, 64, 2), (16, 2, 128, 128, 0), (4, 4, 64, 0, 0)])
+@pytest.mark.parametrize("ctx", [1, 17, 300])
+def test_attn_decode_matches_reference(cuda_device, H, Hkv, d, rope_dim, rope_type, ctx):
+    from realizar_b200 import ops
+    from realizar_b200.models.reference import apply_rope
+    torch.manual_seed(ctx + H)
+    B, splits, pages_per_seq = 2, 4, 32
+    n_pages = B * pages_per_seq
+    kc = torch.zeros(n_pages, Hkv, 16, d, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    page_table = torch.arange(n_pages, device="cuda", dtype=torch.int32).reshape(B, pages_per_seq).flip(1).contiguous()
+    lens = [ctx, max(1, ctx // 2)]
+    hist_k = [torch.randn(L - 1, Hkv, d) for L in lens]
+    hist_v = [torch.randn(L - 1, Hkv, d) for L in lens]
+    for b in range(B):          # history is stored already rotated, as the kernel would have written it
+        for t in range(lens[b] - 1):
+            pg, slot = int(page_table[b, t // 16]), t % 16
+            kr = apply_rope(hist_k[b][t:t + 1], torch.tensor([t]), rope_dim, 10000.0, rope_type)[0]
+            kc[pg, :, slot] = kr.to(torch.bfloat16).cuda()
+            vc[pg, :, slot] = hist_v[b][t].to(torch.bfloat16).cuda()
+    qkv = torch.randn(B, (H + 2 * Hkv) * d, device="cuda")
+    positions = torch.tensor([L - 1 for L in lens], device="cuda", dtype=torch.int32)
+    out = torch.zeros(B, H * d, device="cuda")
+    partial, counters = ops.attn_decode_scratch(B, H, splits, d, "cuda")
+    p = ops.build_attn_decode_params(qkv, out, kc, vc, positions, page_table, partial, counters, H, Hkv, d, splits, B, rope_dim, rope_type,
+                                     10000.0, 0, H * d, (H + Hkv) * d)
+    for _ in range(2):          # second launch checks the self-cleaning counters
+        ops.attn_decode_launch(p)
+    torch.cuda.synchronize()
+    assert int(counters.abs().sum()) == 0
+    for b in range(B):
+        L = lens[b]
+        row = qkv[b].cpu()
+        q = row[: H * d].reshape(1, H, d)
+        kn = row[H * d:(H + Hkv) * d].reshape(1, Hkv, d)
+        vn = row[(H + Hkv) * d:].reshape(1, Hkv, d)
+        pos = torch.tensor([L - 1])
+        q = apply_rope(q, pos, rope_dim, 10000.0, rope_type)[0]
+        kn = apply_rope(kn, pos, rope_dim, 10000.0, rope_type)
+        kh = apply_rope(hist_k[b], torch.arange(L - 1), rope_dim, 10000.0, rope_type) if L > 1 else hist_k[b]
+        k_all = torch.cat([kh, kn]).to(torch.bfloat16).float()
+        v_all = torch.cat([hist_v[b], vn]).to(torch.bfloat16).float()
+        ref = _ref_attention(q, k_all, v_all, d ** -0.5).reshape(-1)
+        assert _rel(out[b], ref) < 5e-3, (b, _rel(out[b], ref))
+        # the new row was appended to the cache
+        pg, slot = int(page_table[b, (L - 1) // 16]), (L - 1) % 16
+        assert _rel(kc[pg, :, slot].float(), kn[0].to(torch.bfloat16).float()) < 1e-2
+
+
+def test_attn_decode_inactive_slot_and_qk_norm(cuda_device):
+    from realizar_b200 import ops
+    H, Hkv, d, B, splits = 4, 2, 64, 2, 2
+    kc = torch.zeros(8, Hkv, 16, d, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    pt = torch.arange(8, device="cuda", dtype=torch.int32).reshape(B, 4)
+    qkv = torch.randn(B, (H + 2 * Hkv) * d, device="cuda")
+    out = torch.full((B, H * d), 7.0, device="cuda")
+    positions = torch.tensor([0, -1], device="cuda", dtype=torch.int32)
+    partial, counters = ops.attn_decode_scratch(B, H, splits, d, "cuda")
+    qn, kn = torch.rand(d, device="cuda") + 0.5, torch.rand(d, device="cuda") + 0.5
+    ops.attn_decode_launch(ops.build_attn_decode_params(qkv, out, kc, vc, positions, pt, partial, counters, H, Hkv, d, splits, B, 0, 0, 1e4,
+                                                        0, H * d, (H + Hkv) * d, qn, kn, 1e-6))
+    torch.cuda.synchronize()
+    assert torch.all(out[1] == 7.0)                 # idle slot untouched
+    v_new = qkv[0, (H + Hkv) * d:].reshape(Hkv, d).to(torch.bfloat16).float()
+    ref = v_new.repeat_interleave(H // Hkv, dim=0).reshape(-1)      # single token: output = v
+    assert _rel(out[0], ref) < 1e-2
+    k_new = qkv[0, H * d:(H + Hkv) * d].reshape(Hkv, d).cpu()
+    k_ref = k_new / torch.sqrt((k_new * k_new).mean(-1, keepdim=True) + 1e-6) * kn.cpu()
+    assert _rel(kc[0, :, 0].float(), k_ref) < 1e-2
+
+
+def test_embed_norm_rope_elementwise(cuda_device):
+    from realizar_b200 import ops
+    from realizar_b200.models.reference import apply_rope
+    rng = np.random.default_rng(0)
+    V, Hd = 64, 512
+    for qt in (QType.Q4_K, QType.Q8_0, QType.F32, QType.Q5_0):
+        w = (rng.standard_normal((V, Hd)) * 0.05).astype(np.float32)
+        q = quant.quantize(w, qt)
+        table = torch.from_numpy(q).cuda()
+        toks = torch.tensor([3, 63, -1, 0], device="cuda", dtype=torch.int32)
+        out = torch.empty(4, Hd, device="cuda")
+        ops.embed(table, qt, quant.row_bytes(qt, Hd), Hd, V, toks, out)
+        ref = torch.from_numpy(quant.dequantize(q, qt, (V, Hd)))
+        assert torch.allclose(out[0].cpu(), ref[3], atol=1e-6) and torch.allclose(out[1].cpu(), ref[63], atol=1e-6)
+        assert float(out[2].abs().max()) == 0.0
+    x = torch.randn(5, 320, device="cuda") * 2 + 1
+    g, b = torch.rand(320, device="cuda"), torch.randn(320, device="cuda")
+    assert _rel(ops.norm(x, g, b, ops.NORM_LAYER, 1e-5), torch.nn.functional.layer_norm(x.cpu(), (320,), g.cpu(), b.cpu(), 1e-5)) < 1e-5
+    xr = x.cpu()
+    assert _rel(ops.norm(x, g, None, ops.NORM_RMS, 1e-6), xr / torch.sqrt((xr * xr).mean(-1, keepdim=True) + 1e-6) * g.cpu()) < 1e-5
+    for rope_type, rd in ((0, 64), (2, 32), (2, 80)):
+        t = torch.randn(6, 4 * 80, device="cuda")
+        pos = torch.tensor([0, 1, 5, 100, 2047, 7], device="cuda", dtype=torch.int32)
+        ref = apply_rope(t.cpu().reshape(6, 4, 80), pos.cpu(), rd, 1e4, rope_type).reshape(6, -1)
+        ops.rope_(t, pos, 4, 80, rd, rope_type, 1e4)
+        assert _rel(t, ref) < 1e-4
+    a, bb = torch.randn(7, 100, device="cuda"), torch.randn(7, 100, device="cuda")
+    y = ops.elementwise(a, bb, act=ops.ACT_SILU)
+    assert _rel(y, torch.nn.functional.silu(a.cpu()) * bb.cpu()) < 1e-5
+
+
+def test_argmax_and_sampling(cuda_device):
+    from realizar_b200 import ops
+    torch.manual_seed(0)
+    B, V = 3, 50257
+    logits = torch.randn(B, V, device="cuda")
+    logits[1, 777] = 50.0
+    am = ops.argmax(logits)
+    assert am.cpu().tolist() == logits.argmax(-1).cpu().tolist()
+    temp = torch.tensor([0.0, 1.0, 0.8], device="cuda")
+    top_k = torch.tensor([0, 40, 5], device="cuda", dtype=torch.int32)
+    top_p = torch.tensor([1.0, 0.9, 1.0], device="cuda")
+    u = torch.tensor([0.3, 0.5, 0.999], device="cuda")
+    out = ops.sample(logits, temp, top_k, top_p, u).cpu().tolist()
+    assert out[0] == int(logits[0].argmax())            # temperature 0 -> greedy
+    assert out[1] == 777                                # dominant token inside the nucleus
+    top5 = logits[2].topk(5).indices.cpu().tolist()
+    assert out[2] in top5
+    # distribution check: top-k=4 sampling frequencies follow the softmax over the top 4
+    row = torch.tensor([[2.0, 1.0, 0.5, 0.0, -1.0, -3.0] + [-20.0] * 58], device="cuda")
+    n = 4000
+    us = torch.rand(n, device="cuda")
+    counts = torch.zeros(64)
+    big = row.repeat(n, 1).contiguous()
+    o = ops.sample(big, torch.ones(n, device="cuda"), torch.full((n,), 4, device="cuda", dtype=torch.int32), torch.ones(n, device="cuda"), us)
+    for t in o.cpu().tolist():
+        counts[t] += 1
+    assert counts[4:].sum() == 0
+    expect = torch.softmax(row[0, :4].cpu(), -1)
+    assert float((counts[:4] / n - expect).abs().max()) < 0.03
+    # penalties
+    lg = torch.zeros(1, 16, device="cuda"); lg[0, 3] = 2.0; lg[0, 5] = -2.0
+    hist = torch.tensor([[3, 5, 3, -1]], device="cuda", dtype=torch.int32)
+    ops.penalties_(lg, hist, torch.tensor([2.0], device="cuda"), torch.tensor([0.5], device="cuda"), torch.tensor([0.25], device="cuda"))
+    assert abs(float(lg[0, 3]) - (1.0 - 0.5 - 0.5)) < 1e-6 and abs(float(lg[0, 5]) - (-4.0 - 0.5 - 0.25)) < 1e-6
