@@ -13,7 +13,7 @@ void emu_rows(const uint8_t* W, int64_t stride, const ActView& a, float* y, int6
   const int upr = dev_units_per_row(QT, k);
   for (int64_t r = 0; r < n; ++r) {
     for (int b = 0; b < batch; ++b) {
-      ActView ab{a.q + (int64_t)b * k, a.d + (int64_t)b * (k >> 5), a.s + (int64_t)b * (k >> 4), k};
+      ActView ab{a.q + (int64_t)b * k, a.d + (int64_t)b * (k >> 5), a.s + (int64_t)b * (k >> 4), a.m + (int64_t)b * (k >> 6), k};
       // 32 lanes, each striding over units, then a tree reduction like the warp shuffle
       float lane[32];
       for (int l = 0; l < 32; ++l) { float acc = 0.f; for (int u = l; u < upr; u += 32) unit_dot<QT, 1>(W + r * stride, u, ab, &acc); lane[l] = acc; }
@@ -31,12 +31,12 @@ int64_t rlz_dev_row_bytes(int qtype, int64_t k) { return dev_row_bytes(qtype, k)
 // y[batch, n] = W_dev[n, k] x[batch, k] with int8 activations, exactly as the GPU fast path computes it.
 int rlz_emu_gemv(int qtype, const void* W, int64_t stride, const float* x, float* y, int64_t n, int k, int batch) {
   if (k % 32) return -1;
-  std::vector<int8_t> q((size_t)batch * k); std::vector<float> d((size_t)batch * (k / 32)), s((size_t)batch * (k / 16));
+  std::vector<int8_t> q((size_t)batch * k); std::vector<float> d((size_t)batch * (k / 32));
+  std::vector<int32_t> s((size_t)batch * (k / 16)); std::vector<U4> m((size_t)batch * (k / 64) + 1);
   for (int b = 0; b < batch; ++b)
-    for (int i = 0; i < k / 32; ++i)
-      quantize_act_block32(x + (int64_t)b * k + 32 * i, q.data() + (int64_t)b * k + 32 * i, d.data() + (int64_t)b * (k / 32) + i,
-                           s.data() + (int64_t)b * (k / 16) + 2 * i);
-  ActView a{q.data(), d.data(), s.data(), k};
+    quantize_act_row(x + (int64_t)b * k, k, q.data() + (int64_t)b * k, d.data() + (int64_t)b * (k / 32), s.data() + (int64_t)b * (k / 16),
+                     m.data() + (int64_t)b * (k / 64));
+  ActView a{q.data(), d.data(), s.data(), m.data(), k};
   const uint8_t* w = (const uint8_t*)W;
   switch (qtype) {
     case QT_Q4_K: emu_rows<QT_Q4_K>(w, stride, a, y, n, k, batch); return 0;

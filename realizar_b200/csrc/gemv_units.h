@@ -41,8 +41,7 @@ RLZ_HD int64_t dev_row_bytes(int qtype, int64_t k) {
 // units (lane work items) per row for the int8 fast path; 0 = not a fast-path type
 RLZ_HD int dev_units_per_row(int qtype, int k) {
   switch (qtype) {
-    case QT_Q4_K: case QT_Q5_K: return k / 32;
-    case QT_Q6_K: return k / 64;
+    case QT_Q4_K: case QT_Q5_K: case QT_Q6_K: return k / 64;
     case QT_Q8_0: return k / 16;
     case QT_Q4_0: return k / 32;
     default: return 0;
@@ -52,7 +51,7 @@ RLZ_HD int dev_units_per_row(int qtype, int k) {
 #if defined(__CUDA_ARCH__)
 __device__ __forceinline__ U4 ld_w16(const uint8_t* p) {   // streaming weight load: read once
   U4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+  asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
@@ -93,61 +92,105 @@ RLZ_HD void k4_scale_min(uint32_t y, uint32_t z, uint32_t w, int j, float* sc, f
   *sc = (float)s; *m = (float)mm;
 }
 
-struct ActView {         // activations of B rows, row strides derived from k
-  const int8_t* q; const float* d; const float* s; int k;
+// Activations of B rows in shared memory.  Layout per row (strides derived from k):
+//   q : int8[k], stored in 16-byte chunks whose position inside each group of four chunks is
+//       rotated by (chunk >> 3) so that lanes reading 64-byte-strided chunks hit distinct banks
+//   d : float[k/32]  scale of each 32-block
+//   s : int32[k/16]  sum of the 16 ints of each 16-chunk
+//   m : 16 bytes per 64 values {d[2i], d[2i+1], sum32[2i], sum32[2i+1]} for the K-quant units
+struct ActView {
+  const int8_t* q; const float* d; const int32_t* s; const U4* m; int k;
 };
 
-// ---- Q4_K: unit u covers sub-blocks (2g, 2g+1) elements [16h, 16h+16) ---------------------
+RLZ_HD int act_chunk_off(int chunk) { return ((chunk & ~3) | ((chunk + (chunk >> 3)) & 3)) << 4; }
+
+#if defined(__CUDA_ARCH__)
+__device__ __forceinline__ float as_f(uint32_t u) { return __uint_as_float(u); }
+__device__ __forceinline__ uint32_t as_u(float f) { return __float_as_uint(f); }
+#else
+inline float as_f(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+inline uint32_t as_u(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+#endif
+// int -> float for |i| < 2^22 without the conversion unit: 1.5 * 2^23 + i is exact
+RLZ_HD float i2f(int i) { return as_f(0x4B400000u + (uint32_t)i) - 12582912.0f; }
+// fp16 bits -> float with integer ops and one multiply (exact for zero, subnormals and normals)
+RLZ_HD float h2f_alu(uint32_t h) {
+  const float mag = as_f((h & 0x7FFFu) << 13) * 5.192296858534828e33f;   // * 2^112
+  return as_f(as_u(mag) | ((h & 0x8000u) << 16));
+}
+
+RLZ_HD void k4_scale_min_i(uint32_t y, uint32_t z, uint32_t w, int j, int* sc, int* m) {
+  uint32_t s, mm;
+  if (j < 4) { s = k4_byte(y, z, w, j) & 63u; mm = k4_byte(y, z, w, j + 4) & 63u; }
+  else {
+    const uint32_t hi = k4_byte(y, z, w, j + 4);
+    s = (hi & 0xFu) | ((k4_byte(y, z, w, j - 4) >> 6) << 4);
+    mm = (hi >> 4) | ((k4_byte(y, z, w, j) >> 6) << 4);
+  }
+  *sc = (int)s; *m = (int)mm;
+}
+
+#define RLZ_LO4(v) U4{(v).x & 0x0F0F0F0Fu, (v).y & 0x0F0F0F0Fu, (v).z & 0x0F0F0F0Fu, (v).w & 0x0F0F0F0Fu}
+#define RLZ_HI4(v) U4{((v).x >> 4) & 0x0F0F0F0Fu, ((v).y >> 4) & 0x0F0F0F0Fu, ((v).z >> 4) & 0x0F0F0F0Fu, ((v).w >> 4) & 0x0F0F0F0Fu}
+
+// ---- Q4_K: unit u = one 64-weight group g of a super-block (32 bytes of nibbles): low nibbles
+// are sub-block 2g, high nibbles sub-block 2g+1, so one scale decode serves 64 weights ----------
 template <int B>
 RLZ_HD void unit_q4k(const uint8_t* row, int u, const ActView& a, float* acc) {
-  const int sb = u >> 3, t = u & 7, g = t >> 1, h = t & 1;
+  const int sb = u >> 2, g = u & 3;
   const uint8_t* base = row + (int64_t)sb * 144;
   const U4 hdr = ld_c16(base);
-  const U4 qs = ld_w16(base + 16 + 16 * t);
-  const float d = h2f(hdr.x & 0xFFFFu), dmin = h2f(hdr.x >> 16);
-  float sc0, m0, sc1, m1;
-  k4_scale_min(hdr.y, hdr.z, hdr.w, 2 * g, &sc0, &m0);
-  k4_scale_min(hdr.y, hdr.z, hdr.w, 2 * g + 1, &sc1, &m1);
-  const U4 lo{qs.x & 0x0F0F0F0Fu, qs.y & 0x0F0F0F0Fu, qs.z & 0x0F0F0F0Fu, qs.w & 0x0F0F0F0Fu};
-  const U4 hi{(qs.x >> 4) & 0x0F0F0F0Fu, (qs.y >> 4) & 0x0F0F0F0Fu, (qs.z >> 4) & 0x0F0F0F0Fu, (qs.w >> 4) & 0x0F0F0F0Fu};
-  const int kb = sb * 256 + g * 64 + h * 16;
+  const U4 q0 = ld_w16(base + 16 + 32 * g), q1 = ld_w16(base + 32 + 32 * g);
+  const float d = h2f_alu(hdr.x & 0xFFFFu), dmin = h2f_alu(hdr.x >> 16);
+  int sc0, m0, sc1, m1;
+  k4_scale_min_i(hdr.y, hdr.z, hdr.w, 2 * g, &sc0, &m0);
+  k4_scale_min_i(hdr.y, hdr.z, hdr.w, 2 * g + 1, &sc1, &m1);
+  const U4 lo0 = RLZ_LO4(q0), hi0 = RLZ_HI4(q0), lo1 = RLZ_LO4(q1), hi1 = RLZ_HI4(q1);
+  const int c = u * 4;                          // first 16-byte activation chunk of this unit
+  const int o0 = act_chunk_off(c), o1 = act_chunk_off(c + 1), o2 = act_chunk_off(c + 2), o3 = act_chunk_off(c + 3);
 #pragma unroll
   for (int b = 0; b < B; ++b) {
     const int8_t* xq = a.q + (int64_t)b * a.k;
-    const float* xd = a.d + (int64_t)b * (a.k >> 5);
-    const float* xs = a.s + (int64_t)b * (a.k >> 4);
-    const int dlo = dot16(lo, ld_a16(xq + kb)), dhi = dot16(hi, ld_a16(xq + kb + 32));
-    acc[b] += d * (sc0 * xd[kb >> 5] * (float)dlo + sc1 * xd[(kb >> 5) + 1] * (float)dhi)
-            - dmin * (m0 * xs[kb >> 4] + m1 * xs[(kb >> 4) + 2]);
+    const U4 mm = *(const U4*)((const uint8_t*)(a.m + (int64_t)b * (a.k >> 6) + u));
+    const int dlo = dot16(lo0, ld_a16(xq + o0)) + dot16(lo1, ld_a16(xq + o1));
+    const int dhi = dot16(hi0, ld_a16(xq + o2)) + dot16(hi1, ld_a16(xq + o3));
+    const float t0 = d * i2f(sc0 * dlo) - dmin * i2f(m0 * (int)mm.z);
+    const float t1 = d * i2f(sc1 * dhi) - dmin * i2f(m1 * (int)mm.w);
+    acc[b] += as_f(mm.x) * t0 + as_f(mm.y) * t1;
   }
 }
 
-// ---- Q5_K: as Q4_K plus the fifth bit from qh ----------------------------------------------
+// ---- Q5_K: as Q4_K plus the fifth bit from qh (bit 2g / 2g+1 of qh[l]) ------------------------
 template <int B>
 RLZ_HD void unit_q5k(const uint8_t* row, int u, const ActView& a, float* acc) {
-  const int sb = u >> 3, t = u & 7, g = t >> 1, h = t & 1;
+  const int sb = u >> 2, g = u & 3;
   const uint8_t* base = row + (int64_t)sb * 176;
   const U4 hdr = ld_c16(base);
-  const U4 qh = ld_c16(base + 16 + 16 * h);
-  const U4 qs = ld_w16(base + 48 + 16 * t);
-  const float d = h2f(hdr.x & 0xFFFFu), dmin = h2f(hdr.x >> 16);
-  float sc0, m0, sc1, m1;
-  k4_scale_min(hdr.y, hdr.z, hdr.w, 2 * g, &sc0, &m0);
-  k4_scale_min(hdr.y, hdr.z, hdr.w, 2 * g + 1, &sc1, &m1);
+  const U4 h0 = ld_c16(base + 16), h1 = ld_c16(base + 32);
+  const U4 q0 = ld_w16(base + 48 + 32 * g), q1 = ld_w16(base + 64 + 32 * g);
+  const float d = h2f_alu(hdr.x & 0xFFFFu), dmin = h2f_alu(hdr.x >> 16);
+  int sc0, m0, sc1, m1;
+  k4_scale_min_i(hdr.y, hdr.z, hdr.w, 2 * g, &sc0, &m0);
+  k4_scale_min_i(hdr.y, hdr.z, hdr.w, 2 * g + 1, &sc1, &m1);
   const int s0 = 2 * g, s1 = 2 * g + 1;
-  const U4 lo{(qs.x & 0x0F0F0F0Fu) | (((qh.x >> s0) & 0x01010101u) << 4), (qs.y & 0x0F0F0F0Fu) | (((qh.y >> s0) & 0x01010101u) << 4),
-              (qs.z & 0x0F0F0F0Fu) | (((qh.z >> s0) & 0x01010101u) << 4), (qs.w & 0x0F0F0F0Fu) | (((qh.w >> s0) & 0x01010101u) << 4)};
-  const U4 hi{((qs.x >> 4) & 0x0F0F0F0Fu) | (((qh.x >> s1) & 0x01010101u) << 4), ((qs.y >> 4) & 0x0F0F0F0Fu) | (((qh.y >> s1) & 0x01010101u) << 4),
-              ((qs.z >> 4) & 0x0F0F0F0Fu) | (((qh.z >> s1) & 0x01010101u) << 4), ((qs.w >> 4) & 0x0F0F0F0Fu) | (((qh.w >> s1) & 0x01010101u) << 4)};
-  const int kb = sb * 256 + g * 64 + h * 16;
+#define RLZ_Q5(qw, hw, sh, hi) ((((hi) ? ((qw) >> 4) : (qw)) & 0x0F0F0F0Fu) | ((((hw) >> (sh)) & 0x01010101u) << 4))
+  const U4 lo0{RLZ_Q5(q0.x, h0.x, s0, 0), RLZ_Q5(q0.y, h0.y, s0, 0), RLZ_Q5(q0.z, h0.z, s0, 0), RLZ_Q5(q0.w, h0.w, s0, 0)};
+  const U4 hi0{RLZ_Q5(q0.x, h0.x, s1, 1), RLZ_Q5(q0.y, h0.y, s1, 1), RLZ_Q5(q0.z, h0.z, s1, 1), RLZ_Q5(q0.w, h0.w, s1, 1)};
+  const U4 lo1{RLZ_Q5(q1.x, h1.x, s0, 0), RLZ_Q5(q1.y, h1.y, s0, 0), RLZ_Q5(q1.z, h1.z, s0, 0), RLZ_Q5(q1.w, h1.w, s0, 0)};
+  const U4 hi1{RLZ_Q5(q1.x, h1.x, s1, 1), RLZ_Q5(q1.y, h1.y, s1, 1), RLZ_Q5(q1.z, h1.z, s1, 1), RLZ_Q5(q1.w, h1.w, s1, 1)};
+#undef RLZ_Q5
+  const int c = u * 4;
+  const int o0 = act_chunk_off(c), o1 = act_chunk_off(c + 1), o2 = act_chunk_off(c + 2), o3 = act_chunk_off(c + 3);
+  const float fs0 = d * i2f(sc0), fs1 = d * i2f(sc1);
 #pragma unroll
   for (int b = 0; b < B; ++b) {
     const int8_t* xq = a.q + (int64_t)b * a.k;
-    const float* xd = a.d + (int64_t)b * (a.k >> 5);
-    const float* xs = a.s + (int64_t)b * (a.k >> 4);
-    const int dlo = dot16(lo, ld_a16(xq + kb)), dhi = dot16(hi, ld_a16(xq + kb + 32));
-    acc[b] += d * (sc0 * xd[kb >> 5] * (float)dlo + sc1 * xd[(kb >> 5) + 1] * (float)dhi)
-            - dmin * (m0 * xs[kb >> 4] + m1 * xs[(kb >> 4) + 2]);
+    const U4 mm = *(const U4*)((const uint8_t*)(a.m + (int64_t)b * (a.k >> 6) + u));
+    const int dlo = dot16(lo0, ld_a16(xq + o0)) + dot16(lo1, ld_a16(xq + o1));
+    const int dhi = dot16(hi0, ld_a16(xq + o2)) + dot16(hi1, ld_a16(xq + o3));
+    const float t0 = fs0 * i2f(dlo) - dmin * i2f(m0 * (int)mm.z);
+    const float t1 = fs1 * i2f(dhi) - dmin * i2f(m1 * (int)mm.w);
+    acc[b] += as_f(mm.x) * t0 + as_f(mm.y) * t1;
   }
 }
 
@@ -161,14 +204,14 @@ RLZ_HD void unit_q6k(const uint8_t* row, int u, const ActView& a, float* acc) {
   const U4 qh = ld_w16(base + 128 + n * 32 + 16 * lh);
   const U4 scv = ld_c16(base + 192);
   const U4 tail = ld_c16(base + 208);
-  const float d = h2f(tail.x & 0xFFFFu);
+  const float d = h2f_alu(tail.x & 0xFFFFu);
   const uint32_t scw0 = n ? scv.z : scv.x, scw1 = n ? scv.w : scv.y;   // 8 scales of this half
   float sc[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int idx = lh + 2 * j;                       // 0..7
     const uint32_t wv = idx < 4 ? scw0 : scw1;
-    sc[j] = (float)(int)(int8_t)((wv >> (8 * (idx & 3))) & 0xFFu);
+    sc[j] = d * i2f((int)(int8_t)((wv >> (8 * (idx & 3))) & 0xFFu));
   }
   U4 w[4];
   w[0] = U4{(qa.x & 0x0F0F0F0Fu) | ((qh.x & 0x03030303u) << 4), (qa.y & 0x0F0F0F0Fu) | ((qh.y & 0x03030303u) << 4),
@@ -184,15 +227,15 @@ RLZ_HD void unit_q6k(const uint8_t* row, int u, const ActView& a, float* acc) {
   for (int b = 0; b < B; ++b) {
     const int8_t* xq = a.q + (int64_t)b * a.k;
     const float* xd = a.d + (int64_t)b * (a.k >> 5);
-    const float* xs = a.s + (int64_t)b * (a.k >> 4);
+    const int32_t* xs = a.s + (int64_t)b * (a.k >> 4);
     float sum = 0.f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int kk = kb + 32 * j;
-      const int dj = dot16(w[j], ld_a16(xq + kk));
-      sum += sc[j] * (xd[kk >> 5] * (float)dj - 32.f * xs[kk >> 4]);
+      const int dj = dot16(w[j], ld_a16(xq + act_chunk_off(kk >> 4))) - 32 * xs[kk >> 4];
+      sum += sc[j] * xd[kk >> 5] * i2f(dj);
     }
-    acc[b] += d * sum;
+    acc[b] += sum;
   }
 }
 
@@ -200,13 +243,13 @@ RLZ_HD void unit_q6k(const uint8_t* row, int u, const ActView& a, float* acc) {
 template <int B>
 RLZ_HD void unit_q8_0(const uint8_t* row, int u, const ActView& a, float* acc) {
   const int nb = a.k >> 5, blk = u >> 1;
-  const float d = h2f((uint32_t)load_u16(row + 2 * blk));
+  const float d = h2f_alu((uint32_t)load_u16(row + 2 * blk));
   const U4 w = ld_w16(row + dev_planar_qoff(nb) + 16 * u);
-  const int kb = 16 * u;
+  const int off = act_chunk_off(u);
 #pragma unroll
   for (int b = 0; b < B; ++b) {
-    const int dj = dot16(w, ld_a16(a.q + (int64_t)b * a.k + kb));
-    acc[b] += d * a.d[(int64_t)b * nb + blk] * (float)dj;
+    const int dj = dot16(w, ld_a16(a.q + (int64_t)b * a.k + off));
+    acc[b] += d * a.d[(int64_t)b * nb + blk] * i2f(dj);
   }
 }
 
@@ -214,17 +257,16 @@ RLZ_HD void unit_q8_0(const uint8_t* row, int u, const ActView& a, float* acc) {
 template <int B>
 RLZ_HD void unit_q4_0(const uint8_t* row, int u, const ActView& a, float* acc) {
   const int nb = a.k >> 5;
-  const float d = h2f((uint32_t)load_u16(row + 2 * u));
+  const float d = h2f_alu((uint32_t)load_u16(row + 2 * u));
   const U4 qs = ld_w16(row + dev_planar_qoff(nb) + 16 * u);
-  const U4 lo{qs.x & 0x0F0F0F0Fu, qs.y & 0x0F0F0F0Fu, qs.z & 0x0F0F0F0Fu, qs.w & 0x0F0F0F0Fu};
-  const U4 hi{(qs.x >> 4) & 0x0F0F0F0Fu, (qs.y >> 4) & 0x0F0F0F0Fu, (qs.z >> 4) & 0x0F0F0F0Fu, (qs.w >> 4) & 0x0F0F0F0Fu};
-  const int kb = 32 * u;
+  const U4 lo = RLZ_LO4(qs), hi = RLZ_HI4(qs);
+  const int o0 = act_chunk_off(2 * u), o1 = act_chunk_off(2 * u + 1);
 #pragma unroll
   for (int b = 0; b < B; ++b) {
     const int8_t* xq = a.q + (int64_t)b * a.k;
-    const float* xs = a.s + (int64_t)b * (a.k >> 4);
-    const int dj = dot16(lo, ld_a16(xq + kb)) + dot16(hi, ld_a16(xq + kb + 16));
-    acc[b] += d * (a.d[(int64_t)b * nb + u] * (float)dj - 8.f * (xs[2 * u] + xs[2 * u + 1]));
+    const int32_t* xs = a.s + (int64_t)b * (a.k >> 4);
+    const int dj = dot16(lo, ld_a16(xq + o0)) + dot16(hi, ld_a16(xq + o1)) - 8 * (xs[2 * u] + xs[2 * u + 1]);
+    acc[b] += d * a.d[(int64_t)b * nb + u] * i2f(dj);
   }
 }
 
@@ -237,18 +279,28 @@ RLZ_HD void unit_dot(const uint8_t* row, int u, const ActView& a, float* acc) {
   else if (QT == QT_Q4_0) unit_q4_0<B>(row, u, a, acc);
 }
 
-// Activation quantisation of one 32-block (host form; the kernel does the same arithmetic
-// cooperatively): q = rint(v * 127/amax), d = amax/127, s16 = d * sum of each 16 ints.
-inline void quantize_act_block32(const float* v, int8_t* q, float* d, float* s16) {
-  float amax = 0.f;
-  for (int i = 0; i < 32; ++i) { float a = v[i] < 0 ? -v[i] : v[i]; if (a > amax) amax = a; }
-  const float dd = amax / 127.f, inv = amax > 0.f ? 127.f / amax : 0.f;
-  int s0 = 0, s1 = 0;
-  for (int i = 0; i < 32; ++i) {
-    const int qi = (int)lrintf(v[i] * inv);
-    q[i] = (int8_t)qi; if (i < 16) s0 += qi; else s1 += qi;
+// Activation quantisation of one row (host form; the kernel does the same arithmetic
+// cooperatively): per 32-block q = rint(v * 127/amax), d = amax/127; integer sums per 16.
+// Output arrays follow the ActView layout (k must be a multiple of 64 for the `m` records,
+// which are only filled for complete 64-groups).
+inline void quantize_act_row(const float* v, int k, int8_t* q, float* d, int32_t* s16, U4* m) {
+  for (int blk = 0; blk < k / 32; ++blk) {
+    float amax = 0.f;
+    for (int i = 0; i < 32; ++i) { float a = fabsf(v[blk * 32 + i]); if (a > amax) amax = a; }
+    const float dd = amax / 127.f, inv = amax > 0.f ? 127.f / amax : 0.f;
+    int sum[2] = {0, 0};
+    for (int i = 0; i < 32; ++i) {
+      const int qi = (int)lrintf(v[blk * 32 + i] * inv);
+      const int e = blk * 32 + i;
+      q[act_chunk_off(e >> 4) + (e & 15)] = (int8_t)qi;
+      sum[i >> 4] += qi;
+    }
+    d[blk] = dd; s16[2 * blk] = sum[0]; s16[2 * blk + 1] = sum[1];
+    if (m && (blk >> 1) < k / 64) {
+      U4& r = m[blk >> 1];
+      if (blk & 1) { r.y = as_u(dd); r.w = (uint32_t)(sum[0] + sum[1]); } else { r.x = as_u(dd); r.z = (uint32_t)(sum[0] + sum[1]); }
+    }
   }
-  *d = dd; s16[0] = dd * (float)s0; s16[1] = dd * (float)s1;
 }
 
 }  // namespace rlz

@@ -59,9 +59,10 @@ __device__ __forceinline__ float4 load_normed(const GemvX& X, const float* x, in
   return v;
 }
 
-// int8 staging: xq[B][k], xd[B][k/32], xs[B][k/16]
+// int8 staging in the ActView layout: xq[B][k] (chunk-rotated), xd[B][k/32], xs[B][k/16] (int sums),
+// xm[B][k/64] records {d0, d1, sum32_0, sum32_1}
 template <int B>
-__device__ void stage_x_q8(const GemvX& X, int8_t* xq, float* xd, float* xs, float* red) {
+__device__ void stage_x_q8(const GemvX& X, int8_t* xq, float* xd, int32_t* xs, uint32_t* xm, float* red) {
   const int k = X.k;
 #pragma unroll 1
   for (int b = 0; b < B; ++b) {
@@ -79,13 +80,20 @@ __device__ void stage_x_q8(const GemvX& X, int8_t* xq, float* xd, float* xs, flo
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
       const float d = amax / 127.f, inv = amax > 0.f ? 127.f / amax : 0.f;
       const int q0 = __float2int_rn(v.x * inv), q1 = __float2int_rn(v.y * inv), q2 = __float2int_rn(v.z * inv), q3 = __float2int_rn(v.w * inv);
-      int s = q0 + q1 + q2 + q3;
-      s += __shfl_xor_sync(0xffffffffu, s, 1);
-      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      int s16 = q0 + q1 + q2 + q3;
+      s16 += __shfl_xor_sync(0xffffffffu, s16, 1);
+      s16 += __shfl_xor_sync(0xffffffffu, s16, 2);
+      const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 4);
       if (ok) {
-        *(uint32_t*)(xq + (int64_t)b * k + i) = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
-        if ((threadIdx.x & 3) == 0) xs[(int64_t)b * (k >> 4) + (i >> 4)] = d * (float)s;
-        if ((threadIdx.x & 7) == 0) xd[(int64_t)b * (k >> 5) + (i >> 5)] = d;
+        *(uint32_t*)(xq + (int64_t)b * k + act_chunk_off(i >> 4) + (i & 15)) =
+            (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
+        if ((threadIdx.x & 3) == 0) xs[(int64_t)b * (k >> 4) + (i >> 4)] = s16;
+        if ((threadIdx.x & 7) == 0) {
+          xd[(int64_t)b * (k >> 5) + (i >> 5)] = d;
+          uint32_t* rec = xm + ((int64_t)b * (k >> 6) + (i >> 6)) * 4 + ((i >> 5) & 1);
+          rec[0] = __float_as_uint(d);
+          rec[2] = (uint32_t)s32;
+        }
       }
     }
   }
@@ -105,23 +113,72 @@ __device__ void stage_x_f32(const GemvX& X, float* xf, float* red) {
 }
 
 // ---- row loops ---------------------------------------------------------------------------
+// A warp takes GEMV_RG consecutive rows at a time and its lanes stride over the flattened
+// (row, unit) space of that group, so every lane has several independent 16-byte weight loads
+// in flight even when a single row is only a few units long.
+constexpr int GEMV_RG = 4;
+
 template <int QT, int B>
-__device__ __forceinline__ void rows_q8(const GemvSeg& S, int r0, int r1, const ActView& a, float* rowacc, int s) {
+__device__ __forceinline__ void rows_q8(const GemvSeg& S, int r0, int r1, const ActView& a, float* rowacc, float* part, int s) {
   const int upr = dev_units_per_row(QT, S.k);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  for (int r = r0 + warp; r < r1; r += nw) {
-    const uint8_t* row = S.W + (int64_t)r * S.stride;
-    float acc[B];
+  const int ngroups = (r1 - r0 + GEMV_RG - 1) / GEMV_RG;
+  // few rows per CTA: several warps share one row group (each takes every `share`-th slice of
+  // 32 units) and their partial sums are combined through shared memory in a fixed order
+  const int share = ngroups >= nw || ngroups == 0 ? 1 : nw / ngroups;
+  const int gstep = share == 1 ? nw : ngroups;           // share > 1: every group is visited once
+  const int sub = share == 1 ? 0 : warp % share;
+  for (int gi = share == 1 ? warp : warp / share; gi < ngroups; gi += gstep) {
+    const int g0 = r0 + gi * GEMV_RG;
+    const int rows = min(GEMV_RG, r1 - g0);
+    const uint8_t* base = S.W + (int64_t)g0 * S.stride;
+    const int total = rows * upr;
+    float acc[GEMV_RG][B];
 #pragma unroll
-    for (int b = 0; b < B; ++b) acc[b] = 0.f;
+    for (int r = 0; r < GEMV_RG; ++r)
+#pragma unroll
+      for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
+    int rl = 0, u = sub * 32 + lane;            // row within the group, unit within the row
+    while (u >= upr) { u -= upr; ++rl; }
+    const int fstep = 32 * share;
 #pragma unroll 4
-    for (int u = lane; u < upr; u += 32) unit_dot<QT, B>(row, u, a, acc);
+    for (int f = sub * 32 + lane; f < total; f += fstep) {
+      float t[B];
 #pragma unroll
-    for (int b = 0; b < B; ++b) acc[b] = warp_sum(acc[b]);
+      for (int b = 0; b < B; ++b) t[b] = 0.f;
+      unit_dot<QT, B>(base + (int64_t)rl * S.stride, u, a, t);
+#pragma unroll
+      for (int r = 0; r < GEMV_RG; ++r)
+#pragma unroll
+        for (int b = 0; b < B; ++b) acc[r][b] += rl == r ? t[b] : 0.f;
+      u += fstep;
+      while (u >= upr) { u -= upr; ++rl; }
+    }
+#pragma unroll
+    for (int r = 0; r < GEMV_RG; ++r)
+#pragma unroll
+      for (int b = 0; b < B; ++b) acc[r][b] = warp_sum(acc[r][b]);
     if (lane == 0) {
 #pragma unroll
-      for (int b = 0; b < B; ++b) rowacc[((r - r0) * 2 + s) * B + b] = acc[b];
+      for (int r = 0; r < GEMV_RG; ++r) {
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+          if (share == 1) { if (r < rows) rowacc[((g0 + r - r0) * 2 + s) * B + b] = acc[r][b]; }
+          else part[(warp * GEMV_RG + r) * B + b] = acc[r][b];
+        }
+      }
     }
+    if (share > 1) break;                       // one group per warp in the shared regime
+  }
+  if (share > 1) {                              // uniform over the CTA
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < (r1 - r0) * B; idx += blockDim.x) {
+      const int rl = idx / B, b = idx - rl * B, gi = rl / GEMV_RG, r = rl - gi * GEMV_RG;
+      float v = 0.f;
+      for (int w = 0; w < share; ++w) v += part[((gi * share + w) * GEMV_RG + r) * B + b];
+      rowacc[(rl * 2 + s) * B + b] = v;
+    }
+    __syncthreads();
   }
 }
 
@@ -174,7 +231,7 @@ __device__ void rows_f32(const GemvSeg& S, int r0, int r1, const float* xf, floa
 }
 
 template <int B, bool FAST>
-__global__ void __launch_bounds__(GEMV_THREADS, (FAST && B <= 2 ? 2 : 1)) gemv_kernel(const __grid_constant__ GemvParams p) {
+__global__ void __launch_bounds__(GEMV_THREADS, (FAST && B <= 1 ? 2 : 1)) gemv_kernel(const __grid_constant__ GemvParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   int m = 0;
   while (m + 1 < p.nmat && (int)blockIdx.x >= p.mat[m + 1].cta_begin) ++m;
@@ -195,30 +252,32 @@ __global__ void __launch_bounds__(GEMV_THREADS, (FAST && B <= 2 ? 2 : 1)) gemv_k
   const int kq = p.max_k;
   constexpr bool fast = FAST;
   int8_t* xq = (int8_t*)smem;
-  float* xd = (float*)(smem + (size_t)B * kq);
-  float* xs = xd + (size_t)B * (kq >> 5);
+  uint32_t* xm = (uint32_t*)(smem + (size_t)B * kq);
+  float* xd = (float*)(xm + (size_t)B * (kq >> 6) * 4);
+  int32_t* xs = (int32_t*)(xd + (size_t)B * (kq >> 5));
   float* xf = (float*)smem;
-  const size_t act_bytes = !FAST ? (size_t)B * kq * 4 : (size_t)B * kq + (size_t)B * (kq >> 5) * 4 + (size_t)B * (kq >> 4) * 4;
+  const size_t act_bytes = !FAST ? (size_t)B * kq * 4 : (size_t)B * kq + (size_t)B * (kq >> 6) * 16 + (size_t)B * (kq >> 5) * 4 + (size_t)B * (kq >> 4) * 4;
   float* red = (float*)(smem + ((act_bytes + 15) & ~(size_t)15));
-  float* rowacc = red + 40;
+  float* part = red + 40;                                  // [warps][GEMV_RG][B] partial sums
+  float* rowacc = part + (GEMV_THREADS / 32) * GEMV_RG * B;
 
   int staged = -1;
   for (int s = 0; s < M.nseg; ++s) {
     const GemvSeg& S = M.seg[s];
     if (S.x_id != staged) {
       __syncthreads();
-      if constexpr (fast) stage_x_q8<B>(p.xs[S.x_id], xq, xd, xs, red); else stage_x_f32<B>(p.xs[S.x_id], xf, red);
+      if constexpr (fast) stage_x_q8<B>(p.xs[S.x_id], xq, xd, xs, xm, red); else stage_x_f32<B>(p.xs[S.x_id], xf, red);
       staged = S.x_id;
       __syncthreads();
     }
     if constexpr (fast) {
-      const ActView a{xq, xd, xs, S.k};
+      const ActView a{xq, xd, xs, (const U4*)xm, S.k};
       switch (S.qtype) {
-        case QT_Q4_K: rows_q8<QT_Q4_K, B>(S, r0, r1, a, rowacc, s); break;
-        case QT_Q5_K: rows_q8<QT_Q5_K, B>(S, r0, r1, a, rowacc, s); break;
-        case QT_Q6_K: rows_q8<QT_Q6_K, B>(S, r0, r1, a, rowacc, s); break;
-        case QT_Q8_0: rows_q8<QT_Q8_0, B>(S, r0, r1, a, rowacc, s); break;
-        default: rows_q8<QT_Q4_0, B>(S, r0, r1, a, rowacc, s); break;
+        case QT_Q4_K: rows_q8<QT_Q4_K, B>(S, r0, r1, a, rowacc, part, s); break;
+        case QT_Q5_K: rows_q8<QT_Q5_K, B>(S, r0, r1, a, rowacc, part, s); break;
+        case QT_Q6_K: rows_q8<QT_Q6_K, B>(S, r0, r1, a, rowacc, part, s); break;
+        case QT_Q8_0: rows_q8<QT_Q8_0, B>(S, r0, r1, a, rowacc, part, s); break;
+        default: rows_q8<QT_Q4_0, B>(S, r0, r1, a, rowacc, part, s); break;
       }
     } else {
       rows_f32<B>(S, r0, r1, xf, rowacc, s);
@@ -251,8 +310,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, (FAST && B <= 2 ? 2 : 1)) gemv_k
 
 size_t gemv_smem_bytes(const GemvParams& p) {
   const size_t B = (size_t)p.batch, kq = (size_t)p.max_k;
-  const size_t act = p.any_generic ? B * kq * 4 : B * kq + B * (kq >> 5) * 4 + B * (kq >> 4) * 4;
-  return ((act + 15) & ~(size_t)15) + 40 * 4 + (size_t)p.max_rows * 2 * B * 4;
+  const size_t act = p.any_generic ? B * kq * 4 : B * kq + B * (kq >> 6) * 16 + B * (kq >> 5) * 4 + B * (kq >> 4) * 4;
+  return ((act + 15) & ~(size_t)15) + 40 * 4 + (size_t)(GEMV_THREADS / 32) * GEMV_RG * B * 4 + (size_t)p.max_rows * 2 * B * 4;
 }
 
 template <int B, bool FAST>
@@ -292,7 +351,7 @@ int rlz_gemv(const rlz::GemvParams* pp, void* stream) {
       if (!f) any_generic = 1;
       if (m > 0 && (int)!f != any_generic) return -3;   // and so is a launch
       if (S.x_id < 0 || S.x_id >= GEMV_MAX_X || p.xs[S.x_id].k != S.k) return -4;
-      if (S.k % 32 || (S.stride & 15) || ((uintptr_t)S.W & 15)) return -5;
+      if (S.k % 32 || (f && S.k % 64) || (S.stride & 15) || ((uintptr_t)S.W & 15)) return -5;   // int8 path stages 64-value groups
       if (qtype_block_elems(S.qtype) == 0 || S.k % qtype_block_elems(S.qtype)) return -6;
       if (S.k > max_k) max_k = S.k;
     }

@@ -225,6 +225,11 @@ class StepBuffers:
     attn_counters: torch.Tensor
 
 
+def _is_fast(w: DeviceWeight) -> bool:
+    from ..quant.device_layout import FAST_TYPES
+    return QType(w.qtype) in FAST_TYPES
+
+
 class DecodePlan:
     """The launch sequence of one decode step for a fixed batch size; ``run()`` issues it on
     the current stream (eagerly or under graph capture)."""
@@ -238,6 +243,27 @@ class DecodePlan:
         self.keep.append(p)
         self.thunks.append(lambda p=p: ops.gemv_launch(p))
         self.kernel_launches += 1
+
+    def add_gemv_auto(self, xs, mats, y, batch, ldy, residual=None, ld_res=None, target_ctas=296):
+        """Emit one GEMV launch, or several when the matrices mix int8-fast-path block types with
+        generic ones (a launch is homogeneous).  A two-matrix accumulate of mixed kinds becomes two
+        launches, the second one accumulating onto the output of the first."""
+        fast, generic = [], []
+        for m in mats:
+            kinds = {_is_fast(w) for w, _ in m.segs}
+            if len(kinds) == 2:
+                if m.combine != COMBINE_ADD or m.out_off != 0 or len(mats) != 1:
+                    raise ValueError("gated pairs must share a block-type family")
+                (w0, x0), (w1, x1) = m.segs
+                first = MatOut([(w0, 0)], bias=m.bias, act=ACT_NONE, residual=m.residual)
+                self.add_gemv(ops.build_gemv_params([xs[x0]], [first], y, batch, ldy=ldy, residual=residual, ld_res=ld_res, target_ctas=target_ctas))
+                second = MatOut([(w1, 0)], bias=m.bias2, act=m.act, residual=True)
+                self.add_gemv(ops.build_gemv_params([xs[x1]], [second], y, batch, ldy=ldy, residual=y, ld_res=ldy, target_ctas=target_ctas))
+                return
+            (fast if kinds == {True} else generic).append(m)
+        for group in (fast, generic):
+            if group:
+                self.add_gemv(ops.build_gemv_params(xs, group, y, batch, ldy=ldy, residual=residual, ld_res=ld_res, target_ctas=target_ctas))
 
     def add_attn(self, p):
         self.keep.append(p)
@@ -288,7 +314,7 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
                     MatOut([(L.v, 0)], out_off=qd + kvd, bias=L.v_b)]
             if cfg.parallel_residual:
                 mats.append(MatOut([(L.up, 0)], out_off=model.act_col0 + L.down_in_off, bias=L.up_b, act=ACT_GELU if cfg.constraints.activation == "gelu" else ops.ACT_SILU))
-            plan.add_gemv(ops.build_gemv_params([xin], mats, buf.y1[c0:], cb, ldy=ld1, target_ctas=target))
+            plan.add_gemv_auto([xin], mats, buf.y1[c0:], cb, ld1, target_ctas=target)
         plan.add_attn(ops.build_attn_decode_params(
             buf.y1, buf.attn_out[:, L.o_in_off:], kc, vc, buf.positions, buf.page_table, buf.attn_partial, buf.attn_counters,
             model.heads, model.kv_heads, hd, splits, batch, cfg.rope_dim if cfg.uses_rope else 0, cfg.rope_type, cfg.rope_theta,
@@ -299,16 +325,16 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
                 m_in = VecIn(buf.y1[c0:, model.act_col0:], L.down.k, ld=ld1)
                 mat = MatOut([(L.o, 0), (L.down, 1)], bias=L.o_b, bias2=L.down_b, combine=COMBINE_ADD, residual=not tp)
                 dst = buf.partial_out if tp else buf.x
-                plan.add_gemv(ops.build_gemv_params([a_in, m_in], [mat], dst[c0:], cb, ldy=dst.stride(0), residual=None if tp else buf.x[c0:],
-                                                    ld_res=buf.x.stride(0), target_ctas=target))
+                plan.add_gemv_auto([a_in, m_in], [mat], dst[c0:], cb, dst.stride(0), residual=None if tp else buf.x[c0:],
+                                   ld_res=buf.x.stride(0), target_ctas=target)
             if tp:
                 plan.add(lambda: reduce_into_x(buf.partial_out[:batch]), launches=1)
         else:
             for c0, cb in chunks:
                 a_in = VecIn(buf.attn_out[c0:], L.o.k, ld=buf.attn_out.stride(0))
                 dst = buf.partial_out if tp else buf.x
-                plan.add_gemv(ops.build_gemv_params([a_in], [MatOut([(L.o, 0)], bias=L.o_b, residual=not tp)], dst[c0:], cb, ldy=dst.stride(0),
-                                                    residual=None if tp else buf.x[c0:], ld_res=buf.x.stride(0), target_ctas=target))
+                plan.add_gemv_auto([a_in], [MatOut([(L.o, 0)], bias=L.o_b, residual=not tp)], dst[c0:], cb, dst.stride(0),
+                                   residual=None if tp else buf.x[c0:], ld_res=buf.x.stride(0), target_ctas=target)
             if tp:
                 plan.add(lambda: reduce_into_x(buf.partial_out[:batch]), launches=1)
             for c0, cb in chunks:
@@ -318,19 +344,19 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
                     mat = MatOut([(L.gate, 0), (L.up, 0)], combine=comb, bias2=L.up_b)
                 else:
                     mat = MatOut([(L.up, 0)], bias=L.up_b, act=ACT_GELU if cfg.constraints.activation == "gelu" else ops.ACT_SILU)
-                plan.add_gemv(ops.build_gemv_params([xin], [mat], buf.act[c0:, L.down_in_off:], cb, ldy=buf.act.stride(0), target_ctas=target))
+                plan.add_gemv_auto([xin], [mat], buf.act[c0:, L.down_in_off:], cb, buf.act.stride(0), target_ctas=target)
             for c0, cb in chunks:
                 d_in = VecIn(buf.act[c0:], L.down.k, ld=buf.act.stride(0))
                 dst = buf.partial_out if tp else buf.x
-                plan.add_gemv(ops.build_gemv_params([d_in], [MatOut([(L.down, 0)], bias=L.down_b, residual=not tp)], dst[c0:], cb, ldy=dst.stride(0),
-                                                    residual=None if tp else buf.x[c0:], ld_res=buf.x.stride(0), target_ctas=target))
+                plan.add_gemv_auto([d_in], [MatOut([(L.down, 0)], bias=L.down_b, residual=not tp)], dst[c0:], cb, dst.stride(0),
+                                   residual=None if tp else buf.x[c0:], ld_res=buf.x.stride(0), target_ctas=target)
             if tp:
                 plan.add(lambda: reduce_into_x(buf.partial_out[:batch]), launches=1)
 
     for c0, cb in chunks:
         xin = VecIn(buf.x[c0:], H, ld=buf.x.stride(0), norm=norm_t, norm_w=model.out_norm_w, norm_b=model.out_norm_b, eps=cfg.eps)
-        plan.add_gemv(ops.build_gemv_params([xin], [MatOut([(model.lm_head, 0)], bias=model.lm_head_b)], buf.logits[c0:], cb,
-                                            ldy=buf.logits.stride(0), target_ctas=2 * sm_count))
+        plan.add_gemv_auto([xin], [MatOut([(model.lm_head, 0)], bias=model.lm_head_b)], buf.logits[c0:], cb,
+                           buf.logits.stride(0), target_ctas=2 * sm_count)
     if tp:
         plan.add(lambda: comm.gather_logits_(buf.logits[:batch], model), launches=0)
     if greedy_only:

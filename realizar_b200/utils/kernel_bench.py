@@ -1,0 +1,138 @@
+"""Per-kernel micro-benchmarks with roofline fractions.
+
+    python -m realizar_b200.utils.kernel_bench gemv --qtype Q4_K --n 200000 --k 2560 --batch 1
+    python -m realizar_b200.utils.kernel_bench attn --heads 32 --kv-heads 32 --head-dim 80 --ctx 4096 --batch 8
+    python -m realizar_b200.utils.kernel_bench gemm --qtype Q4_K --n 10240 --k 2560 --m 512
+
+Each kernel is timed with CUDA events after warm-up.  Working sets are larger than the 126 MB
+L2 (or rotated over several copies) so the numbers are DRAM numbers.  The achieved rate is
+reported against the measured copy bandwidth / GEMM throughput of this machine when a
+``MEASURED_PEAKS.json`` is present in the working directory, else against 6650 GB/s and
+1590 TFLOP/s.  (Role of the reference's brick budgets, src/brick/mod.rs:47-442.)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+
+def peaks():
+    for p in ("MEASURED_PEAKS.json", os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json")):
+        if os.path.exists(p):
+            d = json.load(open(p))
+            return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def time_cuda(fn, iters: int, warmup: int = 3) -> float:
+    """Median milliseconds per call over ``iters`` timed calls (events on the current stream)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return float(np.median(times))
+
+
+def random_weight(n: int, k: int, qtype, device):
+    """Random valid blocks of ``qtype`` generated on the device, in the device layout."""
+    from .. import ops
+    from ..quant.torch_quant import quantize_torch
+    step = max(1, (32 << 20) // k)
+    parts = [quantize_torch(torch.randn(min(step, n - r), k, device=device) * 0.02, qtype) for r in range(0, n, step)]
+    data = torch.cat(parts) if len(parts) > 1 else parts[0]
+    return ops.upload_weight(data, qtype, n, k, device)
+
+
+def bench_gemv(a):
+    from .. import ops
+    from ..quant import QType
+    qt = QType[a.qtype]
+    dev = torch.device("cuda")
+    w = random_weight(a.n, a.k, qt, dev)
+    x = torch.randn(a.batch, a.k, device=dev)
+    y = torch.empty(a.batch, a.n, device=dev)
+    g = torch.rand(a.k, device=dev) + 0.5
+    xin = ops.VecIn(x, a.k, norm=ops.NORM_RMS if a.norm else ops.NORM_NONE, norm_w=g if a.norm else None)
+    p = ops.build_gemv_params([xin], [ops.MatOut([(w, 0)])], y, a.batch, target_ctas=a.ctas)
+    ms = time_cuda(lambda: ops.gemv_launch(p), a.iters)
+    byts = w.nbytes + x.numel() * 4 + y.numel() * 4
+    pk = peaks()
+    return {"kernel": "gemv", "qtype": a.qtype, "n": a.n, "k": a.k, "batch": a.batch, "ms": ms, "bytes": byts,
+            "gbs": byts / ms / 1e6, "frac_of_%s_hbm" % pk["source"]: byts / ms / 1e6 / pk["hbm_gbs"],
+            "l2_note": "weights %.0f MB %s L2" % (w.nbytes / 1e6, ">" if w.nbytes > 126e6 else "<=")}
+
+
+def bench_attn(a):
+    from .. import ops
+    dev = torch.device("cuda")
+    B, H, Hkv, d, ctx = a.batch, a.heads, a.kv_heads, a.head_dim, a.ctx
+    pages_per_seq = -(-ctx // 16)
+    n_pages = B * pages_per_seq
+    kc = (torch.randn(n_pages, Hkv, 16, d, device=dev) * 0.5).to(torch.bfloat16)
+    vc = (torch.randn(n_pages, Hkv, 16, d, device=dev) * 0.5).to(torch.bfloat16)
+    pt = torch.randperm(n_pages, device=dev).to(torch.int32).reshape(B, pages_per_seq).contiguous()
+    qkv = torch.randn(B, (H + 2 * Hkv) * d, device=dev)
+    out = torch.empty(B, H * d, device=dev)
+    pos = torch.full((B,), ctx - 1, device=dev, dtype=torch.int32)
+    splits = a.splits or max(1, min(32, (2 * 148) // (Hkv * B)))
+    partial, counters = ops.attn_decode_scratch(B, H, splits, d, dev)
+    p = ops.build_attn_decode_params(qkv, out, kc, vc, pos, pt, partial, counters, H, Hkv, d, splits, B, a.rope_dim, 2, 1e4, 0, H * d, (H + Hkv) * d)
+    ms = time_cuda(lambda: ops.attn_decode_launch(p), a.iters)
+    byts = 2 * B * ctx * Hkv * d * 2
+    pk = peaks()
+    return {"kernel": "attn_decode", "batch": B, "heads": H, "kv_heads": Hkv, "head_dim": d, "ctx": ctx, "splits": splits, "ms": ms,
+            "kv_bytes": byts, "gbs": byts / ms / 1e6, "frac_of_%s_hbm" % pk["source"]: byts / ms / 1e6 / pk["hbm_gbs"],
+            "l2_note": "KV %.0f MB %s L2" % (byts / 1e6, ">" if byts > 126e6 else "<=")}
+
+
+def bench_gemm(a):
+    from ..ops import gemm as gemm_ops
+    from ..quant import QType
+    dev = torch.device("cuda")
+    qt = QType[a.qtype]
+    w = random_weight(a.n, a.k, qt, dev)
+    x = (torch.randn(a.m, a.k, device=dev)).to(torch.bfloat16)
+    y = torch.empty(a.m, a.n, device=dev, dtype=torch.float32)
+    plan = gemm_ops.GemmPlan(w, a.m, dev)
+    ms = time_cuda(lambda: plan.run(x, y), a.iters)
+    flops = 2.0 * a.m * a.n * a.k
+    pk = peaks()
+    return {"kernel": "gemm_kquant_tcgen05", "qtype": a.qtype, "m": a.m, "n": a.n, "k": a.k, "ms": ms, "tflops": flops / ms / 1e9,
+            "frac_of_%s_bf16" % pk["source"]: flops / ms / 1e9 / pk["bf16_tflops"],
+            "weight_gbs": w.nbytes / ms / 1e6, "frac_of_%s_hbm_weights" % pk["source"]: w.nbytes / ms / 1e6 / pk["hbm_gbs"]}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("gemv")
+    g.add_argument("--qtype", default="Q4_K"); g.add_argument("--n", type=int, default=200000); g.add_argument("--k", type=int, default=2560)
+    g.add_argument("--batch", type=int, default=1); g.add_argument("--iters", type=int, default=10); g.add_argument("--norm", action="store_true")
+    g.add_argument("--ctas", type=int, default=296)
+    t = sub.add_parser("attn")
+    t.add_argument("--heads", type=int, default=32); t.add_argument("--kv-heads", type=int, default=32); t.add_argument("--head-dim", type=int, default=80)
+    t.add_argument("--ctx", type=int, default=4096); t.add_argument("--batch", type=int, default=8); t.add_argument("--splits", type=int, default=0)
+    t.add_argument("--rope-dim", type=int, default=32); t.add_argument("--iters", type=int, default=10)
+    m = sub.add_parser("gemm")
+    m.add_argument("--qtype", default="Q4_K"); m.add_argument("--n", type=int, default=10240); m.add_argument("--k", type=int, default=2560)
+    m.add_argument("--m", type=int, default=512); m.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args(argv)
+    res = {"gemv": bench_gemv, "attn": bench_attn, "gemm": bench_gemm}[a.cmd](a)
+    print(json.dumps(res))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
