@@ -13,6 +13,7 @@
 // flash_decoding_chunk+reduce kernels (src/cuda/executor/kv_scatter.rs:15-388,
 // src/cuda/executor/flash_decoding_graphed.rs:14-209, src/cuda/executor/batch.rs:18-400).
 #include "common.cuh"
+#include "attn_decode_static.h"
 #include <cuda_bf16.h>
 #include <math.h>
 
@@ -279,6 +280,70 @@ int rlz_attn_decode(const rlz::AttnDecodeParams* pp, void* stream) {
   dim3 grid(p.n_kv_heads * hgroups, p.splits, p.batch), block(ATT_THREADS);
   cudaError_t e;
   cudaStream_t st = (cudaStream_t)stream;
+  switch (GT) {
+    case 1: e = launch(attn_decode_kernel<1>, grid, block, 0, st, p); break;
+    case 2: e = launch(attn_decode_kernel<2>, grid, block, 0, st, p); break;
+    case 8: e = launch(attn_decode_kernel<8>, grid, block, 0, st, p); break;
+    default: e = launch(attn_decode_kernel<4>, grid, block, 0, st, p); break;
+  }
+  return (int)e;
+}
+
+}  // extern "C"
+
+// ---- allocation-free variant: scratch lives in the library image (see attn_decode_static.h) -----
+namespace rlz {
+static __device__ __align__(256) float g_static_partial[RLZ_ATTN_STATIC_MAX_PARTIAL_FLOATS];
+static __device__ __align__(256) int32_t g_static_counters[RLZ_ATTN_STATIC_MAX_COUNTERS];
+
+constexpr int STATIC_MAX_DEVICES = 64;
+struct StaticScratch { float* partial; int32_t* counters; bool ready; };
+static StaticScratch g_static_scratch[STATIC_MAX_DEVICES];
+}  // namespace rlz
+
+extern "C" {
+
+const char* rlz_attn_decode_static_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case RLZ_STATIC_TOO_LARGE: return "attention launch needs more scratch than the built-in arrays hold (see attn_decode_static.h for the limits)";
+    case RLZ_STATIC_NO_DEVICE: return "no current CUDA device, or its ordinal is beyond the supported range";
+    default: return code < 0 ? "invalid attention parameters" : "CUDA error (see cudaGetErrorString)";
+  }
+}
+
+int rlz_attn_decode_static(const rlz::AttnDecodeParams* pp, void* stream) {
+  using namespace rlz;
+  AttnDecodeParams p = *pp;
+  if (p.head_dim % 8 || p.head_dim > 128 || p.head_dim < 8) return -1;
+  if (p.n_kv_heads < 1 || p.n_heads % p.n_kv_heads || p.splits < 1 || p.batch < 1) return -2;
+  if (p.rope_dim > p.head_dim || (p.rope_dim & 1)) return -3;
+  if (((uintptr_t)p.k_cache & 15) || ((uintptr_t)p.v_cache & 15)) return -4;
+  const long long need_f = (long long)p.batch * p.n_heads * p.splits * (p.head_dim + 2);
+  const long long need_c = (long long)p.batch * p.n_heads;
+  if (need_f > RLZ_ATTN_STATIC_MAX_PARTIAL_FLOATS || need_c > RLZ_ATTN_STATIC_MAX_COUNTERS) return RLZ_STATIC_TOO_LARGE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= STATIC_MAX_DEVICES) return RLZ_STATIC_NO_DEVICE;
+  cudaStream_t st = (cudaStream_t)stream;
+  StaticScratch& sc = g_static_scratch[dev];
+  if (!sc.ready) {
+    // In host code the array names are stand-ins; the device addresses come from the runtime,
+    // once per device, with that device current.
+    cudaError_t e = cudaGetSymbolAddress((void**)&sc.partial, g_static_partial);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaGetSymbolAddress((void**)&sc.counters, g_static_counters);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaMemsetAsync(sc.counters, 0, sizeof(int32_t) * RLZ_ATTN_STATIC_MAX_COUNTERS, st);   // counters must start at zero
+    if (e != cudaSuccess) return (int)e;
+    sc.ready = true;
+  }
+  p.partial = sc.partial;
+  p.counters = sc.counters;
+  const int G = p.n_heads / p.n_kv_heads;
+  const int GT = G == 1 ? 1 : G == 2 ? 2 : G == 8 ? 8 : 4;
+  const int hgroups = (G + GT - 1) / GT;
+  dim3 grid(p.n_kv_heads * hgroups, p.splits, p.batch), block(ATT_THREADS);
+  cudaError_t e;
   switch (GT) {
     case 1: e = launch(attn_decode_kernel<1>, grid, block, 0, st, p); break;
     case 2: e = launch(attn_decode_kernel<2>, grid, block, 0, st, p); break;
