@@ -228,8 +228,12 @@ def main():
         }
         print(json.dumps(line))
     if world > 1:
+        # leave without tearing NCCL down: communicator destruction after graph-captured collectives can block
+        torch.cuda.synchronize(dev)
         dist.barrier()
-        dist.destroy_process_group()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     return 0
 
 

@@ -56,7 +56,8 @@ def cpu_lib() -> ctypes.CDLL:
 
 
 def cuda_lib_path() -> Path:
-    return _build.LIB / "librlz_cuda.so"
+    """The kernel library; ``RLZ_CUDA_LIB`` may point at an alternative build (kernel tuning runs)."""
+    return Path(os.environ["RLZ_CUDA_LIB"]) if os.environ.get("RLZ_CUDA_LIB") else _build.LIB / "librlz_cuda.so"
 
 
 def cuda_lib() -> ctypes.CDLL:

@@ -1,7 +1,7 @@
 // Host emulation of the GPU decode GEMV: runs the very same unit functions the kernel runs
 // (csrc/gemv_units.h) over weights in the device layout, so the bit manipulation of every
 // fast-path block type is verifiable without a GPU.
-#include "gemv_units.h"
+#include "gemv_blocks.h"
 
 #include <vector>
 
@@ -46,6 +46,32 @@ int rlz_emu_gemv(int qtype, const void* W, int64_t stride, const float* x, float
     case QT_Q4_0: emu_rows<QT_Q4_0>(w, stride, a, y, n, k, batch); return 0;
     default: return -2;
   }
+}
+
+
+// Same product through the half-block functions of the streamed GEMV (csrc/gemv_blocks.h).
+int rlz_emu_gemv_blocks(int qtype, const void* W, int64_t stride, const float* x, float* y, int64_t n, int k, int batch) {
+  if (k % 256 || dev_block_bytes(qtype) == 0) return -1;
+  std::vector<int8_t> q((size_t)batch * k); std::vector<U4> rec4((size_t)batch * (k / 64)); std::vector<F2> rec6((size_t)batch * (k / 16));
+  for (int b = 0; b < batch; ++b)
+    quantize_act_row_blk(x + (int64_t)b * k, k, q.data() + (int64_t)b * k, rec4.data() + (int64_t)b * (k / 64), rec6.data() + (int64_t)b * (k / 16));
+  const int bb = dev_block_bytes(qtype), nsb = k / 256;
+  for (int64_t r = 0; r < n; ++r)
+    for (int b = 0; b < batch; ++b) {
+      ActBlk ab{q.data() + (int64_t)b * k, rec4.data() + (int64_t)b * (k / 64), rec6.data() + (int64_t)b * (k / 16), k, nsb};
+      float acc = 0.f;
+      for (int sb = 0; sb < nsb; ++sb)
+        for (int h = 0; h < 2; ++h) {
+          const uint8_t* blk = (const uint8_t*)W + r * stride + (int64_t)sb * bb;
+          float t = 0.f;
+          if (qtype == QT_Q4_K) halfblock_dot<QT_Q4_K, 1>(blk, sb, h, ab, &t);
+          else if (qtype == QT_Q5_K) halfblock_dot<QT_Q5_K, 1>(blk, sb, h, ab, &t);
+          else halfblock_dot<QT_Q6_K, 1>(blk, sb, h, ab, &t);
+          acc += t;
+        }
+      y[(int64_t)b * n + r] = acc;
+    }
+  return 0;
 }
 
 }  // extern "C"

@@ -13,51 +13,23 @@
 #include "common.cuh"
 #include "../gemv_units.h"
 #include "gemv_params.h"
+#include "gemv_common.cuh"
 
 namespace rlz {
 
 constexpr int GEMV_THREADS = 512;
-
-// ---- input staging ---------------------------------------------------------------------
-// mean / rstd of one input row (block-wide).  LayerNorm uses two passes for accuracy.
-__device__ void row_stats(const GemvX& X, const float* x, float* red, float* mean_out, float* rstd_out) {
-  float mean = 0.f, rstd = 1.f;
-  if (X.norm == NORM_RMS) {
-    float ss = 0.f;
-    for (int i = threadIdx.x * 4; i < X.k; i += blockDim.x * 4) {
-      const float4 v = *(const float4*)(x + i);
-      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-    }
-    ss = block_sum(ss, red);
-    rstd = rsqrtf(ss / (float)X.k + X.eps);
-  } else if (X.norm == NORM_LAYER) {
-    float s = 0.f;
-    for (int i = threadIdx.x * 4; i < X.k; i += blockDim.x * 4) {
-      const float4 v = *(const float4*)(x + i);
-      s += v.x + v.y + v.z + v.w;
-    }
-    mean = block_sum(s, red) / (float)X.k;
-    float ss = 0.f;
-    for (int i = threadIdx.x * 4; i < X.k; i += blockDim.x * 4) {
-      const float4 v = *(const float4*)(x + i);
-      const float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
-      ss += a * a + b * b + c * c + d * d;
-    }
-    ss = block_sum(ss, red);
-    rstd = rsqrtf(ss / (float)X.k + X.eps);
-  }
-  *mean_out = mean; *rstd_out = rstd;
-}
-
-__device__ __forceinline__ float4 load_normed(const GemvX& X, const float* x, int i, float mean, float rstd) {
-  float4 v = *(const float4*)(x + i);
-  if (X.norm != NORM_NONE) {
-    v.x = (v.x - mean) * rstd; v.y = (v.y - mean) * rstd; v.z = (v.z - mean) * rstd; v.w = (v.w - mean) * rstd;
-    if (X.nw) { const float4 w = __ldg((const float4*)(X.nw + i)); v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w; }
-    if (X.nb) { const float4 b = __ldg((const float4*)(X.nb + i)); v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w; }
-  }
-  return v;
-}
+#ifndef GEMV_OCC2_MAXB
+#define GEMV_OCC2_MAXB 1          // batch sizes up to this run two CTAs per SM (64 registers per thread)
+#endif
+#ifndef GEMV_UNROLL
+#define GEMV_UNROLL 1          // rolled unit loop: smaller code measured faster at decode sizes
+#endif
+#ifndef GEMV_RG_ROWS
+#define GEMV_RG_ROWS 4
+#endif
+#ifndef GEMV_REG_STAGING
+#define GEMV_REG_STAGING 0        // 1: stage the input through registers (larger code, one memory round trip)
+#endif
 
 // int8 staging in the ActView layout: xq[B][k] (chunk-rotated), xd[B][k/32], xs[B][k/16] (int sums),
 // xm[B][k/64] records {d0, d1, sum32_0, sum32_1}
@@ -116,7 +88,8 @@ __device__ void stage_x_f32(const GemvX& X, float* xf, float* red) {
 // A warp takes GEMV_RG consecutive rows at a time and its lanes stride over the flattened
 // (row, unit) space of that group, so every lane has several independent 16-byte weight loads
 // in flight even when a single row is only a few units long.
-constexpr int GEMV_RG = 4;
+constexpr int GEMV_RG = GEMV_RG_ROWS;
+constexpr int GEMV_UNROLL_C = GEMV_UNROLL;
 
 template <int QT, int B>
 __device__ __forceinline__ void rows_q8(const GemvSeg& S, int r0, int r1, const ActView& a, float* rowacc, float* part, int s) {
@@ -141,7 +114,7 @@ __device__ __forceinline__ void rows_q8(const GemvSeg& S, int r0, int r1, const 
     int rl = 0, u = sub * 32 + lane;            // row within the group, unit within the row
     while (u >= upr) { u -= upr; ++rl; }
     const int fstep = 32 * share;
-#pragma unroll 4
+#pragma unroll GEMV_UNROLL_C
     for (int f = sub * 32 + lane; f < total; f += fstep) {
       float t[B];
 #pragma unroll
@@ -231,7 +204,7 @@ __device__ void rows_f32(const GemvSeg& S, int r0, int r1, const float* xf, floa
 }
 
 template <int B, bool FAST>
-__global__ void __launch_bounds__(GEMV_THREADS, (FAST && B <= 1 ? 2 : 1)) gemv_kernel(const __grid_constant__ GemvParams p) {
+__global__ void __launch_bounds__(GEMV_THREADS, (FAST && B <= GEMV_OCC2_MAXB ? 2 : 1)) gemv_kernel(const __grid_constant__ GemvParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   int m = 0;
   while (m + 1 < p.nmat && (int)blockIdx.x >= p.mat[m + 1].cta_begin) ++m;
@@ -266,7 +239,30 @@ __global__ void __launch_bounds__(GEMV_THREADS, (FAST && B <= 1 ? 2 : 1)) gemv_k
     const GemvSeg& S = M.seg[s];
     if (S.x_id != staged) {
       __syncthreads();
-      if constexpr (fast) stage_x_q8<B>(p.xs[S.x_id], xq, xd, xs, xm, red); else stage_x_f32<B>(p.xs[S.x_id], xf, red);
+      const GemvX& X = p.xs[S.x_id];
+      const bool in_regs = GEMV_REG_STAGING && X.k <= STAGE_MAXV * 4 * GEMV_THREADS;
+      if constexpr (fast) {
+        if (in_regs) {
+          const int k = X.k;
+          stage_rows_regs<B, true>(X, red,
+            [&](int b, int i, uint32_t packed, float d, int s16, int s32) {
+              *(uint32_t*)(xq + (int64_t)b * k + act_chunk_off(i >> 4) + (i & 15)) = packed;
+              if ((threadIdx.x & 3) == 0) xs[(int64_t)b * (k >> 4) + (i >> 4)] = s16;
+              if ((threadIdx.x & 7) == 0) {
+                xd[(int64_t)b * (k >> 5) + (i >> 5)] = d;
+                uint32_t* rec = xm + ((int64_t)b * (k >> 6) + (i >> 6)) * 4 + ((i >> 5) & 1);
+                rec[0] = __float_as_uint(d); rec[2] = (uint32_t)s32;
+              }
+            },
+            [](int, int, float4) {});
+        } else stage_x_q8<B>(X, xq, xd, xs, xm, red);
+      } else {
+        if (in_regs) {
+          const int k = X.k;
+          stage_rows_regs<B, false>(X, red, [](int, int, uint32_t, float, int, int) {},
+                                    [&](int b, int i, float4 w) { *(float4*)(xf + (int64_t)b * k + i) = w; });
+        } else stage_x_f32<B>(X, xf, red);
+      }
       staged = S.x_id;
       __syncthreads();
     }
@@ -276,8 +272,12 @@ __global__ void __launch_bounds__(GEMV_THREADS, (FAST && B <= 1 ? 2 : 1)) gemv_k
         case QT_Q4_K: rows_q8<QT_Q4_K, B>(S, r0, r1, a, rowacc, part, s); break;
         case QT_Q5_K: rows_q8<QT_Q5_K, B>(S, r0, r1, a, rowacc, part, s); break;
         case QT_Q6_K: rows_q8<QT_Q6_K, B>(S, r0, r1, a, rowacc, part, s); break;
+#ifndef GEMV_ONLY_KQ
         case QT_Q8_0: rows_q8<QT_Q8_0, B>(S, r0, r1, a, rowacc, part, s); break;
         default: rows_q8<QT_Q4_0, B>(S, r0, r1, a, rowacc, part, s); break;
+#else
+        default: break;
+#endif
       }
     } else {
       rows_f32<B>(S, r0, r1, xf, rowacc, s);
@@ -285,27 +285,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, (FAST && B <= 1 ? 2 : 1)) gemv_k
   }
   __syncthreads();
 
-  // epilogue
-  for (int idx = threadIdx.x; idx < (r1 - r0) * B; idx += blockDim.x) {
-    const int rl = idx / B, b = idx - rl * B, r = r0 + rl;
-    float v = rowacc[(rl * 2 + 0) * B + b];
-    if (M.nseg == 2) {
-      const float v1 = rowacc[(rl * 2 + 1) * B + b];
-      if (M.combine == COMBINE_ADD) v += v1;
-      else {
-        if (M.bias) v += M.bias[r];
-        if (M.bias2) { const float u = v1 + M.bias2[r]; v = (M.combine == COMBINE_SILU_MUL ? silu(v) : gelu_tanh(v)) * u; }
-        else v = (M.combine == COMBINE_SILU_MUL ? silu(v) : gelu_tanh(v)) * v1;
-      }
-    }
-    if (M.nseg == 1 || M.combine == COMBINE_ADD) {
-      if (M.bias) v += M.bias[r];
-      if (M.bias2) v += M.bias2[r];
-    }
-    if (M.act == ACT_GELU) v = gelu_tanh(v); else if (M.act == ACT_SILU) v = silu(v);
-    if (M.has_residual) v += p.residual[(int64_t)b * p.ld_res + r];
-    p.y[(int64_t)b * p.ldy + M.out_off + r] = v;
-  }
+  gemv_epilogue<B>(p, M, rowacc, r0, r1);
 }
 
 size_t gemv_smem_bytes(const GemvParams& p) {
@@ -317,11 +297,11 @@ size_t gemv_smem_bytes(const GemvParams& p) {
 template <int B, bool FAST>
 cudaError_t launch_gemv_t(const GemvParams& p, int grid, cudaStream_t stream) {
   const size_t smem = gemv_smem_bytes(p);
-  static bool configured = false;
-  if (smem > 48 * 1024 && !configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<B, FAST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  static size_t configured = 48 * 1024;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<B, FAST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    configured = true;
+    configured = smem;
   }
   return launch(gemv_kernel<B, FAST>, dim3(grid), dim3(GEMV_THREADS), smem, stream, p);
 }
@@ -339,6 +319,7 @@ int rlz_gemv(const rlz::GemvParams* pp, void* stream) {
   using namespace rlz;
   GemvParams p = *pp;
   if (p.nmat < 1 || p.nmat > GEMV_MAX_MATS || p.batch < 1 || p.batch > 4) return -1;
+  if (p.ar.enabled && (p.nmat != 1 || p.ar.world < 1 || p.ar.world > GEMV_AR_MAX_RANKS || p.mat[0].out_off != 0)) return -8;
   int grid = 0, max_rows = 0, max_k = 0, any_generic = 0;
   for (int m = 0; m < p.nmat; ++m) {
     GemvMat& M = p.mat[m];
@@ -360,7 +341,8 @@ int rlz_gemv(const rlz::GemvParams* pp, void* stream) {
     if (M.rows_per_cta > max_rows) max_rows = M.rows_per_cta;
   }
   p.max_k = max_k; p.max_rows = max_rows; p.any_generic = any_generic;
-  if (gemv_smem_bytes(p) > 227 * 1024) return -7;
+  if (gemv_smem_bytes(p) > 226 * 1024) return -7;
+  if (p.ar.enabled && p.mat[0].n > p.ar.n) return -9;
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
   switch (p.batch) {

@@ -42,6 +42,23 @@ struct GemvX {              // an input vector (batch rows `ld` floats apart) an
   int32_t _pad;
 };
 
+constexpr int GEMV_AR_MAX_RANKS = 8;
+
+// In-kernel all-reduce of the outputs of a row-parallel GEMV over peer memory (tensor parallel).
+// Low-latency protocol without fences or separate flags: every value travels as one 8-byte store
+// {float bits, step epoch}.  A rank stores its partial rows into slot [parity][rank] of every
+// rank's inbox; each output element is then polled (bounded) in every slot until its epoch word
+// matches, and the values are summed in rank order.  parity = epoch & 1 keeps a slot from being
+// overwritten while a slower rank still reads the previous step.
+// Inbox of one call site: [parity 2][rank][4 batch rows][n] pairs of 32-bit words.
+struct GemvAr {
+  uint2* inbox[GEMV_AR_MAX_RANKS];        // rank r's inbox for this call site (own entry = local memory)
+  const uint32_t* epoch;                  // device word, incremented once per step before the first use
+  int32_t* status;                        // device word receiving an error code when a wait expires
+  int64_t spin_limit;                     // polls per element before giving up
+  int32_t rank, world, enabled, n;        // n = elements per batch row in the inbox
+};
+
 struct GemvParams {
   GemvMat mat[GEMV_MAX_MATS];
   GemvX xs[GEMV_MAX_X];
@@ -55,6 +72,7 @@ struct GemvParams {
   int32_t max_rows;         // filled by the launcher
   int32_t any_generic;      // filled by the launcher
   int32_t _pad;
+  GemvAr ar;                // all-reduce of matrix 0's outputs (single-matrix launches only)
 };
 
 }  // namespace rlz

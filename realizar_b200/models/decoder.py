@@ -18,6 +18,7 @@ same kernels.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Callable, List, Optional
 
@@ -223,6 +224,9 @@ class StepBuffers:
     uniform: torch.Tensor
     attn_partial: torch.Tensor
     attn_counters: torch.Tensor
+    local_val: Optional[torch.Tensor] = None     # TP: this rank's best logit per sequence
+    local_idx: Optional[torch.Tensor] = None     # TP: its global token id
+    logits_full: Optional[torch.Tensor] = None   # TP sampling: gathered logits
 
 
 def _is_fast(w: DeviceWeight) -> bool:
@@ -234,17 +238,19 @@ class DecodePlan:
     """The launch sequence of one decode step for a fixed batch size; ``run()`` issues it on
     the current stream (eagerly or under graph capture)."""
 
-    def __init__(self):
+    def __init__(self, sm_count: int = 148):
+        self.sm_count = sm_count
         self.thunks: List[Callable[[], None]] = []
         self.keep: list = []
         self.kernel_launches = 0
 
-    def add_gemv(self, p):
+    def add_gemv(self, p, stream=False):
         self.keep.append(p)
-        self.thunks.append(lambda p=p: ops.gemv_launch(p))
+        fn = ops.gemv_stream_launch if stream else ops.gemv_launch
+        self.thunks.append(lambda p=p, fn=fn: fn(p))
         self.kernel_launches += 1
 
-    def add_gemv_auto(self, xs, mats, y, batch, ldy, residual=None, ld_res=None, target_ctas=296):
+    def add_gemv_auto(self, xs, mats, y, batch, ldy, residual=None, ld_res=None, target_ctas=296, ar=None):
         """Emit one GEMV launch, or several when the matrices mix int8-fast-path block types with
         generic ones (a launch is homogeneous).  A two-matrix accumulate of mixed kinds becomes two
         launches, the second one accumulating onto the output of the first."""
@@ -252,7 +258,7 @@ class DecodePlan:
         for m in mats:
             kinds = {_is_fast(w) for w, _ in m.segs}
             if len(kinds) == 2:
-                if m.combine != COMBINE_ADD or m.out_off != 0 or len(mats) != 1:
+                if m.combine != COMBINE_ADD or m.out_off != 0 or len(mats) != 1 or ar is not None:
                     raise ValueError("gated pairs must share a block-type family")
                 (w0, x0), (w1, x1) = m.segs
                 first = MatOut([(w0, 0)], bias=m.bias, act=ACT_NONE, residual=m.residual)
@@ -263,7 +269,9 @@ class DecodePlan:
             (fast if kinds == {True} else generic).append(m)
         for group in (fast, generic):
             if group:
-                self.add_gemv(ops.build_gemv_params(xs, group, y, batch, ldy=ldy, residual=residual, ld_res=ld_res, target_ctas=target_ctas))
+                st = group is fast and ops.stream_eligible(group)
+                self.add_gemv(ops.build_gemv_params(xs, group, y, batch, ldy=ldy, residual=residual, ld_res=ld_res,
+                                                    target_ctas=self.sm_count if st else target_ctas, ar=ar), stream=st)
 
     def add_attn(self, p):
         self.keep.append(p)
@@ -287,12 +295,12 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
     tensor-parallel communicator (``None`` on one GPU); it provides ``all_reduce_sum_(tensor)``.
     """
     cfg = model.cfg
-    plan = DecodePlan()
+    plan = DecodePlan(sm_count)
     H, hd = cfg.hidden_dim, cfg.head_dim
     qd, kvd, I = model.q_dim, model.kv_dim, model.inter
     norm_t = NORM_LAYER if cfg.uses_layernorm else NORM_RMS
     tp = model.tp_size > 1
-    target = 2 * sm_count if batch <= 2 else sm_count
+    target = int(os.environ.get("RLZ_GEMV_CTAS", 2 * sm_count if batch <= 1 else sm_count))   # register-path kernel: 2 CTAs/SM at batch 1
     chunks = [(c, min(4, batch - c)) for c in range(0, batch, 4)]       # GEMV kernels take <= 4 rows at a time
     qkv_w = qd + 2 * kvd
     ld1 = buf.y1.stride(0)
@@ -300,10 +308,35 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
     plan.add(lambda: ops.embed(model.embed_table, model.embed_qtype, model.embed_row_bytes, H, cfg.vocab_size, buf.tokens[:batch], buf.x,
                                model.pos_table, buf.positions))
 
+    fused = tp and getattr(comm, "fused", False)
+    site = [0]
+    if fused:
+        plan.add(comm.begin_step, launches=comm.step_launches())
+
     def reduce_into_x(partial_rows):
-        """TP: x += all_reduce(partial).  The residual add is one fused elementwise launch."""
+        """Baseline TP: x += all_reduce(partial) as a library collective plus one residual-add launch."""
         comm.all_reduce_sum_(partial_rows)
         ops.elementwise(partial_rows, residual=buf.x[:batch], out=buf.x[:batch])
+
+    def row_parallel(xs_of, mat_of):
+        """Emit the row-parallel GEMV(s) of a layer: x += W_shard . inputs (+ bias on rank 0), all-reduced
+        across ranks.  One GPU: a plain fused-residual GEMV.  Fused TP: the all-reduce happens inside the
+        kernel.  Baseline TP: partial sums, NCCL all-reduce, residual-add kernel."""
+        mixed = len({_is_fast(w) for w, _ in mat_of(True).segs}) == 2     # block-type families that cannot share a launch
+        use_ar = fused and not mixed
+        for c0, cb in chunks:
+            mat = mat_of(not tp or use_ar)
+            if not tp or use_ar:
+                ar = None
+                if use_ar:
+                    ar = comm.ar_desc(site[0])
+                    site[0] += 1
+                plan.add_gemv_auto(xs_of(c0), [mat], buf.x[c0:], cb, buf.x.stride(0), residual=buf.x[c0:], ld_res=buf.x.stride(0),
+                                   target_ctas=target, ar=ar)
+            else:
+                plan.add_gemv_auto(xs_of(c0), [mat], buf.partial_out[c0:], cb, buf.partial_out.stride(0), target_ctas=target)
+        if tp and not use_ar:
+            plan.add(lambda: reduce_into_x(buf.partial_out[:batch]), launches=1)
 
     for l, L in enumerate(model.layers):
         kc, vc = k_cache[l], v_cache[l]
@@ -313,30 +346,19 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
             mats = [MatOut([(L.q, 0)], out_off=0, bias=L.q_b), MatOut([(L.k, 0)], out_off=qd, bias=L.k_b),
                     MatOut([(L.v, 0)], out_off=qd + kvd, bias=L.v_b)]
             if cfg.parallel_residual:
-                mats.append(MatOut([(L.up, 0)], out_off=model.act_col0 + L.down_in_off, bias=L.up_b, act=ACT_GELU if cfg.constraints.activation == "gelu" else ops.ACT_SILU))
+                mats.append(MatOut([(L.up, 0)], out_off=model.act_col0 + L.down_in_off, bias=L.up_b,
+                                   act=ACT_GELU if cfg.constraints.activation == "gelu" else ops.ACT_SILU))
             plan.add_gemv_auto([xin], mats, buf.y1[c0:], cb, ld1, target_ctas=target)
         plan.add_attn(ops.build_attn_decode_params(
             buf.y1, buf.attn_out[:, L.o_in_off:], kc, vc, buf.positions, buf.page_table, buf.attn_partial, buf.attn_counters,
             model.heads, model.kv_heads, hd, splits, batch, cfg.rope_dim if cfg.uses_rope else 0, cfg.rope_type, cfg.rope_theta,
             0, qd, qd + kvd, L.q_norm_w, L.k_norm_w, cfg.eps, ld_qkv=ld1, ld_out=buf.attn_out.stride(0)))
         if cfg.parallel_residual:
-            for c0, cb in chunks:
-                a_in = VecIn(buf.attn_out[c0:], L.o.k, ld=buf.attn_out.stride(0))
-                m_in = VecIn(buf.y1[c0:, model.act_col0:], L.down.k, ld=ld1)
-                mat = MatOut([(L.o, 0), (L.down, 1)], bias=L.o_b, bias2=L.down_b, combine=COMBINE_ADD, residual=not tp)
-                dst = buf.partial_out if tp else buf.x
-                plan.add_gemv_auto([a_in, m_in], [mat], dst[c0:], cb, dst.stride(0), residual=None if tp else buf.x[c0:],
-                                   ld_res=buf.x.stride(0), target_ctas=target)
-            if tp:
-                plan.add(lambda: reduce_into_x(buf.partial_out[:batch]), launches=1)
+            row_parallel(lambda c0: [VecIn(buf.attn_out[c0:], L.o.k, ld=buf.attn_out.stride(0)), VecIn(buf.y1[c0:, model.act_col0:], L.down.k, ld=ld1)],
+                         lambda res: MatOut([(L.o, 0), (L.down, 1)], bias=L.o_b, bias2=L.down_b, combine=COMBINE_ADD, residual=res))
         else:
-            for c0, cb in chunks:
-                a_in = VecIn(buf.attn_out[c0:], L.o.k, ld=buf.attn_out.stride(0))
-                dst = buf.partial_out if tp else buf.x
-                plan.add_gemv_auto([a_in], [MatOut([(L.o, 0)], bias=L.o_b, residual=not tp)], dst[c0:], cb, dst.stride(0),
-                                   residual=None if tp else buf.x[c0:], ld_res=buf.x.stride(0), target_ctas=target)
-            if tp:
-                plan.add(lambda: reduce_into_x(buf.partial_out[:batch]), launches=1)
+            row_parallel(lambda c0: [VecIn(buf.attn_out[c0:], L.o.k, ld=buf.attn_out.stride(0))],
+                         lambda res: MatOut([(L.o, 0)], bias=L.o_b, residual=res))
             for c0, cb in chunks:
                 xin = VecIn(buf.x[c0:], H, ld=buf.x.stride(0), norm=norm_t, norm_w=L.ffn_norm_w, norm_b=L.ffn_norm_b, eps=cfg.eps)
                 if cfg.gated_ffn:
@@ -345,25 +367,31 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
                 else:
                     mat = MatOut([(L.up, 0)], bias=L.up_b, act=ACT_GELU if cfg.constraints.activation == "gelu" else ops.ACT_SILU)
                 plan.add_gemv_auto([xin], [mat], buf.act[c0:, L.down_in_off:], cb, buf.act.stride(0), target_ctas=target)
-            for c0, cb in chunks:
-                d_in = VecIn(buf.act[c0:], L.down.k, ld=buf.act.stride(0))
-                dst = buf.partial_out if tp else buf.x
-                plan.add_gemv_auto([d_in], [MatOut([(L.down, 0)], bias=L.down_b, residual=not tp)], dst[c0:], cb, dst.stride(0),
-                                   residual=None if tp else buf.x[c0:], ld_res=buf.x.stride(0), target_ctas=target)
-            if tp:
-                plan.add(lambda: reduce_into_x(buf.partial_out[:batch]), launches=1)
+            row_parallel(lambda c0: [VecIn(buf.act[c0:], L.down.k, ld=buf.act.stride(0))],
+                         lambda res: MatOut([(L.down, 0)], bias=L.down_b, residual=res))
 
     for c0, cb in chunks:
         xin = VecIn(buf.x[c0:], H, ld=buf.x.stride(0), norm=norm_t, norm_w=model.out_norm_w, norm_b=model.out_norm_b, eps=cfg.eps)
         plan.add_gemv_auto([xin], [MatOut([(model.lm_head, 0)], bias=model.lm_head_b)], buf.logits[c0:], cb,
-                           buf.logits.stride(0), target_ctas=2 * sm_count)
-    if tp:
-        plan.add(lambda: comm.gather_logits_(buf.logits[:batch], model), launches=0)
-    if greedy_only:
-        plan.add(lambda: ops.argmax(buf.logits[:batch], out=buf.sampled, vocab=cfg.vocab_size))
+                           buf.logits.stride(0), target_ctas=sm_count)
+    V = cfg.vocab_size
+    if tp and greedy_only:
+        def pick():
+            ops.argmax(buf.logits[:batch], out=buf.local_idx, out_val=buf.local_val, index_offset=model.vocab_start, vocab=model.vocab_local)
+            comm.select_greedy(buf.local_val, buf.local_idx, buf.sampled, batch)
+        plan.add(pick, launches=2 if fused else 1)
+    elif tp:
+        def pick_sampled():
+            buf.logits_full[:batch].copy_(comm.gather_logits(buf.logits[:batch, :model.vocab_local], V))
+            ops.sample_launch(sp_full)
+        sp_full = ops.build_sample_params(buf.logits_full[:batch], buf.temperature, buf.top_k, buf.top_p, buf.uniform, buf.sampled, buf.min_p, vocab=V)
+        plan.keep.append(sp_full)
+        plan.add(pick_sampled, launches=1)
+    elif greedy_only:
+        plan.add(lambda: ops.argmax(buf.logits[:batch], out=buf.sampled, vocab=V))
     else:
-        sp = ops.build_sample_params(buf.logits[:batch], buf.temperature, buf.top_k, buf.top_p, buf.uniform, buf.sampled, buf.min_p,
-                                     vocab=cfg.vocab_size)
+        sp = ops.build_sample_params(buf.logits[:batch], buf.temperature, buf.top_k, buf.top_p, buf.uniform, buf.sampled, buf.min_p, vocab=V)
         plan.keep.append(sp)
         plan.add(lambda: ops.sample_launch(sp))
+    plan.ar_sites = site[0]
     return plan

@@ -7,6 +7,7 @@ is missing on a GPU host the import of :func:`lib` raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
@@ -122,7 +123,8 @@ def plan_rows_per_cta(mats: Sequence[MatOut], target_ctas: int) -> List[int]:
 
 
 def build_gemv_params(xs: Sequence[VecIn], mats: Sequence[MatOut], y: torch.Tensor, batch: int, ldy: Optional[int] = None,
-                      residual: Optional[torch.Tensor] = None, ld_res: Optional[int] = None, target_ctas: int = 296) -> S.GemvParams:
+                      residual: Optional[torch.Tensor] = None, ld_res: Optional[int] = None, target_ctas: int = 148,
+                      ar: Optional[S.GemvAr] = None) -> S.GemvParams:
     """Fill a parameter block.  The caller keeps every referenced tensor alive."""
     if not (1 <= len(mats) <= S.GEMV_MAX_MATS and 1 <= len(xs) <= S.GEMV_MAX_X):
         raise ValueError("a GEMV launch takes 1..4 matrices and 1..4 inputs")
@@ -149,6 +151,8 @@ def build_gemv_params(xs: Sequence[VecIn], mats: Sequence[MatOut], y: torch.Tens
     p.y, p.ldy = y.data_ptr(), ldy if ldy is not None else (y.stride(0) if y.dim() > 1 else y.numel())
     p.residual = ptr(residual)
     p.ld_res = ld_res if ld_res is not None else (residual.stride(0) if residual is not None and residual.dim() > 1 else 0)
+    if ar is not None:
+        ctypes.memmove(ctypes.addressof(p.ar), ctypes.addressof(ar), ctypes.sizeof(S.GemvAr))
     return p
 
 
@@ -156,16 +160,41 @@ def gemv_launch(p: S.GemvParams) -> None:
     check(lib().rlz_gemv(ctypes.byref(p), stream_ptr()), "gemv")
 
 
+STREAM_TYPES = (int(QType.Q4_K), int(QType.Q5_K), int(QType.Q6_K))
+
+
+def stream_eligible(mats: Sequence[MatOut]) -> bool:
+    """True when every matrix of a launch can go through the TMA-streamed GEMV kernel."""
+    if os.environ.get("RLZ_GEMV_STREAM", "0") != "1":       # opt-in: the register-path kernel measures faster at decode sizes
+        return False
+    for m in mats:
+        for w, _ in m.segs:
+            if w.qtype not in STREAM_TYPES or w.k % 256 or w.stride != dev_row_bytes(w.qtype, w.k):
+                return False
+    return True
+
+
+def gemv_stream_launch(p: S.GemvParams) -> None:
+    check(lib().rlz_gemv_stream(ctypes.byref(p), stream_ptr()), "gemv_stream")
+
+
+def device_error(clear: bool = True) -> int:
+    """Error code recorded by a kernel whose bounded wait expired (0 = none)."""
+    return int(lib().rlz_device_error(1 if clear else 0))
+
+
 def gemv(w: DeviceWeight, x: torch.Tensor, bias=None, act=ACT_NONE, residual=None, norm=NORM_NONE, norm_w=None, norm_b=None,
-         eps=1e-5) -> torch.Tensor:
+         eps=1e-5, stream: Optional[bool] = None) -> torch.Tensor:
     """``y = act(W norm(x) + bias) + residual`` for ``x`` of shape ``[batch<=4, k]`` (convenience form)."""
     x2 = x.reshape(-1, w.k).contiguous().float()
     batch = x2.shape[0]
     y = torch.empty(batch, w.n, device=x.device, dtype=torch.float32)
     res = residual.reshape(batch, w.n).contiguous().float() if residual is not None else None
-    p = build_gemv_params([VecIn(x2, w.k, norm=norm, norm_w=norm_w, norm_b=norm_b, eps=eps)],
-                          [MatOut([(w, 0)], bias=bias, act=act, residual=res is not None)], y, batch, residual=res)
-    gemv_launch(p)
+    mats = [MatOut([(w, 0)], bias=bias, act=act, residual=res is not None)]
+    use_stream = stream_eligible(mats) if stream is None else stream
+    p = build_gemv_params([VecIn(x2, w.k, norm=norm, norm_w=norm_w, norm_b=norm_b, eps=eps)], mats, y, batch, residual=res,
+                          target_ctas=148)
+    (gemv_stream_launch if use_stream else gemv_launch)(p)
     return y.reshape(*x.shape[:-1], w.n)
 
 

@@ -28,10 +28,23 @@ class GemvX(Structure):
                 ("eps", c_float), ("_pad", c_int32)]
 
 
+AR_MAX_RANKS = 8
+
+
+class GemvAr(Structure):
+    _fields_ = [("inbox", c_void_p * AR_MAX_RANKS), ("epoch", c_void_p), ("status", c_void_p), ("spin_limit", c_int64),
+                ("rank", c_int32), ("world", c_int32), ("enabled", c_int32), ("n", c_int32)]
+
+
 class GemvParams(Structure):
     _fields_ = [("mat", GemvMat * GEMV_MAX_MATS), ("xs", GemvX * GEMV_MAX_X), ("y", c_void_p), ("residual", c_void_p),
                 ("ldy", c_int64), ("ld_res", c_int64), ("nmat", c_int32), ("batch", c_int32), ("max_k", c_int32),
-                ("max_rows", c_int32), ("any_generic", c_int32), ("_pad", c_int32)]
+                ("max_rows", c_int32), ("any_generic", c_int32), ("_pad", c_int32), ("ar", GemvAr)]
+
+
+class CandExchange(Structure):
+    _fields_ = [("inbox", c_void_p * AR_MAX_RANKS), ("epoch", c_void_p), ("status", c_void_p), ("spin_limit", c_int64),
+                ("rank", c_int32), ("world", c_int32), ("batch", c_int32), ("max_batch", c_int32)]
 
 
 class AttnDecodeParams(Structure):
@@ -56,6 +69,14 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_cuda_error_string.argtypes = [c_int]
     lib.rlz_cuda_error_string.restype = ctypes.c_char_p
     lib.rlz_gemv.argtypes = [POINTER(GemvParams), c_void_p]
+    lib.rlz_gemv_stream.argtypes = [POINTER(GemvParams), c_void_p]
+    lib.rlz_device_error.argtypes = [c_int]
+    lib.rlz_symm_alloc.argtypes = [ctypes.c_ulonglong, POINTER(c_void_p), c_void_p]
+    lib.rlz_symm_open.argtypes = [c_void_p, POINTER(c_void_p)]
+    lib.rlz_symm_close.argtypes = [c_void_p]
+    lib.rlz_symm_free.argtypes = [c_void_p]
+    lib.rlz_epoch_bump.argtypes = [c_void_p, c_void_p]
+    lib.rlz_cand_exchange.argtypes = [POINTER(CandExchange), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.rlz_attn_decode.argtypes = [POINTER(AttnDecodeParams), c_void_p]
     lib.rlz_attn_decode_partial_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.rlz_attn_decode_partial_floats.restype = c_longlong

@@ -1,0 +1,190 @@
+"""Tensor-parallel communication for the decode engine, one process per GPU.
+
+Two interchangeable communicators:
+
+* ``NcclTpComm`` – the baseline: ``torch.distributed`` (NCCL) all-reduce of the row-parallel
+  partial sums followed by a residual-add kernel, NCCL all-gather of argmax candidates / logits.
+* ``FusedTpComm`` – the product: row-parallel GEMV kernels all-reduce their own outputs over
+  peer memory (each CTA stores its rows into every rank's inbox, publishes an epoch flag, waits
+  bounded for the peers and sums in rank order, fused with the residual add; values travel as
+  epoch-tagged 8-byte stores, so there are no fences and no separate flags), and the greedy
+  token is agreed on by a one-CTA candidate exchange.  No extra launches per all-reduce and no
+  library collective on the decode path; buffers are CUDA-IPC-mapped symmetric memory.
+
+The reference has no real communicator (single-process mock,
+src/parallel/mod_all_reduce_communicator.rs:2-110).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..ops import _signatures as S
+
+
+class SymmetricBuffer:
+    """A zero-initialised device buffer of ``nbytes`` on every rank, mapped into every other rank
+    of the group through CUDA IPC.  ``ptrs[r]`` is the address of rank r's buffer in this process."""
+
+    def __init__(self, nbytes: int, rank: int, world: int, group=None):
+        lib = ops.lib()
+        self.nbytes, self.rank, self.world = int(nbytes), rank, world
+        self._local = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        ops.check(lib.rlz_symm_alloc(self.nbytes, ctypes.byref(self._local), handle), "symm_alloc")
+        handles: List[Optional[bytes]] = [None] * world
+        if world > 1:
+            dist.all_gather_object(handles, handle.raw, group=group)
+        else:
+            handles[0] = handle.raw
+        self.ptrs: List[int] = []
+        self._opened: List[int] = []
+        for r in range(world):
+            if r == rank:
+                self.ptrs.append(self._local.value)
+                continue
+            p = ctypes.c_void_p()
+            ops.check(lib.rlz_symm_open(ctypes.create_string_buffer(handles[r], 64), ctypes.byref(p)), f"symm_open(rank {r})")
+            self.ptrs.append(p.value)
+            self._opened.append(p.value)
+        if world > 1:
+            dist.barrier(group=group)
+
+    def close(self):
+        lib = ops.lib()
+        for p in self._opened:
+            lib.rlz_symm_close(ctypes.c_void_p(p))
+        self._opened = []
+        if self._local and self._local.value:
+            lib.rlz_symm_free(self._local)
+            self._local = ctypes.c_void_p()
+
+
+class TpCommBase:
+    mode = "base"
+
+    def __init__(self, rank: int, world: int, device):
+        self.rank, self.world, self.device = rank, world, torch.device(device)
+        self.fused = False
+
+    # hooks used by the decode plan ---------------------------------------------------------
+    def begin_step(self) -> None:
+        """Issued once at the start of every step (before the first collective)."""
+
+    def step_launches(self) -> int:
+        return 0
+
+    def ar_desc(self, site: int):
+        return None
+
+    def close(self):
+        pass
+
+
+class NcclTpComm(TpCommBase):
+    mode = "nccl"
+
+    def __init__(self, rank, world, device, group=None):
+        super().__init__(rank, world, device)
+        self.group = group
+
+    def all_reduce_sum_(self, t: torch.Tensor) -> None:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+
+    def select_greedy(self, local_val: torch.Tensor, local_idx: torch.Tensor, out_idx: torch.Tensor, batch: int) -> None:
+        """local (value, global token id) per batch row -> global argmax in ``out_idx``."""
+        pair = torch.stack([local_val[:batch], local_idx[:batch].to(torch.float32)], dim=1).contiguous()
+        allp = torch.empty(self.world, batch, 2, device=self.device, dtype=torch.float32)
+        dist.all_gather_into_tensor(allp, pair, group=self.group)
+        best = allp[:, :, 0].argmax(dim=0)
+        out_idx[:batch] = allp[best, torch.arange(batch, device=self.device), 1].to(torch.int32)
+
+    def gather_logits(self, local_logits: torch.Tensor, vocab: int) -> torch.Tensor:
+        """[batch, vocab_local] on every rank -> [batch, vocab] (rank-major concatenation)."""
+        b, vl = local_logits.shape
+        allp = torch.empty(self.world, b, vl, device=self.device, dtype=local_logits.dtype)
+        dist.all_gather_into_tensor(allp, local_logits.contiguous(), group=self.group)
+        return allp.permute(1, 0, 2).reshape(b, self.world * vl)[:, :vocab].contiguous()
+
+
+class FusedTpComm(NcclTpComm):
+    """In-kernel collectives over symmetric peer memory (NCCL is kept only for set-up and for the
+    non-greedy logits gather)."""
+    mode = "fused"
+
+    def __init__(self, rank, world, device, group=None, spin_limit: int = 20_000_000):
+        super().__init__(rank, world, device, group)
+        self.fused = True
+        self.spin_limit = spin_limit
+        self.buf: Optional[SymmetricBuffer] = None
+        self.epoch = torch.zeros(1, device=self.device, dtype=torch.int32)
+        self.status = torch.zeros(1, device=self.device, dtype=torch.int32)
+        self._sites = []
+        self._cand = None
+
+    def allocate(self, n_sites: int, n: int, max_batch: int, max_ctas: int = 0) -> None:
+        """Reserve symmetric memory for ``n_sites`` all-reduce call sites of ``n`` outputs each and
+        for the candidate exchange of up to ``max_batch`` sequences."""
+        w = self.world
+        n_pad = (n + 3) // 4 * 4
+        self.n, self.max_batch = n_pad, max_batch
+        self._inbox_site = 2 * w * 4 * n_pad * 8           # [parity][rank][4 batch rows][n] pairs of 32-bit words
+        self._off_cand = n_sites * self._inbox_site
+        cand_inbox = 2 * w * max_batch * 2 * 8
+        total = (self._off_cand + cand_inbox + 255) // 256 * 256
+        self.buf = SymmetricBuffer(total, self.rank, w, self.group)
+        self.n_sites = n_sites
+
+    def ar_desc(self, site: int) -> S.GemvAr:
+        if not 0 <= site < self.n_sites:
+            raise IndexError(f"all-reduce site {site} out of range ({self.n_sites} reserved)")
+        ar = S.GemvAr()
+        for r in range(self.world):
+            ar.inbox[r] = self.buf.ptrs[r] + site * self._inbox_site
+        ar.epoch, ar.status = self.epoch.data_ptr(), self.status.data_ptr()
+        ar.spin_limit = self.spin_limit
+        ar.rank, ar.world, ar.enabled, ar.n = self.rank, self.world, 1, self.n
+        return ar
+
+    def begin_step(self) -> None:
+        ops.check(ops.lib().rlz_epoch_bump(self.epoch.data_ptr(), ops.stream_ptr()), "epoch_bump")
+
+    def step_launches(self) -> int:
+        return 1
+
+    def select_greedy(self, local_val, local_idx, out_idx, batch: int) -> None:
+        if self._cand is None:
+            c = S.CandExchange()
+            for r in range(self.world):
+                c.inbox[r] = self.buf.ptrs[r] + self._off_cand
+            c.epoch, c.status, c.spin_limit = self.epoch.data_ptr(), self.status.data_ptr(), self.spin_limit
+            c.rank, c.world, c.max_batch = self.rank, self.world, self.max_batch
+            self._cand = c
+        c = self._cand
+        c.batch = batch
+        ops.check(ops.lib().rlz_cand_exchange(ctypes.byref(c), local_val.data_ptr(), local_idx.data_ptr(), out_idx.data_ptr(), None,
+                                              ops.stream_ptr()), "cand_exchange")
+
+    def check_status(self) -> int:
+        """Error code recorded by a kernel whose peer wait expired (0 = healthy)."""
+        v = int(self.status.item())
+        if v:
+            self.status.zero_()
+        return v
+
+    def close(self):
+        if self.buf is not None:
+            self.buf.close()
+            self.buf = None
+
+
+def make_tp_comm(rank: int, world: int, device, mode: str = "fused", group=None) -> TpCommBase:
+    if mode == "nccl":
+        return NcclTpComm(rank, world, device, group)
+    if mode == "fused":
+        return FusedTpComm(rank, world, device, group)
+    raise ValueError(f"unknown tensor-parallel communication mode '{mode}'")

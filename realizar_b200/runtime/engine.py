@@ -94,7 +94,13 @@ class DecodeEngine:
             attn_out=z(B, o_k), act=z(B, d_k + 256), partial_out=z(B, self.mcfg.hidden_dim) if tp_size > 1 else None,
             logits=z(B, m.vocab_local if tp_size > 1 else self.mcfg.vocab_size), sampled=z(B, dt=torch.int32),
             temperature=z(B), top_k=z(B, dt=torch.int32), top_p=torch.ones(B, device=dev), min_p=z(B), uniform=z(B),
-            attn_partial=part, attn_counters=ctr)
+            attn_partial=part, attn_counters=ctr,
+            local_val=z(B) if tp_size > 1 else None, local_idx=z(B, dt=torch.int32) if tp_size > 1 else None,
+            logits_full=z(B, self.mcfg.vocab_size) if (tp_size > 1 and not c.greedy_only) else None)
+        if comm is not None and getattr(comm, "fused", False):
+            chunks_max = -(-B // 4)
+            per_layer = 1 if self.mcfg.parallel_residual else 2
+            comm.allocate(self.mcfg.num_layers * per_layer * chunks_max, self.mcfg.hidden_dim, max_batch=B)
         self.slots = [Slot() for _ in range(B)]
         self.buckets = sorted(set(c.batch_buckets or [b for b in (1, 2, 4, 8, 16, 32, 64, 128) if b < B] + [B]))
         self._plans: Dict[int, DecodePlan] = {}

@@ -29,19 +29,43 @@ def peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
+REPS = 1
+GRAPH = False
+
+
 def time_cuda(fn, iters: int, warmup: int = 3) -> float:
-    """Median milliseconds per call over ``iters`` timed calls (events on the current stream)."""
+    """Median milliseconds per call over ``iters`` timed regions of ``REPS`` back-to-back calls
+    (events on the current stream).  ``--reps`` > 1 amortises the launch and event overhead so the
+    fixed cost of short kernels becomes visible (at the price of a warm L2 for small operands)."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
+    run = None
+    if GRAPH:                                   # replay the launches from a CUDA graph: no host launch cost in the timing
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            fn()
+        torch.cuda.current_stream().wait_stream(s)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(REPS):
+                fn()
+        run = g.replay
+        run()
+        torch.cuda.synchronize()
     times = []
     for _ in range(iters):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        fn()
+        if run is not None:
+            run()
+        else:
+            for _ in range(REPS):
+                fn()
         e1.record()
         torch.cuda.synchronize()
-        times.append(e0.elapsed_time(e1))
+        times.append(e0.elapsed_time(e1) / REPS)
     return float(np.median(times))
 
 
@@ -65,11 +89,21 @@ def bench_gemv(a):
     y = torch.empty(a.batch, a.n, device=dev)
     g = torch.rand(a.k, device=dev) + 0.5
     xin = ops.VecIn(x, a.k, norm=ops.NORM_RMS if a.norm else ops.NORM_NONE, norm_w=g if a.norm else None)
-    p = ops.build_gemv_params([xin], [ops.MatOut([(w, 0)])], y, a.batch, target_ctas=a.ctas)
-    ms = time_cuda(lambda: ops.gemv_launch(p), a.iters)
+    mats = [ops.MatOut([(w, 0)])]
+    use_stream = ops.stream_eligible(mats) and not a.no_stream
+    ar = None
+    if a.ar:                                   # single-rank self-loop of the in-kernel all-reduce epilogue
+        from ..parallel.tp import FusedTpComm
+        comm = FusedTpComm(0, 1, dev)
+        comm.allocate(1, a.n, max_batch=4)
+        comm.begin_step()
+        ar = comm.ar_desc(0)
+    p = ops.build_gemv_params([xin], mats, y, a.batch, target_ctas=a.ctas or 148, ar=ar)
+    launch = ops.gemv_stream_launch if use_stream else ops.gemv_launch
+    ms = time_cuda(lambda: launch(p), a.iters)
     byts = w.nbytes + x.numel() * 4 + y.numel() * 4
     pk = peaks()
-    return {"kernel": "gemv", "qtype": a.qtype, "n": a.n, "k": a.k, "batch": a.batch, "ms": ms, "bytes": byts,
+    return {"kernel": "gemv_stream" if use_stream else "gemv", "qtype": a.qtype, "n": a.n, "k": a.k, "batch": a.batch, "ms": ms, "bytes": byts,
             "gbs": byts / ms / 1e6, "frac_of_%s_hbm" % pk["source"]: byts / ms / 1e6 / pk["hbm_gbs"],
             "l2_note": "weights %.0f MB %s L2" % (w.nbytes / 1e6, ">" if w.nbytes > 126e6 else "<=")}
 
@@ -116,11 +150,14 @@ def bench_gemm(a):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--reps", type=int, default=1, help="back-to-back launches per timed region")
+    ap.add_argument("--graph", action="store_true", help="time a CUDA-graph replay of the launches")
+    ap.add_argument("--pdl", action="store_true", help="launch with programmatic dependent launch")
     sub = ap.add_subparsers(dest="cmd", required=True)
     g = sub.add_parser("gemv")
     g.add_argument("--qtype", default="Q4_K"); g.add_argument("--n", type=int, default=200000); g.add_argument("--k", type=int, default=2560)
     g.add_argument("--batch", type=int, default=1); g.add_argument("--iters", type=int, default=10); g.add_argument("--norm", action="store_true")
-    g.add_argument("--ctas", type=int, default=296)
+    g.add_argument("--ctas", type=int, default=0); g.add_argument("--no-stream", action="store_true"); g.add_argument("--ar", action="store_true")
     t = sub.add_parser("attn")
     t.add_argument("--heads", type=int, default=32); t.add_argument("--kv-heads", type=int, default=32); t.add_argument("--head-dim", type=int, default=80)
     t.add_argument("--ctx", type=int, default=4096); t.add_argument("--batch", type=int, default=8); t.add_argument("--splits", type=int, default=0)
@@ -129,6 +166,11 @@ def main(argv=None):
     m.add_argument("--qtype", default="Q4_K"); m.add_argument("--n", type=int, default=10240); m.add_argument("--k", type=int, default=2560)
     m.add_argument("--m", type=int, default=512); m.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
+    global REPS, GRAPH
+    REPS, GRAPH = max(1, a.reps), a.graph
+    if a.pdl:
+        from .. import ops
+        ops.set_pdl(True)
     res = {"gemv": bench_gemv, "attn": bench_attn, "gemm": bench_gemm}[a.cmd](a)
     print(json.dumps(res))
     return 0

@@ -43,11 +43,32 @@ def test_gemv_matches_fp32(cuda_device, qt, batch):
 
 
 @pytest.mark.parametrize("n,k", [(37, 256), (2560, 2560), (513, 10240), (1000, 4096)])
-def test_gemv_shapes_q4k(cuda_device, n, k):
+@pytest.mark.parametrize("stream", [False, True])
+def test_gemv_shapes_q4k(cuda_device, n, k, stream):
     from realizar_b200 import ops
     w, wd = _weight(n, k, QType.Q4_K, seed=n)
     x = torch.randn(1, k, device="cuda")
-    assert _rel(ops.gemv(w, x), x.cpu() @ wd.T) < 0.02
+    assert _rel(ops.gemv(w, x, stream=stream), x.cpu() @ wd.T) < 0.02
+    assert ops.device_error() == 0
+
+
+@pytest.mark.parametrize("qt", [QType.Q4_K, QType.Q5_K, QType.Q6_K])
+@pytest.mark.parametrize("batch", [1, 2, 4])
+def test_gemv_stream_kernel_matches_register_kernel(cuda_device, qt, batch):
+    """The TMA-streamed kernel and the register-path kernel share prologue / epilogue semantics."""
+    from realizar_b200 import ops
+    n, k = 3000, 2048
+    w, wd = _weight(n, k, qt, seed=21)
+    x = torch.randn(batch, k, device="cuda") * 2
+    g = torch.rand(k, device="cuda") + 0.5
+    bias, res = torch.randn(n, device="cuda") * 0.1, torch.randn(batch, n, device="cuda")
+    a = ops.gemv(w, x, bias=bias, act=ops.ACT_SILU, residual=res, norm=ops.NORM_RMS, norm_w=g, stream=True)
+    b = ops.gemv(w, x, bias=bias, act=ops.ACT_SILU, residual=res, norm=ops.NORM_RMS, norm_w=g, stream=False)
+    xc = x.cpu()
+    h = xc / torch.sqrt((xc * xc).mean(-1, keepdim=True) + 1e-5) * g.cpu()
+    ref = torch.nn.functional.silu(h @ wd.T + bias.cpu()) + res.cpu()
+    assert _rel(a, ref) < 0.02 and _rel(b, ref) < 0.02 and _rel(a, b) < 5e-3
+    assert ops.device_error() == 0
 
 
 @pytest.mark.parametrize("norm", ["rms", "layer"])

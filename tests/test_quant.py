@@ -100,6 +100,24 @@ def test_gpu_unit_functions_on_host(qt, k):
     assert np.abs(y - ref).max() / np.abs(ref).max() < 0.02
 
 
+@pytest.mark.parametrize("qt", [QType.Q4_K, QType.Q5_K, QType.Q6_K])
+@pytest.mark.parametrize("k", [256, 2560])
+def test_gpu_block_functions_on_host(qt, k):
+    """Whole-block dot products of the streamed GEMV (csrc/gemv_blocks.h) run on the CPU."""
+    lib = cpu_lib()
+    lib.rlz_emu_gemv_blocks.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_int]
+    n, B = 7, 2
+    w = _w(n, k, 13)
+    q = quant.quantize(w, qt)
+    wd = quant.dequantize(q, qt, w.shape)
+    dev = to_device_layout(torch.from_numpy(q), qt, n, k).numpy().copy()
+    x = np.random.default_rng(3).standard_normal((B, k)).astype(np.float32)
+    y = np.zeros((B, n), np.float32)
+    assert lib.rlz_emu_gemv_blocks(int(qt), dev.ctypes.data, dev.shape[1], x.ctypes.data, y.ctypes.data, n, k, B) == 0
+    ref = x @ wd.T
+    assert np.abs(y - ref).max() / np.abs(ref).max() < 0.02
+
+
 def test_rejects_bad_shapes():
     with pytest.raises(ValueError):
         quant.quantize(np.zeros((2, 100), np.float32), QType.Q4_K)
