@@ -62,6 +62,12 @@ class SampleParams(Structure):
                 ("out_logprob", c_void_p)]
 
 
+class GemmParams(Structure):
+    _fields_ = [("W", c_void_p), ("w_stride", c_int64), ("qtype", c_int32), ("n", c_int32), ("k", c_int32), ("m", c_int32),
+                ("X", c_void_p), ("ldx", c_int64), ("Y", c_void_p), ("ldy", c_int64), ("bias", c_void_p), ("residual", c_void_p),
+                ("ld_res", c_int64), ("act", c_int32), ("splitk", c_int32), ("atomic_out", c_int32), ("_pad", c_int32)]
+
+
 def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_launch_count.restype = c_longlong
     lib.rlz_set_pdl.argtypes = [c_int]
@@ -71,6 +77,8 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_gemv.argtypes = [POINTER(GemvParams), c_void_p]
     lib.rlz_gemv_stream.argtypes = [POINTER(GemvParams), c_void_p]
     lib.rlz_device_error.argtypes = [c_int]
+    lib.rlz_gemm_kquant.argtypes = [POINTER(GemmParams), c_void_p]
+    lib.rlz_gemm_error.argtypes = [c_int]
     lib.rlz_symm_alloc.argtypes = [ctypes.c_ulonglong, POINTER(c_void_p), c_void_p]
     lib.rlz_symm_open.argtypes = [c_void_p, POINTER(c_void_p)]
     lib.rlz_symm_close.argtypes = [c_void_p]

@@ -1,0 +1,76 @@
+"""Tensor-core dequant-GEMM (tcgen05 / TMEM) over block-quantised weights: prefill and large
+decode batches.  ``Y[m, n] = act(X[m, k] W[n, k]^T + bias) + residual`` with X in bf16."""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import DeviceWeight, check, lib, ptr, stream_ptr, ACT_NONE
+from . import _signatures as S
+from ..quant import QType
+
+GEMM_TYPES = (int(QType.Q4_K), int(QType.Q5_K), int(QType.Q6_K), int(QType.BF16), int(QType.F16))
+
+
+def gemm_eligible(w: DeviceWeight) -> bool:
+    if w.qtype not in GEMM_TYPES:
+        return False
+    return w.k % 256 == 0 if w.qtype in GEMM_TYPES[:3] else w.k % 64 == 0
+
+
+def choose_splitk(n: int, k: int, m: int, sm_count: int = 148) -> int:
+    """Split K across CTAs when the (n, m) tile grid alone would leave most SMs idle."""
+    mt = 32 if m <= 32 else 64 if m <= 64 else 128
+    tiles = -(-n // 128) * -(-m // mt)
+    if tiles >= sm_count:
+        return 1
+    return max(1, min(k // 256, sm_count // tiles, 16))
+
+
+def build_gemm_params(w: DeviceWeight, x: torch.Tensor, y: torch.Tensor, m: int, bias=None, residual=None, act=ACT_NONE,
+                      splitk: int = 1, ldx: Optional[int] = None, ldy: Optional[int] = None, ld_res: Optional[int] = None) -> S.GemmParams:
+    if x.dtype != torch.bfloat16 or y.dtype != torch.float32:
+        raise TypeError("gemm expects bf16 activations and an fp32 output")
+    p = S.GemmParams()
+    p.W, p.w_stride, p.qtype, p.n, p.k, p.m = w.data.data_ptr(), w.stride, w.qtype, w.n, w.k, m
+    p.X, p.ldx = x.data_ptr(), ldx if ldx is not None else x.stride(0)
+    p.Y, p.ldy = y.data_ptr(), ldy if ldy is not None else y.stride(0)
+    p.bias, p.residual = ptr(bias), ptr(residual)
+    p.ld_res = ld_res if ld_res is not None else (residual.stride(0) if residual is not None else 0)
+    p.act, p.splitk = act, splitk
+    return p
+
+
+def gemm_launch(p: S.GemmParams) -> None:
+    check(lib().rlz_gemm_kquant(ctypes.byref(p), stream_ptr()), "gemm_kquant")
+
+
+def gemm(w: DeviceWeight, x: torch.Tensor, bias=None, residual=None, act=ACT_NONE, splitk: Optional[int] = None) -> torch.Tensor:
+    """Convenience form: allocates the output.  With split-K the output starts as the residual (or
+    zeros) and the partial products are accumulated atomically."""
+    x2 = x.reshape(-1, w.k).to(torch.bfloat16).contiguous()
+    m = x2.shape[0]
+    sk = splitk if splitk is not None else (choose_splitk(w.n, w.k, m) if act == ACT_NONE else 1)
+    if sk > 1:
+        y = residual.reshape(m, w.n).float().clone() if residual is not None else torch.zeros(m, w.n, device=x.device, dtype=torch.float32)
+        gemm_launch(build_gemm_params(w, x2, y, m, bias=bias, splitk=sk))
+    else:
+        y = torch.empty(m, w.n, device=x.device, dtype=torch.float32)
+        res = residual.reshape(m, w.n).float().contiguous() if residual is not None else None
+        gemm_launch(build_gemm_params(w, x2, y, m, bias=bias, residual=res, act=act))
+    return y.reshape(*x.shape[:-1], w.n)
+
+
+class GemmPlan:
+    """Reusable launch of one weight matrix at a fixed token count (micro-benchmarks)."""
+
+    def __init__(self, w: DeviceWeight, m: int, device, splitk: Optional[int] = None):
+        self.w, self.m = w, m
+        self.splitk = splitk if splitk is not None else choose_splitk(w.n, w.k, m)
+
+    def run(self, x: torch.Tensor, y: torch.Tensor) -> None:
+        if self.splitk > 1:
+            y.zero_()
+        gemm_launch(build_gemm_params(self.w, x, y, self.m, splitk=self.splitk))

@@ -1,0 +1,52 @@
+"""tcgen05 dequant-GEMM against an fp32 reference on dequantised weights and bf16-rounded inputs."""
+import numpy as np
+import pytest
+import torch
+
+from realizar_b200 import quant
+from realizar_b200.quant import QType
+
+pytestmark = pytest.mark.gpu
+
+
+def _weight(n, k, qt, seed):
+    from realizar_b200 import ops
+    w = (np.random.default_rng(seed).standard_normal((n, k)) * 0.05).astype(np.float32)
+    q = quant.quantize(w, qt)
+    return ops.upload_weight(q, qt, n, k, "cuda"), torch.from_numpy(quant.dequantize(q, qt, (n, k)))
+
+
+@pytest.mark.parametrize("qt", [QType.Q4_K, QType.Q5_K, QType.Q6_K, QType.BF16, QType.F16])
+@pytest.mark.parametrize("m,n,k", [(5, 128, 256), (64, 200, 512), (130, 384, 1024), (33, 2560, 2560)])
+def test_gemm_matches_fp32(cuda_device, qt, m, n, k):
+    from realizar_b200 import ops
+    from realizar_b200.ops import gemm
+    w, wd = _weight(n, k, qt, seed=m + n)
+    x = torch.randn(m, k, device="cuda")
+    y = gemm.gemm(w, x, splitk=1)
+    assert ops.device_error() == 0
+    xr = x.to(torch.bfloat16).float().cpu()
+    ref = xr @ wd.to(torch.bfloat16).float().T           # operands are rounded to bf16 before the tensor core
+    rel = float((y.cpu() - ref).abs().max() / ref.abs().max())
+    assert rel < 2e-2, rel
+    ref32 = xr @ wd.T
+    assert float((y.cpu() - ref32).abs().max() / ref32.abs().max()) < 3e-2
+
+
+def test_gemm_epilogue_and_splitk(cuda_device):
+    from realizar_b200 import ops
+    from realizar_b200.ops import gemm
+    m, n, k = 48, 256, 2048
+    w, wd = _weight(n, k, QType.Q4_K, 9)
+    x = torch.randn(m, k, device="cuda")
+    bias, res = torch.randn(n, device="cuda"), torch.randn(m, n, device="cuda")
+    xr = x.to(torch.bfloat16).float().cpu()
+    base = xr @ wd.to(torch.bfloat16).float().T
+    y = gemm.gemm(w, x, bias=bias, residual=res, act=ops.ACT_GELU, splitk=1)
+    ref = torch.nn.functional.gelu(base + bias.cpu(), approximate="tanh") + res.cpu()
+    assert float((y.cpu() - ref).abs().max() / ref.abs().max()) < 2e-2
+    y2 = gemm.gemm(w, x, bias=bias, residual=res, splitk=4)
+    ref2 = base + bias.cpu() + res.cpu()
+    assert float((y2.cpu() - ref2).abs().max() / ref2.abs().max()) < 2e-2
+    assert gemm.choose_splitk(2560, 10240, 64) > 1 and gemm.choose_splitk(17920 * 2, 2560, 128) == 1
+    assert ops.device_error() == 0
