@@ -37,8 +37,10 @@ struct AttnDecodeParams {
   int64_t ld_qkv, ld_out;
   int32_t n_heads, n_kv_heads, head_dim, max_pages;
   int32_t rope_dim, rope_type, splits, batch;
-  int32_t q_off, k_off, v_off, _pad;   // element offsets of the q / k / v sections in a qkv row
-  float rope_theta, eps, scale, _padf;
+  int32_t q_off, k_off, v_off;         // element offsets of the q / k / v sections in a qkv row
+  int32_t pt_stride;                   // page_table elements between batch rows (0: every row shares one table)
+  float rope_theta, eps, scale;
+  int32_t no_append;                   // 1: the new rows are already in the cache (prefill), only attend
 };
 
 __device__ __forceinline__ void rope_inplace(float* v, int d_rot, int rope_type, int pos, float theta, int tid, int nthreads) {
@@ -79,7 +81,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
   int chunk = (seq_len + p.splits - 1) / p.splits;
   chunk = (chunk + ATT_PAGE - 1) / ATT_PAGE * ATT_PAGE;
   const int start = split * chunk, end = min(seq_len, start + chunk);
-  const bool owner = start <= pos && pos < end;
+  const bool owner = !p.no_append && start <= pos && pos < end;
 
   // ---- stage q (this head group), and k/v of the new token ---------------------------------
   const float* row = p.qkv + (int64_t)b * p.ld_qkv;
@@ -111,7 +113,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
     if (owner) rope_inplace(k_s, p.rope_dim, p.rope_type, pos, p.rope_theta, tid, ATT_THREADS);
     __syncthreads();
   }
-  const int32_t* pt = p.page_table + (int64_t)b * p.max_pages;
+  const int32_t* pt = p.page_table + (int64_t)b * p.pt_stride;
   if (owner && hg == 0) {   // append the new row to the cache (one head group does it)
     const int page = pt[pos / ATT_PAGE], slot = pos % ATT_PAGE;
     const int64_t off = (((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE + slot) * d;
@@ -147,7 +149,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
     uint4 kr[ATT_TB], vr[ATT_TB];
 #pragma unroll
     for (int t = 0; t < ATT_TB; ++t) {
-      const bool ok = lane_ok && base + t < end && !(hg != 0 && base + t == pos);
+      const bool ok = lane_ok && base + t < end && !(hg != 0 && base + t == pos && !p.no_append);
       kr[t] = ok ? *(const uint4*)(p.k_cache + off + (int64_t)t * d) : make_uint4(0, 0, 0, 0);
       vr[t] = ok ? *(const uint4*)(p.v_cache + off + (int64_t)t * d) : make_uint4(0, 0, 0, 0);
     }
@@ -160,7 +162,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
         kf[t][2 * j] = __uint_as_float(kw[j] << 16); kf[t][2 * j + 1] = __uint_as_float(kw[j] & 0xFFFF0000u);
         vf[t][2 * j] = __uint_as_float(vw[j] << 16); vf[t][2 * j + 1] = __uint_as_float(vw[j] & 0xFFFF0000u);
       }
-      if (hg != 0 && base + t == pos && lane_ok) {   // new row straight from shared memory (bf16-rounded like the cache)
+      if (hg != 0 && base + t == pos && lane_ok && !p.no_append) {   // new row straight from shared memory (bf16-rounded like the cache)
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           kf[t][j] = __bfloat162float(__float2bfloat16_rn(k_s[j0 + j]));

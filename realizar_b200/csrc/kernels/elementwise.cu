@@ -150,6 +150,57 @@ __global__ void kv_append_kernel(const float* k, const float* v, int64_t ld, __n
   }
 }
 
+// bf16 producers for the tensor-core GEMM operands
+__global__ void to_bf16_kernel(const float* src, __nv_bfloat16* dst, int64_t rows, int cols, int64_t ld_s, int64_t ld_d) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t total = rows * cols;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / cols; const int c = (int)(idx - r * cols);
+    dst[r * ld_d + c] = __float2bfloat16_rn(src[r * ld_s + c]);
+  }
+}
+
+__global__ void norm_bf16_kernel(const float* x, const float* w, const float* b, __nv_bfloat16* y, int n, int64_t ld_x, int64_t ld_y,
+                                 int norm_type, float eps) {
+  __shared__ float red[40];
+  pdl_launch_dependents();
+  pdl_wait();
+  const float* xr = x + (int64_t)blockIdx.x * ld_x;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) { const float v = xr[i]; s += norm_type == NORM_LAYER ? v : v * v; }
+  s = block_sum(s, red);
+  float mean = 0.f, rstd;
+  if (norm_type == NORM_LAYER) {
+    mean = s / (float)n;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) { const float v = xr[i] - mean; ss += v * v; }
+    rstd = rsqrtf(block_sum(ss, red) / (float)n + eps);
+  } else if (norm_type == NORM_RMS) {
+    rstd = rsqrtf(s / (float)n + eps);
+  } else { rstd = 1.f; }
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = (xr[i] - mean) * rstd;
+    if (w) v *= w[i];
+    if (b) v += b[i];
+    y[(int64_t)blockIdx.x * ld_y + i] = __float2bfloat16_rn(v);
+  }
+}
+
+__global__ void swiglu_bf16_kernel(const float* gate, const float* up, __nv_bfloat16* y, int64_t rows, int cols, int64_t ld_g, int64_t ld_u,
+                                   int64_t ld_y, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t total = rows * cols;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / cols; const int c = (int)(idx - r * cols);
+    float v = gate[r * ld_g + c];
+    if (act == ACT_GELU) v = gelu_tanh(v); else if (act == ACT_SILU) v = silu(v);
+    if (up) v *= up[r * ld_u + c];
+    y[r * ld_y + c] = __float2bfloat16_rn(v);
+  }
+}
+
 // Feed sampled tokens back as the next step's inputs and advance positions of active slots.
 __global__ void advance_kernel(int32_t* tokens, const int32_t* sampled, int32_t* positions, int batch) {
   pdl_launch_dependents();
@@ -162,6 +213,25 @@ __global__ void advance_kernel(int32_t* tokens, const int32_t* sampled, int32_t*
 
 extern "C" {
 using namespace rlz;
+
+static int ew_grid(long long total) { long long g = (total + 255) / 256; if (g > 148 * 8) g = 148 * 8; if (g < 1) g = 1; return (int)g; }
+
+int rlz_to_bf16(const float* src, void* dst, long long rows, int cols, long long ld_s, long long ld_d, void* stream) {
+  return (int)launch(to_bf16_kernel, dim3(ew_grid(rows * cols)), dim3(256), 0, (cudaStream_t)stream, src, (__nv_bfloat16*)dst, (int64_t)rows, cols,
+                     (int64_t)ld_s, (int64_t)ld_d);
+}
+
+int rlz_norm_bf16(const float* x, const float* w, const float* b, void* y, int rows, int n, long long ld_x, long long ld_y, int norm_type,
+                  float eps, void* stream) {
+  return (int)launch(norm_bf16_kernel, dim3(rows), dim3(n >= 2048 ? 512 : 256), 0, (cudaStream_t)stream, x, w, b, (__nv_bfloat16*)y, n,
+                     (int64_t)ld_x, (int64_t)ld_y, norm_type, eps);
+}
+
+int rlz_swiglu_bf16(const float* gate, const float* up, void* y, long long rows, int cols, long long ld_g, long long ld_u, long long ld_y,
+                    int act, void* stream) {
+  return (int)launch(swiglu_bf16_kernel, dim3(ew_grid(rows * cols)), dim3(256), 0, (cudaStream_t)stream, gate, up, (__nv_bfloat16*)y,
+                     (int64_t)rows, cols, (int64_t)ld_g, (int64_t)ld_u, (int64_t)ld_y, act);
+}
 
 int rlz_advance(int32_t* tokens, const int32_t* sampled, int32_t* positions, int batch, void* stream) {
   return (int)launch(advance_kernel, dim3((batch + 63) / 64), dim3(64), 0, (cudaStream_t)stream, tokens, sampled, positions, batch);

@@ -1,0 +1,137 @@
+"""Token-batch forward pass on the tensor-core GEMM path: prompt prefill (one sequence, many
+tokens) and decode steps of batches too large for the GEMV kernels (many sequences, one token).
+
+Per layer and token batch of T rows:
+``norm -> bf16`` -> GEMM Q/K/V (+bias) -> [QK-norm] -> RoPE -> paged KV append ->
+attention over the paged cache (the decode kernel with one "sequence" per token row) ->
+``bf16`` -> GEMM o_proj (+residual) -> ``norm -> bf16`` -> GEMM gate/up -> SwiGLU/GELU ->
+GEMM down (+residual).  Everything is a static launch sequence over preallocated buffers, so a
+whole pass can be captured in a CUDA graph per token-count bucket.
+
+Replaces the reference's ``prefill_all_layers_gpu`` / ``transformer_layer_batched`` chain
+(src/cuda/executor/layers/prefill.rs:31-490, src/cuda/executor/layers/transformer_layer_batched.rs:24-143),
+whose GEMMs are cuBLAS calls and whose attention is strided-batched SGEMM + a softmax kernel.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional
+
+import torch
+
+from .. import ops
+from ..ops import ACT_GELU, ACT_NONE, ACT_SILU, NORM_LAYER, NORM_RMS, gemm as G
+from .decoder import GpuModel
+
+
+def gemm_capable(model: GpuModel) -> bool:
+    """True when every projection of the model can run on the tensor-core GEMM kernel."""
+    ws = [model.lm_head]
+    for L in model.layers:
+        ws += [w for w in (L.q, L.k, L.v, L.o, L.gate, L.up, L.down) if w is not None]
+    return all(G.gemm_eligible(w) for w in ws)
+
+
+class BatchedForward:
+    def __init__(self, model: GpuModel, max_tokens: int, k_cache: torch.Tensor, v_cache: torch.Tensor, max_pages: int, comm=None,
+                 sm_count: int = 148):
+        self.model, self.comm, self.sm_count = model, comm, sm_count
+        self.T = max_tokens
+        cfg = model.cfg
+        dev = model.device
+        H, qd, kvd, I = cfg.hidden_dim, model.q_dim, model.kv_dim, model.inter
+        self.qkv_w = qd + 2 * kvd
+        o_k = max(L.o.k for L in model.layers)
+        d_k = max(L.down.k for L in model.layers)
+        T = max_tokens
+        z = lambda *s, dt=torch.float32: torch.zeros(*s, device=dev, dtype=dt)
+        self.tokens, self.positions, self.page_rows = z(T, dt=torch.int32), z(T, dt=torch.int32), z(T, dt=torch.int32)
+        self.x = z(T, H)
+        self.xb = z(T, H, dt=torch.bfloat16)
+        self.qkv = z(T, self.qkv_w)
+        self.attn = z(T, o_k)                       # zero padding around this rank's slice under TP
+        self.attn_b = z(T, o_k, dt=torch.bfloat16)
+        self.gate, self.up = z(T, I), (z(T, I) if cfg.gated_ffn else None)
+        self.act_b = z(T, d_k, dt=torch.bfloat16)   # down-proj input (padded under TP)
+        self.partial = z(T, H) if model.tp_size > 1 else None
+        self.k_cache, self.v_cache = k_cache, v_cache
+        self.max_pages = max_pages
+        self.splits = 1
+        self.attn_partial, self.attn_counters = ops.attn_decode_scratch(T, model.heads, self.splits, cfg.head_dim, dev)
+        self.launches_per_pass = 0
+
+    # -- helpers ---------------------------------------------------------------------------
+    def _gemm(self, w, x_b, y, T, bias=None, act=ACT_NONE, residual_inplace=False, y_col=0):
+        """y[:, y_col:y_col+n] (+)= x_b W^T.  ``residual_inplace``: y already holds the residual."""
+        yv = y[:, y_col:]
+        if residual_inplace:
+            sk = G.choose_splitk(w.n, w.k, T, self.sm_count)
+            if sk > 1:
+                G.gemm_launch(G.build_gemm_params(w, x_b, yv, T, bias=bias, splitk=sk, ldy=y.stride(0)))
+            else:
+                G.gemm_launch(G.build_gemm_params(w, x_b, yv, T, bias=bias, residual=yv, ldy=y.stride(0), ld_res=y.stride(0)))
+        else:
+            G.gemm_launch(G.build_gemm_params(w, x_b, yv, T, bias=bias, act=act, ldy=y.stride(0)))
+        self.launches_per_pass += 1
+
+    def _row_parallel(self, w, x_b, T, bias):
+        """x += W_shard . x_b (+ bias), summed over tensor-parallel ranks."""
+        if self.model.tp_size == 1:
+            self._gemm(w, x_b, self.x, T, bias=bias, residual_inplace=True)
+            return
+        self._gemm(w, x_b, self.partial, T, bias=bias)
+        self.comm.all_reduce_sum_(self.partial[:T])
+        ops.elementwise(self.partial[:T], residual=self.x[:T], out=self.x[:T])
+        self.launches_per_pass += 1
+
+    # -- the pass ------------------------------------------------------------------------------
+    def forward(self, T: int, page_table: torch.Tensor, shared_table: bool) -> torch.Tensor:
+        """Run all layers for rows 0..T-1 (``tokens`` / ``positions`` / ``page_rows`` must be set).
+        ``page_table``: ``[max_pages]`` shared by all rows (prefill) or ``[T, max_pages]``.
+        Returns the residual stream ``x[:T]`` (the caller applies the final norm + lm_head)."""
+        m, cfg = self.model, self.model.cfg
+        H, qd, kvd, hd = cfg.hidden_dim, m.q_dim, m.kv_dim, cfg.head_dim
+        norm_t = NORM_LAYER if cfg.uses_layernorm else NORM_RMS
+        act_code = ACT_GELU if cfg.constraints.activation == "gelu" else ACT_SILU
+        self.launches_per_pass = 0
+        x, xb, qkv = self.x[:T], self.xb[:T], self.qkv[:T]
+        ops.embed(m.embed_table, m.embed_qtype, m.embed_row_bytes, H, cfg.vocab_size, self.tokens[:T], self.x, m.pos_table, self.positions)
+        self.launches_per_pass += 1
+        for l, L in enumerate(m.layers):
+            ops.norm_bf16(x, xb, L.attn_norm_w, L.attn_norm_b, norm_t, cfg.eps)
+            self._gemm(L.q, xb, self.qkv, T, bias=L.q_b, y_col=0)
+            self._gemm(L.k, xb, self.qkv, T, bias=L.k_b, y_col=qd)
+            self._gemm(L.v, xb, self.qkv, T, bias=L.v_b, y_col=qd + kvd)
+            if cfg.parallel_residual:
+                self._gemm(L.up, xb, self.gate, T, bias=L.up_b)        # activation applied when the bf16 operand is produced
+            if L.q_norm_w is not None:
+                ops.head_rmsnorm_(qkv, L.q_norm_w, m.heads, hd, cfg.eps)
+                ops.head_rmsnorm_(qkv[:, qd:], L.k_norm_w, m.kv_heads, hd, cfg.eps)
+                self.launches_per_pass += 2
+            if cfg.uses_rope:
+                ops.rope_(qkv, self.positions[:T], m.heads, hd, cfg.rope_dim, cfg.rope_type, cfg.rope_theta)
+                ops.rope_(qkv[:, qd:], self.positions[:T], m.kv_heads, hd, cfg.rope_dim, cfg.rope_type, cfg.rope_theta)
+                self.launches_per_pass += 2
+            ops.kv_append(qkv[:, qd:], qkv[:, qd + kvd:], self.k_cache[l], self.v_cache[l], self.positions[:T], self.page_rows[:T], m.kv_heads, hd)
+            ops.attn_decode_launch(ops.build_attn_decode_params(
+                self.qkv, self.attn[:, L.o_in_off:], self.k_cache[l], self.v_cache[l], self.positions, page_table, self.attn_partial,
+                self.attn_counters, m.heads, m.kv_heads, hd, self.splits, T, 0, cfg.rope_type, cfg.rope_theta, 0, qd, qd + kvd,
+                None, None, cfg.eps, ld_qkv=self.qkv.stride(0), ld_out=self.attn.stride(0), shared_table=shared_table, no_append=True))
+            ops.to_bf16(self.attn[:T], self.attn_b[:T])
+            self.launches_per_pass += 4
+            self._row_parallel(L.o, self.attn_b[:T, : L.o.k], T, L.o_b)
+            if cfg.parallel_residual:
+                ops.swiglu_bf16(self.gate[:T], None, self.act_b[:T, L.down_in_off:], act_code)
+                self.launches_per_pass += 1
+                self._row_parallel(L.down, self.act_b[:T, : L.down.k], T, L.down_b)
+            else:
+                ops.norm_bf16(x, xb, L.ffn_norm_w, L.ffn_norm_b, norm_t, cfg.eps)
+                if cfg.gated_ffn:
+                    self._gemm(L.gate, xb, self.gate, T)
+                    self._gemm(L.up, xb, self.up, T, bias=L.up_b)
+                    ops.swiglu_bf16(self.gate[:T], self.up[:T], self.act_b[:T, L.down_in_off:], act_code)
+                else:
+                    self._gemm(L.up, xb, self.gate, T, bias=L.up_b)
+                    ops.swiglu_bf16(self.gate[:T], None, self.act_b[:T, L.down_in_off:], act_code)
+                self.launches_per_pass += 2
+                self._row_parallel(L.down, self.act_b[:T, : L.down.k], T, L.down_b)
+        return x

@@ -287,6 +287,42 @@ class DecodePlan:
             t()
 
 
+def emit_head(plan: "DecodePlan", model: GpuModel, buf: StepBuffers, r0: int, batch: int, comm, greedy_only: bool, sm_count: int) -> None:
+    """Final norm + lm_head + token selection for rows ``r0 .. r0+batch-1`` of the step buffers."""
+    cfg = model.cfg
+    H, V = cfg.hidden_dim, cfg.vocab_size
+    norm_t = NORM_LAYER if cfg.uses_layernorm else NORM_RMS
+    tp = model.tp_size > 1
+    fused = tp and getattr(comm, "fused", False)
+    rows = slice(r0, r0 + batch)
+    for c0 in range(0, batch, 4):
+        cb = min(4, batch - c0)
+        xin = VecIn(buf.x[r0 + c0:], H, ld=buf.x.stride(0), norm=norm_t, norm_w=model.out_norm_w, norm_b=model.out_norm_b, eps=cfg.eps)
+        plan.add_gemv_auto([xin], [MatOut([(model.lm_head, 0)], bias=model.lm_head_b)], buf.logits[r0 + c0:], cb,
+                           buf.logits.stride(0), target_ctas=sm_count)
+    if tp and greedy_only:
+        def pick():
+            ops.argmax(buf.logits[rows], out=buf.local_idx[rows], out_val=buf.local_val[rows], index_offset=model.vocab_start, vocab=model.vocab_local)
+            comm.select_greedy(buf.local_val[rows], buf.local_idx[rows], buf.sampled[rows], batch)
+        plan.add(pick, launches=2 if fused else 1)
+    elif tp:
+        sp_full = ops.build_sample_params(buf.logits_full[rows], buf.temperature[rows], buf.top_k[rows], buf.top_p[rows], buf.uniform[rows],
+                                          buf.sampled[rows], buf.min_p[rows], vocab=V)
+        plan.keep.append(sp_full)
+
+        def pick_sampled():
+            buf.logits_full[rows].copy_(comm.gather_logits(buf.logits[rows, :model.vocab_local], V))
+            ops.sample_launch(sp_full)
+        plan.add(pick_sampled, launches=1)
+    elif greedy_only:
+        plan.add(lambda: ops.argmax(buf.logits[rows], out=buf.sampled[rows], vocab=V))
+    else:
+        sp = ops.build_sample_params(buf.logits[rows], buf.temperature[rows], buf.top_k[rows], buf.top_p[rows], buf.uniform[rows],
+                                     buf.sampled[rows], buf.min_p[rows], vocab=V)
+        plan.keep.append(sp)
+        plan.add(lambda: ops.sample_launch(sp))
+
+
 def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, v_cache: torch.Tensor, batch: int, splits: int,
                       comm=None, greedy_only: bool = False, sm_count: int = 148) -> DecodePlan:
     """Create the launch plan for ``batch`` sequences (rows 0..batch-1 of the step buffers).
@@ -370,28 +406,6 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
             row_parallel(lambda c0: [VecIn(buf.act[c0:], L.down.k, ld=buf.act.stride(0))],
                          lambda res: MatOut([(L.down, 0)], bias=L.down_b, residual=res))
 
-    for c0, cb in chunks:
-        xin = VecIn(buf.x[c0:], H, ld=buf.x.stride(0), norm=norm_t, norm_w=model.out_norm_w, norm_b=model.out_norm_b, eps=cfg.eps)
-        plan.add_gemv_auto([xin], [MatOut([(model.lm_head, 0)], bias=model.lm_head_b)], buf.logits[c0:], cb,
-                           buf.logits.stride(0), target_ctas=sm_count)
-    V = cfg.vocab_size
-    if tp and greedy_only:
-        def pick():
-            ops.argmax(buf.logits[:batch], out=buf.local_idx, out_val=buf.local_val, index_offset=model.vocab_start, vocab=model.vocab_local)
-            comm.select_greedy(buf.local_val, buf.local_idx, buf.sampled, batch)
-        plan.add(pick, launches=2 if fused else 1)
-    elif tp:
-        def pick_sampled():
-            buf.logits_full[:batch].copy_(comm.gather_logits(buf.logits[:batch, :model.vocab_local], V))
-            ops.sample_launch(sp_full)
-        sp_full = ops.build_sample_params(buf.logits_full[:batch], buf.temperature, buf.top_k, buf.top_p, buf.uniform, buf.sampled, buf.min_p, vocab=V)
-        plan.keep.append(sp_full)
-        plan.add(pick_sampled, launches=1)
-    elif greedy_only:
-        plan.add(lambda: ops.argmax(buf.logits[:batch], out=buf.sampled, vocab=V))
-    else:
-        sp = ops.build_sample_params(buf.logits[:batch], buf.temperature, buf.top_k, buf.top_p, buf.uniform, buf.sampled, buf.min_p, vocab=V)
-        plan.keep.append(sp)
-        plan.add(lambda: ops.sample_launch(sp))
+    emit_head(plan, model, buf, 0, batch, comm, greedy_only, sm_count)
     plan.ar_sites = site[0]
     return plan

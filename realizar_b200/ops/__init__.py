@@ -207,7 +207,7 @@ def attn_decode_scratch(batch: int, n_heads: int, splits: int, head_dim: int, de
 
 def build_attn_decode_params(qkv, out, k_cache, v_cache, positions, page_table, partial, counters, n_heads, n_kv_heads, head_dim,
                              splits, batch, rope_dim, rope_type, rope_theta, q_off, k_off, v_off, q_norm_w=None, k_norm_w=None,
-                             eps=1e-6, ld_qkv=None, ld_out=None) -> S.AttnDecodeParams:
+                             eps=1e-6, ld_qkv=None, ld_out=None, shared_table=False, no_append=False) -> S.AttnDecodeParams:
     p = S.AttnDecodeParams()
     p.qkv, p.out, p.k_cache, p.v_cache = qkv.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr()
     p.positions, p.page_table = positions.data_ptr(), page_table.data_ptr()
@@ -219,6 +219,8 @@ def build_attn_decode_params(qkv, out, k_cache, v_cache, positions, page_table, 
     p.rope_dim, p.rope_type, p.splits, p.batch = rope_dim, rope_type, splits, batch
     p.q_off, p.k_off, p.v_off = q_off, k_off, v_off
     p.rope_theta, p.eps, p.scale = rope_theta, eps, head_dim ** -0.5
+    p.pt_stride = 0 if shared_table else (page_table.stride(0) if page_table.dim() > 1 else page_table.shape[-1])
+    p.no_append = 1 if no_append else 0
     return p
 
 
@@ -259,6 +261,29 @@ def elementwise(a: torch.Tensor, b=None, bias=None, residual=None, act=ACT_NONE,
     check(lib().rlz_elementwise(a2.data_ptr(), ptr(b2), ptr(bias), ptr(residual), y2.data_ptr(), a2.shape[0], a2.shape[1], a2.stride(0),
                                 b2.stride(0) if b2 is not None else 0, y2.stride(0), act, 1 if b is not None else 0, stream_ptr()), "elementwise")
     return y.reshape(a.shape) if out is None else y
+
+
+def to_bf16(src: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp32 [rows, cols] -> bf16 (own kernel; row strides taken from the tensors)."""
+    s2 = src.reshape(-1, src.shape[-1])
+    if out is None:
+        out = torch.empty(s2.shape, device=src.device, dtype=torch.bfloat16)
+    check(lib().rlz_to_bf16(s2.data_ptr(), out.data_ptr(), s2.shape[0], s2.shape[1], s2.stride(0), out.stride(0), stream_ptr()), "to_bf16")
+    return out
+
+
+def norm_bf16(x: torch.Tensor, out: torch.Tensor, w=None, b=None, norm_type=NORM_RMS, eps=1e-5) -> torch.Tensor:
+    """``out = bf16(norm(x))`` for 2-D ``x`` (one launch: the GEMM operand producer of prefill)."""
+    check(lib().rlz_norm_bf16(x.data_ptr(), ptr(w), ptr(b), out.data_ptr(), x.shape[0], x.shape[1], x.stride(0), out.stride(0), norm_type, eps,
+                              stream_ptr()), "norm_bf16")
+    return out
+
+
+def swiglu_bf16(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor, act=ACT_SILU) -> torch.Tensor:
+    """``out = bf16(act(gate) * up)`` (``up`` may be None: plain activation)."""
+    check(lib().rlz_swiglu_bf16(gate.data_ptr(), ptr(up), out.data_ptr(), gate.shape[0], gate.shape[1], gate.stride(0),
+                                up.stride(0) if up is not None else 0, out.stride(0), act, stream_ptr()), "swiglu_bf16")
+    return out
 
 
 def kv_append(k, v, k_cache, v_cache, positions, page_rows, n_kv_heads, d, page=16) -> None:

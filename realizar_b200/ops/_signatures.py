@@ -52,8 +52,8 @@ class AttnDecodeParams(Structure):
                 ("page_table", c_void_p), ("q_norm_w", c_void_p), ("k_norm_w", c_void_p), ("partial", c_void_p),
                 ("counters", c_void_p), ("ld_qkv", c_int64), ("ld_out", c_int64), ("n_heads", c_int32), ("n_kv_heads", c_int32),
                 ("head_dim", c_int32), ("max_pages", c_int32), ("rope_dim", c_int32), ("rope_type", c_int32), ("splits", c_int32),
-                ("batch", c_int32), ("q_off", c_int32), ("k_off", c_int32), ("v_off", c_int32), ("_pad", c_int32),
-                ("rope_theta", c_float), ("eps", c_float), ("scale", c_float), ("_padf", c_float)]
+                ("batch", c_int32), ("q_off", c_int32), ("k_off", c_int32), ("v_off", c_int32), ("pt_stride", c_int32),
+                ("rope_theta", c_float), ("eps", c_float), ("scale", c_float), ("no_append", c_int32)]
 
 
 class SampleParams(Structure):
@@ -97,6 +97,9 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_elementwise.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_longlong,
                                     c_longlong, c_int, c_int, c_void_p]
     lib.rlz_kv_append.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+    lib.rlz_to_bf16.argtypes = [c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_longlong, c_void_p]
+    lib.rlz_norm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_float, c_void_p]
+    lib.rlz_swiglu_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_longlong, c_longlong, c_int, c_void_p]
     lib.rlz_advance.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     lib.rlz_argmax.argtypes = [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
     lib.rlz_sample.argtypes = [POINTER(SampleParams), c_void_p]

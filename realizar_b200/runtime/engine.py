@@ -20,7 +20,8 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from .. import ops
-from ..models.decoder import DecodePlan, GpuModel, StepBuffers, build_decode_plan
+from ..models.batched import BatchedForward, gemm_capable
+from ..models.decoder import DecodePlan, GpuModel, StepBuffers, build_decode_plan, emit_head
 from ..models.weights import ModelWeights
 from .paged_kv import PagedKvCache
 
@@ -38,6 +39,8 @@ class EngineConfig:
     pdl: bool = True                       # programmatic dependent launch between kernels
     attn_splits: int = 0                   # 0 = choose from the SM count
     greedy_only: bool = False              # compile plans with argmax instead of the sampling kernel
+    prefill_chunk: int = 512               # tokens per tensor-core prefill pass
+    batched_prefill_min: int = 8           # shorter prompts go through the decode kernels token by token
     batch_buckets: Sequence[int] = ()      # graph buckets; default powers of two up to max_batch
     seed: int = 0
 
@@ -115,6 +118,9 @@ class DecodeEngine:
         self.pdl = c.pdl
         ops.set_pdl(self.pdl)
         self.steps_run = 0
+        self.gemm_ok = gemm_capable(self.model)
+        self._batched: Optional[BatchedForward] = None
+        self._head_plans: Dict[int, DecodePlan] = {}
 
     # -- configuration helpers --------------------------------------------------------------
     def _choose_splits(self, batch: int) -> int:
@@ -248,14 +254,58 @@ class DecodeEngine:
                 self.slots[i].position += 1
         return self._h_sampled
 
+    def batched(self) -> BatchedForward:
+        if self._batched is None:
+            self._batched = BatchedForward(self.model, self.cfg.prefill_chunk, self.kv[0], self.kv[1], self.max_pages_per_seq, self.comm, self.sm_count)
+        return self._batched
+
+    def _head(self, slot: int) -> DecodePlan:
+        """Final norm + lm_head + token selection for one row of the step buffers."""
+        if slot not in self._head_plans:
+            plan = DecodePlan(self.sm_count)
+            emit_head(plan, self.model, self.buf, slot, 1, self.comm, self.cfg.greedy_only, self.sm_count)
+            self._head_plans[slot] = plan
+        return self._head_plans[slot]
+
     def prefill(self, slot: int, tokens: Sequence[int]) -> int:
-        """Run the prompt through the decode path token by token (serial prefill, as the reference's
-        ``run_prefill`` loop, src/gguf/cuda/generate_2.rs:261-273).  Returns the token sampled after
-        the last prompt token."""
+        """Run a prompt (or a prompt continuation) for ``slot`` and return the token sampled after its
+        last token.  Prompts of at least ``batched_prefill_min`` tokens go through the tensor-core GEMM
+        pass in chunks of ``prefill_chunk`` tokens when every projection supports it; otherwise the
+        prompt is fed through the decode kernels token by token (as the reference's ``run_prefill``
+        loop, src/gguf/cuda/generate_2.rs:261-273)."""
+        n = len(tokens)
+        if n >= self.cfg.batched_prefill_min and self.gemm_ok:
+            return self._prefill_batched(slot, tokens)
         out = 0
         for t in tokens:
             out = int(self.feed({slot: int(t)})[slot])
         return out
+
+    def _prefill_batched(self, slot: int, tokens: Sequence[int]) -> int:
+        s = self.slots[slot]
+        bf = self.batched()
+        n, pos0 = len(tokens), s.position
+        self._ensure_pages(slot, pos0 + n)
+        pages = self.pages.seqs[s.seq_id].pages
+        toks = torch.as_tensor(list(tokens), dtype=torch.int32)
+        x_last = None
+        for c0 in range(0, n, bf.T):
+            T = min(bf.T, n - c0)
+            pos = torch.arange(pos0 + c0, pos0 + c0 + T, dtype=torch.int32)
+            rows = torch.tensor([pages[int(p) // PAGE] for p in pos], dtype=torch.int32)
+            bf.tokens[:T].copy_(toks[c0:c0 + T], non_blocking=True)
+            bf.positions[:T].copy_(pos, non_blocking=True)
+            bf.page_rows[:T].copy_(rows, non_blocking=True)
+            x = bf.forward(T, self.buf.page_table[slot], shared_table=True)
+            x_last = x[T - 1]
+        self.buf.x[slot].copy_(x_last)
+        if not self.cfg.greedy_only:
+            self.buf.uniform[slot: slot + 1].copy_(torch.rand(1, device=self.device, generator=self._gen))
+        self._head(slot).run()
+        self._h_sampled[slot: slot + 1].copy_(self.buf.sampled[slot: slot + 1], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        s.position = pos0 + n
+        return int(self._h_sampled[slot])
 
     # -- convenience ----------------------------------------------------------------------------
     def generate(self, prompt: Sequence[int], sampling: Optional[SamplingParams] = None, on_token=None) -> List[int]:
