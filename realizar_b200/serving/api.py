@@ -1,0 +1,464 @@
+"""HTTP API: OpenAI-compatible chat / completions / embeddings / models, native generate /
+tokenize / batch / stream routes, health, Prometheus and JSON metrics, dispatch metrics, audit
+trail, GPU status / warm-up, log-probabilities and perplexity.
+
+Route set and JSON schemas follow the reference router (src/api/router.rs:57-135;
+chat request / response / chunk types src/api/mod_create_demo.rs:62-330; SSE sequence
+role -> content deltas -> finish -> ``[DONE]`` src/api/openai_handlers.rs:179-275; native types
+src/api/types.rs).  A full queue answers 503, malformed bodies 422 with a sanitised message,
+unknown paths a JSON 404.
+"""
+from __future__ import annotations
+
+import asyncio
+import json
+import math
+import threading
+import time
+import uuid
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+from fastapi import FastAPI, Header, HTTPException, Request as HttpRequest
+from fastapi.exceptions import RequestValidationError
+from fastapi.middleware.cors import CORSMiddleware
+from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+from pydantic import BaseModel, Field
+
+from .. import __version__
+from ..runtime.scheduler import FinishReason, QueueFull, Request, ServingEngine
+from .chat_template import ChatMessage, ChatTemplate, RawTemplate, auto_detect_template
+from .metrics import DispatchMetrics, MetricsCollector
+from .tokenizer import StreamDecoder
+
+KEEP_ALIVE_SECONDS = 15.0
+
+
+# ------------------------------------------------------------------ schemas ---------------
+class ChatMessageIn(BaseModel):
+    role: str
+    content: str = ""
+    name: Optional[str] = None
+
+
+class ChatCompletionRequest(BaseModel):
+    model: str = "default"
+    messages: List[ChatMessageIn]
+    max_tokens: Optional[int] = None
+    temperature: Optional[float] = None
+    top_p: Optional[float] = None
+    n: int = 1
+    stream: bool = False
+    stop: Optional[List[str]] = None
+    user: Optional[str] = None
+
+
+class CompletionRequest(BaseModel):
+    model: str = "default"
+    prompt: str
+    max_tokens: Optional[int] = None
+    temperature: Optional[float] = None
+    top_p: Optional[float] = None
+    stop: Optional[List[str]] = None
+    stream: bool = False
+
+
+class GenerateRequest(BaseModel):
+    prompt: str
+    max_tokens: int = 50
+    temperature: float = 1.0
+    strategy: str = "greedy"
+    top_k: int = 50
+    top_p: float = 0.9
+    seed: Optional[int] = None
+    model_id: Optional[str] = None
+
+
+class TokenizeRequest(BaseModel):
+    text: str
+    model_id: Optional[str] = None
+
+
+class BatchTokenizeRequest(BaseModel):
+    texts: List[str]
+
+
+class BatchGenerateRequest(BaseModel):
+    prompts: List[str]
+    max_tokens: int = 50
+    temperature: float = 1.0
+    strategy: str = "greedy"
+    top_k: int = 50
+    top_p: float = 0.9
+
+
+class EmbeddingRequest(BaseModel):
+    model: str = "default"
+    input: Any
+
+
+class LogprobsRequest(BaseModel):
+    prompt: str
+    top_logprobs: int = 5
+
+
+@dataclass
+class AppState:
+    serving: Optional[ServingEngine]
+    tokenizer: Any
+    template: ChatTemplate = field(default_factory=RawTemplate)
+    model_name: str = "default"
+    eos_token_id: Optional[int] = None
+    metrics: MetricsCollector = field(default_factory=MetricsCollector)
+    dispatch: DispatchMetrics = field(default_factory=DispatchMetrics)
+    audit: Dict[str, dict] = field(default_factory=dict)
+    compute_mode: str = "gpu"
+    scorer: Any = None                  # optional callable(tokens) -> per-position logits (logprobs / perplexity / embeddings)
+    context_length: int = 4096
+
+    @classmethod
+    def demo(cls) -> "AppState":
+        """A self-contained state with a fake engine and a byte tokenizer (tests, smoke runs)."""
+        from ..runtime.scheduler import FakeEngine
+        from .tokenizer import ByteTokenizer
+        return cls(ServingEngine(FakeEngine(vocab=256)).start(), ByteTokenizer(256), RawTemplate(), "demo", None, compute_mode="cpu")
+
+
+def _finish_reason(r: Request) -> str:
+    return "stop" if r.finish_reason == FinishReason.STOP else "length"
+
+
+def create_app(state: AppState) -> FastAPI:
+    app = FastAPI(title="realizar-b200", version=__version__)
+    app.add_middleware(CORSMiddleware, allow_origins=["*"], allow_methods=["*"], allow_headers=["*"])
+    app.state.rlz = state
+
+    @app.exception_handler(RequestValidationError)
+    async def _validation(_req, exc: RequestValidationError):
+        msgs = "; ".join(f"{'.'.join(str(x) for x in e.get('loc', [])[1:])}: {e.get('msg', '')}" for e in exc.errors())
+        return JSONResponse({"error": f"invalid request: {msgs}"[:500]}, status_code=422)
+
+    @app.exception_handler(404)
+    async def _not_found(_req, _exc):
+        return JSONResponse({"error": "not found"}, status_code=404)
+
+    # -- helpers ---------------------------------------------------------------------------------
+    def encode(text: str) -> List[int]:
+        ids = state.tokenizer.encode(text)
+        if not ids:
+            raise HTTPException(400, "prompt is empty after tokenisation")
+        if len(ids) >= state.context_length:                      # context-window manager: keep the most recent tokens
+            ids = ids[-(state.context_length - 1):]
+        return ids
+
+    def stop_ids() -> List[int]:
+        return [state.eos_token_id] if state.eos_token_id is not None else []
+
+    def submit(prompt_ids, max_tokens, temperature, top_k, top_p, on_token=None, on_finish=None) -> Request:
+        if state.serving is None:
+            raise HTTPException(503, "no model loaded")
+        r = Request(prompt_ids, max_tokens=max_tokens, temperature=temperature, top_k=top_k, top_p=top_p, stop_token_ids=stop_ids(),
+                    on_token=on_token, on_finish=on_finish)
+        try:
+            state.serving.submit(r)
+        except QueueFull:
+            state.metrics.record_failure()
+            raise HTTPException(503, "server is at capacity, retry later")
+        except RuntimeError as e:
+            state.metrics.record_failure()
+            raise HTTPException(503, str(e))
+        return r
+
+    async def run_blocking(prompt_ids, max_tokens, temperature, top_k, top_p) -> Request:
+        loop = asyncio.get_running_loop()
+        fut = loop.create_future()
+        r = submit(prompt_ids, max_tokens, temperature, top_k, top_p,
+                   on_finish=lambda rq: loop.call_soon_threadsafe(lambda: fut.done() or fut.set_result(rq)))
+        await fut
+        record(r)
+        if r.finish_reason == FinishReason.ERROR:
+            raise HTTPException(500, r.error or "generation failed")
+        return r
+
+    def record(r: Request) -> None:
+        state.dispatch.record(state.compute_mode, (r.finish_time or time.monotonic()) - r.arrival)
+        if r.finish_reason == FinishReason.ERROR:
+            state.metrics.record_failure()
+        else:
+            state.metrics.record_success(len(r.output), (r.finish_time or time.monotonic()) - r.arrival, r.ttft, r.token_times)
+
+    def text_of(r: Request) -> str:
+        toks = r.output[:-1] if r.finish_reason == FinishReason.STOP and r.output and r.output[-1] in stop_ids() else r.output
+        return state.tokenizer.decode(toks)
+
+    def apply_stops(text: str, stops: Optional[List[str]]) -> str:
+        for s in stops or []:
+            i = text.find(s)
+            if i >= 0:
+                text = text[:i]
+        return text
+
+    def chat_params(req) -> tuple:
+        t = 0.7 if req.temperature is None else req.temperature
+        return (req.max_tokens or 256, t, 1 if t == 0 else 40, 1.0 if req.top_p is None else req.top_p)
+
+    def audit(rid: str, kind: str, prompt_tokens: int, completion_tokens: int, latency: float) -> None:
+        state.audit[rid] = {"request_id": rid, "endpoint": kind, "model": state.model_name, "prompt_tokens": prompt_tokens,
+                            "completion_tokens": completion_tokens, "latency_ms": 1e3 * latency, "timestamp": time.time()}
+        if len(state.audit) > 10000:
+            state.audit.pop(next(iter(state.audit)))
+
+    def trace_block(level: Optional[str], r: Request) -> dict:
+        if level not in ("brick", "step", "layer"):
+            return {}
+        total = 1e6 * ((r.finish_time or time.monotonic()) - r.arrival)
+        return {f"{level}_trace": {"level": level, "total_time_us": total, "ttft_us": 1e6 * (r.ttft or 0.0),
+                                   "operations": [{"name": "prefill", "time_us": 1e6 * (r.ttft or 0.0)}, {"name": "decode", "time_us": total - 1e6 * (r.ttft or 0.0)}]}}
+
+    def sse_stream(r_holder: dict, first_chunk: Optional[dict], make_chunk, done_chunk):
+        """Server-sent events fed by the engine thread through an asyncio queue."""
+        async def gen():
+            loop = asyncio.get_running_loop()
+            q: asyncio.Queue = asyncio.Queue()
+            dec = StreamDecoder(state.tokenizer)
+            stops = set(stop_ids())
+            r = submit(*r_holder["args"], on_token=lambda t: loop.call_soon_threadsafe(q.put_nowait, ("tok", t)),
+                       on_finish=lambda rq: loop.call_soon_threadsafe(q.put_nowait, ("end", rq)))
+            if first_chunk is not None:
+                yield f"data: {json.dumps(first_chunk)}\n\n"
+            try:
+                while True:
+                    try:
+                        kind, val = await asyncio.wait_for(q.get(), KEEP_ALIVE_SECONDS)
+                    except asyncio.TimeoutError:
+                        yield ": keep-alive\n\n"
+                        continue
+                    if kind == "tok":
+                        if val in stops:
+                            continue
+                        text = dec.push(val)
+                        if text:
+                            yield f"data: {json.dumps(make_chunk(val, text))}\n\n"
+                    else:
+                        record(val)
+                        if val.finish_reason == FinishReason.ERROR:
+                            yield f"data: {json.dumps({'error': val.error or 'generation failed'})}\n\n"
+                        else:
+                            tail = dec.flush()
+                            if tail:
+                                yield f"data: {json.dumps(make_chunk(-1, tail))}\n\n"
+                            yield f"data: {json.dumps(done_chunk(val))}\n\n"
+                        yield "data: [DONE]\n\n"
+                        return
+            finally:
+                r.cancelled = r.finish_reason is None          # client went away: stop generating
+        return StreamingResponse(gen(), media_type="text/event-stream")
+
+    # -- health / metrics --------------------------------------------------------------------------
+    @app.get("/health")
+    async def health():
+        h = state.serving.health if state.serving is not None else "no_model"
+        body = {"status": "healthy" if h == "ok" else h, "version": __version__, "compute_mode": state.compute_mode}
+        return JSONResponse(body, status_code=200 if h in ("ok", "no_model") else 503)
+
+    def refresh_gauges():
+        if state.serving is not None:
+            m = state.serving.metrics()
+            for k in ("queue_depth", "running", "kv_page_utilization", "avg_step_ms"):
+                state.metrics.set_gauge(k, m.get(k, 0))
+
+    @app.get("/metrics")
+    async def metrics():
+        refresh_gauges()
+        return PlainTextResponse(state.metrics.prometheus(), media_type="text/plain; version=0.0.4")
+
+    @app.get("/v1/metrics")
+    async def metrics_json():
+        refresh_gauges()
+        snap = state.metrics.snapshot()
+        if state.serving is not None:
+            snap["scheduler"] = state.serving.metrics()
+        return snap
+
+    @app.get("/metrics/dispatch")
+    async def dispatch(format: str = "json"):
+        return PlainTextResponse(state.dispatch.prometheus()) if format == "prometheus" else state.dispatch.to_dict()
+
+    @app.post("/metrics/dispatch/reset")
+    async def dispatch_reset():
+        state.dispatch.reset()
+        return {"status": "reset"}
+
+    # -- models ------------------------------------------------------------------------------------
+    @app.get("/models")
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": state.model_name, "object": "model", "created": int(state.metrics.start), "owned_by": "realizar-b200"}]}
+
+    @app.get("/realize/model")
+    async def realize_model():
+        return {"model": state.model_name, "context_length": state.context_length, "template": state.template.format, "compute_mode": state.compute_mode}
+
+    @app.post("/realize/reload")
+    async def realize_reload():
+        raise HTTPException(501, "hot reload needs the process to be started with a model registry (see `realizar-b200 serve --help`)")
+
+    # -- tokenize / native generate ----------------------------------------------------------------
+    @app.post("/tokenize")
+    async def tokenize(req: TokenizeRequest):
+        ids = state.tokenizer.encode(req.text)
+        return {"token_ids": ids, "num_tokens": len(ids)}
+
+    @app.post("/batch/tokenize")
+    async def batch_tokenize(req: BatchTokenizeRequest):
+        out = [state.tokenizer.encode(t) for t in req.texts]
+        return {"results": [{"token_ids": ids, "num_tokens": len(ids)} for ids in out]}
+
+    def native_params(req) -> tuple:
+        greedy = req.strategy == "greedy" or req.temperature == 0
+        return (req.max_tokens, 0.0 if greedy else req.temperature, 1 if greedy else (req.top_k if req.strategy in ("top_k", "top_p") else 0),
+                req.top_p if req.strategy == "top_p" else 1.0)
+
+    @app.post("/generate")
+    @app.post("/realize/generate")
+    async def generate(req: GenerateRequest):
+        if req.strategy not in ("greedy", "top_k", "top_p", "sample"):
+            raise HTTPException(400, f"unknown strategy '{req.strategy}'")
+        ids = encode(req.prompt)
+        r = await run_blocking(ids, *native_params(req))
+        return {"token_ids": r.output, "text": text_of(r), "num_generated": len(r.output)}
+
+    @app.post("/batch/generate")
+    @app.post("/realize/batch")
+    async def batch_generate(req: BatchGenerateRequest):
+        if not req.prompts:
+            raise HTTPException(400, "prompts is empty")
+        rs = await asyncio.gather(*[run_blocking(encode(p), *native_params(req)) for p in req.prompts])
+        return {"results": [{"token_ids": r.output, "text": text_of(r), "num_generated": len(r.output)} for r in rs]}
+
+    @app.post("/stream/generate")
+    async def stream_generate(req: GenerateRequest):
+        ids = encode(req.prompt)
+        holder = {"args": (ids, *native_params(req))}
+        return sse_stream(holder, None, lambda tid, text: {"token_id": tid, "text": text}, lambda r: {"num_generated": len(r.output)})
+
+    # -- OpenAI ------------------------------------------------------------------------------------
+    @app.post("/v1/chat/completions")
+    async def chat_completions(req: ChatCompletionRequest, x_trace_level: Optional[str] = Header(default=None)):
+        if not req.messages:
+            raise HTTPException(400, "messages is empty")
+        prompt = state.template.format_conversation([ChatMessage(m.role, m.content, m.name) for m in req.messages])
+        ids = encode(prompt)
+        rid, created = f"chatcmpl-{uuid.uuid4().hex[:24]}", int(time.time())
+        params = chat_params(req)
+        if req.stream:
+            base = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": req.model}
+            first = {**base, "choices": [{"index": 0, "delta": {"role": "assistant"}, "finish_reason": None}]}
+            return sse_stream({"args": (ids, *params)}, first,
+                              lambda _tid, text: {**base, "choices": [{"index": 0, "delta": {"content": text}, "finish_reason": None}]},
+                              lambda r: {**base, "choices": [{"index": 0, "delta": {}, "finish_reason": _finish_reason(r)}]})
+        r = await run_blocking(ids, *params)
+        text = apply_stops(text_of(r), req.stop)
+        audit(rid, "chat.completions", len(ids), len(r.output), (r.finish_time or time.monotonic()) - r.arrival)
+        return {"id": rid, "object": "chat.completion", "created": created, "model": req.model,
+                "choices": [{"index": 0, "message": {"role": "assistant", "content": text}, "finish_reason": _finish_reason(r)}],
+                "usage": {"prompt_tokens": len(ids), "completion_tokens": len(r.output), "total_tokens": len(ids) + len(r.output)},
+                **trace_block(x_trace_level, r)}
+
+    @app.post("/v1/chat/completions/stream")
+    async def chat_completions_stream(req: ChatCompletionRequest):
+        req.stream = True
+        return await chat_completions(req, None)
+
+    @app.post("/v1/completions")
+    async def completions(req: CompletionRequest):
+        ids = encode(req.prompt)
+        rid, created = f"cmpl-{uuid.uuid4().hex[:24]}", int(time.time())
+        t = 0.7 if req.temperature is None else req.temperature
+        params = (req.max_tokens or 256, t, 1 if t == 0 else 40, 1.0 if req.top_p is None else req.top_p)
+        if req.stream:
+            base = {"id": rid, "object": "text_completion", "created": created, "model": req.model}
+            return sse_stream({"args": (ids, *params)}, None,
+                              lambda _tid, text: {**base, "choices": [{"index": 0, "text": text, "finish_reason": None}]},
+                              lambda r: {**base, "choices": [{"index": 0, "text": "", "finish_reason": _finish_reason(r)}]})
+        r = await run_blocking(ids, *params)
+        audit(rid, "completions", len(ids), len(r.output), (r.finish_time or time.monotonic()) - r.arrival)
+        return {"id": rid, "object": "text_completion", "created": created, "model": req.model,
+                "choices": [{"index": 0, "text": apply_stops(text_of(r), req.stop), "finish_reason": _finish_reason(r)}],
+                "usage": {"prompt_tokens": len(ids), "completion_tokens": len(r.output), "total_tokens": len(ids) + len(r.output)}}
+
+    @app.post("/v1/batch/completions")
+    async def batch_completions(body: Dict[str, Any]):
+        prompts = body.get("prompts") or []
+        if not prompts:
+            raise HTTPException(400, "prompts is empty")
+        t = body.get("temperature", 0.7)
+        rs = await asyncio.gather(*[run_blocking(encode(p), body.get("max_tokens", 256), t, 1 if t == 0 else 40, body.get("top_p", 1.0)) for p in prompts])
+        return {"object": "list", "data": [{"index": i, "text": text_of(r), "finish_reason": _finish_reason(r)} for i, r in enumerate(rs)]}
+
+    @app.post("/v1/embeddings")
+    @app.post("/realize/embed")
+    async def embeddings(req: EmbeddingRequest):
+        texts = req.input if isinstance(req.input, list) else [req.input]
+        if state.scorer is None or not hasattr(state.scorer, "embed"):
+            raise HTTPException(501, "this server was started without an embedding-capable model")
+        data = [{"object": "embedding", "index": i, "embedding": [float(v) for v in state.scorer.embed(state.tokenizer.encode(str(t)))]} for i, t in enumerate(texts)]
+        return {"object": "list", "data": data, "model": req.model, "usage": {"prompt_tokens": sum(len(state.tokenizer.encode(str(t))) for t in texts)}}
+
+    @app.post("/v1/logprobs")
+    async def logprobs(req: LogprobsRequest):
+        if state.scorer is None:
+            raise HTTPException(501, "this server was started without a scoring model")
+        ids = encode(req.prompt)
+        lp = state.scorer.logprobs(ids)                      # [T-1] log p(token_t | prefix)
+        return {"tokens": ids, "token_logprobs": [None] + [float(x) for x in lp]}
+
+    @app.post("/v1/perplexity")
+    async def perplexity(body: Dict[str, Any]):
+        if state.scorer is None:
+            raise HTTPException(501, "this server was started without a scoring model")
+        ids = encode(str(body.get("text", "")))
+        if len(ids) < 2:
+            raise HTTPException(400, "need at least two tokens")
+        lp = state.scorer.logprobs(ids)
+        nll = -float(sum(lp)) / len(lp)
+        return {"perplexity": math.exp(nll), "nll": nll, "num_tokens": len(ids)}
+
+    @app.get("/v1/audit/{request_id}")
+    async def audit_get(request_id: str):
+        if request_id not in state.audit:
+            raise HTTPException(404, "unknown request id")
+        return state.audit[request_id]
+
+    @app.post("/v1/predict")
+    @app.post("/v1/explain")
+    async def classical(_body: Dict[str, Any]):
+        raise HTTPException(501, "classical-ML .apr models are served by `realizar-b200 serve --classical <model.apr>`")
+
+    # -- GPU ---------------------------------------------------------------------------------------
+    @app.get("/v1/gpu/status")
+    async def gpu_status():
+        try:
+            import torch
+            if not torch.cuda.is_available():
+                return {"available": False}
+            free, total = torch.cuda.mem_get_info()
+            return {"available": True, "device": torch.cuda.get_device_name(0), "memory_free": free, "memory_total": total,
+                    "engine": state.serving.metrics() if state.serving else None}
+        except Exception as e:
+            return {"available": False, "error": str(e)}
+
+    @app.post("/v1/gpu/warmup")
+    async def gpu_warmup():
+        if state.serving is None:
+            raise HTTPException(503, "no model loaded")
+        t0 = time.monotonic()
+        r = await run_blocking(encode("warm up"), 4, 0.0, 1, 1.0)
+        return {"status": "ok", "tokens": len(r.output), "seconds": time.monotonic() - t0}
+
+    return app
+
+
+def serve(state: AppState, host: str = "127.0.0.1", port: int = 8080, log_level: str = "warning") -> None:
+    import uvicorn
+    uvicorn.run(create_app(state), host=host, port=port, log_level=log_level)

@@ -281,7 +281,7 @@ class SentencePieceTokenizer:
             if t is None or (skip_special and t in self.special):
                 continue
             buf.extend(self.token_bytes(int(i)))
-        text = buf.decode("utf-8", "replace")
+        text = buf.decode("utf-8", "replace").replace(self.SPACE, " ")     # a byte-fallback "▁" is a space too
         return text[1:] if text.startswith(" ") else text
 
 
