@@ -20,7 +20,7 @@ from __future__ import annotations
 
 import os
 from dataclasses import dataclass, field
-from typing import Callable, List, Optional
+from typing import Callable, List, Optional, Sequence
 
 import numpy as np
 import torch
@@ -324,8 +324,9 @@ def emit_head(plan: "DecodePlan", model: GpuModel, buf: StepBuffers, r0: int, ba
 
 
 def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, v_cache: torch.Tensor, batch: int, splits: int,
-                      comm=None, greedy_only: bool = False, sm_count: int = 148) -> DecodePlan:
+                      comm=None, greedy_only: bool = False, sm_count: int = 148, layer_subset: Optional[Sequence[int]] = None) -> DecodePlan:
     """Create the launch plan for ``batch`` sequences (rows 0..batch-1 of the step buffers).
+    ``layer_subset`` restricts the pass to those layers (the layer-skipping draft of self-speculative decoding).
 
     ``k_cache`` / ``v_cache`` are ``[layers, pages, kv_heads, 16, head_dim]`` bf16.  ``comm`` is the
     tensor-parallel communicator (``None`` on one GPU); it provides ``all_reduce_sum_(tensor)``.
@@ -375,6 +376,8 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
             plan.add(lambda: reduce_into_x(buf.partial_out[:batch]), launches=1)
 
     for l, L in enumerate(model.layers):
+        if layer_subset is not None and l not in layer_subset:
+            continue
         kc, vc = k_cache[l], v_cache[l]
         for c0, cb in chunks:
             x = buf.x[c0:]

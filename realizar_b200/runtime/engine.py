@@ -307,6 +307,75 @@ class DecodeEngine:
         s.position = pos0 + n
         return int(self._h_sampled[slot])
 
+    # -- multi-token verification / speculative support ------------------------------------------
+    def forward_tokens(self, slot: int, tokens: Sequence[int]) -> List[int]:
+        """Feed ``tokens`` at the slot's current position (KV appended) and return the greedy next
+        token after EACH of them: one tensor-core pass over all rows plus one lm_head pass per
+        ``max_batch`` rows.  Used to verify draft tokens in a single weight read
+        (the reference verifies through its batched GEMV, src/gguf/cuda/speculative.rs:120-200)."""
+        n = len(tokens)
+        s = self.slots[slot]
+        if n == 0:
+            return []
+        if not self.gemm_ok or n < 2:
+            self.buf.temperature[slot] = 0.0
+            return [int(self.feed({slot: int(t)})[slot]) for t in tokens]
+        bf = self.batched()
+        if n > bf.T:
+            raise ValueError(f"{n} tokens exceed the batched-pass capacity {bf.T}")
+        pos0 = s.position
+        self._ensure_pages(slot, pos0 + n)
+        pages = self.pages.seqs[s.seq_id].pages
+        pos = torch.arange(pos0, pos0 + n, dtype=torch.int32)
+        bf.tokens[:n].copy_(torch.as_tensor(list(tokens), dtype=torch.int32), non_blocking=True)
+        bf.positions[:n].copy_(pos, non_blocking=True)
+        bf.page_rows[:n].copy_(torch.tensor([pages[int(p) // PAGE] for p in pos], dtype=torch.int32), non_blocking=True)
+        x = bf.forward(n, self.buf.page_table[slot], shared_table=True)
+        out: List[int] = []
+        B = self.cfg.max_batch
+        for c0 in range(0, n, B):
+            cb = min(B, n - c0)
+            self.buf.x[:cb].copy_(x[c0:c0 + cb])
+            key = ("verify", cb)
+            if key not in self._head_plans:
+                plan = DecodePlan(self.sm_count)
+                emit_head(plan, self.model, self.buf, 0, cb, self.comm, True, self.sm_count)
+                self._head_plans[key] = plan
+            self._head_plans[key].run()
+            out += [int(v) for v in self.buf.sampled[:cb].cpu()]
+        s.position = pos0 + n
+        return out
+
+    def rollback(self, slot: int, position: int) -> None:
+        """Forget everything at and after ``position`` (rejected draft tokens): the pages past it
+        go back to the pool and later appends overwrite the stale entries."""
+        s = self.slots[slot]
+        if not 0 <= position <= s.position:
+            raise ValueError(f"rollback to {position} outside 0..{s.position}")
+        self.pages.rollback(s.seq_id, position)
+        s.position = position
+        s.n_pages = -1                       # force a page-table refresh on the next reserve
+
+    def draft_step(self, slot: int, token: int, layer_subset: Sequence[int]) -> int:
+        """One greedy decode step of ``slot`` through a subset of the layers (shared KV cache)."""
+        key = tuple(layer_subset)
+        if not hasattr(self, "_draft_plans"):
+            self._draft_plans: Dict[tuple, DecodePlan] = {}
+        if key not in self._draft_plans:
+            if slot != 0:
+                raise ValueError("the layer-skipping draft runs in slot 0")
+            self._draft_plans[key] = build_decode_plan(self.model, self.buf, self.kv[0], self.kv[1], 1, self.splits, self.comm, True,
+                                                       self.sm_count, layer_subset=set(key))
+        s = self.slots[slot]
+        self._ensure_pages(slot, s.position + 1)
+        self._h_tokens[slot] = int(token)
+        self._h_positions[slot] = s.position
+        self.buf.tokens[slot:slot + 1].copy_(self._h_tokens[slot:slot + 1], non_blocking=True)
+        self.buf.positions[slot:slot + 1].copy_(self._h_positions[slot:slot + 1], non_blocking=True)
+        self._draft_plans[key].run()
+        s.position += 1
+        return int(self.buf.sampled[slot].item())
+
     # -- convenience ----------------------------------------------------------------------------
     def generate(self, prompt: Sequence[int], sampling: Optional[SamplingParams] = None, on_token=None) -> List[int]:
         """Generate for a single prompt in slot 0 (streams through ``on_token`` if given)."""

@@ -115,6 +115,7 @@ class AppState:
     compute_mode: str = "gpu"
     scorer: Any = None                  # optional callable(tokens) -> per-position logits (logprobs / perplexity / embeddings)
     context_length: int = 4096
+    classical: Any = None               # optional ClassicalServeState behind /v1/predict, /v1/explain
 
     @classmethod
     def demo(cls) -> "AppState":
@@ -426,14 +427,32 @@ def create_app(state: AppState) -> FastAPI:
 
     @app.get("/v1/audit/{request_id}")
     async def audit_get(request_id: str):
+        if state.classical is not None:
+            rec = state.classical.sink.get(request_id)
+            if rec is not None:
+                return json.loads(rec.to_json())
         if request_id not in state.audit:
-            raise HTTPException(404, "unknown request id")
+            raise HTTPException(404, f"audit record '{request_id}' not found")
         return state.audit[request_id]
 
+    def _classical(body: Dict[str, Any], explain: bool):
+        if state.classical is None:
+            raise HTTPException(501, "no classical model loaded (start with `serve --classical <model.apr>`)")
+        feats = body.get("features")
+        if not isinstance(feats, list) or not feats:
+            raise HTTPException(400, "features must be a non-empty list of numbers")
+        try:
+            return state.classical.predict(feats, explain=explain or bool(body.get("explain")), client=body.get("user"))
+        except ValueError as e:
+            raise HTTPException(400, str(e))
+
     @app.post("/v1/predict")
+    async def predict(body: Dict[str, Any]):
+        return _classical(body, False)
+
     @app.post("/v1/explain")
-    async def classical(_body: Dict[str, Any]):
-        raise HTTPException(501, "classical-ML .apr models are served by `realizar-b200 serve --classical <model.apr>`")
+    async def explain(body: Dict[str, Any]):
+        return _classical(body, True)
 
     # -- GPU ---------------------------------------------------------------------------------------
     @app.get("/v1/gpu/status")
