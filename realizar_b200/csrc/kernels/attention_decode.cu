@@ -2,8 +2,13 @@
 // work that surrounds it in a decode layer fused in:
 //   * per-head RMSNorm of q/k (QK-norm models), RoPE (NORM / NEOX, partial rotary) on q and k
 //   * append of the new k/v row to the paged cache
-//   * split-K over the context (grid.y) with the log-sum-exp merge done by the last CTA to
-//     finish for a (sequence, kv-head group), so there is no separate reduce launch.
+//   * split-K over the context (grid.y) merged without a second launch.  Up to 8 splits the CTAs
+//     of one (sequence, kv-head group) form a thread-block cluster and CTA 0 merges the others'
+//     partial results straight out of their shared memory (DSMEM); beyond 8 splits the partials go
+//     through global memory and the last CTA to finish (atomic ticket) merges them; one split
+//     writes its result directly.
+//   * optional sliding window (attend to the last `window` positions only) and a precomputed
+//     cos/sin table for RoPE (no transcendental math on the critical path).
 //
 // Cache layout: k_cache / v_cache = bf16 [num_pages, n_kv_heads, PAGE, head_dim]; a
 // sequence's pages are listed in page_table[b, :].  Positions are read from device memory so
@@ -14,14 +19,19 @@
 // src/cuda/executor/flash_decoding_graphed.rs:14-209, src/cuda/executor/batch.rs:18-400).
 #include "common.cuh"
 #include "attn_decode_static.h"
+#include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <math.h>
+
+namespace cg = cooperative_groups;
 
 namespace rlz {
 
 constexpr int ATT_PAGE = 16;
 constexpr int ATT_THREADS = 128;
 constexpr int ATT_TB = 4;            // tokens per half-warp per iteration
+constexpr int ATT_MAX_CLUSTER = 8;   // portable cluster size
+enum { MERGE_GLOBAL = 0, MERGE_CLUSTER = 1, MERGE_NONE = 2 };
 
 struct AttnDecodeParams {
   const float* qkv;        // [B, ld_qkv]: q heads | k heads | v heads (after bias)
@@ -41,14 +51,22 @@ struct AttnDecodeParams {
   int32_t pt_stride;                   // page_table elements between batch rows (0: every row shares one table)
   float rope_theta, eps, scale;
   int32_t no_append;                   // 1: the new rows are already in the cache (prefill), only attend
+  int32_t window;                      // > 0: attend to positions (pos - window, pos] only
+  int32_t rope_table_len;              // positions covered by rope_table
+  const float2* rope_table;            // [rope_table_len, rope_dim / 2] (cos, sin) or null
 };
 
-__device__ __forceinline__ void rope_inplace(float* v, int d_rot, int rope_type, int pos, float theta, int tid, int nthreads) {
+__device__ __forceinline__ void rope_inplace(float* v, int d_rot, int rope_type, int pos, float theta, const float2* table, int tid, int nthreads) {
   const int half = d_rot >> 1;
   for (int i = tid; i < half; i += nthreads) {
-    const float freq = powf(theta, -2.f * (float)i / (float)d_rot);
     float sn, cs;
-    sincosf((float)pos * freq, &sn, &cs);
+    if (table) {
+      const float2 t = __ldg(table + (int64_t)pos * half + i);
+      cs = t.x; sn = t.y;
+    } else {
+      const float freq = powf(theta, -2.f * (float)i / (float)d_rot);
+      sincosf((float)pos * freq, &sn, &cs);
+    }
     const int i0 = rope_type == 2 ? i : 2 * i, i1 = rope_type == 2 ? i + half : 2 * i + 1;
     const float a = v[i0], b = v[i1];
     v[i0] = a * cs - b * sn;
@@ -56,7 +74,7 @@ __device__ __forceinline__ void rope_inplace(float* v, int d_rot, int rope_type,
   }
 }
 
-template <int GT>
+template <int GT, int MERGE>
 __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_constant__ AttnDecodeParams p) {
   const int G = p.n_heads / p.n_kv_heads;
   const int hgroups = (G + GT - 1) / GT;
@@ -70,6 +88,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
   __shared__ float q_s[GT][128];
   __shared__ float k_s[128], v_s[128];
   __shared__ float part_s[ATT_THREADS / 16][GT][128 + 2];
+  __shared__ float res_s[GT][128 + 2];      // this CTA's split result (read by cluster rank 0 in MERGE_CLUSTER)
   __shared__ int last_flag;
 
   pdl_launch_dependents();
@@ -78,9 +97,11 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
   const int pos = p.positions[b];
   if (pos < 0) return;
   const int seq_len = pos + 1;
-  int chunk = (seq_len + p.splits - 1) / p.splits;
+  const int lo = p.window > 0 ? max(0, seq_len - p.window) : 0;      // first position attended to
+  const int lo_al = lo / ATT_PAGE * ATT_PAGE;
+  int chunk = (seq_len - lo_al + p.splits - 1) / p.splits;
   chunk = (chunk + ATT_PAGE - 1) / ATT_PAGE * ATT_PAGE;
-  const int start = split * chunk, end = min(seq_len, start + chunk);
+  const int start = lo_al + split * chunk, end = min(seq_len, start + chunk);
   const bool owner = !p.no_append && start <= pos && pos < end;
 
   // ---- stage q (this head group), and k/v of the new token ---------------------------------
@@ -109,8 +130,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
     __syncthreads();
   }
   if (p.rope_dim > 0) {
-    for (int g = 0; g < gn; ++g) rope_inplace(q_s[g], p.rope_dim, p.rope_type, pos, p.rope_theta, tid, ATT_THREADS);
-    if (owner) rope_inplace(k_s, p.rope_dim, p.rope_type, pos, p.rope_theta, tid, ATT_THREADS);
+    const float2* tab = (p.rope_table && pos < p.rope_table_len) ? p.rope_table : nullptr;
+    for (int g = 0; g < gn; ++g) rope_inplace(q_s[g], p.rope_dim, p.rope_type, pos, p.rope_theta, tab, tid, ATT_THREADS);
+    if (owner) rope_inplace(k_s, p.rope_dim, p.rope_type, pos, p.rope_theta, tab, tid, ATT_THREADS);
     __syncthreads();
   }
   const int32_t* pt = p.page_table + (int64_t)b * p.pt_stride;
@@ -182,7 +204,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
         x += __shfl_xor_sync(hmask, x, 4);
         x += __shfl_xor_sync(hmask, x, 2);
         x += __shfl_xor_sync(hmask, x, 1);
-        s[t] = base + t < end ? x : -INFINITY;
+        s[t] = (base + t < end && base + t >= lo) ? x : -INFINITY;
       }
       float mn = m[g];
 #pragma unroll
@@ -216,8 +238,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
   }
   __syncthreads();
   const int S = p.splits;
-  for (int i = tid; i < gn * d; i += ATT_THREADS) {
-    const int g = i / d, j = i - g * d;
+  for (int i = tid; i < gn * d + gn; i += ATT_THREADS) {
+    const bool stat = i >= gn * d;                 // the trailing gn items carry (max, sum) of each head
+    const int g = stat ? i - gn * d : i / d, j = stat ? 0 : i - g * d;
     float mm = -INFINITY;
     for (int w = 0; w < ATT_THREADS / 16; ++w) mm = fmaxf(mm, part_s[w][g][128]);
     float a = 0.f, ll = 0.f;
@@ -226,9 +249,38 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
       const float c = mw == -INFINITY ? 0.f : exp2f(mw - mm);
       a += c * part_s[w][g][j]; ll += c * part_s[w][g][129];
     }
-    float* dst = p.partial + (((int64_t)b * p.n_heads + kvh * G + g0 + g) * S + split) * (d + 2);
-    dst[j] = a;
-    if (j == 0) { dst[d] = mm; dst[d + 1] = ll; }
+    if (MERGE == MERGE_NONE) {
+      if (!stat) p.out[(int64_t)b * p.ld_out + (kvh * G + g0 + g) * d + j] = a / ll;
+    } else if (MERGE == MERGE_CLUSTER) {
+      if (stat) { res_s[g][128] = mm; res_s[g][129] = ll; } else res_s[g][j] = a;
+    } else {
+      float* dst = p.partial + (((int64_t)b * p.n_heads + kvh * G + g0 + g) * S + split) * (d + 2);
+      if (stat) { dst[d] = mm; dst[d + 1] = ll; } else dst[j] = a;
+    }
+  }
+  if (MERGE == MERGE_NONE) return;
+
+  if (MERGE == MERGE_CLUSTER) {
+    // ---- cluster rank 0 merges the splits out of its peers' shared memory ----------------------
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();                                  // every CTA's res_s is complete and visible
+    if (cluster.block_rank() == 0) {
+      for (int i = tid; i < gn * d; i += ATT_THREADS) {
+        const int g = i / d, j = i - g * d;
+        float mm = -INFINITY;
+        for (int s = 0; s < S; ++s) mm = fmaxf(mm, cluster.map_shared_rank(&res_s[0][0], s)[g * 130 + 128]);
+        float a = 0.f, ll = 0.f;
+        for (int s = 0; s < S; ++s) {
+          const float* r = cluster.map_shared_rank(&res_s[0][0], s) + g * 130;
+          const float ms = r[128];
+          const float c = ms == -INFINITY ? 0.f : exp2f(ms - mm);
+          a += c * r[j]; ll += c * r[129];
+        }
+        p.out[(int64_t)b * p.ld_out + (kvh * G + g0 + g) * d + j] = a / ll;
+      }
+    }
+    cluster.sync();                                  // peers keep their shared memory alive until rank 0 has read it
+    return;
   }
 
   // ---- last CTA of this (sequence, kv head, head group) merges the splits ----------------------
@@ -259,6 +311,34 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
   }
 }
 
+// Validate and launch: picks the head-group tile and the merge strategy.
+static int attn_decode_dispatch(const AttnDecodeParams& p, cudaStream_t st) {
+  if (p.head_dim % 8 || p.head_dim > 128 || p.head_dim < 8) return -1;
+  if (p.n_kv_heads < 1 || p.n_heads % p.n_kv_heads || p.splits < 1 || p.batch < 1) return -2;
+  if (p.rope_dim > p.head_dim || (p.rope_dim & 1)) return -3;
+  if (((uintptr_t)p.k_cache & 15) || ((uintptr_t)p.v_cache & 15)) return -4;
+  if (p.window < 0) return -5;
+  const int G = p.n_heads / p.n_kv_heads;
+  const int GT = G == 1 ? 1 : G == 2 ? 2 : G == 8 ? 8 : 4;
+  const int hgroups = (G + GT - 1) / GT;
+  const int merge = p.splits == 1 ? MERGE_NONE : p.splits <= ATT_MAX_CLUSTER ? MERGE_CLUSTER : MERGE_GLOBAL;
+  dim3 grid(p.n_kv_heads * hgroups, p.splits, p.batch), block(ATT_THREADS);
+  dim3 cl(1, merge == MERGE_CLUSTER ? p.splits : 1, 1);
+#define RLZ_ATT_CASE(GT_) \
+  (merge == MERGE_NONE ? launch_cluster(attn_decode_kernel<GT_, MERGE_NONE>, grid, block, cl, 0, st, p) \
+   : merge == MERGE_CLUSTER ? launch_cluster(attn_decode_kernel<GT_, MERGE_CLUSTER>, grid, block, cl, 0, st, p) \
+                            : launch_cluster(attn_decode_kernel<GT_, MERGE_GLOBAL>, grid, block, cl, 0, st, p))
+  cudaError_t e;
+  switch (GT) {
+    case 1: e = RLZ_ATT_CASE(1); break;
+    case 2: e = RLZ_ATT_CASE(2); break;
+    case 8: e = RLZ_ATT_CASE(8); break;
+    default: e = RLZ_ATT_CASE(4); break;
+  }
+#undef RLZ_ATT_CASE
+  return (int)e;
+}
+
 }  // namespace rlz
 
 extern "C" {
@@ -269,27 +349,7 @@ long long rlz_attn_decode_partial_floats(int batch, int n_heads, int splits, int
 }
 long long rlz_attn_decode_counter_ints(int batch, int n_heads) { return (long long)batch * n_heads; }
 
-int rlz_attn_decode(const rlz::AttnDecodeParams* pp, void* stream) {
-  using namespace rlz;
-  const AttnDecodeParams& p = *pp;
-  if (p.head_dim % 8 || p.head_dim > 128 || p.head_dim < 8) return -1;
-  if (p.n_heads % p.n_kv_heads || p.splits < 1 || p.batch < 1) return -2;
-  if (p.rope_dim > p.head_dim || (p.rope_dim & 1)) return -3;
-  if (((uintptr_t)p.k_cache & 15) || ((uintptr_t)p.v_cache & 15)) return -4;
-  const int G = p.n_heads / p.n_kv_heads;
-  const int GT = G == 1 ? 1 : G == 2 ? 2 : G == 8 ? 8 : 4;
-  const int hgroups = (G + GT - 1) / GT;
-  dim3 grid(p.n_kv_heads * hgroups, p.splits, p.batch), block(ATT_THREADS);
-  cudaError_t e;
-  cudaStream_t st = (cudaStream_t)stream;
-  switch (GT) {
-    case 1: e = launch(attn_decode_kernel<1>, grid, block, 0, st, p); break;
-    case 2: e = launch(attn_decode_kernel<2>, grid, block, 0, st, p); break;
-    case 8: e = launch(attn_decode_kernel<8>, grid, block, 0, st, p); break;
-    default: e = launch(attn_decode_kernel<4>, grid, block, 0, st, p); break;
-  }
-  return (int)e;
-}
+int rlz_attn_decode(const rlz::AttnDecodeParams* pp, void* stream) { return rlz::attn_decode_dispatch(*pp, (cudaStream_t)stream); }
 
 }  // extern "C"
 
@@ -341,18 +401,7 @@ int rlz_attn_decode_static(const rlz::AttnDecodeParams* pp, void* stream) {
   }
   p.partial = sc.partial;
   p.counters = sc.counters;
-  const int G = p.n_heads / p.n_kv_heads;
-  const int GT = G == 1 ? 1 : G == 2 ? 2 : G == 8 ? 8 : 4;
-  const int hgroups = (G + GT - 1) / GT;
-  dim3 grid(p.n_kv_heads * hgroups, p.splits, p.batch), block(ATT_THREADS);
-  cudaError_t e;
-  switch (GT) {
-    case 1: e = launch(attn_decode_kernel<1>, grid, block, 0, st, p); break;
-    case 2: e = launch(attn_decode_kernel<2>, grid, block, 0, st, p); break;
-    case 8: e = launch(attn_decode_kernel<8>, grid, block, 0, st, p); break;
-    default: e = launch(attn_decode_kernel<4>, grid, block, 0, st, p); break;
-  }
-  return (int)e;
+  return attn_decode_dispatch(p, st);
 }
 
 }  // extern "C"

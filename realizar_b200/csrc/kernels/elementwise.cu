@@ -150,6 +150,16 @@ __global__ void kv_append_kernel(const float* k, const float* v, int64_t ld, __n
   }
 }
 
+// physical page of each row's current position (rows with position < 0 are idle)
+__global__ void page_rows_kernel(const int32_t* page_table, int64_t ld, const int32_t* positions, int32_t* out, int n, int page) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int pos = positions[i];
+  out[i] = pos >= 0 ? page_table[(int64_t)i * ld + pos / page] : 0;
+}
+
 // bf16 producers for the tensor-core GEMM operands
 __global__ void to_bf16_kernel(const float* src, __nv_bfloat16* dst, int64_t rows, int cols, int64_t ld_s, int64_t ld_d) {
   pdl_launch_dependents();
@@ -272,6 +282,10 @@ int rlz_kv_append(const float* k, const float* v, long long ld, void* k_cache, v
                   const int32_t* page_rows, int n_tokens, int n_kv_heads, int d, int page, void* stream) {
   return (int)launch(kv_append_kernel, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, k, v, (int64_t)ld, (__nv_bfloat16*)k_cache,
                      (__nv_bfloat16*)v_cache, positions, page_rows, n_kv_heads, d, page);
+}
+
+int rlz_page_rows(const int32_t* page_table, long long ld, const int32_t* positions, int32_t* out, int n, int page, void* stream) {
+  return (int)launch(page_rows_kernel, dim3((n + 127) / 128), dim3(128), 0, (cudaStream_t)stream, page_table, (int64_t)ld, positions, out, n, page);
 }
 
 }  // extern "C"

@@ -2,30 +2,37 @@
 // K-quant block layout (Q4_K / Q5_K / Q6_K) or dense bf16/f16, X in bf16, fp32 accumulation in
 // tensor memory.  Used for prefill and for decode batches too large for the GEMV kernels.
 //
-// One CTA (128 threads) owns 128 weight rows x MT tokens (x one K split):
-//   * every thread dequantises 64 weights of "its" row per K step straight into shared memory as
-//     bf16 in the K-major 128-byte-swizzled layout that tcgen05.mma reads (operand A), and copies
-//     64 activations of "its" token the same way (operand B);
-//   * one elected thread issues four tcgen05.mma (M=128, N=MT, K=16) per K step and commits them
-//     to an mbarrier; the two shared-memory stages alternate, so dequantisation of step s+1
-//     overlaps the tensor-core work of step s;
-//   * the accumulator lives in TMEM (MT columns); the epilogue reads it back with tcgen05.ld,
-//     applies bias / activation / residual and stores (or atomically adds, with split-K) fp32.
-// Every mbarrier wait is bounded; on expiry the CTA records error 3001, releases its tensor
-// memory and returns.
+// One CTA owns 128 weight rows x NT tokens (x one K split) and is warp-specialised:
+//   * warps 0-7 (256 threads) dequantise: per K step of 64 columns each thread turns 32 weights of
+//     "its" row into bf16 and stores them into shared memory in the K-major 128-byte-swizzled
+//     layout that tcgen05.mma reads (operand A);
+//   * warp 8 (one thread) streams the activations (operand B, NT x 64 bf16) with TMA
+//     (cp.async.bulk.tensor, 128-byte swizzle, zero fill beyond the last token);
+//   * warp 9 (one thread) issues four tcgen05.mma (M=128, N=NT, K=16) per K step and commits them
+//     to the stage's "empty" mbarrier;
+//   * a ring of GM_STAGES shared-memory stages decouples the three roles ("full" barrier: 8 warp
+//     arrivals + the TMA transaction bytes; "empty" barrier: the MMA commit);
+//   * the accumulator lives in TMEM (NT columns); after the last commit all 8 dequant warps read it
+//     back with tcgen05.ld, apply bias / activation / residual and store (or, with split-K,
+//     atomically add) fp32.
+// Every mbarrier wait is bounded; on expiry the CTA records error 3001, drains, releases its
+// tensor memory and returns.
 //
 // Replaces the reference's q4k/q5k/q6k_gemm_ggml, tensor_core_q4k_gemm (WMMA), dp4a_q4k_gemm,
 // dequant-to-f16/f32 + cuBLAS HGEMM/SGEMM and cuBLASLt FP8 call sites
 // (src/cuda/executor/layers/cublas_prefill/gemm.rs:70-1100).
 #include "common.cuh"
 #include "../gemv_blocks.h"
+#include <cuda.h>
 #include <cuda_bf16.h>
 
 namespace rlz {
 
 __device__ int g_gemm_error = 0;
 
-constexpr int GM_THREADS = 128;
+constexpr int GM_PRODUCERS = 256;      // dequant threads (warps 0-7)
+constexpr int GM_THREADS = GM_PRODUCERS + 64;   // + TMA warp + MMA warp
+constexpr int GM_STAGES = 4;
 constexpr int GM_ROWS = 128;          // weight rows per CTA = MMA M
 constexpr int GM_KSTEP = 64;          // K elements per stage (one 128-byte swizzle row of bf16)
 constexpr uint32_t GM_WAIT_LIMIT = 1u << 24;
@@ -80,70 +87,74 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *(const uint32_t*)&v;
 }
 
-// 64 weights of one row starting at column k0 (multiple of 64) as 32 packed bf16 pairs
-__device__ __forceinline__ void dequant_row64(const uint8_t* row, int qtype, int k0, uint32_t* out) {
+// Move the bit field that starts at bit `from` of w so that it starts at bit `to` (both compile-time after unrolling).
+__device__ __forceinline__ uint32_t place_bits(uint32_t w, int from, int to) { return to >= from ? (w << (to - from)) : (w >> (from - to)); }
+
+// 32 weights of one row: columns [k0 + 32*half, k0 + 32*half + 32) with k0 a multiple of 64, as 16 packed bf16 pairs.
+// The integer code q of a weight is dropped into the top mantissa bits of 1.0f, giving 1 + q / 2^bits exactly, so the
+// whole affine dequantisation is one FMA per weight:  scale * q - off  =  (scale * 2^bits) * (1 + q / 2^bits) - (scale * 2^bits + off).
+__device__ __forceinline__ void dequant_row32(const uint8_t* row, int qtype, int k0, int half, uint32_t* out) {
   const int sb = k0 >> 8, g = (k0 >> 6) & 3;
   if (qtype == QT_Q4_K || qtype == QT_Q5_K) {
-    const int bb = qtype == QT_Q4_K ? 144 : 176;
-    const uint8_t* blk = row + (int64_t)sb * bb;
+    const bool q5 = qtype == QT_Q5_K;
+    const uint8_t* blk = row + (int64_t)sb * (q5 ? 176 : 144);
     const uint4 hdr = __ldg((const uint4*)blk);
     const float d = h2f_alu(hdr.x & 0xFFFFu), dmin = h2f_alu(hdr.x >> 16);
     const K4Scales ks = k4_unpack(hdr.y, hdr.z, hdr.w);
-    const float d0 = d * (float)k4_pick(ks.sc_lo, ks.sc_hi, 2 * g), d1 = d * (float)k4_pick(ks.sc_lo, ks.sc_hi, 2 * g + 1);
-    const float m0 = dmin * (float)k4_pick(ks.m_lo, ks.m_hi, 2 * g), m1 = dmin * (float)k4_pick(ks.m_lo, ks.m_hi, 2 * g + 1);
-    const uint8_t* qs = blk + (qtype == QT_Q4_K ? 16 : 48) + 32 * g;
+    const float dd = d * (float)k4_pick(ks.sc_lo, ks.sc_hi, 2 * g + half) * (q5 ? 32.f : 16.f);
+    const float cc = -(dd + dmin * (float)k4_pick(ks.m_lo, ks.m_hi, 2 * g + half));
+    const uint8_t* qs = blk + (q5 ? 48 : 16) + 32 * g;
     const uint4 q0 = __ldg((const uint4*)qs), q1 = __ldg((const uint4*)(qs + 16));
     const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
     uint32_t hw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (qtype == QT_Q5_K) {
+    if (q5) {
       const uint4 h0 = __ldg((const uint4*)(blk + 16)), h1 = __ldg((const uint4*)(blk + 32));
       hw[0] = h0.x; hw[1] = h0.y; hw[2] = h0.z; hw[3] = h0.w; hw[4] = h1.x; hw[5] = h1.y; hw[6] = h1.z; hw[7] = h1.w;
     }
+    const int nsh = 4 * half, hsh = 2 * g + half;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {                         // word i holds elements 4i..4i+3 (low nibbles) and 32+4i.. (high)
-      float lo[4], hi[4];
+    for (int i = 0; i < 8; ++i) {                         // word i holds elements 4i..4i+3 of this half
+      const uint32_t wq = qw[i] >> nsh, hq = hw[i] >> hsh;   // nibble b at bits 8b..8b+3, fifth bit at bit 8b
+      float v[4];
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
-        int ql = (qw[i] >> (8 * b)) & 0xF, qh = (qw[i] >> (8 * b + 4)) & 0xF;
-        if (qtype == QT_Q5_K) { ql |= ((hw[i] >> (8 * b + 2 * g)) & 1) << 4; qh |= ((hw[i] >> (8 * b + 2 * g + 1)) & 1) << 4; }
-        lo[b] = d0 * (float)ql - m0; hi[b] = d1 * (float)qh - m1;
+        uint32_t m;
+        if (q5) m = (place_bits(wq, 8 * b, 18) & 0x003C0000u) | (place_bits(hq, 8 * b, 22) & 0x00400000u);
+        else m = place_bits(wq, 8 * b, 19) & 0x00780000u;
+        v[b] = fmaf(dd, __uint_as_float(m | 0x3F800000u), cc);
       }
-      out[2 * i] = pack_bf16(lo[0], lo[1]); out[2 * i + 1] = pack_bf16(lo[2], lo[3]);
-      out[16 + 2 * i] = pack_bf16(hi[0], hi[1]); out[16 + 2 * i + 1] = pack_bf16(hi[2], hi[3]);
+      out[2 * i] = pack_bf16(v[0], v[1]); out[2 * i + 1] = pack_bf16(v[2], v[3]);
     }
   } else if (qtype == QT_Q6_K) {
-    // the 64 columns [64g', 64g'+64) of a block: half n = g >> 1, positions 64*(g&1) .. +63 within the half
+    // the 64 columns of group g: block half n = g >> 1, elements 64*(g&1) .. +63 of that half (upper: high nibbles)
     const uint8_t* blk = row + (int64_t)sb * Q6K_DEV_STRIDE;
-    const int n = g >> 1, upper = g & 1;                  // upper: elements 64..127 of the half use the high nibbles
+    const int n = g >> 1, upper = g & 1, part = half;     // 32 elements: l = 0..31 of ql[l + 32*part]
     const float d = h2f_alu((uint32_t)blk[208] | ((uint32_t)blk[209] << 8));
-    const int8_t* sc = (const int8_t*)(blk + 192 + 8 * n + 4 * upper);     // scales of the four 16-chunks
+    const int8_t* sc = (const int8_t*)(blk + 192 + 8 * n + 4 * upper);
+    const uint8_t* ql = blk + 64 * n + 32 * part;
+    const uint8_t* qh = blk + 128 + 32 * n;
+    const float s0 = d * (float)sc[2 * part] * 64.f, s1 = d * (float)sc[2 * part + 1] * 64.f;
+    const float c0 = -1.5f * s0, c1 = -1.5f * s1;         // -(64 s + 32 s): value = s * (q - 32)
+    const int hs = 2 * (2 * upper + part), ns = 4 * upper;
 #pragma unroll
-    for (int part = 0; part < 2; ++part) {                // 32 elements each: l = 0..31 of ql[l] / ql[l+32]
-      const uint8_t* ql = blk + 64 * n + 32 * part;
-      const uint8_t* qh = blk + 128 + 32 * n;
-      const float s0 = d * (float)sc[2 * part], s1 = d * (float)sc[2 * part + 1];
+    for (int w4 = 0; w4 < 8; ++w4) {
+      const uint32_t lw = __ldg((const uint32_t*)(ql + 4 * w4)) >> ns, hwv = __ldg((const uint32_t*)(qh + 4 * w4)) >> hs;
+      float v[4];
 #pragma unroll
-      for (int w4 = 0; w4 < 8; ++w4) {
-        const uint32_t lw = __ldg((const uint32_t*)(ql + 4 * w4)), hwv = __ldg((const uint32_t*)(qh + 4 * w4));
-        float v[4];
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          const int l = 4 * w4 + b;
-          const int nib = upper ? ((lw >> (8 * b + 4)) & 0xF) : ((lw >> (8 * b)) & 0xF);
-          const int hb = (hwv >> (8 * b + 2 * (2 * upper + part))) & 3;
-          v[b] = (l < 16 ? s0 : s1) * (float)((nib | (hb << 4)) - 32);
-        }
-        out[16 * part + 2 * w4] = pack_bf16(v[0], v[1]); out[16 * part + 2 * w4 + 1] = pack_bf16(v[2], v[3]);
+      for (int b = 0; b < 4; ++b) {
+        const uint32_t m = (place_bits(lw, 8 * b, 17) & 0x001E0000u) | (place_bits(hwv, 8 * b, 21) & 0x00600000u);
+        v[b] = fmaf(w4 < 4 ? s0 : s1, __uint_as_float(m | 0x3F800000u), w4 < 4 ? c0 : c1);
       }
+      out[2 * w4] = pack_bf16(v[0], v[1]); out[2 * w4 + 1] = pack_bf16(v[2], v[3]);
     }
   } else if (qtype == QT_BF16) {
-    const uint4* src = (const uint4*)(row + (int64_t)k0 * 2);
+    const uint4* src = (const uint4*)(row + (int64_t)(k0 + 32 * half) * 2);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { const uint4 t = __ldg(src + i); out[4 * i] = t.x; out[4 * i + 1] = t.y; out[4 * i + 2] = t.z; out[4 * i + 3] = t.w; }
+    for (int i = 0; i < 4; ++i) { const uint4 t = __ldg(src + i); out[4 * i] = t.x; out[4 * i + 1] = t.y; out[4 * i + 2] = t.z; out[4 * i + 3] = t.w; }
   } else {                                                // F16
-    const uint4* src = (const uint4*)(row + (int64_t)k0 * 2);
+    const uint4* src = (const uint4*)(row + (int64_t)(k0 + 32 * half) * 2);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 4; ++i) {
       const uint4 t = __ldg(src + i); const uint32_t w[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) out[4 * i + j] = pack_bf16(h2f_alu(w[j] & 0xFFFFu), h2f_alu(w[j] >> 16));
@@ -151,34 +162,51 @@ __device__ __forceinline__ void dequant_row64(const uint8_t* row, int qtype, int
   }
 }
 
-// store 64 bf16 (32 words) as row r of a [rows x 64] K-major SWIZZLE_128B tile
-__device__ __forceinline__ void store_row_sw128(uint8_t* tile, int r, const uint32_t* v) {
+// store 32 bf16 (16 words) as columns [32*half, 32*half+32) of row r of a [rows x 64] K-major SWIZZLE_128B tile
+__device__ __forceinline__ void store_half_row_sw128(uint8_t* tile, int r, int half, const uint32_t* v) {
   uint8_t* base = tile + (r >> 3) * 1024 + (r & 7) * 128;
 #pragma unroll
-  for (int c = 0; c < 8; ++c)
-    *(uint4*)(base + ((c ^ (r & 7)) << 4)) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+  for (int j = 0; j < 4; ++j) {
+    const int c = 4 * half + j;
+    *(uint4*)(base + ((c ^ (r & 7)) << 4)) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+  }
 }
 
-template <int MT>
-__global__ void __launch_bounds__(GM_THREADS) gemm_kquant_tcgen05_kernel(const __grid_constant__ GemmParams p) {
+__device__ __forceinline__ void gm_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(gm_smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void gm_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(gm_smem_u32(bar)), "r"(bytes) : "memory");
+}
+// 2-D tiled TMA load of a [rows x 64] bf16 box at (column x, row y) into shared memory; x * 2 bytes is a multiple of 128
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(gm_smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(gm_smem_u32(bar)) : "memory");
+}
+
+template <int NT>
+__global__ void __launch_bounds__(GM_THREADS) gemm_kquant_tcgen05_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap xmap) {
   extern __shared__ __align__(1024) uint8_t gsm[];
-  __shared__ __align__(8) uint64_t bar[2];
+  __shared__ __align__(8) uint64_t full_bar[GM_STAGES], empty_bar[GM_STAGES], done_bar;
   __shared__ uint32_t tmem_base_s;
   __shared__ int failed_s;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n0 = blockIdx.x * GM_ROWS, m0 = blockIdx.y * MT;
-  // shared memory: 2 stages x (A tile 128 x 64 bf16 = 16 KB, B tile MT x 64 bf16)
+  const int n0 = blockIdx.x * GM_ROWS, m0 = blockIdx.y * NT;
   uint8_t* sm = (uint8_t*)(((uintptr_t)gsm + 1023) & ~(uintptr_t)1023);
-  constexpr int A_BYTES = GM_ROWS * 128, B_BYTES = MT * 128, STAGE = A_BYTES + B_BYTES;
+  constexpr int A_BYTES = GM_ROWS * 128, B_BYTES = NT * 128, STAGE = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = NT < 32 ? 32 : NT;
 
   if (tid == 0) {
     failed_s = 0;
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gm_smem_u32(&bar[0])));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gm_smem_u32(&bar[1])));
+    for (int s = 0; s < GM_STAGES; ++s) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(gm_smem_u32(&full_bar[s])), "r"(GM_PRODUCERS / 32 + 1));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gm_smem_u32(&empty_bar[s])));
+    }
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gm_smem_u32(&done_bar)));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 0) {                                        // one warp allocates MT columns of tensor memory
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(gm_smem_u32(&tmem_base_s)), "r"((uint32_t)(MT < 32 ? 32 : MT)) : "memory");
+  if (warp == 0) {                                        // one warp allocates the accumulator columns of tensor memory
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(gm_smem_u32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -192,84 +220,99 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_kquant_tcgen05_kernel(const _
   const int ksteps_total = p.k / GM_KSTEP;
   const int per = (ksteps_total + p.splitk - 1) / p.splitk;
   const int ks0 = blockIdx.z * per, ks1 = min(ksteps_total, ks0 + per);
-  const uint32_t idesc = make_idesc_bf16(GM_ROWS, MT);
-  const int wrow = n0 + tid;                              // my weight row
-  const uint8_t* wptr = p.W + (int64_t)min(wrow, p.n - 1) * p.w_stride;
+  const int nit = max(0, ks1 - ks0);
   bool ok = true;
 
-  for (int ks = ks0, it = 0; ks < ks1; ++ks, ++it) {
-    const int s = it & 1;
-    if (it >= 2) {                                        // stage s is free once the MMAs issued two steps ago completed
-      ok = ok && gm_wait(&bar[s], (uint32_t)((it >> 1) - 1) & 1u);
-      if (!ok) break;
-    }
-    uint8_t* At = sm + s * STAGE;
-    uint8_t* Bt = At + A_BYTES;
-    uint32_t v[32];
-    if (wrow < p.n) dequant_row64(wptr, p.qtype, ks * GM_KSTEP, v);
-    else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = 0u;
-    }
-    store_row_sw128(At, tid, v);
-    for (int t = tid; t < MT; t += GM_THREADS) {          // activations: token t of this tile
-      const int tok = m0 + t;
-      if (tok < p.m) {
-        const uint4* src = (const uint4*)(p.X + (int64_t)tok * p.ldx + (int64_t)ks * GM_KSTEP);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { const uint4 x4 = src[i]; v[4 * i] = x4.x; v[4 * i + 1] = x4.y; v[4 * i + 2] = x4.z; v[4 * i + 3] = x4.w; }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = 0u;
+  if (warp < GM_PRODUCERS / 32) {
+    // ---- dequant producers: thread -> (row, half of the 64-column step) ---------------------
+    const int r = tid & (GM_ROWS - 1), half = tid >> 7;
+    const int wrow = n0 + r;
+    const uint8_t* wptr = p.W + (int64_t)min(wrow, p.n - 1) * p.w_stride;
+    for (int it = 0; it < nit; ++it) {
+      const int s = it % GM_STAGES;
+      if (it >= GM_STAGES) {                              // the MMAs that read this stage GM_STAGES steps ago are done
+        ok = gm_wait(&empty_bar[s], (uint32_t)(it / GM_STAGES - 1) & 1u);
+        if (!ok) break;
       }
-      store_row_sw128(Bt, t, v);
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic-proxy writes -> visible to the tensor core
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (tid == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint64_t da = make_sdesc_k_sw128(gm_smem_u32(At)), db = make_sdesc_k_sw128(gm_smem_u32(Bt));
+      uint32_t v[16];
+      if (wrow < p.n) dequant_row32(wptr, p.qtype, (ks0 + it) * GM_KSTEP, half, v);
+      else {
 #pragma unroll
-      for (int kk = 0; kk < GM_KSTEP / 16; ++kk)          // advance 32 bytes (two 16-byte units) per K=16 slice
-        umma_bf16(tmem_d, da + (uint64_t)(2 * kk), db + (uint64_t)(2 * kk), idesc, (it > 0 || kk > 0) ? 1u : 0u);
-      umma_commit(&bar[s]);
+        for (int i = 0; i < 16; ++i) v[i] = 0u;
+      }
+      store_half_row_sw128(sm + s * STAGE, r, half, v);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic-proxy writes -> visible to the tensor core
+      __syncwarp();
+      if (lane == 0) gm_arrive(&full_bar[s]);
+    }
+  } else if (warp == GM_PRODUCERS / 32) {
+    // ---- TMA producer: activations of this token tile -------------------------------------------
+    if (lane == 0) {
+      for (int it = 0; it < nit; ++it) {
+        const int s = it % GM_STAGES;
+        if (it >= GM_STAGES) {
+          ok = gm_wait(&empty_bar[s], (uint32_t)(it / GM_STAGES - 1) & 1u);
+          if (!ok) break;
+        }
+        uint8_t* Bt = sm + s * STAGE + A_BYTES;
+        gm_arrive_expect_tx(&full_bar[s], (uint32_t)B_BYTES);
+        tma_load_2d(Bt, &xmap, (ks0 + it) * GM_KSTEP, m0, &full_bar[s]);
+      }
+    }
+  } else {
+    // ---- MMA issuer --------------------------------------------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(GM_ROWS, NT);
+      for (int it = 0; it < nit; ++it) {
+        const int s = it % GM_STAGES;
+        ok = gm_wait(&full_bar[s], (uint32_t)(it / GM_STAGES) & 1u);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t da = make_sdesc_k_sw128(gm_smem_u32(sm + s * STAGE)), db = make_sdesc_k_sw128(gm_smem_u32(sm + s * STAGE + A_BYTES));
+#pragma unroll
+        for (int kk = 0; kk < GM_KSTEP / 16; ++kk)        // advance 32 bytes (two 16-byte units) per K=16 slice
+          umma_bf16(tmem_d, da + (uint64_t)(2 * kk), db + (uint64_t)(2 * kk), idesc, (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&empty_bar[s]);
+      }
+      if (ok) umma_commit(&done_bar);                     // arrives when every MMA above has completed
     }
   }
-  // wait for the last commits of both stages
-  const int nit = max(0, ks1 - ks0);
-  if (ok && nit >= 1) { const int it = nit - 1; ok = gm_wait(&bar[it & 1], (uint32_t)(it >> 1) & 1u); }
-  if (ok && nit >= 2) { const int it = nit - 2; ok = gm_wait(&bar[it & 1], (uint32_t)(it >> 1) & 1u); }
   if (!ok) { failed_s = 1; atomicExch(&g_gemm_error, 3001); }
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-  // ---- epilogue: TMEM lane = weight row, column = token --------------------------------------
-  if (ok && nit > 0) {
-    const int row = n0 + warp * 32 + lane;
-    const float bias = (p.bias && row < p.n && blockIdx.z == 0) ? p.bias[row] : 0.f;
+  // ---- epilogue: TMEM lane = weight row, column = token; 8 warps, each a lane quarter x column half ----
+  if (warp < GM_PRODUCERS / 32 && nit > 0) {
+    if (ok && !gm_wait(&done_bar, 0u)) { ok = false; failed_s = 1; atomicExch(&g_gemm_error, 3001); }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    constexpr int COLS_PER_WARP = NT >= 64 ? NT / 2 : NT;
+    const int q = warp & 3, chalf = warp >> 2;
+    if (ok && (NT >= 64 || chalf == 0)) {
+      const int row = n0 + q * 32 + lane;
+      const float bias = (p.bias && row < p.n && blockIdx.z == 0) ? p.bias[row] : 0.f;
 #pragma unroll 1
-    for (int c0 = 0; c0 < MT; c0 += 32) {
-      uint32_t r[32];
-      const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
-      asm volatile(
-          "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-          : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
-            "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-            "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-          : "r"(taddr) : "memory");
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (row < p.n) {
+      for (int c0 = chalf * COLS_PER_WARP; c0 < (chalf + 1) * COLS_PER_WARP; c0 += 32) {
+        if (m0 + c0 >= p.m) break;                        // warp-uniform: no tokens left in this tile
+        uint32_t r[32];
+        const uint32_t taddr = tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+              "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+              "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr) : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < p.n) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int tok = m0 + c0 + j;
-          if (tok < p.m) {
-            float v = __uint_as_float(r[j]) + bias;
-            float* dst = p.Y + (int64_t)tok * p.ldy + row;
-            if (p.atomic_out) atomicAdd(dst, v);
-            else {
-              if (p.act == ACT_GELU) v = gelu_tanh(v); else if (p.act == ACT_SILU) v = silu(v);
-              if (p.residual) v += p.residual[(int64_t)tok * p.ld_res + row];
-              *dst = v;
+          for (int j = 0; j < 32; ++j) {
+            const int tok = m0 + c0 + j;
+            if (tok < p.m) {
+              float v = __uint_as_float(r[j]) + bias;
+              float* dst = p.Y + (int64_t)tok * p.ldy + row;
+              if (p.atomic_out) atomicAdd(dst, v);
+              else {
+                if (p.act == ACT_GELU) v = gelu_tanh(v); else if (p.act == ACT_SILU) v = silu(v);
+                if (p.residual) v += p.residual[(int64_t)tok * p.ld_res + row];
+                *dst = v;
+              }
             }
           }
         }
@@ -278,20 +321,56 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_kquant_tcgen05_kernel(const _
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)(MT < 32 ? 32 : MT)) : "memory");
+  if (failed_s && warp == GM_PRODUCERS / 32 && lane == 0) {
+    // error path: give TMA copies still in flight a bounded chance to land before the CTA's shared memory is released
+    for (int s = 0; s < GM_STAGES && s < nit; ++s) gm_wait(&full_bar[s], 0u);
+  }
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(TMEM_COLS) : "memory");
 }
 
-template <int MT>
-cudaError_t launch_gemm(const GemmParams& p, cudaStream_t st) {
-  const size_t smem = 2 * (GM_ROWS * 128 + MT * 128) + 1024;
+// ---- host side: tensor map for the activations, launch --------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+  }
+  return fn;
+}
+
+// X viewed as a 2-D bf16 tensor [m rows, k columns] with a row pitch of ldx elements; boxes of [box_rows x 64]
+static int make_x_map(CUtensorMap* map, const GemmParams& p, int box_rows) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return -6;
+  const cuuint64_t gdim[2] = {(cuuint64_t)p.k, (cuuint64_t)p.m};
+  const cuuint64_t gstride[1] = {(cuuint64_t)p.ldx * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)GM_KSTEP, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)p.X, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -7;
+}
+
+template <int NT>
+int launch_gemm(const GemmParams& p, cudaStream_t st) {
+  const size_t smem = GM_STAGES * (GM_ROWS * 128 + NT * 128) + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kquant_tcgen05_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
+    cudaError_t e = cudaFuncSetAttribute(gemm_kquant_tcgen05_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((p.n + GM_ROWS - 1) / GM_ROWS, (p.m + MT - 1) / MT, p.splitk);
-  return launch(gemm_kquant_tcgen05_kernel<MT>, grid, dim3(GM_THREADS), smem, st, p);
+  alignas(64) CUtensorMap xmap;
+  const int rc = make_x_map(&xmap, p, NT);
+  if (rc) return rc;
+  dim3 grid((p.n + GM_ROWS - 1) / GM_ROWS, (p.m + NT - 1) / NT, p.splitk);
+  return (int)launch(gemm_kquant_tcgen05_kernel<NT>, grid, dim3(GM_THREADS), smem, st, p, xmap);
 }
 
 }  // namespace rlz
@@ -320,12 +399,12 @@ int rlz_gemm_kquant(const rlz::GemmParams* pp, void* stream) {
   if (p.splitk > p.k / GM_KSTEP) p.splitk = p.k / GM_KSTEP;
   p.atomic_out = p.splitk > 1 ? 1 : 0;
   if (p.atomic_out && p.act != ACT_NONE) return -5;
+  if ((p.ldx * 2) % 16) return -4;
   cudaStream_t st = (cudaStream_t)stream;
-  cudaError_t e;
-  if (p.m <= 32) e = launch_gemm<32>(p, st);
-  else if (p.m <= 64) e = launch_gemm<64>(p, st);
-  else e = launch_gemm<128>(p, st);
-  return (int)e;
+  if (p.m <= 32) return launch_gemm<32>(p, st);
+  if (p.m <= 64) return launch_gemm<64>(p, st);
+  if (p.m <= 128) return launch_gemm<128>(p, st);
+  return launch_gemm<256>(p, st);
 }
 
 }  // extern "C"

@@ -70,7 +70,11 @@ class BatchedForward:
             else:
                 G.gemm_launch(G.build_gemm_params(w, x_b, yv, T, bias=bias, residual=yv, ldy=y.stride(0), ld_res=y.stride(0)))
         else:
-            G.gemm_launch(G.build_gemm_params(w, x_b, yv, T, bias=bias, act=act, ldy=y.stride(0)))
+            sk = G.choose_splitk(w.n, w.k, T, self.sm_count) if act == ACT_NONE else 1
+            if sk > 1:                                      # few tokens: split K for occupancy, partial products add into zeros
+                y[:T, y_col:y_col + w.n].zero_()
+                self.launches_per_pass += 1
+            G.gemm_launch(G.build_gemm_params(w, x_b, yv, T, bias=bias, act=act, splitk=sk, ldy=y.stride(0)))
         self.launches_per_pass += 1
 
     def _row_parallel(self, w, x_b, T, bias):
@@ -115,7 +119,8 @@ class BatchedForward:
             ops.attn_decode_launch(ops.build_attn_decode_params(
                 self.qkv, self.attn[:, L.o_in_off:], self.k_cache[l], self.v_cache[l], self.positions, page_table, self.attn_partial,
                 self.attn_counters, m.heads, m.kv_heads, hd, self.splits, T, 0, cfg.rope_type, cfg.rope_theta, 0, qd, qd + kvd,
-                None, None, cfg.eps, ld_qkv=self.qkv.stride(0), ld_out=self.attn.stride(0), shared_table=shared_table, no_append=True))
+                None, None, cfg.eps, ld_qkv=self.qkv.stride(0), ld_out=self.attn.stride(0), shared_table=shared_table, no_append=True,
+                window=cfg.sliding_window or 0))
             ops.to_bf16(self.attn[:T], self.attn_b[:T])
             self.launches_per_pass += 4
             self._row_parallel(L.o, self.attn_b[:T, : L.o.k], T, L.o_b)

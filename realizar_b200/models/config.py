@@ -107,6 +107,8 @@ class ModelConfig:
     fused_qkv: bool = False              # checkpoint stores attn_qkv as one tensor
     rope_scaling_type: str = "none"
     rope_scaling_factor: float = 1.0
+    rope_original_context: int = 0       # pre-scaling context length (YaRN / dynamic NTK)
+    sliding_window: Optional[int] = None # attend to the last N positions only (Mistral style)
 
     def __post_init__(self):
         if self.head_dim == 0 and self.num_heads:
@@ -187,6 +189,8 @@ class ModelConfig:
             constraints=c, parallel_residual=(arch == "phi2" or arch == "gptj"),
             fused_qkv="blk.0.attn_qkv.weight" in g.tensors,
             rope_scaling_type=str(k("rope.scaling.type", "none")), rope_scaling_factor=float(k("rope.scaling.factor", 1.0)),
+            rope_original_context=int(k("rope.scaling.original_context_length", 0)),
+            sliding_window=(int(k("attention.sliding_window", 0)) or None),
         )
         cfg.validate()
         return cfg
@@ -217,6 +221,10 @@ class ModelConfig:
             rope_type=infer_rope_type(arch), eps=float(pick("rms_norm_eps", "layer_norm_eps", "layer_norm_epsilon", "eps", default=c.default_eps)),
             bos_token_id=pick("bos_token_id", default=_DEFAULT_BOS.get(arch)), eos_token_id=pick("eos_token_id", default=_DEFAULT_EOS.get(arch)),
             constraints=c, parallel_residual=(arch == "phi2"),
+            rope_scaling_type=str((pick("rope_scaling") or {}).get("rope_type", (pick("rope_scaling") or {}).get("type", "none"))),
+            rope_scaling_factor=float((pick("rope_scaling") or {}).get("factor", 1.0)),
+            rope_original_context=int((pick("rope_scaling") or {}).get("original_max_position_embeddings", 0)),
+            sliding_window=(int(pick("sliding_window", default=0) or 0) or None),
         )
         cfg.validate()
         return cfg

@@ -114,6 +114,19 @@ class LayerWeights:
     down_in_off: int = 0       # same for the MLP activation inside the down-proj input buffer
 
 
+def make_rope_table(cfg, device, max_positions: Optional[int] = None) -> torch.Tensor:
+    """(cos, sin) per position and rotary pair, with the checkpoint's context scaling
+    (linear / NTK / YaRN; src/layers ``ScaledRoPE`` in the reference) folded in."""
+    from .layers import RoPE, RopeScaling, RopeScalingType
+    n = max_positions or min(cfg.context_length, 1 << 17)
+    kind = {"linear": RopeScalingType.LINEAR, "ntk": RopeScalingType.NTK, "yarn": RopeScalingType.YARN}.get(str(cfg.rope_scaling_type).lower())
+    if kind is None or cfg.rope_scaling_factor == 1.0:
+        return ops.make_rope_table(n, cfg.rope_dim, cfg.rope_theta, device)
+    inv, mscale = RoPE(cfg.rope_dim, cfg.rope_theta, scaling=RopeScaling(kind, cfg.rope_scaling_factor, cfg.rope_original_context or cfg.context_length)).inv_freq(n)
+    ang = torch.arange(n, dtype=torch.float64)[:, None] * inv.double()[None, :]
+    return torch.stack([ang.cos() * mscale, ang.sin() * mscale], -1).to(torch.float32).contiguous().to(device)
+
+
 class GpuModel:
     """Weights of one (shard of a) decoder on one GPU."""
 
@@ -141,6 +154,9 @@ class GpuModel:
         self.embed_table = emb.torch_bytes(dev).contiguous()
         pe = weights.get("token_pos_embd.weight")
         self.pos_table = _f32(pe, dev)
+        self.rope_table = None
+        if cfg.uses_rope:
+            self.rope_table = make_rope_table(cfg, dev)
 
         out_w = weights.output_weight()
         self.vocab = cfg.vocab_size
@@ -290,16 +306,22 @@ class DecodePlan:
 def emit_head(plan: "DecodePlan", model: GpuModel, buf: StepBuffers, r0: int, batch: int, comm, greedy_only: bool, sm_count: int) -> None:
     """Final norm + lm_head + token selection for rows ``r0 .. r0+batch-1`` of the step buffers."""
     cfg = model.cfg
-    H, V = cfg.hidden_dim, cfg.vocab_size
+    H = cfg.hidden_dim
     norm_t = NORM_LAYER if cfg.uses_layernorm else NORM_RMS
-    tp = model.tp_size > 1
-    fused = tp and getattr(comm, "fused", False)
-    rows = slice(r0, r0 + batch)
     for c0 in range(0, batch, 4):
         cb = min(4, batch - c0)
         xin = VecIn(buf.x[r0 + c0:], H, ld=buf.x.stride(0), norm=norm_t, norm_w=model.out_norm_w, norm_b=model.out_norm_b, eps=cfg.eps)
         plan.add_gemv_auto([xin], [MatOut([(model.lm_head, 0)], bias=model.lm_head_b)], buf.logits[r0 + c0:], cb,
                            buf.logits.stride(0), target_ctas=sm_count)
+    emit_select(plan, model, buf, r0, batch, comm, greedy_only)
+
+
+def emit_select(plan: "DecodePlan", model: GpuModel, buf: StepBuffers, r0: int, batch: int, comm, greedy_only: bool) -> None:
+    """Token selection from ``buf.logits`` rows ``r0 .. r0+batch-1`` into ``buf.sampled``."""
+    V = model.cfg.vocab_size
+    tp = model.tp_size > 1
+    fused = tp and getattr(comm, "fused", False)
+    rows = slice(r0, r0 + batch)
     if tp and greedy_only:
         def pick():
             ops.argmax(buf.logits[rows], out=buf.local_idx[rows], out_val=buf.local_val[rows], index_offset=model.vocab_start, vocab=model.vocab_local)
@@ -391,7 +413,8 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
         plan.add_attn(ops.build_attn_decode_params(
             buf.y1, buf.attn_out[:, L.o_in_off:], kc, vc, buf.positions, buf.page_table, buf.attn_partial, buf.attn_counters,
             model.heads, model.kv_heads, hd, splits, batch, cfg.rope_dim if cfg.uses_rope else 0, cfg.rope_type, cfg.rope_theta,
-            0, qd, qd + kvd, L.q_norm_w, L.k_norm_w, cfg.eps, ld_qkv=ld1, ld_out=buf.attn_out.stride(0)))
+            0, qd, qd + kvd, L.q_norm_w, L.k_norm_w, cfg.eps, ld_qkv=ld1, ld_out=buf.attn_out.stride(0),
+            window=cfg.sliding_window or 0, rope_table=model.rope_table if cfg.uses_rope else None))
         if cfg.parallel_residual:
             row_parallel(lambda c0: [VecIn(buf.attn_out[c0:], L.o.k, ld=buf.attn_out.stride(0)), VecIn(buf.y1[c0:, model.act_col0:], L.down.k, ld=ld1)],
                          lambda res: MatOut([(L.o, 0), (L.down, 1)], bias=L.o_b, bias2=L.down_b, combine=COMBINE_ADD, residual=res))

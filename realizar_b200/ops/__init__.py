@@ -207,7 +207,7 @@ def attn_decode_scratch(batch: int, n_heads: int, splits: int, head_dim: int, de
 
 def build_attn_decode_params(qkv, out, k_cache, v_cache, positions, page_table, partial, counters, n_heads, n_kv_heads, head_dim,
                              splits, batch, rope_dim, rope_type, rope_theta, q_off, k_off, v_off, q_norm_w=None, k_norm_w=None,
-                             eps=1e-6, ld_qkv=None, ld_out=None, shared_table=False, no_append=False) -> S.AttnDecodeParams:
+                             eps=1e-6, ld_qkv=None, ld_out=None, shared_table=False, no_append=False, window=0, rope_table=None) -> S.AttnDecodeParams:
     p = S.AttnDecodeParams()
     p.qkv, p.out, p.k_cache, p.v_cache = qkv.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr()
     p.positions, p.page_table = positions.data_ptr(), page_table.data_ptr()
@@ -221,7 +221,19 @@ def build_attn_decode_params(qkv, out, k_cache, v_cache, positions, page_table, 
     p.rope_theta, p.eps, p.scale = rope_theta, eps, head_dim ** -0.5
     p.pt_stride = 0 if shared_table else (page_table.stride(0) if page_table.dim() > 1 else page_table.shape[-1])
     p.no_append = 1 if no_append else 0
+    p.window = int(window or 0)
+    if rope_table is not None:
+        if rope_table.dtype != torch.float32 or rope_table.dim() != 3 or rope_table.shape[1] != rope_dim // 2 or rope_table.shape[2] != 2 or not rope_table.is_contiguous():
+            raise ValueError("rope_table must be a contiguous float32 [positions, rope_dim / 2, 2] (cos, sin) tensor")
+        p.rope_table, p.rope_table_len = rope_table.data_ptr(), rope_table.shape[0]
     return p
+
+
+def make_rope_table(max_positions: int, rope_dim: int, theta: float, device) -> torch.Tensor:
+    """(cos, sin) of ``pos * theta^(-2i/rope_dim)`` for every position and rotary pair, computed in float64."""
+    i = torch.arange(rope_dim // 2, dtype=torch.float64)
+    ang = torch.arange(max_positions, dtype=torch.float64)[:, None] * torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * i / rope_dim)[None, :]
+    return torch.stack([ang.cos(), ang.sin()], -1).to(torch.float32).contiguous().to(device)
 
 
 def attn_decode_launch(p: S.AttnDecodeParams) -> None:
@@ -289,6 +301,10 @@ def swiglu_bf16(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor, act=ACT
 def kv_append(k, v, k_cache, v_cache, positions, page_rows, n_kv_heads, d, page=16) -> None:
     check(lib().rlz_kv_append(k.data_ptr(), v.data_ptr(), k.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(),
                               page_rows.data_ptr(), k.shape[0], n_kv_heads, d, page, stream_ptr()), "kv_append")
+
+
+def page_rows(page_table: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n: int, page: int) -> None:
+    check(lib().rlz_page_rows(page_table.data_ptr(), page_table.stride(0), positions.data_ptr(), out.data_ptr(), n, page, stream_ptr()), "page_rows")
 
 
 def advance_(tokens: torch.Tensor, sampled: torch.Tensor, positions: torch.Tensor) -> None:

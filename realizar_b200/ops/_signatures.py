@@ -53,7 +53,8 @@ class AttnDecodeParams(Structure):
                 ("counters", c_void_p), ("ld_qkv", c_int64), ("ld_out", c_int64), ("n_heads", c_int32), ("n_kv_heads", c_int32),
                 ("head_dim", c_int32), ("max_pages", c_int32), ("rope_dim", c_int32), ("rope_type", c_int32), ("splits", c_int32),
                 ("batch", c_int32), ("q_off", c_int32), ("k_off", c_int32), ("v_off", c_int32), ("pt_stride", c_int32),
-                ("rope_theta", c_float), ("eps", c_float), ("scale", c_float), ("no_append", c_int32)]
+                ("rope_theta", c_float), ("eps", c_float), ("scale", c_float), ("no_append", c_int32), ("window", c_int32),
+                ("rope_table_len", c_int32), ("rope_table", c_void_p)]
 
 
 class SampleParams(Structure):
@@ -101,6 +102,7 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_norm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_float, c_void_p]
     lib.rlz_swiglu_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_longlong, c_longlong, c_int, c_void_p]
     lib.rlz_advance.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+    lib.rlz_page_rows.argtypes = [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_void_p]
     lib.rlz_argmax.argtypes = [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
     lib.rlz_sample.argtypes = [POINTER(SampleParams), c_void_p]
     lib.rlz_penalties.argtypes = [c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]

@@ -20,13 +20,20 @@ def gemm_eligible(w: DeviceWeight) -> bool:
     return w.k % 256 == 0 if w.qtype in GEMM_TYPES[:3] else w.k % 64 == 0
 
 
+def token_tile(m: int) -> int:
+    """Tokens per CTA (the MMA N dimension) that the kernel picks for ``m`` tokens."""
+    return 32 if m <= 32 else 64 if m <= 64 else 128 if m <= 128 else 256
+
+
 def choose_splitk(n: int, k: int, m: int, sm_count: int = 148) -> int:
-    """Split K across CTAs when the (n, m) tile grid alone would leave most SMs idle."""
-    mt = 32 if m <= 32 else 64 if m <= 64 else 128
+    """Split K across CTAs when the (n, m) tile grid alone would leave most SMs idle; every split
+    keeps at least eight 64-column steps so that the pipeline fill is amortised."""
+    mt = token_tile(m)
     tiles = -(-n // 128) * -(-m // mt)
-    if tiles >= sm_count:
+    slots = sm_count * (2 if mt <= 64 else 1)
+    if tiles >= slots:
         return 1
-    return max(1, min(k // 256, sm_count // tiles, 16))
+    return max(1, min(k // 512, slots // tiles, 16))
 
 
 def build_gemm_params(w: DeviceWeight, x: torch.Tensor, y: torch.Tensor, m: int, bias=None, residual=None, act=ACT_NONE,

@@ -21,7 +21,8 @@ import torch
 
 from .. import ops
 from ..models.batched import BatchedForward, gemm_capable
-from ..models.decoder import DecodePlan, GpuModel, StepBuffers, build_decode_plan, emit_head
+from ..models.decoder import DecodePlan, GpuModel, StepBuffers, build_decode_plan, emit_head, emit_select
+from ..ops import gemm as G
 from ..models.weights import ModelWeights
 from .paged_kv import PagedKvCache
 
@@ -41,6 +42,9 @@ class EngineConfig:
     greedy_only: bool = False              # compile plans with argmax instead of the sampling kernel
     prefill_chunk: int = 512               # tokens per tensor-core prefill pass
     batched_prefill_min: int = 8           # shorter prompts go through the decode kernels token by token
+    gemm_decode_min_batch: int = 16        # decode batches at least this large run on the tensor-core GEMM path
+    prefix_cache: bool = False             # share full KV pages between prompts with a common prefix
+    parity_gate: bool = False              # at load: GPU vs CPU logits on the BOS token must agree (cosine >= 0.99)
     batch_buckets: Sequence[int] = ()      # graph buckets; default powers of two up to max_batch
     seed: int = 0
 
@@ -62,6 +66,7 @@ class Slot:
     active: bool = False
     position: int = -1          # position of the token fed in the next step
     n_pages: int = 0
+    history: Optional[List[int]] = None    # prompt tokens seen so far (prefix cache only)
 
 
 class DecodeEngine:
@@ -121,12 +126,20 @@ class DecodeEngine:
         self.gemm_ok = gemm_capable(self.model)
         self._batched: Optional[BatchedForward] = None
         self._head_plans: Dict[int, DecodePlan] = {}
+        self.prefix_hits = self.prefix_tokens_reused = 0
+        if c.parity_gate:
+            cos = self.parity_check(weights)
+            if not cos >= 0.99:
+                raise RuntimeError(f"parity gate failed: GPU vs CPU logits cosine {cos:.4f} < 0.99")
 
     # -- configuration helpers --------------------------------------------------------------
     def _choose_splits(self, batch: int) -> int:
         ctas_per_split = self.model.kv_heads * max(1, batch)
         want = max(1, (2 * self.sm_count) // max(1, ctas_per_split))
-        return int(min(32, want))
+        s = 1
+        while s * 2 <= min(8, want):          # power of two up to the cluster size: splits merge through DSMEM
+            s *= 2
+        return s
 
     def bucket_for(self, batch: int) -> int:
         for b in self.buckets:
@@ -136,13 +149,20 @@ class DecodeEngine:
 
     # -- plans and graphs -------------------------------------------------------------------
     def plan(self, bucket: int) -> DecodePlan:
+        if bucket not in self._plans and self._use_batched_step(bucket):
+            self._plans[bucket] = self._batched_step_plan(bucket)
         if bucket not in self._plans:
             self._plans[bucket] = build_decode_plan(self.model, self.buf, self.kv[0], self.kv[1], bucket, self.splits, self.comm,
                                                     self.cfg.greedy_only, self.sm_count)
         return self._plans[bucket]
 
     def kernels_per_step(self, bucket: int) -> int:
-        return self.plan(bucket).kernel_launches
+        p = self.plan(bucket)
+        if self._use_batched_step(bucket):
+            if self.batched().launches_per_pass == 0:
+                p.run()
+            return p.kernel_launches + self.batched().launches_per_pass + 5
+        return p.kernel_launches
 
     def _capture(self, bucket: int) -> Optional[torch.cuda.CUDAGraph]:
         plan = self.plan(bucket)
@@ -168,6 +188,32 @@ class DecodeEngine:
                     plan.run()
                 return g
             raise
+
+    def _batched_step_plan(self, bucket: int) -> DecodePlan:
+        """Decode step for a large batch on the tensor-core path: every projection is one GEMM over
+        all ``bucket`` rows (weights read once per step, not once per 4 rows), attention runs per row
+        over its own page-table row, and the lm_head is a GEMM as well."""
+        bf = self.batched()
+        m, b, cfg = self.model, self.buf, self.mcfg
+        norm_t = ops.NORM_LAYER if cfg.uses_layernorm else ops.NORM_RMS
+        plan = DecodePlan(self.sm_count)
+        B = bucket
+
+        def body():
+            bf.tokens[:B].copy_(b.tokens[:B])
+            bf.positions[:B].copy_(b.positions[:B])
+            ops.page_rows(b.page_table, b.positions, bf.page_rows, B, PAGE)
+            x = bf.forward(B, b.page_table, shared_table=False)
+            ops.norm_bf16(x, bf.xb[:B], m.out_norm_w, m.out_norm_b, norm_t, cfg.eps)
+            G.gemm_launch(self._lm_head_gemm[B])
+        self._lm_head_gemm = getattr(self, "_lm_head_gemm", {})
+        self._lm_head_gemm[B] = G.build_gemm_params(m.lm_head, bf.xb, b.logits, B, bias=m.lm_head_b, ldy=b.logits.stride(0))
+        plan.add(body, launches=0)
+        emit_select(plan, m, b, 0, B, self.comm, self.cfg.greedy_only)
+        return plan
+
+    def _use_batched_step(self, bucket: int) -> bool:
+        return self.gemm_ok and bucket >= self.cfg.gemm_decode_min_batch and bucket <= self.cfg.prefill_chunk
 
     def run_step(self, batch: int) -> None:
         """Issue one decode step for slots ``0..batch-1`` on the current stream."""
@@ -200,6 +246,7 @@ class DecodeEngine:
         self._next_seq += 1
         self.pages.add_sequence(seq_id)
         s.seq_id, s.active, s.position, s.n_pages = seq_id, True, 0, 0
+        s.history = [] if self.cfg.prefix_cache else None
         self._ensure_pages(slot, reserve_tokens)
         return seq_id
 
@@ -273,13 +320,54 @@ class DecodeEngine:
         pass in chunks of ``prefill_chunk`` tokens when every projection supports it; otherwise the
         prompt is fed through the decode kernels token by token (as the reference's ``run_prefill``
         loop, src/gguf/cuda/generate_2.rs:261-273)."""
+        s = self.slots[slot]
+        if s.history is not None:
+            tokens = list(tokens)
+            if s.position == 0 and len(tokens) > PAGE:
+                # swap the slot's fresh pages for cached ones that already hold this prompt's leading pages
+                reserved = len(self.pages.seqs[s.seq_id].pages) * PAGE
+                self.pages.rollback(s.seq_id, 0)
+                covered = self.pages.match_prefix(s.seq_id, tokens)
+                s.n_pages = -1
+                self._ensure_pages(slot, max(reserved, len(tokens)))
+                if covered:
+                    self.prefix_hits += 1
+                    self.prefix_tokens_reused += covered
+                    s.position = covered
+                    s.history = tokens[:covered]
+                    tokens = tokens[covered:]
+            s.history.extend(int(t) for t in tokens)
         n = len(tokens)
         if n >= self.cfg.batched_prefill_min and self.gemm_ok:
-            return self._prefill_batched(slot, tokens)
-        out = 0
-        for t in tokens:
-            out = int(self.feed({slot: int(t)})[slot])
+            out = self._prefill_batched(slot, tokens)
+        else:
+            out = 0
+            for t in tokens:
+                out = int(self.feed({slot: int(t)})[slot])
+        if s.history is not None:
+            self.pages.publish_prefix(s.seq_id, s.history)
         return out
+
+    def parity_check(self, weights: ModelWeights, token: Optional[int] = None) -> float:
+        """Cosine similarity of the logits of one token (BOS by default) between this engine and the
+        C++ CPU engine on the same weights (the reference gates its CUDA model the same way,
+        src/gguf/cuda/mod.rs parity gate)."""
+        from ..models.cpu_model import CpuModel
+        tok = token if token is not None else (self.mcfg.bos_token_id if self.mcfg.bos_token_id is not None else 1)
+        cpu = CpuModel(weights, 16).forward(int(tok), 0)
+        slot = self.free_slots()[0]
+        self.open_slot(slot, 16)
+        try:
+            self.feed({slot: int(tok)})
+            gpu = self.buf.logits[slot, : self.mcfg.vocab_size].float().cpu().numpy()
+        finally:
+            self.close_slot(slot)
+        import numpy as np
+        a, b = np.asarray(cpu, np.float64), np.asarray(gpu, np.float64)
+        if self.model.tp_size > 1:                    # vocabulary-sharded lm_head: compare this rank's slice
+            b = b[: self.model.vocab_local]
+            a = a[self.model.vocab_start: self.model.vocab_start + b.shape[0]]
+        return float(a @ b / max(1e-30, np.linalg.norm(a) * np.linalg.norm(b)))
 
     def _prefill_batched(self, slot: int, tokens: Sequence[int]) -> int:
         s = self.slots[slot]

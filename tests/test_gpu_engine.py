@@ -130,3 +130,83 @@ def test_batched_prefill_matches_serial_and_oracle(cuda_device, which):
     eng.prefill(0, toks)
     b = int(eng.feed({0: nxt_b})[0])
     assert nxt_b != nxt_s or a == b
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_tensor_core_decode_batch_matches_gemv_path(cuda_device, graphs):
+    """A decode step of 16 sequences on the GEMM path gives the logits of the GEMV path."""
+    from realizar_b200.models.weights import synthetic_weights
+    from realizar_b200.runtime.engine import DecodeEngine, EngineConfig
+    cfg = _kq_llama()
+    w = synthetic_weights(cfg, seed=3, std=0.05)
+    rng = np.random.default_rng(1)
+    prompts = [[int(t) for t in rng.integers(0, cfg.vocab_size, 3 + (i % 5))] for i in range(16)]
+
+    def run(min_batch):
+        eng = DecodeEngine(w, EngineConfig(max_batch=16, max_seq_len=64, greedy_only=True, cuda_graphs=graphs, gemm_decode_min_batch=min_batch))
+        for s, p in enumerate(prompts):
+            eng.open_slot(s, 32)
+            for t in p[:-1]:
+                eng.feed({s: t})
+        outs = []
+        last = {s: p[-1] for s, p in enumerate(prompts) if s != 5}          # slot 5 idles
+        for _ in range(3):
+            got = eng.feed(last)
+            outs.append(eng.buf.logits[:16, :cfg.vocab_size].float().cpu().numpy().copy())
+            last = {s: int(got[s]) for s in last}
+        return eng, outs
+    e_ref, ref = run(10 ** 9)
+    e_tc, tc = run(16)
+    assert e_tc._use_batched_step(16) and not e_ref._use_batched_step(16) and e_tc.kernels_per_step(16) > 0
+    for a, b in zip(ref, tc):
+        for s in range(16):
+            if s != 5:
+                assert _cos(a[s], b[s]) > 0.995, s
+
+
+def test_forward_tokens_rollback_and_speculative(cuda_device):
+    from realizar_b200.models.weights import synthetic_weights
+    from realizar_b200.runtime.engine import DecodeEngine, EngineConfig, SamplingParams
+    from realizar_b200.runtime.speculative import EngineSpecModel, LayerSkipDraft, SpeculativeConfig, SpeculativeDecoder
+    cfg = _kq_llama()
+    w = synthetic_weights(cfg, seed=5, std=0.05)
+    prompt = [int(t) for t in np.random.default_rng(2).integers(0, cfg.vocab_size, 9)]
+    eng = DecodeEngine(w, EngineConfig(max_batch=4, max_seq_len=128, greedy_only=True))
+    ref = eng.generate(prompt, SamplingParams(max_tokens=20))
+    # one pass over several tokens gives the same next-token choices as token-by-token decoding
+    eng.open_slot(0, 64)
+    nxt = eng.forward_tokens(0, prompt + ref[:6])
+    assert nxt[len(prompt) - 1:] == ref[:7] and eng.slots[0].position == len(prompt) + 6
+    # rollback then replay reproduces the continuation
+    eng.rollback(0, len(prompt))
+    assert eng.forward_tokens(0, ref[:3])[-1] == ref[3]
+    eng.close_slot(0)
+    # draft = the target itself: every draft accepted, output identical to plain greedy decoding
+    t, d = EngineSpecModel(eng, 0, 96), EngineSpecModel(eng, 1, 96)
+    dec = SpeculativeDecoder(t, d, SpeculativeConfig(4, 20))
+    assert dec.generate(prompt) == ref and dec.stats.acceptance_rate == 1.0 and dec.stats.rounds <= 5
+    t.close(); d.close()
+    # self-speculative (layer-skipping draft over the shared cache): whatever is accepted, the output is the target's
+    t = EngineSpecModel(eng, 0, 96)
+    dec = SpeculativeDecoder(t, LayerSkipDraft(t), SpeculativeConfig(3, 20), shared_cache=True)
+    assert dec.generate(prompt) == ref
+    t.close()
+
+
+def test_prefix_cache_reuses_pages_and_parity_gate(cuda_device):
+    from realizar_b200.models.weights import synthetic_weights
+    from realizar_b200.runtime.engine import DecodeEngine, EngineConfig, SamplingParams
+    cfg = _kq_llama()
+    w = synthetic_weights(cfg, seed=9, std=0.05)
+    rng = np.random.default_rng(4)
+    shared = [int(t) for t in rng.integers(0, cfg.vocab_size, 40)]
+    p1, p2 = shared + [5, 6, 7], shared + [9, 8]
+    plain = DecodeEngine(w, EngineConfig(max_batch=2, max_seq_len=128, greedy_only=True, parity_gate=True))
+    assert plain.parity_check(w) > 0.99
+    want1, want2 = plain.generate(p1, SamplingParams(max_tokens=6)), plain.generate(p2, SamplingParams(max_tokens=6))
+    eng = DecodeEngine(w, EngineConfig(max_batch=2, max_seq_len=128, greedy_only=True, prefix_cache=True))
+    assert eng.generate(p1, SamplingParams(max_tokens=6)) == want1 and eng.prefix_hits == 0
+    assert eng.generate(p2, SamplingParams(max_tokens=6)) == want2
+    assert eng.prefix_hits == 1 and eng.prefix_tokens_reused == 32          # two full 16-token pages of the shared prefix
+    assert eng.generate(p1, SamplingParams(max_tokens=6)) == want1 and eng.prefix_hits == 2
+    assert eng.pages.stats().sequences == 0
