@@ -53,6 +53,11 @@ def build_parser() -> argparse.ArgumentParser:
     for name in ("bench-convoy", "bench-saturation"):
         q = sub.add_parser(name); q.add_argument("--model", default=None); q.add_argument("--output", "-o", default=None)
         q.add_argument("--concurrency", type=int, default=16); q.add_argument("--requests", type=int, default=64)
+    bs = sub.add_parser("bench-serving", help="open-loop load against the OpenAI API (Poisson arrivals, SSE streaming)")
+    bs.add_argument("--url", default=None, help="running server; default: load the model in-process"); bs.add_argument("--model", default=None)
+    bs.add_argument("--requests", type=int, default=200); bs.add_argument("--rate", type=float, default=20.0); bs.add_argument("--concurrency", type=int, default=256)
+    bs.add_argument("--prompt-tokens", type=int, default=64); bs.add_argument("--max-tokens", type=int, default=32); bs.add_argument("--max-batch", type=int, default=64)
+    bs.add_argument("--output", "-o", default=None)
     bc = sub.add_parser("bench-compare"); bc.add_argument("file1"); bc.add_argument("file2"); bc.add_argument("--threshold", type=float, default=5.0)
     br = sub.add_parser("bench-regression"); br.add_argument("baseline"); br.add_argument("current"); br.add_argument("--strict", action="store_true")
     v = sub.add_parser("viz"); v.add_argument("file", nargs="?"); v.add_argument("--samples", type=int, default=100)
@@ -286,6 +291,24 @@ def cmd_bench_serving(a) -> int:
     return 0 if r.get("ok", True) else 1
 
 
+def cmd_bench_load(a) -> int:
+    from .utils.loadgen import LoadConfig, run_load
+    cfg = LoadConfig(a.requests, a.rate, a.concurrency, a.prompt_tokens, a.max_tokens)
+    if a.url:
+        r = run_load(cfg, url=a.url)
+    else:
+        from .serving.api import create_app
+        st = build_app_state(a.model, None, a.max_batch, 4096, warmup=a.model is not None)
+        try:
+            r = run_load(cfg, app=create_app(st))
+        finally:
+            st.serving.stop()
+    print(json.dumps(r, indent=1))
+    if a.output:
+        Path(a.output).write_text(json.dumps(r))
+    return 0 if r["errors"] == 0 else 1
+
+
 def cmd_bench_compare(a, strict: bool = False) -> int:
     from .utils.benchlib import compare_results, has_regression, load_results
     f1, f2 = (a.file1, a.file2) if hasattr(a, "file1") else (a.baseline, a.current)
@@ -355,7 +378,7 @@ def cmd_info(a) -> int:
 def main(argv: Optional[List[str]] = None) -> int:
     a = build_parser().parse_args(argv)
     table = {"run": cmd_run, "chat": cmd_chat, "serve": cmd_serve, "list": cmd_list, "pull": cmd_registry_offline, "push": cmd_registry_offline,
-             "bench": cmd_bench, "bench-convoy": cmd_bench_serving, "bench-saturation": cmd_bench_serving, "bench-compare": cmd_bench_compare,
+             "bench": cmd_bench, "bench-serving": cmd_bench_load, "bench-convoy": cmd_bench_serving, "bench-saturation": cmd_bench_serving, "bench-compare": cmd_bench_compare,
              "bench-regression": lambda x: cmd_bench_compare(x, strict=True), "viz": cmd_viz, "convert": cmd_convert, "monitor": cmd_monitor, "info": cmd_info}
     try:
         return table[a.cmd](a)

@@ -22,9 +22,8 @@
 // dequant-to-f16/f32 + cuBLAS HGEMM/SGEMM and cuBLASLt FP8 call sites
 // (src/cuda/executor/layers/cublas_prefill/gemm.rs:70-1100).
 #include "common.cuh"
+#include "tcgen05_common.cuh"
 #include "../gemv_blocks.h"
-#include <cuda.h>
-#include <cuda_bf16.h>
 
 namespace rlz {
 
@@ -35,7 +34,6 @@ constexpr int GM_THREADS = GM_PRODUCERS + 64;   // + TMA warp + MMA warp
 constexpr int GM_STAGES = 4;
 constexpr int GM_ROWS = 128;          // weight rows per CTA = MMA M
 constexpr int GM_KSTEP = 64;          // K elements per stage (one 128-byte swizzle row of bf16)
-constexpr uint32_t GM_WAIT_LIMIT = 1u << 24;
 
 struct GemmParams {
   const uint8_t* W; int64_t w_stride; int32_t qtype; int32_t n; int32_t k; int32_t m;
@@ -45,119 +43,97 @@ struct GemmParams {
   int32_t act; int32_t splitk; int32_t atomic_out; int32_t _pad;
 };
 
-__device__ __forceinline__ uint32_t gm_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// ---- producers: raw block bytes -> registers (issued one K step ahead), registers -> bf16 pairs -------------
+// The integer code q of a weight is dropped into the mantissa of a bf16 power of two (magic + q is exact), the
+// magic is subtracted again (exact) and one bf16x2 FMA applies scale and offset to two weights at a time:
+//   PRMT (two code bytes -> two 16-bit lanes), LOP3 (mask | magic), HADD2, HFMA2  per pair.
+// The scale (and the Q4_K / Q5_K minimum) is rounded to bf16 first; the operand fed to the tensor core is bf16 anyway.
+struct RawW { uint4 r[5]; };
 
-__device__ __forceinline__ uint64_t make_sdesc_k_sw128(uint32_t smem_addr) {
-  // K-major, SWIZZLE_128B: rows of 128 bytes, 8-row groups 1024 bytes apart
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);            // start address
-  d |= (uint64_t)1 << 16;                                  // leading byte offset (unused for swizzled K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;                        // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;                                  // descriptor version (Blackwell)
-  d |= (uint64_t)2 << 61;                                  // SWIZZLE_128B
-  return d;
-}
-
-__device__ __forceinline__ uint32_t make_idesc_bf16(int mma_m, int mma_n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(mma_n >> 3) << 17) | ((uint32_t)(mma_m >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(gm_smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool gm_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-               : "=r"(ok) : "r"(gm_smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool gm_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < GM_WAIT_LIMIT; ++i) if (gm_try_wait(bar, parity)) return true;
-  return false;
+template <int QT>
+__device__ __forceinline__ void load_raw(const uint8_t* row, int k0, int half, RawW& w) {
+  const int sb = k0 >> 8, g = (k0 >> 6) & 3;
+  if (QT == QT_Q4_K || QT == QT_Q5_K) {
+    const uint8_t* blk = row + (int64_t)sb * (QT == QT_Q5_K ? 176 : 144);
+    w.r[0] = __ldg((const uint4*)blk);
+    const uint8_t* qs = blk + (QT == QT_Q5_K ? 48 : 16) + 32 * g;
+    w.r[1] = __ldg((const uint4*)qs); w.r[2] = __ldg((const uint4*)(qs + 16));
+    if (QT == QT_Q5_K) { w.r[3] = __ldg((const uint4*)(blk + 16)); w.r[4] = __ldg((const uint4*)(blk + 32)); }
+  } else if (QT == QT_Q6_K) {
+    const uint8_t* blk = row + (int64_t)sb * Q6K_DEV_STRIDE;
+    const int n = g >> 1, upper = g & 1;
+    const uint8_t* ql = blk + 64 * n + 32 * half;
+    const uint8_t* qh = blk + 128 + 32 * n;
+    w.r[0] = __ldg((const uint4*)ql); w.r[1] = __ldg((const uint4*)(ql + 16));
+    w.r[2] = __ldg((const uint4*)qh); w.r[3] = __ldg((const uint4*)(qh + 16));
+    w.r[4].x = __ldg((const uint32_t*)(blk + 192 + 8 * n + 4 * upper));     // the four int8 scales of this 64-column group
+    w.r[4].y = __ldg((const uint32_t*)(blk + 208));                        // d (f16) in the low half
+  } else {                                                                  // BF16 / F16: 32 elements = 64 bytes
+    const uint4* src = (const uint4*)(row + (int64_t)(k0 + 32 * half) * 2);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w.r[i] = __ldg(src + i);
+  }
 }
 
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+__device__ __forceinline__ uint32_t bf2_splat(float x) { const __nv_bfloat162 v = __float2bfloat162_rn(x); return *(const uint32_t*)&v; }
+__device__ __forceinline__ float bf_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+// (codes | magic) - magic, then * scale + offset, two weights per call; all operands packed bf16x2
+__device__ __forceinline__ uint32_t bf2_affine(uint32_t codes_magic, uint32_t magic, uint32_t scale, uint32_t offset) {
+  const __nv_bfloat162 q = __hsub2(*(const __nv_bfloat162*)&codes_magic, *(const __nv_bfloat162*)&magic);
+  const __nv_bfloat162 v = __hfma2(q, *(const __nv_bfloat162*)&scale, *(const __nv_bfloat162*)&offset);
   return *(const uint32_t*)&v;
 }
 
-// Move the bit field that starts at bit `from` of w so that it starts at bit `to` (both compile-time after unrolling).
-__device__ __forceinline__ uint32_t place_bits(uint32_t w, int from, int to) { return to >= from ? (w << (to - from)) : (w >> (from - to)); }
-
-// 32 weights of one row: columns [k0 + 32*half, k0 + 32*half + 32) with k0 a multiple of 64, as 16 packed bf16 pairs.
-// The integer code q of a weight is dropped into the top mantissa bits of 1.0f, giving 1 + q / 2^bits exactly, so the
-// whole affine dequantisation is one FMA per weight:  scale * q - off  =  (scale * 2^bits) * (1 + q / 2^bits) - (scale * 2^bits + off).
-__device__ __forceinline__ void dequant_row32(const uint8_t* row, int qtype, int k0, int half, uint32_t* out) {
-  const int sb = k0 >> 8, g = (k0 >> 6) & 3;
-  if (qtype == QT_Q4_K || qtype == QT_Q5_K) {
-    const bool q5 = qtype == QT_Q5_K;
-    const uint8_t* blk = row + (int64_t)sb * (q5 ? 176 : 144);
-    const uint4 hdr = __ldg((const uint4*)blk);
+template <int QT>
+__device__ __forceinline__ void dequant_raw32(const RawW& w, int k0, int half, uint32_t* out) {
+  const int g = (k0 >> 6) & 3;
+  if (QT == QT_Q4_K || QT == QT_Q5_K) {
+    constexpr bool q5 = QT == QT_Q5_K;
+    const uint4 hdr = w.r[0];
     const float d = h2f_alu(hdr.x & 0xFFFFu), dmin = h2f_alu(hdr.x >> 16);
     const K4Scales ks = k4_unpack(hdr.y, hdr.z, hdr.w);
-    const float dd = d * (float)k4_pick(ks.sc_lo, ks.sc_hi, 2 * g + half) * (q5 ? 32.f : 16.f);
-    const float cc = -(dd + dmin * (float)k4_pick(ks.m_lo, ks.m_hi, 2 * g + half));
-    const uint8_t* qs = blk + (q5 ? 48 : 16) + 32 * g;
-    const uint4 q0 = __ldg((const uint4*)qs), q1 = __ldg((const uint4*)(qs + 16));
-    const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-    uint32_t hw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (q5) {
-      const uint4 h0 = __ldg((const uint4*)(blk + 16)), h1 = __ldg((const uint4*)(blk + 32));
-      hw[0] = h0.x; hw[1] = h0.y; hw[2] = h0.z; hw[3] = h0.w; hw[4] = h1.x; hw[5] = h1.y; hw[6] = h1.z; hw[7] = h1.w;
-    }
-    const int nsh = 4 * half, hsh = 2 * g + half;
+    const uint32_t sc2 = bf2_splat(d * (float)k4_pick(ks.sc_lo, ks.sc_hi, 2 * g + half));
+    const uint32_t mn2 = bf2_splat(-dmin * (float)k4_pick(ks.m_lo, ks.m_hi, 2 * g + half));
+    // codes sit at bits 3..6 (Q4_K: magic 16, ulp 1/8) or 2..6 (Q5_K: magic 32, ulp 1/4) of their byte
+    constexpr uint32_t MAGIC = q5 ? 0x42004200u : 0x41804180u;
+    const uint32_t qw[8] = {w.r[1].x, w.r[1].y, w.r[1].z, w.r[1].w, w.r[2].x, w.r[2].y, w.r[2].z, w.r[2].w};
+    const uint32_t hw[8] = {w.r[3].x, w.r[3].y, w.r[3].z, w.r[3].w, w.r[4].x, w.r[4].y, w.r[4].z, w.r[4].w};
+    const int hsh = 2 * g + half;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {                         // word i holds elements 4i..4i+3 of this half
-      const uint32_t wq = qw[i] >> nsh, hq = hw[i] >> hsh;   // nibble b at bits 8b..8b+3, fifth bit at bit 8b
-      float v[4];
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        uint32_t m;
-        if (q5) m = (place_bits(wq, 8 * b, 18) & 0x003C0000u) | (place_bits(hq, 8 * b, 22) & 0x00400000u);
-        else m = place_bits(wq, 8 * b, 19) & 0x00780000u;
-        v[b] = fmaf(dd, __uint_as_float(m | 0x3F800000u), cc);
-      }
-      out[2 * i] = pack_bf16(v[0], v[1]); out[2 * i + 1] = pack_bf16(v[2], v[3]);
+      uint32_t ws;
+      if (q5) ws = ((half ? qw[i] >> 2 : qw[i] << 2) & 0x3C3C3C3Cu) | (((hw[i] >> hsh) << 6) & 0x40404040u);
+      else ws = (half ? qw[i] >> 1 : qw[i] << 3) & 0x78787878u;
+      out[2 * i] = bf2_affine(__byte_perm(ws, 0, 0x4140) | MAGIC, MAGIC, sc2, mn2);
+      out[2 * i + 1] = bf2_affine(__byte_perm(ws, 0, 0x4342) | MAGIC, MAGIC, sc2, mn2);
     }
-  } else if (qtype == QT_Q6_K) {
-    // the 64 columns of group g: block half n = g >> 1, elements 64*(g&1) .. +63 of that half (upper: high nibbles)
-    const uint8_t* blk = row + (int64_t)sb * Q6K_DEV_STRIDE;
-    const int n = g >> 1, upper = g & 1, part = half;     // 32 elements: l = 0..31 of ql[l + 32*part]
-    const float d = h2f_alu((uint32_t)blk[208] | ((uint32_t)blk[209] << 8));
-    const int8_t* sc = (const int8_t*)(blk + 192 + 8 * n + 4 * upper);
-    const uint8_t* ql = blk + 64 * n + 32 * part;
-    const uint8_t* qh = blk + 128 + 32 * n;
-    const float s0 = d * (float)sc[2 * part] * 64.f, s1 = d * (float)sc[2 * part + 1] * 64.f;
-    const float c0 = -1.5f * s0, c1 = -1.5f * s1;         // -(64 s + 32 s): value = s * (q - 32)
-    const int hs = 2 * (2 * upper + part), ns = 4 * upper;
+  } else if (QT == QT_Q6_K) {
+    const int upper = g & 1, part = half;
+    const float d = h2f_alu(w.r[4].y & 0xFFFFu);
+    const uint32_t scw = w.r[4].x;
+    const int s0i = (int)(int8_t)((scw >> (16 * part)) & 0xFFu), s1i = (int)(int8_t)((scw >> (16 * part + 8)) & 0xFFu);
+    const uint32_t s0 = bf2_splat(d * (float)s0i), s1 = bf2_splat(d * (float)s1i);
+    constexpr uint32_t MAGIC = 0x42804280u;               // 64: codes at bits 1..6 of their byte (ulp 1/2)
+    constexpr uint32_t MAGIC_OFF = 0x42C042C0u;           // 96 = 64 + 32: subtracting it also centres the code (q - 32)
+    const uint32_t lq[8] = {w.r[0].x, w.r[0].y, w.r[0].z, w.r[0].w, w.r[1].x, w.r[1].y, w.r[1].z, w.r[1].w};
+    const uint32_t hq[8] = {w.r[2].x, w.r[2].y, w.r[2].z, w.r[2].w, w.r[3].x, w.r[3].y, w.r[3].z, w.r[3].w};
+    const int hs = 2 * (2 * upper + part);
 #pragma unroll
     for (int w4 = 0; w4 < 8; ++w4) {
-      const uint32_t lw = __ldg((const uint32_t*)(ql + 4 * w4)) >> ns, hwv = __ldg((const uint32_t*)(qh + 4 * w4)) >> hs;
-      float v[4];
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const uint32_t m = (place_bits(lw, 8 * b, 17) & 0x001E0000u) | (place_bits(hwv, 8 * b, 21) & 0x00600000u);
-        v[b] = fmaf(w4 < 4 ? s0 : s1, __uint_as_float(m | 0x3F800000u), w4 < 4 ? c0 : c1);
-      }
-      out[2 * w4] = pack_bf16(v[0], v[1]); out[2 * w4 + 1] = pack_bf16(v[2], v[3]);
+      const uint32_t ws = ((upper ? lq[w4] >> 3 : lq[w4] << 1) & 0x1E1E1E1Eu) | (((hq[w4] >> hs) << 5) & 0x60606060u);
+      const uint32_t s = w4 < 4 ? s0 : s1;
+      out[2 * w4] = bf2_affine(__byte_perm(ws, 0, 0x4140) | MAGIC, MAGIC_OFF, s, 0u);
+      out[2 * w4 + 1] = bf2_affine(__byte_perm(ws, 0, 0x4342) | MAGIC, MAGIC_OFF, s, 0u);
     }
-  } else if (qtype == QT_BF16) {
-    const uint4* src = (const uint4*)(row + (int64_t)(k0 + 32 * half) * 2);
+  } else if (QT == QT_BF16) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { const uint4 t = __ldg(src + i); out[4 * i] = t.x; out[4 * i + 1] = t.y; out[4 * i + 2] = t.z; out[4 * i + 3] = t.w; }
+    for (int i = 0; i < 4; ++i) { out[4 * i] = w.r[i].x; out[4 * i + 1] = w.r[i].y; out[4 * i + 2] = w.r[i].z; out[4 * i + 3] = w.r[i].w; }
   } else {                                                // F16
-    const uint4* src = (const uint4*)(row + (int64_t)(k0 + 32 * half) * 2);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint4 t = __ldg(src + i); const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+      const uint32_t x[4] = {w.r[i].x, w.r[i].y, w.r[i].z, w.r[i].w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j) out[4 * i + j] = pack_bf16(h2f_alu(w[j] & 0xFFFFu), h2f_alu(w[j] >> 16));
+      for (int j = 0; j < 4; ++j) out[4 * i + j] = pack_bf16(h2f_alu(x[j] & 0xFFFFu), h2f_alu(x[j] >> 16));
     }
   }
 }
@@ -172,19 +148,7 @@ __device__ __forceinline__ void store_half_row_sw128(uint8_t* tile, int r, int h
   }
 }
 
-__device__ __forceinline__ void gm_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(gm_smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void gm_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(gm_smem_u32(bar)), "r"(bytes) : "memory");
-}
-// 2-D tiled TMA load of a [rows x 64] bf16 box at (column x, row y) into shared memory; x * 2 bytes is a multiple of 128
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(gm_smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(gm_smem_u32(bar)) : "memory");
-}
-
-template <int NT>
+template <int NT, int QT>
 __global__ void __launch_bounds__(GM_THREADS) gemm_kquant_tcgen05_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap xmap) {
   extern __shared__ __align__(1024) uint8_t gsm[];
   __shared__ __align__(8) uint64_t full_bar[GM_STAGES], empty_bar[GM_STAGES], done_bar;
@@ -228,14 +192,17 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_kquant_tcgen05_kernel(const _
     const int r = tid & (GM_ROWS - 1), half = tid >> 7;
     const int wrow = n0 + r;
     const uint8_t* wptr = p.W + (int64_t)min(wrow, p.n - 1) * p.w_stride;
+    RawW cur, nxt;
+    if (nit > 0) load_raw<QT>(wptr, ks0 * GM_KSTEP, half, cur);
     for (int it = 0; it < nit; ++it) {
       const int s = it % GM_STAGES;
+      if (it + 1 < nit) load_raw<QT>(wptr, (ks0 + it + 1) * GM_KSTEP, half, nxt);   // next step's bytes are in flight while this one is converted
       if (it >= GM_STAGES) {                              // the MMAs that read this stage GM_STAGES steps ago are done
         ok = gm_wait(&empty_bar[s], (uint32_t)(it / GM_STAGES - 1) & 1u);
         if (!ok) break;
       }
       uint32_t v[16];
-      if (wrow < p.n) dequant_row32(wptr, p.qtype, (ks0 + it) * GM_KSTEP, half, v);
+      if (wrow < p.n) dequant_raw32<QT>(cur, (ks0 + it) * GM_KSTEP, half, v);
       else {
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] = 0u;
@@ -244,6 +211,7 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_kquant_tcgen05_kernel(const _
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic-proxy writes -> visible to the tensor core
       __syncwarp();
       if (lane == 0) gm_arrive(&full_bar[s]);
+      cur = nxt;
     }
   } else if (warp == GM_PRODUCERS / 32) {
     // ---- TMA producer: activations of this token tile -------------------------------------------
@@ -357,12 +325,12 @@ static int make_x_map(CUtensorMap* map, const GemmParams& p, int box_rows) {
   return r == CUDA_SUCCESS ? 0 : -7;
 }
 
-template <int NT>
-int launch_gemm(const GemmParams& p, cudaStream_t st) {
+template <int NT, int QT>
+int launch_gemm_q(const GemmParams& p, cudaStream_t st) {
   const size_t smem = GM_STAGES * (GM_ROWS * 128 + NT * 128) + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kquant_tcgen05_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_kquant_tcgen05_kernel<NT, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -370,7 +338,18 @@ int launch_gemm(const GemmParams& p, cudaStream_t st) {
   const int rc = make_x_map(&xmap, p, NT);
   if (rc) return rc;
   dim3 grid((p.n + GM_ROWS - 1) / GM_ROWS, (p.m + NT - 1) / NT, p.splitk);
-  return (int)launch(gemm_kquant_tcgen05_kernel<NT>, grid, dim3(GM_THREADS), smem, st, p, xmap);
+  return (int)launch(gemm_kquant_tcgen05_kernel<NT, QT>, grid, dim3(GM_THREADS), smem, st, p, xmap);
+}
+
+template <int NT>
+int launch_gemm(const GemmParams& p, cudaStream_t st) {
+  switch (p.qtype) {
+    case QT_Q4_K: return launch_gemm_q<NT, QT_Q4_K>(p, st);
+    case QT_Q5_K: return launch_gemm_q<NT, QT_Q5_K>(p, st);
+    case QT_Q6_K: return launch_gemm_q<NT, QT_Q6_K>(p, st);
+    case QT_BF16: return launch_gemm_q<NT, QT_BF16>(p, st);
+    default: return launch_gemm_q<NT, QT_F16>(p, st);
+  }
 }
 
 }  // namespace rlz

@@ -58,6 +58,8 @@ class BatchedForward:
         self.splits = 1
         self.attn_partial, self.attn_counters = ops.attn_decode_scratch(T, model.heads, self.splits, cfg.head_dim, dev)
         self.launches_per_pass = 0
+        self.flash_ok = ops.attn_prefill_supported(cfg.head_dim) and self.attn.stride(0) % 4 == 0
+        self.flash_min_tokens = 16
 
     # -- helpers ---------------------------------------------------------------------------
     def _gemm(self, w, x_b, y, T, bias=None, act=ACT_NONE, residual_inplace=False, y_col=0):
@@ -88,9 +90,11 @@ class BatchedForward:
         self.launches_per_pass += 1
 
     # -- the pass ------------------------------------------------------------------------------
-    def forward(self, T: int, page_table: torch.Tensor, shared_table: bool) -> torch.Tensor:
+    def forward(self, T: int, page_table: torch.Tensor, shared_table: bool, pos0: Optional[int] = None) -> torch.Tensor:
         """Run all layers for rows 0..T-1 (``tokens`` / ``positions`` / ``page_rows`` must be set).
         ``page_table``: ``[max_pages]`` shared by all rows (prefill) or ``[T, max_pages]``.
+        ``pos0``: rows are the consecutive positions ``pos0 .. pos0+T-1`` of one sequence (a prompt chunk);
+        attention then runs on the tensor-core flash kernel instead of one decode-kernel row per token.
         Returns the residual stream ``x[:T]`` (the caller applies the final norm + lm_head)."""
         m, cfg = self.model, self.model.cfg
         H, qd, kvd, hd = cfg.hidden_dim, m.q_dim, m.kv_dim, cfg.head_dim
@@ -116,11 +120,15 @@ class BatchedForward:
                 ops.rope_(qkv[:, qd:], self.positions[:T], m.kv_heads, hd, cfg.rope_dim, cfg.rope_type, cfg.rope_theta)
                 self.launches_per_pass += 2
             ops.kv_append(qkv[:, qd:], qkv[:, qd + kvd:], self.k_cache[l], self.v_cache[l], self.positions[:T], self.page_rows[:T], m.kv_heads, hd)
-            ops.attn_decode_launch(ops.build_attn_decode_params(
-                self.qkv, self.attn[:, L.o_in_off:], self.k_cache[l], self.v_cache[l], self.positions, page_table, self.attn_partial,
-                self.attn_counters, m.heads, m.kv_heads, hd, self.splits, T, 0, cfg.rope_type, cfg.rope_theta, 0, qd, qd + kvd,
-                None, None, cfg.eps, ld_qkv=self.qkv.stride(0), ld_out=self.attn.stride(0), shared_table=shared_table, no_append=True,
-                window=cfg.sliding_window or 0))
+            if pos0 is not None and shared_table and T >= self.flash_min_tokens and self.flash_ok:
+                ops.attn_prefill(self.qkv, self.attn[:, L.o_in_off:], self.k_cache[l], self.v_cache[l], page_table, T, pos0, m.heads, m.kv_heads, hd,
+                                 q_off=0, window=cfg.sliding_window or 0)
+            else:
+                ops.attn_decode_launch(ops.build_attn_decode_params(
+                    self.qkv, self.attn[:, L.o_in_off:], self.k_cache[l], self.v_cache[l], self.positions, page_table, self.attn_partial,
+                    self.attn_counters, m.heads, m.kv_heads, hd, self.splits, T, 0, cfg.rope_type, cfg.rope_theta, 0, qd, qd + kvd,
+                    None, None, cfg.eps, ld_qkv=self.qkv.stride(0), ld_out=self.attn.stride(0), shared_table=shared_table, no_append=True,
+                    window=cfg.sliding_window or 0))
             ops.to_bf16(self.attn[:T], self.attn_b[:T])
             self.launches_per_pass += 4
             self._row_parallel(L.o, self.attn_b[:T, : L.o.k], T, L.o_b)

@@ -259,11 +259,46 @@ class DecodePlan:
         self.thunks: List[Callable[[], None]] = []
         self.keep: list = []
         self.kernel_launches = 0
+        self._side: Optional[torch.cuda.Stream] = None
+        self._side_mode = False
+        self._ev_fork: Optional[torch.cuda.Event] = None
+        self._ev_join: Optional[torch.cuda.Event] = None
+
+    # -- a second stream for work that is independent of the main chain (captured as a parallel graph branch) --
+    def fork(self) -> None:
+        """Launches added until ``join()`` run on a lower-priority side stream, concurrently with the
+        launches added to the main chain after ``join_later()``."""
+        def _fork():
+            if self._side is None:
+                self._side = torch.cuda.Stream(priority=0)
+                self._ev_fork, self._ev_join = torch.cuda.Event(), torch.cuda.Event()
+            self._ev_fork.record()
+            self._side.wait_event(self._ev_fork)
+        self.thunks.append(_fork)
+        self._side_mode = True
+
+    def end_fork(self) -> None:
+        self._side_mode = False
+
+    def join(self) -> None:
+        def _join():
+            self._ev_join.record(self._side)
+            torch.cuda.current_stream().wait_event(self._ev_join)
+        self.thunks.append(_join)
+
+    def _push(self, fn) -> None:
+        if self._side_mode:
+            def on_side(fn=fn):
+                with torch.cuda.stream(self._side):
+                    fn()
+            self.thunks.append(on_side)
+        else:
+            self.thunks.append(fn)
 
     def add_gemv(self, p, stream=False):
         self.keep.append(p)
         fn = ops.gemv_stream_launch if stream else ops.gemv_launch
-        self.thunks.append(lambda p=p, fn=fn: fn(p))
+        self._push(lambda p=p, fn=fn: fn(p))
         self.kernel_launches += 1
 
     def add_gemv_auto(self, xs, mats, y, batch, ldy, residual=None, ld_res=None, target_ctas=296, ar=None):
@@ -361,6 +396,7 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
     tp = model.tp_size > 1
     target = int(os.environ.get("RLZ_GEMV_CTAS", 2 * sm_count if batch <= 1 else sm_count))   # register-path kernel: 2 CTAs/SM at batch 1
     chunks = [(c, min(4, batch - c)) for c in range(0, batch, 4)]       # GEMV kernels take <= 4 rows at a time
+    overlap_up = cfg.parallel_residual and len(chunks) == 1 and os.environ.get("RLZ_OVERLAP_UP", "1") != "0"
     qkv_w = qd + 2 * kvd
     ld1 = buf.y1.stride(0)
 
@@ -407,14 +443,24 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
             mats = [MatOut([(L.q, 0)], out_off=0, bias=L.q_b), MatOut([(L.k, 0)], out_off=qd, bias=L.k_b),
                     MatOut([(L.v, 0)], out_off=qd + kvd, bias=L.v_b)]
             if cfg.parallel_residual:
-                mats.append(MatOut([(L.up, 0)], out_off=model.act_col0 + L.down_in_off, bias=L.up_b,
-                                   act=ACT_GELU if cfg.constraints.activation == "gelu" else ops.ACT_SILU))
+                up_mat = MatOut([(L.up, 0)], out_off=model.act_col0 + L.down_in_off, bias=L.up_b,
+                                act=ACT_GELU if cfg.constraints.activation == "gelu" else ops.ACT_SILU)
+                if overlap_up:
+                    # the MLP up-projection does not depend on attention: it streams its weights on a side
+                    # stream while the main chain runs QKV -> attention (whose latency it hides)
+                    plan.fork()
+                    plan.add_gemv_auto([xin], [up_mat], buf.y1[c0:], cb, ld1, target_ctas=target)
+                    plan.end_fork()
+                else:
+                    mats.append(up_mat)
             plan.add_gemv_auto([xin], mats, buf.y1[c0:], cb, ld1, target_ctas=target)
         plan.add_attn(ops.build_attn_decode_params(
             buf.y1, buf.attn_out[:, L.o_in_off:], kc, vc, buf.positions, buf.page_table, buf.attn_partial, buf.attn_counters,
             model.heads, model.kv_heads, hd, splits, batch, cfg.rope_dim if cfg.uses_rope else 0, cfg.rope_type, cfg.rope_theta,
             0, qd, qd + kvd, L.q_norm_w, L.k_norm_w, cfg.eps, ld_qkv=ld1, ld_out=buf.attn_out.stride(0),
             window=cfg.sliding_window or 0, rope_table=model.rope_table if cfg.uses_rope else None))
+        if cfg.parallel_residual and overlap_up:
+            plan.join()
         if cfg.parallel_residual:
             row_parallel(lambda c0: [VecIn(buf.attn_out[c0:], L.o.k, ld=buf.attn_out.stride(0)), VecIn(buf.y1[c0:, model.act_col0:], L.down.k, ld=ld1)],
                          lambda res: MatOut([(L.o, 0), (L.down, 1)], bias=L.o_b, bias2=L.down_b, combine=COMBINE_ADD, residual=res))

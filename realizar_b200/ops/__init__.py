@@ -240,6 +240,26 @@ def attn_decode_launch(p: S.AttnDecodeParams) -> None:
     check(lib().rlz_attn_decode(ctypes.byref(p), stream_ptr()), "attn_decode")
 
 
+def attn_prefill_supported(head_dim: int) -> bool:
+    return bool(lib().rlz_attn_prefill_supported(int(head_dim)))
+
+
+def attn_prefill(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor, n_tokens: int,
+                 pos0: int, n_heads: int, n_kv_heads: int, head_dim: int, q_off: int = 0, window: int = 0) -> None:
+    """Causal attention of chunk rows ``pos0 .. pos0+n_tokens-1`` of one sequence over its paged cache
+    (tensor-core kernel; the chunk's own K/V rows must already be in the cache)."""
+    p = S.AttnPrefillParams()
+    p.qkv, p.out, p.k_cache, p.v_cache, p.page_table = qkv.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_table.data_ptr()
+    p.ld_qkv, p.ld_out = qkv.stride(0), out.stride(0)
+    p.n_heads, p.n_kv_heads, p.head_dim, p.q_off = n_heads, n_kv_heads, head_dim, q_off
+    p.n_tokens, p.pos0, p.window, p.scale = int(n_tokens), int(pos0), int(window or 0), head_dim ** -0.5
+    check(lib().rlz_attn_prefill(ctypes.byref(p), stream_ptr()), "attn_prefill")
+
+
+def attn_prefill_error(clear: bool = True) -> int:
+    return int(lib().rlz_attn_prefill_error(1 if clear else 0))
+
+
 # ------------------------------------------------------------------------------ small ops --
 def embed(table: torch.Tensor, qtype: int, row_bytes: int, hidden: int, vocab: int, tokens: torch.Tensor, out: torch.Tensor,
           pos_table: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None) -> None:

@@ -57,6 +57,12 @@ class AttnDecodeParams(Structure):
                 ("rope_table_len", c_int32), ("rope_table", c_void_p)]
 
 
+class AttnPrefillParams(Structure):
+    _fields_ = [("qkv", c_void_p), ("out", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p), ("page_table", c_void_p),
+                ("ld_qkv", c_int64), ("ld_out", c_int64), ("n_heads", c_int32), ("n_kv_heads", c_int32), ("head_dim", c_int32),
+                ("q_off", c_int32), ("n_tokens", c_int32), ("pos0", c_int32), ("window", c_int32), ("_pad", c_int32), ("scale", c_float)]
+
+
 class SampleParams(Structure):
     _fields_ = [("logits", c_void_p), ("ld", c_int64), ("vocab", c_int32), ("batch", c_int32), ("temperature", c_void_p),
                 ("top_k", c_void_p), ("top_p", c_void_p), ("min_p", c_void_p), ("uniform", c_void_p), ("out", c_void_p),
@@ -101,6 +107,9 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_to_bf16.argtypes = [c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_longlong, c_void_p]
     lib.rlz_norm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_float, c_void_p]
     lib.rlz_swiglu_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_longlong, c_longlong, c_int, c_void_p]
+    lib.rlz_attn_prefill.argtypes = [POINTER(AttnPrefillParams), c_void_p]
+    lib.rlz_attn_prefill_supported.argtypes = [c_int]
+    lib.rlz_attn_prefill_error.argtypes = [c_int]
     lib.rlz_advance.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     lib.rlz_page_rows.argtypes = [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_void_p]
     lib.rlz_argmax.argtypes = [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]

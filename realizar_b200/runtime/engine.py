@@ -384,7 +384,7 @@ class DecodeEngine:
             bf.tokens[:T].copy_(toks[c0:c0 + T], non_blocking=True)
             bf.positions[:T].copy_(pos, non_blocking=True)
             bf.page_rows[:T].copy_(rows, non_blocking=True)
-            x = bf.forward(T, self.buf.page_table[slot], shared_table=True)
+            x = bf.forward(T, self.buf.page_table[slot], shared_table=True, pos0=pos0 + c0)
             x_last = x[T - 1]
         self.buf.x[slot].copy_(x_last)
         if not self.cfg.greedy_only:
@@ -418,7 +418,7 @@ class DecodeEngine:
         bf.tokens[:n].copy_(torch.as_tensor(list(tokens), dtype=torch.int32), non_blocking=True)
         bf.positions[:n].copy_(pos, non_blocking=True)
         bf.page_rows[:n].copy_(torch.tensor([pages[int(p) // PAGE] for p in pos], dtype=torch.int32), non_blocking=True)
-        x = bf.forward(n, self.buf.page_table[slot], shared_table=True)
+        x = bf.forward(n, self.buf.page_table[slot], shared_table=True, pos0=pos0)
         out: List[int] = []
         B = self.cfg.max_batch
         for c0 in range(0, n, B):

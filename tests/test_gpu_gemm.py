@@ -50,3 +50,29 @@ def test_gemm_epilogue_and_splitk(cuda_device):
     assert float((y2.cpu() - ref2).abs().max() / ref2.abs().max()) < 2e-2
     assert gemm.choose_splitk(2560, 10240, 64) > 1 and gemm.choose_splitk(17920 * 2, 2560, 128) == 1
     assert ops.device_error() == 0
+
+
+@pytest.mark.parametrize("m", [16, 31, 64, 200, 300])
+@pytest.mark.parametrize("splitk", [1, 2, 4])
+def test_gemm_strided_inplace_residual(cuda_device, m, splitk):
+    """The way the batched forward pass calls it: output is a column window of a wider buffer that
+    already holds the residual (split-K adds into it, one split stores residual + product); rows
+    and columns outside the window must stay untouched."""
+    from realizar_b200 import ops
+    from realizar_b200.ops import gemm as G
+    n, k = 512, 1024
+    w, wd = _weight(n, k, QType.Q4_K, 3)
+    x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    buf = torch.randn(m + 3, n + 40, device="cuda")
+    before = buf.clone()
+    win = buf[:, 8:]
+    if splitk > 1:
+        G.gemm_launch(G.build_gemm_params(w, x, win, m, splitk=splitk, ldy=buf.stride(0)))
+    else:
+        G.gemm_launch(G.build_gemm_params(w, x, win, m, residual=win, ldy=buf.stride(0), ld_res=buf.stride(0)))
+    torch.cuda.synchronize()
+    assert ops.lib().rlz_gemm_error(0) == 0
+    ref = before[:m, 8:8 + n].cpu() + x.float().cpu() @ wd.to(torch.bfloat16).float().T
+    got = buf[:m, 8:8 + n].cpu()
+    assert float((got - ref).abs().max() / ref.abs().max()) < 2e-2
+    assert torch.equal(buf[m:], before[m:]) and torch.equal(buf[:, :8], before[:, :8]) and torch.equal(buf[:, 8 + n:], before[:, 8 + n:])

@@ -324,3 +324,16 @@ def test_targets_and_http_client_and_bricks():
     bn = lb.bottleneck()
     assert bn.brick == "GateUpProjection" and bn.gap > 1 and lb.total_budget_us() > 0
     assert any(not v.passed for v in lb.verify())
+
+
+def test_load_generator_inprocess(capsys):
+    from realizar_b200.serving.api import AppState, create_app
+    from realizar_b200.utils.loadgen import LoadConfig, run_load
+    st = AppState.demo()
+    try:
+        r = run_load(LoadConfig(requests=12, rate_per_s=500, max_concurrency=4, prompt_tokens=6, max_tokens=5), app=create_app(st))
+    finally:
+        st.serving.stop()
+    assert r["completed"] == 12 and r["errors"] == 0 and r["tokens"] >= 12 and r["ttft_ms"]["p50"] is not None and r["itl_ms"]["p99"] is not None
+    assert cli.main(["bench-serving", "--requests", "6", "--rate", "0", "--concurrency", "3", "--max-tokens", "4", "--prompt-tokens", "4"]) == 0
+    assert json.loads(capsys.readouterr().out)["completed"] == 6
