@@ -41,6 +41,13 @@ struct GemmParams {
   float* Y; int64_t ldy;
   const float* bias; const float* residual; int64_t ld_res;
   int32_t act; int32_t splitk; int32_t atomic_out; int32_t _pad;
+  // tensor-parallel row-parallel GEMM: instead of storing, push {value, epoch} pairs into this rank's slot of every
+  // rank's inbox (peer memory); a reduce kernel on each rank sums the slots.  Layout of an inbox:
+  // [parity 2][rank][ar_rows token rows][ar_row_pairs] pairs.
+  uint2* ar_inbox[8];
+  const uint32_t* ar_epoch;
+  int64_t ar_row_pairs;
+  int32_t ar_rank, ar_world, ar_rows, ar_enabled;
 };
 
 // ---- producers: raw block bytes -> registers (issued one K step ahead), registers -> bf16 pairs -------------
@@ -192,26 +199,34 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_kquant_tcgen05_kernel(const _
     const int r = tid & (GM_ROWS - 1), half = tid >> 7;
     const int wrow = n0 + r;
     const uint8_t* wptr = p.W + (int64_t)min(wrow, p.n - 1) * p.w_stride;
-    RawW cur, nxt;
-    if (nit > 0) load_raw<QT>(wptr, ks0 * GM_KSTEP, half, cur);
-    for (int it = 0; it < nit; ++it) {
-      const int s = it % GM_STAGES;
-      if (it + 1 < nit) load_raw<QT>(wptr, (ks0 + it + 1) * GM_KSTEP, half, nxt);   // next step's bytes are in flight while this one is converted
-      if (it >= GM_STAGES) {                              // the MMAs that read this stage GM_STAGES steps ago are done
-        ok = gm_wait(&empty_bar[s], (uint32_t)(it / GM_STAGES - 1) & 1u);
-        if (!ok) break;
-      }
-      uint32_t v[16];
-      if (wrow < p.n) dequant_raw32<QT>(cur, (ks0 + it) * GM_KSTEP, half, v);
-      else {
+    // a ring of PF K steps of raw block bytes per thread keeps enough loads in flight to cover HBM latency
+    constexpr int PF = QT == QT_Q4_K ? 4 : 3;
+    RawW ring[PF];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = 0u;
+    for (int j = 0; j < PF; ++j)
+      if (j < nit) load_raw<QT>(wptr, (ks0 + j) * GM_KSTEP, half, ring[j]);
+    for (int it0 = 0; it0 < nit && ok; it0 += PF) {
+#pragma unroll
+      for (int j = 0; j < PF; ++j) {
+        const int it = it0 + j;
+        if (it >= nit) break;
+        const int s = it % GM_STAGES;
+        if (it >= GM_STAGES) {                            // the MMAs that read this stage GM_STAGES steps ago are done
+          ok = gm_wait(&empty_bar[s], (uint32_t)(it / GM_STAGES - 1) & 1u);
+          if (!ok) break;
+        }
+        uint32_t v[16];
+        if (wrow < p.n) dequant_raw32<QT>(ring[j], (ks0 + it) * GM_KSTEP, half, v);
+        else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = 0u;
+        }
+        if (it + PF < nit) load_raw<QT>(wptr, (ks0 + it + PF) * GM_KSTEP, half, ring[j]);   // refill the slot just consumed
+        store_half_row_sw128(sm + s * STAGE, r, half, v);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic-proxy writes -> visible to the tensor core
+        __syncwarp();
+        if (lane == 0) gm_arrive(&full_bar[s]);
       }
-      store_half_row_sw128(sm + s * STAGE, r, half, v);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic-proxy writes -> visible to the tensor core
-      __syncwarp();
-      if (lane == 0) gm_arrive(&full_bar[s]);
-      cur = nxt;
     }
   } else if (warp == GM_PRODUCERS / 32) {
     // ---- TMA producer: activations of this token tile -------------------------------------------
@@ -256,6 +271,8 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_kquant_tcgen05_kernel(const _
     if (ok && (NT >= 64 || chalf == 0)) {
       const int row = n0 + q * 32 + lane;
       const float bias = (p.bias && row < p.n && blockIdx.z == 0) ? p.bias[row] : 0.f;
+      const uint32_t epoch = p.ar_enabled ? *p.ar_epoch : 0u;
+      const int64_t ar_slot = ((int64_t)(epoch & 1u) * p.ar_world + p.ar_rank) * p.ar_rows * p.ar_row_pairs;
 #pragma unroll 1
       for (int c0 = chalf * COLS_PER_WARP; c0 < (chalf + 1) * COLS_PER_WARP; c0 += 32) {
         if (m0 + c0 >= p.m) break;                        // warp-uniform: no tokens left in this tile
@@ -275,7 +292,10 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_kquant_tcgen05_kernel(const _
             if (tok < p.m) {
               float v = __uint_as_float(r[j]) + bias;
               float* dst = p.Y + (int64_t)tok * p.ldy + row;
-              if (p.atomic_out) atomicAdd(dst, v);
+              if (p.ar_enabled) {                         // one 8-byte store per rank; lanes cover consecutive rows (coalesced)
+                const int64_t off = ar_slot + (int64_t)tok * p.ar_row_pairs + row;
+                for (int pr = 0; pr < p.ar_world; ++pr) st_pair_sys(p.ar_inbox[pr] + off, __float_as_uint(v), epoch);
+              } else if (p.atomic_out) atomicAdd(dst, v);
               else {
                 if (p.act == ACT_GELU) v = gelu_tanh(v); else if (p.act == ACT_SILU) v = silu(v);
                 if (p.residual) v += p.residual[(int64_t)tok * p.ld_res + row];
@@ -378,6 +398,7 @@ int rlz_gemm_kquant(const rlz::GemmParams* pp, void* stream) {
   if (p.splitk > p.k / GM_KSTEP) p.splitk = p.k / GM_KSTEP;
   p.atomic_out = p.splitk > 1 ? 1 : 0;
   if (p.atomic_out && p.act != ACT_NONE) return -5;
+  if (p.ar_enabled && (p.splitk != 1 || p.act != ACT_NONE || p.residual || p.ar_world < 1 || p.ar_world > 8 || p.m > p.ar_rows || p.n > p.ar_row_pairs)) return -8;
   if ((p.ldx * 2) % 16) return -4;
   cudaStream_t st = (cudaStream_t)stream;
   if (p.m <= 32) return launch_gemm<32>(p, st);

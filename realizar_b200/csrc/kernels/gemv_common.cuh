@@ -137,13 +137,6 @@ __device__ __forceinline__ float gemv_value(const GemvMat& M, const float* rowac
   return v;
 }
 
-__device__ __forceinline__ void st_pair_sys(uint2* p, uint32_t a, uint32_t b) {       // one 8-byte store, visible system-wide
-  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory");
-}
-__device__ __forceinline__ uint2 ld_pair_sys(const uint2* p) {
-  uint2 v; asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory"); return v;
-}
-
 // Epilogue over the rows [r0, r1) of matrix M: rowacc holds [row][segment][batch] sums.
 // With p.ar.enabled the partial outputs are all-reduced across the tensor-parallel ranks inside
 // the kernel before the residual is added; every rank ends with the same sum.

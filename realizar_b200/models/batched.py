@@ -60,6 +60,13 @@ class BatchedForward:
         self.launches_per_pass = 0
         self.flash_ok = ops.attn_prefill_supported(cfg.head_dim) and self.attn.stride(0) % 4 == 0
         self.flash_min_tokens = 16
+        # tensor parallel, fused mode: row-parallel GEMMs of up to ll_tokens rows push their partial tiles into the peers'
+        # inboxes from the epilogue (one-shot all-reduce, latency-optimal); longer chunks use NCCL (bandwidth-optimal)
+        self.ll_tokens = 0
+        if model.tp_size > 1 and getattr(comm, "fused", False):
+            self.ll_tokens = min(max_tokens, 128)
+            comm.allocate_gemm(2 * cfg.num_layers, H, self.ll_tokens)
+        self._site = 0
 
     # -- helpers ---------------------------------------------------------------------------
     def _gemm(self, w, x_b, y, T, bias=None, act=ACT_NONE, residual_inplace=False, y_col=0):
@@ -84,6 +91,14 @@ class BatchedForward:
         if self.model.tp_size == 1:
             self._gemm(w, x_b, self.x, T, bias=bias, residual_inplace=True)
             return
+        if 0 < T <= self.ll_tokens:
+            p = G.build_gemm_params(w, x_b, self.partial, T, bias=bias, ldy=self.partial.stride(0))
+            self.comm.gemm_ar_fill(p, self._site)
+            G.gemm_launch(p)
+            self.comm.ll_reduce(self._site, self.x, T, w.n)
+            self._site += 1
+            self.launches_per_pass += 2
+            return
         self._gemm(w, x_b, self.partial, T, bias=bias)
         self.comm.all_reduce_sum_(self.partial[:T])
         ops.elementwise(self.partial[:T], residual=self.x[:T], out=self.x[:T])
@@ -101,6 +116,10 @@ class BatchedForward:
         norm_t = NORM_LAYER if cfg.uses_layernorm else NORM_RMS
         act_code = ACT_GELU if cfg.constraints.activation == "gelu" else ACT_SILU
         self.launches_per_pass = 0
+        if self.ll_tokens:
+            self._site = 0
+            self.comm.begin_step()                         # one epoch per pass tags this pass's peer stores
+            self.launches_per_pass += 1
         x, xb, qkv = self.x[:T], self.xb[:T], self.qkv[:T]
         ops.embed(m.embed_table, m.embed_qtype, m.embed_row_bytes, H, cfg.vocab_size, self.tokens[:T], self.x, m.pos_table, self.positions)
         self.launches_per_pass += 1

@@ -396,7 +396,7 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
     tp = model.tp_size > 1
     target = int(os.environ.get("RLZ_GEMV_CTAS", 2 * sm_count if batch <= 1 else sm_count))   # register-path kernel: 2 CTAs/SM at batch 1
     chunks = [(c, min(4, batch - c)) for c in range(0, batch, 4)]       # GEMV kernels take <= 4 rows at a time
-    overlap_up = cfg.parallel_residual and len(chunks) == 1 and os.environ.get("RLZ_OVERLAP_UP", "1") != "0"
+    overlap_up = cfg.parallel_residual and len(chunks) == 1 and os.environ.get("RLZ_OVERLAP_UP", "0") == "1"   # measured slower than the single chain; opt-in
     qkv_w = qd + 2 * kvd
     ld1 = buf.y1.stride(0)
 

@@ -39,6 +39,8 @@ def main(argv=None) -> int:
     if a.model == "small-phi2":
         cfg = ModelConfig("phi2", 1280, 2, 16, 16, 80, 2560, 512, 512, 1e4, 32, ROPE_NEOX, 1e-5, None, 2,
                           arch_constraints("phi2"), parallel_residual=True, fused_qkv=True)
+    elif a.model == "kq-llama":                              # every projection a K-quant: the tensor-core batched path under TP
+        cfg = ModelConfig("llama", 512, 2, 8, 2, 64, 1024, 512, 512, 1e4, 64, 0, 1e-5, 1, 2, arch_constraints("llama"))
     else:
         cfg = named_config(a.model)
     w = synthetic_weights(cfg, seed=5, std=0.05)            # CPU generator: identical on every rank
@@ -59,8 +61,20 @@ def main(argv=None) -> int:
         eng.close_slot(0)
         cos = float(gathered @ want_logits / (np.linalg.norm(gathered) * np.linalg.norm(want_logits)))
         status = comm.check_status() if hasattr(comm, "check_status") else 0
-        results[mode] = {"tokens": toks, "cos": cos, "first": first, "status": status}
+        results[mode] = {"tokens": toks, "cos": cos, "first": first, "status": status, "batched_prefill": bool(eng.gemm_ok),
+                         "ll_tokens": int(eng.batched().ll_tokens) if eng.gemm_ok else 0}
         ok &= cos > 0.99 and first == toks[0] and status == 0
+        if eng.gemm_ok:
+            # a longer prompt (beyond the one-shot limit when chunked at 128+) and a multi-token verification pass
+            long_prompt = [(7 * i + 3) % cfg.vocab_size for i in range(150)]
+            eng.open_slot(0, 200)
+            eng.prefill(0, long_prompt)
+            ll = comm.gather_logits(eng.buf.logits[0:1, : eng.model.vocab_local].clone(), cfg.vocab_size)[0].cpu().numpy()
+            eng.close_slot(0)
+            wl = ref.forward(long_prompt)[-1].numpy()
+            cos2 = float(ll @ wl / (np.linalg.norm(ll) * np.linalg.norm(wl)))
+            results[mode]["cos_long"] = cos2
+            ok &= cos2 > 0.99 and (comm.check_status() if hasattr(comm, "check_status") else 0) == 0
         t = torch.tensor(toks, device=dev)
         t0 = t.clone()
         dist.broadcast(t0, 0)

@@ -150,6 +150,31 @@ class FusedTpComm(NcclTpComm):
         ar.rank, ar.world, ar.enabled, ar.n = self.rank, self.world, 1, self.n
         return ar
 
+    # -- row-parallel GEMMs of token batches (batched decode, short prompt chunks) -------------------
+    def allocate_gemm(self, n_sites: int, n: int, max_tokens: int) -> None:
+        """Symmetric inboxes for ``n_sites`` GEMM call sites of up to ``max_tokens`` x ``n`` outputs:
+        per site ``[parity 2][rank][max_tokens][n]`` 8-byte {value, epoch} pairs on every rank."""
+        self.g_n = (n + 3) // 4 * 4
+        self.g_rows = max_tokens
+        self._g_site = 2 * self.world * self.g_rows * self.g_n * 8
+        self.g_sites = n_sites
+        self.gbuf = SymmetricBuffer(n_sites * self._g_site, self.rank, self.world, self.group)
+
+    def gemm_ar_fill(self, p: "S.GemmParams", site: int) -> None:
+        """Turn a GEMM launch into "push my partial tile to every rank" for call site ``site``."""
+        if not 0 <= site < self.g_sites:
+            raise IndexError(f"GEMM all-reduce site {site} out of range ({self.g_sites} reserved)")
+        for r in range(self.world):
+            p.ar_inbox[r] = self.gbuf.ptrs[r] + site * self._g_site
+        p.ar_epoch = self.epoch.data_ptr()
+        p.ar_row_pairs, p.ar_rank, p.ar_world, p.ar_rows, p.ar_enabled = self.g_n, self.rank, self.world, self.g_rows, 1
+
+    def ll_reduce(self, site: int, x: torch.Tensor, tokens: int, n: int) -> None:
+        """``x[:tokens, :n] += sum over ranks`` of what the GEMMs of call site ``site`` pushed (bounded polls)."""
+        ops.check(ops.lib().rlz_ll_reduce(self.gbuf.ptrs[self.rank] + site * self._g_site, self.epoch.data_ptr(), self.status.data_ptr(),
+                                          self.spin_limit, self.world, self.g_rows, self.g_n, tokens, n, x.data_ptr(), x.stride(0),
+                                          ops.stream_ptr()), "ll_reduce")
+
     def begin_step(self) -> None:
         ops.check(ops.lib().rlz_epoch_bump(self.epoch.data_ptr(), ops.stream_ptr()), "epoch_bump")
 
@@ -180,6 +205,9 @@ class FusedTpComm(NcclTpComm):
         if self.buf is not None:
             self.buf.close()
             self.buf = None
+        if getattr(self, "gbuf", None) is not None:
+            self.gbuf.close()
+            self.gbuf = None
 
 
 def make_tp_comm(rank: int, world: int, device, mode: str = "fused", group=None) -> TpCommBase:

@@ -76,3 +76,47 @@ def test_gemm_strided_inplace_residual(cuda_device, m, splitk):
     got = buf[:m, 8:8 + n].cpu()
     assert float((got - ref).abs().max() / ref.abs().max()) < 2e-2
     assert torch.equal(buf[m:], before[m:]) and torch.equal(buf[:, :8], before[:, :8]) and torch.equal(buf[:, 8 + n:], before[:, 8 + n:])
+
+
+def test_gemm_all_reduce_push_and_reduce_two_emulated_ranks(cuda_device):
+    """Row-parallel GEMM with the all-reduce in the epilogue, two ranks emulated on one GPU one after
+    the other (both pushes complete before the reduce runs, so nothing waits on a peer)."""
+    import ctypes
+    from realizar_b200 import ops
+    from realizar_b200.ops import gemm as G
+    m, n, k, world, rows_cap = 40, 384, 512, 2, 64
+    ws = [_weight(n, k, QType.Q4_K, 20 + r) for r in range(world)]
+    xs = [torch.randn(m, k, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    n_pad = n
+    inbox = [torch.zeros(2 * world * rows_cap * n_pad, 2, dtype=torch.int32, device="cuda") for _ in range(world)]   # 8-byte pairs
+    epoch = torch.tensor([5], dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    bias = torch.randn(n, device="cuda")
+    dummy = torch.zeros(m, n, device="cuda")
+    for r in range(world):
+        p = G.build_gemm_params(ws[r][0], xs[r], dummy, m, bias=bias if r == 0 else None)
+        for q in range(world):
+            p.ar_inbox[q] = inbox[q].data_ptr()
+        p.ar_epoch, p.ar_row_pairs, p.ar_rank, p.ar_world, p.ar_rows, p.ar_enabled = epoch.data_ptr(), n_pad, r, world, rows_cap, 1
+        G.gemm_launch(p)
+    torch.cuda.synchronize()
+    assert float(dummy.abs().max()) == 0.0                     # nothing is stored locally in this mode
+    ref = bias.cpu() + sum(xs[r].float().cpu() @ ws[r][1].to(torch.bfloat16).float().T for r in range(world))
+    for r in range(world):
+        x = torch.randn(m + 2, n + 8, device="cuda")
+        before = x.clone()
+        ops.check(ops.lib().rlz_ll_reduce(inbox[r].data_ptr(), epoch.data_ptr(), status.data_ptr(), 1000, world, rows_cap, n_pad, m, n,
+                                          x.data_ptr(), x.stride(0), ops.stream_ptr()), "ll_reduce")
+        torch.cuda.synchronize()
+        got = (x[:m, :n] - before[:m, :n]).cpu()
+        assert float((got - ref).abs().max() / ref.abs().max()) < 2e-2
+        assert torch.equal(x[m:], before[m:]) and torch.equal(x[:, n:], before[:, n:])
+    assert int(status.item()) == 0
+    # a wait that cannot complete (no rank wrote this epoch) gives up after the poll limit and reports 2003
+    epoch.fill_(9)
+    x = torch.zeros(m, n, device="cuda")
+    ops.check(ops.lib().rlz_ll_reduce(inbox[0].data_ptr(), epoch.data_ptr(), status.data_ptr(), 50, world, rows_cap, n_pad, 2, 16,
+                                      x.data_ptr(), x.stride(0), ops.stream_ptr()), "ll_reduce")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 2003
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0     # the context is still usable

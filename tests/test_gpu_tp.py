@@ -84,7 +84,7 @@ def _run_selftest(nproc, model, extra=()):
     return subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
-@pytest.mark.parametrize("model", ["tiny-llama", "small-phi2"])
+@pytest.mark.parametrize("model", ["tiny-llama", "small-phi2", "kq-llama"])
 def test_two_rank_tp_matches_oracle(cuda_device, model):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
