@@ -29,9 +29,7 @@ namespace rlz {
 
 __device__ int g_gemm_error = 0;
 
-constexpr int GM_PRODUCERS = 256;      // dequant threads (warps 0-7)
-constexpr int GM_THREADS = GM_PRODUCERS + 64;   // + TMA warp + MMA warp
-constexpr int GM_STAGES = 4;
+constexpr int GM_PRODUCERS = 256;      // dequant threads per 128-row tile (8 warps); the TMA warp and the MMA warp follow them
 constexpr int GM_ROWS = 128;          // weight rows per CTA = MMA M
 constexpr int GM_KSTEP = 64;          // K elements per stage (one 128-byte swizzle row of bf16)
 
@@ -41,13 +39,15 @@ struct GemmParams {
   float* Y; int64_t ldy;
   const float* bias; const float* residual; int64_t ld_res;
   int32_t act; int32_t splitk; int32_t atomic_out; int32_t _pad;
-  // tensor-parallel row-parallel GEMM: instead of storing, push {value, epoch} pairs into this rank's slot of every
+  // tensor-parallel row-parallel GEMM: instead of storing, push {value, tag} pairs into this rank's slots of every
   // rank's inbox (peer memory); a reduce kernel on each rank sums the slots.  Layout of an inbox:
-  // [parity 2][rank][ar_rows token rows][ar_row_pairs] pairs.
+  // [2 alternating buffers][world * ar_splits writers][ar_rows token rows][ar_row_pairs] pairs; writer = rank * ar_splits
+  // + K split; buffer = (epoch * ar_nsites + ar_site) & 1; tag = epoch * 256 + ar_site (epoch: device word, one per pass).
   uint2* ar_inbox[8];
   const uint32_t* ar_epoch;
   int64_t ar_row_pairs;
   int32_t ar_rank, ar_world, ar_rows, ar_enabled;
+  int32_t ar_site, ar_nsites, ar_splits, _pad2;
 };
 
 // ---- producers: raw block bytes -> registers (issued one K step ahead), registers -> bf16 pairs -------------
@@ -155,22 +155,26 @@ __device__ __forceinline__ void store_half_row_sw128(uint8_t* tile, int r, int h
   }
 }
 
-template <int NT, int QT>
-__global__ void __launch_bounds__(GM_THREADS) gemm_kquant_tcgen05_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap xmap) {
+// RT = 128-row weight tiles per CTA (1 or 2).  With RT = 2 the CTA owns 256 weight rows, keeps two accumulators in TMEM
+// and issues two MMAs per K slice that share the activation tile, which halves the activation traffic from L2 per FLOP.
+template <int NT, int QT, int RT>
+__global__ void __launch_bounds__(RT * GM_PRODUCERS + 64) gemm_kquant_tcgen05_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap xmap) {
+  constexpr int GM_STAGES = RT == 2 ? 3 : 4;
+  constexpr int PRODUCERS = RT * GM_PRODUCERS, PWARPS = PRODUCERS / 32, ROWS = RT * GM_ROWS;
   extern __shared__ __align__(1024) uint8_t gsm[];
   __shared__ __align__(8) uint64_t full_bar[GM_STAGES], empty_bar[GM_STAGES], done_bar;
   __shared__ uint32_t tmem_base_s;
   __shared__ int failed_s;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n0 = blockIdx.x * GM_ROWS, m0 = blockIdx.y * NT;
+  const int n0 = blockIdx.x * ROWS, m0 = blockIdx.y * NT;
   uint8_t* sm = (uint8_t*)(((uintptr_t)gsm + 1023) & ~(uintptr_t)1023);
-  constexpr int A_BYTES = GM_ROWS * 128, B_BYTES = NT * 128, STAGE = A_BYTES + B_BYTES;
-  constexpr uint32_t TMEM_COLS = NT < 32 ? 32 : NT;
+  constexpr int A_BYTES = ROWS * 128, B_BYTES = NT * 128, STAGE = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = RT * NT < 32 ? 32 : RT * NT;
 
   if (tid == 0) {
     failed_s = 0;
     for (int s = 0; s < GM_STAGES; ++s) {
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(gm_smem_u32(&full_bar[s])), "r"(GM_PRODUCERS / 32 + 1));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(gm_smem_u32(&full_bar[s])), "r"(PWARPS + 1));
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gm_smem_u32(&empty_bar[s])));
     }
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gm_smem_u32(&done_bar)));
@@ -194,13 +198,13 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_kquant_tcgen05_kernel(const _
   const int nit = max(0, ks1 - ks0);
   bool ok = true;
 
-  if (warp < GM_PRODUCERS / 32) {
+  if (warp < PWARPS) {
     // ---- dequant producers: thread -> (row, half of the 64-column step) ---------------------
-    const int r = tid & (GM_ROWS - 1), half = tid >> 7;
+    const int r = tid & (ROWS - 1), half = tid / ROWS;
     const int wrow = n0 + r;
     const uint8_t* wptr = p.W + (int64_t)min(wrow, p.n - 1) * p.w_stride;
     // a ring of PF K steps of raw block bytes per thread keeps enough loads in flight to cover HBM latency
-    constexpr int PF = QT == QT_Q4_K ? 4 : 3;
+    constexpr int PF = RT == 2 ? (QT == QT_Q4_K ? 3 : 2) : (QT == QT_Q4_K ? 4 : 3);
     RawW ring[PF];
 #pragma unroll
     for (int j = 0; j < PF; ++j)
@@ -228,7 +232,7 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_kquant_tcgen05_kernel(const _
         if (lane == 0) gm_arrive(&full_bar[s]);
       }
     }
-  } else if (warp == GM_PRODUCERS / 32) {
+  } else if (warp == PWARPS) {
     // ---- TMA producer: activations of this token tile -------------------------------------------
     if (lane == 0) {
       for (int it = 0; it < nit; ++it) {
@@ -251,10 +255,15 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_kquant_tcgen05_kernel(const _
         ok = gm_wait(&full_bar[s], (uint32_t)(it / GM_STAGES) & 1u);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t da = make_sdesc_k_sw128(gm_smem_u32(sm + s * STAGE)), db = make_sdesc_k_sw128(gm_smem_u32(sm + s * STAGE + A_BYTES));
+        const uint64_t db = make_sdesc_k_sw128(gm_smem_u32(sm + s * STAGE + A_BYTES));
 #pragma unroll
-        for (int kk = 0; kk < GM_KSTEP / 16; ++kk)        // advance 32 bytes (two 16-byte units) per K=16 slice
-          umma_bf16(tmem_d, da + (uint64_t)(2 * kk), db + (uint64_t)(2 * kk), idesc, (it > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < GM_KSTEP / 16; ++kk) {      // advance 32 bytes (two 16-byte units) per K=16 slice
+#pragma unroll
+          for (int j = 0; j < RT; ++j) {                  // row tile j: rows 128j.. of the A stage, accumulator columns NT*j..
+            const uint64_t da = make_sdesc_k_sw128(gm_smem_u32(sm + s * STAGE + j * GM_ROWS * 128));
+            umma_bf16(tmem_d + (uint32_t)(j * NT), da + (uint64_t)(2 * kk), db + (uint64_t)(2 * kk), idesc, (it > 0 || kk > 0) ? 1u : 0u);
+          }
+        }
         umma_commit(&empty_bar[s]);
       }
       if (ok) umma_commit(&done_bar);                     // arrives when every MMA above has completed
@@ -262,22 +271,29 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_kquant_tcgen05_kernel(const _
   }
   if (!ok) { failed_s = 1; atomicExch(&g_gemm_error, 3001); }
 
-  // ---- epilogue: TMEM lane = weight row, column = token; 8 warps, each a lane quarter x column half ----
-  if (warp < GM_PRODUCERS / 32 && nit > 0) {
-    if (ok && !gm_wait(&done_bar, 0u)) { ok = false; failed_s = 1; atomicExch(&g_gemm_error, 3001); }
+  // ---- epilogue: TMEM lane = weight row, column = token; each warp a lane quarter x column half (x row tile) ----
+  // (a K split without work still pushes zeros in all-reduce mode: the reducer counts on every writer)
+  if (warp < PWARPS && (nit > 0 || p.ar_enabled)) {
+    if (ok && nit > 0 && !gm_wait(&done_bar, 0u)) { ok = false; failed_s = 1; atomicExch(&g_gemm_error, 3001); }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     constexpr int COLS_PER_WARP = NT >= 64 ? NT / 2 : NT;
-    const int q = warp & 3, chalf = warp >> 2;
+    const int q = warp & 3, chalf = (warp >> 2) & 1, rt = warp >> 3;
     if (ok && (NT >= 64 || chalf == 0)) {
-      const int row = n0 + q * 32 + lane;
+      const int row = n0 + rt * GM_ROWS + q * 32 + lane;
       const float bias = (p.bias && row < p.n && blockIdx.z == 0) ? p.bias[row] : 0.f;
       const uint32_t epoch = p.ar_enabled ? *p.ar_epoch : 0u;
-      const int64_t ar_slot = ((int64_t)(epoch & 1u) * p.ar_world + p.ar_rank) * p.ar_rows * p.ar_row_pairs;
+      const uint32_t tag = epoch * 256u + (uint32_t)p.ar_site;
+      const int64_t ar_buf = (int64_t)((epoch * (uint32_t)p.ar_nsites + (uint32_t)p.ar_site) & 1u) * p.ar_world * p.ar_splits;
+      const int64_t ar_slot = (ar_buf + (int64_t)p.ar_rank * p.ar_splits + blockIdx.z) * p.ar_rows * p.ar_row_pairs;
 #pragma unroll 1
       for (int c0 = chalf * COLS_PER_WARP; c0 < (chalf + 1) * COLS_PER_WARP; c0 += 32) {
         if (m0 + c0 >= p.m) break;                        // warp-uniform: no tokens left in this tile
         uint32_t r[32];
-        const uint32_t taddr = tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+        const uint32_t taddr = tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(rt * NT + c0);
+        if (nit == 0) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        } else
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
@@ -294,7 +310,7 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_kquant_tcgen05_kernel(const _
               float* dst = p.Y + (int64_t)tok * p.ldy + row;
               if (p.ar_enabled) {                         // one 8-byte store per rank; lanes cover consecutive rows (coalesced)
                 const int64_t off = ar_slot + (int64_t)tok * p.ar_row_pairs + row;
-                for (int pr = 0; pr < p.ar_world; ++pr) st_pair_sys(p.ar_inbox[pr] + off, __float_as_uint(v), epoch);
+                for (int pr = 0; pr < p.ar_world; ++pr) st_pair_sys(p.ar_inbox[pr] + off, __float_as_uint(v), tag);
               } else if (p.atomic_out) atomicAdd(dst, v);
               else {
                 if (p.act == ACT_GELU) v = gelu_tanh(v); else if (p.act == ACT_SILU) v = silu(v);
@@ -309,7 +325,7 @@ __global__ void __launch_bounds__(GM_THREADS) gemm_kquant_tcgen05_kernel(const _
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (failed_s && warp == GM_PRODUCERS / 32 && lane == 0) {
+  if (failed_s && warp == PWARPS && lane == 0) {
     // error path: give TMA copies still in flight a bounded chance to land before the CTA's shared memory is released
     for (int s = 0; s < GM_STAGES && s < nit; ++s) gm_wait(&full_bar[s], 0u);
   }
@@ -345,30 +361,30 @@ static int make_x_map(CUtensorMap* map, const GemmParams& p, int box_rows) {
   return r == CUDA_SUCCESS ? 0 : -7;
 }
 
-template <int NT, int QT>
+template <int NT, int QT, int RT>
 int launch_gemm_q(const GemmParams& p, cudaStream_t st) {
-  const size_t smem = GM_STAGES * (GM_ROWS * 128 + NT * 128) + 1024;
+  const size_t smem = (RT == 2 ? 3 : 4) * (RT * GM_ROWS * 128 + NT * 128) + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kquant_tcgen05_kernel<NT, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_kquant_tcgen05_kernel<NT, QT, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   alignas(64) CUtensorMap xmap;
   const int rc = make_x_map(&xmap, p, NT);
   if (rc) return rc;
-  dim3 grid((p.n + GM_ROWS - 1) / GM_ROWS, (p.m + NT - 1) / NT, p.splitk);
-  return (int)launch(gemm_kquant_tcgen05_kernel<NT, QT>, grid, dim3(GM_THREADS), smem, st, p, xmap);
+  dim3 grid((p.n + RT * GM_ROWS - 1) / (RT * GM_ROWS), (p.m + NT - 1) / NT, p.splitk);
+  return (int)launch(gemm_kquant_tcgen05_kernel<NT, QT, RT>, grid, dim3(RT * GM_PRODUCERS + 64), smem, st, p, xmap);
 }
 
-template <int NT>
+template <int NT, int RT>
 int launch_gemm(const GemmParams& p, cudaStream_t st) {
   switch (p.qtype) {
-    case QT_Q4_K: return launch_gemm_q<NT, QT_Q4_K>(p, st);
-    case QT_Q5_K: return launch_gemm_q<NT, QT_Q5_K>(p, st);
-    case QT_Q6_K: return launch_gemm_q<NT, QT_Q6_K>(p, st);
-    case QT_BF16: return launch_gemm_q<NT, QT_BF16>(p, st);
-    default: return launch_gemm_q<NT, QT_F16>(p, st);
+    case QT_Q4_K: return launch_gemm_q<NT, QT_Q4_K, RT>(p, st);
+    case QT_Q5_K: return launch_gemm_q<NT, QT_Q5_K, RT>(p, st);
+    case QT_Q6_K: return launch_gemm_q<NT, QT_Q6_K, RT>(p, st);
+    case QT_BF16: return launch_gemm_q<NT, QT_BF16, RT>(p, st);
+    default: return launch_gemm_q<NT, QT_F16, RT>(p, st);
   }
 }
 
@@ -396,15 +412,22 @@ int rlz_gemm_kquant(const rlz::GemmParams* pp, void* stream) {
   if (((uintptr_t)p.X & 15) || (p.ldx % 8) || ((uintptr_t)p.W & 15) || (p.w_stride & 15)) return -4;
   if (p.splitk < 1) p.splitk = 1;
   if (p.splitk > p.k / GM_KSTEP) p.splitk = p.k / GM_KSTEP;
-  p.atomic_out = p.splitk > 1 ? 1 : 0;
+  p.atomic_out = (p.splitk > 1 && !p.ar_enabled) ? 1 : 0;
   if (p.atomic_out && p.act != ACT_NONE) return -5;
-  if (p.ar_enabled && (p.splitk != 1 || p.act != ACT_NONE || p.residual || p.ar_world < 1 || p.ar_world > 8 || p.m > p.ar_rows || p.n > p.ar_row_pairs)) return -8;
+  if (p.ar_enabled && (p.splitk > p.ar_splits || p.act != ACT_NONE || p.residual || p.ar_world < 1 || p.ar_world > 8 || p.m > p.ar_rows ||
+                       p.n > p.ar_row_pairs || p.ar_site < 0 || p.ar_site >= 256 || p.ar_site >= p.ar_nsites)) return -8;
+  if (p.ar_enabled) p.splitk = p.ar_splits;              // the reducer expects exactly ar_splits writers per rank
   if ((p.ldx * 2) % 16) return -4;
   cudaStream_t st = (cudaStream_t)stream;
-  if (p.m <= 32) return launch_gemm<32>(p, st);
-  if (p.m <= 64) return launch_gemm<64>(p, st);
-  if (p.m <= 128) return launch_gemm<128>(p, st);
-  return launch_gemm<256>(p, st);
+  if (p.m <= 32) return launch_gemm<32, 1>(p, st);
+  if (p.m <= 64) return launch_gemm<64, 1>(p, st);
+  if (p.m <= 128) return launch_gemm<128, 1>(p, st);
+  // 256-row CTAs when they still fill the GPU for more than two waves (or when asked to through p._pad = 2)
+  const long long tiles2 = (long long)((p.n + 255) / 256) * ((p.m + 255) / 256) * p.splitk;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const bool wide = p._pad == 2 || (p._pad != 1 && tiles2 >= 2LL * sms);
+  return wide ? launch_gemm<256, 2>(p, st) : launch_gemm<256, 1>(p, st);
 }
 
 }  // extern "C"

@@ -17,22 +17,25 @@ __global__ void epoch_bump_kernel(uint32_t* epoch) {
   if (threadIdx.x == 0 && blockIdx.x == 0) *epoch += 1;
 }
 
-// x[t, j] += sum over ranks of the value pushed into this rank's inbox for (t, j); every element is polled until its
-// epoch tag matches (bounded; on expiry status = 2003 and the element contributes what was read).
-__global__ void ll_reduce_kernel(const uint2* inbox, const uint32_t* epoch_p, int32_t* status, int64_t spin_limit, int world, int rows_cap,
-                                 int64_t row_pairs, int n, float* x, int64_t ldx) {
+// x[t, j] += sum over all writers (ranks x K splits) of the value pushed into this rank's inbox for (t, j) at call site
+// `site`; every element is polled until its tag matches (bounded; on expiry status = 2003 and the element contributes
+// what was read).  Buffer and tag follow the GEMM epilogue: buffer = (epoch * nsites + site) & 1, tag = epoch * 256 + site.
+__global__ void ll_reduce_kernel(const uint2* inbox, const uint32_t* epoch_p, int32_t* status, int64_t spin_limit, int writers, int rows_cap,
+                                 int64_t row_pairs, int site, int nsites, int n, float* x, int64_t ldx) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.y;
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
   if (j >= n) return;
   const uint32_t epoch = *epoch_p;
-  const uint2* base = inbox + (int64_t)(epoch & 1u) * world * rows_cap * row_pairs + (int64_t)t * row_pairs + j;
+  const uint32_t tag = epoch * 256u + (uint32_t)site;
+  const int64_t buf = (int64_t)((epoch * (uint32_t)nsites + (uint32_t)site) & 1u) * writers;
+  const uint2* base = inbox + buf * rows_cap * row_pairs + (int64_t)t * row_pairs + j;
   float v = 0.f;
-  for (int q = 0; q < world; ++q) {
+  for (int q = 0; q < writers; ++q) {
     const uint2* src = base + (int64_t)q * rows_cap * row_pairs;
     uint2 w = ld_pair_sys(src);
-    for (int64_t spins = 0; w.y != epoch; ++spins) {
+    for (int64_t spins = 0; w.y != tag; ++spins) {
       if (spins > spin_limit) { atomicExch(status, 2003); break; }
       w = ld_pair_sys(src);
     }
@@ -117,11 +120,11 @@ int rlz_epoch_bump(uint32_t* epoch, void* stream) {
   return (int)launch(epoch_bump_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, epoch);
 }
 
-int rlz_ll_reduce(const void* inbox, const uint32_t* epoch, int32_t* status, long long spin_limit, int world, int rows_cap, long long row_pairs,
-                  int tokens, int n, float* x, long long ldx, void* stream) {
-  if (tokens < 1 || tokens > rows_cap || n < 1 || n > row_pairs || world < 1 || world > GEMV_AR_MAX_RANKS) return -1;
+int rlz_ll_reduce(const void* inbox, const uint32_t* epoch, int32_t* status, long long spin_limit, int writers, int rows_cap, long long row_pairs,
+                  int site, int nsites, int tokens, int n, float* x, long long ldx, void* stream) {
+  if (tokens < 1 || tokens > rows_cap || n < 1 || n > row_pairs || writers < 1 || writers > 64 || site < 0 || site >= nsites || site >= 256) return -1;
   return (int)launch(ll_reduce_kernel, dim3((n + 255) / 256, tokens), dim3(256), 0, (cudaStream_t)stream, (const uint2*)inbox, epoch, status,
-                     (int64_t)spin_limit, world, rows_cap, (int64_t)row_pairs, n, x, (int64_t)ldx);
+                     (int64_t)spin_limit, writers, rows_cap, (int64_t)row_pairs, site, nsites, n, x, (int64_t)ldx);
 }
 
 int rlz_cand_exchange(const CandExchange* c, const float* val, const int32_t* idx, int32_t* out_idx, float* out_val, void* stream) {

@@ -95,7 +95,7 @@ class BatchedForward:
             p = G.build_gemm_params(w, x_b, self.partial, T, bias=bias, ldy=self.partial.stride(0))
             self.comm.gemm_ar_fill(p, self._site)
             G.gemm_launch(p)
-            self.comm.ll_reduce(self._site, self.x, T, w.n)
+            self.comm.ll_reduce(self._site, self.x, T, w.n, w.k)
             self._site += 1
             self.launches_per_pass += 2
             return

@@ -74,7 +74,7 @@ class GemmParams(Structure):
                 ("X", c_void_p), ("ldx", c_int64), ("Y", c_void_p), ("ldy", c_int64), ("bias", c_void_p), ("residual", c_void_p),
                 ("ld_res", c_int64), ("act", c_int32), ("splitk", c_int32), ("atomic_out", c_int32), ("_pad", c_int32),
                 ("ar_inbox", c_void_p * 8), ("ar_epoch", c_void_p), ("ar_row_pairs", c_int64), ("ar_rank", c_int32), ("ar_world", c_int32),
-                ("ar_rows", c_int32), ("ar_enabled", c_int32)]
+                ("ar_rows", c_int32), ("ar_enabled", c_int32), ("ar_site", c_int32), ("ar_nsites", c_int32), ("ar_splits", c_int32), ("_pad2", c_int32)]
 
 
 def declare(lib: ctypes.CDLL) -> None:
@@ -112,7 +112,7 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_attn_prefill.argtypes = [POINTER(AttnPrefillParams), c_void_p]
     lib.rlz_attn_prefill_supported.argtypes = [c_int]
     lib.rlz_attn_prefill_error.argtypes = [c_int]
-    lib.rlz_ll_reduce.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_longlong, c_int, c_int, c_void_p, c_longlong, c_void_p]
+    lib.rlz_ll_reduce.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p]
     lib.rlz_advance.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     lib.rlz_page_rows.argtypes = [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_void_p]
     lib.rlz_argmax.argtypes = [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]

@@ -37,7 +37,8 @@ def choose_splitk(n: int, k: int, m: int, sm_count: int = 148) -> int:
 
 
 def build_gemm_params(w: DeviceWeight, x: torch.Tensor, y: torch.Tensor, m: int, bias=None, residual=None, act=ACT_NONE,
-                      splitk: int = 1, ldx: Optional[int] = None, ldy: Optional[int] = None, ld_res: Optional[int] = None) -> S.GemmParams:
+                      splitk: int = 1, ldx: Optional[int] = None, ldy: Optional[int] = None, ld_res: Optional[int] = None,
+                      wide: int = 0) -> S.GemmParams:
     if x.dtype != torch.bfloat16 or y.dtype != torch.float32:
         raise TypeError("gemm expects bf16 activations and an fp32 output")
     p = S.GemmParams()
@@ -47,6 +48,7 @@ def build_gemm_params(w: DeviceWeight, x: torch.Tensor, y: torch.Tensor, m: int,
     p.bias, p.residual = ptr(bias), ptr(residual)
     p.ld_res = ld_res if ld_res is not None else (residual.stride(0) if residual is not None else 0)
     p.act, p.splitk = act, splitk
+    p._pad = wide                       # 0: kernel decides between 128- and 256-row CTAs (m > 128), 1: 128 rows, 2: 256 rows
     return p
 
 
@@ -73,11 +75,11 @@ def gemm(w: DeviceWeight, x: torch.Tensor, bias=None, residual=None, act=ACT_NON
 class GemmPlan:
     """Reusable launch of one weight matrix at a fixed token count (micro-benchmarks)."""
 
-    def __init__(self, w: DeviceWeight, m: int, device, splitk: Optional[int] = None):
-        self.w, self.m = w, m
+    def __init__(self, w: DeviceWeight, m: int, device, splitk: Optional[int] = None, wide: int = 0):
+        self.w, self.m, self.wide = w, m, wide
         self.splitk = splitk if splitk is not None else choose_splitk(w.n, w.k, m)
 
     def run(self, x: torch.Tensor, y: torch.Tensor) -> None:
         if self.splitk > 1:
             y.zero_()
-        gemm_launch(build_gemm_params(self.w, x, y, self.m, splitk=self.splitk))
+        gemm_launch(build_gemm_params(self.w, x, y, self.m, splitk=self.splitk, wide=self.wide))

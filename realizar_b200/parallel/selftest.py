@@ -50,7 +50,7 @@ def main(argv=None) -> int:
     results, ok = {}, True
     for mode in a.modes.split(","):
         comm = make_tp_comm(rank, world, dev, mode=mode)
-        eng = DecodeEngine(w, EngineConfig(max_batch=2, max_seq_len=128, cuda_graphs=bool(a.graphs), greedy_only=True), device=dev,
+        eng = DecodeEngine(w, EngineConfig(max_batch=2, max_seq_len=256, cuda_graphs=bool(a.graphs), greedy_only=True), device=dev,
                            comm=comm, tp_rank=rank, tp_size=world)
         dist.barrier()
         toks = eng.generate(prompt, SamplingParams(max_tokens=a.tokens))

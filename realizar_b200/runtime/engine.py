@@ -489,6 +489,26 @@ class DecodeEngine:
         finally:
             self.close_slot(slot)
 
+    # -- KV snapshots (host-side prefix cache, migration between engines) ----------------------------
+    def snapshot_kv(self, slot: int) -> dict:
+        """Copy the slot's KV pages to pinned host memory.  Returns what ``restore_kv`` needs."""
+        s = self.slots[slot]
+        pages = list(self.pages.seqs[s.seq_id].pages[: self.pages.pages_needed(s.position)])
+        idx = torch.tensor(pages, dtype=torch.long, device=self.device)
+        data = self.kv[:, :, idx].to("cpu", non_blocking=False)
+        return {"position": s.position, "pages": len(pages), "kv": data.pin_memory() if torch.cuda.is_available() else data}
+
+    def restore_kv(self, slot: int, snap: dict) -> None:
+        """Load a snapshot into a freshly opened slot (its pages may differ from the original ones)."""
+        s = self.slots[slot]
+        if s.position != 0:
+            raise RuntimeError("restore_kv needs an empty slot")
+        self._ensure_pages(slot, max(1, snap["position"]))
+        pages = self.pages.seqs[s.seq_id].pages[: snap["pages"]]
+        idx = torch.tensor(pages, dtype=torch.long, device=self.device)
+        self.kv[:, :, idx] = snap["kv"].to(self.device, non_blocking=True)
+        s.position = snap["position"]
+
     def logits_of_last_step(self, slot: int = 0) -> torch.Tensor:
         return self.buf.logits[slot, : self.mcfg.vocab_size].clone()
 

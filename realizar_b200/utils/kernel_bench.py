@@ -139,11 +139,11 @@ def bench_gemm(a):
     w = random_weight(a.n, a.k, qt, dev)
     x = (torch.randn(a.m, a.k, device=dev)).to(torch.bfloat16)
     y = torch.empty(a.m, a.n, device=dev, dtype=torch.float32)
-    plan = gemm_ops.GemmPlan(w, a.m, dev)
+    plan = gemm_ops.GemmPlan(w, a.m, dev, wide=a.wide)
     ms = time_cuda(lambda: plan.run(x, y), a.iters)
     flops = 2.0 * a.m * a.n * a.k
     pk = peaks()
-    return {"kernel": "gemm_kquant_tcgen05", "qtype": a.qtype, "m": a.m, "n": a.n, "k": a.k, "ms": ms, "tflops": flops / ms / 1e9,
+    return {"kernel": "gemm_kquant_tcgen05", "qtype": a.qtype, "m": a.m, "n": a.n, "k": a.k, "wide": a.wide, "splitk": plan.splitk, "ms": ms, "tflops": flops / ms / 1e9,
             "frac_of_%s_bf16" % pk["source"]: flops / ms / 1e9 / pk["bf16_tflops"],
             "weight_gbs": w.nbytes / ms / 1e6, "frac_of_%s_hbm_weights" % pk["source"]: w.nbytes / ms / 1e6 / pk["hbm_gbs"]}
 
@@ -165,6 +165,7 @@ def main(argv=None):
     m = sub.add_parser("gemm")
     m.add_argument("--qtype", default="Q4_K"); m.add_argument("--n", type=int, default=10240); m.add_argument("--k", type=int, default=2560)
     m.add_argument("--m", type=int, default=512); m.add_argument("--iters", type=int, default=10)
+    m.add_argument("--wide", type=int, default=0, help="0 auto, 1 force 128-row CTAs, 2 force 256-row CTAs (m > 128)")
     a = ap.parse_args(argv)
     global REPS, GRAPH
     REPS, GRAPH = max(1, a.reps), a.graph

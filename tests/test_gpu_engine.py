@@ -213,3 +213,23 @@ def test_prefix_cache_reuses_pages_and_parity_gate(cuda_device):
     assert eng.prefix_hits == 1 and eng.prefix_tokens_reused == 32          # two full 16-token pages of the shared prefix
     assert eng.generate(p1, SamplingParams(max_tokens=6)) == want1 and eng.prefix_hits == 2
     assert eng.pages.stats().sequences == 0
+
+
+def test_kv_snapshot_restore(cuda_device):
+    from realizar_b200.models.weights import synthetic_weights
+    from realizar_b200.runtime.engine import DecodeEngine, EngineConfig
+    cfg = _kq_llama()
+    w = synthetic_weights(cfg, seed=13, std=0.05)
+    toks = [int(t) for t in np.random.default_rng(5).integers(0, cfg.vocab_size, 37)]
+    eng = DecodeEngine(w, EngineConfig(max_batch=2, max_seq_len=128, greedy_only=True))
+    eng.open_slot(0, 64)
+    nxt = eng.prefill(0, toks)
+    snap = eng.snapshot_kv(0)
+    a = [int(eng.feed({0: nxt})[0])]
+    a.append(int(eng.feed({0: a[-1]})[0]))
+    eng.close_slot(0)
+    eng.open_slot(1, 64)                     # other slot, other pages
+    eng.restore_kv(1, snap)
+    b = [int(eng.feed({1: nxt})[1])]
+    b.append(int(eng.feed({1: b[-1]})[1]))
+    assert snap["position"] == 37 and snap["pages"] == 3 and a == b

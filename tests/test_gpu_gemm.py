@@ -80,43 +80,66 @@ def test_gemm_strided_inplace_residual(cuda_device, m, splitk):
 
 def test_gemm_all_reduce_push_and_reduce_two_emulated_ranks(cuda_device):
     """Row-parallel GEMM with the all-reduce in the epilogue, two ranks emulated on one GPU one after
-    the other (both pushes complete before the reduce runs, so nothing waits on a peer)."""
-    import ctypes
+    the other (both pushes complete before the reduce runs, so nothing waits on a peer).  Each rank
+    writes through 4 K splits, one of which has no K range at k = 192 and must push zeros."""
     from realizar_b200 import ops
     from realizar_b200.ops import gemm as G
-    m, n, k, world, rows_cap = 40, 384, 512, 2, 64
-    ws = [_weight(n, k, QType.Q4_K, 20 + r) for r in range(world)]
-    xs = [torch.randn(m, k, device="cuda").to(torch.bfloat16) for _ in range(world)]
-    n_pad = n
-    inbox = [torch.zeros(2 * world * rows_cap * n_pad, 2, dtype=torch.int32, device="cuda") for _ in range(world)]   # 8-byte pairs
-    epoch = torch.tensor([5], dtype=torch.int32, device="cuda")
-    status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    bias = torch.randn(n, device="cuda")
-    dummy = torch.zeros(m, n, device="cuda")
-    for r in range(world):
-        p = G.build_gemm_params(ws[r][0], xs[r], dummy, m, bias=bias if r == 0 else None)
-        for q in range(world):
-            p.ar_inbox[q] = inbox[q].data_ptr()
-        p.ar_epoch, p.ar_row_pairs, p.ar_rank, p.ar_world, p.ar_rows, p.ar_enabled = epoch.data_ptr(), n_pad, r, world, rows_cap, 1
-        G.gemm_launch(p)
-    torch.cuda.synchronize()
-    assert float(dummy.abs().max()) == 0.0                     # nothing is stored locally in this mode
-    ref = bias.cpu() + sum(xs[r].float().cpu() @ ws[r][1].to(torch.bfloat16).float().T for r in range(world))
-    for r in range(world):
-        x = torch.randn(m + 2, n + 8, device="cuda")
-        before = x.clone()
-        ops.check(ops.lib().rlz_ll_reduce(inbox[r].data_ptr(), epoch.data_ptr(), status.data_ptr(), 1000, world, rows_cap, n_pad, m, n,
-                                          x.data_ptr(), x.stride(0), ops.stream_ptr()), "ll_reduce")
+    for k in (512, 192):
+        m, n, world, rows_cap, splits, site, nsites = 40, 384, 2, 64, 4, 1, 3
+        qt = QType.Q4_K if k % 256 == 0 else QType.BF16
+        ws = [_weight(n, k, qt, 20 + r) for r in range(world)]
+        xs = [torch.randn(m, k, device="cuda").to(torch.bfloat16) for _ in range(world)]
+        inbox = [torch.zeros(2 * world * splits * rows_cap * n, 2, dtype=torch.int32, device="cuda") for _ in range(world)]   # 8-byte pairs
+        epoch = torch.tensor([5], dtype=torch.int32, device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        bias = torch.randn(n, device="cuda")
+        dummy = torch.zeros(m, n, device="cuda")
+        for r in range(world):
+            p = G.build_gemm_params(ws[r][0], xs[r], dummy, m, bias=bias if r == 0 else None)
+            for q in range(world):
+                p.ar_inbox[q] = inbox[q].data_ptr()
+            p.ar_epoch, p.ar_row_pairs, p.ar_rank, p.ar_world, p.ar_rows, p.ar_enabled = epoch.data_ptr(), n, r, world, rows_cap, 1
+            p.ar_site, p.ar_nsites, p.ar_splits = site, nsites, splits
+            G.gemm_launch(p)
         torch.cuda.synchronize()
-        got = (x[:m, :n] - before[:m, :n]).cpu()
-        assert float((got - ref).abs().max() / ref.abs().max()) < 2e-2
-        assert torch.equal(x[m:], before[m:]) and torch.equal(x[:, n:], before[:, n:])
-    assert int(status.item()) == 0
-    # a wait that cannot complete (no rank wrote this epoch) gives up after the poll limit and reports 2003
+        assert ops.lib().rlz_gemm_error(0) == 0
+        assert float(dummy.abs().max()) == 0.0                 # nothing is stored locally in this mode
+        ref = bias.cpu() + sum(xs[r].float().cpu() @ ws[r][1].to(torch.bfloat16).float().T for r in range(world))
+        for r in range(world):
+            x = torch.randn(m + 2, n + 8, device="cuda")
+            before = x.clone()
+            ops.check(ops.lib().rlz_ll_reduce(inbox[r].data_ptr(), epoch.data_ptr(), status.data_ptr(), 1000, world * splits, rows_cap, n, site, nsites,
+                                              m, n, x.data_ptr(), x.stride(0), ops.stream_ptr()), "ll_reduce")
+            torch.cuda.synchronize()
+            got = (x[:m, :n] - before[:m, :n]).cpu()
+            assert float((got - ref).abs().max() / ref.abs().max()) < 2e-2
+            assert torch.equal(x[m:], before[m:]) and torch.equal(x[:, n:], before[:, n:])
+        assert int(status.item()) == 0
+    # a wait that cannot complete (nobody wrote this epoch) gives up after the poll limit and reports 2003
     epoch.fill_(9)
     x = torch.zeros(m, n, device="cuda")
-    ops.check(ops.lib().rlz_ll_reduce(inbox[0].data_ptr(), epoch.data_ptr(), status.data_ptr(), 50, world, rows_cap, n_pad, 2, 16,
+    ops.check(ops.lib().rlz_ll_reduce(inbox[0].data_ptr(), epoch.data_ptr(), status.data_ptr(), 50, world * splits, rows_cap, n, site, nsites, 2, 16,
                                       x.data_ptr(), x.stride(0), ops.stream_ptr()), "ll_reduce")
     torch.cuda.synchronize()
     assert int(status.item()) == 2003
     assert float(torch.ones(4, device="cuda").sum()) == 4.0     # the context is still usable
+
+
+@pytest.mark.parametrize("qt", [QType.Q4_K, QType.Q6_K, QType.Q5_K, QType.BF16])
+def test_gemm_wide_row_tiles(cuda_device, qt):
+    """256-row CTAs (two TMEM accumulators) give the same result as 128-row CTAs, including ragged edges."""
+    from realizar_b200 import ops
+    from realizar_b200.ops import gemm as G
+    m, n, k = 300, 600, 768
+    w, wd = _weight(n, k, qt, 31)
+    x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    ref = x.float().cpu() @ wd.to(torch.bfloat16).float().T
+    outs = []
+    for wide in (1, 2):
+        y = torch.full((m, n), float("nan"), device="cuda")
+        G.gemm_launch(G.build_gemm_params(w, x, y, m, wide=wide))
+        torch.cuda.synchronize()
+        assert ops.lib().rlz_gemm_error(0) == 0
+        assert float((y.cpu() - ref).abs().max() / ref.abs().max()) < 2e-2
+        outs.append(y)
+    assert float((outs[0] - outs[1]).abs().max()) < 1e-3 * float(ref.abs().max())

@@ -1,0 +1,115 @@
+"""GPU profile, memory pools, streaming plan, hybrid dispatch and the small batch / queue types."""
+import pytest
+import torch
+
+from realizar_b200.runtime import batch_types as B
+from realizar_b200.runtime import memory as M
+from realizar_b200.runtime.gpu_profile import GpuProfile
+
+
+def test_gpu_profile_env_overrides_and_policy():
+    p = GpuProfile.detect(env={"RLZ_GEMV_STREAM": "1", "RLZ_PDL": "0", "RLZ_PREFILL_CHUNK": "256"})
+    assert p.gemv_stream_variant and not p.pdl and p.prefill_chunk == 256 and p.cuda_graphs
+    assert p.engine_config_overrides()["prefill_chunk"] == 256
+    q = GpuProfile(sm_count=148, compute_capability=(10, 0))
+    assert q.supported and q.gemv_target_ctas(1) == 296 and q.gemv_target_ctas(4) == 148
+    assert q.attn_splits(32, 1) == 8 and q.attn_splits(8, 1) == 8 and q.attn_splits(32, 64) == 1 and q.attn_splits(2, 40) == 2
+    assert not GpuProfile().supported and "gemm_decode_min_batch" in q.describe()
+
+
+def test_memory_pools():
+    assert M.size_class(1) == 256 and M.size_class(257) == 512 and M.size_class(4096) == 4096
+    pool = M.GpuMemoryPool("cpu", max_pooled_bytes=2048)
+    a = pool.acquire(300)
+    assert a.numel() == 512 and pool.stats.bytes_in_use == 512
+    pool.release(a)
+    b = pool.acquire(400)
+    assert b.data_ptr() == a.data_ptr() and pool.stats.hits == 1 and pool.stats.hit_rate == 0.5
+    big = pool.acquire(4000)
+    pool.release(big)                      # larger than the pooled-bytes cap: dropped
+    pool.release(b)
+    assert pool.stats.bytes_pooled == 512 and pool.trim() == 512 and not pool.free
+    sp = M.StagingBufferPool(1024, 2)
+    i0, b0 = sp.acquire()
+    i1, _ = sp.acquire()
+    assert sp.acquire() is None and b0.view(torch.float32, 4).numel() == 4
+    sp.release(i0)
+    assert sp.acquire()[0] == i0 and sp.mode in (M.TransferMode.PINNED, M.TransferMode.PAGEABLE)
+    t = M.cache_aligned_empty(100, torch.float32, 64)
+    assert t.data_ptr() % 64 == 0 and t.numel() == 100
+
+
+def test_vram_check_and_layer_streamer():
+    GB = 1 << 30
+    c = M.check_vram_sufficient(40 * GB, 10 * GB, 180 * GB, 80)
+    assert c.mode == M.StreamingMode.RESIDENT and c.resident_layers == 80
+    c = M.check_vram_sufficient(400 * GB, 10 * GB, 180 * GB, 80)
+    assert c.mode == M.StreamingMode.LAYER_STREAMING and 0 < c.resident_layers < 80 and c.layer_bytes == 5 * GB
+    with pytest.raises(MemoryError):
+        M.check_vram_sufficient(400 * GB, 175 * GB, 180 * GB, 80)
+    log = []
+    s = M.LayerStreamer(4, lambda l, b: log.append(("c", l, b)), lambda l, b: log.append(("x", l, b)), use_cuda=False)
+    s.run()
+    assert log == [("c", 0, 0), ("c", 1, 1), ("x", 0, 0), ("c", 2, 0), ("x", 1, 1), ("c", 3, 1), ("x", 2, 0), ("x", 3, 1)]
+
+
+def test_hybrid_scheduler():
+    h = M.HybridScheduler()
+    assert h.choose(100) == M.ComputeBackend.CPU
+    assert h.choose(1 << 20, operands_on_device=True) == M.ComputeBackend.GPU
+    assert h.choose(1 << 20, operands_on_device=False) == M.ComputeBackend.GPU       # 6/20 of the CPU cost
+    assert M.HybridScheduler(gpu_speedup=4.0).choose(1 << 20) == M.ComputeBackend.CPU  # transfer dominates
+    assert M.HybridScheduler(gpu_available=False).choose(1 << 30) == M.ComputeBackend.CPU
+    assert h.choose(10, preference=M.ComputeBackend.GPU) == M.ComputeBackend.GPU
+
+
+def test_batch_and_queue_types():
+    tb = B.TokenBatch(3)
+    assert tb.push(1) is None and tb.push(2) is None and tb.push(3) == [1, 2, 3] and len(tb) == 0
+    sb = B.SpeculativeBuffer(3)
+    assert sb.add_candidate(5, 0.9) and sb.add_candidate(6, 0.8) and sb.add_candidate(7, 0.5) and not sb.add_candidate(8, 0.1)
+    assert sb.verify([5, 6, 9]) == (2, 2) and sb.verify([5, 6, 7]) == (3, None)
+    sb.accept(2)
+    assert len(sb) == 1
+    r = B.AsyncGpuResult()
+    assert not r.is_ready()
+    with pytest.raises(TimeoutError):
+        r.wait(0.01)
+    r.set_result(42)
+    assert r.wait() == 42
+    e = B.AsyncGpuResult(); e.set_error(ValueError("x"))
+    with pytest.raises(ValueError):
+        e.wait()
+    q = B.AsyncRequestQueue(2)
+    assert q.try_push(1) and q.try_push(2) and not q.try_push(3) and q.is_full and q.try_pop() == 1
+    seen = []
+    n = B.InferenceEventNotifier(); n.register(lambda *a: seen.append(a)); n.notify(1, 2.0, 3)
+    assert seen == [(1, 2.0, 3)]
+    m = B.InferenceMetrics(); [m.record(float(i), 2) for i in range(1, 101)]
+    assert m.total_tokens == 200 and m.percentile(50) == 51.0 and m.percentile(99) == 100.0
+    mb = B.MicroBatch(max_tokens=3)
+    assert mb.add(B.BatchToken(1, 0, 0, True)) and mb.add(B.BatchToken(2, 0, 1, True)) and mb.add(B.BatchToken(9, 1, 5)) and not mb.add(B.BatchToken(0, 2, 0))
+    assert (mb.num_prompt, mb.num_decode, mb.sequences()) == (2, 1, [0, 1])
+
+
+def test_multi_request_policies_and_collector():
+    s = B.MultiRequestScheduler(B.SchedulingPolicy.SJF, max_concurrent=1)
+    a, b, c = s.submit(4, 10), s.submit(4, 2), s.submit(4, 5)
+    order = []
+    while not s.idle:
+        for i in s.step():
+            if i not in order:
+                order.append(i)
+    assert order == [b, c, a]
+    f = B.MultiRequestScheduler(B.SchedulingPolicy.FCFS, max_concurrent=2)
+    x, y, z = f.submit(1, 2), f.submit(1, 2), f.submit(1, 1)
+    assert f.step() == [x, y] and f.step() == [x, y] and f.step() == [z] and f.idle
+    rr = B.MultiRequestScheduler(B.SchedulingPolicy.ROUND_ROBIN, max_concurrent=2)
+    p, q = rr.submit(1, 2), rr.submit(1, 2)
+    assert [rr.step()[0] for _ in range(4)] == [p, q, p, q] and rr.idle
+    now = [0.0]
+    col = B.BatchRequestCollector(3, window_ms=5.0, clock=lambda: now[0])
+    assert col.add("a") is None and col.poll() is None
+    now[0] = 0.006
+    assert col.poll() == ["a"]
+    assert col.add(1) is None and col.add(2) is None and col.add(3) == [1, 2, 3]
