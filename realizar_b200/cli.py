@@ -151,8 +151,21 @@ def build_app_state(model: Optional[str], use_gpu: Optional[bool], max_batch: in
     from .serving.api import AppState
     if model is None:
         return AppState.demo()
-    path = resolve_uri(model)
-    w = load_model(path)
+    if model.startswith("synthetic:"):
+        # "synthetic:<named shape>[:<scheme>]": random-initialised weights of a named architecture (benchmarks without checkpoints)
+        from .models.config import named_config
+        from .models.weights import synthetic_weights
+        from .serving.tokenizer import ByteTokenizer
+        parts = model.split(":")
+        cfg = named_config(parts[1])
+        gpu = torch.cuda.is_available() if use_gpu is None else use_gpu
+        w = synthetic_weights(cfg, scheme=parts[2] if len(parts) > 2 else "Q4_K_M", seed=0, device="cuda" if gpu else "cpu")
+        path = Path(parts[1])
+        tok_override = ByteTokenizer(cfg.vocab_size, None)
+    else:
+        path = resolve_uri(model)
+        w = load_model(path)
+        tok_override = None
     gpu = torch.cuda.is_available() if use_gpu is None else use_gpu
     msl = min(max_seq_len, w.config.context_length)
     if gpu:
@@ -162,7 +175,8 @@ def build_app_state(model: Optional[str], use_gpu: Optional[bool], max_batch: in
         from .runtime.cpu_engine import CpuEngineConfig, CpuSlotEngine
         eng = CpuSlotEngine(w, CpuEngineConfig(max_batch=min(max_batch, 2), max_seq_len=msl))
     serving = ServingEngine(eng, SchedulerConfig(max_batch=eng.cfg.max_batch, max_seq_len=eng.cfg.max_seq_len)).start()
-    st = AppState(serving, build_tokenizer(w), build_template(w, path.stem), path.stem, w.config.eos_token_id, compute_mode="gpu" if gpu else "cpu",
+    st = AppState(serving, tok_override or build_tokenizer(w), build_template(w, path.stem), path.stem, None if tok_override else w.config.eos_token_id,
+                  compute_mode="gpu" if gpu else "cpu",
                   context_length=eng.cfg.max_seq_len)
     if warmup:
         res = ModelWarmer(WarmupConfig(iterations=2)).warm(lambda p, n: serving.generate(p, timeout=120.0, max_tokens=n), w.config.vocab_size, ModelHealth())

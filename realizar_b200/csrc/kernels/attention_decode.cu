@@ -28,8 +28,9 @@ namespace cg = cooperative_groups;
 namespace rlz {
 
 constexpr int ATT_PAGE = 16;
-constexpr int ATT_THREADS = 128;
-constexpr int ATT_TB = 4;            // tokens per half-warp per iteration
+constexpr int ATT_THREADS = 128;     // 8 half-warps; each takes up to TB tokens per iteration (TB by head-group size, below)
+constexpr int ATT_WARPS = ATT_THREADS / 32;
+constexpr int ATT_PT_MAX = 64;       // page-table entries of a split staged in shared memory (1024 tokens)
 constexpr int ATT_MAX_CLUSTER = 8;   // portable cluster size
 enum { MERGE_GLOBAL = 0, MERGE_CLUSTER = 1, MERGE_NONE = 2 };
 
@@ -74,7 +75,7 @@ __device__ __forceinline__ void rope_inplace(float* v, int d_rot, int rope_type,
   }
 }
 
-template <int GT, int MERGE>
+template <int GT, int MERGE, int DEEP>
 __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_constant__ AttnDecodeParams p) {
   const int G = p.n_heads / p.n_kv_heads;
   const int hgroups = (G + GT - 1) / GT;
@@ -87,8 +88,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
 
   __shared__ float q_s[GT][128];
   __shared__ float k_s[128], v_s[128];
-  __shared__ float part_s[ATT_THREADS / 16][GT][128 + 2];
+  __shared__ float part_s[ATT_WARPS][GT][128 + 2];   // per-warp partials
   __shared__ float res_s[GT][128 + 2];      // this CTA's split result (read by cluster rank 0 in MERGE_CLUSTER)
+  __shared__ int32_t pt_s[ATT_PT_MAX];      // physical pages of this split's token range
   __shared__ int last_flag;
 
   pdl_launch_dependents();
@@ -104,7 +106,11 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
   const int start = lo_al + split * chunk, end = min(seq_len, start + chunk);
   const bool owner = !p.no_append && start <= pos && pos < end;
 
-  // ---- stage q (this head group), and k/v of the new token ---------------------------------
+  // ---- stage the split's page-table entries, q (this head group), and k/v of the new token: independent loads ----
+  const int32_t* pt = p.page_table + (int64_t)b * p.pt_stride;
+  const int npages = (max(0, end - start) + ATT_PAGE - 1) / ATT_PAGE;
+  const bool pt_staged = npages <= ATT_PT_MAX;
+  if (pt_staged && tid < npages) pt_s[tid] = pt[start / ATT_PAGE + tid];
   const float* row = p.qkv + (int64_t)b * p.ld_qkv;
   for (int i = tid; i < gn * d; i += ATT_THREADS) {
     const int g = i / d, j = i - g * d;
@@ -135,7 +141,6 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
     if (owner) rope_inplace(k_s, p.rope_dim, p.rope_type, pos, p.rope_theta, tab, tid, ATT_THREADS);
     __syncthreads();
   }
-  const int32_t* pt = p.page_table + (int64_t)b * p.pt_stride;
   if (owner && hg == 0) {   // append the new row to the cache (one head group does it)
     const int page = pt[pos / ATT_PAGE], slot = pos % ATT_PAGE;
     const int64_t off = (((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE + slot) * d;
@@ -162,78 +167,108 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
   // cache (another CTA is writing it), everyone else reads the cache only
   // shuffles stay inside a half-warp (all 16 lanes share base / validity), so each half uses its own mask
   const unsigned hmask = 0xFFFFu << (lane & 16);
-  const int iters = (max(0, end - start) + (ATT_THREADS / 16) * ATT_TB - 1) / ((ATT_THREADS / 16) * ATT_TB);
+  // tokens per half-warp per iteration: as many as the registers of this head-group size allow, so that a split of up
+  // to 8 * TB tokens (96 for MHA) has all its K/V loads in flight at once and pays the memory latency a single time
+  // (DEEP = 0, used when the grid already fills the GPU several times over: 4 tokens, fewer registers, more CTAs per SM)
+  constexpr int TB = !DEEP ? 4 : GT == 1 ? 12 : GT == 2 ? 10 : GT == 4 ? 8 : 4;
+  constexpr int TOK_IT = (ATT_THREADS / 16) * TB;
+  const int iters = (max(0, end - start) + TOK_IT - 1) / TOK_IT;
+  // head groups > 0 of the split that owns the new position read that row from shared memory (only the owner staged it)
+  const bool new_from_smem = owner && hg != 0;
   for (int it = 0; it < iters; ++it) {
-    const int base = start + (it * (ATT_THREADS / 16) + hw) * ATT_TB;
-    const bool any = base < end;
-    const int page = any ? pt[base / ATT_PAGE] : 0, slot = base % ATT_PAGE;
-    const int64_t off = (((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE + slot) * d + j0;
-    uint4 kr[ATT_TB], vr[ATT_TB];
+    const int base = start + (it * (ATT_THREADS / 16) + hw) * TB;
+    uint4 kr[TB], vr[TB];
 #pragma unroll
-    for (int t = 0; t < ATT_TB; ++t) {
-      const bool ok = lane_ok && base + t < end && !(hg != 0 && base + t == pos && !p.no_append);
-      kr[t] = ok ? *(const uint4*)(p.k_cache + off + (int64_t)t * d) : make_uint4(0, 0, 0, 0);
-      vr[t] = ok ? *(const uint4*)(p.v_cache + off + (int64_t)t * d) : make_uint4(0, 0, 0, 0);
+    for (int t = 0; t < TB; ++t) {
+      const int tok = base + t;
+      const bool okl = lane_ok && tok < end && !(new_from_smem && tok == pos);
+      const int tk = min(tok, end - 1 > start ? end - 1 : start);
+      const int page = pt_staged ? pt_s[(tk - start) / ATT_PAGE] : pt[tk / ATT_PAGE];
+      const int64_t off = (((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE + (tk % ATT_PAGE)) * d + j0;
+      kr[t] = okl ? *(const uint4*)(p.k_cache + off) : make_uint4(0, 0, 0, 0);
+      vr[t] = okl ? *(const uint4*)(p.v_cache + off) : make_uint4(0, 0, 0, 0);
     }
-    float kf[ATT_TB][8], vf[ATT_TB][8];
+    float sc[GT][TB];
+    // pass 1: scores (K converted one token at a time)
 #pragma unroll
-    for (int t = 0; t < ATT_TB; ++t) {
-      const uint32_t kw[4] = {kr[t].x, kr[t].y, kr[t].z, kr[t].w}, vw[4] = {vr[t].x, vr[t].y, vr[t].z, vr[t].w};
+    for (int t = 0; t < TB; ++t) {
+      float kf[8];
+      const uint32_t kw[4] = {kr[t].x, kr[t].y, kr[t].z, kr[t].w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        kf[t][2 * j] = __uint_as_float(kw[j] << 16); kf[t][2 * j + 1] = __uint_as_float(kw[j] & 0xFFFF0000u);
-        vf[t][2 * j] = __uint_as_float(vw[j] << 16); vf[t][2 * j + 1] = __uint_as_float(vw[j] & 0xFFFF0000u);
+      for (int j = 0; j < 4; ++j) { kf[2 * j] = __uint_as_float(kw[j] << 16); kf[2 * j + 1] = __uint_as_float(kw[j] & 0xFFFF0000u); }
+      if (new_from_smem && base + t == pos && lane_ok) {   // new row straight from shared memory (bf16-rounded like the cache)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) kf[j] = __bfloat162float(__float2bfloat16_rn(k_s[j0 + j]));
       }
-      if (hg != 0 && base + t == pos && lane_ok && !p.no_append) {   // new row straight from shared memory (bf16-rounded like the cache)
+      const bool valid = base + t < end && base + t >= lo;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          kf[t][j] = __bfloat162float(__float2bfloat16_rn(k_s[j0 + j]));
-          vf[t][j] = __bfloat162float(__float2bfloat16_rn(v_s[j0 + j]));
-        }
-      }
-    }
-#pragma unroll
-    for (int g = 0; g < GT; ++g) {
-      float s[ATT_TB];
-#pragma unroll
-      for (int t = 0; t < ATT_TB; ++t) {
+      for (int g = 0; g < GT; ++g) {
         float x = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) x += q[g][j] * kf[t][j];
+        for (int j = 0; j < 8; ++j) x += q[g][j] * kf[j];
         x += __shfl_xor_sync(hmask, x, 8);
         x += __shfl_xor_sync(hmask, x, 4);
         x += __shfl_xor_sync(hmask, x, 2);
         x += __shfl_xor_sync(hmask, x, 1);
-        s[t] = (base + t < end && base + t >= lo) ? x : -INFINITY;
+        sc[g][t] = valid ? x : -INFINITY;
       }
+    }
+    // running max / rescale per head, scores -> probabilities
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
       float mn = m[g];
 #pragma unroll
-      for (int t = 0; t < ATT_TB; ++t) mn = fmaxf(mn, s[t]);
-      if (mn == -INFINITY) continue;           // nothing valid seen yet by this stream
-      const float corr = exp2f(m[g] - mn);     // m = -inf on the first valid pass -> 0
+      for (int t = 0; t < TB; ++t) mn = fmaxf(mn, sc[g][t]);
+      const bool none = mn == -INFINITY;       // nothing valid seen yet by this stream
+      const float corr = none ? 1.f : exp2f(m[g] - mn);     // m = -inf on the first valid pass -> 0
       l[g] *= corr;
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[g][j] *= corr;
 #pragma unroll
-      for (int t = 0; t < ATT_TB; ++t) {
-        const float pr = exp2f(s[t] - mn);
-        l[g] += pr;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[g][j] += pr * vf[t][j];
-      }
+      for (int t = 0; t < TB; ++t) { sc[g][t] = none ? 0.f : exp2f(sc[g][t] - mn); l[g] += sc[g][t]; }
       m[g] = mn;
+    }
+    // pass 2: weighted values (V converted one token at a time)
+#pragma unroll
+    for (int t = 0; t < TB; ++t) {
+      float vf[8];
+      const uint32_t vw[4] = {vr[t].x, vr[t].y, vr[t].z, vr[t].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { vf[2 * j] = __uint_as_float(vw[j] << 16); vf[2 * j + 1] = __uint_as_float(vw[j] & 0xFFFF0000u); }
+      if (new_from_smem && base + t == pos && lane_ok) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vf[j] = __bfloat162float(__float2bfloat16_rn(v_s[j0 + j]));
+      }
+#pragma unroll
+      for (int g = 0; g < GT; ++g)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[g][j] += sc[g][t] * vf[j];
     }
   }
 
+  // ---- combine: the two half-warps of a warp through shuffles, then the warps through shared memory ----
+#pragma unroll
+  for (int g = 0; g < GT; ++g) {
+    const float mo = __shfl_xor_sync(0xFFFFFFFFu, m[g], 16), lo2 = __shfl_xor_sync(0xFFFFFFFFu, l[g], 16);
+    const float mm = fmaxf(m[g], mo);
+    const float c0 = m[g] == -INFINITY ? 0.f : exp2f(m[g] - mm), c1 = mo == -INFINITY ? 0.f : exp2f(mo - mm);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float ao = __shfl_xor_sync(0xFFFFFFFFu, acc[g][j], 16);
+      acc[g][j] = c0 * acc[g][j] + c1 * ao;
+    }
+    l[g] = c0 * l[g] + c1 * lo2;
+    m[g] = mm;
+  }
   // ---- combine the 8 half-warp streams of this CTA -------------------------------------------
 #pragma unroll
   for (int g = 0; g < GT; ++g) {
-    if (g < gn) {
+    if (g < gn && lane < 16) {
       if (lane_ok) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) part_s[hw][g][j0 + j] = acc[g][j];
+        for (int j = 0; j < 8; ++j) part_s[warp][g][j0 + j] = acc[g][j];
       }
-      if (l16 == 0) { part_s[hw][g][128] = m[g]; part_s[hw][g][129] = l[g]; }
+      if (lane == 0) { part_s[warp][g][128] = m[g]; part_s[warp][g][129] = l[g]; }
     }
   }
   __syncthreads();
@@ -242,9 +277,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
     const bool stat = i >= gn * d;                 // the trailing gn items carry (max, sum) of each head
     const int g = stat ? i - gn * d : i / d, j = stat ? 0 : i - g * d;
     float mm = -INFINITY;
-    for (int w = 0; w < ATT_THREADS / 16; ++w) mm = fmaxf(mm, part_s[w][g][128]);
+    for (int w = 0; w < ATT_WARPS; ++w) mm = fmaxf(mm, part_s[w][g][128]);
     float a = 0.f, ll = 0.f;
-    for (int w = 0; w < ATT_THREADS / 16; ++w) {
+    for (int w = 0; w < ATT_WARPS; ++w) {
       const float mw = part_s[w][g][128];
       const float c = mw == -INFINITY ? 0.f : exp2f(mw - mm);
       a += c * part_s[w][g][j]; ll += c * part_s[w][g][129];
@@ -265,16 +300,23 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
     cg::cluster_group cluster = cg::this_cluster();
     cluster.sync();                                  // every CTA's res_s is complete and visible
     if (cluster.block_rank() == 0) {
+      // the loops over the splits are unrolled to the cluster size so that the remote loads are independent and in flight together
       for (int i = tid; i < gn * d; i += ATT_THREADS) {
         const int g = i / d, j = i - g * d;
+        float ms[ATT_MAX_CLUSTER], av[ATT_MAX_CLUSTER], lv[ATT_MAX_CLUSTER];
+#pragma unroll
+        for (int sp = 0; sp < ATT_MAX_CLUSTER; ++sp) {
+          const float* r = cluster.map_shared_rank(&res_s[0][0], sp < S ? sp : 0) + g * 130;
+          ms[sp] = sp < S ? r[128] : -INFINITY; av[sp] = r[j]; lv[sp] = r[129];
+        }
         float mm = -INFINITY;
-        for (int s = 0; s < S; ++s) mm = fmaxf(mm, cluster.map_shared_rank(&res_s[0][0], s)[g * 130 + 128]);
+#pragma unroll
+        for (int sp = 0; sp < ATT_MAX_CLUSTER; ++sp) mm = fmaxf(mm, ms[sp]);
         float a = 0.f, ll = 0.f;
-        for (int s = 0; s < S; ++s) {
-          const float* r = cluster.map_shared_rank(&res_s[0][0], s) + g * 130;
-          const float ms = r[128];
-          const float c = ms == -INFINITY ? 0.f : exp2f(ms - mm);
-          a += c * r[j]; ll += c * r[129];
+#pragma unroll
+        for (int sp = 0; sp < ATT_MAX_CLUSTER; ++sp) {
+          const float c = ms[sp] == -INFINITY ? 0.f : exp2f(ms[sp] - mm);
+          a += c * av[sp]; ll += c * lv[sp];
         }
         p.out[(int64_t)b * p.ld_out + (kvh * G + g0 + g) * d + j] = a / ll;
       }
@@ -324,10 +366,13 @@ static int attn_decode_dispatch(const AttnDecodeParams& p, cudaStream_t st) {
   const int merge = p.splits == 1 ? MERGE_NONE : p.splits <= ATT_MAX_CLUSTER ? MERGE_CLUSTER : MERGE_GLOBAL;
   dim3 grid(p.n_kv_heads * hgroups, p.splits, p.batch), block(ATT_THREADS);
   dim3 cl(1, merge == MERGE_CLUSTER ? p.splits : 1, 1);
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const bool deep = (long long)grid.x * grid.y * grid.z < 4LL * sms;     // latency-bound launch: keep more loads in flight per thread
+#define RLZ_ATT_LAUNCH(GT_, M_) (deep ? launch_cluster(attn_decode_kernel<GT_, M_, 1>, grid, block, cl, 0, st, p) \
+                                      : launch_cluster(attn_decode_kernel<GT_, M_, 0>, grid, block, cl, 0, st, p))
 #define RLZ_ATT_CASE(GT_) \
-  (merge == MERGE_NONE ? launch_cluster(attn_decode_kernel<GT_, MERGE_NONE>, grid, block, cl, 0, st, p) \
-   : merge == MERGE_CLUSTER ? launch_cluster(attn_decode_kernel<GT_, MERGE_CLUSTER>, grid, block, cl, 0, st, p) \
-                            : launch_cluster(attn_decode_kernel<GT_, MERGE_GLOBAL>, grid, block, cl, 0, st, p))
+  (merge == MERGE_NONE ? RLZ_ATT_LAUNCH(GT_, MERGE_NONE) : merge == MERGE_CLUSTER ? RLZ_ATT_LAUNCH(GT_, MERGE_CLUSTER) : RLZ_ATT_LAUNCH(GT_, MERGE_GLOBAL))
   cudaError_t e;
   switch (GT) {
     case 1: e = RLZ_ATT_CASE(1); break;
@@ -335,6 +380,7 @@ static int attn_decode_dispatch(const AttnDecodeParams& p, cudaStream_t st) {
     case 8: e = RLZ_ATT_CASE(8); break;
     default: e = RLZ_ATT_CASE(4); break;
   }
+#undef RLZ_ATT_LAUNCH
 #undef RLZ_ATT_CASE
   return (int)e;
 }
@@ -403,5 +449,7 @@ int rlz_attn_decode_static(const rlz::AttnDecodeParams* pp, void* stream) {
   p.counters = sc.counters;
   return attn_decode_dispatch(p, st);
 }
+
+int rlz_sizeof_attn_decode_params() { return (int)sizeof(rlz::AttnDecodeParams); }
 
 }  // extern "C"

@@ -272,4 +272,6 @@ int rlz_attn_prefill(const rlz::AttnPrefillParams* pp, void* stream) {
   }
 }
 
+int rlz_sizeof_attn_prefill_params() { return (int)sizeof(rlz::AttnPrefillParams); }
+
 }  // extern "C"

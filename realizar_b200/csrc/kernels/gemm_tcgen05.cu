@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(RT * GM_PRODUCERS + 64) gemm_kquant_tcgen05_ke
     const int wrow = n0 + r;
     const uint8_t* wptr = p.W + (int64_t)min(wrow, p.n - 1) * p.w_stride;
     // a ring of PF K steps of raw block bytes per thread keeps enough loads in flight to cover HBM latency
-    constexpr int PF = RT == 2 ? (QT == QT_Q4_K ? 3 : 2) : (QT == QT_Q4_K ? 4 : 3);
+    constexpr int PF = NT <= 64 ? 2 : RT == 2 ? (QT == QT_Q4_K ? 3 : 2) : (QT == QT_Q4_K ? 4 : 3);   // short kernels: smaller code wins
     RawW ring[PF];
 #pragma unroll
     for (int j = 0; j < PF; ++j)
@@ -302,20 +302,32 @@ __global__ void __launch_bounds__(RT * GM_PRODUCERS + 64) gemm_kquant_tcgen05_ke
             : "r"(taddr) : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (row < p.n) {
+          // one compact loop per output mode (the mode is uniform over the launch): only the code of the mode in use is fetched
+          const int ntok = min(32, p.m - (m0 + c0));
+          float* dst = p.Y + (int64_t)(m0 + c0) * p.ldy + row;
+          if (p.ar_enabled) {                             // one 8-byte store per rank; lanes cover consecutive rows (coalesced)
+            const int64_t off0 = ar_slot + (int64_t)(m0 + c0) * p.ar_row_pairs + row;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int tok = m0 + c0 + j;
-            if (tok < p.m) {
-              float v = __uint_as_float(r[j]) + bias;
-              float* dst = p.Y + (int64_t)tok * p.ldy + row;
-              if (p.ar_enabled) {                         // one 8-byte store per rank; lanes cover consecutive rows (coalesced)
-                const int64_t off = ar_slot + (int64_t)tok * p.ar_row_pairs + row;
-                for (int pr = 0; pr < p.ar_world; ++pr) st_pair_sys(p.ar_inbox[pr] + off, __float_as_uint(v), tag);
-              } else if (p.atomic_out) atomicAdd(dst, v);
-              else {
+            for (int j = 0; j < 32; ++j)
+              if (j < ntok)
+                for (int pr = 0; pr < p.ar_world; ++pr) st_pair_sys(p.ar_inbox[pr] + off0 + (int64_t)j * p.ar_row_pairs, __float_as_uint(__uint_as_float(r[j]) + bias), tag);
+          } else if (p.atomic_out) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < ntok) atomicAdd(dst + (int64_t)j * p.ldy, __uint_as_float(r[j]) + bias);
+          } else if (p.act == ACT_NONE && !p.residual) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < ntok) dst[(int64_t)j * p.ldy] = __uint_as_float(r[j]) + bias;
+          } else {
+            const float* res = p.residual ? p.residual + (int64_t)(m0 + c0) * p.ld_res + row : nullptr;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (j < ntok) {
+                float v = __uint_as_float(r[j]) + bias;
                 if (p.act == ACT_GELU) v = gelu_tanh(v); else if (p.act == ACT_SILU) v = silu(v);
-                if (p.residual) v += p.residual[(int64_t)tok * p.ld_res + row];
-                *dst = v;
+                if (res) v += res[(int64_t)j * p.ld_res];
+                dst[(int64_t)j * p.ldy] = v;
               }
             }
           }
@@ -429,5 +441,7 @@ int rlz_gemm_kquant(const rlz::GemmParams* pp, void* stream) {
   const bool wide = p._pad == 2 || (p._pad != 1 && tiles2 >= 2LL * sms);
   return wide ? launch_gemm<256, 2>(p, st) : launch_gemm<256, 1>(p, st);
 }
+
+int rlz_sizeof_gemm_params() { return (int)sizeof(rlz::GemmParams); }
 
 }  // extern "C"

@@ -354,4 +354,6 @@ int rlz_gemv(const rlz::GemvParams* pp, void* stream) {
   return (int)e;
 }
 
+int rlz_sizeof_gemv_params() { return (int)sizeof(rlz::GemvParams); }
+
 }  // extern "C"

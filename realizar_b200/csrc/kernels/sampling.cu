@@ -57,6 +57,42 @@ __global__ void __launch_bounds__(SAMP_THREADS) argmax_kernel(const float* logit
   if (threadIdx.x == 0) { out[blockIdx.x] = i + index_offset; if (out_val) out_val[blockIdx.x] = v; }
 }
 
+// Multi-CTA argmax: grid (rows, slices).  Every CTA reduces its slice of the row, folds (value, smallest index) into a
+// 64-bit key with atomicMax, and the last CTA of the row to finish (ticket counter) decodes the key, writes the result
+// and leaves key and counter zeroed for the next launch (the scratch is a file-scope device array, self-cleaning).
+constexpr int ARGMAX_MAX_ROWS = 4096;
+__device__ unsigned long long g_argmax_key[ARGMAX_MAX_ROWS];
+__device__ unsigned int g_argmax_cnt[ARGMAX_MAX_ROWS];
+
+__global__ void __launch_bounds__(SAMP_THREADS) argmax_sliced_kernel(const float* logits, int64_t ld, int vocab, int32_t* out, float* out_val,
+                                                                     int index_offset) {
+  __shared__ float sval[33]; __shared__ int sidx[33];
+  __shared__ int last_s;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x, nsl = gridDim.y;
+  const float* row = logits + (int64_t)r * ld;
+  const int per = ((vocab + nsl - 1) / nsl + 3) & ~3;
+  const int i0 = blockIdx.y * per, i1 = min(vocab, i0 + per);
+  float best = -INFINITY; int bi = 0x7fffffff;
+  for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) { const float v = row[i]; if (v > best) { best = v; bi = i; } }
+  float v; int i;
+  block_argmax(best, bi, sval, sidx, &v, &i);
+  if (threadIdx.x == 0) {
+    if (i != 0x7fffffff) atomicMax(&g_argmax_key[r], ((unsigned long long)float_key(v) << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)i));
+    __threadfence();
+    last_s = atomicAdd(&g_argmax_cnt[r], 1u) == (unsigned)nsl - 1;
+  }
+  __syncthreads();
+  if (!last_s || threadIdx.x != 0) return;
+  __threadfence();
+  const unsigned long long key = atomicExch(&g_argmax_key[r], 0ull);
+  g_argmax_cnt[r] = 0;
+  const uint32_t kv = (uint32_t)(key >> 32), idx = 0xFFFFFFFFu - (uint32_t)key;
+  out[r] = (key ? (int)idx : 0) + index_offset;
+  if (out_val) out_val[r] = key ? __uint_as_float((kv & 0x80000000u) ? (kv & 0x7FFFFFFFu) : ~kv) : -INFINITY;
+}
+
 struct SampleParams {
   const float* logits; int64_t ld; int32_t vocab; int32_t batch;
   const float* temperature;   // [B]; <= 0 -> greedy
@@ -207,6 +243,12 @@ extern "C" {
 using namespace rlz;
 
 int rlz_argmax(const float* logits, long long ld, int vocab, int batch, int32_t* out, float* out_val, int index_offset, void* stream) {
+  if (vocab < 1 || batch < 1) return -1;
+  // wide rows and few sequences: split every row over several CTAs (one CTA per row leaves the GPU idle)
+  const int slices = vocab >= 16384 && batch <= ARGMAX_MAX_ROWS ? (batch >= 64 ? 4 : vocab / 4096 > 32 ? 32 : vocab / 4096) : 1;
+  if (slices > 1)
+    return (int)launch(argmax_sliced_kernel, dim3(batch, slices), dim3(SAMP_THREADS), 0, (cudaStream_t)stream, logits, (int64_t)ld, vocab, out, out_val,
+                       index_offset);
   return (int)launch(argmax_kernel, dim3(batch), dim3(SAMP_THREADS), 0, (cudaStream_t)stream, logits, (int64_t)ld, vocab, out, out_val, index_offset);
 }
 
@@ -220,5 +262,7 @@ int rlz_penalties(float* logits, long long ld, int vocab, int batch, const int32
   return (int)launch(penalties_kernel, dim3(batch), dim3(256), 0, (cudaStream_t)stream, logits, (int64_t)ld, vocab, history, window,
                      repetition, presence, frequency);
 }
+
+int rlz_sizeof_sample_params() { return (int)sizeof(rlz::SampleParams); }
 
 }  // extern "C"

@@ -133,4 +133,6 @@ int rlz_cand_exchange(const CandExchange* c, const float* val, const int32_t* id
   return (int)launch(cand_exchange_kernel, dim3(1), dim3(threads), 0, (cudaStream_t)stream, *c, val, idx, out_idx, out_val);
 }
 
+int rlz_sizeof_cand_exchange() { return (int)sizeof(rlz::CandExchange); }
+
 }  // extern "C"

@@ -116,9 +116,9 @@ class BatchedForward:
         norm_t = NORM_LAYER if cfg.uses_layernorm else NORM_RMS
         act_code = ACT_GELU if cfg.constraints.activation == "gelu" else ACT_SILU
         self.launches_per_pass = 0
-        if self.ll_tokens:
+        if self.model.tp_size > 1 and getattr(self.comm, "fused", False):
             self._site = 0
-            self.comm.begin_step()                         # one epoch per pass tags this pass's peer stores
+            self.comm.begin_step()                         # one epoch per pass tags this pass's peer stores (GEMM pushes, candidate exchange)
             self.launches_per_pass += 1
         x, xb, qkv = self.x[:T], self.xb[:T], self.qkv[:T]
         ops.embed(m.embed_table, m.embed_qtype, m.embed_row_bytes, H, cfg.vocab_size, self.tokens[:T], self.x, m.pos_table, self.positions)

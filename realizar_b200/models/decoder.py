@@ -347,7 +347,7 @@ def emit_head(plan: "DecodePlan", model: GpuModel, buf: StepBuffers, r0: int, ba
         cb = min(4, batch - c0)
         xin = VecIn(buf.x[r0 + c0:], H, ld=buf.x.stride(0), norm=norm_t, norm_w=model.out_norm_w, norm_b=model.out_norm_b, eps=cfg.eps)
         plan.add_gemv_auto([xin], [MatOut([(model.lm_head, 0)], bias=model.lm_head_b)], buf.logits[r0 + c0:], cb,
-                           buf.logits.stride(0), target_ctas=sm_count)
+                           buf.logits.stride(0), target_ctas=int(os.environ.get("RLZ_GEMV_CTAS", 2 * sm_count if cb <= 1 else sm_count)))
     emit_select(plan, model, buf, r0, batch, comm, greedy_only)
 
 

@@ -278,3 +278,21 @@ def test_argmax_and_sampling(cuda_device):
     hist = torch.tensor([[3, 5, 3, -1]], device="cuda", dtype=torch.int32)
     ops.penalties_(lg, hist, torch.tensor([2.0], device="cuda"), torch.tensor([0.5], device="cuda"), torch.tensor([0.25], device="cuda"))
     assert abs(float(lg[0, 3]) - (1.0 - 0.5 - 0.5)) < 1e-6 and abs(float(lg[0, 5]) - (-4.0 - 0.5 - 0.25)) < 1e-6
+
+
+def test_argmax_sliced_rows(cuda_device):
+    """Wide vocabularies split each row over several CTAs; ties resolve to the smallest index; repeat launches reuse the scratch."""
+    from realizar_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(3)
+    for batch, vocab in ((1, 51200), (3, 151936), (70, 32000), (2, 16384)):
+        logits = torch.randn(batch, vocab + 5, device="cuda", generator=g)[:, :vocab]      # row pitch larger than the vocabulary
+        logits[0, 777] = logits[0, vocab - 3] = 50.0                                        # a tie: the smaller index wins
+        val = torch.empty(batch, device="cuda")
+        for _ in range(3):
+            am = ops.argmax(logits, out_val=val, index_offset=11, vocab=vocab)
+            assert (am.cpu() - 11).tolist() == logits.argmax(-1).cpu().tolist() or (am.cpu()[0] - 11 == 777 and (am.cpu()[1:] - 11).tolist() == logits[1:].argmax(-1).cpu().tolist())
+            assert int(am[0]) - 11 == 777
+            assert torch.allclose(val, logits.max(-1).values)
+    neg = -torch.rand(1, 20000, device="cuda") - 1.0                                       # all-negative rows decode correctly too
+    v = torch.empty(1, device="cuda")
+    assert int(ops.argmax(neg, out_val=v)) == int(neg.argmax()) and torch.allclose(v, neg.max(-1).values)
