@@ -250,6 +250,11 @@ def _is_fast(w: DeviceWeight) -> bool:
     return QType(w.qtype) in FAST_TYPES
 
 
+# Timing diagnostic only (results are wrong): RLZ_DIAG_SKIP=attn,qkv,oproj leaves those launches out of the decode plan so
+# that the marginal cost of a kernel inside the real launch sequence can be read from the step time.
+_DIAG_SKIP = set(filter(None, os.environ.get("RLZ_DIAG_SKIP", "").split(",")))
+
+
 class DecodePlan:
     """The launch sequence of one decode step for a fixed batch size; ``run()`` issues it on
     the current stream (eagerly or under graph capture)."""
@@ -295,13 +300,15 @@ class DecodePlan:
         else:
             self.thunks.append(fn)
 
-    def add_gemv(self, p, stream=False):
+    def add_gemv(self, p, stream=False, tag=""):
         self.keep.append(p)
+        if tag and tag in _DIAG_SKIP:
+            return
         fn = ops.gemv_stream_launch if stream else ops.gemv_launch
         self._push(lambda p=p, fn=fn: fn(p))
         self.kernel_launches += 1
 
-    def add_gemv_auto(self, xs, mats, y, batch, ldy, residual=None, ld_res=None, target_ctas=296, ar=None):
+    def add_gemv_auto(self, xs, mats, y, batch, ldy, residual=None, ld_res=None, target_ctas=296, ar=None, tag=""):
         """Emit one GEMV launch, or several when the matrices mix int8-fast-path block types with
         generic ones (a launch is homogeneous).  A two-matrix accumulate of mixed kinds becomes two
         launches, the second one accumulating onto the output of the first."""
@@ -322,10 +329,12 @@ class DecodePlan:
             if group:
                 st = group is fast and ops.stream_eligible(group)
                 self.add_gemv(ops.build_gemv_params(xs, group, y, batch, ldy=ldy, residual=residual, ld_res=ld_res,
-                                                    target_ctas=self.sm_count if st else target_ctas, ar=ar), stream=st)
+                                                    target_ctas=self.sm_count if st else target_ctas, ar=ar), stream=st, tag=tag)
 
     def add_attn(self, p):
         self.keep.append(p)
+        if "attn" in _DIAG_SKIP:
+            return
         self.thunks.append(lambda p=p: ops.attn_decode_launch(p))
         self.kernel_launches += 1
 
@@ -427,7 +436,7 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
                     ar = comm.ar_desc(site[0])
                     site[0] += 1
                 plan.add_gemv_auto(xs_of(c0), [mat], buf.x[c0:], cb, buf.x.stride(0), residual=buf.x[c0:], ld_res=buf.x.stride(0),
-                                   target_ctas=target, ar=ar)
+                                   target_ctas=target, ar=ar, tag="oproj")
             else:
                 plan.add_gemv_auto(xs_of(c0), [mat], buf.partial_out[c0:], cb, buf.partial_out.stride(0), target_ctas=target)
         if tp and not use_ar:
@@ -453,7 +462,7 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
                     plan.end_fork()
                 else:
                     mats.append(up_mat)
-            plan.add_gemv_auto([xin], mats, buf.y1[c0:], cb, ld1, target_ctas=target)
+            plan.add_gemv_auto([xin], mats, buf.y1[c0:], cb, ld1, target_ctas=target, tag="qkv")
         plan.add_attn(ops.build_attn_decode_params(
             buf.y1, buf.attn_out[:, L.o_in_off:], kc, vc, buf.positions, buf.page_table, buf.attn_partial, buf.attn_counters,
             model.heads, model.kv_heads, hd, splits, batch, cfg.rope_dim if cfg.uses_rope else 0, cfg.rope_type, cfg.rope_theta,

@@ -178,109 +178,6 @@ class FusedTpComm(NcclTpComm):
                                           x.stride(0), ops.stream_ptr()), "ll_reduce")
 
     def begin_step(self) -> None:
-        """Issued once at the start of every step (before the first collective)."""
-
-    def step_launches(self) -> int:
-        return 0
-
-    def ar_desc(self, site: int):
-        return None
-
-    def close(self):
-        pass
-
-
-class NcclTpComm(TpCommBase):
-    mode = "nccl"
-
-    def __init__(self, rank, world, device, group=None):
-        super().__init__(rank, world, device)
-        self.group = group
-
-    def all_reduce_sum_(self, t: torch.Tensor) -> None:
-        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
-
-    def select_greedy(self, local_val: torch.Tensor, local_idx: torch.Tensor, out_idx: torch.Tensor, batch: int) -> None:
-        """local (value, global token id) per batch row -> global argmax in ``out_idx``."""
-        pair = torch.stack([local_val[:batch], local_idx[:batch].to(torch.float32)], dim=1).contiguous()
-        allp = torch.empty(self.world, batch, 2, device=self.device, dtype=torch.float32)
-        dist.all_gather_into_tensor(allp, pair, group=self.group)
-        best = allp[:, :, 0].argmax(dim=0)
-        out_idx[:batch] = allp[best, torch.arange(batch, device=self.device), 1].to(torch.int32)
-
-    def gather_logits(self, local_logits: torch.Tensor, vocab: int) -> torch.Tensor:
-        """[batch, vocab_local] on every rank -> [batch, vocab] (rank-major concatenation)."""
-        b, vl = local_logits.shape
-        allp = torch.empty(self.world, b, vl, device=self.device, dtype=local_logits.dtype)
-        dist.all_gather_into_tensor(allp, local_logits.contiguous(), group=self.group)
-        return allp.permute(1, 0, 2).reshape(b, self.world * vl)[:, :vocab].contiguous()
-
-
-class FusedTpComm(NcclTpComm):
-    """In-kernel collectives over symmetric peer memory (NCCL is kept only for set-up and for the
-    non-greedy logits gather)."""
-    mode = "fused"
-
-    def __init__(self, rank, world, device, group=None, spin_limit: int = 20_000_000):
-        super().__init__(rank, world, device, group)
-        self.fused = True
-        self.spin_limit = spin_limit
-        self.buf: Optional[SymmetricBuffer] = None
-        self.epoch = torch.zeros(1, device=self.device, dtype=torch.int32)
-        self.status = torch.zeros(1, device=self.device, dtype=torch.int32)
-        self._sites = []
-        self._cand = None
-
-    def allocate(self, n_sites: int, n: int, max_batch: int, max_ctas: int = 0) -> None:
-        """Reserve symmetric memory for ``n_sites`` all-reduce call sites of ``n`` outputs each and
-        for the candidate exchange of up to ``max_batch`` sequences."""
-        w = self.world
-        n_pad = (n + 3) // 4 * 4
-        self.n, self.max_batch = n_pad, max_batch
-        self._inbox_site = 2 * w * 4 * n_pad * 8           # [parity][rank][4 batch rows][n] pairs of 32-bit words
-        self._off_cand = n_sites * self._inbox_site
-        cand_inbox = 2 * w * max_batch * 2 * 8
-        total = (self._off_cand + cand_inbox + 255) // 256 * 256
-        self.buf = SymmetricBuffer(total, self.rank, w, self.group)
-        self.n_sites = n_sites
-
-    def ar_desc(self, site: int) -> S.GemvAr:
-        if not 0 <= site < self.n_sites:
-            raise IndexError(f"all-reduce site {site} out of range ({self.n_sites} reserved)")
-        ar = S.GemvAr()
-        for r in range(self.world):
-            ar.inbox[r] = self.buf.ptrs[r] + site * self._inbox_site
-        ar.epoch, ar.status = self.epoch.data_ptr(), self.status.data_ptr()
-        ar.spin_limit = self.spin_limit
-        ar.rank, ar.world, ar.enabled, ar.n = self.rank, self.world, 1, self.n
-        return ar
-
-    # -- row-parallel GEMMs of token batches (batched decode, short prompt chunks) -------------------
-    def allocate_gemm(self, n_sites: int, n: int, max_tokens: int) -> None:
-        """Symmetric inboxes for ``n_sites`` GEMM call sites of up to ``max_tokens`` x ``n`` outputs:
-        per site ``[parity 2][rank][max_tokens][n]`` 8-byte {value, epoch} pairs on every rank."""
-        self.g_n = (n + 3) // 4 * 4
-        self.g_rows = max_tokens
-        self._g_site = 2 * self.world * self.g_rows * self.g_n * 8
-        self.g_sites = n_sites
-        self.gbuf = SymmetricBuffer(n_sites * self._g_site, self.rank, self.world, self.group)
-
-    def gemm_ar_fill(self, p: "S.GemmParams", site: int) -> None:
-        """Turn a GEMM launch into "push my partial tile to every rank" for call site ``site``."""
-        if not 0 <= site < self.g_sites:
-            raise IndexError(f"GEMM all-reduce site {site} out of range ({self.g_sites} reserved)")
-        for r in range(self.world):
-            p.ar_inbox[r] = self.gbuf.ptrs[r] + site * self._g_site
-        p.ar_epoch = self.epoch.data_ptr()
-        p.ar_row_pairs, p.ar_rank, p.ar_world, p.ar_rows, p.ar_enabled = self.g_n, self.rank, self.world, self.g_rows, 1
-
-    def ll_reduce(self, site: int, x: torch.Tensor, tokens: int, n: int) -> None:
-        """``x[:tokens, :n] += sum over ranks`` of what the GEMMs of call site ``site`` pushed (bounded polls)."""
-        ops.check(ops.lib().rlz_ll_reduce(self.gbuf.ptrs[self.rank] + site * self._g_site, self.epoch.data_ptr(), self.status.data_ptr(),
-                                          self.spin_limit, self.world, self.g_rows, self.g_n, tokens, n, x.data_ptr(), x.stride(0),
-                                          ops.stream_ptr()), "ll_reduce")
-
-    def begin_step(self) -> None:
         ops.check(ops.lib().rlz_epoch_bump(self.epoch.data_ptr(), ops.stream_ptr()), "epoch_bump")
 
     def step_launches(self) -> int:
