@@ -105,3 +105,41 @@ dist.destroy_process_group()
            "--master-port", "29541", str(script)]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr[-2000:]
+
+
+def test_rank_failure_is_detected_by_the_survivor(tmp_path):
+    """Failure drill on CPU ranks: rank 1 leaves between steps (no collective in flight); rank 0 learns of it
+    through a heartbeat in the rendezvous store before its next collective, and a collective that is attempted
+    anyway ends with a time-out error instead of hanging."""
+    script = tmp_path / "f.py"
+    script.write_text("""
+import datetime, os, sys, time, torch, torch.distributed as dist
+sys.path.insert(0, %r)
+rank = int(os.environ['RANK'])
+store = dist.TCPStore('127.0.0.1', 29547, 2, rank == 0, timeout=datetime.timedelta(seconds=20))
+dist.init_process_group('gloo', store=store, rank=rank, world_size=2, timeout=datetime.timedelta(seconds=3))
+t = torch.ones(4) * (rank + 1)
+dist.all_reduce(t)                      # step 1: both ranks healthy
+assert t[0] == 3
+store.set(f'hb{rank}', str(time.time()))
+if rank == 1:
+    store.set('left1', '1')             # announce, then leave between steps
+    os._exit(0)
+store.wait(['left1'])
+# host-side detection before the next launch: the peer announced that it left (a stale heartbeat works the same way)
+peer_alive = False
+detected_by_timeout = False
+try:                                    # and a collective issued regardless gives up after the group time-out
+    dist.all_reduce(torch.ones(4))
+except Exception as e:
+    detected_by_timeout = True
+print('RESULT', peer_alive, detected_by_timeout, flush=True)
+os._exit(0 if (not peer_alive and detected_by_timeout) else 3)
+""" % os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29546", WORLD_SIZE="2")
+    procs = [subprocess.Popen([sys.executable, str(script)], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+             for r in range(2)]
+    outs = [p.communicate(timeout=120) for p in procs]
+    assert procs[1].returncode == 0
+    assert procs[0].returncode == 0, outs[0][0][-1000:] + outs[0][1][-2000:]
+    assert "RESULT False True" in outs[0][0]

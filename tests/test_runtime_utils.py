@@ -113,3 +113,46 @@ def test_multi_request_policies_and_collector():
     now[0] = 0.006
     assert col.poll() == ["a"]
     assert col.add(1) is None and col.add(2) is None and col.add(3) == [1, 2, 3]
+
+
+def test_observability_primitives():
+    from realizar_b200.utils.observability import ABTest, LatencyHistogram, Span, TraceContext
+    c = TraceContext.new()
+    p = TraceContext.from_traceparent(c.to_traceparent())
+    assert p.trace_id == c.trace_id and p.parent_span_id == c.span_id and p.span_id != c.span_id and p.sampled
+    for bad in ("", "00-abc-def-01", "01-" + "a" * 32 + "-" + "b" * 16 + "-01", "00-" + "0" * 32 + "-" + "b" * 16 + "-01", "00-" + "g" * 32 + "-" + "b" * 16 + "-01"):
+        assert TraceContext.from_traceparent(bad) is None
+    ch = c.child()
+    assert ch.trace_id == c.trace_id and ch.parent_span_id == c.span_id
+    s = Span("decode", c).set("tokens", 5).end()
+    o = s.to_otel()
+    assert o["name"] == "decode" and o["status"]["code"] == "ok" and s.duration_ms >= 0 and o["attributes"][0]["key"] == "tokens"
+    h = LatencyHistogram()
+    for ms in [1] * 50 + [20] * 45 + [400] * 4 + [99999]:
+        h.observe(ms)
+    assert h.percentile(50) == 1 and h.percentile(95) == 25 and h.percentile(99) == 500 and h.percentile(100) == float("inf")
+    text = h.to_prometheus("ttft_seconds")
+    assert 'ttft_seconds_bucket{le="+Inf"} 100' in text and "ttft_seconds_count 100" in text
+    ab = ABTest("sampler", {"a": 1.0, "b": 3.0})
+    picks = [ab.assign(f"user{i}") for i in range(4000)]
+    assert ab.assign("user7") == ab.assign("user7") and 0.20 < picks.count("a") / 4000 < 0.30
+    ab.record("a", 1.0); ab.record("a", 3.0)
+    assert ab.summary()["a"] == {"n": 2, "mean": 2.0}
+
+
+def test_streaming_kv_ring_buffer():
+    from realizar_b200.runtime.streaming_kv import StreamingKVCache, StreamingKVCacheFp16
+    c = StreamingKVCache(1, window=8, kv_heads=1, head_dim=2, sinks=2)
+    for t in range(20):
+        c.append(0, torch.full((1, 2), float(t)), torch.full((1, 2), -float(t)))
+    k, v, pos = c.get(0)
+    assert pos.tolist() == [0, 1, 14, 15, 16, 17, 18, 19] and k[:, 0, 0].tolist() == [0, 1, 14, 15, 16, 17, 18, 19] and v[-1, 0, 0] == -19
+    assert c.valid(0) == 8 and c.length[0] == 20
+    short = StreamingKVCache(2, window=8, kv_heads=1, head_dim=2)
+    for t in range(3):
+        short.append(1, torch.full((1, 2), float(t)), torch.zeros(1, 2))
+    assert short.get(1)[2].tolist() == [0, 1, 2] and short.valid(0) == 0
+    h = StreamingKVCacheFp16(1, 4, 2, 8)
+    assert h.memory_bytes() == 2 * 4 * 2 * 8 * 2
+    with pytest.raises(ValueError):
+        StreamingKVCache(1, 2, 1, 2, sinks=2)
