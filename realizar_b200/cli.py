@@ -29,6 +29,7 @@ def _add_gen_args(p):
     p.add_argument("--gpu", dest="gpu", action="store_true", default=None)
     p.add_argument("--no-gpu", dest="gpu", action="store_false")
     p.add_argument("--max-seq-len", type=int, default=4096)
+    p.add_argument("--kv-dtype", choices=["bf16", "q8"], default="bf16", help="KV cache rows on the GPU engine")
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -43,7 +44,7 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--model", default=None); s.add_argument("--host", default="127.0.0.1"); s.add_argument("--port", type=int, default=8080)
     s.add_argument("--demo", action="store_true"); s.add_argument("--max-batch", type=int, default=4); s.add_argument("--max-seq-len", type=int, default=4096)
     s.add_argument("--gpu", dest="gpu", action="store_true", default=None); s.add_argument("--no-gpu", dest="gpu", action="store_false")
-    s.add_argument("--no-warmup", action="store_true"); s.add_argument("--classical", default=None, help="classical-ML .apr model behind /v1/predict")
+    s.add_argument("--kv-dtype", choices=["bf16", "q8"], default="bf16"); s.add_argument("--no-warmup", action="store_true"); s.add_argument("--classical", default=None, help="classical-ML .apr model behind /v1/predict")
     l = sub.add_parser("list", help="models in the local store"); l.add_argument("--format", choices=["table", "json"], default="table")
     for name in ("pull", "push"):
         q = sub.add_parser(name, help=f"{name} a model ({'needs a network' })"); q.add_argument("model")
@@ -75,7 +76,7 @@ def cmd_run(a) -> int:
     prompt = a.prompt if a.prompt is not None else sys.stdin.read()
     cfg = InferenceConfig(str(resolve_uri(a.model)), prompt=prompt, max_tokens=a.max_tokens, temperature=a.temperature, top_k=a.top_k, top_p=a.top_p,
                           use_gpu=a.gpu, chat=not a.raw, system_prompt=a.system, trace=a.trace is not None,
-                          trace_output=None if a.trace in (None, "-") else a.trace, max_seq_len=a.max_seq_len, verbose=a.verbose)
+                          trace_output=None if a.trace in (None, "-") else a.trace, max_seq_len=a.max_seq_len, verbose=a.verbose, kv_dtype=a.kv_dtype)
     r = run_inference(cfg)
     if a.format == "json":
         print(json.dumps({"text": r.text, "tokens_generated": r.generated_token_count, "input_tokens": r.input_token_count, "inference_ms": r.inference_ms,
@@ -110,7 +111,7 @@ def cmd_chat(a, stdin=None, stdout=None) -> int:
     from .runtime.registry import resolve_uri
     from .serving.chat_template import ChatMessage
     stdin, stdout = stdin or sys.stdin, stdout or sys.stdout
-    llm = LLM(str(resolve_uri(a.model)), a.gpu, a.max_seq_len, max_batch=1)
+    llm = LLM(str(resolve_uri(a.model)), a.gpu, a.max_seq_len, max_batch=1, kv_dtype=a.kv_dtype)
     history: list = [ChatMessage.system(a.system)] if a.system else []
     print(f"model {llm.path.name} ({llm.format}, {'gpu' if llm.used_gpu else 'cpu'}); /exit to quit, /clear to reset", file=stdout)
     while True:
@@ -141,7 +142,7 @@ def cmd_chat(a, stdin=None, stdout=None) -> int:
     return 0
 
 
-def build_app_state(model: Optional[str], use_gpu: Optional[bool], max_batch: int, max_seq_len: int, warmup: bool = True):
+def build_app_state(model: Optional[str], use_gpu: Optional[bool], max_batch: int, max_seq_len: int, warmup: bool = True, kv_dtype: str = "bf16"):
     """Load a model and wire engine -> continuous-batching loop -> API state."""
     import torch
     from .formats.detect import load_model
@@ -170,7 +171,7 @@ def build_app_state(model: Optional[str], use_gpu: Optional[bool], max_batch: in
     msl = min(max_seq_len, w.config.context_length)
     if gpu:
         from .runtime.engine import DecodeEngine, EngineConfig
-        eng = DecodeEngine(w, EngineConfig(max_batch=max_batch, max_seq_len=msl))
+        eng = DecodeEngine(w, EngineConfig(max_batch=max_batch, max_seq_len=msl, kv_dtype=kv_dtype))
     else:
         from .runtime.cpu_engine import CpuEngineConfig, CpuSlotEngine
         eng = CpuSlotEngine(w, CpuEngineConfig(max_batch=min(max_batch, 2), max_seq_len=msl))
@@ -186,7 +187,7 @@ def build_app_state(model: Optional[str], use_gpu: Optional[bool], max_batch: in
 
 def cmd_serve(a) -> int:
     from .serving.api import serve
-    st = build_app_state(None if a.demo else a.model, a.gpu, a.max_batch, a.max_seq_len, warmup=not a.no_warmup)
+    st = build_app_state(None if a.demo else a.model, a.gpu, a.max_batch, a.max_seq_len, warmup=not a.no_warmup, kv_dtype=a.kv_dtype)
     if a.classical:
         from .serving.classical import ClassicalModel, ClassicalServeState
         data = Path(a.classical).read_bytes()

@@ -37,7 +37,7 @@ enum { MERGE_GLOBAL = 0, MERGE_CLUSTER = 1, MERGE_NONE = 2 };
 struct AttnDecodeParams {
   const float* qkv;        // [B, ld_qkv]: q heads | k heads | v heads (after bias)
   float* out;              // [B, ld_out]: attention output, head-major
-  __nv_bfloat16* k_cache;
+  __nv_bfloat16* k_cache;     // bf16 rows, or int8 rows when kv_q8 (see below)
   __nv_bfloat16* v_cache;
   const int32_t* positions;   // [B]
   const int32_t* page_table;  // [B, max_pages]
@@ -55,7 +55,24 @@ struct AttnDecodeParams {
   int32_t window;                      // > 0: attend to positions (pos - window, pos] only
   int32_t rope_table_len;              // positions covered by rope_table
   const float2* rope_table;            // [rope_table_len, rope_dim / 2] (cos, sin) or null
+  int32_t kv_q8;                       // 1: int8 cache rows of head_dim + 16 bytes (codes, then the fp32 scale of the row)
+  int32_t _pad3;
 };
+
+// ---- int8 KV rows: [head_dim codes][fp32 scale][12 bytes padding]; value = code * scale, scale = max|x| / 127 per (token, kv head) ----
+__device__ __forceinline__ int kv_row_bytes(int d, int q8) { return q8 ? d + 16 : 2 * d; }
+// four codes of a word -> floats: the biased byte goes into the mantissa of 2^23, one FMA applies scale and removes the bias
+__device__ __forceinline__ void q8_word_to_float(uint32_t w, float sc, float* out) {
+  const uint32_t b = w ^ 0x80808080u;
+  const float off = -(8388608.f + 128.f) * sc;
+  out[0] = fmaf(__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7540)), sc, off);
+  out[1] = fmaf(__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7541)), sc, off);
+  out[2] = fmaf(__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7542)), sc, off);
+  out[3] = fmaf(__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7543)), sc, off);
+}
+__device__ __forceinline__ float q8_round(float x, float sc) {      // what the cache will return for x
+  return sc > 0.f ? fminf(127.f, fmaxf(-127.f, rintf(x / sc))) * sc : 0.f;
+}
 
 __device__ __forceinline__ void rope_inplace(float* v, int d_rot, int rope_type, int pos, float theta, const float2* table, int tid, int nthreads) {
   const int half = d_rot >> 1;
@@ -91,6 +108,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
   __shared__ float part_s[ATT_WARPS][GT][128 + 2];   // per-warp partials
   __shared__ float res_s[GT][128 + 2];      // this CTA's split result (read by cluster rank 0 in MERGE_CLUSTER)
   __shared__ int32_t pt_s[ATT_PT_MAX];      // physical pages of this split's token range
+  __shared__ float qs_s[2][ATT_THREADS / 32 + 1];   // int8 cache: max|k|, max|v| of the new row (per warp, then total)
   __shared__ int last_flag;
 
   pdl_launch_dependents();
@@ -141,12 +159,39 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
     if (owner) rope_inplace(k_s, p.rope_dim, p.rope_type, pos, p.rope_theta, tab, tid, ATT_THREADS);
     __syncthreads();
   }
+  const int q8 = p.kv_q8;
+  const int64_t rowb = kv_row_bytes(d, q8);              // bytes per cached row
+  float sck = 0.f, scv = 0.f;                            // int8 cache: scales of the new row
+  if (q8 && owner) {
+    float ak = 0.f, av = 0.f;
+    for (int j = tid; j < d; j += ATT_THREADS) { ak = fmaxf(ak, fabsf(k_s[j])); av = fmaxf(av, fabsf(v_s[j])); }
+    ak = warp_max(ak); av = warp_max(av);
+    if (lane == 0) { qs_s[0][warp] = ak; qs_s[1][warp] = av; }
+  }
+  if (q8) {
+    __syncthreads();
+    if (owner) {
+      for (int w = 0; w < ATT_THREADS / 32; ++w) { sck = fmaxf(sck, qs_s[0][w]); scv = fmaxf(scv, qs_s[1][w]); }
+      sck *= 1.f / 127.f; scv *= 1.f / 127.f;
+    }
+  }
   if (owner && hg == 0) {   // append the new row to the cache (one head group does it)
     const int page = pt[pos / ATT_PAGE], slot = pos % ATT_PAGE;
-    const int64_t off = (((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE + slot) * d;
-    for (int j = tid; j < d; j += ATT_THREADS) {
-      p.k_cache[off + j] = __float2bfloat16_rn(k_s[j]);
-      p.v_cache[off + j] = __float2bfloat16_rn(v_s[j]);
+    const int64_t rowi = ((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE + slot;
+    if (q8) {
+      int8_t* kd = (int8_t*)p.k_cache + rowi * rowb;
+      int8_t* vd = (int8_t*)p.v_cache + rowi * rowb;
+      for (int j = tid; j < d; j += ATT_THREADS) {
+        kd[j] = (int8_t)(sck > 0.f ? fminf(127.f, fmaxf(-127.f, rintf(k_s[j] / sck))) : 0.f);
+        vd[j] = (int8_t)(scv > 0.f ? fminf(127.f, fmaxf(-127.f, rintf(v_s[j] / scv))) : 0.f);
+      }
+      if (tid == 0) { *(float*)(kd + d) = sck; *(float*)(vd + d) = scv; }
+    } else {
+      const int64_t off = rowi * d;
+      for (int j = tid; j < d; j += ATT_THREADS) {
+        p.k_cache[off + j] = __float2bfloat16_rn(k_s[j]);
+        p.v_cache[off + j] = __float2bfloat16_rn(v_s[j]);
+      }
     }
   }
   __syncthreads();
@@ -184,21 +229,36 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
       const bool okl = lane_ok && tok < end && !(new_from_smem && tok == pos);
       const int tk = min(tok, end - 1 > start ? end - 1 : start);
       const int page = pt_staged ? pt_s[(tk - start) / ATT_PAGE] : pt[tk / ATT_PAGE];
-      const int64_t off = (((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE + (tk % ATT_PAGE)) * d + j0;
-      kr[t] = okl ? *(const uint4*)(p.k_cache + off) : make_uint4(0, 0, 0, 0);
-      vr[t] = okl ? *(const uint4*)(p.v_cache + off) : make_uint4(0, 0, 0, 0);
+      const int64_t rowi = ((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE + (tk % ATT_PAGE);
+      if (q8) {                                           // 8 codes (x, y) and the row scale (z)
+        const uint8_t* kp = (const uint8_t*)p.k_cache + rowi * rowb;
+        const uint8_t* vp = (const uint8_t*)p.v_cache + rowi * rowb;
+        const uint2 kc = okl ? *(const uint2*)(kp + j0) : make_uint2(0x80808080u ^ 0x80808080u, 0);
+        const uint2 vc = okl ? *(const uint2*)(vp + j0) : make_uint2(0, 0);
+        kr[t] = make_uint4(kc.x, kc.y, okl ? *(const uint32_t*)(kp + d) : 0u, 0u);
+        vr[t] = make_uint4(vc.x, vc.y, okl ? *(const uint32_t*)(vp + d) : 0u, 0u);
+      } else {
+        const int64_t off = rowi * d + j0;
+        kr[t] = okl ? *(const uint4*)(p.k_cache + off) : make_uint4(0, 0, 0, 0);
+        vr[t] = okl ? *(const uint4*)(p.v_cache + off) : make_uint4(0, 0, 0, 0);
+      }
     }
     float sc[GT][TB];
     // pass 1: scores (K converted one token at a time)
 #pragma unroll
     for (int t = 0; t < TB; ++t) {
       float kf[8];
-      const uint32_t kw[4] = {kr[t].x, kr[t].y, kr[t].z, kr[t].w};
+      if (q8) {
+        const float sc = __uint_as_float(kr[t].z);
+        q8_word_to_float(kr[t].x, sc, kf); q8_word_to_float(kr[t].y, sc, kf + 4);
+      } else {
+        const uint32_t kw[4] = {kr[t].x, kr[t].y, kr[t].z, kr[t].w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j) { kf[2 * j] = __uint_as_float(kw[j] << 16); kf[2 * j + 1] = __uint_as_float(kw[j] & 0xFFFF0000u); }
-      if (new_from_smem && base + t == pos && lane_ok) {   // new row straight from shared memory (bf16-rounded like the cache)
+        for (int j = 0; j < 4; ++j) { kf[2 * j] = __uint_as_float(kw[j] << 16); kf[2 * j + 1] = __uint_as_float(kw[j] & 0xFFFF0000u); }
+      }
+      if (new_from_smem && base + t == pos && lane_ok) {   // new row straight from shared memory (rounded like the cache)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) kf[j] = __bfloat162float(__float2bfloat16_rn(k_s[j0 + j]));
+        for (int j = 0; j < 8; ++j) kf[j] = q8 ? q8_round(k_s[j0 + j], sck) : __bfloat162float(__float2bfloat16_rn(k_s[j0 + j]));
       }
       const bool valid = base + t < end && base + t >= lo;
 #pragma unroll
@@ -232,12 +292,17 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
 #pragma unroll
     for (int t = 0; t < TB; ++t) {
       float vf[8];
-      const uint32_t vw[4] = {vr[t].x, vr[t].y, vr[t].z, vr[t].w};
+      if (q8) {
+        const float sc = __uint_as_float(vr[t].z);
+        q8_word_to_float(vr[t].x, sc, vf); q8_word_to_float(vr[t].y, sc, vf + 4);
+      } else {
+        const uint32_t vw[4] = {vr[t].x, vr[t].y, vr[t].z, vr[t].w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j) { vf[2 * j] = __uint_as_float(vw[j] << 16); vf[2 * j + 1] = __uint_as_float(vw[j] & 0xFFFF0000u); }
+        for (int j = 0; j < 4; ++j) { vf[2 * j] = __uint_as_float(vw[j] << 16); vf[2 * j + 1] = __uint_as_float(vw[j] & 0xFFFF0000u); }
+      }
       if (new_from_smem && base + t == pos && lane_ok) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) vf[j] = __bfloat162float(__float2bfloat16_rn(v_s[j0 + j]));
+        for (int j = 0; j < 8; ++j) vf[j] = q8 ? q8_round(v_s[j0 + j], scv) : __bfloat162float(__float2bfloat16_rn(v_s[j0 + j]));
       }
 #pragma unroll
       for (int g = 0; g < GT; ++g)

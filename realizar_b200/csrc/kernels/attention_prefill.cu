@@ -35,7 +35,7 @@ struct AttnPrefillParams {
   int64_t ld_qkv, ld_out;
   int32_t n_heads, n_kv_heads, head_dim, q_off;
   int32_t n_tokens, pos0;      // chunk rows are positions pos0 .. pos0 + n_tokens - 1
-  int32_t window, _pad;
+  int32_t window, kv_q8;       // kv_q8: int8 cache rows of head_dim + 16 bytes (codes, then the fp32 row scale)
   float scale;
 };
 
@@ -104,17 +104,32 @@ __global__ void __launch_bounds__(FP_THREADS) attn_prefill_tcgen05_kernel(const 
     // ---- K tile: key k0 + tid ------------------------------------------------------------------
     const int key = k0 + tid;
     const bool kvalid = key < ctx;
-    const int64_t cbase = (((int64_t)p.page_table[min(key, ctx - 1) / FP_PAGE] * p.n_kv_heads + kvh) * FP_PAGE + (min(key, ctx - 1) % FP_PAGE)) * D;
+    const int64_t crow = ((int64_t)p.page_table[min(key, ctx - 1) / FP_PAGE] * p.n_kv_heads + kvh) * FP_PAGE + (min(key, ctx - 1) % FP_PAGE);
+    const int64_t cbase = crow * D;                       // bf16 rows; int8 rows are D + 16 bytes
+    const uint8_t* k8 = (const uint8_t*)p.k_cache + crow * (D + 16);
+    const uint8_t* v8 = (const uint8_t*)p.v_cache + crow * (D + 16);
     {
       const uint4* src = (const uint4*)(p.k_cache + cbase);
+      const float ksc = (p.kv_q8 && kvalid) ? *(const float*)(k8 + D) : 0.f;
 #pragma unroll
       for (int s = 0; s < NSLAB; ++s) {
         uint32_t v[32];
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           const int j = 64 * s + 8 * c;
-          const uint4 t = (j < D && kvalid) ? __ldg(src + (j >> 3)) : make_uint4(0, 0, 0, 0);
-          v[4 * c] = t.x; v[4 * c + 1] = t.y; v[4 * c + 2] = t.z; v[4 * c + 3] = t.w;
+          if (p.kv_q8) {                                  // 8 codes -> 8 bf16
+            const uint2 cw = (j < D && kvalid) ? __ldg((const uint2*)(k8 + j)) : make_uint2(0, 0);
+            const uint32_t w2[2] = {cw.x, cw.y};
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const float f0 = ksc * (float)(int8_t)(w2[h] & 0xFF), f1 = ksc * (float)(int8_t)((w2[h] >> 8) & 0xFF);
+              const float f2 = ksc * (float)(int8_t)((w2[h] >> 16) & 0xFF), f3 = ksc * (float)(int8_t)(w2[h] >> 24);
+              v[4 * c + 2 * h] = pack_bf16(f0, f1); v[4 * c + 2 * h + 1] = pack_bf16(f2, f3);
+            }
+          } else {
+            const uint4 t = (j < D && kvalid) ? __ldg(src + (j >> 3)) : make_uint4(0, 0, 0, 0);
+            v[4 * c] = t.x; v[4 * c + 1] = t.y; v[4 * c + 2] = t.z; v[4 * c + 3] = t.w;
+          }
         }
         store_row_sw128(KVs + s * FP_SLAB, tid, v);
       }
@@ -142,10 +157,22 @@ __global__ void __launch_bounds__(FP_THREADS) attn_prefill_tcgen05_kernel(const 
       const int slab = tid >> 6, kc = tid & 63;           // key column inside the slab
       uint8_t* vb = KVs + slab * FP_SLAB + (kc & 7) * 2;
       const int chunk = kc >> 3;
+      const float vsc = (p.kv_q8 && kvalid) ? *(const float*)(v8 + D) : 0.f;
 #pragma unroll
       for (int c = 0; c < D / 8; ++c) {
-        const uint4 t = kvalid ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
-        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+        uint32_t w[4];
+        if (p.kv_q8) {
+          const uint2 cw = kvalid ? __ldg((const uint2*)(v8 + 8 * c)) : make_uint2(0, 0);
+          const uint32_t w2[2] = {cw.x, cw.y};
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            w[2 * h] = pack_bf16(vsc * (float)(int8_t)(w2[h] & 0xFF), vsc * (float)(int8_t)((w2[h] >> 8) & 0xFF));
+            w[2 * h + 1] = pack_bf16(vsc * (float)(int8_t)((w2[h] >> 16) & 0xFF), vsc * (float)(int8_t)(w2[h] >> 24));
+          }
+        } else {
+          const uint4 t = kvalid ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
+          w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
+        }
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int j = 8 * c + e;                        // row of V^T

@@ -150,6 +150,29 @@ __global__ void kv_append_kernel(const float* k, const float* v, int64_t ld, __n
   }
 }
 
+// int8 cache rows (head_dim codes, then the fp32 scale max|x| / 127 of the row): one warp per (token, kv head) and tensor
+__global__ void kv_append_q8_kernel(const float* k, const float* v, int64_t ld, uint8_t* k_cache, uint8_t* v_cache, const int32_t* positions,
+                                    const int32_t* page_rows, int n_kv_heads, int d, int page) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int pos = positions[t];
+  if (pos < 0) return;
+  const int pg = page_rows[t], slot = pos % page;
+  const int rowb = d + 16;
+  for (int job = warp; job < 2 * n_kv_heads; job += nw) {
+    const int h = job >> 1;
+    const float* src = (job & 1 ? v : k) + (int64_t)t * ld + h * d;
+    uint8_t* dst = (job & 1 ? v_cache : k_cache) + (((int64_t)pg * n_kv_heads + h) * page + slot) * rowb;
+    float amax = 0.f;
+    for (int j = lane; j < d; j += 32) amax = fmaxf(amax, fabsf(src[j]));
+    amax = warp_max(amax);
+    const float sc = amax * (1.f / 127.f);
+    for (int j = lane; j < d; j += 32) ((int8_t*)dst)[j] = (int8_t)(sc > 0.f ? fminf(127.f, fmaxf(-127.f, rintf(src[j] / sc))) : 0.f);
+    if (lane == 0) *(float*)(dst + d) = sc;
+  }
+}
+
 // physical page of each row's current position (rows with position < 0 are idle)
 __global__ void page_rows_kernel(const int32_t* page_table, int64_t ld, const int32_t* positions, int32_t* out, int n, int page) {
   pdl_launch_dependents();
@@ -276,6 +299,12 @@ int rlz_elementwise(const float* a, const float* b, const float* bias, const flo
   int grid = (int)((total + 255) / 256); if (grid > 148 * 8) grid = 148 * 8; if (grid < 1) grid = 1;
   return (int)launch(elementwise_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, a, b, bias, residual, y, (int64_t)rows, cols,
                      (int64_t)ld_a, (int64_t)ld_b, (int64_t)ld_y, act, mul);
+}
+
+int rlz_kv_append_q8(const float* k, const float* v, long long ld, void* k_cache, void* v_cache, const int32_t* positions,
+                     const int32_t* page_rows, int n_tokens, int n_kv_heads, int d, int page, void* stream) {
+  return (int)launch(kv_append_q8_kernel, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, k, v, (int64_t)ld, (uint8_t*)k_cache,
+                     (uint8_t*)v_cache, positions, page_rows, n_kv_heads, d, page);
 }
 
 int rlz_kv_append(const float* k, const float* v, long long ld, void* k_cache, void* v_cache, const int32_t* positions,

@@ -34,6 +34,7 @@ class InferenceConfig:
     trace_output: Optional[str] = None
     max_seq_len: int = 2048
     verbose: bool = False
+    kv_dtype: str = "bf16"                 # "q8": int8 KV cache on the GPU engine
 
     def with_prompt(self, p): self.prompt = p; return self
     def with_max_tokens(self, n): self.max_tokens = n; return self
@@ -89,7 +90,7 @@ def build_template(w: ModelWeights, model_name: str = "") -> ChatTemplate:
 class LLM:
     """A loaded model with tokenizer, chat template and a generation backend."""
 
-    def __init__(self, model_path: str, use_gpu: Optional[bool] = None, max_seq_len: int = 2048, max_batch: int = 4):
+    def __init__(self, model_path: str, use_gpu: Optional[bool] = None, max_seq_len: int = 2048, max_batch: int = 4, kv_dtype: str = "bf16"):
         import torch
         t0 = time.perf_counter()
         self.path = validate_model_path(model_path)
@@ -102,7 +103,7 @@ class LLM:
         self.max_seq_len = min(max_seq_len, self.cfg.context_length)
         if self.used_gpu:
             from .runtime.engine import DecodeEngine, EngineConfig
-            self.engine = DecodeEngine(self.weights, EngineConfig(max_batch=max_batch, max_seq_len=self.max_seq_len))
+            self.engine = DecodeEngine(self.weights, EngineConfig(max_batch=max_batch, max_seq_len=self.max_seq_len, kv_dtype=kv_dtype))
             self.cpu = None
         else:
             from .models.cpu_model import CpuModel
@@ -165,7 +166,7 @@ class LLM:
 def run_inference(config: InferenceConfig) -> InferenceResult:
     tracer = InferenceTracer(enabled=config.trace)
     tracer.enter("LOAD", path=str(config.model_path))
-    llm = LLM(config.model_path, config.use_gpu, config.max_seq_len, max_batch=1)
+    llm = LLM(config.model_path, config.use_gpu, config.max_seq_len, max_batch=1, kv_dtype=config.kv_dtype)
     tracer.exit("LOAD", format=llm.format, load_ms=llm.load_ms)
     tracer.enter("TOKENIZE")
     if config.input_tokens is not None:

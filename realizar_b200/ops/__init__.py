@@ -222,6 +222,7 @@ def build_attn_decode_params(qkv, out, k_cache, v_cache, positions, page_table, 
     p.pt_stride = 0 if shared_table else (page_table.stride(0) if page_table.dim() > 1 else page_table.shape[-1])
     p.no_append = 1 if no_append else 0
     p.window = int(window or 0)
+    p.kv_q8 = 1 if k_cache.dtype in (torch.uint8, torch.int8) else 0
     if rope_table is not None:
         if rope_table.dtype != torch.float32 or rope_table.dim() != 3 or rope_table.shape[1] != rope_dim // 2 or rope_table.shape[2] != 2 or not rope_table.is_contiguous():
             raise ValueError("rope_table must be a contiguous float32 [positions, rope_dim / 2, 2] (cos, sin) tensor")
@@ -253,11 +254,31 @@ def attn_prefill(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_
     p.ld_qkv, p.ld_out = qkv.stride(0), out.stride(0)
     p.n_heads, p.n_kv_heads, p.head_dim, p.q_off = n_heads, n_kv_heads, head_dim, q_off
     p.n_tokens, p.pos0, p.window, p.scale = int(n_tokens), int(pos0), int(window or 0), head_dim ** -0.5
+    p.kv_q8 = 1 if k_cache.dtype in (torch.uint8, torch.int8) else 0
     check(lib().rlz_attn_prefill(ctypes.byref(p), stream_ptr()), "attn_prefill")
 
 
 def attn_prefill_error(clear: bool = True) -> int:
     return int(lib().rlz_attn_prefill_error(1 if clear else 0))
+
+
+def kv_cache_alloc(layers: int, pages: int, kv_heads: int, head_dim: int, device, dtype: str = "bf16", page: int = 16) -> torch.Tensor:
+    """``[2 (k, v), layers, pages, kv_heads, page, row]``: bf16 rows of ``head_dim``, or with ``dtype="q8"`` uint8 rows of
+    ``head_dim + 16`` bytes (int8 codes, the fp32 scale of the row, padding)."""
+    if dtype == "q8":
+        return torch.zeros(2, layers, pages, kv_heads, page, head_dim + 16, device=device, dtype=torch.uint8)
+    if dtype != "bf16":
+        raise ValueError(f"unknown KV cache dtype '{dtype}' (bf16 | q8)")
+    return torch.zeros(2, layers, pages, kv_heads, page, head_dim, device=device, dtype=torch.bfloat16)
+
+
+def kv_rows_to_float(cache: torch.Tensor, head_dim: int) -> torch.Tensor:
+    """Decode cache rows ``[..., row]`` (either layout) to fp32 ``[..., head_dim]`` (tests, snapshots, debugging)."""
+    if cache.dtype == torch.bfloat16:
+        return cache.float()
+    codes = cache[..., :head_dim].contiguous().view(torch.int8).float()
+    scale = cache[..., head_dim:head_dim + 4].contiguous().view(torch.float32)
+    return codes * scale
 
 
 # ------------------------------------------------------------------------------ small ops --
@@ -319,7 +340,9 @@ def swiglu_bf16(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor, act=ACT
 
 
 def kv_append(k, v, k_cache, v_cache, positions, page_rows, n_kv_heads, d, page=16) -> None:
-    check(lib().rlz_kv_append(k.data_ptr(), v.data_ptr(), k.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(),
+    """Write the rows of ``k`` / ``v`` at their positions into the paged cache (bf16 rows, or int8 rows with a per-row scale)."""
+    fn = lib().rlz_kv_append_q8 if k_cache.dtype in (torch.uint8, torch.int8) else lib().rlz_kv_append
+    check(fn(k.data_ptr(), v.data_ptr(), k.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(),
                               page_rows.data_ptr(), k.shape[0], n_kv_heads, d, page, stream_ptr()), "kv_append")
 
 

@@ -54,13 +54,13 @@ class AttnDecodeParams(Structure):
                 ("head_dim", c_int32), ("max_pages", c_int32), ("rope_dim", c_int32), ("rope_type", c_int32), ("splits", c_int32),
                 ("batch", c_int32), ("q_off", c_int32), ("k_off", c_int32), ("v_off", c_int32), ("pt_stride", c_int32),
                 ("rope_theta", c_float), ("eps", c_float), ("scale", c_float), ("no_append", c_int32), ("window", c_int32),
-                ("rope_table_len", c_int32), ("rope_table", c_void_p)]
+                ("rope_table_len", c_int32), ("rope_table", c_void_p), ("kv_q8", c_int32), ("_pad3", c_int32)]
 
 
 class AttnPrefillParams(Structure):
     _fields_ = [("qkv", c_void_p), ("out", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p), ("page_table", c_void_p),
                 ("ld_qkv", c_int64), ("ld_out", c_int64), ("n_heads", c_int32), ("n_kv_heads", c_int32), ("head_dim", c_int32),
-                ("q_off", c_int32), ("n_tokens", c_int32), ("pos0", c_int32), ("window", c_int32), ("_pad", c_int32), ("scale", c_float)]
+                ("q_off", c_int32), ("n_tokens", c_int32), ("pos0", c_int32), ("window", c_int32), ("kv_q8", c_int32), ("scale", c_float)]
 
 
 class SampleParams(Structure):
@@ -106,6 +106,7 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_elementwise.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_longlong,
                                     c_longlong, c_int, c_int, c_void_p]
     lib.rlz_kv_append.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+    lib.rlz_kv_append_q8.argtypes = lib.rlz_kv_append.argtypes
     lib.rlz_to_bf16.argtypes = [c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_longlong, c_void_p]
     lib.rlz_norm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_float, c_void_p]
     lib.rlz_swiglu_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_longlong, c_longlong, c_int, c_void_p]

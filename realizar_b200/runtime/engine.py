@@ -45,6 +45,7 @@ class EngineConfig:
     gemm_decode_min_batch: int = 16        # decode batches at least this large run on the tensor-core GEMM path
     prefix_cache: bool = False             # share full KV pages between prompts with a common prefix
     parity_gate: bool = False              # at load: GPU vs CPU logits on the BOS token must agree (cosine >= 0.99)
+    kv_dtype: str = "bf16"                 # "q8": int8 KV rows with a per-(token, head) scale (half the cache memory)
     batch_buckets: Sequence[int] = ()      # graph buckets; default powers of two up to max_batch
     seed: int = 0
 
@@ -87,7 +88,7 @@ class DecodeEngine:
         self.num_pages = c.num_pages or B * self.max_pages_per_seq
         hd = self.mcfg.head_dim
         # [2 (k,v), layers, pages, kv_heads, PAGE, head_dim] bf16
-        self.kv = torch.zeros(2, self.mcfg.num_layers, self.num_pages, m.kv_heads, PAGE, hd, device=dev, dtype=torch.bfloat16)
+        self.kv = ops.kv_cache_alloc(self.mcfg.num_layers, self.num_pages, m.kv_heads, hd, dev, c.kv_dtype, PAGE)
         self.pages = PagedKvCache(self.num_pages, PAGE)
         self.splits = c.attn_splits or self._choose_splits(B)
         qkv_w = m.q_dim + 2 * m.kv_dim
@@ -513,5 +514,5 @@ class DecodeEngine:
         return self.buf.logits[slot, : self.mcfg.vocab_size].clone()
 
     def memory_report(self) -> dict:
-        return {"weights_bytes": self.model.weight_bytes(), "kv_bytes": self.kv.numel() * 2, "kv_pages": self.num_pages,
+        return {"weights_bytes": self.model.weight_bytes(), "kv_bytes": self.kv.numel() * self.kv.element_size(), "kv_pages": self.num_pages,
                 "kv_utilization": self.pages.stats().utilization}

@@ -233,3 +233,28 @@ def test_kv_snapshot_restore(cuda_device):
     b = [int(eng.feed({1: nxt})[1])]
     b.append(int(eng.feed({1: b[-1]})[1]))
     assert snap["position"] == 37 and snap["pages"] == 3 and a == b
+
+
+def test_engine_int8_kv_cache_tracks_bf16(cuda_device):
+    """Decode and tensor-core prefill over the int8 KV cache stay close to the bf16 cache (same tokens early on,
+    logits cosine > 0.995) and the cache takes (d + 16) / 2d of the memory."""
+    from realizar_b200.models.weights import synthetic_weights
+    from realizar_b200.runtime.engine import DecodeEngine, EngineConfig
+    cfg = _kq_llama()
+    w = synthetic_weights(cfg, seed=21, std=0.05)
+    toks = [int(t) for t in np.random.default_rng(8).integers(0, cfg.vocab_size, 90)]
+    res = {}
+    for kd in ("bf16", "q8"):
+        eng = DecodeEngine(w, EngineConfig(max_batch=2, max_seq_len=160, greedy_only=True, kv_dtype=kd, prefill_chunk=64))
+        eng.open_slot(0, 128)
+        nxt = eng.prefill(0, toks)                            # flash prefill over the cache (two chunks)
+        logits = [eng.logits_of_last_step(0).float().cpu().numpy()]
+        out = [nxt]
+        for _ in range(6):
+            out.append(int(eng.feed({0: out[-1]})[0]))
+            logits.append(eng.logits_of_last_step(0).float().cpu().numpy())
+        res[kd] = (out, logits, eng.memory_report()["kv_bytes"])
+    assert res["q8"][2] * 2 * 64 == res["bf16"][2] * (64 + 16)
+    for a, b in zip(res["bf16"][1][:3], res["q8"][1][:3]):
+        assert _cos(a, b) > 0.995
+    assert res["bf16"][0][:2] == res["q8"][0][:2]

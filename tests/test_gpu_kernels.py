@@ -296,3 +296,44 @@ def test_argmax_sliced_rows(cuda_device):
     neg = -torch.rand(1, 20000, device="cuda") - 1.0                                       # all-negative rows decode correctly too
     v = torch.empty(1, device="cuda")
     assert int(ops.argmax(neg, out_val=v)) == int(neg.argmax()) and torch.allclose(v, neg.max(-1).values)
+
+
+@pytest.mark.parametrize("H,Hkv,d,splits", [(8, 8, 80, 4), (14, 2, 64, 2), (16, 2, 128, 1)])
+def test_attn_decode_int8_kv(cuda_device, H, Hkv, d, splits):
+    """int8 cache rows (codes + per-row scale): the kernel matches fp32 attention over the dequantised rows,
+    and the row it appends dequantises back to the new k / v within one quantisation step."""
+    from realizar_b200 import ops
+    torch.manual_seed(H + d)
+    B, pages_per_seq, ctx = 2, 8, 45
+    n_pages = B * pages_per_seq
+    kv = ops.kv_cache_alloc(1, n_pages, Hkv, d, "cuda", "q8")
+    kc, vc = kv[0, 0], kv[1, 0]
+    page_table = torch.arange(n_pages, device="cuda", dtype=torch.int32).reshape(B, pages_per_seq).flip(1).contiguous()
+    lens = [ctx, 20]
+    hist_k = [torch.randn(L - 1, Hkv, d, device="cuda") for L in lens]
+    hist_v = [torch.randn(L - 1, Hkv, d, device="cuda") for L in lens]
+    for b in range(B):          # history goes in through the append kernel (no RoPE in this test)
+        L = lens[b] - 1
+        pos = torch.arange(L, device="cuda", dtype=torch.int32)
+        rows = page_table[b, (pos // 16).long()].contiguous()
+        ops.kv_append(hist_k[b].reshape(L, -1).contiguous(), hist_v[b].reshape(L, -1).contiguous(), kc, vc, pos, rows, Hkv, d)
+    qkv = torch.randn(B, (H + 2 * Hkv) * d, device="cuda")
+    positions = torch.tensor([L - 1 for L in lens], device="cuda", dtype=torch.int32)
+    out = torch.zeros(B, H * d, device="cuda")
+    partial, counters = ops.attn_decode_scratch(B, H, splits, d, "cuda")
+    p = ops.build_attn_decode_params(qkv, out, kc, vc, positions, page_table, partial, counters, H, Hkv, d, splits, B, 0, 0, 10000.0, 0, H * d, (H + Hkv) * d)
+    assert p.kv_q8 == 1
+    ops.attn_decode_launch(p)
+    torch.cuda.synchronize()
+    for b in range(B):
+        L = lens[b]
+        pages = page_table[b, : (L + 15) // 16].long()
+        k_all = ops.kv_rows_to_float(kc[pages], d).permute(0, 2, 1, 3).reshape(-1, Hkv, d)[:L]      # [tokens, Hkv, d]
+        v_all = ops.kv_rows_to_float(vc[pages], d).permute(0, 2, 1, 3).reshape(-1, Hkv, d)[:L]
+        row = qkv[b]
+        kn, vn = row[H * d:(H + Hkv) * d].reshape(Hkv, d), row[(H + Hkv) * d:].reshape(Hkv, d)
+        step = kn.abs().amax(-1, keepdim=True) / 127
+        assert float((k_all[L - 1] - kn).abs().max()) <= float(step.max()) * 0.51 + 1e-6      # appended row: within half a step
+        assert float((k_all[: L - 1] - hist_k[b]).abs().max()) <= float(hist_k[b].abs().amax(-1).max()) / 127 * 0.51 + 1e-6
+        ref = _ref_attention(row[: H * d].reshape(H, d).cpu(), k_all.cpu(), v_all.cpu(), d ** -0.5).reshape(-1)
+        assert _rel(out[b], ref) < 5e-3, (b, _rel(out[b], ref))
