@@ -151,8 +151,9 @@ def main():
     prompts = torch.randint(0, cfg.vocab_size, (B, args.prompt_len), generator=g)
     for b in range(B):
         eng.open_slot(b, max_seq)
-    # warm the prefill path once on a scratch slot-0 sequence (kernel attributes, allocator), then time TTFT
-    eng.prefill(0, [int(t) for t in prompts[0, :64]])
+    # warm the prefill path once with a full-length scratch prompt in slot 0 (kernel attributes, allocator, and the
+    # first NCCL collective of that message size under tensor parallelism), then time TTFT
+    eng.prefill(0, [int(t) for t in torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g)])
     eng.close_slot(0)
     eng.open_slot(0, max_seq)
     sync_all()

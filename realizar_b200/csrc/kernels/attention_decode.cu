@@ -61,14 +61,13 @@ struct AttnDecodeParams {
 
 // ---- int8 KV rows: [head_dim codes][fp32 scale][12 bytes padding]; value = code * scale, scale = max|x| / 127 per (token, kv head) ----
 __device__ __forceinline__ int kv_row_bytes(int d, int q8) { return q8 ? d + 16 : 2 * d; }
-// four codes of a word -> floats: the biased byte goes into the mantissa of 2^23, one FMA applies scale and removes the bias
+// four codes of a word -> floats: the biased byte goes into the mantissa of 2^23, the bias comes off exactly, then the scale
 __device__ __forceinline__ void q8_word_to_float(uint32_t w, float sc, float* out) {
-  const uint32_t b = w ^ 0x80808080u;
-  const float off = -(8388608.f + 128.f) * sc;
-  out[0] = fmaf(__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7540)), sc, off);
-  out[1] = fmaf(__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7541)), sc, off);
-  out[2] = fmaf(__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7542)), sc, off);
-  out[3] = fmaf(__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7543)), sc, off);
+  const uint32_t b = w ^ 0x80808080u;                     // bias the code to 0..255; (2^23 + byte) - (2^23 + 128) is exact
+  out[0] = (__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7540)) - 8388736.f) * sc;
+  out[1] = (__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7541)) - 8388736.f) * sc;
+  out[2] = (__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7542)) - 8388736.f) * sc;
+  out[3] = (__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7543)) - 8388736.f) * sc;
 }
 __device__ __forceinline__ float q8_round(float x, float sc) {      // what the cache will return for x
   return sc > 0.f ? fminf(127.f, fmaxf(-127.f, rintf(x / sc))) * sc : 0.f;
@@ -92,7 +91,7 @@ __device__ __forceinline__ void rope_inplace(float* v, int d_rot, int rope_type,
   }
 }
 
-template <int GT, int MERGE, int DEEP>
+template <int GT, int MERGE, int DEEP, int Q8>
 __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_constant__ AttnDecodeParams p) {
   const int G = p.n_heads / p.n_kv_heads;
   const int hgroups = (G + GT - 1) / GT;
@@ -106,7 +105,11 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
   __shared__ float q_s[GT][128];
   __shared__ float k_s[128], v_s[128];
   __shared__ float part_s[ATT_WARPS][GT][128 + 2];   // per-warp partials
-  __shared__ float res_s[GT][128 + 2];      // this CTA's split result (read by cluster rank 0 in MERGE_CLUSTER)
+  // MERGE_CLUSTER: up to 4 heads per CTA the splits PUSH their results into the gather buffer of cluster rank 0 and leave;
+  // with 8 heads the buffer would not fit in static shared memory and rank 0 pulls the peers' res_s instead
+  constexpr bool PUSH = MERGE == MERGE_CLUSTER && GT <= 4;
+  __shared__ float res_s[PUSH ? 1 : GT][128 + 2];
+  __shared__ float gat_s[PUSH ? ATT_MAX_CLUSTER : 1][PUSH ? GT : 1][128 + 2];
   __shared__ int32_t pt_s[ATT_PT_MAX];      // physical pages of this split's token range
   __shared__ float qs_s[2][ATT_THREADS / 32 + 1];   // int8 cache: max|k|, max|v| of the new row (per warp, then total)
   __shared__ int last_flag;
@@ -115,7 +118,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
   pdl_wait();
 
   const int pos = p.positions[b];
-  if (pos < 0) return;
+  if (pos < 0) return;                                   // uniform over the cluster (same sequence)
+  if (PUSH) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");     // phase 1: "I have started"; waited on before the push
   const int seq_len = pos + 1;
   const int lo = p.window > 0 ? max(0, seq_len - p.window) : 0;      // first position attended to
   const int lo_al = lo / ATT_PAGE * ATT_PAGE;
@@ -159,7 +163,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
     if (owner) rope_inplace(k_s, p.rope_dim, p.rope_type, pos, p.rope_theta, tab, tid, ATT_THREADS);
     __syncthreads();
   }
-  const int q8 = p.kv_q8;
+  constexpr int q8 = Q8;                                 // compile-time: the bf16 instantiation carries none of the int8 code
   const int64_t rowb = kv_row_bytes(d, q8);              // bytes per cached row
   float sck = 0.f, scv = 0.f;                            // int8 cache: scales of the new row
   if (q8 && owner) {
@@ -338,6 +342,11 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
   }
   __syncthreads();
   const int S = p.splits;
+  float* push_dst = nullptr;                              // (push mode) this split's slot in rank 0's gather buffer
+  if (PUSH) {
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");               // phase 1 complete: every CTA of the cluster is running
+    push_dst = cg::this_cluster().map_shared_rank(&gat_s[0][0][0], 0) + (int64_t)split * GT * 130;
+  }
   for (int i = tid; i < gn * d + gn; i += ATT_THREADS) {
     const bool stat = i >= gn * d;                 // the trailing gn items carry (max, sum) of each head
     const int g = stat ? i - gn * d : i / d, j = stat ? 0 : i - g * d;
@@ -352,7 +361,11 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
     if (MERGE == MERGE_NONE) {
       if (!stat) p.out[(int64_t)b * p.ld_out + (kvh * G + g0 + g) * d + j] = a / ll;
     } else if (MERGE == MERGE_CLUSTER) {
-      if (stat) { res_s[g][128] = mm; res_s[g][129] = ll; } else res_s[g][j] = a;
+      if (PUSH) {                                          // straight into rank 0's shared memory
+        if (stat) { push_dst[g * 130 + 128] = mm; push_dst[g * 130 + 129] = ll; } else push_dst[g * 130 + j] = a;
+      } else {
+        if (stat) { res_s[g][128] = mm; res_s[g][129] = ll; } else res_s[g][j] = a;
+      }
     } else {
       float* dst = p.partial + (((int64_t)b * p.n_heads + kvh * G + g0 + g) * S + split) * (d + 2);
       if (stat) { dst[d] = mm; dst[d + 1] = ll; } else dst[j] = a;
@@ -360,8 +373,31 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
   }
   if (MERGE == MERGE_NONE) return;
 
+  if (MERGE == MERGE_CLUSTER && PUSH) {
+    // ---- every split stores its result into rank 0's gather buffer, signals, and leaves; rank 0 merges locally ----
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");             // phase 2: my stores are done
+    if (cg::this_cluster().block_rank() != 0) return;
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    for (int i = tid; i < gn * d; i += ATT_THREADS) {
+      const int g = i / d, j = i - g * d;
+      float mm = -INFINITY;
+#pragma unroll
+      for (int sp = 0; sp < ATT_MAX_CLUSTER; ++sp) if (sp < S) mm = fmaxf(mm, gat_s[sp][g][128]);
+      float a = 0.f, ll = 0.f;
+#pragma unroll
+      for (int sp = 0; sp < ATT_MAX_CLUSTER; ++sp) {
+        if (sp < S) {
+          const float ms = gat_s[sp][g][128];
+          const float c = ms == -INFINITY ? 0.f : exp2f(ms - mm);
+          a += c * gat_s[sp][g][j]; ll += c * gat_s[sp][g][129];
+        }
+      }
+      p.out[(int64_t)b * p.ld_out + (kvh * G + g0 + g) * d + j] = a / ll;
+    }
+    return;
+  }
   if (MERGE == MERGE_CLUSTER) {
-    // ---- cluster rank 0 merges the splits out of its peers' shared memory ----------------------
+    // ---- (8 heads per CTA) cluster rank 0 merges the splits out of its peers' shared memory ----------------------
     cg::cluster_group cluster = cg::this_cluster();
     cluster.sync();                                  // every CTA's res_s is complete and visible
     if (cluster.block_rank() == 0) {
@@ -434,8 +470,10 @@ static int attn_decode_dispatch(const AttnDecodeParams& p, cudaStream_t st) {
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const bool deep = (long long)grid.x * grid.y * grid.z < 4LL * sms;     // latency-bound launch: keep more loads in flight per thread
-#define RLZ_ATT_LAUNCH(GT_, M_) (deep ? launch_cluster(attn_decode_kernel<GT_, M_, 1>, grid, block, cl, 0, st, p) \
-                                      : launch_cluster(attn_decode_kernel<GT_, M_, 0>, grid, block, cl, 0, st, p))
+#define RLZ_ATT_LAUNCH(GT_, M_) (p.kv_q8 ? (deep ? launch_cluster(attn_decode_kernel<GT_, M_, 1, 1>, grid, block, cl, 0, st, p)  \
+                                                 : launch_cluster(attn_decode_kernel<GT_, M_, 0, 1>, grid, block, cl, 0, st, p)) \
+                                         : (deep ? launch_cluster(attn_decode_kernel<GT_, M_, 1, 0>, grid, block, cl, 0, st, p)  \
+                                                 : launch_cluster(attn_decode_kernel<GT_, M_, 0, 0>, grid, block, cl, 0, st, p)))
 #define RLZ_ATT_CASE(GT_) \
   (merge == MERGE_NONE ? RLZ_ATT_LAUNCH(GT_, MERGE_NONE) : merge == MERGE_CLUSTER ? RLZ_ATT_LAUNCH(GT_, MERGE_CLUSTER) : RLZ_ATT_LAUNCH(GT_, MERGE_GLOBAL))
   cudaError_t e;

@@ -242,7 +242,15 @@ __global__ void __launch_bounds__(GEMV_THREADS, (FAST && B <= GEMV_OCC2_MAXB ? 2
       const GemvX& X = p.xs[S.x_id];
       const bool in_regs = GEMV_REG_STAGING && X.k <= STAGE_MAXV * 4 * GEMV_THREADS;
       if constexpr (fast) {
-        if (in_regs) {
+        if (B == 1 && X.pre) {                              // the producer left this activation quantised: plain 16-byte copies
+          const int k = X.k;                                // sections of the block: codes | per-64 records | per-32 scales | per-16 sums
+          const uint8_t* g = X.pre;
+          const int n_q = k >> 4, n_m = k >> 6, n_d = k >> 7, n_s = k >> 6;      // 16-byte vectors per section (k is a multiple of 128)
+          for (int i = threadIdx.x; i < n_q; i += blockDim.x) ((uint4*)xq)[i] = ((const uint4*)g)[i];
+          for (int i = threadIdx.x; i < n_m; i += blockDim.x) ((uint4*)xm)[i] = ((const uint4*)(g + k))[i];
+          for (int i = threadIdx.x; i < n_d; i += blockDim.x) ((uint4*)xd)[i] = ((const uint4*)(g + k + (k >> 2)))[i];
+          for (int i = threadIdx.x; i < n_s; i += blockDim.x) ((uint4*)xs)[i] = ((const uint4*)(g + k + (k >> 2) + (k >> 3)))[i];
+        } else if (in_regs) {
           const int k = X.k;
           stage_rows_regs<B, true>(X, red,
             [&](int b, int i, uint32_t packed, float d, int s16, int s32) {
@@ -324,6 +332,7 @@ int rlz_gemv(const rlz::GemvParams* pp, void* stream) {
   for (int m = 0; m < p.nmat; ++m) {
     GemvMat& M = p.mat[m];
     if (M.nseg < 1 || M.nseg > 2 || M.n < 1 || M.rows_per_cta < 1) return -2;
+    if (M.q_out && (p.batch != 1 || M.rows_per_cta % 32 || M.q_out_col0 % 32 || M.q_out_k % 128 || M.q_out_col0 + M.n > M.q_out_k || ((uintptr_t)M.q_out & 15))) return -9;
     const bool fast0 = M.seg[0].qtype == QT_Q4_K || M.seg[0].qtype == QT_Q5_K || M.seg[0].qtype == QT_Q6_K || M.seg[0].qtype == QT_Q8_0 || M.seg[0].qtype == QT_Q4_0;
     for (int s = 0; s < M.nseg; ++s) {
       const GemvSeg& S = M.seg[s];

@@ -144,6 +144,38 @@ template <int B>
 __device__ __forceinline__ void gemv_epilogue(const GemvParams& p, const GemvMat& M, float* rowacc, int r0, int r1) {
   const int count = (r1 - r0) * B;
   if (!p.ar.enabled) {
+    if (B == 1 && M.q_out) {
+      // a warp owns 32 consecutive outputs = one quantisation block of the next launch's activation (r0 is a multiple of 32)
+      const int k = M.q_out_k, lane = threadIdx.x & 31;
+      uint8_t* q = M.q_out;
+      uint32_t* xm = (uint32_t*)(q + k);
+      float* xd = (float*)(xm + (size_t)(k >> 6) * 4);
+      int32_t* xs = (int32_t*)(xd + (k >> 5));
+      for (int base = (threadIdx.x & ~31); base < count; base += blockDim.x) {
+        const int rl = base + lane, r = r0 + rl;
+        const bool ok = rl < count;
+        float v = ok ? gemv_value<1>(M, rowacc, rl, 0, r) : 0.f;
+        if (ok && M.has_residual) v += p.residual[r];
+        if (ok) p.y[M.out_off + r] = v;
+        const float amax = warp_max(fabsf(v));
+        const float d = amax / 127.f, inv = amax > 0.f ? 127.f / amax : 0.f;
+        const int qi = __float2int_rn(v * inv);
+        int s16 = qi;
+        s16 += __shfl_xor_sync(0xffffffffu, s16, 1); s16 += __shfl_xor_sync(0xffffffffu, s16, 2);
+        s16 += __shfl_xor_sync(0xffffffffu, s16, 4); s16 += __shfl_xor_sync(0xffffffffu, s16, 8);
+        const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 16);
+        const int i = M.q_out_col0 + r;                   // position in the destination activation
+        if (ok) q[act_chunk_off(i >> 4) + (i & 15)] = (uint8_t)(qi & 0xFF);
+        if ((lane & 15) == 0 && ok) xs[i >> 4] = s16;
+        if (lane == 0 && ok) {
+          xd[i >> 5] = d;
+          uint32_t* rec = xm + (size_t)(i >> 6) * 4 + ((i >> 5) & 1);
+          rec[0] = __float_as_uint(d);
+          rec[2] = (uint32_t)s32;
+        }
+      }
+      return;
+    }
     for (int idx = threadIdx.x; idx < count; idx += blockDim.x) {
       const int rl = idx / B, b = idx - rl * B, r = r0 + rl;
       float v = gemv_value<B>(M, rowacc, rl, b, r);

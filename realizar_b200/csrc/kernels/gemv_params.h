@@ -29,6 +29,11 @@ struct GemvMat {            // a block of output rows
   int32_t has_residual;     // add p.residual[b, row]
   int32_t rows_per_cta;
   int32_t cta_begin;        // filled by the launcher
+  // batch 1 only: besides the fp32 store, write the outputs as the int8 activation of the NEXT launch (the layout that
+  // launch stages in shared memory: codes, per-64 records, per-32 scales, per-16 sums), so that it copies instead of quantising
+  uint8_t* q_out;           // destination activation block (null = off); rows_per_cta and q_out_col0 are multiples of 32
+  int32_t q_out_k;          // length of the destination activation vector
+  int32_t q_out_col0;       // column of output row 0 in that vector
 };
 
 struct GemvX {              // an input vector (batch rows `ld` floats apart) and its fused norm
@@ -40,6 +45,7 @@ struct GemvX {              // an input vector (batch rows `ld` floats apart) an
   int32_t norm;             // NORM_*
   float eps;
   int32_t _pad;
+  const uint8_t* pre;       // batch 1: this input already quantised by the producing launch (see GemvMat::q_out), or null
 };
 
 constexpr int GEMV_AR_MAX_RANKS = 8;

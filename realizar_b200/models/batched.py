@@ -14,6 +14,7 @@ whose GEMMs are cuBLAS calls and whose attention is strided-batched SGEMM + a so
 """
 from __future__ import annotations
 
+import os
 from typing import Callable, List, Optional
 
 import torch
@@ -64,7 +65,9 @@ class BatchedForward:
         # inboxes from the epilogue (one-shot all-reduce, latency-optimal); longer chunks use NCCL (bandwidth-optimal)
         self.ll_tokens = 0
         if model.tp_size > 1 and getattr(comm, "fused", False):
-            self.ll_tokens = min(max_tokens, 128)
+            # measured: at 64 rows the one-shot push loses to NCCL at every world size (2 GPUs 0.76x, 4 GPUs 0.98x,
+            # 8 GPUs 0.67x of the NCCL step rate); it is kept for the short batches where latency decides
+            self.ll_tokens = min(max_tokens, int(os.environ.get("RLZ_LL_TOKENS", max(8, 64 // model.tp_size))))
             comm.allocate_gemm(2 * cfg.num_layers, H, self.ll_tokens)
         self._site = 0
 

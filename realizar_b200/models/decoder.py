@@ -243,6 +243,7 @@ class StepBuffers:
     local_val: Optional[torch.Tensor] = None     # TP: this rank's best logit per sequence
     local_idx: Optional[torch.Tensor] = None     # TP: its global token id
     logits_full: Optional[torch.Tensor] = None   # TP sampling: gathered logits
+    act_q: Optional[torch.Tensor] = None         # batch 1: the MLP activation as the int8 block the down-projection launch stages
 
 
 def _is_fast(w: DeviceWeight) -> bool:
@@ -405,6 +406,12 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
     tp = model.tp_size > 1
     target = int(os.environ.get("RLZ_GEMV_CTAS", 2 * sm_count if batch <= 1 else sm_count))   # register-path kernel: 2 CTAs/SM at batch 1
     chunks = [(c, min(4, batch - c)) for c in range(0, batch, 4)]       # GEMV kernels take <= 4 rows at a time
+    # batch 1, one GPU: the launch that produces the MLP activation also writes it as the int8 block that the down-projection
+    # launch stages, so all of that launch's CTAs copy 1.9 bytes per value instead of reading 4 and quantising
+    def handoff(L) -> bool:
+        return (batch == 1 and not tp and buf.act_q is not None and os.environ.get("RLZ_ACT_HANDOFF", "1") != "0" and _is_fast(L.down)
+                and _is_fast(L.up) and (L.gate is None or _is_fast(L.gate)) and L.down.k % 128 == 0 and L.up.n == L.down.k
+                and buf.act_q.numel() >= ops.act_block_bytes(L.down.k))
     overlap_up = cfg.parallel_residual and len(chunks) == 1 and os.environ.get("RLZ_OVERLAP_UP", "0") == "1"   # measured slower than the single chain; opt-in
     qkv_w = qd + 2 * kvd
     ld1 = buf.y1.stride(0)
@@ -454,6 +461,8 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
             if cfg.parallel_residual:
                 up_mat = MatOut([(L.up, 0)], out_off=model.act_col0 + L.down_in_off, bias=L.up_b,
                                 act=ACT_GELU if cfg.constraints.activation == "gelu" else ops.ACT_SILU)
+                if handoff(L):
+                    up_mat.q_out, up_mat.q_out_k, up_mat.q_out_col0 = buf.act_q, L.down.k, 0
                 if overlap_up:
                     # the MLP up-projection does not depend on attention: it streams its weights on a side
                     # stream while the main chain runs QKV -> attention (whose latency it hides)
@@ -471,7 +480,8 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
         if cfg.parallel_residual and overlap_up:
             plan.join()
         if cfg.parallel_residual:
-            row_parallel(lambda c0: [VecIn(buf.attn_out[c0:], L.o.k, ld=buf.attn_out.stride(0)), VecIn(buf.y1[c0:, model.act_col0:], L.down.k, ld=ld1)],
+            row_parallel(lambda c0: [VecIn(buf.attn_out[c0:], L.o.k, ld=buf.attn_out.stride(0)),
+                                     VecIn(buf.y1[c0:, model.act_col0:], L.down.k, ld=ld1, pre=buf.act_q if handoff(L) else None)],
                          lambda res: MatOut([(L.o, 0), (L.down, 1)], bias=L.o_b, bias2=L.down_b, combine=COMBINE_ADD, residual=res))
         else:
             row_parallel(lambda c0: [VecIn(buf.attn_out[c0:], L.o.k, ld=buf.attn_out.stride(0))],
@@ -483,8 +493,10 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
                     mat = MatOut([(L.gate, 0), (L.up, 0)], combine=comb, bias2=L.up_b)
                 else:
                     mat = MatOut([(L.up, 0)], bias=L.up_b, act=ACT_GELU if cfg.constraints.activation == "gelu" else ops.ACT_SILU)
+                if handoff(L):
+                    mat.q_out, mat.q_out_k, mat.q_out_col0 = buf.act_q, L.down.k, 0
                 plan.add_gemv_auto([xin], [mat], buf.act[c0:, L.down_in_off:], cb, buf.act.stride(0), target_ctas=target)
-            row_parallel(lambda c0: [VecIn(buf.act[c0:], L.down.k, ld=buf.act.stride(0))],
+            row_parallel(lambda c0: [VecIn(buf.act[c0:], L.down.k, ld=buf.act.stride(0), pre=buf.act_q if handoff(L) else None)],
                          lambda res: MatOut([(L.down, 0)], bias=L.down_b, residual=res))
 
     emit_head(plan, model, buf, 0, batch, comm, greedy_only, sm_count)

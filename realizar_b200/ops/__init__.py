@@ -95,6 +95,12 @@ class VecIn:
     norm_w: Optional[torch.Tensor] = None
     norm_b: Optional[torch.Tensor] = None
     eps: float = 1e-5
+    pre: Optional[torch.Tensor] = None     # batch 1: the int8 activation block written by the producing launch (MatOut.q_out)
+
+
+def act_block_bytes(k: int) -> int:
+    """Bytes of a pre-quantised activation block of ``k`` values: codes, per-64 records, per-32 scales, per-16 sums."""
+    return k + k // 4 + k // 8 + k // 4
 
 
 @dataclass
@@ -108,6 +114,9 @@ class MatOut:
     act: int = ACT_NONE
     residual: bool = False
     rows_per_cta: int = 0                  # 0 = choose automatically
+    q_out: Optional[torch.Tensor] = None   # batch 1: also write the outputs as the int8 activation block of the next launch
+    q_out_k: int = 0                       # length of that activation vector
+    q_out_col0: int = 0                    # column of this matrix's row 0 in it
 
 
 def plan_rows_per_cta(mats: Sequence[MatOut], target_ctas: int) -> List[int]:
@@ -135,6 +144,10 @@ def build_gemv_params(xs: Sequence[VecIn], mats: Sequence[MatOut], y: torch.Tens
         X.x, X.nw, X.nb = v.x.data_ptr(), ptr(v.norm_w), ptr(v.norm_b)
         X.ld = v.ld if v.ld is not None else v.x.stride(0) if v.x.dim() > 1 else v.k
         X.k, X.norm, X.eps = v.k, v.norm, v.eps
+        if v.pre is not None:
+            if batch != 1 or v.norm != NORM_NONE or v.k % 128 or v.pre.numel() < act_block_bytes(v.k):
+                raise ValueError("a pre-quantised input needs batch 1, no norm, k % 128 == 0 and a block of act_block_bytes(k)")
+            X.pre = v.pre.data_ptr()
     for i, m in enumerate(mats):
         M = p.mat[i]
         M.nseg = len(m.segs)
@@ -147,6 +160,11 @@ def build_gemv_params(xs: Sequence[VecIn], mats: Sequence[MatOut], y: torch.Tens
         M.combine, M.act, M.has_residual = m.combine, m.act, 1 if m.residual else 0
         M.n, M.out_off = m.segs[0][0].n, m.out_off
         M.rows_per_cta = m.rows_per_cta or auto[i]
+        if m.q_out is not None:
+            if batch != 1:
+                raise ValueError("quantised output is a batch-1 feature")
+            M.rows_per_cta = -(-M.rows_per_cta // 32) * 32        # a warp of the epilogue owns one 32-value quantisation block
+            M.q_out, M.q_out_k, M.q_out_col0 = m.q_out.data_ptr(), m.q_out_k, m.q_out_col0
     p.nmat, p.batch = len(mats), batch
     p.y, p.ldy = y.data_ptr(), ldy if ldy is not None else (y.stride(0) if y.dim() > 1 else y.numel())
     p.residual = ptr(residual)

@@ -20,12 +20,12 @@ class GemvSeg(Structure):
 class GemvMat(Structure):
     _fields_ = [("seg", GemvSeg * 2), ("bias", c_void_p), ("bias2", c_void_p), ("nseg", c_int32), ("combine", c_int32),
                 ("n", c_int32), ("out_off", c_int32), ("act", c_int32), ("has_residual", c_int32), ("rows_per_cta", c_int32),
-                ("cta_begin", c_int32)]
+                ("cta_begin", c_int32), ("q_out", c_void_p), ("q_out_k", c_int32), ("q_out_col0", c_int32)]
 
 
 class GemvX(Structure):
     _fields_ = [("x", c_void_p), ("nw", c_void_p), ("nb", c_void_p), ("ld", c_int64), ("k", c_int32), ("norm", c_int32),
-                ("eps", c_float), ("_pad", c_int32)]
+                ("eps", c_float), ("_pad", c_int32), ("pre", c_void_p)]
 
 
 AR_MAX_RANKS = 8

@@ -105,7 +105,8 @@ class DecodeEngine:
             temperature=z(B), top_k=z(B, dt=torch.int32), top_p=torch.ones(B, device=dev), min_p=z(B), uniform=z(B),
             attn_partial=part, attn_counters=ctr,
             local_val=z(B) if tp_size > 1 else None, local_idx=z(B, dt=torch.int32) if tp_size > 1 else None,
-            logits_full=z(B, self.mcfg.vocab_size) if (tp_size > 1 and not c.greedy_only) else None)
+            logits_full=z(B, self.mcfg.vocab_size) if (tp_size > 1 and not c.greedy_only) else None,
+            act_q=z(ops.act_block_bytes((d_k + 127) // 128 * 128), dt=torch.uint8) if tp_size == 1 else None)
         if comm is not None and getattr(comm, "fused", False):
             chunks_max = -(-B // 4)
             per_layer = 1 if self.mcfg.parallel_residual else 2
