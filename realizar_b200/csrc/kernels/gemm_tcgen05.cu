@@ -57,24 +57,33 @@ struct GemmParams {
 // The scale (and the Q4_K / Q5_K minimum) is rounded to bf16 first; the operand fed to the tensor core is bf16 anyway.
 struct RawW { uint4 r[5]; };
 
+// bytes of one 256-weight block of a K-quant row in the device layout
+template <int QT> struct BlockBytes { static constexpr int value = QT == QT_Q4_K ? 144 : QT == QT_Q5_K ? 176 : QT == QT_Q6_K ? Q6K_DEV_STRIDE : 0; };
+
+// the bytes of one thread's 32 weights of K group g (0..3) of the block at `blk` (global or shared memory)
 template <int QT>
-__device__ __forceinline__ void load_raw(const uint8_t* row, int k0, int half, RawW& w) {
-  const int sb = k0 >> 8, g = (k0 >> 6) & 3;
+__device__ __forceinline__ void load_block(const uint8_t* blk, int g, int half, RawW& w) {
   if (QT == QT_Q4_K || QT == QT_Q5_K) {
-    const uint8_t* blk = row + (int64_t)sb * (QT == QT_Q5_K ? 176 : 144);
-    w.r[0] = __ldg((const uint4*)blk);
+    w.r[0] = *(const uint4*)blk;
     const uint8_t* qs = blk + (QT == QT_Q5_K ? 48 : 16) + 32 * g;
-    w.r[1] = __ldg((const uint4*)qs); w.r[2] = __ldg((const uint4*)(qs + 16));
-    if (QT == QT_Q5_K) { w.r[3] = __ldg((const uint4*)(blk + 16)); w.r[4] = __ldg((const uint4*)(blk + 32)); }
+    w.r[1] = *(const uint4*)qs; w.r[2] = *(const uint4*)(qs + 16);
+    if (QT == QT_Q5_K) { w.r[3] = *(const uint4*)(blk + 16); w.r[4] = *(const uint4*)(blk + 32); }
   } else if (QT == QT_Q6_K) {
-    const uint8_t* blk = row + (int64_t)sb * Q6K_DEV_STRIDE;
     const int n = g >> 1, upper = g & 1;
     const uint8_t* ql = blk + 64 * n + 32 * half;
     const uint8_t* qh = blk + 128 + 32 * n;
-    w.r[0] = __ldg((const uint4*)ql); w.r[1] = __ldg((const uint4*)(ql + 16));
-    w.r[2] = __ldg((const uint4*)qh); w.r[3] = __ldg((const uint4*)(qh + 16));
-    w.r[4].x = __ldg((const uint32_t*)(blk + 192 + 8 * n + 4 * upper));     // the four int8 scales of this 64-column group
-    w.r[4].y = __ldg((const uint32_t*)(blk + 208));                        // d (f16) in the low half
+    w.r[0] = *(const uint4*)ql; w.r[1] = *(const uint4*)(ql + 16);
+    w.r[2] = *(const uint4*)qh; w.r[3] = *(const uint4*)(qh + 16);
+    w.r[4].x = *(const uint32_t*)(blk + 192 + 8 * n + 4 * upper);     // the four int8 scales of this 64-column group
+    w.r[4].y = *(const uint32_t*)(blk + 208);                          // d (f16) in the low half
+  }
+}
+
+template <int QT>
+__device__ __forceinline__ void load_raw(const uint8_t* row, int k0, int half, RawW& w) {
+  const int sb = k0 >> 8, g = (k0 >> 6) & 3;
+  if (QT == QT_Q4_K || QT == QT_Q5_K || QT == QT_Q6_K) {
+    load_block<QT>(row + (int64_t)sb * BlockBytes<QT>::value, g, half, w);
   } else {                                                                  // BF16 / F16: 32 elements = 64 bytes
     const uint4* src = (const uint4*)(row + (int64_t)(k0 + 32 * half) * 2);
 #pragma unroll
@@ -157,12 +166,29 @@ __device__ __forceinline__ void store_half_row_sw128(uint8_t* tile, int r, int h
 
 // RT = 128-row weight tiles per CTA (1 or 2).  With RT = 2 the CTA owns 256 weight rows, keeps two accumulators in TMEM
 // and issues two MMAs per K slice that share the activation tile, which halves the activation traffic from L2 per FLOP.
+// K-quant weights do not go through the load/store units at all: a third single-thread role streams the raw 256-weight
+// blocks of the CTA's rows with TMA (box = rows x block bytes) into a two-deep shared-memory ring, one block per four K steps,
+// and the dequant warps read their row's bytes from there.  Row-strided 16-byte global loads (one sector per lane) were the
+// limit of the earlier version (lg_throttle / long_scoreboard).  Dense bf16 / f16 weights keep the register prefetch ring.
+template <int NT, int QT, int RT> struct GemmCfg {
+  static constexpr bool RAWTMA = QT == QT_Q4_K || QT == QT_Q5_K || QT == QT_Q6_K;
+  static constexpr int ROWS = RT * GM_ROWS;
+  static constexpr int STAGES = RAWTMA ? (RT == 2 ? 2 : NT == 256 ? 3 : 4) : (RT == 2 ? 3 : 4);
+  static constexpr int RAW_BYTES = RAWTMA ? ROWS * BlockBytes<QT>::value : 0;      // one ring slot
+  static constexpr int STAGE = ROWS * 128 + NT * 128;
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE + 2 * RAW_BYTES + 1024;
+  static constexpr int THREADS = RT * GM_PRODUCERS + 96;                           // dequant warps + B TMA + MMA + raw TMA
+};
+
 template <int NT, int QT, int RT>
-__global__ void __launch_bounds__(RT * GM_PRODUCERS + 64) gemm_kquant_tcgen05_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap xmap) {
-  constexpr int GM_STAGES = RT == 2 ? 3 : 4;
+__global__ void __launch_bounds__(RT * GM_PRODUCERS + 96) gemm_kquant_tcgen05_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap xmap,
+                                                                                     const __grid_constant__ CUtensorMap wmap) {
+  using Cfg = GemmCfg<NT, QT, RT>;
+  constexpr int GM_STAGES = Cfg::STAGES;
+  constexpr bool RAWTMA = Cfg::RAWTMA;
   constexpr int PRODUCERS = RT * GM_PRODUCERS, PWARPS = PRODUCERS / 32, ROWS = RT * GM_ROWS;
   extern __shared__ __align__(1024) uint8_t gsm[];
-  __shared__ __align__(8) uint64_t full_bar[GM_STAGES], empty_bar[GM_STAGES], done_bar;
+  __shared__ __align__(8) uint64_t full_bar[GM_STAGES], empty_bar[GM_STAGES], done_bar, raw_full[2], raw_empty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int failed_s;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -178,6 +204,10 @@ __global__ void __launch_bounds__(RT * GM_PRODUCERS + 64) gemm_kquant_tcgen05_ke
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gm_smem_u32(&empty_bar[s])));
     }
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gm_smem_u32(&done_bar)));
+    for (int i = 0; i < 2; ++i) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gm_smem_u32(&raw_full[i])));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(gm_smem_u32(&raw_empty[i])), "r"(PWARPS));
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {                                        // one warp allocates the accumulator columns of tensor memory
@@ -203,6 +233,33 @@ __global__ void __launch_bounds__(RT * GM_PRODUCERS + 64) gemm_kquant_tcgen05_ke
     const int r = tid & (ROWS - 1), half = tid / ROWS;
     const int wrow = n0 + r;
     const uint8_t* wptr = p.W + (int64_t)min(wrow, p.n - 1) * p.w_stride;
+    if constexpr (RAWTMA) {
+      constexpr int BB = BlockBytes<QT>::value;
+      const uint8_t* raw = sm + GM_STAGES * STAGE;          // ring of two block tiles [ROWS][BB]; rows past n arrive zero-filled
+      const int kb0 = ks0 >> 2;
+      for (int it = 0; it < nit; ++it) {
+        const int step = ks0 + it, kbi = (step >> 2) - kb0, g = step & 3, rb = kbi & 1, s = it % GM_STAGES;
+        if (it == 0 || g == 0) {                            // first step of a block: its bytes have landed
+          ok = gm_wait(&raw_full[rb], (uint32_t)(kbi >> 1) & 1u);
+          if (!ok) break;
+        }
+        if (it >= GM_STAGES) {                              // the MMAs that read this stage GM_STAGES steps ago are done
+          ok = gm_wait(&empty_bar[s], (uint32_t)(it / GM_STAGES - 1) & 1u);
+          if (!ok) break;
+        }
+        RawW w;
+        load_block<QT>(raw + (size_t)rb * Cfg::RAW_BYTES + (size_t)r * BB, g, half, w);
+        uint32_t v[16];
+        dequant_raw32<QT>(w, step * GM_KSTEP, half, v);
+        store_half_row_sw128(sm + s * STAGE, r, half, v);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic-proxy writes -> visible to the tensor core
+        __syncwarp();
+        if (lane == 0) {
+          gm_arrive(&full_bar[s]);
+          if (g == 3 || it == nit - 1) gm_arrive(&raw_empty[rb]);       // this warp is done with the block tile
+        }
+      }
+    } else {
     // a ring of PF K steps of raw block bytes per thread keeps enough loads in flight to cover HBM latency
     constexpr int PF = NT <= 64 ? 2 : RT == 2 ? (QT == QT_Q4_K ? 3 : 2) : (QT == QT_Q4_K ? 4 : 3);   // short kernels: smaller code wins
     RawW ring[PF];
@@ -232,6 +289,23 @@ __global__ void __launch_bounds__(RT * GM_PRODUCERS + 64) gemm_kquant_tcgen05_ke
         if (lane == 0) gm_arrive(&full_bar[s]);
       }
     }
+    }
+  } else if (warp == PWARPS + 2) {
+    // ---- raw weight blocks by TMA (K-quants): one [ROWS x block] tile per four K steps, two in flight ----
+    if (RAWTMA && lane == 0) {
+      constexpr int BB = BlockBytes<QT>::value;
+      uint8_t* raw = sm + GM_STAGES * STAGE;
+      const int kb0 = ks0 >> 2, nkb = nit > 0 ? ((ks1 - 1) >> 2) - kb0 + 1 : 0;
+      for (int kbi = 0; kbi < nkb; ++kbi) {
+        const int rb = kbi & 1;
+        if (kbi >= 2) {                                     // every dequant warp has finished with the tile two blocks ago
+          ok = gm_wait(&raw_empty[rb], (uint32_t)((kbi >> 1) - 1) & 1u);
+          if (!ok) break;
+        }
+        gm_arrive_expect_tx(&raw_full[rb], (uint32_t)Cfg::RAW_BYTES);
+        tma_load_2d(raw + (size_t)rb * Cfg::RAW_BYTES, &wmap, (kb0 + kbi) * BB, n0, &raw_full[rb]);
+      }
+    }
   } else if (warp == PWARPS) {
     // ---- TMA producer: activations of this token tile -------------------------------------------
     if (lane == 0) {
@@ -246,7 +320,7 @@ __global__ void __launch_bounds__(RT * GM_PRODUCERS + 64) gemm_kquant_tcgen05_ke
         tma_load_2d(Bt, &xmap, (ks0 + it) * GM_KSTEP, m0, &full_bar[s]);
       }
     }
-  } else {
+  } else if (warp == PWARPS + 1) {
     // ---- MMA issuer --------------------------------------------------------------------------------
     if (lane == 0) {
       const uint32_t idesc = make_idesc_bf16(GM_ROWS, NT);
@@ -340,6 +414,7 @@ __global__ void __launch_bounds__(RT * GM_PRODUCERS + 64) gemm_kquant_tcgen05_ke
   if (failed_s && warp == PWARPS && lane == 0) {
     // error path: give TMA copies still in flight a bounded chance to land before the CTA's shared memory is released
     for (int s = 0; s < GM_STAGES && s < nit; ++s) gm_wait(&full_bar[s], 0u);
+    if (RAWTMA && nit > 0) gm_wait(&raw_full[0], 0u);
   }
   __syncthreads();
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(TMEM_COLS) : "memory");
@@ -373,20 +448,37 @@ static int make_x_map(CUtensorMap* map, const GemmParams& p, int box_rows) {
   return r == CUDA_SUCCESS ? 0 : -7;
 }
 
+// W viewed as a 2-D byte tensor [n rows, row bytes] with a row pitch of w_stride; boxes of [box_rows x block bytes]
+static int make_w_map(CUtensorMap* map, const GemmParams& p, int box_rows, int block_bytes) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return -6;
+  const cuuint64_t gdim[2] = {(cuuint64_t)(p.k / 256) * block_bytes, (cuuint64_t)p.n};
+  const cuuint64_t gstride[1] = {(cuuint64_t)p.w_stride};
+  const cuuint32_t box[2] = {(cuuint32_t)block_bytes, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)p.W, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -7;
+}
+
 template <int NT, int QT, int RT>
 int launch_gemm_q(const GemmParams& p, cudaStream_t st) {
-  const size_t smem = (RT == 2 ? 3 : 4) * (RT * GM_ROWS * 128 + NT * 128) + 1024;
+  using Cfg = GemmCfg<NT, QT, RT>;
+  const size_t smem = Cfg::SMEM;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_kquant_tcgen05_kernel<NT, QT, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  alignas(64) CUtensorMap xmap;
-  const int rc = make_x_map(&xmap, p, NT);
+  alignas(64) CUtensorMap xmap, wmap;
+  int rc = make_x_map(&xmap, p, NT);
+  if (rc) return rc;
+  if (Cfg::RAWTMA) rc = make_w_map(&wmap, p, Cfg::ROWS, BlockBytes<QT>::value);
+  else wmap = xmap;                                        // unused by the dense-weight instantiations
   if (rc) return rc;
   dim3 grid((p.n + RT * GM_ROWS - 1) / (RT * GM_ROWS), (p.m + NT - 1) / NT, p.splitk);
-  return (int)launch(gemm_kquant_tcgen05_kernel<NT, QT, RT>, grid, dim3(RT * GM_PRODUCERS + 64), smem, st, p, xmap);
+  return (int)launch(gemm_kquant_tcgen05_kernel<NT, QT, RT>, grid, dim3(Cfg::THREADS), smem, st, p, xmap, wmap);
 }
 
 template <int NT, int RT>
@@ -438,7 +530,9 @@ int rlz_gemm_kquant(const rlz::GemmParams* pp, void* stream) {
   const long long tiles2 = (long long)((p.n + 255) / 256) * ((p.m + 255) / 256) * p.splitk;
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const bool wide = p._pad == 2 || (p._pad != 1 && tiles2 >= 2LL * sms);
+  // (256-row CTAs with the raw-block ring fit in shared memory for Q4_K blocks only)
+  const bool wide_fits = !(p.qtype == QT_Q5_K || p.qtype == QT_Q6_K);
+  const bool wide = wide_fits && (p._pad == 2 || (p._pad != 1 && tiles2 >= 2LL * sms));
   return wide ? launch_gemm<256, 2>(p, st) : launch_gemm<256, 1>(p, st);
 }
 
