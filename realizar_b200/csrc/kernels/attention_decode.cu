@@ -19,439 +19,19 @@
 // src/cuda/executor/flash_decoding_graphed.rs:14-209, src/cuda/executor/batch.rs:18-400).
 #include "common.cuh"
 #include "attn_decode_static.h"
+#include "attention_decode_body.cuh"
 #include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <math.h>
 
-namespace cg = cooperative_groups;
-
 namespace rlz {
-
-constexpr int ATT_PAGE = 16;
-constexpr int ATT_THREADS = 128;     // 8 half-warps; each takes up to TB tokens per iteration (TB by head-group size, below)
-constexpr int ATT_WARPS = ATT_THREADS / 32;
-constexpr int ATT_PT_MAX = 64;       // page-table entries of a split staged in shared memory (1024 tokens)
-constexpr int ATT_MAX_CLUSTER = 8;   // portable cluster size
-enum { MERGE_GLOBAL = 0, MERGE_CLUSTER = 1, MERGE_NONE = 2 };
-
-struct AttnDecodeParams {
-  const float* qkv;        // [B, ld_qkv]: q heads | k heads | v heads (after bias)
-  float* out;              // [B, ld_out]: attention output, head-major
-  __nv_bfloat16* k_cache;     // bf16 rows, or int8 rows when kv_q8 (see below)
-  __nv_bfloat16* v_cache;
-  const int32_t* positions;   // [B]
-  const int32_t* page_table;  // [B, max_pages]
-  const float* q_norm_w;   // [head_dim] or null
-  const float* k_norm_w;   // [head_dim] or null
-  float* partial;          // scratch [B, H, splits, head_dim + 2]
-  int32_t* counters;       // scratch [B, n_kv_heads * head_groups], zero before first use
-  int64_t ld_qkv, ld_out;
-  int32_t n_heads, n_kv_heads, head_dim, max_pages;
-  int32_t rope_dim, rope_type, splits, batch;
-  int32_t q_off, k_off, v_off;         // element offsets of the q / k / v sections in a qkv row
-  int32_t pt_stride;                   // page_table elements between batch rows (0: every row shares one table)
-  float rope_theta, eps, scale;
-  int32_t no_append;                   // 1: the new rows are already in the cache (prefill), only attend
-  int32_t window;                      // > 0: attend to positions (pos - window, pos] only
-  int32_t rope_table_len;              // positions covered by rope_table
-  const float2* rope_table;            // [rope_table_len, rope_dim / 2] (cos, sin) or null
-  int32_t kv_q8;                       // 1: int8 cache rows of head_dim + 16 bytes (codes, then the fp32 scale of the row)
-  int32_t _pad3;
-};
-
-// ---- int8 KV rows: [head_dim codes][fp32 scale][12 bytes padding]; value = code * scale, scale = max|x| / 127 per (token, kv head) ----
-__device__ __forceinline__ int kv_row_bytes(int d, int q8) { return q8 ? d + 16 : 2 * d; }
-// four codes of a word -> floats: the biased byte goes into the mantissa of 2^23, the bias comes off exactly, then the scale
-__device__ __forceinline__ void q8_word_to_float(uint32_t w, float sc, float* out) {
-  const uint32_t b = w ^ 0x80808080u;                     // bias the code to 0..255; (2^23 + byte) - (2^23 + 128) is exact
-  out[0] = (__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7540)) - 8388736.f) * sc;
-  out[1] = (__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7541)) - 8388736.f) * sc;
-  out[2] = (__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7542)) - 8388736.f) * sc;
-  out[3] = (__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7543)) - 8388736.f) * sc;
-}
-__device__ __forceinline__ float q8_round(float x, float sc) {      // what the cache will return for x
-  return sc > 0.f ? fminf(127.f, fmaxf(-127.f, rintf(x / sc))) * sc : 0.f;
-}
-
-__device__ __forceinline__ void rope_inplace(float* v, int d_rot, int rope_type, int pos, float theta, const float2* table, int tid, int nthreads) {
-  const int half = d_rot >> 1;
-  for (int i = tid; i < half; i += nthreads) {
-    float sn, cs;
-    if (table) {
-      const float2 t = __ldg(table + (int64_t)pos * half + i);
-      cs = t.x; sn = t.y;
-    } else {
-      const float freq = powf(theta, -2.f * (float)i / (float)d_rot);
-      sincosf((float)pos * freq, &sn, &cs);
-    }
-    const int i0 = rope_type == 2 ? i : 2 * i, i1 = rope_type == 2 ? i + half : 2 * i + 1;
-    const float a = v[i0], b = v[i1];
-    v[i0] = a * cs - b * sn;
-    v[i1] = a * sn + b * cs;
-  }
-}
 
 template <int GT, int MERGE, int DEEP, int Q8>
 __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_constant__ AttnDecodeParams p) {
-  const int G = p.n_heads / p.n_kv_heads;
-  const int hgroups = (G + GT - 1) / GT;
-  const int kvh = blockIdx.x / hgroups, hg = blockIdx.x - kvh * hgroups;
-  const int split = blockIdx.y, b = blockIdx.z;
-  const int d = p.head_dim;
-  const int g0 = hg * GT, gn = min(GT, G - g0);          // query heads [g0, g0+gn) of this kv head
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int l16 = lane & 15, hw = tid >> 4;              // half-warp id 0..7
-
-  __shared__ float q_s[GT][128];
-  __shared__ float k_s[128], v_s[128];
-  __shared__ float part_s[ATT_WARPS][GT][128 + 2];   // per-warp partials
-  // MERGE_CLUSTER: up to 4 heads per CTA the splits PUSH their results into the gather buffer of cluster rank 0 and leave;
-  // with 8 heads the buffer would not fit in static shared memory and rank 0 pulls the peers' res_s instead
-  constexpr bool PUSH = MERGE == MERGE_CLUSTER && GT <= 4;
-  __shared__ float res_s[PUSH ? 1 : GT][128 + 2];
-  __shared__ float gat_s[PUSH ? ATT_MAX_CLUSTER : 1][PUSH ? GT : 1][128 + 2];
-  __shared__ int32_t pt_s[ATT_PT_MAX];      // physical pages of this split's token range
-  __shared__ float qs_s[2][ATT_THREADS / 32 + 1];   // int8 cache: max|k|, max|v| of the new row (per warp, then total)
-  __shared__ int last_flag;
-
+  __shared__ AttnSmem<GT, MERGE> sm;
   pdl_launch_dependents();
   pdl_wait();
-
-  const int pos = p.positions[b];
-  if (pos < 0) return;                                   // uniform over the cluster (same sequence)
-  if (PUSH) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");     // phase 1: "I have started"; waited on before the push
-  const int seq_len = pos + 1;
-  const int lo = p.window > 0 ? max(0, seq_len - p.window) : 0;      // first position attended to
-  const int lo_al = lo / ATT_PAGE * ATT_PAGE;
-  int chunk = (seq_len - lo_al + p.splits - 1) / p.splits;
-  chunk = (chunk + ATT_PAGE - 1) / ATT_PAGE * ATT_PAGE;
-  const int start = lo_al + split * chunk, end = min(seq_len, start + chunk);
-  const bool owner = !p.no_append && start <= pos && pos < end;
-
-  // ---- stage the split's page-table entries, q (this head group), and k/v of the new token: independent loads ----
-  const int32_t* pt = p.page_table + (int64_t)b * p.pt_stride;
-  const int npages = (max(0, end - start) + ATT_PAGE - 1) / ATT_PAGE;
-  const bool pt_staged = npages <= ATT_PT_MAX;
-  if (pt_staged && tid < npages) pt_s[tid] = pt[start / ATT_PAGE + tid];
-  const float* row = p.qkv + (int64_t)b * p.ld_qkv;
-  for (int i = tid; i < gn * d; i += ATT_THREADS) {
-    const int g = i / d, j = i - g * d;
-    q_s[g][j] = row[p.q_off + (kvh * G + g0 + g) * d + j];
-  }
-  if (owner) {
-    for (int j = tid; j < d; j += ATT_THREADS) {
-      k_s[j] = row[p.k_off + kvh * d + j];
-      v_s[j] = row[p.v_off + kvh * d + j];
-    }
-  }
-  __syncthreads();
-  if (p.q_norm_w) {      // per-head RMSNorm, one warp per head
-    for (int g = warp; g < gn + (owner ? 1 : 0); g += ATT_THREADS / 32) {
-      float* v = g < gn ? q_s[g] : k_s;
-      const float* w = g < gn ? p.q_norm_w : p.k_norm_w;
-      float ss = 0.f;
-      for (int j = lane; j < d; j += 32) ss += v[j] * v[j];
-      ss = warp_sum(ss);
-      const float r = rsqrtf(ss / (float)d + p.eps);
-      for (int j = lane; j < d; j += 32) v[j] = v[j] * r * w[j];
-    }
-    __syncthreads();
-  }
-  if (p.rope_dim > 0) {
-    const float2* tab = (p.rope_table && pos < p.rope_table_len) ? p.rope_table : nullptr;
-    for (int g = 0; g < gn; ++g) rope_inplace(q_s[g], p.rope_dim, p.rope_type, pos, p.rope_theta, tab, tid, ATT_THREADS);
-    if (owner) rope_inplace(k_s, p.rope_dim, p.rope_type, pos, p.rope_theta, tab, tid, ATT_THREADS);
-    __syncthreads();
-  }
-  constexpr int q8 = Q8;                                 // compile-time: the bf16 instantiation carries none of the int8 code
-  const int64_t rowb = kv_row_bytes(d, q8);              // bytes per cached row
-  float sck = 0.f, scv = 0.f;                            // int8 cache: scales of the new row
-  if (q8 && owner) {
-    float ak = 0.f, av = 0.f;
-    for (int j = tid; j < d; j += ATT_THREADS) { ak = fmaxf(ak, fabsf(k_s[j])); av = fmaxf(av, fabsf(v_s[j])); }
-    ak = warp_max(ak); av = warp_max(av);
-    if (lane == 0) { qs_s[0][warp] = ak; qs_s[1][warp] = av; }
-  }
-  if (q8) {
-    __syncthreads();
-    if (owner) {
-      for (int w = 0; w < ATT_THREADS / 32; ++w) { sck = fmaxf(sck, qs_s[0][w]); scv = fmaxf(scv, qs_s[1][w]); }
-      sck *= 1.f / 127.f; scv *= 1.f / 127.f;
-    }
-  }
-  if (owner && hg == 0) {   // append the new row to the cache (one head group does it)
-    const int page = pt[pos / ATT_PAGE], slot = pos % ATT_PAGE;
-    const int64_t rowi = ((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE + slot;
-    if (q8) {
-      int8_t* kd = (int8_t*)p.k_cache + rowi * rowb;
-      int8_t* vd = (int8_t*)p.v_cache + rowi * rowb;
-      for (int j = tid; j < d; j += ATT_THREADS) {
-        kd[j] = (int8_t)(sck > 0.f ? fminf(127.f, fmaxf(-127.f, rintf(k_s[j] / sck))) : 0.f);
-        vd[j] = (int8_t)(scv > 0.f ? fminf(127.f, fmaxf(-127.f, rintf(v_s[j] / scv))) : 0.f);
-      }
-      if (tid == 0) { *(float*)(kd + d) = sck; *(float*)(vd + d) = scv; }
-    } else {
-      const int64_t off = rowi * d;
-      for (int j = tid; j < d; j += ATT_THREADS) {
-        p.k_cache[off + j] = __float2bfloat16_rn(k_s[j]);
-        p.v_cache[off + j] = __float2bfloat16_rn(v_s[j]);
-      }
-    }
-  }
-  __syncthreads();
-
-  // ---- per-lane query slice: 8 dims, pre-scaled so that exp2 can be used ---------------------
-  const int j0 = l16 * 8;
-  const bool lane_ok = j0 < d;
-  const float qscale = p.scale * 1.4426950408889634f;
-  float q[GT][8], acc[GT][8], m[GT], l[GT];
-#pragma unroll
-  for (int g = 0; g < GT; ++g) {
-    m[g] = -INFINITY; l[g] = 0.f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { acc[g][j] = 0.f; q[g][j] = (g < gn && lane_ok) ? q_s[g][j0 + j] * qscale : 0.f; }
-  }
-
-  // the owner CTA of a non-zero head group reads the new row from shared memory instead of the
-  // cache (another CTA is writing it), everyone else reads the cache only
-  // shuffles stay inside a half-warp (all 16 lanes share base / validity), so each half uses its own mask
-  const unsigned hmask = 0xFFFFu << (lane & 16);
-  // tokens per half-warp per iteration: as many as the registers of this head-group size allow, so that a split of up
-  // to 8 * TB tokens (96 for MHA) has all its K/V loads in flight at once and pays the memory latency a single time
-  // (DEEP = 0, used when the grid already fills the GPU several times over: 4 tokens, fewer registers, more CTAs per SM)
-  constexpr int TB = !DEEP ? 4 : GT == 1 ? 12 : GT == 2 ? 10 : GT == 4 ? 8 : 4;
-  constexpr int TOK_IT = (ATT_THREADS / 16) * TB;
-  const int iters = (max(0, end - start) + TOK_IT - 1) / TOK_IT;
-  // head groups > 0 of the split that owns the new position read that row from shared memory (only the owner staged it)
-  const bool new_from_smem = owner && hg != 0;
-  for (int it = 0; it < iters; ++it) {
-    const int base = start + (it * (ATT_THREADS / 16) + hw) * TB;
-    uint4 kr[TB], vr[TB];
-#pragma unroll
-    for (int t = 0; t < TB; ++t) {
-      const int tok = base + t;
-      const bool okl = lane_ok && tok < end && !(new_from_smem && tok == pos);
-      const int tk = min(tok, end - 1 > start ? end - 1 : start);
-      const int page = pt_staged ? pt_s[(tk - start) / ATT_PAGE] : pt[tk / ATT_PAGE];
-      const int64_t rowi = ((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE + (tk % ATT_PAGE);
-      if (q8) {                                           // 8 codes (x, y) and the row scale (z)
-        const uint8_t* kp = (const uint8_t*)p.k_cache + rowi * rowb;
-        const uint8_t* vp = (const uint8_t*)p.v_cache + rowi * rowb;
-        const uint2 kc = okl ? *(const uint2*)(kp + j0) : make_uint2(0x80808080u ^ 0x80808080u, 0);
-        const uint2 vc = okl ? *(const uint2*)(vp + j0) : make_uint2(0, 0);
-        kr[t] = make_uint4(kc.x, kc.y, okl ? *(const uint32_t*)(kp + d) : 0u, 0u);
-        vr[t] = make_uint4(vc.x, vc.y, okl ? *(const uint32_t*)(vp + d) : 0u, 0u);
-      } else {
-        const int64_t off = rowi * d + j0;
-        kr[t] = okl ? *(const uint4*)(p.k_cache + off) : make_uint4(0, 0, 0, 0);
-        vr[t] = okl ? *(const uint4*)(p.v_cache + off) : make_uint4(0, 0, 0, 0);
-      }
-    }
-    float sc[GT][TB];
-    // pass 1: scores (K converted one token at a time)
-#pragma unroll
-    for (int t = 0; t < TB; ++t) {
-      float kf[8];
-      if (q8) {
-        const float sc = __uint_as_float(kr[t].z);
-        q8_word_to_float(kr[t].x, sc, kf); q8_word_to_float(kr[t].y, sc, kf + 4);
-      } else {
-        const uint32_t kw[4] = {kr[t].x, kr[t].y, kr[t].z, kr[t].w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) { kf[2 * j] = __uint_as_float(kw[j] << 16); kf[2 * j + 1] = __uint_as_float(kw[j] & 0xFFFF0000u); }
-      }
-      if (new_from_smem && base + t == pos && lane_ok) {   // new row straight from shared memory (rounded like the cache)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) kf[j] = q8 ? q8_round(k_s[j0 + j], sck) : __bfloat162float(__float2bfloat16_rn(k_s[j0 + j]));
-      }
-      const bool valid = base + t < end && base + t >= lo;
-#pragma unroll
-      for (int g = 0; g < GT; ++g) {
-        float x = 0.f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) x += q[g][j] * kf[j];
-        x += __shfl_xor_sync(hmask, x, 8);
-        x += __shfl_xor_sync(hmask, x, 4);
-        x += __shfl_xor_sync(hmask, x, 2);
-        x += __shfl_xor_sync(hmask, x, 1);
-        sc[g][t] = valid ? x : -INFINITY;
-      }
-    }
-    // running max / rescale per head, scores -> probabilities
-#pragma unroll
-    for (int g = 0; g < GT; ++g) {
-      float mn = m[g];
-#pragma unroll
-      for (int t = 0; t < TB; ++t) mn = fmaxf(mn, sc[g][t]);
-      const bool none = mn == -INFINITY;       // nothing valid seen yet by this stream
-      const float corr = none ? 1.f : exp2f(m[g] - mn);     // m = -inf on the first valid pass -> 0
-      l[g] *= corr;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc[g][j] *= corr;
-#pragma unroll
-      for (int t = 0; t < TB; ++t) { sc[g][t] = none ? 0.f : exp2f(sc[g][t] - mn); l[g] += sc[g][t]; }
-      m[g] = mn;
-    }
-    // pass 2: weighted values (V converted one token at a time)
-#pragma unroll
-    for (int t = 0; t < TB; ++t) {
-      float vf[8];
-      if (q8) {
-        const float sc = __uint_as_float(vr[t].z);
-        q8_word_to_float(vr[t].x, sc, vf); q8_word_to_float(vr[t].y, sc, vf + 4);
-      } else {
-        const uint32_t vw[4] = {vr[t].x, vr[t].y, vr[t].z, vr[t].w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) { vf[2 * j] = __uint_as_float(vw[j] << 16); vf[2 * j + 1] = __uint_as_float(vw[j] & 0xFFFF0000u); }
-      }
-      if (new_from_smem && base + t == pos && lane_ok) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) vf[j] = q8 ? q8_round(v_s[j0 + j], scv) : __bfloat162float(__float2bfloat16_rn(v_s[j0 + j]));
-      }
-#pragma unroll
-      for (int g = 0; g < GT; ++g)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[g][j] += sc[g][t] * vf[j];
-    }
-  }
-
-  // ---- combine: the two half-warps of a warp through shuffles, then the warps through shared memory ----
-#pragma unroll
-  for (int g = 0; g < GT; ++g) {
-    const float mo = __shfl_xor_sync(0xFFFFFFFFu, m[g], 16), lo2 = __shfl_xor_sync(0xFFFFFFFFu, l[g], 16);
-    const float mm = fmaxf(m[g], mo);
-    const float c0 = m[g] == -INFINITY ? 0.f : exp2f(m[g] - mm), c1 = mo == -INFINITY ? 0.f : exp2f(mo - mm);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float ao = __shfl_xor_sync(0xFFFFFFFFu, acc[g][j], 16);
-      acc[g][j] = c0 * acc[g][j] + c1 * ao;
-    }
-    l[g] = c0 * l[g] + c1 * lo2;
-    m[g] = mm;
-  }
-  // ---- combine the 8 half-warp streams of this CTA -------------------------------------------
-#pragma unroll
-  for (int g = 0; g < GT; ++g) {
-    if (g < gn && lane < 16) {
-      if (lane_ok) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) part_s[warp][g][j0 + j] = acc[g][j];
-      }
-      if (lane == 0) { part_s[warp][g][128] = m[g]; part_s[warp][g][129] = l[g]; }
-    }
-  }
-  __syncthreads();
-  const int S = p.splits;
-  float* push_dst = nullptr;                              // (push mode) this split's slot in rank 0's gather buffer
-  if (PUSH) {
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");               // phase 1 complete: every CTA of the cluster is running
-    push_dst = cg::this_cluster().map_shared_rank(&gat_s[0][0][0], 0) + (int64_t)split * GT * 130;
-  }
-  for (int i = tid; i < gn * d + gn; i += ATT_THREADS) {
-    const bool stat = i >= gn * d;                 // the trailing gn items carry (max, sum) of each head
-    const int g = stat ? i - gn * d : i / d, j = stat ? 0 : i - g * d;
-    float mm = -INFINITY;
-    for (int w = 0; w < ATT_WARPS; ++w) mm = fmaxf(mm, part_s[w][g][128]);
-    float a = 0.f, ll = 0.f;
-    for (int w = 0; w < ATT_WARPS; ++w) {
-      const float mw = part_s[w][g][128];
-      const float c = mw == -INFINITY ? 0.f : exp2f(mw - mm);
-      a += c * part_s[w][g][j]; ll += c * part_s[w][g][129];
-    }
-    if (MERGE == MERGE_NONE) {
-      if (!stat) p.out[(int64_t)b * p.ld_out + (kvh * G + g0 + g) * d + j] = a / ll;
-    } else if (MERGE == MERGE_CLUSTER) {
-      if (PUSH) {                                          // straight into rank 0's shared memory
-        if (stat) { push_dst[g * 130 + 128] = mm; push_dst[g * 130 + 129] = ll; } else push_dst[g * 130 + j] = a;
-      } else {
-        if (stat) { res_s[g][128] = mm; res_s[g][129] = ll; } else res_s[g][j] = a;
-      }
-    } else {
-      float* dst = p.partial + (((int64_t)b * p.n_heads + kvh * G + g0 + g) * S + split) * (d + 2);
-      if (stat) { dst[d] = mm; dst[d + 1] = ll; } else dst[j] = a;
-    }
-  }
-  if (MERGE == MERGE_NONE) return;
-
-  if (MERGE == MERGE_CLUSTER && PUSH) {
-    // ---- every split stores its result into rank 0's gather buffer, signals, and leaves; rank 0 merges locally ----
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");             // phase 2: my stores are done
-    if (cg::this_cluster().block_rank() != 0) return;
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-    for (int i = tid; i < gn * d; i += ATT_THREADS) {
-      const int g = i / d, j = i - g * d;
-      float mm = -INFINITY;
-#pragma unroll
-      for (int sp = 0; sp < ATT_MAX_CLUSTER; ++sp) if (sp < S) mm = fmaxf(mm, gat_s[sp][g][128]);
-      float a = 0.f, ll = 0.f;
-#pragma unroll
-      for (int sp = 0; sp < ATT_MAX_CLUSTER; ++sp) {
-        if (sp < S) {
-          const float ms = gat_s[sp][g][128];
-          const float c = ms == -INFINITY ? 0.f : exp2f(ms - mm);
-          a += c * gat_s[sp][g][j]; ll += c * gat_s[sp][g][129];
-        }
-      }
-      p.out[(int64_t)b * p.ld_out + (kvh * G + g0 + g) * d + j] = a / ll;
-    }
-    return;
-  }
-  if (MERGE == MERGE_CLUSTER) {
-    // ---- (8 heads per CTA) cluster rank 0 merges the splits out of its peers' shared memory ----------------------
-    cg::cluster_group cluster = cg::this_cluster();
-    cluster.sync();                                  // every CTA's res_s is complete and visible
-    if (cluster.block_rank() == 0) {
-      // the loops over the splits are unrolled to the cluster size so that the remote loads are independent and in flight together
-      for (int i = tid; i < gn * d; i += ATT_THREADS) {
-        const int g = i / d, j = i - g * d;
-        float ms[ATT_MAX_CLUSTER], av[ATT_MAX_CLUSTER], lv[ATT_MAX_CLUSTER];
-#pragma unroll
-        for (int sp = 0; sp < ATT_MAX_CLUSTER; ++sp) {
-          const float* r = cluster.map_shared_rank(&res_s[0][0], sp < S ? sp : 0) + g * 130;
-          ms[sp] = sp < S ? r[128] : -INFINITY; av[sp] = r[j]; lv[sp] = r[129];
-        }
-        float mm = -INFINITY;
-#pragma unroll
-        for (int sp = 0; sp < ATT_MAX_CLUSTER; ++sp) mm = fmaxf(mm, ms[sp]);
-        float a = 0.f, ll = 0.f;
-#pragma unroll
-        for (int sp = 0; sp < ATT_MAX_CLUSTER; ++sp) {
-          const float c = ms[sp] == -INFINITY ? 0.f : exp2f(ms[sp] - mm);
-          a += c * av[sp]; ll += c * lv[sp];
-        }
-        p.out[(int64_t)b * p.ld_out + (kvh * G + g0 + g) * d + j] = a / ll;
-      }
-    }
-    cluster.sync();                                  // peers keep their shared memory alive until rank 0 has read it
-    return;
-  }
-
-  // ---- last CTA of this (sequence, kv head, head group) merges the splits ----------------------
-  __threadfence();
-  __syncthreads();
-  int32_t* ctr = p.counters + (int64_t)b * (p.n_kv_heads * hgroups) + blockIdx.x;
-  if (tid == 0) {
-    const int ticket = atomicAdd(ctr, 1);
-    last_flag = ticket == S - 1;
-    if (last_flag) *ctr = 0;       // self-cleaning for the next launch
-  }
-  __syncthreads();
-  if (!last_flag) return;
-  __threadfence();
-  for (int i = tid; i < gn * d; i += ATT_THREADS) {
-    const int g = i / d, j = i - g * d;
-    const float* src = p.partial + ((int64_t)b * p.n_heads + kvh * G + g0 + g) * S * (d + 2);
-    float mm = -INFINITY;
-    for (int s = 0; s < S; ++s) mm = fmaxf(mm, __ldcg(src + (int64_t)s * (d + 2) + d));
-    float a = 0.f, ll = 0.f;
-    for (int s = 0; s < S; ++s) {
-      const float ms = __ldcg(src + (int64_t)s * (d + 2) + d);
-      const float c = ms == -INFINITY ? 0.f : exp2f(ms - mm);
-      a += c * __ldcg(src + (int64_t)s * (d + 2) + j);
-      ll += c * __ldcg(src + (int64_t)s * (d + 2) + d + 1);
-    }
-    p.out[(int64_t)b * p.ld_out + (kvh * G + g0 + g) * d + j] = a / ll;
-  }
+  attn_decode_body<GT, MERGE, DEEP, Q8, 0, false>(p, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, (int)threadIdx.x, sm, 0);
 }
 
 // Validate and launch: picks the head-group tile and the merge strategy.

@@ -18,6 +18,7 @@ same kernels.
 """
 from __future__ import annotations
 
+import logging
 import os
 from dataclasses import dataclass, field
 from typing import Callable, List, Optional, Sequence
@@ -31,6 +32,8 @@ from ..ops import (ACT_GELU, ACT_NONE, COMBINE_ADD, COMBINE_GELU_MUL, COMBINE_SI
 from ..quant import BLOCK_SPECS, QType, row_bytes
 from .config import ModelConfig
 from .weights import ModelWeights, QTensor
+
+log = logging.getLogger(__name__)
 
 
 def _f32(t: Optional[QTensor], device) -> Optional[torch.Tensor]:
@@ -263,8 +266,10 @@ class DecodePlan:
     def __init__(self, sm_count: int = 148):
         self.sm_count = sm_count
         self.thunks: List[Callable[[], None]] = []
+        self.records: list = []             # one entry per thunk: ("gemv", params) | ("attn", params) | ("embed", args) | ("argmax", args) | None
         self.keep: list = []
         self.kernel_launches = 0
+        self.program = None                 # persistent step program, when the plan was compiled into one
         self._side: Optional[torch.cuda.Stream] = None
         self._side_mode = False
         self._ev_fork: Optional[torch.cuda.Event] = None
@@ -281,6 +286,7 @@ class DecodePlan:
             self._ev_fork.record()
             self._side.wait_event(self._ev_fork)
         self.thunks.append(_fork)
+        self.records.append(None)
         self._side_mode = True
 
     def end_fork(self) -> None:
@@ -291,22 +297,25 @@ class DecodePlan:
             self._ev_join.record(self._side)
             torch.cuda.current_stream().wait_event(self._ev_join)
         self.thunks.append(_join)
+        self.records.append(None)
 
-    def _push(self, fn) -> None:
+    def _push(self, fn, record=None) -> None:
         if self._side_mode:
             def on_side(fn=fn):
                 with torch.cuda.stream(self._side):
                     fn()
             self.thunks.append(on_side)
+            self.records.append(None)
         else:
             self.thunks.append(fn)
+            self.records.append(record)
 
     def add_gemv(self, p, stream=False, tag=""):
         self.keep.append(p)
         if tag and tag in _DIAG_SKIP:
             return
         fn = ops.gemv_stream_launch if stream else ops.gemv_launch
-        self._push(lambda p=p, fn=fn: fn(p))
+        self._push(lambda p=p, fn=fn: fn(p), None if stream else ("gemv", p))
         self.kernel_launches += 1
 
     def add_gemv_auto(self, xs, mats, y, batch, ldy, residual=None, ld_res=None, target_ctas=296, ar=None, tag=""):
@@ -337,18 +346,68 @@ class DecodePlan:
         if "attn" in _DIAG_SKIP:
             return
         self.thunks.append(lambda p=p: ops.attn_decode_launch(p))
+        self.records.append(("attn", p))
         self.kernel_launches += 1
 
-    def add(self, fn, launches=1):
+    def add(self, fn, launches=1, record=None):
         self.thunks.append(fn)
+        self.records.append(record)
         self.kernel_launches += launches
+
+    def compile_persistent(self, device, occ: int, attn_gt: int) -> bool:
+        """Fuse the leading run of embedding / GEMV / attention / argmax launches into one persistent
+        cooperative kernel (``ops.step_program``).  Returns False, leaving the plan untouched, when the
+        run is too short or holds an operation the step kernel does not take."""
+        from ..ops.step_program import StepProgramBuilder
+        n = 0
+        while n < len(self.records) and self.records[n] is not None:
+            n += 1
+            if self.records[n - 1][0] == "argmax":
+                break
+        if n < 3:
+            return False
+        b = StepProgramBuilder(ops.lib(), device, occ, attn_gt, self.sm_count)
+        slots = b.grid * 4
+        scratch = None
+        try:
+            for kind, arg in self.records[:n]:
+                if kind == "gemv":
+                    b.add_gemv(arg)
+                elif kind == "attn":
+                    q = type(arg).from_buffer_copy(bytes(arg))
+                    gx = q.n_kv_heads * -(-(q.n_heads // q.n_kv_heads) // attn_gt)
+                    q.splits = max(1, min(32, slots // max(1, gx)))
+                    if scratch is None:
+                        scratch = (torch.zeros(q.n_heads * q.splits * (q.head_dim + 2), dtype=torch.float32, device=device),
+                                   torch.zeros(max(1, q.n_heads), dtype=torch.int32, device=device))
+                        self.keep.append(scratch)
+                    q.partial, q.counters = scratch[0].data_ptr(), scratch[1].data_ptr()
+                    b.add_attn(q)
+                elif kind == "embed":
+                    b.add_embed(*arg)
+                else:
+                    b.add_argmax(*arg)
+            program = b.finish()
+        except ValueError as e:
+            log.info("decode plan stays one launch per operation: %s", e)
+            return False
+        self.program = program
+        rest = self.thunks[n:]
+
+        def launch_program(program=program):
+            ops.check(program.launch(ops.stream_ptr()), "decode_step")
+        self.thunks = [launch_program] + rest
+        self.records = [None] * len(self.thunks)
+        self.kernel_launches = self.kernel_launches - n + 1
+        return True
 
     def run(self):
         for t in self.thunks:
             t()
 
 
-def emit_head(plan: "DecodePlan", model: GpuModel, buf: StepBuffers, r0: int, batch: int, comm, greedy_only: bool, sm_count: int) -> None:
+def emit_head(plan: "DecodePlan", model: GpuModel, buf: StepBuffers, r0: int, batch: int, comm, greedy_only: bool, sm_count: int,
+              target_ctas: Optional[int] = None) -> None:
     """Final norm + lm_head + token selection for rows ``r0 .. r0+batch-1`` of the step buffers."""
     cfg = model.cfg
     H = cfg.hidden_dim
@@ -357,7 +416,8 @@ def emit_head(plan: "DecodePlan", model: GpuModel, buf: StepBuffers, r0: int, ba
         cb = min(4, batch - c0)
         xin = VecIn(buf.x[r0 + c0:], H, ld=buf.x.stride(0), norm=norm_t, norm_w=model.out_norm_w, norm_b=model.out_norm_b, eps=cfg.eps)
         plan.add_gemv_auto([xin], [MatOut([(model.lm_head, 0)], bias=model.lm_head_b)], buf.logits[r0 + c0:], cb,
-                           buf.logits.stride(0), target_ctas=int(os.environ.get("RLZ_GEMV_CTAS", 2 * sm_count if cb <= 1 else sm_count)))
+                           buf.logits.stride(0),
+                           target_ctas=target_ctas or int(os.environ.get("RLZ_GEMV_CTAS", 2 * sm_count if cb <= 1 else sm_count)))
     emit_select(plan, model, buf, r0, batch, comm, greedy_only)
 
 
@@ -382,7 +442,8 @@ def emit_select(plan: "DecodePlan", model: GpuModel, buf: StepBuffers, r0: int, 
             ops.sample_launch(sp_full)
         plan.add(pick_sampled, launches=1)
     elif greedy_only:
-        plan.add(lambda: ops.argmax(buf.logits[rows], out=buf.sampled[rows], vocab=V))
+        plan.add(lambda: ops.argmax(buf.logits[rows], out=buf.sampled[rows], vocab=V),
+                 record=("argmax", (buf.logits[rows], V, buf.sampled[rows])) if batch == 1 else None)
     else:
         sp = ops.build_sample_params(buf.logits[rows], buf.temperature[rows], buf.top_k[rows], buf.top_p[rows], buf.uniform[rows],
                                      buf.sampled[rows], buf.min_p[rows], vocab=V)
@@ -391,7 +452,8 @@ def emit_select(plan: "DecodePlan", model: GpuModel, buf: StepBuffers, r0: int, 
 
 
 def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, v_cache: torch.Tensor, batch: int, splits: int,
-                      comm=None, greedy_only: bool = False, sm_count: int = 148, layer_subset: Optional[Sequence[int]] = None) -> DecodePlan:
+                      comm=None, greedy_only: bool = False, sm_count: int = 148, layer_subset: Optional[Sequence[int]] = None,
+                      persistent: bool = False) -> DecodePlan:
     """Create the launch plan for ``batch`` sequences (rows 0..batch-1 of the step buffers).
     ``layer_subset`` restricts the pass to those layers (the layer-skipping draft of self-speculative decoding).
 
@@ -405,6 +467,17 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
     norm_t = NORM_LAYER if cfg.uses_layernorm else NORM_RMS
     tp = model.tp_size > 1
     target = int(os.environ.get("RLZ_GEMV_CTAS", 2 * sm_count if batch <= 1 else sm_count))   # register-path kernel: 2 CTAs/SM at batch 1
+    # persistent step kernel (batch 1, one GPU): the whole step is one cooperative launch; its grid is 2 CTAs per SM for
+    # multi-head attention and 1 CTA per SM (twice the registers) when an attention job carries several query heads
+    p_occ = p_gt = 0
+    if persistent and batch == 1 and model.tp_size == 1:
+        G = model.heads // max(1, model.kv_heads)
+        p_gt = 1 if G == 1 else 2 if G == 2 else 0 if G == 8 else 4
+        p_occ = int(os.environ.get("RLZ_PERSIST_OCC", 2 if p_gt == 1 else 1)) if p_gt else 0
+        if p_occ == 2 and p_gt != 1:
+            p_occ = 1
+        if p_occ:
+            target = p_occ * sm_count
     chunks = [(c, min(4, batch - c)) for c in range(0, batch, 4)]       # GEMV kernels take <= 4 rows at a time
     # batch 1, one GPU: the launch that produces the MLP activation also writes it as the int8 block that the down-projection
     # launch stages, so all of that launch's CTAs copy 1.9 bytes per value instead of reading 4 and quantising
@@ -417,7 +490,9 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
     ld1 = buf.y1.stride(0)
 
     plan.add(lambda: ops.embed(model.embed_table, model.embed_qtype, model.embed_row_bytes, H, cfg.vocab_size, buf.tokens[:batch], buf.x,
-                               model.pos_table, buf.positions))
+                               model.pos_table, buf.positions),
+             record=("embed", (model.embed_table, model.embed_qtype, model.embed_row_bytes, H, cfg.vocab_size, buf.tokens[:batch], buf.x,
+                               model.pos_table, buf.positions)) if batch == 1 else None)
 
     fused = tp and getattr(comm, "fused", False)
     site = [0]
@@ -499,6 +574,8 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
             row_parallel(lambda c0: [VecIn(buf.act[c0:], L.down.k, ld=buf.act.stride(0), pre=buf.act_q if handoff(L) else None)],
                          lambda res: MatOut([(L.down, 0)], bias=L.down_b, residual=res))
 
-    emit_head(plan, model, buf, 0, batch, comm, greedy_only, sm_count)
+    emit_head(plan, model, buf, 0, batch, comm, greedy_only, sm_count, target_ctas=target if p_occ else None)
     plan.ar_sites = site[0]
+    if p_occ:
+        plan.compile_persistent(buf.x.device, p_occ, p_gt)
     return plan

@@ -77,6 +77,24 @@ class GemmParams(Structure):
                 ("ar_rows", c_int32), ("ar_enabled", c_int32), ("ar_site", c_int32), ("ar_nsites", c_int32), ("ar_splits", c_int32), ("_pad2", c_int32)]
 
 
+class StepOp(Structure):
+    _fields_ = [("kind", c_int32), ("grid", c_int32), ("params", c_int64)]
+
+
+class StepEmbed(Structure):
+    _fields_ = [("table", c_void_p), ("tokens", c_void_p), ("pos_table", c_void_p), ("positions", c_void_p), ("out", c_void_p),
+                ("row_bytes", c_int64), ("qtype", c_int32), ("hidden", c_int32), ("vocab", c_int32), ("_pad", c_int32)]
+
+
+class StepArgmax(Structure):
+    _fields_ = [("logits", c_void_p), ("out", c_void_p), ("out_val", c_void_p), ("vocab", c_int32), ("index_offset", c_int32)]
+
+
+class StepProgram(Structure):
+    _fields_ = [("blob", c_void_p), ("sync", c_void_p), ("status", c_void_p), ("spin_limit", c_int64), ("nops", c_int32),
+                ("occ", c_int32), ("attn_gt", c_int32), ("skip", c_int32)]
+
+
 def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_launch_count.restype = c_longlong
     lib.rlz_set_pdl.argtypes = [c_int]
@@ -85,6 +103,11 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_cuda_error_string.restype = ctypes.c_char_p
     lib.rlz_gemv.argtypes = [POINTER(GemvParams), c_void_p]
     lib.rlz_gemv_stream.argtypes = [POINTER(GemvParams), c_void_p]
+    lib.rlz_gemv_prepare.argtypes = [POINTER(GemvParams), POINTER(c_int)]
+    lib.rlz_gemv_smem_bytes.argtypes = [POINTER(GemvParams)]
+    lib.rlz_gemv_smem_bytes.restype = c_longlong
+    lib.rlz_decode_step.argtypes = [POINTER(StepProgram), c_longlong, c_void_p]
+    lib.rlz_decode_step_attn_smem.argtypes = [c_int]
     lib.rlz_device_error.argtypes = [c_int]
     lib.rlz_gemm_kquant.argtypes = [POINTER(GemmParams), c_void_p]
     lib.rlz_gemm_error.argtypes = [c_int]

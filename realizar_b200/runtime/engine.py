@@ -14,6 +14,7 @@ src/cuda/executor/layers/forward_graphed_decode.rs:18-211) and with its batched 
 from __future__ import annotations
 
 import logging
+import os
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
@@ -40,6 +41,7 @@ class EngineConfig:
     pdl: bool = True                       # programmatic dependent launch between kernels
     attn_splits: int = 0                   # 0 = choose from the SM count
     greedy_only: bool = False              # compile plans with argmax instead of the sampling kernel
+    persistent_step: Optional[bool] = None # batch-1 step as one persistent cooperative kernel (None: RLZ_PERSISTENT, default off)
     prefill_chunk: int = 512               # tokens per tensor-core prefill pass
     batched_prefill_min: int = 8           # shorter prompts go through the decode kernels token by token
     gemm_decode_min_batch: int = 16        # decode batches at least this large run on the tensor-core GEMM path
@@ -155,8 +157,14 @@ class DecodeEngine:
             self._plans[bucket] = self._batched_step_plan(bucket)
         if bucket not in self._plans:
             self._plans[bucket] = build_decode_plan(self.model, self.buf, self.kv[0], self.kv[1], bucket, self.splits, self.comm,
-                                                    self.cfg.greedy_only, self.sm_count)
+                                                    self.cfg.greedy_only, self.sm_count, persistent=self._persistent_ok(bucket))
         return self._plans[bucket]
+
+    def _persistent_ok(self, bucket: int) -> bool:
+        want = self.cfg.persistent_step
+        if want is None:
+            want = os.environ.get("RLZ_PERSISTENT", "0") != "0"
+        return bool(want) and bucket == 1 and self.comm is None and self.cfg.kv_dtype != "q8"
 
     def kernels_per_step(self, bucket: int) -> int:
         p = self.plan(bucket)
@@ -220,6 +228,14 @@ class DecodeEngine:
     def run_step(self, batch: int) -> None:
         """Issue one decode step for slots ``0..batch-1`` on the current stream."""
         bucket = self.bucket_for(batch)
+        plan = self.plan(bucket)
+        if plan.program is not None:
+            # one cooperative launch (plus token selection when it is not an argmax): nothing for a graph to save
+            plan.run()
+            self.steps_run += 1
+            if self.steps_run % 256 == 0:
+                plan.program.check()
+            return
         if self.cfg.cuda_graphs:
             g = self._graphs.get(bucket)
             if g is None:
