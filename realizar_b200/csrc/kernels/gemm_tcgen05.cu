@@ -166,6 +166,17 @@ __device__ __forceinline__ void store_half_row_sw128(uint8_t* tile, int r, int h
 
 // RT = 128-row weight tiles per CTA (1 or 2).  With RT = 2 the CTA owns 256 weight rows, keeps two accumulators in TMEM
 // and issues two MMAs per K slice that share the activation tile, which halves the activation traffic from L2 per FLOP.
+// Optional phase trace (diagnostics): thread 0 of each of the first GM_TRACE_CTAS CTAs records the global timer at fixed points.
+constexpr int GM_TRACE_CTAS = 1024, GM_TRACE_PTS = 8;
+__device__ int g_gemm_trace_on = 0;
+__device__ unsigned long long g_gemm_trace[GM_TRACE_CTAS * GM_TRACE_PTS];
+__device__ __forceinline__ void gm_trace(bool on, int cta, int pt) {
+  if (on) {
+    unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_gemm_trace[cta * GM_TRACE_PTS + pt] = t;
+  }
+}
+
 // K-quant weights do not go through the load/store units at all: a third single-thread role streams the raw 256-weight
 // blocks of the CTA's rows with TMA (box = rows x block bytes) into a two-deep shared-memory ring, one block per four K steps,
 // and the dequant warps read their row's bytes from there.  Row-strided 16-byte global loads (one sector per lane) were the
@@ -173,10 +184,13 @@ __device__ __forceinline__ void store_half_row_sw128(uint8_t* tile, int r, int h
 template <int NT, int QT, int RT> struct GemmCfg {
   static constexpr bool RAWTMA = QT == QT_Q4_K || QT == QT_Q5_K || QT == QT_Q6_K;
   static constexpr int ROWS = RT * GM_ROWS;
-  static constexpr int STAGES = RAWTMA ? (RT == 2 ? 2 : NT == 256 ? 3 : 4) : (RT == 2 ? 3 : 4);
+  // token tiles <= 64 (decode batches, K split across CTAs): shared memory is kept under half an SM so that two CTAs are
+  // resident and the split-K grid runs as one wave; the ring is shallow because the dequant warps, not the MMAs, set the pace
+  static constexpr int STAGES = RAWTMA ? (RT == 2 ? 2 : NT == 256 ? 3 : NT <= 64 ? (BlockBytes<QT>::value <= 144 ? 3 : 2) : 4) : (RT == 2 ? 3 : 4);
   static constexpr int RAW_BYTES = RAWTMA ? ROWS * BlockBytes<QT>::value : 0;      // one ring slot
   static constexpr int STAGE = ROWS * 128 + NT * 128;
   static constexpr size_t SMEM = (size_t)STAGES * STAGE + 2 * RAW_BYTES + 1024;
+  static_assert(NT > 64 || !RAWTMA || 2 * SMEM <= 226 * 1024, "decode-size tiles must fit twice per SM");
   static constexpr int THREADS = RT * GM_PRODUCERS + 96;                           // dequant warps + B TMA + MMA + raw TMA
 };
 
@@ -193,6 +207,9 @@ __global__ void __launch_bounds__(RT * GM_PRODUCERS + 96) gemm_kquant_tcgen05_ke
   __shared__ int failed_s;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * ROWS, m0 = blockIdx.y * NT;
+  const int cta_lin = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
+  const bool tr = tid == 0 && cta_lin < GM_TRACE_CTAS && g_gemm_trace_on;
+  gm_trace(tr, cta_lin, 0);
   uint8_t* sm = (uint8_t*)(((uintptr_t)gsm + 1023) & ~(uintptr_t)1023);
   constexpr int A_BYTES = ROWS * 128, B_BYTES = NT * 128, STAGE = A_BYTES + B_BYTES;
   constexpr uint32_t TMEM_COLS = RT * NT < 32 ? 32 : RT * NT;
@@ -218,8 +235,10 @@ __global__ void __launch_bounds__(RT * GM_PRODUCERS + 96) gemm_kquant_tcgen05_ke
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_d = tmem_base_s;
+  gm_trace(tr, cta_lin, 1);
   pdl_launch_dependents();
   pdl_wait();
+  gm_trace(tr, cta_lin, 2);
 
   // K range of this split
   const int ksteps_total = p.k / GM_KSTEP;
@@ -242,6 +261,7 @@ __global__ void __launch_bounds__(RT * GM_PRODUCERS + 96) gemm_kquant_tcgen05_ke
         if (it == 0 || g == 0) {                            // first step of a block: its bytes have landed
           ok = gm_wait(&raw_full[rb], (uint32_t)(kbi >> 1) & 1u);
           if (!ok) break;
+          if (it == 0) gm_trace(tr, cta_lin, 3);
         }
         if (it >= GM_STAGES) {                              // the MMAs that read this stage GM_STAGES steps ago are done
           ok = gm_wait(&empty_bar[s], (uint32_t)(it / GM_STAGES - 1) & 1u);
@@ -344,11 +364,13 @@ __global__ void __launch_bounds__(RT * GM_PRODUCERS + 96) gemm_kquant_tcgen05_ke
     }
   }
   if (!ok) { failed_s = 1; atomicExch(&g_gemm_error, 3001); }
+  gm_trace(tr, cta_lin, 4);
 
   // ---- epilogue: TMEM lane = weight row, column = token; each warp a lane quarter x column half (x row tile) ----
   // (a K split without work still pushes zeros in all-reduce mode: the reducer counts on every writer)
   if (warp < PWARPS && (nit > 0 || p.ar_enabled)) {
     if (ok && nit > 0 && !gm_wait(&done_bar, 0u)) { ok = false; failed_s = 1; atomicExch(&g_gemm_error, 3001); }
+    gm_trace(tr, cta_lin, 5);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     constexpr int COLS_PER_WARP = NT >= 64 ? NT / 2 : NT;
     const int q = warp & 3, chalf = (warp >> 2) & 1, rt = warp >> 3;
@@ -409,6 +431,7 @@ __global__ void __launch_bounds__(RT * GM_PRODUCERS + 96) gemm_kquant_tcgen05_ke
       }
     }
   }
+  gm_trace(tr, cta_lin, 6);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (failed_s && warp == PWARPS && lane == 0) {
@@ -534,6 +557,17 @@ int rlz_gemm_kquant(const rlz::GemmParams* pp, void* stream) {
   const bool wide_fits = !(p.qtype == QT_Q5_K || p.qtype == QT_Q6_K);
   const bool wide = wide_fits && (p._pad == 2 || (p._pad != 1 && tiles2 >= 2LL * sms));
   return wide ? launch_gemm<256, 2>(p, st) : launch_gemm<256, 1>(p, st);
+}
+
+// Diagnostics: switch the phase trace on/off; `rlz_gemm_trace_read` copies the records (GM_TRACE_PTS timestamps in ns per CTA:
+// entry, set-up done, dependency wait done, first weight block landed, producer loop done, MMAs done, epilogue done).
+int rlz_gemm_trace_enable(int on) {
+  const int v = on ? 1 : 0;
+  return (int)cudaMemcpyToSymbol(rlz::g_gemm_trace_on, &v, sizeof(int));
+}
+int rlz_gemm_trace_read(unsigned long long* out, int ctas) {
+  if (ctas < 1 || ctas > rlz::GM_TRACE_CTAS) return -1;
+  return (int)cudaMemcpyFromSymbol(out, rlz::g_gemm_trace, sizeof(unsigned long long) * ctas * rlz::GM_TRACE_PTS);
 }
 
 int rlz_sizeof_gemm_params() { return (int)sizeof(rlz::GemmParams); }

@@ -111,6 +111,8 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_device_error.argtypes = [c_int]
     lib.rlz_gemm_kquant.argtypes = [POINTER(GemmParams), c_void_p]
     lib.rlz_gemm_error.argtypes = [c_int]
+    lib.rlz_gemm_trace_enable.argtypes = [c_int]
+    lib.rlz_gemm_trace_read.argtypes = [c_void_p, c_int]
     lib.rlz_symm_alloc.argtypes = [ctypes.c_ulonglong, POINTER(c_void_p), c_void_p]
     lib.rlz_symm_open.argtypes = [c_void_p, POINTER(c_void_p)]
     lib.rlz_symm_close.argtypes = [c_void_p]

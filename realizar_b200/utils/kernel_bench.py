@@ -139,13 +139,46 @@ def bench_gemm(a):
     w = random_weight(a.n, a.k, qt, dev)
     x = (torch.randn(a.m, a.k, device=dev)).to(torch.bfloat16)
     y = torch.empty(a.m, a.n, device=dev, dtype=torch.float32)
-    plan = gemm_ops.GemmPlan(w, a.m, dev, wide=a.wide)
+    plan = gemm_ops.GemmPlan(w, a.m, dev, splitk=a.splitk or None, wide=a.wide)
     ms = time_cuda(lambda: plan.run(x, y), a.iters)
+    trace = None
+    if a.trace:
+        trace = gemm_phase_trace(lambda: plan.run(x, y))
     flops = 2.0 * a.m * a.n * a.k
     pk = peaks()
     return {"kernel": "gemm_kquant_tcgen05", "qtype": a.qtype, "m": a.m, "n": a.n, "k": a.k, "wide": a.wide, "splitk": plan.splitk, "ms": ms, "tflops": flops / ms / 1e9,
             "frac_of_%s_bf16" % pk["source"]: flops / ms / 1e9 / pk["bf16_tflops"],
-            "weight_gbs": w.nbytes / ms / 1e6, "frac_of_%s_hbm_weights" % pk["source"]: w.nbytes / ms / 1e6 / pk["hbm_gbs"]}
+            "weight_gbs": w.nbytes / ms / 1e6, "frac_of_%s_hbm_weights" % pk["source"]: w.nbytes / ms / 1e6 / pk["hbm_gbs"],
+            **({"phase_trace_us": trace} if trace else {})}
+
+
+def gemm_phase_trace(run) -> dict:
+    """Run one launch with the kernel's phase trace on; medians over CTAs of the time spent in each phase (microseconds)."""
+    import ctypes
+    import numpy as np
+    from .. import ops
+    lib = ops.lib()
+    ops.check(lib.rlz_gemm_trace_enable(1), "gemm_trace_enable")
+    torch.cuda.synchronize()
+    run()
+    torch.cuda.synchronize()
+    ops.check(lib.rlz_gemm_trace_enable(0), "gemm_trace_enable")
+    n = 1024
+    buf = (ctypes.c_ulonglong * (n * 8))()
+    ops.check(lib.rlz_gemm_trace_read(buf, n), "gemm_trace_read")
+    t = np.frombuffer(buf, dtype=np.uint64).reshape(n, 8).astype(np.float64)
+    t = t[t[:, 0] > 0]
+    if not len(t):
+        return {}
+    names = ["setup", "dependency_wait", "first_weights", "k_loop", "mma_drain", "epilogue"]
+    out = {"ctas": int(len(t)), "span": float((t[:, 6].max() - t[:, 0].min()) / 1e3),
+           "start_spread": float((t[:, 0].max() - t[:, 0].min()) / 1e3)}
+    for i, nm in enumerate(names):
+        d = t[:, i + 1] - t[:, i]
+        d = d[(t[:, i + 1] > 0) & (t[:, i] > 0)]
+        if len(d):
+            out[nm] = {"median": float(np.median(d) / 1e3), "max": float(d.max() / 1e3)}
+    return out
 
 
 def main(argv=None):
@@ -165,6 +198,8 @@ def main(argv=None):
     m = sub.add_parser("gemm")
     m.add_argument("--qtype", default="Q4_K"); m.add_argument("--n", type=int, default=10240); m.add_argument("--k", type=int, default=2560)
     m.add_argument("--m", type=int, default=512); m.add_argument("--iters", type=int, default=10)
+    m.add_argument("--splitk", type=int, default=0, help="0 = chosen from the shape")
+    m.add_argument("--trace", action="store_true", help="add the kernel's per-phase times (medians over CTAs)")
     m.add_argument("--wide", type=int, default=0, help="0 auto, 1 force 128-row CTAs, 2 force 256-row CTAs (m > 128)")
     a = ap.parse_args(argv)
     global REPS, GRAPH
