@@ -62,6 +62,21 @@ int rlz_gemv(const rlz::GemvParams* pp, void* stream) {
   return (int)e;
 }
 
+// Diagnostics: phase trace of the one-launch-per-GEMV kernel (8 timestamps in ns per CTA: entry, dependency wait done,
+// first input staged, first segment's rows done, second input staged, second segment's rows done, partial sums ready,
+// epilogue done; unused points stay 0).
+int rlz_gemv_trace_enable(int on) {
+  const int v = on ? 1 : 0;
+  return (int)cudaMemcpyToSymbol(rlz::g_gemv_trace_on, &v, sizeof(int));
+}
+int rlz_gemv_trace_read(unsigned long long* out, int ctas, int clear) {
+  if (ctas < 1 || ctas > rlz::GEMV_TRACE_CTAS) return -1;
+  cudaError_t e = cudaMemcpyFromSymbol(out, rlz::g_gemv_trace, sizeof(unsigned long long) * ctas * rlz::GEMV_TRACE_PTS);
+  if (e != cudaSuccess || !clear) return (int)e;
+  static unsigned long long zeros[rlz::GEMV_TRACE_CTAS * rlz::GEMV_TRACE_PTS];
+  return (int)cudaMemcpyToSymbol(rlz::g_gemv_trace, zeros, sizeof(zeros));
+}
+
 // fills in the derived fields of *pp in place (for callers that embed the description in a step program)
 int rlz_gemv_prepare(rlz::GemvParams* pp, int* grid_out) { return rlz::gemv_prepare(*pp, grid_out); }
 

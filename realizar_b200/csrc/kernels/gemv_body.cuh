@@ -194,6 +194,18 @@ __device__ void rows_f32(const GemvSeg& S, int r0, int r1, const float* xf, floa
   }
 }
 
+// Optional phase trace of the standalone kernel (diagnostics): thread 0 of every CTA records the global timer at
+// entry, after the dependency wait, after input staging, after the row loops and after the epilogue.
+constexpr int GEMV_TRACE_CTAS = 512, GEMV_TRACE_PTS = 8;
+static __device__ int g_gemv_trace_on = 0;
+static __device__ unsigned long long g_gemv_trace[GEMV_TRACE_CTAS * GEMV_TRACE_PTS];
+__device__ __forceinline__ void gemv_trace(bool on, int cta, int pt) {
+  if (on) {
+    unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_gemv_trace[cta * GEMV_TRACE_PTS + pt] = t;
+  }
+}
+
 // L2 prefetch of the weight slab that CTA `bx` of the launch described by p will read
 __device__ __forceinline__ void gemv_prefetch_slab(const GemvParams& p, int bx) {
   int m = 0;
@@ -218,11 +230,14 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, const int bx, uin
   const int r0 = (bx - M.cta_begin) * M.rows_per_cta;
   const int r1 = min(M.n, r0 + M.rows_per_cta);
 
+  const bool tr = STANDALONE && threadIdx.x == 0 && bx < GEMV_TRACE_CTAS && g_gemv_trace_on;
+  gemv_trace(tr, bx, 0);
   if (STANDALONE) {
     gemv_prefetch_slab(p, bx);                    // pull this CTA's weight slab towards L2 while the previous kernel drains
     pdl_launch_dependents();
     pdl_wait();
   }
+  gemv_trace(tr, bx, 1);
 
   // shared memory carve-up (sizes fixed by the launcher from max_k / max_rows)
   const int kq = p.max_k;
@@ -276,6 +291,7 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, const int bx, uin
       }
       staged = S.x_id;
       __syncthreads();
+      gemv_trace(tr, bx, 2 + (s > 0 ? 2 : 0));    // 2: first input staged; 4: second input staged
     }
     if constexpr (fast) {
       const ActView a{xq, xd, xs, (const U4*)xm, S.k};
@@ -293,10 +309,13 @@ __device__ __forceinline__ void gemv_body(const GemvParams& p, const int bx, uin
     } else {
       rows_f32<B>(S, r0, r1, xf, rowacc, s);
     }
+    gemv_trace(tr, bx, 3 + (s > 0 ? 2 : 0));      // 3: rows of the first segment done; 5: of the second
   }
   __syncthreads();
+  gemv_trace(tr, bx, 6);
 
   gemv_epilogue<B>(p, M, rowacc, r0, r1);
+  gemv_trace(tr, bx, 7);
 }
 
 inline size_t gemv_smem_bytes(const GemvParams& p) {

@@ -16,6 +16,7 @@
 //
 // Replaces the same reference kernels as gemv.cu (src/cuda/executor/q4k_mwv_gemv.rs:7-945).
 #include "common.cuh"
+#include <stdlib.h>
 #include "../gemv_blocks.h"
 #include "gemv_common.cuh"
 
@@ -295,6 +296,10 @@ int rlz_gemv_stream(const rlz::GemvParams* pp, void* stream) {
   if (fixed + 2 * (size_t)stage_bytes > budget) return -20;
   int nstage = (int)((budget - fixed) / stage_bytes);
   if (nstage > GS_MAX_STAGES) nstage = GS_MAX_STAGES;
+  // fewer stages = less shared memory per CTA, so that the CTAs of the next launch can become resident (and request their
+  // weights) while this launch still runs; RLZ_GS_STAGES caps the ring depth
+  static const int stage_cap = [] { const char* e = getenv("RLZ_GS_STAGES"); return e ? atoi(e) : 0; }();
+  if (stage_cap >= 2 && nstage > stage_cap) nstage = stage_cap;
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
   switch (p.batch) {

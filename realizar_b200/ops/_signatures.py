@@ -103,6 +103,8 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_cuda_error_string.restype = ctypes.c_char_p
     lib.rlz_gemv.argtypes = [POINTER(GemvParams), c_void_p]
     lib.rlz_gemv_stream.argtypes = [POINTER(GemvParams), c_void_p]
+    lib.rlz_gemv_trace_enable.argtypes = [c_int]
+    lib.rlz_gemv_trace_read.argtypes = [c_void_p, c_int, c_int]
     lib.rlz_gemv_prepare.argtypes = [POINTER(GemvParams), POINTER(c_int)]
     lib.rlz_gemv_smem_bytes.argtypes = [POINTER(GemvParams)]
     lib.rlz_gemv_smem_bytes.restype = c_longlong

@@ -98,14 +98,53 @@ def bench_gemv(a):
         comm.allocate(1, a.n, max_batch=4)
         comm.begin_step()
         ar = comm.ar_desc(0)
-    p = ops.build_gemv_params([xin], mats, y, a.batch, target_ctas=a.ctas or 148, ar=ar)
+    # --rotate R: R copies of the weights taken in turn, so that back-to-back launches stream from DRAM like the layers of a model
+    ws = [w] + [random_weight(a.n, a.k, qt, dev) for _ in range(max(1, a.rotate) - 1)]
+    ps = [ops.build_gemv_params([xin], [ops.MatOut([(wi, 0)])], y, a.batch, target_ctas=a.ctas or 148, ar=ar) for wi in ws]
     launch = ops.gemv_stream_launch if use_stream else ops.gemv_launch
-    ms = time_cuda(lambda: launch(p), a.iters)
+    turn = [0]
+
+    def run():
+        launch(ps[turn[0] % len(ps)])
+        turn[0] += 1
+    ms = time_cuda(run, a.iters)
     byts = w.nbytes + x.numel() * 4 + y.numel() * 4
     pk = peaks()
-    return {"kernel": "gemv_stream" if use_stream else "gemv", "qtype": a.qtype, "n": a.n, "k": a.k, "batch": a.batch, "ms": ms, "bytes": byts,
-            "gbs": byts / ms / 1e6, "frac_of_%s_hbm" % pk["source"]: byts / ms / 1e6 / pk["hbm_gbs"],
-            "l2_note": "weights %.0f MB %s L2" % (w.nbytes / 1e6, ">" if w.nbytes > 126e6 else "<=")}
+    res = {"kernel": "gemv_stream" if use_stream else "gemv", "qtype": a.qtype, "n": a.n, "k": a.k, "batch": a.batch, "ms": ms, "bytes": byts,
+           "gbs": byts / ms / 1e6, "frac_of_%s_hbm" % pk["source"]: byts / ms / 1e6 / pk["hbm_gbs"],
+           "l2_note": "weights %.0f MB x %d %s L2" % (w.nbytes / 1e6, len(ws), ">" if w.nbytes * len(ws) > 126e6 else "<=")}
+    if a.trace and not use_stream:
+        res["phase_trace_us"] = gemv_phase_trace(lambda: time_cuda(run, 2, warmup=0))
+    return res
+
+
+def gemv_phase_trace(run) -> dict:
+    """Phase times of the last GEMV launch of ``run`` (medians over CTAs, microseconds)."""
+    import ctypes
+    from .. import ops
+    lib = ops.lib()
+    n = 512
+    buf = (ctypes.c_ulonglong * (n * 8))()
+    ops.check(lib.rlz_gemv_trace_read(buf, n, 1), "gemv_trace_read")       # clear
+    ops.check(lib.rlz_gemv_trace_enable(1), "gemv_trace_enable")
+    torch.cuda.synchronize()
+    run()
+    torch.cuda.synchronize()
+    ops.check(lib.rlz_gemv_trace_enable(0), "gemv_trace_enable")
+    ops.check(lib.rlz_gemv_trace_read(buf, n, 0), "gemv_trace_read")
+    t = np.frombuffer(buf, dtype=np.uint64).reshape(n, 8).astype(np.float64)
+    t = t[t[:, 0] > 0]
+    if not len(t):
+        return {}
+    names = {(0, 1): "prefetch_and_dependency_wait", (1, 2): "stage_input", (2, 3): "rows", (3, 6): "to_partial_sums", (6, 7): "epilogue"}
+    out = {"ctas": int(len(t)), "span": float((t[:, 7].max() - t[:, 0].min()) / 1e3), "start_spread": float((t[:, 0].max() - t[:, 0].min()) / 1e3),
+           "end_spread": float((t[:, 7].max() - t[:, 7].min()) / 1e3)}
+    for (i, j), nm in names.items():
+        ok = (t[:, i] > 0) & (t[:, j] > 0)
+        if ok.any():
+            d = t[ok, j] - t[ok, i]
+            out[nm] = {"median": float(np.median(d) / 1e3), "max": float(d.max() / 1e3)}
+    return out
 
 
 def bench_attn(a):
@@ -191,6 +230,8 @@ def main(argv=None):
     g.add_argument("--qtype", default="Q4_K"); g.add_argument("--n", type=int, default=200000); g.add_argument("--k", type=int, default=2560)
     g.add_argument("--batch", type=int, default=1); g.add_argument("--iters", type=int, default=10); g.add_argument("--norm", action="store_true")
     g.add_argument("--ctas", type=int, default=0); g.add_argument("--no-stream", action="store_true"); g.add_argument("--ar", action="store_true")
+    g.add_argument("--rotate", type=int, default=1, help="copies of the weights taken in turn (keeps back-to-back launches out of L2)")
+    g.add_argument("--trace", action="store_true", help="add the kernel's per-phase times (medians over CTAs)")
     t = sub.add_parser("attn")
     t.add_argument("--heads", type=int, default=32); t.add_argument("--kv-heads", type=int, default=32); t.add_argument("--head-dim", type=int, default=80)
     t.add_argument("--ctx", type=int, default=4096); t.add_argument("--batch", type=int, default=8); t.add_argument("--splits", type=int, default=0)
