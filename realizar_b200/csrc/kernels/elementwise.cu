@@ -98,16 +98,22 @@ __global__ void head_rmsnorm_kernel(float* x, const float* w, int heads, int d, 
 }
 
 // RoPE in place on x [T, heads, d]: rotates the first rope_dim dims of each head.
-__global__ void rope_kernel(float* x, const int32_t* positions, int heads, int d, int64_t ld, int rope_dim, int rope_type, float theta) {
+__global__ void rope_kernel(float* x, const int32_t* positions, int heads, int d, int64_t ld, int rope_dim, int rope_type, float theta,
+                            const float2* table, int table_len) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, half = rope_dim >> 1;
   const int pos = positions[t];
   if (pos < 0) return;
+  const float2* row = (table && pos < table_len) ? table + (int64_t)pos * half : nullptr;   // (cos, sin) with the context scaling folded in
   for (int idx = threadIdx.x; idx < heads * half; idx += blockDim.x) {
     const int h = idx / half, i = idx - h * half;
-    const float freq = powf(theta, -2.f * (float)i / (float)rope_dim);
-    float sn, cs; sincosf((float)pos * freq, &sn, &cs);
+    float sn, cs;
+    if (row) { const float2 c = __ldg(row + i); cs = c.x; sn = c.y; }
+    else {
+      const float freq = powf(theta, -2.f * (float)i / (float)rope_dim);
+      sincosf((float)pos * freq, &sn, &cs);
+    }
     float* v = x + (int64_t)t * ld + (int64_t)h * d;
     const int i0 = rope_type == 2 ? i : 2 * i, i1 = rope_type == 2 ? i + half : 2 * i + 1;
     const float a = v[i0], bb = v[i1];
@@ -287,10 +293,13 @@ int rlz_head_rmsnorm(float* x, const float* w, int rows, int heads, int d, long 
   return (int)launch(head_rmsnorm_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, x, w, heads, d, (int64_t)ld, eps);
 }
 
-int rlz_rope(float* x, const int32_t* positions, int rows, int heads, int d, long long ld, int rope_dim, int rope_type, float theta, void* stream) {
+// `table`: [table_len, rope_dim / 2] (cos, sin) pairs or null (angles computed from theta)
+int rlz_rope(float* x, const int32_t* positions, int rows, int heads, int d, long long ld, int rope_dim, int rope_type, float theta,
+             const void* table, int table_len, void* stream) {
   if (rope_dim <= 0) return 0;
   if (rope_dim > d || (rope_dim & 1)) return -1;
-  return (int)launch(rope_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, x, positions, heads, d, (int64_t)ld, rope_dim, rope_type, theta);
+  return (int)launch(rope_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, x, positions, heads, d, (int64_t)ld, rope_dim, rope_type, theta,
+                     (const float2*)table, table_len);
 }
 
 int rlz_elementwise(const float* a, const float* b, const float* bias, const float* residual, float* y, long long rows, int cols,

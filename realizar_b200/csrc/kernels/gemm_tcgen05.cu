@@ -549,13 +549,17 @@ int rlz_gemm_kquant(const rlz::GemmParams* pp, void* stream) {
   if (p.m <= 32) return launch_gemm<32, 1>(p, st);
   if (p.m <= 64) return launch_gemm<64, 1>(p, st);
   if (p.m <= 128) return launch_gemm<128, 1>(p, st);
-  // 256-row CTAs when they still fill the GPU for more than two waves (or when asked to through p._pad = 2)
+  // 128- or 256-row CTAs: whichever needs less time by a two-term model - waves of CTAs over the SMs times the measured cost
+  // of one K step of a CTA (128 rows: ~840 cycles, set by its 8 dequant warps; 256 rows: ~1100 cycles, set by the MMAs).
+  // p._pad forces the choice (1 = 128 rows, 2 = 256 rows).
+  const long long tiles1 = (long long)((p.n + 127) / 128) * ((p.m + 255) / 256) * p.splitk;
   const long long tiles2 = (long long)((p.n + 255) / 256) * ((p.m + 255) / 256) * p.splitk;
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   // (256-row CTAs with the raw-block ring fit in shared memory for Q4_K blocks only)
   const bool wide_fits = !(p.qtype == QT_Q5_K || p.qtype == QT_Q6_K);
-  const bool wide = wide_fits && (p._pad == 2 || (p._pad != 1 && tiles2 >= 2LL * sms));
+  const long long cost1 = ((tiles1 + sms - 1) / sms) * 840, cost2 = ((tiles2 + sms - 1) / sms) * 1100;
+  const bool wide = wide_fits && (p._pad == 2 || (p._pad != 1 && cost2 < cost1));
   return wide ? launch_gemm<256, 2>(p, st) : launch_gemm<256, 1>(p, st);
 }
 

@@ -128,19 +128,21 @@ class BatchedForward:
         self.launches_per_pass += 1
         for l, L in enumerate(m.layers):
             ops.norm_bf16(x, xb, L.attn_norm_w, L.attn_norm_b, norm_t, cfg.eps)
-            self._gemm(L.q, xb, self.qkv, T, bias=L.q_b, y_col=0)
-            self._gemm(L.k, xb, self.qkv, T, bias=L.k_b, y_col=qd)
-            self._gemm(L.v, xb, self.qkv, T, bias=L.v_b, y_col=qd + kvd)
+            if L.qkv is not None:                              # one GEMM over the fused rows: fuller waves, no split-K zero fill
+                self._gemm(L.qkv, xb, self.qkv, T, bias=L.qkv_b, y_col=0)
+            else:
+                self._gemm(L.q, xb, self.qkv, T, bias=L.q_b, y_col=0)
+                self._gemm(L.k, xb, self.qkv, T, bias=L.k_b, y_col=qd)
+                self._gemm(L.v, xb, self.qkv, T, bias=L.v_b, y_col=qd + kvd)
             if cfg.parallel_residual:
                 self._gemm(L.up, xb, self.gate, T, bias=L.up_b)        # activation applied when the bf16 operand is produced
             if L.q_norm_w is not None:
                 ops.head_rmsnorm_(qkv, L.q_norm_w, m.heads, hd, cfg.eps)
                 ops.head_rmsnorm_(qkv[:, qd:], L.k_norm_w, m.kv_heads, hd, cfg.eps)
                 self.launches_per_pass += 2
-            if cfg.uses_rope:
-                ops.rope_(qkv, self.positions[:T], m.heads, hd, cfg.rope_dim, cfg.rope_type, cfg.rope_theta)
-                ops.rope_(qkv[:, qd:], self.positions[:T], m.kv_heads, hd, cfg.rope_dim, cfg.rope_type, cfg.rope_theta)
-                self.launches_per_pass += 2
+            if cfg.uses_rope:                                  # the k heads follow the q heads in a row: one launch rotates both
+                ops.rope_(qkv, self.positions[:T], m.heads + m.kv_heads, hd, cfg.rope_dim, cfg.rope_type, cfg.rope_theta, table=m.rope_table)
+                self.launches_per_pass += 1
             ops.kv_append(qkv[:, qd:], qkv[:, qd + kvd:], self.k_cache[l], self.v_cache[l], self.positions[:T], self.page_rows[:T], m.kv_heads, hd)
             if pos0 is not None and shared_table and T >= self.flash_min_tokens and self.flash_ok:
                 ops.attn_prefill(self.qkv, self.attn[:, L.o_in_off:], self.k_cache[l], self.v_cache[l], page_table, T, pos0, m.heads, m.kv_heads, hd,

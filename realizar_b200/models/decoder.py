@@ -102,6 +102,8 @@ class LayerWeights:
     k: Optional[DeviceWeight] = None
     v: Optional[DeviceWeight] = None
     q_b: Optional[torch.Tensor] = None
+    qkv: Optional[DeviceWeight] = None     # Q, K, V as one matrix (their rows are views of it) when they share a block type
+    qkv_b: Optional[torch.Tensor] = None
     k_b: Optional[torch.Tensor] = None
     v_b: Optional[torch.Tensor] = None
     o: Optional[DeviceWeight] = None
@@ -151,6 +153,17 @@ class GpuModel:
         dev = self.device
         up = lambda t: ops.upload_weight(t.data, t.qtype, t.shape[0], t.shape[1], dev)
 
+        def up_group(parts):
+            """Upload Q, K, V.  When they share a block type and width they become row ranges of ONE device matrix, so
+            that the token-batch path can run the three projections as a single GEMM (returns q, k, v, fused-or-None)."""
+            if len({(int(t.qtype), t.shape[1]) for t in parts}) != 1:
+                return (*[up(t) for t in parts], None)
+            flat = [t.data if isinstance(t.data, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(t.data)) for t in parts]
+            rows = [t.shape[0] for t in parts]
+            fused = ops.upload_weight(torch.cat([f.reshape(-1) for f in flat]), parts[0].qtype, sum(rows), parts[0].shape[1], dev)
+            r1, r2 = rows[0], rows[0] + rows[1]
+            return fused.rows(0, r1), fused.rows(r1, r2), fused.rows(r2, r2 + rows[2]), fused
+
         emb = weights["token_embd.weight"]
         self.embed_qtype = int(emb.qtype)
         self.embed_row_bytes = row_bytes(emb.qtype, cfg.hidden_dim)
@@ -186,16 +199,18 @@ class GpuModel:
             k0, k1 = tp_rank * self.kv_dim, (tp_rank + 1) * self.kv_dim
             if g("attn_qkv.weight") is not None:
                 qkv, qkv_b = g("attn_qkv.weight"), _f32(g("attn_qkv.bias"), dev)
-                L.q, L.k, L.v = up(shard_rows(qkv, q0, q1)), up(shard_rows(qkv, qd + k0, qd + k1)), up(shard_rows(qkv, qd + kvd + k0, qd + kvd + k1))
+                L.q, L.k, L.v, L.qkv = up_group([shard_rows(qkv, q0, q1), shard_rows(qkv, qd + k0, qd + k1), shard_rows(qkv, qd + kvd + k0, qd + kvd + k1)])
                 if qkv_b is not None:
                     L.q_b, L.k_b, L.v_b = qkv_b[q0:q1].contiguous(), qkv_b[qd + k0: qd + k1].contiguous(), qkv_b[qd + kvd + k0: qd + kvd + k1].contiguous()
             else:
-                L.q, L.k, L.v = up(shard_rows(g("attn_q.weight"), q0, q1)), up(shard_rows(g("attn_k.weight"), k0, k1)), up(shard_rows(g("attn_v.weight"), k0, k1))
+                L.q, L.k, L.v, L.qkv = up_group([shard_rows(g("attn_q.weight"), q0, q1), shard_rows(g("attn_k.weight"), k0, k1), shard_rows(g("attn_v.weight"), k0, k1)])
                 bq, bk, bv = _f32(g("attn_q.bias"), dev), _f32(g("attn_k.bias"), dev), _f32(g("attn_v.bias"), dev)
                 L.q_b = bq[q0:q1].contiguous() if bq is not None else None
                 L.k_b = bk[k0:k1].contiguous() if bk is not None else None
                 L.v_b = bv[k0:k1].contiguous() if bv is not None else None
             L.q_norm_w, L.k_norm_w = _f32(g("attn_q_norm.weight"), dev), _f32(g("attn_k_norm.weight"), dev)
+            if L.qkv is not None and any(b is not None for b in (L.q_b, L.k_b, L.v_b)):
+                L.qkv_b = torch.cat([b if b is not None else torch.zeros(w.n, device=dev) for b, w in ((L.q_b, L.q), (L.k_b, L.k), (L.v_b, L.v))])
             i0, i1 = tp_rank * self.inter, (tp_rank + 1) * self.inter
             if tp_size > 1:
                 o_sh, o_cover = shard_cols(g("attn_output.weight"), q0, q1)

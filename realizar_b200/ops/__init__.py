@@ -318,9 +318,12 @@ def head_rmsnorm_(x: torch.Tensor, w: torch.Tensor, heads: int, d: int, eps: flo
     check(lib().rlz_head_rmsnorm(x.data_ptr(), w.data_ptr(), x.shape[0], heads, d, x.stride(0), eps, stream_ptr()), "head_rmsnorm")
 
 
-def rope_(x: torch.Tensor, positions: torch.Tensor, heads: int, d: int, rope_dim: int, rope_type: int, theta: float) -> None:
-    """In-place RoPE on ``x [T, >= heads*d]`` (row stride taken from the tensor)."""
-    check(lib().rlz_rope(x.data_ptr(), positions.data_ptr(), x.shape[0], heads, d, x.stride(0), rope_dim, rope_type, theta, stream_ptr()), "rope")
+def rope_(x: torch.Tensor, positions: torch.Tensor, heads: int, d: int, rope_dim: int, rope_type: int, theta: float,
+          table: Optional[torch.Tensor] = None) -> None:
+    """In-place RoPE on ``x [T, >= heads*d]`` (row stride taken from the tensor).  ``table``: ``[positions, rope_dim/2, 2]``
+    (cos, sin) as made by ``make_rope_table`` - carries the checkpoint's context scaling; positions beyond it use ``theta``."""
+    check(lib().rlz_rope(x.data_ptr(), positions.data_ptr(), x.shape[0], heads, d, x.stride(0), rope_dim, rope_type, theta,
+                         ptr(table), int(table.shape[0]) if table is not None else 0, stream_ptr()), "rope")
 
 
 def elementwise(a: torch.Tensor, b=None, bias=None, residual=None, act=ACT_NONE, out=None) -> torch.Tensor:

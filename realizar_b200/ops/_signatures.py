@@ -129,7 +129,7 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_embed.argtypes = [c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p]
     lib.rlz_norm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_int, c_float, c_void_p]
     lib.rlz_head_rmsnorm.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_float, c_void_p]
-    lib.rlz_rope.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_int, c_int, c_float, c_void_p]
+    lib.rlz_rope.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_int, c_int, c_float, c_void_p, c_int, c_void_p]
     lib.rlz_elementwise.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_longlong,
                                     c_longlong, c_int, c_int, c_void_p]
     lib.rlz_kv_append.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
