@@ -398,7 +398,7 @@ class DecodeEngine:
         for c0 in range(0, n, bf.T):
             T = min(bf.T, n - c0)
             pos = torch.arange(pos0 + c0, pos0 + c0 + T, dtype=torch.int32)
-            rows = torch.tensor([pages[int(p) // PAGE] for p in pos], dtype=torch.int32)
+            rows = torch.tensor([pages[p // PAGE] for p in range(pos0 + c0, pos0 + c0 + T)], dtype=torch.int32)
             bf.tokens[:T].copy_(toks[c0:c0 + T], non_blocking=True)
             bf.positions[:T].copy_(pos, non_blocking=True)
             bf.page_rows[:T].copy_(rows, non_blocking=True)
@@ -435,7 +435,7 @@ class DecodeEngine:
         pos = torch.arange(pos0, pos0 + n, dtype=torch.int32)
         bf.tokens[:n].copy_(torch.as_tensor(list(tokens), dtype=torch.int32), non_blocking=True)
         bf.positions[:n].copy_(pos, non_blocking=True)
-        bf.page_rows[:n].copy_(torch.tensor([pages[int(p) // PAGE] for p in pos], dtype=torch.int32), non_blocking=True)
+        bf.page_rows[:n].copy_(torch.tensor([pages[p // PAGE] for p in range(pos0, pos0 + n)], dtype=torch.int32), non_blocking=True)
         x = bf.forward(n, self.buf.page_table[slot], shared_table=True, pos0=pos0)
         out: List[int] = []
         B = self.cfg.max_batch
