@@ -156,3 +156,69 @@ def test_streaming_kv_ring_buffer():
     assert h.memory_bytes() == 2 * 4 * 2 * 8 * 2
     with pytest.raises(ValueError):
         StreamingKVCache(1, 2, 1, 2, sinks=2)
+
+
+def test_step_program_builder_packs_ops_and_rejects_bad_programs():
+    """Blob layout of the persistent decode-step program (CPU: the CUDA library is replaced by a stub)."""
+    import ctypes
+    import torch
+    from realizar_b200.ops import _signatures as S
+    from realizar_b200.ops.step_program import STEP_ARGMAX, STEP_ATTN, STEP_EMBED, STEP_GEMV, StepProgramBuilder
+
+    class StubLib:
+        def rlz_gemv_prepare(self, p, grid):
+            q = ctypes.cast(p, ctypes.POINTER(S.GemvParams)).contents
+            q.max_k, q.max_rows, q.any_generic = 2560, 61, 0
+            ctypes.cast(grid, ctypes.POINTER(ctypes.c_int)).contents.value = 294
+            return 0
+
+        def rlz_gemv_smem_bytes(self, p):
+            return 20000
+
+        def rlz_decode_step_attn_smem(self, gt):
+            return {1: 5000, 2: 8000, 4: 14000}.get(gt, -1)
+
+    dev = torch.device("cpu")
+    b = StepProgramBuilder(StubLib(), dev, occ=2, attn_gt=1, sm_count=148)
+    assert b.grid == 296
+    x = torch.zeros(2560)
+    tok = torch.zeros(1, dtype=torch.int32)
+    table = torch.zeros(1440 * 8, dtype=torch.uint8)
+    b.add_embed(table, 12, 1440, 2560, 8, tok, x)
+    g = S.GemvParams()
+    g.batch, g.nmat = 1, 1
+    b.add_gemv(g)
+    a = S.AttnDecodeParams()
+    a.n_heads, a.n_kv_heads, a.head_dim, a.splits, a.batch = 32, 32, 80, 8, 1
+    b.add_attn(a)
+    logits = torch.zeros(51200)
+    out = torch.zeros(1, dtype=torch.int32)
+    b.add_argmax(logits, 51200, out)
+    prog = b.finish()
+    assert prog.nops == 4 and prog.smem == 20000 and prog.params.occ == 2 and prog.params.attn_gt == 1
+    raw = bytes(prog.blob.numpy())
+    ops_tab = (S.StepOp * 4).from_buffer_copy(raw[: 4 * ctypes.sizeof(S.StepOp)])
+    assert [o.kind for o in ops_tab] == [STEP_EMBED, STEP_GEMV, STEP_ATTN, STEP_ARGMAX]
+    assert ops_tab[1].grid == 294 and ops_tab[2].grid == 32 * 8
+    assert all(o.params % 16 == 0 for o in ops_tab) and ops_tab[0].params >= 4 * ctypes.sizeof(S.StepOp)
+    emb = S.StepEmbed.from_buffer_copy(raw[ops_tab[0].params: ops_tab[0].params + ctypes.sizeof(S.StepEmbed)])
+    assert emb.hidden == 2560 and emb.vocab == 8 and emb.row_bytes == 1440 and emb.out == x.data_ptr()
+    gp = S.GemvParams.from_buffer_copy(raw[ops_tab[1].params: ops_tab[1].params + ctypes.sizeof(S.GemvParams)])
+    assert gp.max_k == 2560 and gp.max_rows == 61          # the prepared copy is what travels, the caller's struct is untouched
+    assert g.max_k == 0
+
+    # argmax must end the program; batched or all-reduce GEMVs and int8 caches are refused
+    b2 = StepProgramBuilder(StubLib(), dev, 1, 4, 148)
+    b2.add_argmax(logits, 51200, out)
+    b2.add_gemv(g)
+    with pytest.raises(ValueError):
+        b2.finish()
+    g4 = S.GemvParams()
+    g4.batch = 4
+    with pytest.raises(ValueError):
+        b2.add_gemv(g4)
+    a.kv_q8 = 1
+    with pytest.raises(ValueError):
+        b2.add_attn(a)
+    with pytest.raises(ValueError):
+        StepProgramBuilder(StubLib(), dev, 1, 8, 148).add_attn(S.AttnDecodeParams(n_heads=8, n_kv_heads=1, splits=1, batch=1))
