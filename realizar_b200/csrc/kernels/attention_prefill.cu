@@ -37,6 +37,7 @@ struct AttnPrefillParams {
   int32_t n_tokens, pos0;      // chunk rows are positions pos0 .. pos0 + n_tokens - 1
   int32_t window, kv_q8;       // kv_q8: int8 cache rows of head_dim + 16 bytes (codes, then the fp32 row scale)
   float scale;
+  int32_t out_bf16;            // 1: `out` is bf16 [T, ld_out] (the operand of the output projection GEMM), else fp32
 };
 
 template <int D>
@@ -247,9 +248,19 @@ __global__ void __launch_bounds__(FP_THREADS) attn_prefill_tcgen05_kernel(const 
   if (!ok) atomicExch(&g_prefill_attn_error, 3101);
   if (ok && qvalid) {
     const float inv = lrow > 0.f ? 1.f / lrow : 0.f;
-    float* dst = p.out + (int64_t)qrow * p.ld_out + head * D;
+    if (p.out_bf16) {
+      __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (int64_t)qrow * p.ld_out + head * D;
 #pragma unroll
-    for (int j = 0; j < D; j += 4) *(float4*)(dst + j) = make_float4(o[j] * inv, o[j + 1] * inv, o[j + 2] * inv, o[j + 3] * inv);
+      for (int j = 0; j < D; j += 8) {
+        __nv_bfloat162 w[4] = {__floats2bfloat162_rn(o[j] * inv, o[j + 1] * inv), __floats2bfloat162_rn(o[j + 2] * inv, o[j + 3] * inv),
+                               __floats2bfloat162_rn(o[j + 4] * inv, o[j + 5] * inv), __floats2bfloat162_rn(o[j + 6] * inv, o[j + 7] * inv)};
+        *(uint4*)(dst + j) = *(const uint4*)w;
+      }
+    } else {
+      float* dst = p.out + (int64_t)qrow * p.ld_out + head * D;
+#pragma unroll
+      for (int j = 0; j < D; j += 4) *(float4*)(dst + j) = make_float4(o[j] * inv, o[j + 1] * inv, o[j + 2] * inv, o[j + 3] * inv);
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -288,7 +299,7 @@ int rlz_attn_prefill(const rlz::AttnPrefillParams* pp, void* stream) {
   using namespace rlz;
   const AttnPrefillParams& p = *pp;
   if (p.n_tokens < 1 || p.n_kv_heads < 1 || p.n_heads % p.n_kv_heads || p.pos0 < 0 || p.window < 0) return -2;
-  if (((uintptr_t)p.k_cache & 15) || ((uintptr_t)p.v_cache & 15) || ((uintptr_t)p.out & 15) || (p.ld_out & 3) || (p.head_dim & 7)) return -4;
+  if (((uintptr_t)p.k_cache & 15) || ((uintptr_t)p.v_cache & 15) || ((uintptr_t)p.out & 15) || (p.ld_out & (p.out_bf16 ? 7 : 3)) || (p.head_dim & 7)) return -4;
   cudaStream_t st = (cudaStream_t)stream;
   switch (p.head_dim) {
     case 64: return launch_prefill<64>(p, st);

@@ -148,11 +148,27 @@ __global__ void kv_append_kernel(const float* k, const float* v, int64_t ld, __n
   if (pos < 0) return;
   const int pg = page_rows[t];                     // physical page holding position `pos`
   const int slot = pos % page;
+  const float* kr = k + (int64_t)t * ld;
+  const float* vr = v + (int64_t)t * ld;
+  if ((d & 7) == 0 && (ld & 3) == 0 && (((uintptr_t)k | (uintptr_t)v) & 15) == 0) {
+    // eight values per thread: two 16-byte loads per tensor, one 16-byte store into the cache row
+    for (int c = threadIdx.x; c < n_kv_heads * d / 8; c += blockDim.x) {
+      const int idx = c * 8, h = idx / d, j = idx - h * d;
+      const int64_t off = (((int64_t)pg * n_kv_heads + h) * page + slot) * d + j;
+      const float4 k0 = *(const float4*)(kr + idx), k1 = *(const float4*)(kr + idx + 4);
+      const float4 v0 = *(const float4*)(vr + idx), v1 = *(const float4*)(vr + idx + 4);
+      __nv_bfloat162 kk[4] = {__floats2bfloat162_rn(k0.x, k0.y), __floats2bfloat162_rn(k0.z, k0.w), __floats2bfloat162_rn(k1.x, k1.y), __floats2bfloat162_rn(k1.z, k1.w)};
+      __nv_bfloat162 vv[4] = {__floats2bfloat162_rn(v0.x, v0.y), __floats2bfloat162_rn(v0.z, v0.w), __floats2bfloat162_rn(v1.x, v1.y), __floats2bfloat162_rn(v1.z, v1.w)};
+      *(uint4*)(k_cache + off) = *(const uint4*)kk;
+      *(uint4*)(v_cache + off) = *(const uint4*)vv;
+    }
+    return;
+  }
   for (int idx = threadIdx.x; idx < n_kv_heads * d; idx += blockDim.x) {
     const int h = idx / d, j = idx - h * d;
     const int64_t off = (((int64_t)pg * n_kv_heads + h) * page + slot) * d + j;
-    k_cache[off] = __float2bfloat16_rn(k[(int64_t)t * ld + idx]);
-    v_cache[off] = __float2bfloat16_rn(v[(int64_t)t * ld + idx]);
+    k_cache[off] = __float2bfloat16_rn(kr[idx]);
+    v_cache[off] = __float2bfloat16_rn(vr[idx]);
   }
 }
 

@@ -47,8 +47,10 @@ struct GemmParams {
   const uint32_t* ar_epoch;
   int64_t ar_row_pairs;
   int32_t ar_rank, ar_world, ar_rows, ar_enabled;
-  int32_t ar_site, ar_nsites, ar_splits, _pad2;
+  int32_t ar_site, ar_nsites, ar_splits;
+  int32_t flags;           // GM_OUT_BF16: Y is bf16 (ldy in elements); GM_RES_MUL: the `residual` operand multiplies instead of adding
 };
+enum { GM_OUT_BF16 = 1, GM_RES_MUL = 2 };
 
 // ---- producers: raw block bytes -> registers (issued one K step ahead), registers -> bf16 pairs -------------
 // The integer code q of a weight is dropped into the mantissa of a bf16 power of two (magic + q is exact), the
@@ -411,19 +413,22 @@ __global__ void __launch_bounds__(RT * GM_PRODUCERS + 96) gemm_kquant_tcgen05_ke
 #pragma unroll
             for (int j = 0; j < 32; ++j)
               if (j < ntok) atomicAdd(dst + (int64_t)j * p.ldy, __uint_as_float(r[j]) + bias);
-          } else if (p.act == ACT_NONE && !p.residual) {
+          } else if (p.act == ACT_NONE && !p.residual && !p.flags) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
               if (j < ntok) dst[(int64_t)j * p.ldy] = __uint_as_float(r[j]) + bias;
           } else {
             const float* res = p.residual ? p.residual + (int64_t)(m0 + c0) * p.ld_res + row : nullptr;
+            const bool mul = (p.flags & GM_RES_MUL) != 0, to_bf16 = (p.flags & GM_OUT_BF16) != 0;
+            __nv_bfloat16* dst16 = (__nv_bfloat16*)p.Y + (int64_t)(m0 + c0) * p.ldy + row;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               if (j < ntok) {
                 float v = __uint_as_float(r[j]) + bias;
                 if (p.act == ACT_GELU) v = gelu_tanh(v); else if (p.act == ACT_SILU) v = silu(v);
-                if (res) v += res[(int64_t)j * p.ld_res];
-                dst[(int64_t)j * p.ldy] = v;
+                if (res) v = mul ? v * res[(int64_t)j * p.ld_res] : v + res[(int64_t)j * p.ld_res];
+                if (to_bf16) dst16[(int64_t)j * p.ldy] = __float2bfloat16_rn(v);      // the operand of the next GEMM, written where it is read
+                else dst[(int64_t)j * p.ldy] = v;
               }
             }
           }
@@ -540,7 +545,8 @@ int rlz_gemm_kquant(const rlz::GemmParams* pp, void* stream) {
   if (p.splitk < 1) p.splitk = 1;
   if (p.splitk > p.k / GM_KSTEP) p.splitk = p.k / GM_KSTEP;
   p.atomic_out = (p.splitk > 1 && !p.ar_enabled) ? 1 : 0;
-  if (p.atomic_out && p.act != ACT_NONE) return -5;
+  if (p.atomic_out && (p.act != ACT_NONE || p.flags)) return -5;
+  if (p.ar_enabled && p.flags) return -8;
   if (p.ar_enabled && (p.splitk > p.ar_splits || p.act != ACT_NONE || p.residual || p.ar_world < 1 || p.ar_world > 8 || p.m > p.ar_rows ||
                        p.n > p.ar_row_pairs || p.ar_site < 0 || p.ar_site >= 256 || p.ar_site >= p.ar_nsites)) return -8;
   if (p.ar_enabled) p.splitk = p.ar_splits;              // the reducer expects exactly ar_splits writers per rank

@@ -89,6 +89,17 @@ class BatchedForward:
             G.gemm_launch(G.build_gemm_params(w, x_b, yv, T, bias=bias, act=act, splitk=sk, ldy=y.stride(0)))
         self.launches_per_pass += 1
 
+    def _gemm_to_operand(self, w, x_b, dst_b, T, bias, act, mul=None) -> bool:
+        """dst_b[:T, :n] = bf16(act(x_b W^T + bias) [* mul]) written by the GEMM epilogue (no fp32 round trip, no
+        separate activation launch).  Returns False when K would be split for occupancy (the caller then takes the
+        fp32 path followed by the activation kernel)."""
+        if G.choose_splitk(w.n, w.k, T, self.sm_count) != 1:
+            return False
+        G.gemm_launch(G.build_gemm_params(w, x_b, dst_b, T, bias=bias, act=act, residual=mul, ldy=dst_b.stride(0),
+                                          ld_res=mul.stride(0) if mul is not None else None, res_mul=mul is not None))
+        self.launches_per_pass += 1
+        return True
+
     def _row_parallel(self, w, x_b, T, bias):
         """x += W_shard . x_b (+ bias), summed over tensor-parallel ranks."""
         if self.model.tp_size == 1:
@@ -134,8 +145,11 @@ class BatchedForward:
                 self._gemm(L.q, xb, self.qkv, T, bias=L.q_b, y_col=0)
                 self._gemm(L.k, xb, self.qkv, T, bias=L.k_b, y_col=qd)
                 self._gemm(L.v, xb, self.qkv, T, bias=L.v_b, y_col=qd + kvd)
-            if cfg.parallel_residual:
-                self._gemm(L.up, xb, self.gate, T, bias=L.up_b)        # activation applied when the bf16 operand is produced
+            up_fused = False
+            if cfg.parallel_residual:                          # GELU(fc1) goes straight into the bf16 operand of fc2 when K is not split
+                up_fused = self._gemm_to_operand(L.up, xb, self.act_b[:, L.down_in_off:], T, L.up_b, act_code)
+                if not up_fused:
+                    self._gemm(L.up, xb, self.gate, T, bias=L.up_b)    # activation applied when the bf16 operand is produced
             if L.q_norm_w is not None:
                 ops.head_rmsnorm_(qkv, L.q_norm_w, m.heads, hd, cfg.eps)
                 ops.head_rmsnorm_(qkv[:, qd:], L.k_norm_w, m.kv_heads, hd, cfg.eps)
@@ -144,31 +158,42 @@ class BatchedForward:
                 ops.rope_(qkv, self.positions[:T], m.heads + m.kv_heads, hd, cfg.rope_dim, cfg.rope_type, cfg.rope_theta, table=m.rope_table)
                 self.launches_per_pass += 1
             ops.kv_append(qkv[:, qd:], qkv[:, qd + kvd:], self.k_cache[l], self.v_cache[l], self.positions[:T], self.page_rows[:T], m.kv_heads, hd)
-            if pos0 is not None and shared_table and T >= self.flash_min_tokens and self.flash_ok:
-                ops.attn_prefill(self.qkv, self.attn[:, L.o_in_off:], self.k_cache[l], self.v_cache[l], page_table, T, pos0, m.heads, m.kv_heads, hd,
-                                 q_off=0, window=cfg.sliding_window or 0)
+            if pos0 is not None and shared_table and T >= self.flash_min_tokens and self.flash_ok and (L.o_in_off * 2) % 16 == 0:
+                ops.attn_prefill(self.qkv, self.attn_b[:, L.o_in_off:], self.k_cache[l], self.v_cache[l], page_table, T, pos0, m.heads, m.kv_heads, hd,
+                                 q_off=0, window=cfg.sliding_window or 0)       # bf16 result, read directly by the o_proj GEMM
+                self.launches_per_pass += 3
             else:
                 ops.attn_decode_launch(ops.build_attn_decode_params(
                     self.qkv, self.attn[:, L.o_in_off:], self.k_cache[l], self.v_cache[l], self.positions, page_table, self.attn_partial,
                     self.attn_counters, m.heads, m.kv_heads, hd, self.splits, T, 0, cfg.rope_type, cfg.rope_theta, 0, qd, qd + kvd,
                     None, None, cfg.eps, ld_qkv=self.qkv.stride(0), ld_out=self.attn.stride(0), shared_table=shared_table, no_append=True,
                     window=cfg.sliding_window or 0))
-            ops.to_bf16(self.attn[:T], self.attn_b[:T])
-            self.launches_per_pass += 4
+                ops.to_bf16(self.attn[:T], self.attn_b[:T])
+                self.launches_per_pass += 4
             self._row_parallel(L.o, self.attn_b[:T, : L.o.k], T, L.o_b)
+            act_dst = self.act_b[:, L.down_in_off:]
             if cfg.parallel_residual:
-                ops.swiglu_bf16(self.gate[:T], None, self.act_b[:T, L.down_in_off:], act_code)
-                self.launches_per_pass += 1
+                if not up_fused:
+                    ops.swiglu_bf16(self.gate[:T], None, self.act_b[:T, L.down_in_off:], act_code)
+                    self.launches_per_pass += 1
                 self._row_parallel(L.down, self.act_b[:T, : L.down.k], T, L.down_b)
             else:
                 ops.norm_bf16(x, xb, L.ffn_norm_w, L.ffn_norm_b, norm_t, cfg.eps)
+                self.launches_per_pass += 1
                 if cfg.gated_ffn:
-                    self._gemm(L.gate, xb, self.gate, T)
-                    self._gemm(L.up, xb, self.up, T, bias=L.up_b)
-                    ops.swiglu_bf16(self.gate[:T], self.up[:T], self.act_b[:T, L.down_in_off:], act_code)
-                else:
+                    # act(gate) in fp32 from the first GEMM's epilogue; the second multiplies it in and writes the bf16 operand
+                    fused = G.choose_splitk(L.up.n, L.up.k, T, self.sm_count) == 1 and G.choose_splitk(L.gate.n, L.gate.k, T, self.sm_count) == 1
+                    if fused:
+                        self._gemm(L.gate, xb, self.gate, T, act=act_code)
+                        self._gemm_to_operand(L.up, xb, act_dst, T, L.up_b, ACT_NONE, mul=self.gate)
+                    else:
+                        self._gemm(L.gate, xb, self.gate, T)
+                        self._gemm(L.up, xb, self.up, T, bias=L.up_b)
+                        ops.swiglu_bf16(self.gate[:T], self.up[:T], self.act_b[:T, L.down_in_off:], act_code)
+                        self.launches_per_pass += 1
+                elif not self._gemm_to_operand(L.up, xb, act_dst, T, L.up_b, act_code):
                     self._gemm(L.up, xb, self.gate, T, bias=L.up_b)
                     ops.swiglu_bf16(self.gate[:T], None, self.act_b[:T, L.down_in_off:], act_code)
-                self.launches_per_pass += 2
+                    self.launches_per_pass += 1
                 self._row_parallel(L.down, self.act_b[:T, : L.down.k], T, L.down_b)
         return x

@@ -273,6 +273,7 @@ def attn_prefill(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_
     p.n_heads, p.n_kv_heads, p.head_dim, p.q_off = n_heads, n_kv_heads, head_dim, q_off
     p.n_tokens, p.pos0, p.window, p.scale = int(n_tokens), int(pos0), int(window or 0), head_dim ** -0.5
     p.kv_q8 = 1 if k_cache.dtype in (torch.uint8, torch.int8) else 0
+    p.out_bf16 = 1 if out.dtype == torch.bfloat16 else 0          # bf16: written as the operand of the output-projection GEMM
     check(lib().rlz_attn_prefill(ctypes.byref(p), stream_ptr()), "attn_prefill")
 
 

@@ -60,7 +60,8 @@ class AttnDecodeParams(Structure):
 class AttnPrefillParams(Structure):
     _fields_ = [("qkv", c_void_p), ("out", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p), ("page_table", c_void_p),
                 ("ld_qkv", c_int64), ("ld_out", c_int64), ("n_heads", c_int32), ("n_kv_heads", c_int32), ("head_dim", c_int32),
-                ("q_off", c_int32), ("n_tokens", c_int32), ("pos0", c_int32), ("window", c_int32), ("kv_q8", c_int32), ("scale", c_float)]
+                ("q_off", c_int32), ("n_tokens", c_int32), ("pos0", c_int32), ("window", c_int32), ("kv_q8", c_int32), ("scale", c_float),
+                ("out_bf16", c_int32)]
 
 
 class SampleParams(Structure):
@@ -74,7 +75,7 @@ class GemmParams(Structure):
                 ("X", c_void_p), ("ldx", c_int64), ("Y", c_void_p), ("ldy", c_int64), ("bias", c_void_p), ("residual", c_void_p),
                 ("ld_res", c_int64), ("act", c_int32), ("splitk", c_int32), ("atomic_out", c_int32), ("_pad", c_int32),
                 ("ar_inbox", c_void_p * 8), ("ar_epoch", c_void_p), ("ar_row_pairs", c_int64), ("ar_rank", c_int32), ("ar_world", c_int32),
-                ("ar_rows", c_int32), ("ar_enabled", c_int32), ("ar_site", c_int32), ("ar_nsites", c_int32), ("ar_splits", c_int32), ("_pad2", c_int32)]
+                ("ar_rows", c_int32), ("ar_enabled", c_int32), ("ar_site", c_int32), ("ar_nsites", c_int32), ("ar_splits", c_int32), ("flags", c_int32)]
 
 
 class StepOp(Structure):

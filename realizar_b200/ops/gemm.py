@@ -11,6 +11,7 @@ from . import DeviceWeight, check, lib, ptr, stream_ptr, ACT_NONE
 from . import _signatures as S
 from ..quant import QType
 
+GM_OUT_BF16, GM_RES_MUL = 1, 2
 GEMM_TYPES = (int(QType.Q4_K), int(QType.Q5_K), int(QType.Q6_K), int(QType.BF16), int(QType.F16))
 
 
@@ -38,9 +39,13 @@ def choose_splitk(n: int, k: int, m: int, sm_count: int = 148) -> int:
 
 def build_gemm_params(w: DeviceWeight, x: torch.Tensor, y: torch.Tensor, m: int, bias=None, residual=None, act=ACT_NONE,
                       splitk: int = 1, ldx: Optional[int] = None, ldy: Optional[int] = None, ld_res: Optional[int] = None,
-                      wide: int = 0) -> S.GemmParams:
-    if x.dtype != torch.bfloat16 or y.dtype != torch.float32:
-        raise TypeError("gemm expects bf16 activations and an fp32 output")
+                      wide: int = 0, res_mul: bool = False) -> S.GemmParams:
+    """``y`` may be bf16 (the epilogue then writes the operand of the next GEMM directly; not with split-K).
+    ``res_mul``: the ``residual`` operand multiplies the activated result instead of being added (gated MLP)."""
+    if x.dtype != torch.bfloat16 or y.dtype not in (torch.float32, torch.bfloat16):
+        raise TypeError("gemm expects bf16 activations and an fp32 or bf16 output")
+    if (y.dtype == torch.bfloat16 or res_mul) and splitk > 1:
+        raise ValueError("bf16 output and the multiplying operand need an unsplit K")
     p = S.GemmParams()
     p.W, p.w_stride, p.qtype, p.n, p.k, p.m = w.data.data_ptr(), w.stride, w.qtype, w.n, w.k, m
     p.X, p.ldx = x.data_ptr(), ldx if ldx is not None else x.stride(0)
@@ -48,6 +53,7 @@ def build_gemm_params(w: DeviceWeight, x: torch.Tensor, y: torch.Tensor, m: int,
     p.bias, p.residual = ptr(bias), ptr(residual)
     p.ld_res = ld_res if ld_res is not None else (residual.stride(0) if residual is not None else 0)
     p.act, p.splitk = act, splitk
+    p.flags = (GM_OUT_BF16 if y.dtype == torch.bfloat16 else 0) | (GM_RES_MUL if res_mul else 0)
     p._pad = wide                       # 0: kernel decides between 128- and 256-row CTAs (m > 128), 1: 128 rows, 2: 256 rows
     return p
 
