@@ -176,12 +176,17 @@ def main():
     sampler.start()
     l0 = ops.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    profile_region = os.environ.get("RLZ_PROFILE_REGION") == "1"     # `ncu --profile-from-start off`: capture the timed steps only
+    if profile_region:
+        torch.cuda.cudart().cudaProfilerStart()
     e0.record()
     for _ in range(K):
         eng.run_step(B)
         eng.advance(B)
     e1.record()
     sync_all()
+    if profile_region:
+        torch.cuda.cudart().cudaProfilerStop()
     clocks = sampler.stop()
     eager_launches = ops.launch_count() - l0
     ms = e0.elapsed_time(e1)

@@ -18,6 +18,7 @@
 // flash_decoding_chunk+reduce kernels (src/cuda/executor/kv_scatter.rs:15-388,
 // src/cuda/executor/flash_decoding_graphed.rs:14-209, src/cuda/executor/batch.rs:18-400).
 #include "common.cuh"
+#include <stdlib.h>
 #include "attn_decode_static.h"
 #include "attention_decode_body.cuh"
 #include <cooperative_groups.h>
@@ -29,12 +30,29 @@ namespace rlz {
 template <int GT, int MERGE, int DEEP, int Q8>
 __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_constant__ AttnDecodeParams p) {
   __shared__ AttnSmem<GT, MERGE> sm;
+  extern __shared__ __align__(128) uint8_t att_ring[];      // streamed mode (DEEP == 2): the K/V page ring
   pdl_launch_dependents();
   pdl_wait();
-  attn_decode_body<GT, MERGE, DEEP, Q8, 0, false>(p, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, (int)threadIdx.x, sm, 0);
+  attn_decode_body<GT, MERGE, DEEP, Q8, 0, false>(p, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, (int)threadIdx.x, sm, 0, att_ring);
 }
 
-// Validate and launch: picks the head-group tile and the merge strategy.
+// launch one instantiation; `ring` bytes of dynamic shared memory (0 unless streamed)
+template <int GT, int MERGE, int DEEP, int Q8>
+static cudaError_t launch_attn(const AttnDecodeParams& p, dim3 grid, dim3 block, dim3 cl, size_t ring, cudaStream_t st) {
+  static size_t configured = 0;
+  if (ring > configured && ring > 16 * 1024) {                // above the default limit once the static part is added: opt in
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<GT, MERGE, DEEP, Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
+    if (e != cudaSuccess) return e;
+    configured = ring;
+  }
+  return launch_cluster(attn_decode_kernel<GT, MERGE, DEEP, Q8>, grid, block, cl, ring, st, p);
+}
+
+}  // namespace rlz
+
+namespace rlz {
+
+// Validate and launch: picks the head-group tile, the K/V access mode and the merge strategy.
 static int attn_decode_dispatch(const AttnDecodeParams& p, cudaStream_t st) {
   if (p.head_dim % 8 || p.head_dim > 128 || p.head_dim < 8) return -1;
   if (p.n_kv_heads < 1 || p.n_heads % p.n_kv_heads || p.splits < 1 || p.batch < 1) return -2;
@@ -49,11 +67,19 @@ static int attn_decode_dispatch(const AttnDecodeParams& p, cudaStream_t st) {
   dim3 cl(1, merge == MERGE_CLUSTER ? p.splits : 1, 1);
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const bool deep = (long long)grid.x * grid.y * grid.z < 4LL * sms;     // latency-bound launch: keep more loads in flight per thread
-#define RLZ_ATT_LAUNCH(GT_, M_) (p.kv_q8 ? (deep ? launch_cluster(attn_decode_kernel<GT_, M_, 1, 1>, grid, block, cl, 0, st, p)  \
-                                                 : launch_cluster(attn_decode_kernel<GT_, M_, 0, 1>, grid, block, cl, 0, st, p)) \
-                                         : (deep ? launch_cluster(attn_decode_kernel<GT_, M_, 1, 0>, grid, block, cl, 0, st, p)  \
-                                                 : launch_cluster(attn_decode_kernel<GT_, M_, 0, 0>, grid, block, cl, 0, st, p)))
+  // K/V access mode: 1 "deep" (latency-bound launch: many loads in flight per thread), 2 "streamed" (the grid fills the GPU
+  // several times over: pages come through a bulk-copy ring in shared memory), 0 plain register loads.  RLZ_ATT_MODE forces one.
+  static const int mode_env = [] { const char* e = getenv("RLZ_ATT_MODE"); return e ? atoi(e) : -1; }();
+  const long long ctas = (long long)grid.x * grid.y * grid.z;
+  // measured at batch 64: streamed 0.94x the time of plain loads with 4 query heads per KV head (head_dim 128), 1.15x with one
+  // (head_dim 80: the arithmetic, not the loads, sets the pace there), so the ring is the default for grouped heads only
+  int mode = ctas < 4LL * sms ? 1 : GT >= 4 ? 2 : 0;
+  if (mode_env >= 0 && mode_env <= 2) mode = mode_env;
+  const size_t ring = mode == 2 ? (size_t)ATT_RING * 4 * ATT_PAGE * (p.kv_q8 ? p.head_dim + 16 : 2 * p.head_dim) : 0;
+#define RLZ_ATT_MODE_LAUNCH(GT_, M_, Q_) (mode == 1 ? launch_attn<GT_, M_, 1, Q_>(p, grid, block, cl, 0, st) \
+                                        : mode == 2 ? launch_attn<GT_, M_, 2, Q_>(p, grid, block, cl, ring, st) \
+                                                    : launch_attn<GT_, M_, 0, Q_>(p, grid, block, cl, 0, st))
+#define RLZ_ATT_LAUNCH(GT_, M_) (p.kv_q8 ? RLZ_ATT_MODE_LAUNCH(GT_, M_, 1) : RLZ_ATT_MODE_LAUNCH(GT_, M_, 0))
 #define RLZ_ATT_CASE(GT_) \
   (merge == MERGE_NONE ? RLZ_ATT_LAUNCH(GT_, MERGE_NONE) : merge == MERGE_CLUSTER ? RLZ_ATT_LAUNCH(GT_, MERGE_CLUSTER) : RLZ_ATT_LAUNCH(GT_, MERGE_GLOBAL))
   cudaError_t e;
@@ -64,6 +90,7 @@ static int attn_decode_dispatch(const AttnDecodeParams& p, cudaStream_t st) {
     default: e = RLZ_ATT_CASE(4); break;
   }
 #undef RLZ_ATT_LAUNCH
+#undef RLZ_ATT_MODE_LAUNCH
 #undef RLZ_ATT_CASE
   return (int)e;
 }
@@ -131,6 +158,14 @@ int rlz_attn_decode_static(const rlz::AttnDecodeParams* pp, void* stream) {
   p.partial = sc.partial;
   p.counters = sc.counters;
   return attn_decode_dispatch(p, st);
+}
+
+// 0 / 3201 (a streamed K/V stage never arrived)
+int rlz_attn_decode_error(int clear) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, rlz::g_attn_decode_error, sizeof(int)) != cudaSuccess) return -1;
+  if (clear && v) { int z = 0; cudaMemcpyToSymbol(rlz::g_attn_decode_error, &z, sizeof(int)); }
+  return v;
 }
 
 int rlz_sizeof_attn_decode_params() { return (int)sizeof(rlz::AttnDecodeParams); }

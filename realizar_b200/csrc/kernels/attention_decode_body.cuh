@@ -15,6 +15,8 @@ constexpr int ATT_THREADS = 128;     // 8 half-warps; each takes up to TB tokens
 constexpr int ATT_WARPS = ATT_THREADS / 32;
 constexpr int ATT_PT_MAX = 64;       // page-table entries of a split staged in shared memory (1024 tokens)
 constexpr int ATT_MAX_CLUSTER = 8;   // portable cluster size
+constexpr int ATT_RING = 4;          // streamed mode: ring stages of two pages (32 tokens) of K and V each
+constexpr uint32_t ATT_WAIT_LIMIT = 1u << 22;
 enum { MERGE_GLOBAL = 0, MERGE_CLUSTER = 1, MERGE_NONE = 2 };
 
 struct AttnDecodeParams {
@@ -74,6 +76,20 @@ __device__ __forceinline__ void rope_inplace(float* v, int d_rot, int rope_type,
   }
 }
 
+static __device__ int g_attn_decode_error = 0;      // 3201: a streamed K/V stage never arrived (bounded wait ran out)
+
+__device__ __forceinline__ uint32_t att_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool att_try_wait(unsigned long long* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(att_smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void att_bulk_g2s(void* dst, const void* src, uint32_t bytes, unsigned long long* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(att_smem_u32(dst)), "l"(src), "r"(bytes), "r"(att_smem_u32(bar)) : "memory");
+}
+
 // Shared memory of one 128-thread attention job.
 // MERGE_CLUSTER: up to 4 heads per CTA the splits PUSH their results into the gather buffer of cluster rank 0 and leave;
 // with 8 heads the buffer would not fit in static shared memory and rank 0 pulls the peers' res_s instead
@@ -87,15 +103,19 @@ template <int GT, int MERGE> struct AttnSmem {
   int32_t pt_s[ATT_PT_MAX];               // physical pages of this split's token range
   float qs_s[2][ATT_THREADS / 32 + 1];    // int8 cache: max|k|, max|v| of the new row (per warp, then total)
   int last_flag;
+  unsigned long long full[ATT_RING];      // streamed mode: one mbarrier per ring stage
 };
 
 // The work of one attention CTA: job (bx = kv head x head group, split, b = sequence), thread tid of 128.
 // SUB = false: the 128 threads are a whole CTA (standalone kernel).  SUB = true: they are one quarter of a larger CTA of a
 // persistent kernel and synchronise on the named barrier `bar`; only the global-memory merge modes are available there.
 // TBO > 0 overrides the tokens taken per half-warp per iteration (register budget of the host kernel).
+// DEEP = 2 ("streamed", for launches that fill the GPU many times over): the pages of the split are brought into a ring in
+// shared memory (`ring`, ATT_RING stages of two pages of K and two of V) by bulk async copies, several stages ahead of the
+// arithmetic, instead of being loaded into registers by the threads that use them.
 template <int GT, int MERGE, int DEEP, int Q8, int TBO, bool SUB>
 __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, const int bx, const int split, const int b, const int tid,
-                                                 AttnSmem<GT, MERGE>& sm, const int bar) {
+                                                 AttnSmem<GT, MERGE>& sm, const int bar, uint8_t* ring = nullptr) {
 #define ATT_SYNC() do { if (SUB) asm volatile("bar.sync %0, %1;" ::"r"(bar), "n"(ATT_THREADS) : "memory"); else __syncthreads(); } while (0)
   static_assert(!SUB || MERGE != MERGE_CLUSTER, "cluster merge needs one job per CTA");
   const int G = p.n_heads / p.n_kv_heads;
@@ -211,14 +231,68 @@ __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, cons
   // tokens per half-warp per iteration: as many as the registers of this head-group size allow, so that a split of up
   // to 8 * TB tokens (96 for MHA) has all its K/V loads in flight at once and pays the memory latency a single time
   // (DEEP = 0, used when the grid already fills the GPU several times over: 4 tokens, fewer registers, more CTAs per SM)
-  constexpr int TB = TBO > 0 ? TBO : !DEEP ? 4 : GT == 1 ? 12 : GT == 2 ? 10 : GT == 4 ? 8 : 4;
+  constexpr int TB = TBO > 0 ? TBO : DEEP != 1 ? 4 : GT == 1 ? 12 : GT == 2 ? 10 : GT == 4 ? 8 : 4;
   constexpr int TOK_IT = (ATT_THREADS / 16) * TB;
   const int iters = (max(0, end - start) + TOK_IT - 1) / TOK_IT;
-  // head groups > 0 of the split that owns the new position read that row from shared memory (only the owner staged it)
-  const bool new_from_smem = owner && hg != 0;
+  constexpr bool STREAM = DEEP == 2;
+  static_assert(!STREAM || (TB == 4 && !SUB), "streamed mode: 32 tokens (two pages) per iteration, standalone kernel");
+  // head groups > 0 of the split that owns the new position read that row from shared memory (only the owner staged it);
+  // in streamed mode every owner does: the page copy may race with the append of the new row
+  const bool new_from_smem = owner && (STREAM || hg != 0);
+  const uint32_t page_bytes = (uint32_t)(ATT_PAGE * rowb), stage_bytes = 4u * page_bytes;     // K page 0, K page 1, V page 0, V page 1
+  bool stream_ok = true;
+  auto issue = [&](int it) {                               // thread 0: request the two pages of iteration `it`
+    const int slot = it % ATT_RING;
+    const int tok0 = start + it * TOK_IT;
+    const int np = min(2, (end - tok0 + ATT_PAGE - 1) / ATT_PAGE);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(att_smem_u32(&sm.full[slot])), "r"(2u * np * page_bytes) : "memory");
+    for (int pi = 0; pi < np; ++pi) {
+      const int tk = tok0 + pi * ATT_PAGE;
+      const int page = pt_staged ? pt_s[(tk - start) / ATT_PAGE] : pt[tk / ATT_PAGE];
+      const int64_t boff = ((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE * rowb;
+      uint8_t* dst = ring + (size_t)slot * stage_bytes + (size_t)pi * page_bytes;
+      att_bulk_g2s(dst, (const uint8_t*)p.k_cache + boff, page_bytes, &sm.full[slot]);
+      att_bulk_g2s(dst + 2 * page_bytes, (const uint8_t*)p.v_cache + boff, page_bytes, &sm.full[slot]);
+    }
+  };
+  if (STREAM) {
+    if (tid == 0) {
+      for (int i = 0; i < ATT_RING; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(att_smem_u32(&sm.full[i])));
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      for (int it = 0; it < min(ATT_RING, iters); ++it) issue(it);
+    }
+    ATT_SYNC();
+  }
   for (int it = 0; it < iters; ++it) {
     const int base = start + (it * (ATT_THREADS / 16) + hw) * TB;
     uint4 kr[TB], vr[TB];
+    if (STREAM) {
+      unsigned long long* fb = &sm.full[it % ATT_RING];
+      const uint32_t parity = (uint32_t)(it / ATT_RING) & 1u;
+      bool arrived = false;
+      const uint32_t limit = stream_ok ? ATT_WAIT_LIMIT : 1024u;       // after a failure the remaining stages get a short wait each
+      for (uint32_t spin = 0; spin < limit; ++spin) if (att_try_wait(fb, parity)) { arrived = true; break; }
+      if (!arrived) { stream_ok = false; atomicExch(&g_attn_decode_error, 3201); }
+      const uint8_t* st = ring + (size_t)(it % ATT_RING) * stage_bytes + (size_t)(hw >> 2) * page_bytes;      // my page of the stage
+#pragma unroll
+      for (int t = 0; t < TB; ++t) {
+        const int tok = base + t;
+        const bool okl = stream_ok && lane_ok && tok < end && !(new_from_smem && tok == pos);
+        const uint8_t* kp = st + (size_t)((hw & 3) * TB + t) * rowb;
+        const uint8_t* vp = kp + 2 * page_bytes;
+        if (q8) {
+          const uint2 kc = okl ? *(const uint2*)(kp + j0) : make_uint2(0, 0);
+          const uint2 vc = okl ? *(const uint2*)(vp + j0) : make_uint2(0, 0);
+          kr[t] = make_uint4(kc.x, kc.y, okl ? *(const uint32_t*)(kp + d) : 0u, 0u);
+          vr[t] = make_uint4(vc.x, vc.y, okl ? *(const uint32_t*)(vp + d) : 0u, 0u);
+        } else {
+          kr[t] = okl ? *(const uint4*)(kp + 2 * j0) : make_uint4(0, 0, 0, 0);
+          vr[t] = okl ? *(const uint4*)(vp + 2 * j0) : make_uint4(0, 0, 0, 0);
+        }
+      }
+      ATT_SYNC();                                          // every thread has taken its rows: the stage may be refilled
+      if (tid == 0 && it + ATT_RING < iters) issue(it + ATT_RING);
+    } else {
 #pragma unroll
     for (int t = 0; t < TB; ++t) {
       const int tok = base + t;
@@ -238,6 +312,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, cons
         kr[t] = okl ? *(const uint4*)(p.k_cache + off) : make_uint4(0, 0, 0, 0);
         vr[t] = okl ? *(const uint4*)(p.v_cache + off) : make_uint4(0, 0, 0, 0);
       }
+    }
     }
     float sc[GT][TB];
     // pass 1: scores (K converted one token at a time)

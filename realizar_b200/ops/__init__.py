@@ -198,7 +198,8 @@ def gemv_stream_launch(p: S.GemvParams) -> None:
 
 def device_error(clear: bool = True) -> int:
     """Error code recorded by a kernel whose bounded wait expired (0 = none)."""
-    return int(lib().rlz_device_error(1 if clear else 0)) or int(lib().rlz_gemm_error(1 if clear else 0))
+    return (int(lib().rlz_device_error(1 if clear else 0)) or int(lib().rlz_gemm_error(1 if clear else 0))
+            or int(lib().rlz_attn_decode_error(1 if clear else 0)))
 
 
 def gemv(w: DeviceWeight, x: torch.Tensor, bias=None, act=ACT_NONE, residual=None, norm=NORM_NONE, norm_w=None, norm_b=None,

@@ -123,6 +123,7 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_epoch_bump.argtypes = [c_void_p, c_void_p]
     lib.rlz_cand_exchange.argtypes = [POINTER(CandExchange), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.rlz_attn_decode.argtypes = [POINTER(AttnDecodeParams), c_void_p]
+    lib.rlz_attn_decode_error.argtypes = [c_int]
     lib.rlz_attn_decode_partial_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.rlz_attn_decode_partial_floats.restype = c_longlong
     lib.rlz_attn_decode_counter_ints.argtypes = [c_int, c_int]
