@@ -157,10 +157,15 @@ def main():
     eng.close_slot(0)
     eng.open_slot(0, max_seq)
     sync_all()
+    profile_prefill = os.environ.get("RLZ_PROFILE_REGION") == "prefill"   # `ncu --profile-from-start off`: capture the timed prefill only
+    if profile_prefill:
+        torch.cuda.cudart().cudaProfilerStart()
     t0 = time.time()
     first = [eng.prefill(b, [int(t) for t in prompts[b]]) for b in range(B)]
     torch.cuda.synchronize(dev)
     prefill_s = time.time() - t0
+    if profile_prefill:
+        torch.cuda.cudart().cudaProfilerStop()
 
     # ---- device-timed decode: graph replays with device-side feedback ---------------------------
     pos0 = eng.slots[0].position
@@ -176,7 +181,7 @@ def main():
     sampler.start()
     l0 = ops.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    profile_region = os.environ.get("RLZ_PROFILE_REGION") == "1"     # `ncu --profile-from-start off`: capture the timed steps only
+    profile_region = os.environ.get("RLZ_PROFILE_REGION") in ("1", "decode")     # `ncu --profile-from-start off`: capture the timed steps only
     if profile_region:
         torch.cuda.cudart().cudaProfilerStart()
     e0.record()

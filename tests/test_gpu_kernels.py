@@ -190,6 +190,40 @@ def test_attn_decode_matches_reference(cuda_device, H, Hkv, d, rope_dim, rope_ty
         assert _rel(kc[pg, :, slot].float(), kn[0].to(torch.bfloat16).float()) < 1e-2
 
 
+def test_attn_decode_streamed_pages_large_batch(cuda_device):
+    """A grouped-head launch that fills the GPU several times over takes the streamed mode (K/V pages through a
+    bulk-copy ring in shared memory): 80 sequences of different lengths, 8 KV heads x 4 query heads, one split and two."""
+    from realizar_b200 import ops
+    torch.manual_seed(5)
+    H, Hkv, d, B, pages_per_seq = 32, 8, 128, 80, 8
+    n_pages = B * pages_per_seq
+    kc = (torch.randn(n_pages, Hkv, 16, d, device="cuda") * 0.5).to(torch.bfloat16)
+    vc = (torch.randn(n_pages, Hkv, 16, d, device="cuda") * 0.5).to(torch.bfloat16)
+    page_table = torch.randperm(n_pages, device="cuda").to(torch.int32).reshape(B, pages_per_seq).contiguous()
+    lens = torch.randint(1, pages_per_seq * 16, (B,))
+    lens[0], lens[1], lens[2] = 1, 16, 17
+    for splits in (1, 2):
+        k0, v0 = kc.clone(), vc.clone()
+        qkv = torch.randn(B, (H + 2 * Hkv) * d, device="cuda")
+        positions = (lens - 1).to(torch.int32).cuda()
+        out = torch.zeros(B, H * d, device="cuda")
+        partial, counters = ops.attn_decode_scratch(B, H, splits, d, "cuda")
+        ops.attn_decode_launch(ops.build_attn_decode_params(qkv, out, k0, v0, positions, page_table, partial, counters, H, Hkv, d, splits, B, 0, 0,
+                                                            1e4, 0, H * d, (H + Hkv) * d))
+        torch.cuda.synchronize()
+        assert ops.lib().rlz_attn_decode_error(1) == 0
+        for b in (0, 1, 2, 7, 33, 79):
+            L = int(lens[b])
+            pages = page_table[b, : (L + 15) // 16].long()
+            k_all = kc[pages].permute(0, 2, 1, 3).reshape(-1, Hkv, d)[:L].float().clone()      # [tokens, Hkv, d]
+            v_all = vc[pages].permute(0, 2, 1, 3).reshape(-1, Hkv, d)[:L].float().clone()
+            row = qkv[b]
+            k_all[L - 1] = row[H * d:(H + Hkv) * d].reshape(Hkv, d).to(torch.bfloat16).float()
+            v_all[L - 1] = row[(H + Hkv) * d:].reshape(Hkv, d).to(torch.bfloat16).float()
+            ref = _ref_attention(row[: H * d].reshape(H, d).cpu(), k_all.cpu(), v_all.cpu(), d ** -0.5).reshape(-1)
+            assert _rel(out[b], ref) < 5e-3, (splits, b, L, _rel(out[b], ref))
+
+
 def test_attn_decode_inactive_slot_and_qk_norm(cuda_device):
     from realizar_b200 import ops
     H, Hkv, d, B, splits = 4, 2, 64, 2, 2
