@@ -36,6 +36,37 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
   attn_decode_body<GT, MERGE, DEEP, Q8, 0, false>(p, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, (int)threadIdx.x, sm, 0, att_ring);
 }
 
+// tensor-core mode: head_dim is a template parameter
+template <int GT, int MERGE, int HD>
+__global__ void __launch_bounds__(ATT_THREADS) attn_decode_mma_kernel(const __grid_constant__ AttnDecodeParams p) {
+  __shared__ AttnSmem<GT, MERGE> sm;
+  extern __shared__ __align__(128) uint8_t att_ring[];
+  pdl_launch_dependents();
+  pdl_wait();
+  attn_decode_body<GT, MERGE, 3, 0, 0, false, HD>(p, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, (int)threadIdx.x, sm, 0, att_ring);
+}
+
+template <int GT, int HD>
+static cudaError_t launch_attn_mma(const AttnDecodeParams& p, dim3 grid, dim3 block, cudaStream_t st) {
+  const size_t ring = (size_t)ATT_RING * 64 * (HD == 80 ? 2 * HD : 2 * HD + 16);       // row bytes as in the kernel
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<GT, MERGE_NONE, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  return launch_cluster(attn_decode_mma_kernel<GT, MERGE_NONE, HD>, grid, block, dim3(1, 1, 1), ring, st, p);
+}
+template <int GT>
+static cudaError_t launch_attn_mma_hd(const AttnDecodeParams& p, dim3 grid, dim3 block, cudaStream_t st) {
+  switch (p.head_dim) {
+    case 64: return launch_attn_mma<GT, 64>(p, grid, block, st);
+    case 80: return launch_attn_mma<GT, 80>(p, grid, block, st);
+    case 96: return launch_attn_mma<GT, 96>(p, grid, block, st);
+    default: return launch_attn_mma<GT, 128>(p, grid, block, st);
+  }
+}
+
 // launch one instantiation; `ring` bytes of dynamic shared memory (0 unless streamed)
 template <int GT, int MERGE, int DEEP, int Q8>
 static cudaError_t launch_attn(const AttnDecodeParams& p, dim3 grid, dim3 block, dim3 cl, size_t ring, cudaStream_t st) {
@@ -74,7 +105,18 @@ static int attn_decode_dispatch(const AttnDecodeParams& p, cudaStream_t st) {
   // measured at batch 64: streamed 0.94x the time of plain loads with 4 query heads per KV head (head_dim 128), 1.15x with one
   // (head_dim 80: the arithmetic, not the loads, sets the pace there), so the ring is the default for grouped heads only
   int mode = ctas < 4LL * sms ? 1 : GT >= 4 ? 2 : 0;
-  if (mode_env >= 0 && mode_env <= 2) mode = mode_env;
+  if (mode_env >= 0 && mode_env <= 3) mode = mode_env;
+  // 3 "tensor-core" (RLZ_ATT_MODE=3): one split, bf16 cache, head_dim 64 / 80 / 96 / 128
+  const bool mma_ok = merge == MERGE_NONE && !p.kv_q8 && (p.head_dim == 64 || p.head_dim == 80 || p.head_dim == 96 || p.head_dim == 128);
+  if (mode == 3 && !mma_ok) mode = ctas < 4LL * sms ? 1 : GT >= 4 ? 2 : 0;
+  if (mode == 3) {
+    switch (GT) {
+      case 1: return (int)launch_attn_mma_hd<1>(p, grid, block, st);
+      case 2: return (int)launch_attn_mma_hd<2>(p, grid, block, st);
+      case 8: return (int)launch_attn_mma_hd<8>(p, grid, block, st);
+      default: return (int)launch_attn_mma_hd<4>(p, grid, block, st);
+    }
+  }
   const size_t ring = mode == 2 ? (size_t)ATT_RING * 4 * ATT_PAGE * (p.kv_q8 ? p.head_dim + 16 : 2 * p.head_dim) : 0;
 #define RLZ_ATT_MODE_LAUNCH(GT_, M_, Q_) (mode == 1 ? launch_attn<GT_, M_, 1, Q_>(p, grid, block, cl, 0, st) \
                                         : mode == 2 ? launch_attn<GT_, M_, 2, Q_>(p, grid, block, cl, ring, st) \

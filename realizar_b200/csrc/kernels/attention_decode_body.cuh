@@ -90,6 +90,19 @@ __device__ __forceinline__ void att_bulk_g2s(void* dst, const void* src, uint32_
                ::"r"(att_smem_u32(dst)), "l"(src), "r"(bytes), "r"(att_smem_u32(bar)) : "memory");
 }
 
+__device__ __forceinline__ uint32_t att_pack_bf16(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *(const uint32_t*)&v;
+}
+__device__ __forceinline__ void att_mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void att_ldmatrix_x4_trans(uint32_t* r, const void* row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(att_smem_u32(row)) : "memory");
+}
+
 // Shared memory of one 128-thread attention job.
 // MERGE_CLUSTER: up to 4 heads per CTA the splits PUSH their results into the gather buffer of cluster rank 0 and leave;
 // with 8 heads the buffer would not fit in static shared memory and rank 0 pulls the peers' res_s instead
@@ -113,7 +126,11 @@ template <int GT, int MERGE> struct AttnSmem {
 // DEEP = 2 ("streamed", for launches that fill the GPU many times over): the pages of the split are brought into a ring in
 // shared memory (`ring`, ATT_RING stages of two pages of K and two of V) by bulk async copies, several stages ahead of the
 // arithmetic, instead of being loaded into registers by the threads that use them.
-template <int GT, int MERGE, int DEEP, int Q8, int TBO, bool SUB>
+// DEEP = 3 ("tensor-core", head_dim HD known at compile time, bf16 cache): every warp owns one ring slot of 32 token rows
+// (padded to HD * 2 + 16 bytes so that fragment loads are conflict-free) and computes S = Q K^T and O += P V of its stages
+// with mma.sync m16n8k16 (rows = the query heads of the group, padded to 16), about a seventh of the instructions per token
+// of the scalar path; the warps' partial results meet in the same merge as the other modes.
+template <int GT, int MERGE, int DEEP, int Q8, int TBO, bool SUB, int HD = 0>
 __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, const int bx, const int split, const int b, const int tid,
                                                  AttnSmem<GT, MERGE>& sm, const int bar, uint8_t* ring = nullptr) {
 #define ATT_SYNC() do { if (SUB) asm volatile("bar.sync %0, %1;" ::"r"(bar), "n"(ATT_THREADS) : "memory"); else __syncthreads(); } while (0)
@@ -234,6 +251,152 @@ __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, cons
   constexpr int TB = TBO > 0 ? TBO : DEEP != 1 ? 4 : GT == 1 ? 12 : GT == 2 ? 10 : GT == 4 ? 8 : 4;
   constexpr int TOK_IT = (ATT_THREADS / 16) * TB;
   const int iters = (max(0, end - start) + TOK_IT - 1) / TOK_IT;
+  if constexpr (DEEP == 3) {
+    static_assert(HD % 16 == 0 && HD >= 16 && HD <= 128 && GT <= 8 && !SUB && Q8 == 0, "tensor-core mode: bf16 cache, head_dim a multiple of 16, up to 8 query heads");
+    // head_dim 80: rows of 160 bytes are at most 2-way bank-conflicted unpadded, so whole pages (16 rows, 2560 bytes) are copied
+    // with one bulk copy each; the other sizes copy row by row into rows padded by 16 bytes (conflict-free fragment loads)
+    constexpr bool PAGE_COPY = HD == 80;
+    constexpr int KS = HD / 16, NTL = HD / 8, RS = PAGE_COPY ? 2 * HD : 2 * HD + 16;   // k steps of QK^T, n tiles of PV, row bytes
+    constexpr int SLOT = 64 * RS;                                          // 32 K rows, then 32 V rows
+    uint8_t* slot = ring + (size_t)warp * SLOT;
+    unsigned long long* fb = &sm.full[warp];
+    const int gq = lane >> 2, tq = lane & 3;                               // fragment coordinates: row group, thread in group
+    if (tid == 0) {
+      for (int i = 0; i < ATT_RING; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(att_smem_u32(&sm.full[i])));
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    ATT_SYNC();
+    // request the 32 token rows of iteration `it` into this warp's slot: every lane copies the K and V row of its token
+    auto issue = [&](int it) {
+      const int tok0 = start + it * 32, nvalid = min(32, end - tok0);
+      if (PAGE_COPY) {
+        const int np = (nvalid + ATT_PAGE - 1) / ATT_PAGE;                 // whole pages: lanes 0..3 = (K, V) x (page 0, page 1)
+        if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(att_smem_u32(fb)), "r"((uint32_t)(np * 2 * ATT_PAGE * RS)) : "memory");
+        __syncwarp();
+        if (lane < 4 && (lane & 1) < np) {
+          const int tok = tok0 + (lane & 1) * ATT_PAGE;
+          const int page = pt_staged ? pt_s[(tok - start) / ATT_PAGE] : pt[tok / ATT_PAGE];
+          const int64_t boff = ((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE * RS;
+          const uint8_t* src = (lane & 2 ? (const uint8_t*)p.v_cache : (const uint8_t*)p.k_cache) + boff;
+          att_bulk_g2s(slot + ((lane & 2 ? 32 : 0) + (lane & 1) * ATT_PAGE) * RS, src, ATT_PAGE * RS, fb);
+        }
+        return;
+      }
+      if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(att_smem_u32(fb)), "r"((uint32_t)(nvalid * 4 * HD)) : "memory");
+      __syncwarp();
+      if (lane < nvalid) {
+        const int tok = tok0 + lane;
+        const int page = pt_staged ? pt_s[(tok - start) / ATT_PAGE] : pt[tok / ATT_PAGE];
+        const int64_t rowi = ((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE + (tok % ATT_PAGE);
+        att_bulk_g2s(slot + lane * RS, (const uint8_t*)p.k_cache + rowi * (2 * HD), 2 * HD, fb);
+        att_bulk_g2s(slot + (32 + lane) * RS, (const uint8_t*)p.v_cache + rowi * (2 * HD), 2 * HD, fb);
+      }
+    };
+    if (warp < iters) issue(warp);
+    // Q fragments (row = query head gq, pre-scaled, bf16): a0 = dims 2tq, 2tq+1 of a k step, a2 = the same + 8
+    uint32_t qa[KS][2];
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int jq = ks * 16 + 2 * tq;
+      qa[ks][0] = gq < gn ? att_pack_bf16(q_s[gq < GT ? gq : 0][jq] * qscale, q_s[gq < GT ? gq : 0][jq + 1] * qscale) : 0u;
+      qa[ks][1] = gq < gn ? att_pack_bf16(q_s[gq < GT ? gq : 0][jq + 8] * qscale, q_s[gq < GT ? gq : 0][jq + 9] * qscale) : 0u;
+    }
+    float o[NTL][4];
+#pragma unroll
+    for (int n = 0; n < NTL; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    float mrow = -INFINITY, lsum = 0.f;
+    bool stream_ok = true;
+    for (int it = warp; it < iters; it += ATT_RING) {
+      const int tok0 = start + it * 32;
+      const uint32_t parity = (uint32_t)(it / ATT_RING) & 1u;
+      bool arrived = false;
+      const uint32_t limit = stream_ok ? ATT_WAIT_LIMIT : 1024u;
+      for (uint32_t spin = 0; spin < limit; ++spin) if (att_try_wait(fb, parity)) { arrived = true; break; }
+      if (!arrived) { stream_ok = false; atomicExch(&g_attn_decode_error, 3201); }
+      {   // rows past the end hold stale bytes: zero them; the new token's row comes from the staged k_s / v_s
+        const int tok = tok0 + lane;
+        uint4* kr4 = (uint4*)(slot + lane * RS); uint4* vr4 = (uint4*)(slot + (32 + lane) * RS);
+        if (tok >= end || !stream_ok) {
+#pragma unroll
+          for (int c = 0; c < HD / 8; ++c) { kr4[c] = make_uint4(0, 0, 0, 0); vr4[c] = make_uint4(0, 0, 0, 0); }
+        } else if (owner && tok == pos) {
+#pragma unroll
+          for (int c = 0; c < HD / 8; ++c) {
+            kr4[c] = make_uint4(att_pack_bf16(k_s[8 * c], k_s[8 * c + 1]), att_pack_bf16(k_s[8 * c + 2], k_s[8 * c + 3]),
+                                att_pack_bf16(k_s[8 * c + 4], k_s[8 * c + 5]), att_pack_bf16(k_s[8 * c + 6], k_s[8 * c + 7]));
+            vr4[c] = make_uint4(att_pack_bf16(v_s[8 * c], v_s[8 * c + 1]), att_pack_bf16(v_s[8 * c + 2], v_s[8 * c + 3]),
+                                att_pack_bf16(v_s[8 * c + 4], v_s[8 * c + 5]), att_pack_bf16(v_s[8 * c + 6], v_s[8 * c + 7]));
+          }
+        }
+      }
+      __syncwarp();
+      // ---- S = Q K^T: 4 tiles of 8 tokens; B fragment = two 4-byte words of the token's K row ----
+      float sacc[4][4];
+#pragma unroll
+      for (int n = 0; n < 4; ++n) { sacc[n][0] = sacc[n][1] = sacc[n][2] = sacc[n][3] = 0.f; }
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+          const uint8_t* kp = slot + (8 * n + gq) * RS + (ks * 16 + 2 * tq) * 2;
+          att_mma_bf16(sacc[n], qa[ks][0], 0u, qa[ks][1], 0u, *(const uint32_t*)kp, *(const uint32_t*)(kp + 16));
+        }
+      }
+      // ---- online softmax of row gq (the 4 lanes of a group hold its 32 scores) ----
+      float mx = -INFINITY;
+      bool vis[4][2];
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int tok = tok0 + 8 * n + 2 * tq + e;
+          vis[n][e] = tok < end && tok >= lo;
+          if (vis[n][e]) mx = fmaxf(mx, sacc[n][e]);
+        }
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+      const float mnew = fmaxf(mrow, mx);
+      const float corr = mnew == -INFINITY ? 1.f : exp2f(mrow - mnew);
+      uint32_t pa[2][2];
+      float psum = 0.f;
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        const float p0 = vis[n][0] ? exp2f(sacc[n][0] - mnew) : 0.f, p1 = vis[n][1] ? exp2f(sacc[n][1] - mnew) : 0.f;
+        const uint32_t pk = att_pack_bf16(p0, p1);
+        psum += __uint_as_float(pk << 16) + __uint_as_float(pk & 0xFFFF0000u);      // the rounded values the tensor core multiplies
+        pa[n >> 1][n & 1] = pk;
+      }
+      lsum = lsum * corr + psum;
+      mrow = mnew;
+#pragma unroll
+      for (int n = 0; n < NTL; ++n) { o[n][0] *= corr; o[n][1] *= corr; }
+      // ---- O += P V: V rows are [token][dim]; ldmatrix.trans hands out the (token pair, dim) fragments ----
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+        for (int n = 0; n < NTL; n += 2) {
+          uint32_t r[4];
+          const uint8_t* vrow = slot + (32 + 16 * kk + ((lane >> 3) & 1) * 8 + (lane & 7)) * RS + (n + (lane >> 4)) * 16;
+          att_ldmatrix_x4_trans(r, vrow);
+          att_mma_bf16(o[n], pa[kk][0], 0u, pa[kk][1], 0u, r[0], r[1]);
+          att_mma_bf16(o[n + 1], pa[kk][0], 0u, pa[kk][1], 0u, r[2], r[3]);
+        }
+      }
+      __syncwarp();
+      if (it + ATT_RING < iters) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // this warp's reads of the slot come before the refill
+        issue(it + ATT_RING);
+      }
+    }
+    lsum += __shfl_xor_sync(0xFFFFFFFFu, lsum, 1);
+    lsum += __shfl_xor_sync(0xFFFFFFFFu, lsum, 2);
+    if (gq < gn) {
+#pragma unroll
+      for (int n = 0; n < NTL; ++n) { part_s[warp][gq < GT ? gq : 0][8 * n + 2 * tq] = o[n][0]; part_s[warp][gq < GT ? gq : 0][8 * n + 2 * tq + 1] = o[n][1]; }
+      if (tq == 0) { part_s[warp][gq < GT ? gq : 0][128] = mrow; part_s[warp][gq < GT ? gq : 0][129] = lsum; }
+    }
+  } else {
   constexpr bool STREAM = DEEP == 2;
   static_assert(!STREAM || (TB == 4 && !SUB), "streamed mode: 32 tokens (two pages) per iteration, standalone kernel");
   // head groups > 0 of the split that owns the new position read that row from shared memory (only the owner staged it);
@@ -406,6 +569,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, cons
       }
       if (lane == 0) { part_s[warp][g][128] = m[g]; part_s[warp][g][129] = l[g]; }
     }
+  }
   }
   ATT_SYNC();
   const int S = p.splits;
