@@ -46,25 +46,29 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_mma_kernel(const __gr
   attn_decode_body<GT, MERGE, 3, 0, 0, false, HD>(p, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, (int)threadIdx.x, sm, 0, att_ring);
 }
 
-template <int GT, int HD>
-static cudaError_t launch_attn_mma(const AttnDecodeParams& p, dim3 grid, dim3 block, cudaStream_t st) {
+template <int GT, int MERGE, int HD>
+static cudaError_t launch_attn_mma(const AttnDecodeParams& p, dim3 grid, dim3 block, dim3 cl, cudaStream_t st) {
   const size_t ring = (size_t)ATT_RING * 64 * (HD == 80 ? 2 * HD : 2 * HD + 16);       // row bytes as in the kernel
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<GT, MERGE_NONE, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<GT, MERGE, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  return launch_cluster(attn_decode_mma_kernel<GT, MERGE_NONE, HD>, grid, block, dim3(1, 1, 1), ring, st, p);
+  return launch_cluster(attn_decode_mma_kernel<GT, MERGE, HD>, grid, block, cl, ring, st, p);
+}
+template <int GT, int MERGE>
+static cudaError_t launch_attn_mma_hd(const AttnDecodeParams& p, dim3 grid, dim3 block, dim3 cl, cudaStream_t st) {
+  switch (p.head_dim) {
+    case 64: return launch_attn_mma<GT, MERGE, 64>(p, grid, block, cl, st);
+    case 80: return launch_attn_mma<GT, MERGE, 80>(p, grid, block, cl, st);
+    case 96: return launch_attn_mma<GT, MERGE, 96>(p, grid, block, cl, st);
+    default: return launch_attn_mma<GT, MERGE, 128>(p, grid, block, cl, st);
+  }
 }
 template <int GT>
-static cudaError_t launch_attn_mma_hd(const AttnDecodeParams& p, dim3 grid, dim3 block, cudaStream_t st) {
-  switch (p.head_dim) {
-    case 64: return launch_attn_mma<GT, 64>(p, grid, block, st);
-    case 80: return launch_attn_mma<GT, 80>(p, grid, block, st);
-    case 96: return launch_attn_mma<GT, 96>(p, grid, block, st);
-    default: return launch_attn_mma<GT, 128>(p, grid, block, st);
-  }
+static cudaError_t launch_attn_mma_merge(const AttnDecodeParams& p, int merge, dim3 grid, dim3 block, dim3 cl, cudaStream_t st) {
+  return merge == MERGE_NONE ? launch_attn_mma_hd<GT, MERGE_NONE>(p, grid, block, cl, st) : launch_attn_mma_hd<GT, MERGE_CLUSTER>(p, grid, block, cl, st);
 }
 
 // launch one instantiation; `ring` bytes of dynamic shared memory (0 unless streamed)
@@ -102,19 +106,20 @@ static int attn_decode_dispatch(const AttnDecodeParams& p, cudaStream_t st) {
   // several times over: pages come through a bulk-copy ring in shared memory), 0 plain register loads.  RLZ_ATT_MODE forces one.
   static const int mode_env = [] { const char* e = getenv("RLZ_ATT_MODE"); return e ? atoi(e) : -1; }();
   const long long ctas = (long long)grid.x * grid.y * grid.z;
-  // measured at batch 64: streamed 0.94x the time of plain loads with 4 query heads per KV head (head_dim 128), 1.15x with one
-  // (head_dim 80: the arithmetic, not the loads, sets the pace there), so the ring is the default for grouped heads only
-  int mode = ctas < 4LL * sms ? 1 : GT >= 4 ? 2 : 0;
+  // 3 "tensor-core": bf16 cache, up to 8 splits, head_dim 64 / 80 / 96 / 128 - the default whenever it applies (measured against
+  // the scalar modes: 7.7 vs 9.4 us at batch 1 x 640 tokens, 82 vs 114 us at batch 64 x 576, 217 vs 363 us at batch 64 x 2048 =
+  // 0.94 of the measured copy bandwidth).  The scalar modes serve int8 caches, more than 8 splits and other head sizes.
+  const bool mma_ok = merge != MERGE_GLOBAL && !p.kv_q8 && (p.head_dim == 64 || p.head_dim == 80 || p.head_dim == 96 || p.head_dim == 128);
+  const int scalar_mode = ctas < 4LL * sms ? 1 : GT >= 4 ? 2 : 0;
+  int mode = mma_ok ? 3 : scalar_mode;
   if (mode_env >= 0 && mode_env <= 3) mode = mode_env;
-  // 3 "tensor-core" (RLZ_ATT_MODE=3): one split, bf16 cache, head_dim 64 / 80 / 96 / 128
-  const bool mma_ok = merge == MERGE_NONE && !p.kv_q8 && (p.head_dim == 64 || p.head_dim == 80 || p.head_dim == 96 || p.head_dim == 128);
-  if (mode == 3 && !mma_ok) mode = ctas < 4LL * sms ? 1 : GT >= 4 ? 2 : 0;
+  if (mode == 3 && !mma_ok) mode = scalar_mode;
   if (mode == 3) {
     switch (GT) {
-      case 1: return (int)launch_attn_mma_hd<1>(p, grid, block, st);
-      case 2: return (int)launch_attn_mma_hd<2>(p, grid, block, st);
-      case 8: return (int)launch_attn_mma_hd<8>(p, grid, block, st);
-      default: return (int)launch_attn_mma_hd<4>(p, grid, block, st);
+      case 1: return (int)launch_attn_mma_merge<1>(p, merge, grid, block, cl, st);
+      case 2: return (int)launch_attn_mma_merge<2>(p, merge, grid, block, cl, st);
+      case 8: return (int)launch_attn_mma_merge<8>(p, merge, grid, block, cl, st);
+      default: return (int)launch_attn_mma_merge<4>(p, merge, grid, block, cl, st);
     }
   }
   const size_t ring = mode == 2 ? (size_t)ATT_RING * 4 * ATT_PAGE * (p.kv_q8 ? p.head_dim + 16 : 2 * p.head_dim) : 0;

@@ -293,13 +293,19 @@ __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, cons
       }
     };
     if (warp < iters) issue(warp);
-    // Q fragments (row = query head gq, pre-scaled, bf16): a0 = dims 2tq, 2tq+1 of a k step, a2 = the same + 8
-    uint32_t qa[KS][2];
+    // Q fragments (row = query head gq, pre-scaled): a0 = dims 2tq, 2tq+1 of a k step, a2 = the same + 8.  q is split into a
+    // bf16 head and a bf16 remainder (two MMAs per tile) so that the scores keep fp32-like precision in q
+    uint32_t qa[KS][2], qb[KS][2];
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
-      const int jq = ks * 16 + 2 * tq;
-      qa[ks][0] = gq < gn ? att_pack_bf16(q_s[gq < GT ? gq : 0][jq] * qscale, q_s[gq < GT ? gq : 0][jq + 1] * qscale) : 0u;
-      qa[ks][1] = gq < gn ? att_pack_bf16(q_s[gq < GT ? gq : 0][jq + 8] * qscale, q_s[gq < GT ? gq : 0][jq + 9] * qscale) : 0u;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int jq = ks * 16 + 2 * tq + 8 * h;
+        const float f0 = gq < gn ? q_s[gq < GT ? gq : 0][jq] * qscale : 0.f, f1 = gq < gn ? q_s[gq < GT ? gq : 0][jq + 1] * qscale : 0.f;
+        const uint32_t hi = att_pack_bf16(f0, f1);
+        qa[ks][h] = hi;
+        qb[ks][h] = att_pack_bf16(f0 - __uint_as_float(hi << 16), f1 - __uint_as_float(hi & 0xFFFF0000u));
+      }
     }
     float o[NTL][4];
 #pragma unroll
@@ -339,7 +345,9 @@ __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, cons
 #pragma unroll
         for (int n = 0; n < 4; ++n) {
           const uint8_t* kp = slot + (8 * n + gq) * RS + (ks * 16 + 2 * tq) * 2;
-          att_mma_bf16(sacc[n], qa[ks][0], 0u, qa[ks][1], 0u, *(const uint32_t*)kp, *(const uint32_t*)(kp + 16));
+          const uint32_t b0 = *(const uint32_t*)kp, b1 = *(const uint32_t*)(kp + 16);
+          att_mma_bf16(sacc[n], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+          att_mma_bf16(sacc[n], qb[ks][0], 0u, qb[ks][1], 0u, b0, b1);
         }
       }
       // ---- online softmax of row gq (the 4 lanes of a group hold its 32 scores) ----

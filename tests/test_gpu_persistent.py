@@ -30,23 +30,32 @@ def test_persistent_step_matches_launch_per_op(cuda_device, monkeypatch, which, 
     monkeypatch.setenv("RLZ_PERSIST_OCC", str(occ))
     w = synthetic_weights(cfg, seed=5, std=0.06)
     prompt = [3, 17, 200, 45, 9, 310, 77, 5, 120, 64, 33, 18, 250, 7, 91, 402, 11, 60, 29, 8, 300]
-    outs, logits = [], []
+    # the same token sequence goes through both plans (the first plan's greedy choices), logits compared step by step:
+    # free-running continuations could part at a near-tie between two logits without either plan being wrong
+    forced, logits = None, []
     for persistent in (False, True):
         eng = DecodeEngine(w, EngineConfig(max_batch=1, max_seq_len=256, greedy_only=True, persistent_step=persistent))
-        toks = eng.generate(prompt, SamplingParams(max_tokens=40))
+        eng.open_slot(0, 128)
+        nxt = eng.prefill(0, prompt)
+        fed, rows = [], []
+        for i in range(40):
+            tok = nxt if forced is None else forced[i]
+            fed.append(tok)
+            nxt = int(eng.feed({0: tok})[0])
+            rows.append(eng.buf.logits[0, :cfg.vocab_size].float().cpu().numpy().copy())
         plan = eng.plan(1)
         assert (plan.program is not None) == persistent
         if persistent:
             assert plan.kernel_launches == 1
             plan.program.check()
-        outs.append(toks)
-        logits.append(eng.buf.logits[0, :cfg.vocab_size].float().cpu().numpy().copy())
+        forced = forced or fed
+        logits.append(rows)
         del eng
         torch.cuda.synchronize()
-    agree = sum(int(a == b) for a, b in zip(*outs))
-    assert agree >= 36, outs          # same kernels' code in both plans; only the attention split count differs
-    if agree == 40:
-        assert _cos(logits[0], logits[1]) > 0.999
+    worst = min(_cos(a, b) for a, b in zip(*logits))
+    assert worst > 0.998, worst          # same GEMV code in both plans; the attention kernels differ (scalar vs tensor-core mode)
+    agree = sum(int(a.argmax() == b.argmax()) for a, b in zip(*logits))
+    assert agree >= 34, agree
 
 
 def test_persistent_step_with_sampling_keeps_selection_kernel(cuda_device):
@@ -54,9 +63,16 @@ def test_persistent_step_with_sampling_keeps_selection_kernel(cuda_device):
     from realizar_b200.runtime.engine import DecodeEngine, EngineConfig, SamplingParams
     w = synthetic_weights(_phi2(), seed=2, std=0.06)
     eng = DecodeEngine(w, EngineConfig(max_batch=1, max_seq_len=128, persistent_step=True))
-    toks = eng.generate([1, 2, 3, 4, 5, 6, 7, 8], SamplingParams(max_tokens=8, temperature=0.0))
+    prompt = [1, 2, 3, 4, 5, 6, 7, 8]
+    toks = eng.generate(prompt, SamplingParams(max_tokens=8, temperature=0.0))
     plan = eng.plan(1)
     assert plan.program is not None and plan.kernel_launches == 2      # step kernel + sampling kernel
-    ref = DecodeEngine(w, EngineConfig(max_batch=1, max_seq_len=128, persistent_step=False)).generate(
-        [1, 2, 3, 4, 5, 6, 7, 8], SamplingParams(max_tokens=8, temperature=0.0))
-    assert sum(int(a == b) for a, b in zip(toks, ref)) >= 7
+    # every emitted token is an (almost) arg-max of the launch-per-operation plan's logits for the same prefix
+    ref = DecodeEngine(w, EngineConfig(max_batch=1, max_seq_len=128, persistent_step=False, greedy_only=True))
+    ref.open_slot(0, 64)
+    ref.prefill(0, prompt)
+    for i, t in enumerate(toks):
+        lg = ref.logits_of_last_step(0).float().cpu().numpy()[:ref.mcfg.vocab_size]
+        assert lg[t] >= lg.max() - 0.12, (i, t)
+        if i + 1 < len(toks):
+            ref.feed({0: int(t)})
