@@ -230,15 +230,16 @@ RLZ_HD void unit_q6k(const uint8_t* row, int u, const ActView& a, float* acc) {
   const U4 qh = ld_w16(base + 128 + n * 32 + 16 * lh);
   const U4 scv = ld_c16(base + 192);
   const U4 tail = ld_c16(base + 208);
-  const float d = h2f_alu(tail.x & 0xFFFFu);
+  float d, d_unused;
+  h2f_pair(tail.x, &d, &d_unused);
   const uint32_t scw0 = n ? scv.z : scv.x, scw1 = n ? scv.w : scv.y;   // 8 scales of this half
+  // scales lh, lh + 2, lh + 4, lh + 6 of the half: bytes lh and lh + 2 of each word (one shift per word, then fixed positions)
+  const uint32_t t0 = scw0 >> (8 * lh), t1 = scw1 >> (8 * lh);
   float sc[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int idx = lh + 2 * j;                       // 0..7
-    const uint32_t wv = idx < 4 ? scw0 : scw1;
-    sc[j] = d * i2f((int)(int8_t)((wv >> (8 * (idx & 3))) & 0xFFu));
-  }
+  sc[0] = d * i2f((int)(int8_t)(t0 & 0xFFu));
+  sc[1] = d * i2f((int)(int8_t)((t0 >> 16) & 0xFFu));
+  sc[2] = d * i2f((int)(int8_t)(t1 & 0xFFu));
+  sc[3] = d * i2f((int)(int8_t)((t1 >> 16) & 0xFFu));
   U4 w[4];
   w[0] = U4{(qa.x & 0x0F0F0F0Fu) | ((qh.x & 0x03030303u) << 4), (qa.y & 0x0F0F0F0Fu) | ((qh.y & 0x03030303u) << 4),
             (qa.z & 0x0F0F0F0Fu) | ((qh.z & 0x03030303u) << 4), (qa.w & 0x0F0F0F0Fu) | ((qh.w & 0x03030303u) << 4)};
