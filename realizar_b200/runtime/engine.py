@@ -99,8 +99,11 @@ class DecodeEngine:
         y1_w = (m.act_col0 + d_k + 256) if self.mcfg.parallel_residual else qkv_w
         z = lambda *s, dt=torch.float32: torch.zeros(*s, device=dev, dtype=dt)
         part, ctr = ops.attn_decode_scratch(B, m.heads, self.splits, hd, dev)
+        # tokens and positions are the two rows of one buffer (and of one pinned host buffer), so a step uploads both with one copy
+        tok_pos = torch.zeros(2, B, device=dev, dtype=torch.int32)
+        tok_pos[1].fill_(-1)
         self.buf = StepBuffers(
-            tokens=z(B, dt=torch.int32), positions=torch.full((B,), -1, device=dev, dtype=torch.int32),
+            tokens=tok_pos[0], positions=tok_pos[1],
             page_table=z(B, self.max_pages_per_seq, dt=torch.int32), x=z(B, self.mcfg.hidden_dim), y1=z(B, y1_w),
             attn_out=z(B, o_k), act=z(B, d_k + 256), partial_out=z(B, self.mcfg.hidden_dim) if tp_size > 1 else None,
             logits=z(B, m.vocab_local if tp_size > 1 else self.mcfg.vocab_size), sampled=z(B, dt=torch.int32),
@@ -119,8 +122,11 @@ class DecodeEngine:
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self._gen = torch.Generator(device=dev).manual_seed(c.seed)
         # pinned staging for the streaming loop
-        self._h_tokens = torch.zeros(B, dtype=torch.int32).pin_memory()
-        self._h_positions = torch.full((B,), -1, dtype=torch.int32).pin_memory()
+        self._h_tok_pos = torch.zeros(2, B, dtype=torch.int32).pin_memory()
+        self._h_tok_pos[1].fill_(-1)
+        self._h_tokens, self._h_positions = self._h_tok_pos[0], self._h_tok_pos[1]
+        self._d_tok_pos = tok_pos
+        self._np_tokens, self._np_positions = self._h_tokens.numpy(), self._h_positions.numpy()     # cheap scalar writes
         self._h_sampled = torch.zeros(B, dtype=torch.int32).pin_memory()
         self._h_table = torch.zeros(B, self.max_pages_per_seq, dtype=torch.int32).pin_memory()
         self._next_seq = 0
@@ -302,13 +308,12 @@ class DecodeEngine:
             s = self.slots[i]
             if i in slot_tokens and s.active:
                 self._ensure_pages(i, s.position + 1)
-                self._h_tokens[i] = slot_tokens[i]
-                self._h_positions[i] = s.position
+                self._np_tokens[i] = slot_tokens[i]
+                self._np_positions[i] = s.position
             else:
-                self._h_positions[i] = -1
+                self._np_positions[i] = -1
         b = self.buf
-        b.tokens[:hi].copy_(self._h_tokens[:hi], non_blocking=True)
-        b.positions[:hi].copy_(self._h_positions[:hi], non_blocking=True)
+        self._d_tok_pos.copy_(self._h_tok_pos, non_blocking=True)      # host state is authoritative in this loop: rows >= hi are idle (-1)
         if not self.cfg.greedy_only:
             b.uniform[:hi].copy_(torch.rand(hi, device=self.device, generator=self._gen))
         self.run_step(hi)
