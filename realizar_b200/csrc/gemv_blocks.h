@@ -27,18 +27,9 @@ RLZ_HD int blk_chunk_off(int nsb, int sb, int c) { return (c * nsb + sb) << 4; }
 
 #if defined(__CUDA_ARCH__)
 __device__ __forceinline__ U4 ld_s16(const uint8_t* p) { const uint4 t = *(const uint4*)p; U4 v{t.x, t.y, t.z, t.w}; return v; }
-// unsigned bytes of a times signed bytes of b
-__device__ __forceinline__ int dp4us(uint32_t a, uint32_t b, int c) {
-  int d; asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
-}
 #else
 inline U4 ld_s16(const uint8_t* p) { U4 v; memcpy(&v, p, 16); return v; }
-inline int dp4us(uint32_t a, uint32_t b, int c) {
-  for (int i = 0; i < 4; ++i) c += (int)(uint8_t)(a >> (8 * i)) * (int)(int8_t)(b >> (8 * i));
-  return c;
-}
 #endif
-RLZ_HD int dot16us(const U4& w, const U4& a) { return dp4us(w.w, a.w, dp4us(w.z, a.z, dp4us(w.y, a.y, dp4us(w.x, a.x, 0)))); }
 
 // all eight 6-bit scales / mins of a Q4_K / Q5_K block as packed bytes
 struct K4Scales { uint32_t sc_lo, sc_hi, m_lo, m_hi; };

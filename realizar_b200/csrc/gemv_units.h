@@ -75,6 +75,18 @@ inline float h2f(uint32_t bits) { return half_bits_to_float((uint16_t)bits); }
 #endif
 
 RLZ_HD int dot16(const U4& w, const U4& a) { return dp4(w.w, a.w, dp4(w.z, a.z, dp4(w.y, a.y, dp4(w.x, a.x, 0)))); }
+// unsigned bytes of a times signed bytes of b
+#if defined(__CUDA_ARCH__)
+__device__ __forceinline__ int dp4us(uint32_t a, uint32_t b, int c) {
+  int d; asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
+}
+#else
+inline int dp4us(uint32_t a, uint32_t b, int c) {
+  for (int i = 0; i < 4; ++i) c += (int)(uint8_t)(a >> (8 * i)) * (int)(int8_t)(b >> (8 * i));
+  return c;
+}
+#endif
+RLZ_HD int dot16us(const U4& w, const U4& a) { return dp4us(w.w, a.w, dp4us(w.z, a.z, dp4us(w.y, a.y, dp4us(w.x, a.x, 0)))); }
 
 // byte i (0..11) of the 12 packed scale bytes held in three words
 RLZ_HD uint32_t k4_byte(uint32_t y, uint32_t z, uint32_t w, int i) {
@@ -169,7 +181,10 @@ RLZ_HD void unit_q4k(const uint8_t* row, int u, const ActView& a, float* acc) {
   h2f_pair(hdr.x, &d, &dmin);
   int sc0, m0, sc1, m1;
   k4_scale_min_pair(hdr.y, hdr.z, hdr.w, g, &sc0, &m0, &sc1, &m1);
-  const U4 lo0 = RLZ_LO4(q0), hi0 = RLZ_HI4(q0), lo1 = RLZ_LO4(q1), hi1 = RLZ_HI4(q1);
+  // high nibbles stay where they are (value * 16, as unsigned bytes): their dot product is an exact multiple of 16
+  const U4 lo0 = RLZ_LO4(q0), lo1 = RLZ_LO4(q1);
+  const U4 hi0{q0.x & 0xF0F0F0F0u, q0.y & 0xF0F0F0F0u, q0.z & 0xF0F0F0F0u, q0.w & 0xF0F0F0F0u};
+  const U4 hi1{q1.x & 0xF0F0F0F0u, q1.y & 0xF0F0F0F0u, q1.z & 0xF0F0F0F0u, q1.w & 0xF0F0F0F0u};
   // the unit's four 16-byte activation chunks 4u .. 4u + 3 (act_chunk_off of each, with the shared parts computed once)
   const int ob = u << 6, rot = u >> 1;
   const int o0 = ob | ((rot & 3) << 4), o1 = ob | (((rot + 1) & 3) << 4), o2 = ob | (((rot + 2) & 3) << 4), o3 = ob | (((rot + 3) & 3) << 4);
@@ -178,7 +193,7 @@ RLZ_HD void unit_q4k(const uint8_t* row, int u, const ActView& a, float* acc) {
     const int8_t* xq = a.q + (int64_t)b * a.k;
     const U4 mm = *(const U4*)((const uint8_t*)(a.m + (int64_t)b * (a.k >> 6) + u));
     const int dlo = dot16(lo0, ld_a16(xq + o0)) + dot16(lo1, ld_a16(xq + o1));
-    const int dhi = dot16(hi0, ld_a16(xq + o2)) + dot16(hi1, ld_a16(xq + o3));
+    const int dhi = (dot16us(hi0, ld_a16(xq + o2)) + dot16us(hi1, ld_a16(xq + o3))) >> 4;
     const float t0 = d * i2f(sc0 * dlo) - dmin * i2f(m0 * (int)mm.z);
     const float t1 = d * i2f(sc1 * dhi) - dmin * i2f(m1 * (int)mm.w);
     acc[b] += as_f(mm.x) * t0 + as_f(mm.y) * t1;
