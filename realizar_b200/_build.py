@@ -23,7 +23,7 @@ CSRC = PKG / "csrc"
 LIB = PKG / "_lib"
 OBJ = PKG / "_lib" / "obj"
 
-CPU_SOURCES = ["quant_cpu.cpp", "cpu_engine.cpp", "gguf_native.cpp", "gemv_emu.cpp", "apr_native.cpp", "sched_native.cpp"]
+CPU_SOURCES = ["quant_cpu.cpp", "cpu_engine.cpp", "gguf_native.cpp", "gemv_emu.cpp", "apr_native.cpp"]
 NVCC_ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
               "-Xptxas", "-v", "-DNDEBUG"]

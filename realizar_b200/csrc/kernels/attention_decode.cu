@@ -49,12 +49,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_mma_kernel(const __gr
 template <int GT, int MERGE, int HD>
 static cudaError_t launch_attn_mma(const AttnDecodeParams& p, dim3 grid, dim3 block, dim3 cl, cudaStream_t st) {
   const size_t ring = (size_t)ATT_RING * 64 * (HD == 80 ? 2 * HD : 2 * HD + 16);       // row bytes as in the kernel
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<GT, MERGE, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  static SmemOptIn opt;
+  if (cudaError_t e = opt.ensure(attn_decode_mma_kernel<GT, MERGE, HD>, ring); e != cudaSuccess) return e;
   return launch_cluster(attn_decode_mma_kernel<GT, MERGE, HD>, grid, block, cl, ring, st, p);
 }
 template <int GT, int MERGE>
@@ -74,12 +70,8 @@ static cudaError_t launch_attn_mma_merge(const AttnDecodeParams& p, int merge, d
 // launch one instantiation; `ring` bytes of dynamic shared memory (0 unless streamed)
 template <int GT, int MERGE, int DEEP, int Q8>
 static cudaError_t launch_attn(const AttnDecodeParams& p, dim3 grid, dim3 block, dim3 cl, size_t ring, cudaStream_t st) {
-  static size_t configured = 0;
-  if (ring > configured && ring > 16 * 1024) {                // above the default limit once the static part is added: opt in
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<GT, MERGE, DEEP, Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
-    if (e != cudaSuccess) return e;
-    configured = ring;
-  }
+  static SmemOptIn opt;                                       // above the default limit once the static part is added: opt in
+  if (cudaError_t e = opt.ensure(attn_decode_kernel<GT, MERGE, DEEP, Q8>, ring, 16 * 1024); e != cudaSuccess) return e;
   return launch_cluster(attn_decode_kernel<GT, MERGE, DEEP, Q8>, grid, block, cl, ring, st, p);
 }
 

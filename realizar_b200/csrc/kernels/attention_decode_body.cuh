@@ -41,7 +41,7 @@ struct AttnDecodeParams {
   int32_t rope_table_len;              // positions covered by rope_table
   const float2* rope_table;            // [rope_table_len, rope_dim / 2] (cos, sin) or null
   int32_t kv_q8;                       // 1: int8 cache rows of head_dim + 16 bytes (codes, then the fp32 scale of the row)
-  int32_t _pad3;
+  int32_t num_pages;                   // pages in the cache (0: unknown, page ids are not checked)
 };
 
 // ---- int8 KV rows: [head_dim codes][fp32 scale][12 bytes padding]; value = code * scale, scale = max|x| / 127 per (token, kv head) ----
@@ -76,7 +76,14 @@ __device__ __forceinline__ void rope_inplace(float* v, int d_rot, int rope_type,
   }
 }
 
-static __device__ int g_attn_decode_error = 0;      // 3201: a streamed K/V stage never arrived (bounded wait ran out)
+// 3201: a streamed K/V stage never arrived (bounded wait ran out); 3301: a position beyond the page-table row (the sequence
+// is skipped); 3302: a page id outside the cache (read as page 0, the append is skipped)
+static __device__ int g_attn_decode_error = 0;
+// page id from the table, checked against the cache size when the launcher knows it
+__device__ __forceinline__ int att_page(const AttnDecodeParams& p, int raw) {
+  if (p.num_pages > 0 && (unsigned)raw >= (unsigned)p.num_pages) { atomicExch(&g_attn_decode_error, 3302); return 0; }
+  return raw;
+}
 
 __device__ __forceinline__ uint32_t att_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ bool att_try_wait(unsigned long long* bar, uint32_t parity) {
@@ -148,6 +155,10 @@ __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, cons
 
   const int pos = p.positions[b];
   if (pos < 0) return;                                   // uniform over the cluster (same sequence)
+  if (p.max_pages > 0 && pos / ATT_PAGE >= p.max_pages) {  // the position has run past the sequence's page-table row: touch nothing
+    if (tid == 0) atomicExch(&g_attn_decode_error, 3301);
+    return;
+  }
   if (PUSH) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");     // phase 1: "I have started"; waited on before the push
   const int seq_len = pos + 1;
   const int lo = p.window > 0 ? max(0, seq_len - p.window) : 0;      // first position attended to
@@ -161,7 +172,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, cons
   const int32_t* pt = p.page_table + (int64_t)b * p.pt_stride;
   const int npages = (max(0, end - start) + ATT_PAGE - 1) / ATT_PAGE;
   const bool pt_staged = npages <= ATT_PT_MAX;
-  if (pt_staged && tid < npages) pt_s[tid] = pt[start / ATT_PAGE + tid];
+  if (pt_staged && tid < npages) pt_s[tid] = att_page(p, pt[start / ATT_PAGE + tid]);
   const float* row = p.qkv + (int64_t)b * p.ld_qkv;
   for (int i = tid; i < gn * d; i += ATT_THREADS) {
     const int g = i / d, j = i - g * d;
@@ -209,9 +220,14 @@ __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, cons
     }
   }
   if (owner && hg == 0) {   // append the new row to the cache (one head group does it)
-    const int page = pt[pos / ATT_PAGE], slot = pos % ATT_PAGE;
+    const int raw_page = pt[pos / ATT_PAGE], slot = pos % ATT_PAGE;
+    const bool page_ok = p.num_pages <= 0 || (unsigned)raw_page < (unsigned)p.num_pages;
+    if (!page_ok && tid == 0) atomicExch(&g_attn_decode_error, 3302);
+    const int page = page_ok ? raw_page : 0;
     const int64_t rowi = ((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE + slot;
-    if (q8) {
+    if (!page_ok) {
+      // a page id outside the cache: nothing is written
+    } else if (q8) {
       int8_t* kd = (int8_t*)p.k_cache + rowi * rowb;
       int8_t* vd = (int8_t*)p.v_cache + rowi * rowb;
       for (int j = tid; j < d; j += ATT_THREADS) {
@@ -275,7 +291,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, cons
         __syncwarp();
         if (lane < 4 && (lane & 1) < np) {
           const int tok = tok0 + (lane & 1) * ATT_PAGE;
-          const int page = pt_staged ? pt_s[(tok - start) / ATT_PAGE] : pt[tok / ATT_PAGE];
+          const int page = pt_staged ? pt_s[(tok - start) / ATT_PAGE] : att_page(p, pt[tok / ATT_PAGE]);
           const int64_t boff = ((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE * RS;
           const uint8_t* src = (lane & 2 ? (const uint8_t*)p.v_cache : (const uint8_t*)p.k_cache) + boff;
           att_bulk_g2s(slot + ((lane & 2 ? 32 : 0) + (lane & 1) * ATT_PAGE) * RS, src, ATT_PAGE * RS, fb);
@@ -286,7 +302,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, cons
       __syncwarp();
       if (lane < nvalid) {
         const int tok = tok0 + lane;
-        const int page = pt_staged ? pt_s[(tok - start) / ATT_PAGE] : pt[tok / ATT_PAGE];
+        const int page = pt_staged ? pt_s[(tok - start) / ATT_PAGE] : att_page(p, pt[tok / ATT_PAGE]);
         const int64_t rowi = ((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE + (tok % ATT_PAGE);
         att_bulk_g2s(slot + lane * RS, (const uint8_t*)p.k_cache + rowi * (2 * HD), 2 * HD, fb);
         att_bulk_g2s(slot + (32 + lane) * RS, (const uint8_t*)p.v_cache + rowi * (2 * HD), 2 * HD, fb);
@@ -419,7 +435,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, cons
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(att_smem_u32(&sm.full[slot])), "r"(2u * np * page_bytes) : "memory");
     for (int pi = 0; pi < np; ++pi) {
       const int tk = tok0 + pi * ATT_PAGE;
-      const int page = pt_staged ? pt_s[(tk - start) / ATT_PAGE] : pt[tk / ATT_PAGE];
+      const int page = pt_staged ? pt_s[(tk - start) / ATT_PAGE] : att_page(p, pt[tk / ATT_PAGE]);
       const int64_t boff = ((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE * rowb;
       uint8_t* dst = ring + (size_t)slot * stage_bytes + (size_t)pi * page_bytes;
       att_bulk_g2s(dst, (const uint8_t*)p.k_cache + boff, page_bytes, &sm.full[slot]);
@@ -469,7 +485,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, cons
       const int tok = base + t;
       const bool okl = lane_ok && tok < end && !(new_from_smem && tok == pos);
       const int tk = min(tok, end - 1 > start ? end - 1 : start);
-      const int page = pt_staged ? pt_s[(tk - start) / ATT_PAGE] : pt[tk / ATT_PAGE];
+      const int page = pt_staged ? pt_s[(tk - start) / ATT_PAGE] : att_page(p, pt[tk / ATT_PAGE]);
       const int64_t rowi = ((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE + (tk % ATT_PAGE);
       if (q8) {                                           // 8 codes (x, y) and the row scale (z)
         const uint8_t* kp = (const uint8_t*)p.k_cache + rowi * rowb;

@@ -273,12 +273,8 @@ template <int D>
 int launch_prefill(const AttnPrefillParams& p, cudaStream_t st) {
   constexpr int NSLAB = (D + 63) / 64;
   const size_t smem = (size_t)(NSLAB + 4) * FP_SLAB + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static SmemOptIn opt;
+  if (cudaError_t e = opt.ensure(attn_prefill_tcgen05_kernel<D>, smem, 0); e != cudaSuccess) return (int)e;
   dim3 grid((p.n_tokens + 127) / 128, p.n_heads);
   return (int)launch(attn_prefill_tcgen05_kernel<D>, grid, dim3(FP_THREADS), smem, st, p);
 }
@@ -479,12 +475,8 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(const __grid_cons
 template <int HD>
 int launch_prefill_mma(const AttnPrefillParams& p, cudaStream_t st) {
   const size_t ring = (size_t)PM_WARPS * 64 * (HD == 80 ? 2 * HD : 2 * HD + 16);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static SmemOptIn opt;
+  if (cudaError_t e = opt.ensure(attn_prefill_mma_kernel<HD>, ring, 0); e != cudaSuccess) return (int)e;
   dim3 grid((p.n_tokens + PM_ROWS - 1) / PM_ROWS, p.n_heads);
   return (int)launch(attn_prefill_mma_kernel<HD>, grid, dim3(128), ring, st, p);
 }

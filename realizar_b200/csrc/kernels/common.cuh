@@ -48,6 +48,25 @@ inline cudaError_t launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// Dynamic shared memory above the default limit has to be opted into per kernel AND per device (the attribute belongs to
+// the function on one device).  One instance per kernel instantiation remembers what each device has been set to; a
+// repeated call from another thread at worst sets the same attribute twice.
+struct SmemOptIn {
+  size_t bytes[64] = {};
+  template <typename K>
+  cudaError_t ensure(K kernel, size_t smem, size_t default_limit = 48 * 1024) {
+    if (smem <= default_limit) return cudaSuccess;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const int slot = dev & 63;
+    if (smem <= bytes[slot]) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) bytes[slot] = smem;
+    return e;
+  }
+};
+
 #if defined(__CUDACC__)
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }

@@ -241,12 +241,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, OCC) decode_step_kernel(const __
 
 template <int OCC, int GT>
 static cudaError_t launch_step(const StepProgram& prog, int sms, size_t smem, cudaStream_t st) {
-  static size_t configured = 48 * 1024;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_step_kernel<OCC, GT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    configured = smem;
-  }
+  static SmemOptIn opt;
+  if (cudaError_t e = opt.ensure(decode_step_kernel<OCC, GT>, smem); e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(OCC * sms); cfg.blockDim = dim3(GEMV_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute attr[1];

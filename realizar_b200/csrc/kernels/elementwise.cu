@@ -257,11 +257,16 @@ __global__ void swiglu_bf16_kernel(const float* gate, const float* up, __nv_bflo
 }
 
 // Feed sampled tokens back as the next step's inputs and advance positions of active slots.
-__global__ void advance_kernel(int32_t* tokens, const int32_t* sampled, int32_t* positions, int batch) {
+// limit > 0: a sequence whose next position would reach `limit` goes idle (-1) instead of running past its reserved pages
+__global__ void advance_kernel(int32_t* tokens, const int32_t* sampled, int32_t* positions, int batch, int limit) {
   pdl_launch_dependents();
   pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
-  if (b < batch && positions[b] >= 0) { tokens[b] = sampled[b]; positions[b] += 1; }
+  if (b < batch && positions[b] >= 0) {
+    tokens[b] = sampled[b];
+    const int next = positions[b] + 1;
+    positions[b] = (limit > 0 && next >= limit) ? -1 : next;
+  }
 }
 
 }  // namespace rlz
@@ -288,8 +293,8 @@ int rlz_swiglu_bf16(const float* gate, const float* up, void* y, long long rows,
                      (int64_t)rows, cols, (int64_t)ld_g, (int64_t)ld_u, (int64_t)ld_y, act);
 }
 
-int rlz_advance(int32_t* tokens, const int32_t* sampled, int32_t* positions, int batch, void* stream) {
-  return (int)launch(advance_kernel, dim3((batch + 63) / 64), dim3(64), 0, (cudaStream_t)stream, tokens, sampled, positions, batch);
+int rlz_advance(int32_t* tokens, const int32_t* sampled, int32_t* positions, int batch, int limit, void* stream) {
+  return (int)launch(advance_kernel, dim3((batch + 63) / 64), dim3(64), 0, (cudaStream_t)stream, tokens, sampled, positions, batch, limit);
 }
 
 int rlz_embed(const void* table, int qtype, long long row_bytes, int hidden, int vocab, const int32_t* tokens, int n_tokens,

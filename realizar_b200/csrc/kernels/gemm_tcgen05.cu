@@ -493,12 +493,8 @@ template <int NT, int QT, int RT>
 int launch_gemm_q(const GemmParams& p, cudaStream_t st) {
   using Cfg = GemmCfg<NT, QT, RT>;
   const size_t smem = Cfg::SMEM;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kquant_tcgen05_kernel<NT, QT, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static SmemOptIn opt;
+  if (cudaError_t e = opt.ensure(gemm_kquant_tcgen05_kernel<NT, QT, RT>, smem, 0); e != cudaSuccess) return (int)e;
   alignas(64) CUtensorMap xmap, wmap;
   int rc = make_x_map(&xmap, p, NT);
   if (rc) return rc;

@@ -27,12 +27,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, (FAST && B <= GEMV_OCC2_MAXB ? 2
 template <int B, bool FAST>
 cudaError_t launch_gemv_t(const GemvParams& p, int grid, cudaStream_t stream) {
   const size_t smem = gemv_smem_bytes(p);
-  static size_t configured = 48 * 1024;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<B, FAST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    configured = smem;
-  }
+  static SmemOptIn opt;
+  if (cudaError_t e = opt.ensure(gemv_kernel<B, FAST>, smem); e != cudaSuccess) return e;
   return launch(gemv_kernel<B, FAST>, dim3(grid), dim3(GEMV_THREADS), smem, stream, p);
 }
 template <int B>

@@ -242,12 +242,8 @@ size_t gs_fixed_smem(const GemvParams& p) {               // everything behind t
 template <int B>
 cudaError_t launch_gs(const GemvParams& p, int grid, int nstage, int stage_bytes, cudaStream_t stream) {
   const size_t smem = (size_t)nstage * stage_bytes + gs_fixed_smem(p);
-  static size_t configured = 0;            // dynamic shared memory this instantiation has been opted into
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    configured = smem;
-  }
+  static SmemOptIn opt;
+  if (cudaError_t e = opt.ensure(gemv_stream_kernel<B>, smem, 0); e != cudaSuccess) return e;
   return launch(gemv_stream_kernel<B>, dim3(grid), dim3(GS_THREADS), smem, stream, p, nstage, stage_bytes);
 }
 

@@ -120,14 +120,32 @@ class MatOut:
 
 
 def plan_rows_per_cta(mats: Sequence[MatOut], target_ctas: int) -> List[int]:
-    total = sum(sum(w.nbytes for w, _ in m.segs) for m in mats) or 1
+    """Rows per CTA of every matrix of a launch: the smallest per-CTA byte budget for which the launch needs at most
+    ``target_ctas`` CTAs (one wave), so that every CTA streams about the same number of weight bytes.  Matrices that
+    also write their outputs as an int8 block hand out rows in multiples of 32 (one quantisation block per warp)."""
+    n = [m.segs[0][0].n for m in mats]
+    rowb = [max(1.0, sum(w.nbytes for w, _ in m.segs) / max(1, ni)) for m, ni in zip(mats, n)]
+    gran = [32 if m.q_out is not None else 1 for m in mats]
+
+    def rows_for(budget: float, i: int) -> int:
+        return min(1024, max(gran[i], int(budget / rowb[i]) // gran[i] * gran[i]))
+
+    def ctas_for(budget: float) -> int:
+        return sum(-(-n[i] // rows_for(budget, i)) for i in range(len(mats)))
+
+    lo, hi = 1.0, max(rb * ni for rb, ni in zip(rowb, n)) + 1.0
+    if ctas_for(hi) > target_ctas:                     # more matrices than CTAs, or rows capped at 1024: one CTA each at least
+        return [rows_for(hi, i) for i in range(len(mats))]
+    for _ in range(48):
+        mid = 0.5 * (lo + hi)
+        if ctas_for(mid) <= target_ctas:
+            hi = mid
+        else:
+            lo = mid
     out = []
-    for m in mats:
-        n = m.segs[0][0].n
-        share = sum(w.nbytes for w, _ in m.segs) / total
-        ctas = max(1, round(target_ctas * share))
-        rpc = max(1, -(-n // ctas))
-        out.append(min(rpc, 1024))
+    for i in range(len(mats)):
+        ctas = -(-n[i] // rows_for(hi, i))
+        out.append(min(1024, max(gran[i], -(-(-(-n[i] // ctas)) // gran[i]) * gran[i])))    # same CTA count, rows evened out
     return out
 
 
@@ -163,7 +181,7 @@ def build_gemv_params(xs: Sequence[VecIn], mats: Sequence[MatOut], y: torch.Tens
         if m.q_out is not None:
             if batch != 1:
                 raise ValueError("quantised output is a batch-1 feature")
-            M.rows_per_cta = -(-M.rows_per_cta // 32) * 32        # a warp of the epilogue owns one 32-value quantisation block
+            M.rows_per_cta = -(-M.rows_per_cta // 32) * 32        # a warp of the epilogue owns one 32-value quantisation block (explicit rows_per_cta)
             M.q_out, M.q_out_k, M.q_out_col0 = m.q_out.data_ptr(), m.q_out_k, m.q_out_col0
     p.nmat, p.batch = len(mats), batch
     p.y, p.ldy = y.data_ptr(), ldy if ldy is not None else (y.stride(0) if y.dim() > 1 else y.numel())
@@ -174,8 +192,24 @@ def build_gemv_params(xs: Sequence[VecIn], mats: Sequence[MatOut], y: torch.Tens
     return p
 
 
+def slab_eligible(p: S.GemvParams) -> bool:
+    """True when the launch can run on the copy-engine-fed GEMV (``csrc/kernels/gemv_slab.cu``): K-quant rows with
+    k % 256 == 0 whose activations plus one pass per warp fit half an SM's shared memory.  ``RLZ_GEMV_SLAB=0`` keeps
+    every launch on the register-path kernel (kernel comparisons)."""
+    if os.environ.get("RLZ_GEMV_SLAB", "1") == "0":
+        return False
+    return int(lib().rlz_gemv_slab_check(ctypes.byref(p))) == 0
+
+
 def gemv_launch(p: S.GemvParams) -> None:
-    check(lib().rlz_gemv(ctypes.byref(p), stream_ptr()), "gemv")
+    """Launch a prepared GEMV description on the kernel that takes it (decided once per description)."""
+    slab = getattr(p, "_slab", None)
+    if slab is None:
+        slab = p._slab = slab_eligible(p)
+    if slab:
+        check(lib().rlz_gemv_slab(ctypes.byref(p), stream_ptr()), "gemv_slab")
+    else:
+        check(lib().rlz_gemv(ctypes.byref(p), stream_ptr()), "gemv")
 
 
 STREAM_TYPES = (int(QType.Q4_K), int(QType.Q5_K), int(QType.Q6_K))
@@ -198,8 +232,9 @@ def gemv_stream_launch(p: S.GemvParams) -> None:
 
 def device_error(clear: bool = True) -> int:
     """Error code recorded by a kernel whose bounded wait expired (0 = none)."""
-    return (int(lib().rlz_device_error(1 if clear else 0)) or int(lib().rlz_gemm_error(1 if clear else 0))
-            or int(lib().rlz_attn_decode_error(1 if clear else 0)))
+    c = 1 if clear else 0
+    return (int(lib().rlz_device_error(c)) or int(lib().rlz_gemv_slab_error(c)) or int(lib().rlz_gemm_error(c))
+            or int(lib().rlz_attn_decode_error(c)) or int(lib().rlz_attn_prefill_error(c)))
 
 
 def gemv(w: DeviceWeight, x: torch.Tensor, bias=None, act=ACT_NONE, residual=None, norm=NORM_NONE, norm_w=None, norm_b=None,
@@ -242,6 +277,7 @@ def build_attn_decode_params(qkv, out, k_cache, v_cache, positions, page_table, 
     p.no_append = 1 if no_append else 0
     p.window = int(window or 0)
     p.kv_q8 = 1 if k_cache.dtype in (torch.uint8, torch.int8) else 0
+    p.num_pages = int(k_cache.shape[0]) if k_cache.dim() >= 4 else 0      # [pages, kv_heads, page, row]: page ids are checked on the device
     if rope_table is not None:
         if rope_table.dtype != torch.float32 or rope_table.dim() != 3 or rope_table.shape[1] != rope_dim // 2 or rope_table.shape[2] != 2 or not rope_table.is_contiguous():
             raise ValueError("rope_table must be a contiguous float32 [positions, rope_dim / 2, 2] (cos, sin) tensor")
@@ -373,8 +409,11 @@ def page_rows(page_table: torch.Tensor, positions: torch.Tensor, out: torch.Tens
     check(lib().rlz_page_rows(page_table.data_ptr(), page_table.stride(0), positions.data_ptr(), out.data_ptr(), n, page, stream_ptr()), "page_rows")
 
 
-def advance_(tokens: torch.Tensor, sampled: torch.Tensor, positions: torch.Tensor) -> None:
-    check(lib().rlz_advance(tokens.data_ptr(), sampled.data_ptr(), positions.data_ptr(), tokens.numel(), stream_ptr()), "advance")
+def advance_(tokens: torch.Tensor, sampled: torch.Tensor, positions: torch.Tensor, limit: int = 0) -> None:
+    """Device-side feedback: sampled ids become the next inputs and positions move on.  With ``limit`` > 0 a sequence
+    whose next position would reach ``limit`` (the length its KV pages were reserved for) goes idle (position -1)
+    instead of running past its page table."""
+    check(lib().rlz_advance(tokens.data_ptr(), sampled.data_ptr(), positions.data_ptr(), tokens.numel(), int(limit), stream_ptr()), "advance")
 
 
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, out_val: Optional[torch.Tensor] = None, index_offset: int = 0,

@@ -54,7 +54,7 @@ class AttnDecodeParams(Structure):
                 ("head_dim", c_int32), ("max_pages", c_int32), ("rope_dim", c_int32), ("rope_type", c_int32), ("splits", c_int32),
                 ("batch", c_int32), ("q_off", c_int32), ("k_off", c_int32), ("v_off", c_int32), ("pt_stride", c_int32),
                 ("rope_theta", c_float), ("eps", c_float), ("scale", c_float), ("no_append", c_int32), ("window", c_int32),
-                ("rope_table_len", c_int32), ("rope_table", c_void_p), ("kv_q8", c_int32), ("_pad3", c_int32)]
+                ("rope_table_len", c_int32), ("rope_table", c_void_p), ("kv_q8", c_int32), ("num_pages", c_int32)]
 
 
 class AttnPrefillParams(Structure):
@@ -104,6 +104,11 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_cuda_error_string.restype = ctypes.c_char_p
     lib.rlz_gemv.argtypes = [POINTER(GemvParams), c_void_p]
     lib.rlz_gemv_stream.argtypes = [POINTER(GemvParams), c_void_p]
+    lib.rlz_gemv_slab.argtypes = [POINTER(GemvParams), c_void_p]
+    lib.rlz_gemv_slab_check.argtypes = [POINTER(GemvParams)]
+    lib.rlz_gemv_slab_error.argtypes = [c_int]
+    lib.rlz_gemv_slab_trace_enable.argtypes = [c_int]
+    lib.rlz_gemv_slab_trace_read.argtypes = [c_void_p, c_int, c_int]
     lib.rlz_gemv_trace_enable.argtypes = [c_int]
     lib.rlz_gemv_trace_read.argtypes = [c_void_p, c_int, c_int]
     lib.rlz_gemv_prepare.argtypes = [POINTER(GemvParams), POINTER(c_int)]
@@ -143,7 +148,7 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_attn_prefill_supported.argtypes = [c_int]
     lib.rlz_attn_prefill_error.argtypes = [c_int]
     lib.rlz_ll_reduce.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p]
-    lib.rlz_advance.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+    lib.rlz_advance.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
     lib.rlz_page_rows.argtypes = [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_void_p]
     lib.rlz_argmax.argtypes = [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
     lib.rlz_sample.argtypes = [POINTER(SampleParams), c_void_p]

@@ -133,6 +133,7 @@ class DecodeEngine:
         self.pdl = c.pdl
         ops.set_pdl(self.pdl)
         self.steps_run = 0
+        self.health_check_every = 256
         self.gemm_ok = gemm_capable(self.model)
         self._batched: Optional[BatchedForward] = None
         self._head_plans: Dict[int, DecodePlan] = {}
@@ -250,10 +251,23 @@ class DecodeEngine:
         else:
             self.plan(bucket).run()
         self.steps_run += 1
+        if self.steps_run % self.health_check_every == 0:
+            self.check_health()
+
+    def check_health(self) -> None:
+        """Read the status words that kernels set when a bounded wait runs out (a peer that never answered, a copy that never
+        landed, a position past its page table) and raise, so that the caller stops using results computed from missing
+        data.  Called every ``health_check_every`` steps and after every prompt pass; it synchronises the device."""
+        code = ops.device_error(clear=True)
+        if not code and self.comm is not None and hasattr(self.comm, "check_status"):
+            code = self.comm.check_status()
+        if code:
+            raise ops.KernelError(f"a device-side check failed with status {code}: a bounded wait expired or an index left its range; "
+                                  "results since the last check are not valid")
 
     def advance(self, batch: int) -> None:
         """Device-side feedback: sampled tokens become the next inputs, positions move on."""
-        ops.advance_(self.buf.tokens[:batch], self.buf.sampled[:batch], self.buf.positions[:batch])
+        ops.advance_(self.buf.tokens[:batch], self.buf.sampled[:batch], self.buf.positions[:batch], limit=self.cfg.max_seq_len)
 
     # -- slots ---------------------------------------------------------------------------------
     def free_slots(self) -> List[int]:
@@ -415,6 +429,7 @@ class DecodeEngine:
         self._head(slot).run()
         self._h_sampled[slot: slot + 1].copy_(self.buf.sampled[slot: slot + 1], non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        self.check_health()
         s.position = pos0 + n
         return int(self._h_sampled[slot])
 
@@ -444,8 +459,13 @@ class DecodeEngine:
         x = bf.forward(n, self.buf.page_table[slot], shared_table=True, pos0=pos0)
         out: List[int] = []
         B = self.cfg.max_batch
+        fused = self.comm is not None and getattr(self.comm, "fused", False)
         for c0 in range(0, n, B):
             cb = min(B, n - c0)
+            if fused and c0 > 0:
+                # the peer stores of the candidate exchange are tagged with the epoch alone: a second exchange needs a new
+                # one, or a rank could read the previous chunk's pairs (same tag) before its peers have stored the new ones
+                self.comm.begin_step()
             self.buf.x[:cb].copy_(x[c0:c0 + cb])
             key = ("verify", cb)
             if key not in self._head_plans:

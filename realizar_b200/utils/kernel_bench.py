@@ -110,28 +110,29 @@ def bench_gemv(a):
     ms = time_cuda(run, a.iters)
     byts = w.nbytes + x.numel() * 4 + y.numel() * 4
     pk = peaks()
-    res = {"kernel": "gemv_stream" if use_stream else "gemv", "qtype": a.qtype, "n": a.n, "k": a.k, "batch": a.batch, "ms": ms, "bytes": byts,
+    res = {"kernel": "gemv_stream" if use_stream else "gemv_slab" if ops.slab_eligible(ps[0]) else "gemv", "qtype": a.qtype, "n": a.n, "k": a.k, "batch": a.batch, "ms": ms, "bytes": byts,
            "gbs": byts / ms / 1e6, "frac_of_%s_hbm" % pk["source"]: byts / ms / 1e6 / pk["hbm_gbs"],
            "l2_note": "weights %.0f MB x %d %s L2" % (w.nbytes / 1e6, len(ws), ">" if w.nbytes * len(ws) > 126e6 else "<=")}
     if a.trace and not use_stream:
-        res["phase_trace_us"] = gemv_phase_trace(lambda: time_cuda(run, 2, warmup=0))
+        res["phase_trace_us"] = gemv_phase_trace(lambda: time_cuda(run, 2, warmup=0), slab=ops.slab_eligible(ps[0]))
     return res
 
 
-def gemv_phase_trace(run) -> dict:
+def gemv_phase_trace(run, slab: bool = False) -> dict:
     """Phase times of the last GEMV launch of ``run`` (medians over CTAs, microseconds)."""
     import ctypes
     from .. import ops
     lib = ops.lib()
+    enable, read = (lib.rlz_gemv_slab_trace_enable, lib.rlz_gemv_slab_trace_read) if slab else (lib.rlz_gemv_trace_enable, lib.rlz_gemv_trace_read)
     n = 512
     buf = (ctypes.c_ulonglong * (n * 8))()
-    ops.check(lib.rlz_gemv_trace_read(buf, n, 1), "gemv_trace_read")       # clear
-    ops.check(lib.rlz_gemv_trace_enable(1), "gemv_trace_enable")
+    ops.check(read(buf, n, 1), "gemv_trace_read")       # clear
+    ops.check(enable(1), "gemv_trace_enable")
     torch.cuda.synchronize()
     run()
     torch.cuda.synchronize()
-    ops.check(lib.rlz_gemv_trace_enable(0), "gemv_trace_enable")
-    ops.check(lib.rlz_gemv_trace_read(buf, n, 0), "gemv_trace_read")
+    ops.check(enable(0), "gemv_trace_enable")
+    ops.check(read(buf, n, 0), "gemv_trace_read")
     t = np.frombuffer(buf, dtype=np.uint64).reshape(n, 8).astype(np.float64)
     t = t[t[:, 0] > 0]
     if not len(t):

@@ -131,6 +131,84 @@ def test_gemv_multi_matrix_launch(cuda_device):
     assert _rel(y, ref) < 0.02
 
 
+def _launch_on(p, slab):
+    from realizar_b200 import ops
+    p._slab = slab
+    ops.gemv_launch(p)
+
+
+@pytest.mark.parametrize("qt", [QType.Q4_K, QType.Q5_K, QType.Q6_K])
+@pytest.mark.parametrize("batch", [1, 2, 4])
+@pytest.mark.parametrize("n,k,ctas", [(3000, 2048, 296), (61, 2560, 1), (700, 10240, 148), (9, 256, 1)])
+def test_gemv_slab_kernel_matches_register_kernel(cuda_device, qt, batch, n, k, ctas):
+    """The copy-engine-fed kernel against the register-path kernel and an fp32 reference (fused norm, bias, act, residual)."""
+    from realizar_b200 import ops
+    from realizar_b200.ops import MatOut, VecIn
+    w, wd = _weight(n, k, qt, seed=21 + n)
+    x = torch.randn(batch, k, device="cuda") * 2 + 0.3
+    g, gb = torch.rand(k, device="cuda") + 0.5, torch.randn(k, device="cuda") * 0.1
+    bias, res = torch.randn(n, device="cuda") * 0.1, torch.randn(batch, n, device="cuda")
+    outs = []
+    for slab in (True, False):
+        y = torch.zeros(batch, n, device="cuda")
+        p = ops.build_gemv_params([VecIn(x, k, norm=ops.NORM_LAYER, norm_w=g, norm_b=gb, eps=1e-5)], [MatOut([(w, 0)], bias=bias, act=ops.ACT_SILU, residual=True)],
+                                  y, batch, residual=res, target_ctas=ctas)
+        if slab and not ops.slab_eligible(p):
+            assert batch * k > 16384           # only activations too large for half an SM's shared memory are turned away
+            return
+        _launch_on(p, slab)
+        outs.append(y)
+    h = torch.nn.functional.layer_norm(x.cpu(), (k,), g.cpu(), gb.cpu(), 1e-5)
+    ref = torch.nn.functional.silu(h @ wd.T + bias.cpu()) + res.cpu()
+    assert _rel(outs[0], ref) < 0.02 and _rel(outs[1], ref) < 0.02 and _rel(outs[0], outs[1]) < 5e-3
+    assert ops.device_error() == 0
+
+
+def test_gemv_slab_two_segments_multi_matrix_and_handoff(cuda_device):
+    """Two accumulated segments with different inputs and block types, a four-matrix launch, and the int8 hand-off:
+    the producer's quantised output block is consumed by the next launch without re-quantising."""
+    from realizar_b200 import ops
+    from realizar_b200.ops import MatOut, VecIn
+    n, k, k2 = 2560, 2560, 10240
+    wo, wod = _weight(n, k, QType.Q4_K, 1)
+    wdn, wdd = _weight(n, k2, QType.Q6_K, 2)
+    x, x2 = torch.randn(1, k, device="cuda"), torch.randn(1, k2, device="cuda")
+    b1, b2, res = torch.randn(n, device="cuda"), torch.randn(n, device="cuda"), torch.randn(1, n, device="cuda")
+    y = torch.empty(1, n, device="cuda")
+    p = ops.build_gemv_params([VecIn(x, k), VecIn(x2, k2)], [MatOut([(wo, 0), (wdn, 1)], bias=b1, bias2=b2, residual=True)], y, 1, residual=res,
+                              target_ctas=296)
+    assert ops.slab_eligible(p)
+    _launch_on(p, True)
+    ref = x.cpu() @ wod.T + x2.cpu() @ wdd.T + b1.cpu() + b2.cpu() + res.cpu()
+    assert _rel(y, ref) < 0.02
+    # producer (register or slab kernel) writes gelu(W x) both as fp32 and as the int8 block; the consumer stages the block
+    wu, wud = _weight(k2, k, QType.Q4_K, 3)
+    for producer_slab in (True, False):
+        act = torch.zeros(1, k2, device="cuda")
+        act_q = torch.zeros(ops.act_block_bytes(k2), device="cuda", dtype=torch.uint8)
+        up = MatOut([(wu, 0)], act=ops.ACT_GELU)
+        up.q_out, up.q_out_k, up.q_out_col0 = act_q, k2, 0
+        _launch_on(ops.build_gemv_params([VecIn(x, k)], [up], act, 1, target_ctas=296), producer_slab)
+        y_pre, y_f32 = torch.empty(1, n, device="cuda"), torch.empty(1, n, device="cuda")
+        _launch_on(ops.build_gemv_params([VecIn(act, k2, pre=act_q)], [MatOut([(wdn, 0)])], y_pre, 1, target_ctas=296), True)
+        _launch_on(ops.build_gemv_params([VecIn(act, k2)], [MatOut([(wdn, 0)])], y_f32, 1, target_ctas=296), True)
+        ref = torch.nn.functional.gelu(x.cpu() @ wud.T, approximate="tanh") @ wdd.T
+        assert _rel(y_pre, ref) < 0.03 and _rel(y_pre, y_f32) < 1e-5
+    # four matrices of three block types sharing one input
+    ws = [_weight(nn, k, qt, 10 + i) for i, (nn, qt) in enumerate([(2560, QType.Q4_K), (640, QType.Q4_K), (640, QType.Q6_K), (3000, QType.Q5_K)])]
+    total = sum(w.n for w, _ in ws)
+    ym = torch.zeros(1, total, device="cuda")
+    mats, off = [], 0
+    for w, _ in ws:
+        mats.append(MatOut([(w, 0)], out_off=off))
+        off += w.n
+    p = ops.build_gemv_params([VecIn(x, k)], mats, ym, 1, target_ctas=296)
+    assert ops.slab_eligible(p)
+    _launch_on(p, True)
+    assert _rel(ym, torch.cat([x.cpu() @ wd.T for _, wd in ws], dim=-1)) < 0.02
+    assert ops.device_error() == 0
+
+
 def _ref_attention(q, kc, vc, scale):
     # q [H, d]; kc/vc [T, Hkv, d]
     H, d = q.shape

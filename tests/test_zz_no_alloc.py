@@ -9,6 +9,13 @@ symbol and checks that it gives the same output as the regular entry point (whic
 caller-allocated scratch), twice in a row, because the built-in scratch is shared by all calls
 and keeps the previous call's contents.
 
+Which launches touch the built-in scratch: up to eight context splits of a head are merged inside a
+thread-block cluster through shared memory and never read the scratch pointers, so the cases
+below use 12 and 16 splits (partial results and arrival counters in global memory), with bf16
+and int8 caches and a head size that only the scalar kernels take.  The two smaller cases keep
+the cluster path covered.  With a wrong scratch address, or counters that do not return to zero,
+the 12- and 16-split cases fail.
+
 The file name makes pytest collect it last, so a run that stops at the first failure has
 already executed every other test.
 """
@@ -20,23 +27,35 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _setup(batch, H, Hkv, d, ctx, splits, seed):
+def _setup(batch, H, Hkv, d, ctx, splits, seed, q8=False):
     from realizar_b200 import ops
     torch.manual_seed(seed)
     pages_per_seq = -(-ctx // 16)
     n_pages = batch * pages_per_seq
-    kc = (torch.randn(n_pages, Hkv, 16, d, device="cuda") * 0.5).to(torch.bfloat16)
-    vc = (torch.randn(n_pages, Hkv, 16, d, device="cuda") * 0.5).to(torch.bfloat16)
+    if q8:                      # int8 rows with a per-row scale, filled through the library's own append kernel
+        kv = ops.kv_cache_alloc(1, n_pages, Hkv, d, "cuda", "q8")
+        kc, vc = kv[0, 0], kv[1, 0]
+        n_tok = n_pages * 16
+        pos = torch.arange(n_tok, device="cuda", dtype=torch.int32) % (pages_per_seq * 16)
+        rows = torch.arange(n_tok, device="cuda", dtype=torch.int32) // 16
+        ops.kv_append((torch.randn(n_tok, Hkv * d, device="cuda") * 0.5).contiguous(), (torch.randn(n_tok, Hkv * d, device="cuda") * 0.5).contiguous(),
+                      kc, vc, pos, rows.contiguous(), Hkv, d)
+    else:
+        kc = (torch.randn(n_pages, Hkv, 16, d, device="cuda") * 0.5).to(torch.bfloat16)
+        vc = (torch.randn(n_pages, Hkv, 16, d, device="cuda") * 0.5).to(torch.bfloat16)
     pt = torch.randperm(n_pages, device="cuda").to(torch.int32).reshape(batch, pages_per_seq).contiguous()
     qkv = torch.randn(batch, (H + 2 * Hkv) * d, device="cuda")
     pos = torch.tensor([ctx - 1 - 3 * b for b in range(batch)], device="cuda", dtype=torch.int32)
     return ops, kc, vc, pt, qkv, pos
 
 
-@pytest.mark.parametrize("H,Hkv,d,ctx,splits", [(8, 8, 80, 200, 4), (16, 4, 128, 333, 6)])
-def test_static_entry_point_matches_regular_one_twice(cuda_device, H, Hkv, d, ctx, splits):
+@pytest.mark.parametrize("H,Hkv,d,ctx,splits,q8", [
+    (8, 8, 80, 200, 4, False), (16, 4, 128, 333, 6, False),            # merged inside a cluster: scratch pointers unused
+    (8, 8, 80, 400, 12, False), (16, 4, 128, 520, 16, False),           # merged through the built-in scratch
+    (8, 2, 72, 300, 12, False), (8, 8, 64, 330, 16, True)])            # scalar kernels: odd head size, int8 cache
+def test_static_entry_point_matches_regular_one_twice(cuda_device, H, Hkv, d, ctx, splits, q8):
     batch = 2
-    ops, kc, vc, pt, qkv, pos = _setup(batch, H, Hkv, d, ctx, splits, seed=H + ctx)
+    ops, kc, vc, pt, qkv, pos = _setup(batch, H, Hkv, d, ctx, splits, seed=H + ctx, q8=q8)
     lib = ops.lib()
     fn = lib.rlz_attn_decode_static                       # the exported C symbol itself
     fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
@@ -50,8 +69,9 @@ def test_static_entry_point_matches_regular_one_twice(cuda_device, H, Hkv, d, ct
         k2, v2 = kc.clone(), vc.clone()
         out = torch.zeros(batch, H * d, device="cuda")
         partial, counters = ops.attn_decode_scratch(batch, H, splits, d, "cuda")
-        p = ops.build_attn_decode_params(qkv_in, out, k2, v2, pos, pt, partial, counters, H, Hkv, d, splits, batch, d // 2, 2, 1e4,
+        p = ops.build_attn_decode_params(qkv_in, out, k2, v2, pos, pt, partial, counters, H, Hkv, d, splits, batch, d // 2 // 2 * 2, 2, 1e4,
                                          0, H * d, (H + Hkv) * d)
+        assert p.kv_q8 == (1 if q8 else 0)
         if static:
             p.partial, p.counters = None, None             # ignored by the static entry point
             rc = fn(ctypes.addressof(p), stream)
