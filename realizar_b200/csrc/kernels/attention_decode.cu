@@ -50,7 +50,7 @@ template <int GT, int MERGE, int HD>
 static cudaError_t launch_attn_mma(const AttnDecodeParams& p, dim3 grid, dim3 block, dim3 cl, cudaStream_t st) {
   const size_t ring = (size_t)ATT_RING * 64 * (HD == 80 ? 2 * HD : 2 * HD + 16);       // row bytes as in the kernel
   static SmemOptIn opt;
-  if (cudaError_t e = opt.ensure(attn_decode_mma_kernel<GT, MERGE, HD>, ring); e != cudaSuccess) return e;
+  if (cudaError_t e = opt.ensure(attn_decode_mma_kernel<GT, MERGE, HD>, ring, 0); e != cudaSuccess) return e;   // static shared memory comes on top: always opt in
   return launch_cluster(attn_decode_mma_kernel<GT, MERGE, HD>, grid, block, cl, ring, st, p);
 }
 template <int GT, int MERGE>

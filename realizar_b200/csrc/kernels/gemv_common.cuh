@@ -188,6 +188,46 @@ __device__ __forceinline__ void gemv_epilogue(const GemvParams& p, const GemvMat
   const uint32_t epoch = *ar.epoch;
   const int64_t slot = (int64_t)ar.n * 4;                        // pairs per (parity, rank) slot
   const int64_t base = (int64_t)(epoch & 1u) * ar.world * slot;
+  const int world = ar.world;
+  if ((world & (world - 1)) == 0) {
+    // One thread per (output, peer) pair: a CTA owns only a handful of rows, so this puts rows x world independent remote
+    // stores and polls in flight instead of `world` serial ones per row.  The partial values first go to slot 0 of their
+    // rows in shared memory (every thread reads only its own element there).
+    for (int idx = threadIdx.x; idx < count; idx += blockDim.x) {
+      const int rl = idx / B, b = idx - rl * B;
+      const float v = gemv_value<B>(M, rowacc, rl, b, r0 + rl);
+      rowacc[(rl * 2) * B + b] = v;
+    }
+    __syncthreads();
+    const int total = count * world, lane = threadIdx.x & 31;
+    for (int first = threadIdx.x & ~31; first < total; first += blockDim.x) {      // warp-uniform bound: the shuffles below are safe
+      const int idx = first + lane;
+      const bool ok = idx < total;
+      const int e = ok ? idx / world : 0, q = idx & (world - 1);
+      const int rl = e / B, b = e - rl * B, r = r0 + rl;
+      const int64_t off = (int64_t)b * ar.n + r;
+      float v = 0.f;
+      if (ok) {
+        // 1. my partial value, tagged with the epoch, into my slot of rank q's inbox
+        st_pair_sys(ar.inbox[q] + base + (int64_t)ar.rank * slot + off, __float_as_uint(rowacc[(rl * 2) * B + b]), epoch);
+        // 2. rank q's partial value of the same element from my inbox (bounded polls)
+        const uint2* src = ar.inbox[ar.rank] + base + (int64_t)q * slot + off;
+        uint2 w = ld_pair_sys(src);
+        for (int64_t spins = 0; w.y != epoch; ++spins) {
+          if (spins > ar.spin_limit) { atomicExch(ar.status, 2001); break; }
+          w = ld_pair_sys(src);
+        }
+        v = __uint_as_float(w.x);
+      }
+      // the world values of an element sit in adjacent lanes: a fixed xor tree, identical on every rank
+      for (int o = 1; o < world; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (ok && q == 0) {
+        if (M.has_residual) v += p.residual[(int64_t)b * p.ld_res + r];
+        p.y[(int64_t)b * p.ldy + M.out_off + r] = v;
+      }
+    }
+    return;
+  }
   for (int idx = threadIdx.x; idx < count; idx += blockDim.x) {
     const int rl = idx / B, b = idx - rl * B, r = r0 + rl;
     // 1. push my partial value, tagged with the epoch, into my slot of every rank's inbox
