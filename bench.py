@@ -8,10 +8,13 @@ random-init weights quantised to the Q4_K_M mixture, after a 512-token prompt, o
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 4 --master-addr 127.0.0.1 \
         --master-port 29500 bench.py --gpus 4 --steps 256 --warmup 8
 
-A step is one decode token for the whole batch.  `value` is measured with CUDA events around
-K graph replays with device-side token feedback; `e2e` is the same loop through the public
-streaming API (pinned-host token in, sampled token out, every step).
-Rank 0 prints one JSON line.
+A step is one decode token for the whole batch.  `value` is the median over `--repeats` regions
+of exactly K graph replays with device-side token feedback, each timed with CUDA events (max over
+ranks); `e2e` is the same loop through the public streaming API (pinned-host token in, sampled
+token out, every step).  The same line carries `aux.bs64` (the batch-64 half of the metric on the
+same engine), `aux.ttft_ms_p50` over at least five distinct prompts and, under tensor
+parallelism, `aux.nccl_arm` (the same steps with NCCL all-reduces) and `aux.tp_parity` (cosine
+of the first decode step's logits between the two communicators).  Rank 0 prints one JSON line.
 """
 from __future__ import annotations
 
@@ -39,6 +42,9 @@ def parse_args():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--scheme", default="Q4_K_M")
     ap.add_argument("--tp-comm", default="fused", choices=["fused", "nccl"], help="row-parallel all-reduce: in-kernel peer stores or NCCL")
+    ap.add_argument("--repeats", type=int, default=10, help="timed regions of --steps steps each; the median is reported")
+    ap.add_argument("--aux-batch", type=int, default=64, help="also report device-timed decode at this batch (aux.bsN); 0 = off")
+    ap.add_argument("--no-nccl-arm", action="store_true", help="tensor parallel: skip the NCCL all-reduce arm and the parity figure")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     return ap.parse_args()
@@ -101,6 +107,11 @@ def reference_arm(args):
     return 0
 
 
+def median(xs):
+    s = sorted(xs)
+    return s[len(s) // 2] if len(s) % 2 else 0.5 * (s[len(s) // 2 - 1] + s[len(s) // 2])
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -130,14 +141,14 @@ def main():
 
     cfg = named_config(args.model)
     K, W, B = args.steps, max(3, args.warmup), args.batch
-    max_seq = ((args.prompt_len + 2 * (K + W) + 64 + 15) // 16) * 16
+    R = max(1, args.repeats)
+    BIG = max(B, args.aux_batch) if args.aux_batch > 0 else B       # one engine serves the headline batch and the bs=64 figure
+    max_seq = ((args.prompt_len + (K + W) + 64 + 15) // 16) * 16
     t0 = time.time()
     weights = synthetic_weights(cfg, scheme=args.scheme, seed=0, device=dev)      # same seed on every rank
-    eng = DecodeEngine(weights, EngineConfig(max_batch=B, max_seq_len=max_seq, cuda_graphs=not args.no_graphs, pdl=not args.no_pdl,
-                                             greedy_only=True), device=dev, comm=comm, tp_rank=rank, tp_size=world)
+    ecfg = EngineConfig(max_batch=BIG, max_seq_len=max_seq, cuda_graphs=not args.no_graphs, pdl=not args.no_pdl, greedy_only=True)
+    eng = DecodeEngine(weights, ecfg, device=dev, comm=comm, tp_rank=rank, tp_size=world)
     total_weight_bytes = weights.total_bytes()
-    del weights
-    torch.cuda.empty_cache()
     load_s = time.time() - t0
 
     def sync_all():
@@ -146,108 +157,175 @@ def main():
             dist.barrier()
             torch.cuda.synchronize(dev)
 
-    # ---- prompt: uniform random ids, prefilled through the engine ---------------------------
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    # ---- prompts: uniform random ids, prefilled through the engine; TTFT = wall time of one prefill call ----------
     g = torch.Generator().manual_seed(0)
-    prompts = torch.randint(0, cfg.vocab_size, (B, args.prompt_len), generator=g)
-    for b in range(B):
-        eng.open_slot(b, max_seq)
-    # warm the prefill path once with a full-length scratch prompt in slot 0 (kernel attributes, allocator, and the
-    # first NCCL collective of that message size under tensor parallelism), then time TTFT
+    prompts = torch.randint(0, cfg.vocab_size, (BIG, args.prompt_len), generator=g)
+
+    def prefill_all(e, n):
+        """Open slots 0..n-1 and run their prompts; returns (first tokens, per-prompt wall times in ms)."""
+        firsts, times = [], []
+        for b in range(n):
+            e.open_slot(b, max_seq)
+            torch.cuda.synchronize(dev)
+            t = time.perf_counter()
+            firsts.append(e.prefill(b, [int(x) for x in prompts[b]]))
+            torch.cuda.synchronize(dev)
+            times.append((time.perf_counter() - t) * 1e3)
+        return firsts, times
+
+    # warm the prefill path once with a scratch prompt (kernel attributes, allocator, first collectives of that size)
+    eng.open_slot(0, max_seq)
     eng.prefill(0, [int(t) for t in torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g)])
     eng.close_slot(0)
-    eng.open_slot(0, max_seq)
     sync_all()
-    profile_prefill = os.environ.get("RLZ_PROFILE_REGION") == "prefill"   # `ncu --profile-from-start off`: capture the timed prefill only
-    if profile_prefill:
-        torch.cuda.cudart().cudaProfilerStart()
-    t0 = time.time()
-    first = [eng.prefill(b, [int(t) for t in prompts[b]]) for b in range(B)]
-    torch.cuda.synchronize(dev)
-    prefill_s = time.time() - t0
-    if profile_prefill:
-        torch.cuda.cudart().cudaProfilerStop()
-
-    # ---- device-timed decode: graph replays with device-side feedback ---------------------------
+    n_ttft = max(B, min(BIG, 8))                         # at least 5 distinct prompts for the TTFT median when the engine has the slots
+    first, ttft = prefill_all(eng, n_ttft)
+    for b in range(B, n_ttft):
+        eng.close_slot(b)
     pos0 = eng.slots[0].position
-    eng.buf.tokens[:B].copy_(torch.tensor(first, dtype=torch.int32))
-    eng.buf.positions[:B].fill_(pos0)
-    for b in range(B):
-        eng._ensure_pages(b, max_seq)
-    for _ in range(W):
-        eng.run_step(B)
-        eng.advance(B)
-    sync_all()
+
+    def timed_decode(e, nb, firsts, repeats):
+        """Device-timed decode of slots 0..nb-1: `repeats` regions of exactly K graph-replayed steps with device-side token
+        feedback, each region restarting at the position after the prompt (+ W warm-up steps).  Returns ms per region."""
+        for b in range(nb):
+            e._ensure_pages(b, max_seq)
+        out = []
+        for _ in range(repeats):
+            e.buf.tokens[:nb].copy_(torch.tensor(firsts[:nb], dtype=torch.int32))
+            e.buf.positions[:nb].fill_(pos0)
+            for _ in range(W):
+                e.run_step(nb)
+                e.advance(nb)
+            sync_all()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(K):
+                e.run_step(nb)
+                e.advance(nb)
+            e1.record()
+            sync_all()
+            out.append(max_over_ranks(e0.elapsed_time(e1)))
+        return out
+
+    # ---- headline: device-timed decode at batch B ----------------------------------------------------------------
+    timed_decode(eng, B, first, 1)                       # graph capture and first replays outside the sampled region
     sampler = ClockSampler(local)
     sampler.start()
     l0 = ops.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     profile_region = os.environ.get("RLZ_PROFILE_REGION") in ("1", "decode")     # `ncu --profile-from-start off`: capture the timed steps only
     if profile_region:
         torch.cuda.cudart().cudaProfilerStart()
-    e0.record()
-    for _ in range(K):
-        eng.run_step(B)
-        eng.advance(B)
-    e1.record()
-    sync_all()
+    regions = timed_decode(eng, B, first, R)
     if profile_region:
         torch.cuda.cudart().cudaProfilerStop()
-    clocks = sampler.stop()
     eager_launches = ops.launch_count() - l0
-    ms = e0.elapsed_time(e1)
-    for b in range(B):
-        eng.slots[b].position = pos0 + W + K
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t)
+    ms = median(regions)
     tok_s = B * K / (ms / 1e3)
     launches = (eng.kernels_per_step(eng.bucket_for(B)) + 1) * K
 
-    # ---- end-to-end: public streaming path, pinned token in / sampled token out every step -----
-    cur = {b: int(eng.buf.sampled[b]) for b in range(B)}
-    for _ in range(3):
-        out = eng.feed(cur)
-        cur = {b: int(out[b]) for b in range(B)}
-    sync_all()
-    t0 = time.perf_counter()
-    for _ in range(K):
-        out = eng.feed(cur)
-        cur = {b: int(out[b]) for b in range(B)}
-    torch.cuda.synchronize(dev)
-    e2e_s = time.perf_counter() - t0
-    if world > 1:
-        t = torch.tensor([e2e_s], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t)
-    e2e_tok_s = B * K / e2e_s
+    # ---- end-to-end: public streaming path, pinned token in / sampled token out every step ------------------------
+    def timed_e2e(e, nb, firsts, repeats):
+        out = []
+        for _ in range(repeats):
+            for b in range(nb):
+                e.slots[b].position = pos0
+            cur = {b: int(firsts[b]) for b in range(nb)}
+            for _ in range(W):
+                o = e.feed(cur)
+                cur = {b: int(o[b]) for b in range(nb)}
+            sync_all()
+            t = time.perf_counter()
+            for _ in range(K):
+                o = e.feed(cur)
+                cur = {b: int(o[b]) for b in range(nb)}
+            torch.cuda.synchronize(dev)
+            out.append(max_over_ranks(time.perf_counter() - t))
+        return out
+
+    e2e_regions = timed_e2e(eng, B, first, R)
+    clocks = sampler.stop()
+    e2e_tok_s = B * K / median(e2e_regions)
+
+    aux = {"load_s": round(load_s, 2), "ttft_ms_p50": round(median(ttft), 2), "ttft_ms_all": [round(t, 2) for t in ttft],
+           "ttft_prompts": len(ttft), "prefill_path": "tcgen05 gemm" if eng.gemm_ok else "serial decode kernels",
+           "weight_bytes_total": int(total_weight_bytes), "launch_calls_outside_graphs": int(eager_launches)}
+
+    # ---- aux: the bs = 64 half of the metric on the same engine (all slots prefilled, device-timed the same way) ------
+    if BIG > B:
+        for b in range(B):
+            eng.close_slot(b)
+        big_first, _ = prefill_all(eng, BIG)
+        timed_decode(eng, BIG, big_first, 1)
+        big = timed_decode(eng, BIG, big_first, max(3, R // 3))
+        aux["bs%d" % BIG] = {"value": round(BIG * K / (median(big) / 1e3), 1), "unit": "tok/s", "ms_per_step": round(median(big) / K, 4),
+                             "repeats": len(big), "kernels_per_step": eng.kernels_per_step(eng.bucket_for(BIG)) + 1}
+
+    # ---- aux under tensor parallelism: the same K steps with NCCL all-reduces, and the agreement of the two paths -----
+    if world > 1 and args.tp_comm == "fused" and not args.no_nccl_arm:
+        from realizar_b200.parallel.tp import make_tp_comm
+        ncomm = make_tp_comm(rank, world, dev, mode="nccl")
+        neng = DecodeEngine(weights, EngineConfig(max_batch=B, max_seq_len=max_seq, cuda_graphs=not args.no_graphs, pdl=not args.no_pdl,
+                                                  greedy_only=True), device=dev, comm=ncomm, tp_rank=rank, tp_size=world)
+        nfirst, _ = prefill_all(neng, B)
+        timed_decode(neng, B, nfirst, 1)
+        nreg = timed_decode(neng, B, nfirst, max(3, R // 2))
+        aux["nccl_arm"] = {"value": round(B * K / (median(nreg) / 1e3), 2), "unit": "tok/s", "ms_per_step": round(median(nreg) / K, 5), "repeats": len(nreg)}
+        # parity: logits of the first decode step after the same prompt, fused vs NCCL communicator (this rank's vocabulary shard)
+        for e in (eng, neng):
+            for b in range(e.cfg.max_batch):
+                e.close_slot(b)
+            e.open_slot(0, max_seq)
+            tok = e.prefill(0, [int(x) for x in prompts[0]])
+            e.feed({0: int(tok)})
+        a_, b_ = eng.buf.logits[0, : eng.model.vocab_local].double(), neng.buf.logits[0, : neng.model.vocab_local].double()
+        stats = torch.stack([(a_ * b_).sum(), (a_ * a_).sum(), (b_ * b_).sum()])
+        dist.all_reduce(stats)
+        aux["tp_parity"] = round(float(stats[0] / (stats[1].sqrt() * stats[2].sqrt() + 1e-30)), 6)
+        neng.close()
+        ncomm.close()
 
     if rank == 0:
         pub = PUBLISHED.get(args.model)
         line = {
             "metric": "decode tok/s (bs=%d, %s)" % (B, args.scheme), "value": round(tok_s, 2), "unit": "tok/s", "n_gpus": world,
-            "steps": K, "warmup": W, "ms_per_step": round(ms / K, 5), "higher_is_better": True, "scaling": "strong",
+            "steps": K, "warmup": W, "ms_per_step": round(ms / K, 5), "repeats": len(regions),
+            "ms_per_step_min": round(min(regions) / K, 5), "ms_per_step_max": round(max(regions) / K, 5),
+            "higher_is_better": True, "scaling": "strong",
             "vs_baseline": round(tok_s / pub, 3) if pub else None, "dtype": "q4_k_m weights, int8/fp32 activations, bf16 KV",
             "data": "synthetic (random-init N(0,0.02) weights, uniform-random prompt ids)",
             "config": {"model": args.model + "-shaped", "global_batch": B, "seq_len": args.prompt_len + W + K, "prompt_len": args.prompt_len,
                        "parallelism": "tp%d" % world, "tp_comm": args.tp_comm if world > 1 else None,
                        "l2": "weights per GPU (%.0f MB) exceed L2; no flush" % (eng.model.weight_bytes() / 1e6),
+                       "timing": "median over %d regions of %d steps, each region after %d warm-up steps" % (len(regions), K, W),
                        "cuda_graphs": not args.no_graphs, "pdl": eng.pdl, "kernels_per_step": eng.kernels_per_step(eng.bucket_for(B)) + 1,
                        "baseline": "published %s tok/s on RTX 4090 (reference README)" % pub},
             "clocks": clocks,
-            "e2e": {"value": round(e2e_tok_s, 2), "unit": "tok/s", "h2d_bytes_per_step": 8 * B, "d2h_bytes_per_step": 4 * B},
+            "e2e": {"value": round(e2e_tok_s, 2), "unit": "tok/s", "h2d_bytes_per_step": 8 * BIG, "d2h_bytes_per_step": 4 * B,
+                    "repeats": len(e2e_regions)},
             "gpu_launches": int(launches),
-            "aux": {"load_s": round(load_s, 2), "ttft_ms_prompt%d" % args.prompt_len: round(prefill_s * 1e3 / B, 2), "prefill_path": "tcgen05 gemm" if eng.gemm_ok else "serial decode kernels", "weight_bytes_total": int(total_weight_bytes),
-                    "launch_calls_outside_graphs": int(eager_launches)},
+            "aux": aux,
         }
         print(json.dumps(line))
+        sys.stdout.flush()
+    # ---- orderly teardown: captured graphs hold communicator work, so they go first -------------------------------
+    eng.close()
+    if comm is not None:
+        comm.close()
     if world > 1:
-        # leave without tearing NCCL down: communicator destruction after graph-captured collectives can block
         torch.cuda.synchronize(dev)
         dist.barrier()
-        sys.stdout.flush()
-        sys.stderr.flush()
-        os._exit(0)
+        guard = threading.Timer(60.0, lambda: (sys.stderr.write("bench.py: process-group teardown did not finish in 60 s; leaving\n"), os._exit(0)))
+        guard.daemon = True
+        guard.start()
+        dist.destroy_process_group()
+        guard.cancel()
     return 0
 
 

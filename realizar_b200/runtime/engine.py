@@ -92,13 +92,14 @@ class DecodeEngine:
         # [2 (k,v), layers, pages, kv_heads, PAGE, head_dim] bf16
         self.kv = ops.kv_cache_alloc(self.mcfg.num_layers, self.num_pages, m.kv_heads, hd, dev, c.kv_dtype, PAGE)
         self.pages = PagedKvCache(self.num_pages, PAGE)
-        self.splits = c.attn_splits or self._choose_splits(B)
+        self.splits = c.attn_splits or self._choose_splits(B)        # at the full batch; smaller buckets split the context further
         qkv_w = m.q_dim + 2 * m.kv_dim
         o_k = max(L.o.k for L in m.layers)
         d_k = max(L.down.k for L in m.layers)
         y1_w = (m.act_col0 + d_k + 256) if self.mcfg.parallel_residual else qkv_w
         z = lambda *s, dt=torch.float32: torch.zeros(*s, device=dev, dtype=dt)
-        part, ctr = ops.attn_decode_scratch(B, m.heads, self.splits, hd, dev)
+        self.buckets = sorted(set(c.batch_buckets or [b for b in (1, 2, 4, 8, 16, 32, 64, 128) if b < B] + [B]))
+        part, ctr = ops.attn_decode_scratch(max(b * self.splits_for(b) for b in self.buckets), m.heads, 1, hd, dev)
         # tokens and positions are the two rows of one buffer (and of one pinned host buffer), so a step uploads both with one copy
         tok_pos = torch.zeros(2, B, device=dev, dtype=torch.int32)
         tok_pos[1].fill_(-1)
@@ -117,7 +118,6 @@ class DecodeEngine:
             per_layer = 1 if self.mcfg.parallel_residual else 2
             comm.allocate(self.mcfg.num_layers * per_layer * chunks_max, self.mcfg.hidden_dim, max_batch=B)
         self.slots = [Slot() for _ in range(B)]
-        self.buckets = sorted(set(c.batch_buckets or [b for b in (1, 2, 4, 8, 16, 32, 64, 128) if b < B] + [B]))
         self._plans: Dict[int, DecodePlan] = {}
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self._gen = torch.Generator(device=dev).manual_seed(c.seed)
@@ -152,6 +152,11 @@ class DecodeEngine:
             s *= 2
         return s
 
+    def splits_for(self, bucket: int) -> int:
+        """Context splits of the decode attention at this batch bucket: few sequences leave SMs idle unless each head's
+        context is cut into more pieces (an engine sized for 64 sequences still decodes a single one with 8 splits)."""
+        return self.cfg.attn_splits or self._choose_splits(bucket)
+
     def bucket_for(self, batch: int) -> int:
         for b in self.buckets:
             if b >= batch:
@@ -163,7 +168,7 @@ class DecodeEngine:
         if bucket not in self._plans and self._use_batched_step(bucket):
             self._plans[bucket] = self._batched_step_plan(bucket)
         if bucket not in self._plans:
-            self._plans[bucket] = build_decode_plan(self.model, self.buf, self.kv[0], self.kv[1], bucket, self.splits, self.comm,
+            self._plans[bucket] = build_decode_plan(self.model, self.buf, self.kv[0], self.kv[1], bucket, self.splits_for(bucket), self.comm,
                                                     self.cfg.greedy_only, self.sm_count, persistent=self._persistent_ok(bucket))
         return self._plans[bucket]
 
@@ -495,7 +500,7 @@ class DecodeEngine:
         if key not in self._draft_plans:
             if slot != 0:
                 raise ValueError("the layer-skipping draft runs in slot 0")
-            self._draft_plans[key] = build_decode_plan(self.model, self.buf, self.kv[0], self.kv[1], 1, self.splits, self.comm, True,
+            self._draft_plans[key] = build_decode_plan(self.model, self.buf, self.kv[0], self.kv[1], 1, self.splits_for(1), self.comm, True,
                                                        self.sm_count, layer_subset=set(key))
         s = self.slots[slot]
         self._ensure_pages(slot, s.position + 1)
@@ -551,6 +556,18 @@ class DecodeEngine:
         idx = torch.tensor(pages, dtype=torch.long, device=self.device)
         self.kv[:, :, idx] = snap["kv"].to(self.device, non_blocking=True)
         s.position = snap["position"]
+
+    def close(self) -> None:
+        """Release the captured graphs and launch plans (they hold kernels, buffers and, under tensor parallelism, work of the
+        process group's communicator) and wait for the device.  Call before ``torch.distributed.destroy_process_group()``:
+        a communicator that still has captured collectives alive can block its own destruction."""
+        self._graphs.clear()
+        self._plans.clear()
+        self._head_plans.clear()
+        if hasattr(self, "_draft_plans"):
+            self._draft_plans.clear()
+        self._batched = None
+        torch.cuda.synchronize(self.device)
 
     def logits_of_last_step(self, slot: int = 0) -> torch.Tensor:
         return self.buf.logits[slot, : self.mcfg.vocab_size].clone()
