@@ -40,6 +40,7 @@ struct AttnPrefillParams {
   int32_t window, kv_q8;       // kv_q8: int8 cache rows of head_dim + 16 bytes (codes, then the fp32 row scale)
   float scale;
   int32_t out_bf16;            // 1: `out` is bf16 [T, ld_out] (the operand of the output projection GEMM), else fp32
+  const int32_t* pos0_ptr;     // when set, the position of row 0 is read from here (a launch captured in a CUDA graph serves any chunk)
 };
 
 template <int D>
@@ -73,11 +74,12 @@ __global__ void __launch_bounds__(FP_THREADS) attn_prefill_tcgen05_kernel(const 
   const uint32_t t_lane = (uint32_t)(warp * 32) << 16;   // this warp's TMEM lanes
   pdl_launch_dependents();
   pdl_wait();
+  const int pos0 = p.pos0_ptr ? *p.pos0_ptr : p.pos0;
 
   // ---- Q tile: my row, fp32 -> bf16, swizzled --------------------------------------------------
   const int qrow = m0 + tid;
   const bool qvalid = qrow < p.n_tokens;
-  const int qpos = p.pos0 + qrow;
+  const int qpos = pos0 + qrow;
   {
     const float* src = p.qkv + (int64_t)min(qrow, p.n_tokens - 1) * p.ld_qkv + p.q_off + head * D;
 #pragma unroll
@@ -91,9 +93,9 @@ __global__ void __launch_bounds__(FP_THREADS) attn_prefill_tcgen05_kernel(const 
       store_row_sw128(Qs + s * FP_SLAB, tid, v);
     }
   }
-  const int ctx = p.pos0 + p.n_tokens;
-  const int kend = min(ctx, p.pos0 + m0 + 128);          // causal: no key beyond the tile's last query
-  const int klo = p.window > 0 ? max(0, p.pos0 + m0 - p.window + 1) / 128 * 128 : 0;
+  const int ctx = pos0 + p.n_tokens;
+  const int kend = min(ctx, pos0 + m0 + 128);          // causal: no key beyond the tile's last query
+  const int klo = p.window > 0 ? max(0, pos0 + m0 - p.window + 1) / 128 * 128 : 0;
   const float sc = p.scale * 1.4426950408889634f;
   const uint32_t idesc_s = make_idesc_bf16(128, 128), idesc_o = make_idesc_bf16(128, D);
   float o[D];
@@ -301,6 +303,7 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(const __grid_cons
   const int m0 = blockIdx.x * PM_ROWS, head = blockIdx.y, kvh = head / (p.n_heads / p.n_kv_heads);
   pdl_launch_dependents();
   pdl_wait();
+  const int pos0 = p.pos0_ptr ? *p.pos0_ptr : p.pos0;
   for (int i = tid; i < PM_ROWS * HD; i += 128) {
     const int r = i / HD, j = i - r * HD;
     q_s[r][j] = m0 + r < p.n_tokens ? p.qkv[(int64_t)(m0 + r) * p.ld_qkv + p.q_off + head * HD + j] : 0.f;
@@ -310,8 +313,8 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(const __grid_cons
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  const int ctx = p.pos0 + p.n_tokens;
-  const int qpos0 = p.pos0 + m0;                                     // position of row 0; row r sits at qpos0 + r
+  const int ctx = pos0 + p.n_tokens;
+  const int qpos0 = pos0 + m0;                                     // position of row 0; row r sits at qpos0 + r
   const int end = min(ctx, qpos0 + PM_ROWS);                         // causal: no key beyond the tile's last query
   const int start = p.window > 0 ? max(0, qpos0 - p.window + 1) / ATT_PAGE * ATT_PAGE : 0;
   const int iters = (end - start + 31) / 32;

@@ -49,8 +49,25 @@ struct GemmParams {
   int32_t ar_rank, ar_world, ar_rows, ar_enabled;
   int32_t ar_site, ar_nsites, ar_splits;
   int32_t flags;           // GM_OUT_BF16: Y is bf16 (ldy in elements); GM_RES_MUL: the `residual` operand multiplies instead of adding
+  // ar_enabled == 2, two-shot all-reduce, first half (reduce-scatter by ownership): token row t belongs to rank t / rs_own_rows;
+  // the CTA stores its fp32 tile (+ bias, + the local `residual` operand) only into the OWNER's inbox
+  // [2 buffers][world writers][ar_splits][ar_rows owned rows][ar_row_pairs floats] (plain peer stores), then one thread fences
+  // and publishes the tile's tag in the owner's flag array [2][world][ar_splits][rs_ntiles][rs_mtiles].  The owner's reduce
+  // kernel (symm_mem.cu) sums the writers, normalises and sends finished rows to every rank.
+  uint32_t* rs_flags[8];
+  int32_t rs_own_rows, rs_ntiles, rs_mtiles, _pad2;
 };
 enum { GM_OUT_BF16 = 1, GM_RES_MUL = 2 };
+
+// element i of an 8-entry array that lives in the kernel parameters, as a chain of selects: a run-time index would make the
+// compiler copy the array to local memory
+template <typename T>
+__device__ __forceinline__ T pick8(T const (&a)[8], int i) {
+  T v = a[0];
+#pragma unroll
+  for (int j = 1; j < 8; ++j) v = i == j ? a[j] : v;
+  return v;
+}
 
 // ---- producers: raw block bytes -> registers (issued one K step ahead), registers -> bf16 pairs -------------
 // The integer code q of a weight is dropped into the mantissa of a bf16 power of two (magic + q is exact), the
@@ -196,7 +213,9 @@ template <int NT, int QT, int RT> struct GemmCfg {
   static constexpr int THREADS = RT * GM_PRODUCERS + 96;                           // dequant warps + B TMA + MMA + raw TMA
 };
 
-template <int NT, int QT, int RT>
+// RS: the reduce-scatter epilogue of the two-shot all-reduce is compiled in (its own instantiations, so that the register
+// allocation of every other launch stays what it was).
+template <int NT, int QT, int RT, bool RS>
 __global__ void __launch_bounds__(RT * GM_PRODUCERS + 96) gemm_kquant_tcgen05_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap xmap,
                                                                                      const __grid_constant__ CUtensorMap wmap) {
   using Cfg = GemmCfg<NT, QT, RT>;
@@ -403,7 +422,22 @@ __global__ void __launch_bounds__(RT * GM_PRODUCERS + 96) gemm_kquant_tcgen05_ke
           // one compact loop per output mode (the mode is uniform over the launch): only the code of the mode in use is fetched
           const int ntok = min(32, p.m - (m0 + c0));
           float* dst = p.Y + (int64_t)(m0 + c0) * p.ldy + row;
-          if (p.ar_enabled) {                             // one 8-byte store per rank; lanes cover consecutive rows (coalesced)
+          if (RS && p.ar_enabled == 2) {                  // reduce-scatter: each token row goes to its owner only (4-byte stores, lanes = consecutive features)
+            const float* res = (p.residual && blockIdx.z == 0) ? p.residual + (int64_t)(m0 + c0) * p.ld_res + row : nullptr;
+            const int64_t slot_row0 = (ar_buf + (int64_t)p.ar_rank * p.ar_splits + blockIdx.z) * p.ar_rows;
+            int owner = (m0 + c0) / p.rs_own_rows, lt = (m0 + c0) - owner * p.rs_own_rows;      // advanced incrementally: no division per token
+            float* dst_o = (float*)pick8(p.ar_inbox, owner) + (slot_row0 + lt) * p.ar_row_pairs + row;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (j < ntok) {
+                float v = __uint_as_float(r[j]) + bias;
+                if (res) v += res[(int64_t)j * p.ld_res];
+                *dst_o = v;
+                dst_o += p.ar_row_pairs;
+                if (++lt == p.rs_own_rows) { lt = 0; ++owner; dst_o = (float*)pick8(p.ar_inbox, owner) + slot_row0 * p.ar_row_pairs + row; }
+              }
+            }
+          } else if (p.ar_enabled) {                      // one 8-byte store per rank; lanes cover consecutive rows (coalesced)
             const int64_t off0 = ar_slot + (int64_t)(m0 + c0) * p.ar_row_pairs + row;
 #pragma unroll
             for (int j = 0; j < 32; ++j)
@@ -439,6 +473,17 @@ __global__ void __launch_bounds__(RT * GM_PRODUCERS + 96) gemm_kquant_tcgen05_ke
   gm_trace(tr, cta_lin, 6);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (RS && p.ar_enabled == 2 && tid == 0 && !failed_s) {
+    // every epilogue thread's peer stores happened before the barrier; the fence makes them visible system-wide before the flag
+    __threadfence_system();
+    const uint32_t epoch = *p.ar_epoch;
+    const uint32_t tag = epoch * 256u + (uint32_t)p.ar_site;
+    const int64_t par = (int64_t)((epoch * (uint32_t)p.ar_nsites + (uint32_t)p.ar_site) & 1u);
+    const int64_t fidx = (((par * p.ar_world + p.ar_rank) * p.ar_splits + blockIdx.z) * p.rs_ntiles + blockIdx.x) * p.rs_mtiles + blockIdx.y;
+    const int mend = min(p.m, m0 + NT);
+    for (int owner = m0 / p.rs_own_rows; owner <= (mend - 1) / p.rs_own_rows; ++owner)
+      asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(pick8(p.rs_flags, owner) + fidx), "r"(tag) : "memory");
+  }
   if (failed_s && warp == PWARPS && lane == 0) {
     // error path: give TMA copies still in flight a bounded chance to land before the CTA's shared memory is released
     for (int s = 0; s < GM_STAGES && s < nit; ++s) gm_wait(&full_bar[s], 0u);
@@ -489,12 +534,12 @@ static int make_w_map(CUtensorMap* map, const GemmParams& p, int box_rows, int b
   return r == CUDA_SUCCESS ? 0 : -7;
 }
 
-template <int NT, int QT, int RT>
-int launch_gemm_q(const GemmParams& p, cudaStream_t st) {
+template <int NT, int QT, int RT, bool RS>
+int launch_gemm_rs(const GemmParams& p, cudaStream_t st) {
   using Cfg = GemmCfg<NT, QT, RT>;
   const size_t smem = Cfg::SMEM;
   static SmemOptIn opt;
-  if (cudaError_t e = opt.ensure(gemm_kquant_tcgen05_kernel<NT, QT, RT>, smem, 0); e != cudaSuccess) return (int)e;
+  if (cudaError_t e = opt.ensure(gemm_kquant_tcgen05_kernel<NT, QT, RT, RS>, smem, 0); e != cudaSuccess) return (int)e;
   alignas(64) CUtensorMap xmap, wmap;
   int rc = make_x_map(&xmap, p, NT);
   if (rc) return rc;
@@ -502,7 +547,11 @@ int launch_gemm_q(const GemmParams& p, cudaStream_t st) {
   else wmap = xmap;                                        // unused by the dense-weight instantiations
   if (rc) return rc;
   dim3 grid((p.n + RT * GM_ROWS - 1) / (RT * GM_ROWS), (p.m + NT - 1) / NT, p.splitk);
-  return (int)launch(gemm_kquant_tcgen05_kernel<NT, QT, RT>, grid, dim3(Cfg::THREADS), smem, st, p, xmap, wmap);
+  return (int)launch(gemm_kquant_tcgen05_kernel<NT, QT, RT, RS>, grid, dim3(Cfg::THREADS), smem, st, p, xmap, wmap);
+}
+template <int NT, int QT, int RT>
+int launch_gemm_q(const GemmParams& p, cudaStream_t st) {
+  return p.ar_enabled == 2 ? launch_gemm_rs<NT, QT, RT, true>(p, st) : launch_gemm_rs<NT, QT, RT, false>(p, st);
 }
 
 template <int NT, int RT>
@@ -528,6 +577,31 @@ int rlz_gemm_error(int clear) {
   return v;
 }
 
+// Tile shape the launcher picks for a call: tokens per CTA, weight rows per CTA, K splits (after clamping).  The owner-side
+// reduce kernel of the two-shot all-reduce needs them to know which tile flags cover a token row.
+int rlz_gemm_plan(const rlz::GemmParams* pp, int* nt, int* rows, int* splitk) {
+  using namespace rlz;
+  const GemmParams& p = *pp;
+  if (p.k % GM_KSTEP || p.m < 1 || p.n < 1) return -1;
+  int sk = p.splitk < 1 ? 1 : p.splitk;
+  if (sk > p.k / GM_KSTEP) sk = p.k / GM_KSTEP;
+  if (p.ar_enabled == 1) sk = p.ar_splits;
+  *splitk = sk;
+  *rows = GM_ROWS;
+  if (p.m <= 32) { *nt = 32; return 0; }
+  if (p.m <= 64) { *nt = 64; return 0; }
+  if (p.m <= 128) { *nt = 128; return 0; }
+  *nt = 256;
+  const long long tiles1 = (long long)((p.n + 127) / 128) * ((p.m + 255) / 256) * sk;
+  const long long tiles2 = (long long)((p.n + 255) / 256) * ((p.m + 255) / 256) * sk;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const bool wide_fits = !(p.qtype == QT_Q5_K || p.qtype == QT_Q6_K);
+  const long long cost1 = ((tiles1 + sms - 1) / sms) * 840, cost2 = ((tiles2 + sms - 1) / sms) * 1100;
+  if (wide_fits && (p._pad == 2 || (p._pad != 1 && cost2 < cost1))) *rows = 2 * GM_ROWS;
+  return 0;
+}
+
 // Y[m, n] = act(X[m, k] W^T + bias) + residual.  With splitk > 1 the partial products are added
 // atomically into Y, which the caller must have initialised (zeros, or the residual); bias is added
 // by split 0 and no activation is applied.  Returns 0, a negative code for bad arguments or a cudaError_t.
@@ -543,9 +617,15 @@ int rlz_gemm_kquant(const rlz::GemmParams* pp, void* stream) {
   p.atomic_out = (p.splitk > 1 && !p.ar_enabled) ? 1 : 0;
   if (p.atomic_out && (p.act != ACT_NONE || p.flags)) return -5;
   if (p.ar_enabled && p.flags) return -8;
-  if (p.ar_enabled && (p.splitk > p.ar_splits || p.act != ACT_NONE || p.residual || p.ar_world < 1 || p.ar_world > 8 || p.m > p.ar_rows ||
-                       p.n > p.ar_row_pairs || p.ar_site < 0 || p.ar_site >= 256 || p.ar_site >= p.ar_nsites)) return -8;
-  if (p.ar_enabled) p.splitk = p.ar_splits;              // the reducer expects exactly ar_splits writers per rank
+  if (p.ar_enabled == 2) {
+    if (p.splitk > p.ar_splits || p.act != ACT_NONE || p.ar_world < 1 || p.ar_world > 8 || p.rs_own_rows < 1 || p.rs_own_rows > p.ar_rows ||
+        (long long)p.rs_own_rows * p.ar_world < p.m || p.n > p.ar_row_pairs || p.ar_site < 0 || p.ar_site >= 256 || p.ar_site >= p.ar_nsites ||
+        (p.n + GM_ROWS - 1) / GM_ROWS > p.rs_ntiles || (p.m + 31) / 32 > p.rs_mtiles) return -8;
+  } else if (p.ar_enabled) {
+    if (p.splitk > p.ar_splits || p.act != ACT_NONE || p.residual || p.ar_world < 1 || p.ar_world > 8 || p.m > p.ar_rows ||
+        p.n > p.ar_row_pairs || p.ar_site < 0 || p.ar_site >= 256 || p.ar_site >= p.ar_nsites) return -8;
+    p.splitk = p.ar_splits;                               // the reducer expects exactly ar_splits writers per rank
+  }
   if ((p.ldx * 2) % 16) return -4;
   cudaStream_t st = (cudaStream_t)stream;
   if (p.m <= 32) return launch_gemm<32, 1>(p, st);

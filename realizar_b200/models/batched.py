@@ -64,12 +64,48 @@ class BatchedForward:
         # tensor parallel, fused mode: row-parallel GEMMs of up to ll_tokens rows push their partial tiles into the peers'
         # inboxes from the epilogue (one-shot all-reduce, latency-optimal); longer chunks use NCCL (bandwidth-optimal)
         self.ll_tokens = 0
-        if model.tp_size > 1 and getattr(comm, "fused", False):
+        # tensor parallel, fused mode (default): two-shot all-reduce.  The row-parallel GEMM stores each token row's partial
+        # result only into the inbox of the rank that owns the row; the owner sums the partials onto its fp32 residual row,
+        # applies the norm that follows and sends the bf16 row to every rank's operand buffer, which the next GEMM reads from
+        # local memory.  Between layers the residual stream is therefore kept per owner; the last site of a pass sends the fp32
+        # rows to every rank instead.  x and xb live in the communicator's symmetric memory.
+        self.two_shot = (model.tp_size > 1 and getattr(comm, "fused", False) and H % 4 == 0 and H <= 8192
+                         and os.environ.get("RLZ_TWO_SHOT", "1") != "0")
+        if self.two_shot:
+            comm.allocate_two_shot(cfg.num_layers * (1 if cfg.parallel_residual else 2), H, max_tokens)
+            self.x, self.xb = comm.ts_x[:, :H], comm.ts_xb[:, :H]
+        elif model.tp_size > 1 and getattr(comm, "fused", False):
             # measured: at 64 rows the one-shot push loses to NCCL at every world size (2 GPUs 0.76x, 4 GPUs 0.98x,
             # 8 GPUs 0.67x of the NCCL step rate); it is kept for the short batches where latency decides
             self.ll_tokens = min(max_tokens, int(os.environ.get("RLZ_LL_TOKENS", max(8, 64 // model.tp_size))))
             comm.allocate_gemm(2 * cfg.num_layers, H, self.ll_tokens)
         self._site = 0
+        # prompt chunks of one sequence: the page-table row and the chunk position are read from static device buffers, so the
+        # launch sequence of a chunk of T tokens is the same for every sequence and position and is replayed from a CUDA graph
+        self.pt_row = z(max_pages, dt=torch.int32)
+        self._chunk_graphs: dict = {}
+        self._chunk_seen: dict = {}
+        self.chunk_graphs = os.environ.get("RLZ_PREFILL_GRAPHS", "1") != "0"
+
+    def forward_chunk(self, T: int, page_table_row: torch.Tensor, pos0: int) -> torch.Tensor:
+        """Rows 0..T-1 are positions ``pos0 .. pos0+T-1`` of the sequence whose page-table row is given (``tokens`` /
+        ``positions`` / ``page_rows`` must be set).  The first pass of a given T runs launch by launch; full-size chunks (and
+        any T seen twice) are then captured and replayed as one graph, which removes the host's launch work (some hundred
+        launches per pass) from the time to first token - under tensor parallelism the pass is otherwise host-bound."""
+        self.pt_row.copy_(page_table_row, non_blocking=True)
+        g = self._chunk_graphs.get(T)
+        if g is not None:
+            g.replay()
+            return self.x[:T]
+        x = self.forward(T, self.pt_row, shared_table=True, pos0=pos0, pos0_dev=self.positions)
+        seen = self._chunk_seen[T] = self._chunk_seen.get(T, 0) + 1
+        if self.chunk_graphs and len(self._chunk_graphs) < 16 and (T == self.T or seen >= 2):
+            torch.cuda.synchronize(self.model.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.forward(T, self.pt_row, shared_table=True, pos0=pos0, pos0_dev=self.positions)
+            self._chunk_graphs[T] = graph
+        return x
 
     # -- helpers ---------------------------------------------------------------------------
     def _gemm(self, w, x_b, y, T, bias=None, act=ACT_NONE, residual_inplace=False, y_col=0):
@@ -100,6 +136,20 @@ class BatchedForward:
         self.launches_per_pass += 1
         return True
 
+    def _two_shot(self, w, x_b, T, bias, local_partial, next_norm, final: bool) -> None:
+        """x += sum over ranks of (W_shard . x_b + bias [+ local_partial]) by the two-shot all-reduce; then either the bf16
+        operand of the following GEMMs (``next_norm`` = (kind, weight, bias) of the norm that follows) or, at the last site
+        of a pass (``final``), the fp32 residual rows arrive on every rank."""
+        sk = G.choose_splitk(w.n, w.k, T, self.sm_count)
+        p = G.build_gemm_params(w, x_b, self.partial, T, bias=bias, residual=local_partial, splitk=sk, ldy=self.partial.stride(0),
+                                ld_res=self.partial.stride(0) if local_partial is not None else None)
+        self.comm.two_shot_fill(p, self._site, T)
+        G.gemm_launch(p)
+        kind, nw, nb = next_norm if next_norm is not None else (ops.NORM_NONE, None, None)
+        self.comm.two_shot_reduce(p, self._site, T, kind, nw, nb, self.model.cfg.eps, to_xb=not final, push_x=final)
+        self._site += 1
+        self.launches_per_pass += 2
+
     def _row_parallel(self, w, x_b, T, bias):
         """x += W_shard . x_b (+ bias), summed over tensor-parallel ranks."""
         if self.model.tp_size == 1:
@@ -119,7 +169,8 @@ class BatchedForward:
         self.launches_per_pass += 1
 
     # -- the pass ------------------------------------------------------------------------------
-    def forward(self, T: int, page_table: torch.Tensor, shared_table: bool, pos0: Optional[int] = None) -> torch.Tensor:
+    def forward(self, T: int, page_table: torch.Tensor, shared_table: bool, pos0: Optional[int] = None,
+                pos0_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run all layers for rows 0..T-1 (``tokens`` / ``positions`` / ``page_rows`` must be set).
         ``page_table``: ``[max_pages]`` shared by all rows (prefill) or ``[T, max_pages]``.
         ``pos0``: rows are the consecutive positions ``pos0 .. pos0+T-1`` of one sequence (a prompt chunk);
@@ -137,8 +188,12 @@ class BatchedForward:
         x, xb, qkv = self.x[:T], self.xb[:T], self.qkv[:T]
         ops.embed(m.embed_table, m.embed_qtype, m.embed_row_bytes, H, cfg.vocab_size, self.tokens[:T], self.x, m.pos_table, self.positions)
         self.launches_per_pass += 1
+        ts = self.two_shot
         for l, L in enumerate(m.layers):
-            ops.norm_bf16(x, xb, L.attn_norm_w, L.attn_norm_b, norm_t, cfg.eps)
+            nxt = m.layers[l + 1] if l + 1 < len(m.layers) else None
+            next_attn_norm = (norm_t, nxt.attn_norm_w, nxt.attn_norm_b) if nxt is not None else None
+            if not ts or l == 0:                               # two-shot: the previous layer's reduce wrote this layer's operand
+                ops.norm_bf16(x, xb, L.attn_norm_w, L.attn_norm_b, norm_t, cfg.eps)
             if L.qkv is not None:                              # one GEMM over the fused rows: fuller waves, no split-K zero fill
                 self._gemm(L.qkv, xb, self.qkv, T, bias=L.qkv_b, y_col=0)
             else:
@@ -160,7 +215,7 @@ class BatchedForward:
             ops.kv_append(qkv[:, qd:], qkv[:, qd + kvd:], self.k_cache[l], self.v_cache[l], self.positions[:T], self.page_rows[:T], m.kv_heads, hd)
             if pos0 is not None and shared_table and T >= self.flash_min_tokens and self.flash_ok and (L.o_in_off * 2) % 16 == 0:
                 ops.attn_prefill(self.qkv, self.attn_b[:, L.o_in_off:], self.k_cache[l], self.v_cache[l], page_table, T, pos0, m.heads, m.kv_heads, hd,
-                                 q_off=0, window=cfg.sliding_window or 0)       # bf16 result, read directly by the o_proj GEMM
+                                 q_off=0, window=cfg.sliding_window or 0, pos0_dev=pos0_dev)       # bf16 result, read directly by the o_proj GEMM
                 self.launches_per_pass += 3
             else:
                 ops.attn_decode_launch(ops.build_attn_decode_params(
@@ -170,16 +225,25 @@ class BatchedForward:
                     window=cfg.sliding_window or 0))
                 ops.to_bf16(self.attn[:T], self.attn_b[:T])
                 self.launches_per_pass += 4
-            self._row_parallel(L.o, self.attn_b[:T, : L.o.k], T, L.o_b)
+            if ts and cfg.parallel_residual:
+                self._gemm(L.o, self.attn_b[:T, : L.o.k], self.partial, T, bias=L.o_b)      # stays local: the down projection adds it before the push
+            elif ts:
+                self._two_shot(L.o, self.attn_b[:T, : L.o.k], T, L.o_b, None, (norm_t, L.ffn_norm_w, L.ffn_norm_b), final=False)
+            else:
+                self._row_parallel(L.o, self.attn_b[:T, : L.o.k], T, L.o_b)
             act_dst = self.act_b[:, L.down_in_off:]
             if cfg.parallel_residual:
                 if not up_fused:
                     ops.swiglu_bf16(self.gate[:T], None, self.act_b[:T, L.down_in_off:], act_code)
                     self.launches_per_pass += 1
-                self._row_parallel(L.down, self.act_b[:T, : L.down.k], T, L.down_b)
+                if ts:
+                    self._two_shot(L.down, self.act_b[:T, : L.down.k], T, L.down_b, self.partial, next_attn_norm, final=nxt is None)
+                else:
+                    self._row_parallel(L.down, self.act_b[:T, : L.down.k], T, L.down_b)
             else:
-                ops.norm_bf16(x, xb, L.ffn_norm_w, L.ffn_norm_b, norm_t, cfg.eps)
-                self.launches_per_pass += 1
+                if not ts:
+                    ops.norm_bf16(x, xb, L.ffn_norm_w, L.ffn_norm_b, norm_t, cfg.eps)
+                    self.launches_per_pass += 1
                 if cfg.gated_ffn:
                     # act(gate) in fp32 from the first GEMM's epilogue; the second multiplies it in and writes the bf16 operand
                     fused = G.choose_splitk(L.up.n, L.up.k, T, self.sm_count) == 1 and G.choose_splitk(L.gate.n, L.gate.k, T, self.sm_count) == 1
@@ -195,5 +259,8 @@ class BatchedForward:
                     self._gemm(L.up, xb, self.gate, T, bias=L.up_b)
                     ops.swiglu_bf16(self.gate[:T], None, self.act_b[:T, L.down_in_off:], act_code)
                     self.launches_per_pass += 1
-                self._row_parallel(L.down, self.act_b[:T, : L.down.k], T, L.down_b)
+                if ts:
+                    self._two_shot(L.down, self.act_b[:T, : L.down.k], T, L.down_b, None, next_attn_norm, final=nxt is None)
+                else:
+                    self._row_parallel(L.down, self.act_b[:T, : L.down.k], T, L.down_b)
         return x

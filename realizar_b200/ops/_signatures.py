@@ -61,7 +61,7 @@ class AttnPrefillParams(Structure):
     _fields_ = [("qkv", c_void_p), ("out", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p), ("page_table", c_void_p),
                 ("ld_qkv", c_int64), ("ld_out", c_int64), ("n_heads", c_int32), ("n_kv_heads", c_int32), ("head_dim", c_int32),
                 ("q_off", c_int32), ("n_tokens", c_int32), ("pos0", c_int32), ("window", c_int32), ("kv_q8", c_int32), ("scale", c_float),
-                ("out_bf16", c_int32)]
+                ("out_bf16", c_int32), ("pos0_ptr", c_void_p)]
 
 
 class SampleParams(Structure):
@@ -75,7 +75,18 @@ class GemmParams(Structure):
                 ("X", c_void_p), ("ldx", c_int64), ("Y", c_void_p), ("ldy", c_int64), ("bias", c_void_p), ("residual", c_void_p),
                 ("ld_res", c_int64), ("act", c_int32), ("splitk", c_int32), ("atomic_out", c_int32), ("_pad", c_int32),
                 ("ar_inbox", c_void_p * 8), ("ar_epoch", c_void_p), ("ar_row_pairs", c_int64), ("ar_rank", c_int32), ("ar_world", c_int32),
-                ("ar_rows", c_int32), ("ar_enabled", c_int32), ("ar_site", c_int32), ("ar_nsites", c_int32), ("ar_splits", c_int32), ("flags", c_int32)]
+                ("ar_rows", c_int32), ("ar_enabled", c_int32), ("ar_site", c_int32), ("ar_nsites", c_int32), ("ar_splits", c_int32), ("flags", c_int32),
+                ("rs_flags", c_void_p * 8), ("rs_own_rows", c_int32), ("rs_ntiles", c_int32), ("rs_mtiles", c_int32), ("_pad2", c_int32)]
+
+
+class RsReduce(Structure):
+    _fields_ = [("inbox", c_void_p), ("flags", c_void_p), ("ag_flags", c_void_p * AR_MAX_RANKS), ("xb", c_void_p * AR_MAX_RANKS),
+                ("xpeer", c_void_p * AR_MAX_RANKS), ("x", c_void_p), ("nw", c_void_p), ("nb", c_void_p), ("epoch", c_void_p),
+                ("status", c_void_p), ("spin_limit", c_int64), ("ldx", c_int64), ("ldxb", c_int64), ("ld_in", c_int64),
+                ("rank", c_int32), ("world", c_int32), ("splits_stride", c_int32), ("splits_used", c_int32), ("rows_cap", c_int32),
+                ("own_rows", c_int32), ("own_cap", c_int32), ("tokens", c_int32), ("n", c_int32), ("nt", c_int32), ("n_tiles", c_int32),
+                ("ntiles_cap", c_int32), ("mtiles_cap", c_int32), ("site", c_int32), ("nsites", c_int32), ("norm", c_int32),
+                ("push_x", c_int32), ("wait_ag", c_int32), ("eps", c_float), ("_pad", c_int32)]
 
 
 class StepOp(Structure):
@@ -119,6 +130,8 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_device_error.argtypes = [c_int]
     lib.rlz_gemm_kquant.argtypes = [POINTER(GemmParams), c_void_p]
     lib.rlz_gemm_error.argtypes = [c_int]
+    lib.rlz_gemm_plan.argtypes = [POINTER(GemmParams), POINTER(c_int), POINTER(c_int), POINTER(c_int)]
+    lib.rlz_rs_reduce.argtypes = [POINTER(RsReduce), c_void_p]
     lib.rlz_gemm_trace_enable.argtypes = [c_int]
     lib.rlz_gemm_trace_read.argtypes = [c_void_p, c_int]
     lib.rlz_symm_alloc.argtypes = [ctypes.c_ulonglong, POINTER(c_void_p), c_void_p]

@@ -58,6 +58,13 @@ def build_gemm_params(w: DeviceWeight, x: torch.Tensor, y: torch.Tensor, m: int,
     return p
 
 
+def gemm_plan(p: S.GemmParams):
+    """(tokens per CTA, weight rows per CTA, K splits) the launcher will use for this description."""
+    nt, rows, sk = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    check(lib().rlz_gemm_plan(ctypes.byref(p), ctypes.byref(nt), ctypes.byref(rows), ctypes.byref(sk)), "gemm_plan")
+    return nt.value, rows.value, sk.value
+
+
 def gemm_launch(p: S.GemmParams) -> None:
     check(lib().rlz_gemm_kquant(ctypes.byref(p), stream_ptr()), "gemm_kquant")
 

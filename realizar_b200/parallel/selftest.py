@@ -75,6 +75,16 @@ def main(argv=None) -> int:
             cos2 = float(ll @ wl / (np.linalg.norm(ll) * np.linalg.norm(wl)))
             results[mode]["cos_long"] = cos2
             ok &= cos2 > 0.99 and (comm.check_status() if hasattr(comm, "check_status") else 0) == 0
+            # multi-token verification with more rows than max_batch: several head passes (and candidate exchanges) in one call
+            eng.open_slot(0, 64)
+            eng.prefill(0, prompt)
+            ver = eng.forward_tokens(0, [5, 9, 13, 2, 8])
+            eng.close_slot(0)
+            v = torch.tensor(ver, device=dev)
+            v0 = v.clone()
+            dist.broadcast(v0, 0)
+            results[mode]["verify"] = ver
+            ok &= bool((v == v0).all()) and (comm.check_status() if hasattr(comm, "check_status") else 0) == 0
         t = torch.tensor(toks, device=dev)
         t0 = t.clone()
         dist.broadcast(t0, 0)

@@ -26,6 +26,18 @@ from .. import ops
 from ..ops import _signatures as S
 
 
+class _RawDeviceMemory:
+    """CUDA array interface over a raw device address (memory owned by a SymmetricBuffer)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def _device_view(ptr: int, nbytes: int, device) -> torch.Tensor:
+    """uint8 tensor over ``nbytes`` of device memory at ``ptr`` (no copy, no ownership)."""
+    return torch.as_tensor(_RawDeviceMemory(ptr, nbytes), device=device)
+
+
 class SymmetricBuffer:
     """A zero-initialised device buffer of ``nbytes`` on every rank, mapped into every other rank
     of the group through CUDA IPC.  ``ptrs[r]`` is the address of rank r's buffer in this process."""
@@ -177,6 +189,76 @@ class FusedTpComm(NcclTpComm):
                                           self.world * self.g_splits, self.g_rows, self.g_n, site, self.g_sites, tokens, n, x.data_ptr(),
                                           x.stride(0), ops.stream_ptr()), "ll_reduce")
 
+    # -- two-shot all-reduce of row-parallel GEMMs: reduce-scatter by row ownership, owner-side reduce + norm, all-gather ----
+    def allocate_two_shot(self, n_sites: int, n: int, max_tokens: int, splits: int = 2) -> None:
+        """Symmetric memory for the two-shot all-reduce of row-parallel GEMMs with up to ``max_tokens`` x ``n`` outputs at
+        ``n_sites`` call sites per pass: the reduce-scatter inbox and tile flags, the all-gather flags, and the two buffers
+        that finished rows are sent to - the bf16 operand ``xb`` and the fp32 residual stream ``x`` (views in ``ts_xb`` /
+        ``ts_x``).  Token row t is owned by rank ``t // own_rows`` with ``own_rows = ceil(tokens / world)`` per call."""
+        if n_sites > 256:
+            raise ValueError("at most 256 all-reduce sites per pass")
+        w = self.world
+        a256 = lambda v: (v + 255) // 256 * 256
+        self.ts_n = (n + 3) // 4 * 4
+        self.ts_tokens, self.ts_sites, self.ts_splits = max_tokens, n_sites, splits
+        self.ts_own_cap = -(-max_tokens // w)
+        self.ts_ntiles, self.ts_mtiles = -(-n // 128), -(-max_tokens // 32)
+        self._ts_off_inbox = 0
+        off = a256(2 * w * splits * self.ts_own_cap * self.ts_n * 4)
+        self._ts_off_flags = off
+        off += a256(2 * w * splits * self.ts_ntiles * self.ts_mtiles * 4)
+        self._ts_off_ag = off
+        off += a256(w * self.ts_own_cap * 4)
+        self._ts_off_x = off
+        off += a256(max_tokens * self.ts_n * 4)
+        self._ts_off_xb = off
+        off += a256(max_tokens * self.ts_n * 2)
+        self.tsbuf = SymmetricBuffer(off, self.rank, w, self.group)
+        base = self.tsbuf.ptrs[self.rank]
+        self.ts_x = _device_view(base + self._ts_off_x, max_tokens * self.ts_n * 4, self.device).view(torch.float32).view(max_tokens, self.ts_n)
+        self.ts_xb = _device_view(base + self._ts_off_xb, max_tokens * self.ts_n * 2, self.device).view(torch.bfloat16).view(max_tokens, self.ts_n)
+
+    def two_shot_fill(self, p: "S.GemmParams", site: int, tokens: int) -> None:
+        """Turn a GEMM launch into the first half of the two-shot all-reduce at call site ``site`` of the pass: every tile
+        goes to the inbox of the rank that owns its token rows, tagged per tile."""
+        if not 0 <= site < self.ts_sites:
+            raise IndexError(f"all-reduce site {site} out of range ({self.ts_sites} reserved)")
+        if tokens > self.ts_tokens or p.n > self.ts_n:
+            raise ValueError("GEMM exceeds the reserved two-shot buffers")
+        for r in range(self.world):
+            p.ar_inbox[r] = self.tsbuf.ptrs[r] + self._ts_off_inbox
+            p.rs_flags[r] = self.tsbuf.ptrs[r] + self._ts_off_flags
+        p.ar_epoch = self.epoch.data_ptr()
+        p.ar_row_pairs, p.ar_rank, p.ar_world, p.ar_rows, p.ar_enabled = self.ts_n, self.rank, self.world, self.ts_own_cap, 2
+        p.ar_site, p.ar_nsites, p.ar_splits = site, self.ts_sites, self.ts_splits
+        p.rs_own_rows, p.rs_ntiles, p.rs_mtiles = -(-tokens // self.world), self.ts_ntiles, self.ts_mtiles
+        p.splitk = max(1, min(p.splitk, self.ts_splits))
+
+    def two_shot_reduce(self, p: "S.GemmParams", site: int, tokens: int, norm: int, nw, nb, eps: float, to_xb: bool, push_x: bool,
+                        wait: bool = True) -> None:
+        """Second half, for the GEMM described by ``p`` (after ``two_shot_fill``): the owner of each token row sums the
+        partial rows onto its fp32 residual row, applies the norm that follows and sends the bf16 row to every rank's
+        ``ts_xb`` (``to_xb``) and / or the fp32 row to every rank's ``ts_x`` (``push_x``); returns, on the stream, once the
+        rows of all owners have arrived on this rank (``wait``)."""
+        from ..ops import gemm as G
+        nt, rows, sk = G.gemm_plan(p)
+        c = S.RsReduce()
+        base = self.tsbuf.ptrs[self.rank]
+        c.inbox, c.flags = base + self._ts_off_inbox, base + self._ts_off_flags
+        for r in range(self.world):
+            c.ag_flags[r] = self.tsbuf.ptrs[r] + self._ts_off_ag
+            c.xb[r] = self.tsbuf.ptrs[r] + self._ts_off_xb if to_xb else None
+            c.xpeer[r] = self.tsbuf.ptrs[r] + self._ts_off_x
+        c.x, c.nw, c.nb = base + self._ts_off_x, ops.ptr(nw), ops.ptr(nb)
+        c.epoch, c.status, c.spin_limit = self.epoch.data_ptr(), self.status.data_ptr(), self.spin_limit
+        c.ldx = c.ldxb = c.ld_in = self.ts_n
+        c.rank, c.world, c.splits_stride, c.splits_used = self.rank, self.world, self.ts_splits, sk
+        c.rows_cap = c.own_cap = self.ts_own_cap
+        c.own_rows, c.tokens, c.n, c.nt = -(-tokens // self.world), tokens, p.n, nt
+        c.n_tiles, c.ntiles_cap, c.mtiles_cap = -(-p.n // rows), self.ts_ntiles, self.ts_mtiles
+        c.site, c.nsites, c.norm, c.push_x, c.wait_ag, c.eps = site, self.ts_sites, norm, 1 if push_x else 0, 1 if wait else 0, eps
+        ops.check(ops.lib().rlz_rs_reduce(ctypes.byref(c), ops.stream_ptr()), "rs_reduce")
+
     def begin_step(self) -> None:
         ops.check(ops.lib().rlz_epoch_bump(self.epoch.data_ptr(), ops.stream_ptr()), "epoch_bump")
 
@@ -210,6 +292,10 @@ class FusedTpComm(NcclTpComm):
         if getattr(self, "gbuf", None) is not None:
             self.gbuf.close()
             self.gbuf = None
+        if getattr(self, "tsbuf", None) is not None:
+            self.ts_x = self.ts_xb = None
+            self.tsbuf.close()
+            self.tsbuf = None
 
 
 def make_tp_comm(rank: int, world: int, device, mode: str = "fused", group=None) -> TpCommBase:

@@ -426,7 +426,7 @@ class DecodeEngine:
             bf.tokens[:T].copy_(toks[c0:c0 + T], non_blocking=True)
             bf.positions[:T].copy_(pos, non_blocking=True)
             bf.page_rows[:T].copy_(rows, non_blocking=True)
-            x = bf.forward(T, self.buf.page_table[slot], shared_table=True, pos0=pos0 + c0)
+            x = bf.forward_chunk(T, self.buf.page_table[slot], pos0 + c0)
             x_last = x[T - 1]
         self.buf.x[slot].copy_(x_last)
         if not self.cfg.greedy_only:
@@ -461,7 +461,7 @@ class DecodeEngine:
         bf.tokens[:n].copy_(torch.as_tensor(list(tokens), dtype=torch.int32), non_blocking=True)
         bf.positions[:n].copy_(pos, non_blocking=True)
         bf.page_rows[:n].copy_(torch.tensor([pages[p // PAGE] for p in range(pos0, pos0 + n)], dtype=torch.int32), non_blocking=True)
-        x = bf.forward(n, self.buf.page_table[slot], shared_table=True, pos0=pos0)
+        x = bf.forward_chunk(n, self.buf.page_table[slot], pos0)
         out: List[int] = []
         B = self.cfg.max_batch
         fused = self.comm is not None and getattr(self.comm, "fused", False)

@@ -125,6 +125,93 @@ def test_gemm_all_reduce_push_and_reduce_two_emulated_ranks(cuda_device):
     assert float(torch.ones(4, device="cuda").sum()) == 4.0     # the context is still usable
 
 
+@pytest.mark.parametrize("m,k,splitk", [(40, 512, 1), (70, 512, 2), (300, 768, 1)])
+def test_gemm_two_shot_all_reduce_two_emulated_ranks(cuda_device, m, k, splitk):
+    """Two-shot all-reduce of a row-parallel GEMM with two ranks emulated on one GPU, one after the other: both GEMMs store
+    their tiles into the inboxes of the row owners (ownership, tile flags), then each owner's reduce kernel sums them onto
+    its residual rows, applies the following norm and writes the bf16 rows into both ranks' operand buffers.  The final wait
+    for the peers' rows is off (a kernel must not wait for a later launch of the same GPU); a last call with a tag nobody
+    wrote shows that the bounded waits give up and report."""
+    import ctypes
+    from realizar_b200 import ops
+    from realizar_b200.ops import gemm as G
+    from realizar_b200.ops import _signatures as S
+    n, world, splits, site, nsites = 384, 2, 2, 1, 4
+    own_rows = -(-m // world)
+    own_cap, ntiles, mtiles = own_rows + 3, -(-n // 128), -(-m // 32) + 1
+    ws = [_weight(n, k, QType.Q4_K if k % 256 == 0 else QType.BF16, 40 + r) for r in range(world)]
+    xs = [torch.randn(m, k, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    local = [torch.randn(m, n, device="cuda") * 0.1 for _ in range(world)]          # each rank's local partial, added before the push
+    inbox = [torch.zeros(2 * world * splits * own_cap * n, device="cuda") for _ in range(world)]
+    flags = [torch.zeros(2 * world * splits * ntiles * mtiles, dtype=torch.int32, device="cuda") for _ in range(world)]
+    ag = [torch.zeros(world * own_cap, dtype=torch.int32, device="cuda") for _ in range(world)]
+    x0 = torch.randn(m, n, device="cuda")
+    xres = [x0.clone() for _ in range(world)]
+    xb = [torch.zeros(m, n, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    epoch = torch.tensor([7], dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    bias = torch.randn(n, device="cuda")
+    gamma, beta = torch.rand(n, device="cuda") + 0.5, torch.randn(n, device="cuda") * 0.1
+    dummy = torch.zeros(m, n, device="cuda")
+    plans = []
+    for r in range(world):
+        p = G.build_gemm_params(ws[r][0], xs[r], dummy, m, bias=bias if r == 0 else None, residual=local[r], splitk=splitk)
+        for q in range(world):
+            p.ar_inbox[q], p.rs_flags[q] = inbox[q].data_ptr(), flags[q].data_ptr()
+        p.ar_epoch, p.ar_row_pairs, p.ar_rank, p.ar_world, p.ar_rows, p.ar_enabled = epoch.data_ptr(), n, r, world, own_cap, 2
+        p.ar_site, p.ar_nsites, p.ar_splits = site, nsites, splits
+        p.rs_own_rows, p.rs_ntiles, p.rs_mtiles = own_rows, ntiles, mtiles
+        G.gemm_launch(p)
+        plans.append(p)
+    torch.cuda.synchronize()
+    assert ops.lib().rlz_gemm_error(0) == 0 and float(dummy.abs().max()) == 0.0
+
+    def reduce(r, push_x, to_xb, wait, limit=1000):
+        nt, rows, sk = G.gemm_plan(plans[r])
+        c = S.RsReduce()
+        c.inbox, c.flags = inbox[r].data_ptr(), flags[r].data_ptr()
+        for q in range(world):
+            c.ag_flags[q], c.xpeer[q] = ag[q].data_ptr(), xres[q].data_ptr()
+            c.xb[q] = xb[q].data_ptr() if to_xb else None
+        c.x, c.nw, c.nb, c.epoch, c.status, c.spin_limit = xres[r].data_ptr(), gamma.data_ptr(), beta.data_ptr(), epoch.data_ptr(), status.data_ptr(), limit
+        c.ldx = c.ldxb = c.ld_in = n
+        c.rank, c.world, c.splits_stride, c.splits_used, c.rows_cap, c.own_rows, c.own_cap = r, world, splits, sk, own_cap, own_rows, own_cap
+        c.tokens, c.n, c.nt, c.n_tiles, c.ntiles_cap, c.mtiles_cap = m, n, nt, -(-n // rows), ntiles, mtiles
+        c.site, c.nsites, c.norm, c.push_x, c.wait_ag, c.eps = site, nsites, ops.NORM_LAYER, int(push_x), int(wait), 1e-5
+        ops.check(ops.lib().rlz_rs_reduce(ctypes.byref(c), ops.stream_ptr()), "rs_reduce")
+        torch.cuda.synchronize()
+
+    for r in range(world):
+        reduce(r, push_x=True, to_xb=True, wait=False)
+    assert int(status.item()) == 0
+    ref = x0.cpu() + bias.cpu() + sum(local[r].cpu() + xs[r].float().cpu() @ ws[r][1].to(torch.bfloat16).float().T for r in range(world))
+    refb = torch.nn.functional.layer_norm(ref, (n,), gamma.cpu(), beta.cpu(), 1e-5)
+    for q in range(world):                                    # fp32 rows and bf16 rows of BOTH owners arrived on every rank
+        assert float((xres[q].cpu() - ref).abs().max() / ref.abs().max()) < 2e-2
+        assert float((xb[q].float().cpu() - refb).abs().max() / refb.abs().max()) < 3e-2
+    assert torch.equal(xres[0], xres[1]) and torch.equal(xb[0], xb[1])
+    for q in range(world):                                    # every owned row published its tag to every rank
+        got = ag[q].reshape(world, own_cap)
+        for o in range(world):
+            cnt = max(0, min(own_rows, m - o * own_rows))
+            assert bool((got[o, :cnt] == 7 * 256 + site).all()) and bool((got[o, cnt:] == 0).all())
+    # now that both owners have published, the wait for the peers' rows passes
+    xres[0].copy_(x0)
+    reduce(0, push_x=False, to_xb=False, wait=True)
+    assert int(status.item()) == 0
+    # waits that cannot complete: a new epoch that no GEMM has written (tile flags: 2004), then rows nobody gathers (2005 overrides)
+    epoch.fill_(9)
+    reduce(0, push_x=False, to_xb=False, wait=False, limit=50)
+    assert int(status.item()) == 2004
+    status.zero_()
+    epoch.fill_(7)
+    ag[0].zero_()
+    ag[1].zero_()
+    reduce(1, push_x=False, to_xb=False, wait=True, limit=50)          # rank 1 publishes its own rows, rank 0's never arrive
+    assert int(status.item()) == 2005
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0     # the context is still usable
+
+
 @pytest.mark.parametrize("qt", [QType.Q4_K, QType.Q6_K, QType.Q5_K, QType.BF16])
 def test_gemm_wide_row_tiles(cuda_device, qt):
     """256-row CTAs (two TMEM accumulators) give the same result as 128-row CTAs, including ragged edges."""
