@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 import time
 from pathlib import Path
@@ -45,6 +46,9 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--demo", action="store_true"); s.add_argument("--max-batch", type=int, default=4); s.add_argument("--max-seq-len", type=int, default=4096)
     s.add_argument("--gpu", dest="gpu", action="store_true", default=None); s.add_argument("--no-gpu", dest="gpu", action="store_false")
     s.add_argument("--kv-dtype", choices=["bf16", "q8"], default="bf16"); s.add_argument("--no-warmup", action="store_true"); s.add_argument("--classical", default=None, help="classical-ML .apr model behind /v1/predict")
+    s.add_argument("--tp-comm", choices=["fused", "nccl"], default="fused", help="tensor parallel (under torch.distributed.run): in-kernel collectives or NCCL")
+    s.add_argument("--draft-layers", type=int, default=0, help="self-speculative decoding for lone greedy streams: layers in the draft (0 = off)")
+    s.add_argument("--prefill-chunk", type=int, default=256, help="prompt tokens run between two decode steps")
     l = sub.add_parser("list", help="models in the local store"); l.add_argument("--format", choices=["table", "json"], default="table")
     for name in ("pull", "push"):
         q = sub.add_parser(name, help=f"{name} a model ({'needs a network' })"); q.add_argument("model")
@@ -58,6 +62,12 @@ def build_parser() -> argparse.ArgumentParser:
     bs.add_argument("--url", default=None, help="running server; default: load the model in-process"); bs.add_argument("--model", default=None)
     bs.add_argument("--requests", type=int, default=200); bs.add_argument("--rate", type=float, default=20.0); bs.add_argument("--concurrency", type=int, default=256)
     bs.add_argument("--prompt-tokens", type=int, default=64); bs.add_argument("--max-tokens", type=int, default=32); bs.add_argument("--max-batch", type=int, default=64)
+    bs.add_argument("--prompt-tokens-max", type=int, default=0, help="> --prompt-tokens: prompt lengths uniform in that range")
+    bs.add_argument("--prompt-chars", action="store_true", help="count prompt length in characters (byte-level tokenizers: tokens)")
+    bs.add_argument("--temperature", type=float, default=0.0); bs.add_argument("--top-p", type=float, default=1.0)
+    bs.add_argument("--http", action="store_true", help="serve the in-process model on a local port and drive it over real HTTP")
+    bs.add_argument("--port", type=int, default=18080); bs.add_argument("--max-seq-len", type=int, default=4096)
+    bs.add_argument("--tp-comm", choices=["fused", "nccl"], default="fused"); bs.add_argument("--prefill-chunk", type=int, default=256)
     bs.add_argument("--output", "-o", default=None)
     bc = sub.add_parser("bench-compare"); bc.add_argument("file1"); bc.add_argument("file2"); bc.add_argument("--threshold", type=float, default=5.0)
     br = sub.add_parser("bench-regression"); br.add_argument("baseline"); br.add_argument("current"); br.add_argument("--strict", action="store_true")
@@ -142,8 +152,12 @@ def cmd_chat(a, stdin=None, stdout=None) -> int:
     return 0
 
 
-def build_app_state(model: Optional[str], use_gpu: Optional[bool], max_batch: int, max_seq_len: int, warmup: bool = True, kv_dtype: str = "bf16"):
-    """Load a model and wire engine -> continuous-batching loop -> API state."""
+def build_app_state(model: Optional[str], use_gpu: Optional[bool], max_batch: int, max_seq_len: int, warmup: bool = True, kv_dtype: str = "bf16",
+                    tp_comm: str = "fused", draft_layers: int = 0, prefill_chunk: int = 256):
+    """Load a model and wire engine -> continuous-batching loop -> API state.  Under ``torch.distributed.run`` with several
+    processes the engine is tensor parallel: rank 0 returns the state, the other ranks serve rank 0's engine calls until it
+    shuts down and then exit.  ``draft_layers`` > 0 turns on self-speculative decoding for lone greedy streams (that many
+    evenly spaced layers form the draft); ``prefill_chunk`` bounds the prompt tokens run between two decode steps."""
     import torch
     from .formats.detect import load_model
     from .infer import build_template, build_tokenizer
@@ -169,16 +183,38 @@ def build_app_state(model: Optional[str], use_gpu: Optional[bool], max_batch: in
         tok_override = None
     gpu = torch.cuda.is_available() if use_gpu is None else use_gpu
     msl = min(max_seq_len, w.config.context_length)
-    if gpu:
+    tp_world = int(os.environ.get("WORLD_SIZE", "1")) if gpu else 1
+    if gpu and tp_world > 1:
+        # one process per GPU under torch.distributed.run: rank 0 serves, the other ranks follow its engine calls and never return
+        from .parallel.tp_serving import TpLeaderEngine, follower_loop, init_tp, leave_group
+        from .runtime.engine import DecodeEngine, EngineConfig
+        rank, world, dev, comm, group = init_tp(tp_comm)
+        inner = DecodeEngine(w, EngineConfig(max_batch=max_batch, max_seq_len=msl, kv_dtype=kv_dtype), device=dev, comm=comm, tp_rank=rank, tp_size=world)
+        if rank != 0:
+            calls = follower_loop(inner, group)
+            leave_group(inner, comm)
+            print(f"rank {rank}: served {calls} engine calls", file=sys.stderr)
+            raise SystemExit(0)
+        eng = TpLeaderEngine(inner, group, comm)
+    elif gpu:
         from .runtime.engine import DecodeEngine, EngineConfig
         eng = DecodeEngine(w, EngineConfig(max_batch=max_batch, max_seq_len=msl, kv_dtype=kv_dtype))
     else:
         from .runtime.cpu_engine import CpuEngineConfig, CpuSlotEngine
         eng = CpuSlotEngine(w, CpuEngineConfig(max_batch=min(max_batch, 2), max_seq_len=msl))
-    serving = ServingEngine(eng, SchedulerConfig(max_batch=eng.cfg.max_batch, max_seq_len=eng.cfg.max_seq_len)).start()
+    layers = None
+    if draft_layers and gpu:
+        n_layers = w.config.num_layers
+        layers = tuple(sorted(set(range(0, n_layers, max(1, n_layers // max(1, draft_layers)))) | {n_layers - 1}))
+    serving = ServingEngine(eng, SchedulerConfig(max_batch=eng.cfg.max_batch, max_seq_len=eng.cfg.max_seq_len, prefill_chunk=prefill_chunk,
+                                                 token_budget=max(prefill_chunk, eng.cfg.max_batch) + eng.cfg.max_batch),
+                            draft_layers=layers).start()
     st = AppState(serving, tok_override or build_tokenizer(w), build_template(w, path.stem), path.stem, None if tok_override else w.config.eos_token_id,
                   compute_mode="gpu" if gpu else "cpu",
                   context_length=eng.cfg.max_seq_len)
+    if gpu:
+        from .runtime.scorer import scorer_for
+        st.scorer = scorer_for(serving)
     if warmup:
         res = ModelWarmer(WarmupConfig(iterations=2)).warm(lambda p, n: serving.generate(p, timeout=120.0, max_tokens=n), w.config.vocab_size, ModelHealth())
         print(f"warm-up: {'ok' if res.success else 'FAILED ' + str(res.error)} ({res.total_ms:.0f} ms)", file=sys.stderr)
@@ -187,13 +223,20 @@ def build_app_state(model: Optional[str], use_gpu: Optional[bool], max_batch: in
 
 def cmd_serve(a) -> int:
     from .serving.api import serve
-    st = build_app_state(None if a.demo else a.model, a.gpu, a.max_batch, a.max_seq_len, warmup=not a.no_warmup, kv_dtype=a.kv_dtype)
+    st = build_app_state(None if a.demo else a.model, a.gpu, a.max_batch, a.max_seq_len, warmup=not a.no_warmup, kv_dtype=a.kv_dtype,
+                         tp_comm=a.tp_comm, draft_layers=a.draft_layers, prefill_chunk=a.prefill_chunk)
     if a.classical:
         from .serving.classical import ClassicalModel, ClassicalServeState
         data = Path(a.classical).read_bytes()
         st.classical = ClassicalServeState(ClassicalModel.from_apr(data), data)
     print(f"serving '{st.model_name}' ({st.compute_mode}) on http://{a.host}:{a.port}", file=sys.stderr)
-    serve(st, a.host, a.port)
+    try:
+        serve(st, a.host, a.port)
+    finally:
+        if st.serving is not None:
+            st.serving.stop()
+            if hasattr(st.serving.engine, "shutdown"):
+                st.serving.engine.shutdown()                  # tensor parallel: release the follower ranks
     return 0
 
 
@@ -308,16 +351,38 @@ def cmd_bench_serving(a) -> int:
 
 def cmd_bench_load(a) -> int:
     from .utils.loadgen import LoadConfig, run_load
-    cfg = LoadConfig(a.requests, a.rate, a.concurrency, a.prompt_tokens, a.max_tokens)
+    cfg = LoadConfig(a.requests, a.rate, a.concurrency, a.prompt_tokens, a.prompt_tokens_max, a.prompt_chars, a.max_tokens, a.temperature, a.top_p)
     if a.url:
         r = run_load(cfg, url=a.url)
     else:
         from .serving.api import create_app
-        st = build_app_state(a.model, None, a.max_batch, 4096, warmup=a.model is not None)
+        st = build_app_state(a.model, None, a.max_batch, a.max_seq_len, warmup=a.model is not None, tp_comm=a.tp_comm, prefill_chunk=a.prefill_chunk)
         try:
-            r = run_load(cfg, app=create_app(st))
+            app = create_app(st)
+            if a.http:
+                # a real listening socket: uvicorn on a local port in a thread of this process, the load goes through TCP + HTTP
+                import threading
+                import uvicorn
+                server = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=a.port, log_level="warning"))
+                th = threading.Thread(target=server.run, daemon=True)
+                th.start()
+                t_end = time.time() + 30
+                while not server.started and time.time() < t_end:
+                    time.sleep(0.05)
+                try:
+                    r = run_load(cfg, url=f"http://127.0.0.1:{a.port}")
+                finally:
+                    server.should_exit = True
+                    th.join(10)
+                r["transport"] = "http"
+            else:
+                r = run_load(cfg, app=app)
+                r["transport"] = "in-process ASGI"
+            r["engine"] = st.serving.metrics()
         finally:
             st.serving.stop()
+            if hasattr(st.serving.engine, "shutdown"):
+                st.serving.engine.shutdown()                  # tensor parallel: release the follower ranks
     print(json.dumps(r, indent=1))
     if a.output:
         Path(a.output).write_text(json.dumps(r))

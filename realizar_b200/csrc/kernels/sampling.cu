@@ -237,10 +237,95 @@ __global__ void penalties_kernel(float* logits, int64_t ld, int vocab, const int
   }
 }
 
+// The token fed at this step joins the sequence's history ring (what the penalties look at): history[b, position % window] = token.
+__global__ void history_push_kernel(int32_t* history, int window, const int32_t* tokens, const int32_t* positions, int batch) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < batch && positions[b] >= 0) history[(int64_t)b * window + positions[b] % window] = tokens[b];
+}
+
+// Per-sequence logit controls applied in place before the sampling kernel, one CTA per row:
+//   * an additive row (`bias`, used for OpenAI-style logit_bias and, with -inf entries, for grammar / tool-call token masks)
+//     for the rows whose `bias_on` flag is set;
+//   * repetition / presence / frequency penalties over the distinct tokens of the history ring.
+// `index_offset` / `vocab` describe the slice of the vocabulary held in `logits` (vocabulary-sharded heads); bias rows hold
+// the same slice.  Replaces the host-side LogitProcessorChain of the reference (src/generate/mod.rs:107-400).
+__global__ void __launch_bounds__(SAMP_THREADS) logit_controls_kernel(float* logits, int64_t ld, int vocab, int index_offset, const int32_t* history,
+                                                                      int window, const float* repetition, const float* presence, const float* frequency,
+                                                                      const float* bias, int64_t ld_bias, const int32_t* bias_on) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x;
+  float* row = logits + (int64_t)b * ld;
+  if (bias && bias_on && bias_on[b]) {
+    const float* br = bias + (int64_t)b * ld_bias;
+    for (int i = threadIdx.x; i < vocab; i += SAMP_THREADS) row[i] += br[i];
+    __syncthreads();
+  }
+  const float rep = repetition ? repetition[b] : 1.f, pres = presence ? presence[b] : 0.f, freq = frequency ? frequency[b] : 0.f;
+  if (!history || (rep == 1.f && pres == 0.f && freq == 0.f)) return;
+  const int32_t* h = history + (int64_t)b * window;
+  for (int i = threadIdx.x; i < window; i += SAMP_THREADS) {
+    const int tok = h[i];
+    if (tok < index_offset || tok >= index_offset + vocab) continue;
+    int count = 0; bool first = true;
+    for (int j = 0; j < window; ++j) if (h[j] == tok) { ++count; if (j < i) first = false; }
+    if (!first) continue;
+    float v = row[tok - index_offset];
+    if (rep != 1.f) v = v > 0.f ? v / rep : v * rep;
+    v -= pres + freq * (float)count;
+    row[tok - index_offset] = v;
+  }
+}
+
+// Scoring: per row, the pieces of log softmax(logits)[target] over this rank's vocabulary slice [index_offset, index_offset + vocab):
+// out[row] = {max, sum exp(logit - max), logit of the target if it lies in the slice else -inf}.  With one slice the log-probability
+// is out[2] - out[0] - log(out[1]); vocabulary-sharded heads combine the triples of all ranks first.  One CTA per row, one pass for
+// the maximum and one for the sum (the row stays in L2 between them).  Replaces the reference's host-side log-softmax over
+// downloaded logits (src/gguf/cuda/generate_2.rs:590-780).
+__global__ void __launch_bounds__(SAMP_THREADS) logprob_rows_kernel(const float* logits, int64_t ld, int vocab, const int32_t* targets, int index_offset,
+                                                                    float* out) {
+  __shared__ float red[40];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const float* l = logits + (int64_t)row * ld;
+  float m = -INFINITY;
+  for (int i = tid; i < vocab; i += SAMP_THREADS) m = fmaxf(m, l[i]);
+  m = block_max(m, red);
+  float s = 0.f;
+  for (int i = tid; i < vocab; i += SAMP_THREADS) s += __expf(l[i] - m);
+  s = block_sum(s, red);
+  if (tid == 0) {
+    const int t = targets[row] - index_offset;
+    out[3 * row + 0] = m;
+    out[3 * row + 1] = s;
+    out[3 * row + 2] = (t >= 0 && t < vocab) ? l[t] : -INFINITY;
+  }
+}
+
 }  // namespace rlz
 
 extern "C" {
 using namespace rlz;
+
+int rlz_history_push(int32_t* history, int window, const int32_t* tokens, const int32_t* positions, int batch, void* stream) {
+  if (window < 1 || batch < 1) return -1;
+  return (int)launch(history_push_kernel, dim3((batch + 63) / 64), dim3(64), 0, (cudaStream_t)stream, history, window, tokens, positions, batch);
+}
+
+int rlz_logit_controls(float* logits, long long ld, int vocab, int index_offset, int batch, const int32_t* history, int window, const float* repetition,
+                       const float* presence, const float* frequency, const float* bias, long long ld_bias, const int32_t* bias_on, void* stream) {
+  if (vocab < 1 || batch < 1) return -1;
+  return (int)launch(logit_controls_kernel, dim3(batch), dim3(SAMP_THREADS), 0, (cudaStream_t)stream, logits, (int64_t)ld, vocab, index_offset, history,
+                     window, repetition, presence, frequency, bias, (int64_t)ld_bias, bias_on);
+}
+
+int rlz_logprob_rows(const float* logits, long long ld, int vocab, int rows, const int32_t* targets, int index_offset, float* out, void* stream) {
+  if (vocab < 1 || rows < 1) return -1;
+  return (int)launch(logprob_rows_kernel, dim3(rows), dim3(SAMP_THREADS), 0, (cudaStream_t)stream, logits, (int64_t)ld, vocab, targets, index_offset, out);
+}
 
 int rlz_argmax(const float* logits, long long ld, int vocab, int batch, int32_t* out, float* out_val, int index_offset, void* stream) {
   if (vocab < 1 || batch < 1) return -1;

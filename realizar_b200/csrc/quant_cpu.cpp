@@ -28,13 +28,16 @@ using namespace rlz;
 namespace {
 
 // ------------------------------------------------------------------ thread pool ------
+// Workers spin for a few microseconds on the epoch word before they go to sleep on the condition variable: a decoder
+// issues a couple of hundred small matrix-vector products per token, and a futex wake per product would cost more than
+// the products themselves.
 class Pool {
  public:
   explicit Pool(int n) : n_(std::max(1, n)) {
     for (int i = 1; i < n_; ++i) workers_.emplace_back([this, i] { loop(i); });
   }
   ~Pool() {
-    { std::lock_guard<std::mutex> l(mu_); stop_ = true; ++epoch_; }
+    { std::lock_guard<std::mutex> l(mu_); stop_ = true; epoch_.fetch_add(1, std::memory_order_release); }
     cv_.notify_all();
     for (auto& t : workers_) t.join();
   }
@@ -42,36 +45,50 @@ class Pool {
   // run fn(worker_index) on every worker (including the caller as worker 0)
   void run(const std::function<void(int)>& fn) {
     if (n_ == 1) { fn(0); return; }
-    { std::lock_guard<std::mutex> l(mu_); fn_ = &fn; pending_ = n_ - 1; ++epoch_; }
-    cv_.notify_all();
+    {
+      std::lock_guard<std::mutex> l(mu_);
+      fn_ = &fn;
+      pending_.store(n_ - 1, std::memory_order_relaxed);
+      epoch_.fetch_add(1, std::memory_order_release);
+    }
+    if (sleepers_.load(std::memory_order_acquire) > 0) cv_.notify_all();
     fn(0);
-    std::unique_lock<std::mutex> l(mu_);
-    done_cv_.wait(l, [this] { return pending_ == 0; });
+    for (int spins = 0; pending_.load(std::memory_order_acquire) != 0; ++spins) {
+      if (spins < 20000) cpu_relax(); else std::this_thread::yield();
+    }
     fn_ = nullptr;
   }
  private:
+  static void cpu_relax() {
+#if defined(__x86_64__) || defined(__i386__)
+    __builtin_ia32_pause();
+#endif
+  }
   void loop(int idx) {
     uint64_t seen = 0;
     for (;;) {
-      const std::function<void(int)>* fn;
-      {
+      int spins = 0;
+      while (epoch_.load(std::memory_order_acquire) == seen) {
+        if (++spins < 4000) { cpu_relax(); continue; }
         std::unique_lock<std::mutex> l(mu_);
-        cv_.wait(l, [&] { return epoch_ != seen; });
-        seen = epoch_;
-        if (stop_) return;
-        fn = fn_;
+        sleepers_.fetch_add(1, std::memory_order_release);
+        cv_.wait(l, [&] { return epoch_.load(std::memory_order_acquire) != seen; });
+        sleepers_.fetch_sub(1, std::memory_order_release);
       }
+      seen = epoch_.load(std::memory_order_acquire);
+      if (stop_) return;
+      const std::function<void(int)>* fn = fn_;
       if (fn) (*fn)(idx);
-      { std::lock_guard<std::mutex> l(mu_); if (--pending_ == 0) done_cv_.notify_one(); }
+      pending_.fetch_sub(1, std::memory_order_release);
     }
   }
   int n_;
   std::vector<std::thread> workers_;
   std::mutex mu_;
-  std::condition_variable cv_, done_cv_;
+  std::condition_variable cv_;
   const std::function<void(int)>* fn_ = nullptr;
-  int pending_ = 0;
-  uint64_t epoch_ = 0;
+  std::atomic<int> pending_{0}, sleepers_{0};
+  std::atomic<uint64_t> epoch_{0};
   bool stop_ = false;
 };
 
@@ -520,13 +537,157 @@ float dot_q6k_q8k_avx2(const uint8_t* w, const Q8K* a, int nb) {
   }
   return sumf;
 }
+// Q5_K: as Q4_K with the fifth bit of every weight taken from qh (bit 2j of byte l for sub-block 2j, bit 2j+1 for 2j+1)
+__attribute__((target("avx2,fma")))
+float dot_q5k_q8k_avx2(const uint8_t* w, const Q8K* a, int nb) {
+  const __m256i m4 = _mm256_set1_epi8(0xF), one = _mm256_set1_epi8(1);
+  float sumf = 0;
+  for (int i = 0; i < nb; ++i, w += 176) {
+    const float d = half_bits_to_float(load_u16(w)) * a[i].d, dmin = half_bits_to_float(load_u16(w + 2)) * a[i].d;
+    const __m256i hb = _mm256_loadu_si256((const __m256i*)(w + 16));
+    const uint8_t* q = w + 48; const int8_t* q8 = a[i].qs;
+    __m256i acc = _mm256_setzero_si256(); int summ = 0;
+    for (int j = 0; j < 4; ++j) {
+      uint8_t sc0, m0, sc1, m1; get_scale_min_k4(2 * j, w + 4, &sc0, &m0); get_scale_min_k4(2 * j + 1, w + 4, &sc1, &m1);
+      const __m256i qb = _mm256_loadu_si256((const __m256i*)q);
+      const __m256i h0 = _mm256_slli_epi16(_mm256_and_si256(_mm256_srli_epi16(hb, 2 * j), one), 4);
+      const __m256i h1 = _mm256_slli_epi16(_mm256_and_si256(_mm256_srli_epi16(hb, 2 * j + 1), one), 4);
+      const __m256i lo = _mm256_or_si256(_mm256_and_si256(qb, m4), h0), hi = _mm256_or_si256(_mm256_and_si256(_mm256_srli_epi16(qb, 4), m4), h1);
+      const __m256i a0 = _mm256_loadu_si256((const __m256i*)q8), a1 = _mm256_loadu_si256((const __m256i*)(q8 + 32));
+      __m256i p0 = _mm256_maddubs_epi16(lo, a0), p1 = _mm256_maddubs_epi16(hi, a1);
+      p0 = _mm256_madd_epi16(p0, _mm256_set1_epi16(sc0)); p1 = _mm256_madd_epi16(p1, _mm256_set1_epi16(sc1));
+      acc = _mm256_add_epi32(acc, _mm256_add_epi32(p0, p1));
+      summ += m0 * (a[i].bsums[4 * j] + a[i].bsums[4 * j + 1]) + m1 * (a[i].bsums[4 * j + 2] + a[i].bsums[4 * j + 3]);
+      q += 32; q8 += 64;
+    }
+    sumf += d * hsum8i(acc) - dmin * summ;
+  }
+  return sumf;
+}
+
+// ---- 32-wide blocks (Q4_0 / Q4_1 / Q5_0 / Q5_1 / Q8_0) against Q8_0-quantised activations -----------------------------
+// 16 bytes of nibbles -> 32 bytes: low nibbles (elements 0..15) then high nibbles (16..31)
+__attribute__((target("avx2"))) inline __m256i nibbles32(const uint8_t* qs) {
+  const __m128i q = _mm_loadu_si128((const __m128i*)qs);
+  return _mm256_and_si256(_mm256_set_m128i(_mm_srli_epi16(q, 4), q), _mm256_set1_epi8(0xF));
+}
+// 32 bits -> 32 bytes, 0x10 where the bit is set (the fifth bit of the 5-bit types)
+__attribute__((target("avx2"))) inline __m256i fifth_bits(uint32_t x) {
+  const __m256i shuf = _mm256_set_epi64x(0x0303030303030303LL, 0x0202020202020202LL, 0x0101010101010101LL, 0x0000000000000000LL);
+  const __m256i sel = _mm256_set1_epi64x((long long)0x8040201008040201ULL);
+  const __m256i b = _mm256_and_si256(_mm256_shuffle_epi8(_mm256_set1_epi32((int)x), shuf), sel);
+  return _mm256_and_si256(_mm256_cmpeq_epi8(b, sel), _mm256_set1_epi8(0x10));
+}
+__attribute__((target("avx2,fma")))
+float dot_legacy_q8_0_avx2(int qtype, const uint8_t* w, const Q80A* a, int nb) {
+  const __m256i ones16 = _mm256_set1_epi16(1);
+  __m256 acc = _mm256_setzero_ps();
+  float extra = 0.f;                                       // minimum terms of Q4_1 / Q5_1
+  const int bb = qtype_block_bytes(qtype);
+  for (int i = 0; i < nb; ++i, w += bb) {
+    const __m256i av = _mm256_loadu_si256((const __m256i*)a[i].qs);
+    const float d = half_bits_to_float(load_u16(w));
+    __m256i p;
+    switch (qtype) {
+      case QT_Q8_0: {
+        const __m256i q = _mm256_loadu_si256((const __m256i*)(w + 2));
+        p = _mm256_madd_epi16(_mm256_maddubs_epi16(_mm256_sign_epi8(q, q), _mm256_sign_epi8(av, q)), ones16);
+        break; }
+      case QT_Q4_0: {
+        const __m256i q = nibbles32(w + 2);
+        p = _mm256_madd_epi16(_mm256_sub_epi16(_mm256_maddubs_epi16(q, av), _mm256_maddubs_epi16(_mm256_set1_epi8(8), av)), ones16);
+        break; }
+      case QT_Q5_0: {
+        const __m256i q = _mm256_or_si256(nibbles32(w + 6), fifth_bits((uint32_t)w[2] | ((uint32_t)w[3] << 8) | ((uint32_t)w[4] << 16) | ((uint32_t)w[5] << 24)));
+        p = _mm256_madd_epi16(_mm256_sub_epi16(_mm256_maddubs_epi16(q, av), _mm256_maddubs_epi16(_mm256_set1_epi8(16), av)), ones16);
+        break; }
+      case QT_Q4_1: case QT_Q5_1: {
+        const float m = half_bits_to_float(load_u16(w + 2));
+        const __m256i q = qtype == QT_Q4_1 ? nibbles32(w + 4)
+            : _mm256_or_si256(nibbles32(w + 8), fifth_bits((uint32_t)w[4] | ((uint32_t)w[5] << 8) | ((uint32_t)w[6] << 16) | ((uint32_t)w[7] << 24)));
+        p = _mm256_madd_epi16(_mm256_maddubs_epi16(q, av), ones16);
+        extra += m * a[i].d * (float)hsum8i(_mm256_madd_epi16(_mm256_maddubs_epi16(_mm256_set1_epi8(1), av), ones16));
+        break; }
+      default: return 0.f;
+    }
+    acc = _mm256_fmadd_ps(_mm256_set1_ps(d * a[i].d), _mm256_cvtepi32_ps(p), acc);
+  }
+  return hsum8(acc) + extra;
+}
+
+// ---- AVX-512 VNNI: one dpbusd does the byte products and their 4-wise sums ----------------------------------------------
+// Q4_K: the 64 activation bytes of a group of two sub-blocks are contiguous, so one 512-bit operand holds the low nibbles
+// (sub-block 2j) in its lower half and the high nibbles (2j + 1) in its upper half; the two sub-block scales sit in the
+// matching halves of a multiplier vector.
+__attribute__((target("avx512f,avx512bw,avx512vl,avx512vnni")))
+float dot_q4k_q8k_vnni(const uint8_t* w, const Q8K* a, int nb) {
+  const __m256i m4 = _mm256_set1_epi8(0xF);
+  float sumf = 0;
+  for (int i = 0; i < nb; ++i, w += 144) {
+    const float d = half_bits_to_float(load_u16(w)) * a[i].d, dmin = half_bits_to_float(load_u16(w + 2)) * a[i].d;
+    const uint8_t* q = w + 16; const int8_t* q8 = a[i].qs;
+    __m512i acc = _mm512_setzero_si512(); int summ = 0;
+    for (int j = 0; j < 4; ++j) {
+      uint8_t sc0, m0, sc1, m1; get_scale_min_k4(2 * j, w + 4, &sc0, &m0); get_scale_min_k4(2 * j + 1, w + 4, &sc1, &m1);
+      const __m256i qb = _mm256_loadu_si256((const __m256i*)q);
+      const __m512i wv = _mm512_inserti64x4(_mm512_castsi256_si512(_mm256_and_si256(qb, m4)), _mm256_and_si256(_mm256_srli_epi16(qb, 4), m4), 1);
+      const __m512i p = _mm512_dpbusd_epi32(_mm512_setzero_si512(), wv, _mm512_loadu_si512((const void*)q8));
+      const __m512i scv = _mm512_inserti64x4(_mm512_castsi256_si512(_mm256_set1_epi32(sc0)), _mm256_set1_epi32(sc1), 1);
+      acc = _mm512_add_epi32(acc, _mm512_mullo_epi32(p, scv));
+      summ += m0 * (a[i].bsums[4 * j] + a[i].bsums[4 * j + 1]) + m1 * (a[i].bsums[4 * j + 2] + a[i].bsums[4 * j + 3]);
+      q += 32; q8 += 64;
+    }
+    sumf += d * (float)_mm512_reduce_add_epi32(acc) - dmin * (float)summ;
+  }
+  return sumf;
+}
+// Q6_K: per 128-weight half, four 32-byte operands; (q - 32) . a = q . a - 32 * sum(a), the sums come from the Q8_K block sums
+__attribute__((target("avx512f,avx512bw,avx512vl,avx512vnni")))
+float dot_q6k_q8k_vnni(const uint8_t* w, const Q8K* a, int nb) {
+  const __m256i m4 = _mm256_set1_epi8(0xF), m2 = _mm256_set1_epi8(3);
+  float sumf = 0;
+  for (int i = 0; i < nb; ++i, w += 210) {
+    const uint8_t* ql = w; const uint8_t* qh = w + 128; const int8_t* sc = (const int8_t*)(w + 192);
+    const float d = half_bits_to_float(load_u16(w + 208)) * a[i].d; const int8_t* q8 = a[i].qs;
+    __m256i acc = _mm256_setzero_si256(); int corr = 0;
+    for (int n = 0; n < 2; ++n) {
+      const __m256i l0 = _mm256_loadu_si256((const __m256i*)ql), l1 = _mm256_loadu_si256((const __m256i*)(ql + 32));
+      const __m256i h = _mm256_loadu_si256((const __m256i*)qh);
+      __m256i q[4];
+      q[0] = _mm256_or_si256(_mm256_and_si256(l0, m4), _mm256_slli_epi16(_mm256_and_si256(h, m2), 4));
+      q[1] = _mm256_or_si256(_mm256_and_si256(l1, m4), _mm256_slli_epi16(_mm256_and_si256(_mm256_srli_epi16(h, 2), m2), 4));
+      q[2] = _mm256_or_si256(_mm256_and_si256(_mm256_srli_epi16(l0, 4), m4), _mm256_slli_epi16(_mm256_and_si256(_mm256_srli_epi16(h, 4), m2), 4));
+      q[3] = _mm256_or_si256(_mm256_and_si256(_mm256_srli_epi16(l1, 4), m4), _mm256_slli_epi16(_mm256_and_si256(_mm256_srli_epi16(h, 6), m2), 4));
+      for (int t = 0; t < 4; ++t) {
+        const __m256i p = _mm256_dpbusd_epi32(_mm256_setzero_si256(), q[t], _mm256_loadu_si256((const __m256i*)(q8 + 32 * t)));
+        // lanes 0..3 cover the first 16 weights (scale 2t), lanes 4..7 the second 16 (scale 2t + 1)
+        const __m256i s = _mm256_set_m128i(_mm_set1_epi32(sc[2 * t + 1]), _mm_set1_epi32(sc[2 * t]));
+        acc = _mm256_add_epi32(acc, _mm256_mullo_epi32(p, s));
+        corr += sc[2 * t] * a[i].bsums[8 * n + 2 * t] + sc[2 * t + 1] * a[i].bsums[8 * n + 2 * t + 1];
+      }
+      ql += 64; qh += 32; sc += 8; q8 += 128;
+    }
+    sumf += d * (float)(hsum8i(acc) - 32 * corr);
+  }
+  return sumf;
+}
 bool has_avx2() { static const bool v = __builtin_cpu_supports("avx2") && __builtin_cpu_supports("fma"); return v; }
+bool has_vnni512() {
+  static const bool v = __builtin_cpu_supports("avx512f") && __builtin_cpu_supports("avx512bw") && __builtin_cpu_supports("avx512vl") &&
+                        __builtin_cpu_supports("avx512vnni") && !std::getenv("RLZ_NO_AVX512");
+  return v;
+}
 #else
 bool has_avx2() { return false; }
+bool has_vnni512() { return false; }
 #endif
 
 float dot_legacy_q8_0(int qtype, const uint8_t* w, const Q80A* a, int nb) {
   // legacy 32-element blocks against Q8_0-quantised activations
+#if RLZ_X86
+  if (has_avx2() && (qtype == QT_Q8_0 || qtype == QT_Q4_0 || qtype == QT_Q5_0 || qtype == QT_Q4_1 || qtype == QT_Q5_1))
+    return dot_legacy_q8_0_avx2(qtype, w, a, nb);
+#endif
   float sumf = 0; const int bb = qtype_block_bytes(qtype);
   for (int i = 0; i < nb; ++i, w += bb) {
     const float da = a[i].d; const int8_t* q8 = a[i].qs;
@@ -554,12 +715,18 @@ float dot_kquant(int qtype, const uint8_t* w, const Q8K* a, int nb) {
   switch (qtype) {
     case QT_Q4_K:
 #if RLZ_X86
+      if (has_vnni512()) return dot_q4k_q8k_vnni(w, a, nb);
       if (has_avx2()) return dot_q4k_q8k_avx2(w, a, nb);
 #endif
       return dot_q4k_q8k_scalar(w, a, nb);
-    case QT_Q5_K: return dot_q5k_q8k_scalar(w, a, nb);
+    case QT_Q5_K:
+#if RLZ_X86
+      if (has_avx2()) return dot_q5k_q8k_avx2(w, a, nb);
+#endif
+      return dot_q5k_q8k_scalar(w, a, nb);
     case QT_Q6_K:
 #if RLZ_X86
+      if (has_vnni512()) return dot_q6k_q8k_vnni(w, a, nb);
       if (has_avx2()) return dot_q6k_q8k_avx2(w, a, nb);
 #endif
       return dot_q6k_q8k_scalar(w, a, nb);
@@ -579,6 +746,15 @@ int rlz_block_elems(int qtype) { return qtype_block_elems(qtype); }
 int rlz_block_bytes(int qtype) { return qtype_block_bytes(qtype); }
 int rlz_cpu_threads() { return pool().size(); }
 int rlz_cpu_has_avx2() { return has_avx2() ? 1 : 0; }
+int rlz_cpu_has_avx512_vnni() { return has_vnni512() ? 1 : 0; }
+// which code path a block type's fused dot takes on this host: 0 scalar, 1 AVX2, 2 AVX-512 VNNI
+int rlz_cpu_dot_path(int qtype) {
+  switch (qtype) {
+    case QT_Q4_K: case QT_Q6_K: return has_vnni512() ? 2 : has_avx2() ? 1 : 0;
+    case QT_Q5_K: case QT_Q8_0: case QT_Q4_0: case QT_Q5_0: case QT_Q4_1: case QT_Q5_1: return has_avx2() ? 1 : 0;
+    default: return 0;
+  }
+}
 
 // bytes of one row of `k` elements, or -1 if k is not a multiple of the block size
 int64_t rlz_row_bytes(int qtype, int64_t k) {

@@ -262,6 +262,13 @@ class StepBuffers:
     local_idx: Optional[torch.Tensor] = None     # TP: its global token id
     logits_full: Optional[torch.Tensor] = None   # TP sampling: gathered logits
     act_q: Optional[torch.Tensor] = None         # batch 1: the MLP activation as the int8 block the down-projection launch stages
+    # per-sequence logit controls of sampling plans (None on greedy-only engines)
+    history: Optional[torch.Tensor] = None       # [B, window] ring of recent token ids (-1: empty)
+    repetition: Optional[torch.Tensor] = None    # [B] repetition penalty (1 = off)
+    presence: Optional[torch.Tensor] = None      # [B]
+    frequency: Optional[torch.Tensor] = None     # [B]
+    bias: Optional[torch.Tensor] = None          # [B, vocab] additive row: logit_bias entries, -inf for tokens a grammar forbids
+    bias_on: Optional[torch.Tensor] = None       # [B] int32: row b of `bias` is in use
 
 
 def _is_fast(w: DeviceWeight) -> bool:
@@ -442,6 +449,17 @@ def emit_select(plan: "DecodePlan", model: GpuModel, buf: StepBuffers, r0: int, 
     tp = model.tp_size > 1
     fused = tp and getattr(comm, "fused", False)
     rows = slice(r0, r0 + batch)
+
+    def controls(logits_rows):
+        """History update and per-sequence logit controls ahead of the sampling kernel (sampling plans only)."""
+        if buf.history is None:
+            return 0
+        def run():
+            ops.history_push(buf.history[rows], buf.tokens[rows], buf.positions[rows], batch)
+            ops.logit_controls(logits_rows, buf.history[rows], buf.repetition[rows], buf.presence[rows], buf.frequency[rows], buf.bias[rows],
+                               buf.bias_on[rows], vocab=V)
+        plan.add(run, launches=2)
+        return 2
     if tp and greedy_only:
         def pick():
             ops.argmax(buf.logits[rows], out=buf.local_idx[rows], out_val=buf.local_val[rows], index_offset=model.vocab_start, vocab=model.vocab_local)
@@ -454,8 +472,9 @@ def emit_select(plan: "DecodePlan", model: GpuModel, buf: StepBuffers, r0: int, 
 
         def pick_sampled():
             buf.logits_full[rows].copy_(comm.gather_logits(buf.logits[rows, :model.vocab_local], V))
-            ops.sample_launch(sp_full)
-        plan.add(pick_sampled, launches=1)
+        plan.add(pick_sampled, launches=0)
+        controls(buf.logits_full[rows])
+        plan.add(lambda: ops.sample_launch(sp_full), launches=1)
     elif greedy_only:
         plan.add(lambda: ops.argmax(buf.logits[rows], out=buf.sampled[rows], vocab=V),
                  record=("argmax", (buf.logits[rows], V, buf.sampled[rows])) if batch == 1 else None)
@@ -463,6 +482,7 @@ def emit_select(plan: "DecodePlan", model: GpuModel, buf: StepBuffers, r0: int, 
         sp = ops.build_sample_params(buf.logits[rows], buf.temperature[rows], buf.top_k[rows], buf.top_p[rows], buf.uniform[rows],
                                      buf.sampled[rows], buf.min_p[rows], vocab=V)
         plan.keep.append(sp)
+        controls(buf.logits[rows])
         plan.add(lambda: ops.sample_launch(sp))
 
 

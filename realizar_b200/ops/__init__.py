@@ -447,6 +447,30 @@ def sample(logits, temperature, top_k, top_p, uniform, min_p=None) -> torch.Tens
     return out
 
 
+def history_push(history: torch.Tensor, tokens: torch.Tensor, positions: torch.Tensor, batch: int) -> None:
+    """``history[b, positions[b] % window] = tokens[b]`` for the active rows (the ring the penalties read)."""
+    check(lib().rlz_history_push(history.data_ptr(), history.shape[-1], tokens.data_ptr(), positions.data_ptr(), batch, stream_ptr()), "history_push")
+
+
+def logit_controls(logits: torch.Tensor, history, repetition, presence, frequency, bias, bias_on, index_offset: int = 0,
+                   vocab: Optional[int] = None) -> None:
+    """In place, per row: additive bias / mask row (rows with ``bias_on``) and repetition / presence / frequency penalties."""
+    l2 = logits.reshape(-1, logits.shape[-1])
+    check(lib().rlz_logit_controls(l2.data_ptr(), l2.stride(0), vocab or l2.shape[1], index_offset, l2.shape[0], ptr(history),
+                                   history.shape[-1] if history is not None else 1, ptr(repetition), ptr(presence), ptr(frequency), ptr(bias),
+                                   bias.stride(0) if bias is not None else 0, ptr(bias_on), stream_ptr()), "logit_controls")
+
+
+def logprob_parts(logits: torch.Tensor, targets: torch.Tensor, index_offset: int = 0, vocab: Optional[int] = None) -> torch.Tensor:
+    """Per row of ``logits`` ``[rows, >= vocab]``: ``[max, sum exp(logit - max), logit[target - index_offset] or -inf]`` (fp32 ``[rows, 3]``).
+    With one vocabulary slice ``log p(target) = out[:, 2] - out[:, 0] - log(out[:, 1])``."""
+    l2 = logits.reshape(-1, logits.shape[-1])
+    out = torch.empty(l2.shape[0], 3, device=logits.device, dtype=torch.float32)
+    check(lib().rlz_logprob_rows(l2.data_ptr(), l2.stride(0), vocab or l2.shape[1], l2.shape[0], targets.data_ptr(), index_offset, out.data_ptr(),
+                                 stream_ptr()), "logprob_rows")
+    return out
+
+
 def penalties_(logits, history, repetition=None, presence=None, frequency=None) -> None:
     l2 = logits.reshape(-1, logits.shape[-1])
     check(lib().rlz_penalties(l2.data_ptr(), l2.stride(0), l2.shape[1], l2.shape[0], history.data_ptr(), history.shape[-1], ptr(repetition),

@@ -165,6 +165,10 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_page_rows.argtypes = [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_void_p]
     lib.rlz_argmax.argtypes = [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
     lib.rlz_sample.argtypes = [POINTER(SampleParams), c_void_p]
+    lib.rlz_history_push.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p]
+    lib.rlz_logit_controls.argtypes = [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
+                                       c_void_p, c_void_p]
+    lib.rlz_logprob_rows.argtypes = [c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p]
     lib.rlz_penalties.argtypes = [c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
     for name in ("rlz_gemm_kquant", "rlz_attn_prefill", "rlz_flash_decode_static", "rlz_symm_alloc"):
         pass  # declared by their own modules when present

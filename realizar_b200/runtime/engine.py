@@ -30,6 +30,7 @@ from .paged_kv import PagedKvCache
 log = logging.getLogger("realizar_b200.engine")
 
 PAGE = 16
+HISTORY_WINDOW = 64          # recent tokens per sequence that the repetition / presence / frequency penalties look at
 
 
 @dataclass
@@ -61,6 +62,10 @@ class SamplingParams:
     max_tokens: int = 64
     stop_token_ids: Sequence[int] = ()
     seed: Optional[int] = None
+    repetition_penalty: float = 1.0        # > 1 discourages tokens of the recent history (divide positive / multiply negative logits)
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    logit_bias: Optional[Dict[int, float]] = None     # token id -> additive bias (OpenAI logit_bias)
 
 
 @dataclass
@@ -113,11 +118,18 @@ class DecodeEngine:
             local_val=z(B) if tp_size > 1 else None, local_idx=z(B, dt=torch.int32) if tp_size > 1 else None,
             logits_full=z(B, self.mcfg.vocab_size) if (tp_size > 1 and not c.greedy_only) else None,
             act_q=z(ops.act_block_bytes((d_k + 127) // 128 * 128), dt=torch.uint8) if tp_size == 1 else None)
+        if not c.greedy_only:                              # sampling plans carry per-sequence logit controls
+            b = self.buf
+            b.history = torch.full((B, HISTORY_WINDOW), -1, device=dev, dtype=torch.int32)
+            b.repetition, b.presence, b.frequency = torch.ones(B, device=dev), z(B), z(B)
+            b.bias, b.bias_on = z(B, self.mcfg.vocab_size), z(B, dt=torch.int32)
         if comm is not None and getattr(comm, "fused", False):
             chunks_max = -(-B // 4)
             per_layer = 1 if self.mcfg.parallel_residual else 2
             comm.allocate(self.mcfg.num_layers * per_layer * chunks_max, self.mcfg.hidden_dim, max_batch=B)
         self.slots = [Slot() for _ in range(B)]
+        self._slot_bias: Dict[int, dict] = {}
+        self._bias_live: Dict[int, bool] = {}
         self._plans: Dict[int, DecodePlan] = {}
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self._gen = torch.Generator(device=dev).manual_seed(c.seed)
@@ -310,6 +322,12 @@ class DecodeEngine:
         s.active, s.seq_id, s.position, s.n_pages = False, -1, -1, 0
         self._h_positions[slot] = -1
         self.buf.positions[slot: slot + 1].fill_(-1)
+        if self.buf.history is not None:
+            self.buf.history[slot].fill_(-1)
+            if self._bias_live.get(slot):
+                self.buf.bias_on[slot] = 0
+                self._bias_live[slot] = False
+            self._slot_bias.pop(slot, None)
 
     def set_sampling(self, slot: int, sp: SamplingParams) -> None:
         b = self.buf
@@ -317,6 +335,57 @@ class DecodeEngine:
         b.top_k[slot] = int(sp.top_k)
         b.top_p[slot] = float(sp.top_p)
         b.min_p[slot] = float(sp.min_p)
+        wants_controls = sp.repetition_penalty != 1.0 or sp.presence_penalty != 0.0 or sp.frequency_penalty != 0.0 or bool(sp.logit_bias)
+        if b.history is None:
+            if wants_controls:
+                raise RuntimeError("penalties and logit_bias need an engine built with greedy_only=False")
+            return
+        b.repetition[slot] = float(sp.repetition_penalty)
+        b.presence[slot] = float(sp.presence_penalty)
+        b.frequency[slot] = float(sp.frequency_penalty)
+        self._slot_bias[slot] = dict(sp.logit_bias or {})
+        self._write_bias_row(slot, None)
+
+    def _write_bias_row(self, slot: int, allowed) -> None:
+        """Row ``slot`` of the additive logit row = the request's logit_bias entries, with -inf for every token outside
+        ``allowed`` (a boolean vocabulary mask from a grammar, or None)."""
+        b = self.buf
+        lb = self._slot_bias.get(slot) or {}
+        if allowed is None and not lb:
+            if self._bias_live.get(slot):
+                b.bias_on[slot] = 0
+                self._bias_live[slot] = False
+            return
+        V = self.mcfg.vocab_size
+        row = torch.zeros(V, dtype=torch.float32)
+        if allowed is not None:
+            m = torch.as_tensor(allowed[:V], dtype=torch.bool)
+            if bool(m.any()):                              # an empty mask would leave nothing to sample: ignore it
+                row[: m.numel()][~m] = float("-inf")
+                row[m.numel():] = float("-inf")
+        for t, v in lb.items():
+            if 0 <= int(t) < V:
+                row[int(t)] += float(v)
+        b.bias[slot].copy_(row, non_blocking=False)
+        b.bias_on[slot] = 1
+        self._bias_live[slot] = True
+
+    def set_token_mask(self, slot: int, allowed) -> None:
+        """Restrict the next sampled token of ``slot`` to the ids where ``allowed`` (boolean array over the vocabulary) is
+        true - the device-side form of a grammar / tool-call token mask; ``None`` lifts the restriction."""
+        if self.buf.history is None:
+            raise RuntimeError("token masks need an engine built with greedy_only=False")
+        self._write_bias_row(slot, allowed)
+
+    def _push_history(self, slot: int, tokens: Sequence[int], pos0: int) -> None:
+        """Prompt tokens at positions ``pos0 ..`` enter the slot's history ring (decode steps add theirs on the device)."""
+        if self.buf.history is None or not tokens:
+            return
+        W = HISTORY_WINDOW
+        tail = list(tokens)[-W:]
+        p0 = pos0 + len(tokens) - len(tail)
+        idx = torch.tensor([(p0 + i) % W for i in range(len(tail))], dtype=torch.long, device=self.device)
+        self.buf.history[slot, idx] = torch.tensor(tail, dtype=torch.int32, device=self.device)
 
     # -- single-token feeding ------------------------------------------------------------------
     def feed(self, slot_tokens: Dict[int, int]) -> torch.Tensor:
@@ -381,6 +450,7 @@ class DecodeEngine:
             s.history.extend(int(t) for t in tokens)
         n = len(tokens)
         if n >= self.cfg.batched_prefill_min and self.gemm_ok:
+            self._push_history(slot, tokens, s.position)       # (the token-by-token path below records them on the device)
             out = self._prefill_batched(slot, tokens)
         else:
             out = 0
@@ -431,6 +501,7 @@ class DecodeEngine:
         self.buf.x[slot].copy_(x_last)
         if not self.cfg.greedy_only:
             self.buf.uniform[slot: slot + 1].copy_(torch.rand(1, device=self.device, generator=self._gen))
+        self.buf.positions[slot: slot + 1].fill_(-1)         # the head plan's history update has nothing to add: the prompt is in already
         self._head(slot).run()
         self._h_sampled[slot: slot + 1].copy_(self.buf.sampled[slot: slot + 1], non_blocking=True)
         torch.cuda.current_stream().synchronize()
@@ -480,6 +551,83 @@ class DecodeEngine:
             self._head_plans[key].run()
             out += [int(v) for v in self.buf.sampled[:cb].cpu()]
         s.position = pos0 + n
+        return out
+
+    # -- scoring: log-probabilities of given tokens, pooled embeddings ------------------------------------------
+    def score_tokens(self, tokens: Sequence[int], want_embedding: bool = False, top_k: int = 0) -> dict:
+        """Teacher-forced pass over ``tokens`` on the tensor-core path: ``logprobs[i] = log p(tokens[i+1] | tokens[:i+1])``
+        for i = 0 .. n-2 (head GEMM over every row + a log-softmax / gather kernel), optionally the top-k alternatives at
+        every position and the mean-pooled final-norm hidden state.  Uses a free slot for the duration of the call (run it on
+        the engine thread).  Under tensor parallelism every rank calls it with the same tokens; the vocabulary-sharded head is
+        combined with small all-reduces.  The reference computes these on the host from downloaded logits
+        (``generate_gpu_resident_logprobs`` / ``perplexity_gpu_resident``, src/gguf/cuda/generate_2.rs:590-780)."""
+        import math
+        n = len(tokens)
+        if n < 1:
+            raise ValueError("score_tokens needs at least one token")
+        if not self.gemm_ok:
+            raise RuntimeError("scoring runs on the tensor-core token-batch path: every projection must be Q4_K / Q5_K / Q6_K / bf16 / f16")
+        if n > self.cfg.max_seq_len:
+            raise ValueError(f"{n} tokens exceed max_seq_len {self.cfg.max_seq_len}")
+        free = self.free_slots()
+        if not free:
+            raise RuntimeError("no free slot for scoring")
+        slot = free[-1]
+        bf, m, cfg = self.batched(), self.model, self.mcfg
+        norm_t = ops.NORM_LAYER if cfg.uses_layernorm else ops.NORM_RMS
+        tp = m.tp_size > 1
+        vloc = m.vocab_local if tp else cfg.vocab_size
+        if getattr(self, "_score_logits", None) is None:
+            self._score_logits = torch.empty(bf.T, vloc, device=self.device, dtype=torch.float32)
+        toks = torch.as_tensor(list(tokens), dtype=torch.int32)
+        lps: List[float] = []
+        tops: List[list] = []
+        pooled = torch.zeros(cfg.hidden_dim, device=self.device, dtype=torch.float32) if want_embedding else None
+        self.open_slot(slot, n)
+        try:
+            s = self.slots[slot]
+            pages = self.pages.seqs[s.seq_id].pages
+            for c0 in range(0, n, bf.T):
+                T = min(bf.T, n - c0)
+                bf.tokens[:T].copy_(toks[c0:c0 + T], non_blocking=True)
+                bf.positions[:T].copy_(torch.arange(c0, c0 + T, dtype=torch.int32), non_blocking=True)
+                bf.page_rows[:T].copy_(torch.tensor([pages[p // PAGE] for p in range(c0, c0 + T)], dtype=torch.int32), non_blocking=True)
+                x = bf.forward_chunk(T, self.buf.page_table[slot], c0)
+                ops.norm_bf16(x, bf.xb[:T], m.out_norm_w, m.out_norm_b, norm_t, cfg.eps)
+                if pooled is not None:
+                    pooled += bf.xb[:T].float().sum(0)
+                rows = min(T, n - 1 - c0)                   # the last token of the sequence has no successor to score
+                if rows > 0:
+                    G.gemm_launch(G.build_gemm_params(m.lm_head, bf.xb, self._score_logits, T, bias=m.lm_head_b, ldy=self._score_logits.stride(0)))
+                    tgt = toks[c0 + 1: c0 + 1 + rows].to(self.device)
+                    parts = ops.logprob_parts(self._score_logits[:rows], tgt, index_offset=m.vocab_start if tp else 0, vocab=vloc)
+                    if tp:
+                        import torch.distributed as dist
+                        gmax = parts[:, 0].clone()
+                        dist.all_reduce(gmax, op=dist.ReduceOp.MAX)
+                        ssum = parts[:, 1] * torch.exp(parts[:, 0] - gmax)
+                        dist.all_reduce(ssum)
+                        tl = parts[:, 2].clone()
+                        dist.all_reduce(tl, op=dist.ReduceOp.MAX)
+                        lp = tl - gmax - torch.log(ssum)
+                    else:
+                        lp = parts[:, 2] - parts[:, 0] - torch.log(parts[:, 1])
+                    lps += [float(v) for v in lp.cpu()]
+                    if top_k > 0 and not tp:
+                        lsm = torch.log_softmax(self._score_logits[:rows, :cfg.vocab_size], dim=-1)
+                        tv, ti = lsm.topk(min(top_k, cfg.vocab_size), dim=-1)
+                        tops += [[(int(i), float(v)) for i, v in zip(ri, rv)] for ri, rv in zip(ti.cpu(), tv.cpu())]
+            self.check_health()
+        finally:
+            self.close_slot(slot)
+        out = {"logprobs": lps, "num_tokens": n}
+        if lps:
+            nll = -sum(lps) / len(lps)
+            out.update({"nll": nll, "perplexity": math.exp(min(nll, 700.0))})
+        if top_k > 0:
+            out["top_logprobs"] = tops
+        if pooled is not None:
+            out["embedding"] = [float(v) for v in (pooled / n).cpu()]
         return out
 
     def rollback(self, slot: int, position: int) -> None:

@@ -49,6 +49,12 @@ class Request:
     top_p: float = 1.0
     min_p: float = 0.0
     stop_token_ids: Sequence[int] = ()
+    repetition_penalty: float = 1.0
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    logit_bias: Optional[Dict[int, float]] = None
+    token_masker: Optional[object] = None  # grammar / tool-call constraint: ``mask() -> bool[vocab]`` and ``accept_token(id)``
+    stop_check: Optional[Callable[["Request"], bool]] = None   # called after every token; True ends the request (stop strings)
     priority: int = 0                      # larger = more urgent
     deadline: Optional[float] = None       # absolute time.monotonic() deadline
     on_token: Optional[Callable[[int], None]] = None
@@ -279,12 +285,17 @@ class ServingEngine:
     steps, streams tokens through callbacks.  ``health`` turns to "unhealthy" when a step raises
     (a circuit-breaker style latch that the API layer reports as 503)."""
 
-    def __init__(self, engine, cfg: Optional[SchedulerConfig] = None, idle_sleep: float = 0.001):
+    def __init__(self, engine, cfg: Optional[SchedulerConfig] = None, idle_sleep: float = 0.001, draft_layers: Optional[Sequence[int]] = None,
+                 spec_k: int = 4):
         self.engine = engine
+        self.draft_layers = tuple(draft_layers) if draft_layers else None
+        self.spec_k = spec_k
+        self.spec_stats = {"rounds": 0, "drafted": 0, "accepted": 0}
         ecfg = engine.cfg
         self.cfg = cfg or SchedulerConfig(max_batch=ecfg.max_batch, max_seq_len=ecfg.max_seq_len)
         self.sched = Scheduler(self.cfg, total_pages=getattr(engine, "num_pages", None))
         self._inbox: "queue.Queue[Request]" = queue.Queue()
+        self._calls: "queue.Queue" = queue.Queue()
         self._stop = threading.Event()
         self._thread: Optional[threading.Thread] = None
         self.idle_sleep = idle_sleep
@@ -316,6 +327,30 @@ class ServingEngine:
         self._inbox.put(r)
         return r
 
+    def call_on_engine(self, fn: Callable[[object], object], timeout: Optional[float] = 120.0):
+        """Run ``fn(engine)`` on the engine thread between two scheduling iterations and return its result (scoring passes,
+        KV snapshots: anything that needs the engine while requests are being served)."""
+        if self.health != "ok":
+            raise RuntimeError(f"engine is {self.health}: {self.last_error}")
+        done = threading.Event()
+        box: dict = {}
+
+        def job(engine):
+            try:
+                box["value"] = fn(engine)
+            except Exception as e:                           # delivered to the caller, the serving loop goes on
+                box["error"] = e
+            done.set()
+        if self._thread is None:                             # no worker thread (tests that drive step() themselves)
+            job(self.engine)
+        else:
+            self._calls.put(job)
+        if not done.wait(timeout):
+            raise TimeoutError("engine call timed out")
+        if "error" in box:
+            raise box["error"]
+        return box.get("value")
+
     def generate(self, prompt: Sequence[int], timeout: Optional[float] = None, **kw) -> Request:
         """Blocking convenience: submit and wait for completion."""
         done = threading.Event()
@@ -344,8 +379,16 @@ class ServingEngine:
     def step(self) -> bool:
         """One scheduling iteration.  Returns False when there was nothing to do."""
         self._drain_inbox()
+        ran_call = False
+        while True:                                          # engine calls queued by other threads (scoring, snapshots)
+            try:
+                job = self._calls.get_nowait()
+            except queue.Empty:
+                break
+            job(self.engine)
+            ran_call = True
         if not self.sched.has_work:
-            return False
+            return ran_call
         t0 = time.monotonic()
         d = self.sched.schedule()
         eng = self.engine
@@ -355,19 +398,25 @@ class ServingEngine:
         for r in d.admitted:
             eng.open_slot(r.slot, min(self.cfg.max_seq_len, len(r.prompt) + len(r.output) + r.max_tokens))
             from .engine import SamplingParams
-            eng.set_sampling(r.slot, SamplingParams(r.temperature, r.top_k, r.top_p, r.min_p, r.max_tokens))
+            eng.set_sampling(r.slot, SamplingParams(r.temperature, r.top_k, r.top_p, r.min_p, r.max_tokens,
+                                                    repetition_penalty=r.repetition_penalty, presence_penalty=r.presence_penalty,
+                                                    frequency_penalty=r.frequency_penalty, logit_bias=r.logit_bias))
+            if r.token_masker is not None:
+                eng.set_token_mask(r.slot, r.token_masker.mask())
             r._engine_slot = r.slot
         # decode first (latency of running streams), then prompt chunks
         live = [r for r in d.decode if not r.cancelled]
         for r in d.decode:
             if r.cancelled:
                 self._finish(r, FinishReason.ABORT)
-        if live:
+        if live and self._speculative_round(live):
+            pass
+        elif live:
             out = eng.feed({r.slot: r.output[-1] for r in live})
             now = time.monotonic()
             for r in live:
                 slot = r.slot
-                self.sched.on_token(r, int(out[slot]), now)
+                self._emit(r, int(out[slot]), now)
                 if r.state == RequestState.FINISHED:
                     eng.close_slot(slot)
         for r, start, end in d.prefill:
@@ -377,11 +426,63 @@ class ServingEngine:
             slot = r.slot
             full = r.prompt + r.output
             tok = eng.prefill(slot, full[start:end])
-            self.sched.on_prefill_done(r, end, tok if end >= len(full) else None)
+            last = end >= len(full)
+            self.sched.on_prefill_done(r, end, tok if last else None)
+            if last and r.state != RequestState.FINISHED:
+                self._after_token(r, int(tok))
             if r.state == RequestState.FINISHED:
                 eng.close_slot(slot)
         self.step_times.append(time.monotonic() - t0)
         return True
+
+    def _emit(self, r: Request, tok: int, now: float) -> None:
+        """A decode step produced ``tok`` for ``r``: scheduler bookkeeping, then the request's own constraints."""
+        self.sched.on_token(r, tok, now)
+        if r.state != RequestState.FINISHED:
+            self._after_token(r, tok)
+
+    def _after_token(self, r: Request, tok: int) -> None:
+        """Grammar state and stop strings after a token; the mask for the NEXT token goes to the device."""
+        if r.token_masker is not None:
+            r.token_masker.accept_token(tok)
+            self.engine.set_token_mask(r.slot, r.token_masker.mask())
+        if r.stop_check is not None and r.stop_check(r):
+            self.sched.finish(r, FinishReason.STOP)
+
+    def _speculative_round(self, live) -> bool:
+        """Self-speculative decoding for a lone greedy stream (server option ``draft_layers``): the layer-skipping draft
+        proposes ``spec_k`` tokens, one tensor-core pass of the full model checks them, and the agreeing prefix plus the
+        model's own next token are emitted - between 1 and ``spec_k + 1`` tokens for one read of the weights.
+        Returns False when the step has to run normally."""
+        if not self.draft_layers or len(live) != 1:
+            return False
+        r, eng = live[0], self.engine
+        if (r.slot != 0 or r.temperature > 0 or r.token_masker is not None or r.logit_bias or r.repetition_penalty != 1.0
+                or r.presence_penalty or r.frequency_penalty or not getattr(eng, "gemm_ok", False)):
+            return False
+        from .speculative import verify_greedy
+        k = min(self.spec_k, r.max_tokens - len(r.output) - 1, self.cfg.max_seq_len - r.total_len - 2)
+        if k < 1:
+            return False
+        pos0 = eng.slots[0].position
+        last, drafts, feed = r.output[-1], [], r.output[-1]
+        for _ in range(k):
+            feed = eng.draft_step(0, int(feed), self.draft_layers)
+            drafts.append(int(feed))
+        eng.rollback(0, pos0)
+        nxt = eng.forward_tokens(0, [last] + drafts)
+        v = verify_greedy(drafts, nxt)
+        eng.rollback(0, pos0 + 1 + v.accepted)
+        self.spec_stats["rounds"] += 1
+        self.spec_stats["drafted"] += k
+        self.spec_stats["accepted"] += v.accepted
+        now = time.monotonic()
+        for t in v.tokens:
+            self._emit(r, int(t), now)
+            if r.state == RequestState.FINISHED:
+                eng.close_slot(0)
+                break
+        return True                                          # the last emitted token has not been fed yet, exactly as after feed()
 
     def _finish(self, r: Request, reason: FinishReason) -> None:
         slot = r.slot
@@ -429,15 +530,41 @@ class FakeEngine:
 
     def close_slot(self, slot):
         self.open.pop(slot, None)
+        getattr(self, "masks", {}).pop(slot, None)
         self.calls.append(("close", slot))
 
     def set_sampling(self, slot, sp):
         self.calls.append(("sampling", slot, sp.temperature))
+        self.sampling = getattr(self, "sampling", {})
+        self.sampling[slot] = sp
+        self.sampling_log = getattr(self, "sampling_log", [])
+        self.sampling_log.append(sp)
+
+    def set_token_mask(self, slot, allowed):
+        self.masks = getattr(self, "masks", {})
+        self.masks[slot] = None if allowed is None else [int(i) for i, a in enumerate(allowed) if a]
+        self.calls.append(("mask", slot, None if allowed is None else int(sum(bool(a) for a in allowed))))
+
+    def free_slots(self):
+        return [i for i in range(self.cfg.max_batch) if i not in self.open]
+
+    def score_tokens(self, tokens, want_embedding=False, top_k=0):
+        """Scores of the toy model: the successor (t + 1) % vocab has probability 1/2."""
+        import math
+        self.calls.append(("score", len(tokens)))
+        lps = [math.log(0.5) if b == (a + 1) % self.vocab else math.log(0.5 / (self.vocab - 1)) for a, b in zip(tokens, tokens[1:])]
+        out = {"logprobs": lps, "num_tokens": len(tokens)}
+        if lps:
+            out["nll"] = -sum(lps) / len(lps)
+            out["perplexity"] = math.exp(out["nll"])
+        if want_embedding:
+            out["embedding"] = [float(sum(tokens)) / len(tokens), float(len(tokens))]
+        return out
 
     def prefill(self, slot, tokens):
         self.open[slot] += len(tokens)
         self.calls.append(("prefill", slot, len(tokens)))
-        return (int(tokens[-1]) + 1) % self.vocab
+        return self._pick(slot, (int(tokens[-1]) + 1) % self.vocab)
 
     def feed(self, slot_tokens):
         self.steps += 1
@@ -447,5 +574,12 @@ class FakeEngine:
         out = [0] * self.cfg.max_batch
         for s, t in slot_tokens.items():
             self.open[s] += 1
-            out[s] = (int(t) + 1) % self.vocab
+            out[s] = self._pick(s, (int(t) + 1) % self.vocab)
         return out
+
+    def _pick(self, slot, default):
+        """A token mask restricts the fake's choice: the default if it is allowed, else the smallest allowed id."""
+        allowed = getattr(self, "masks", {}).get(slot)
+        if allowed is None or default in allowed or not allowed:
+            return default
+        return allowed[0]

@@ -51,6 +51,14 @@ class ChatCompletionRequest(BaseModel):
     stream: bool = False
     stop: Optional[List[str]] = None
     user: Optional[str] = None
+    top_k: Optional[int] = None
+    min_p: Optional[float] = None
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    repetition_penalty: float = 1.0
+    logit_bias: Optional[Dict[str, float]] = None
+    response_format: Optional[Dict[str, Any]] = None       # {"type": "json_object"} | {"type": "json_schema", "json_schema": {...}}
+    grammar: Optional[str] = None                           # GBNF text
 
 
 class CompletionRequest(BaseModel):
@@ -61,6 +69,14 @@ class CompletionRequest(BaseModel):
     top_p: Optional[float] = None
     stop: Optional[List[str]] = None
     stream: bool = False
+    top_k: Optional[int] = None
+    min_p: Optional[float] = None
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    repetition_penalty: float = 1.0
+    logit_bias: Optional[Dict[str, float]] = None
+    response_format: Optional[Dict[str, Any]] = None
+    grammar: Optional[str] = None
 
 
 class GenerateRequest(BaseModel):
@@ -113,7 +129,8 @@ class AppState:
     dispatch: DispatchMetrics = field(default_factory=DispatchMetrics)
     audit: Dict[str, dict] = field(default_factory=dict)
     compute_mode: str = "gpu"
-    scorer: Any = None                  # optional callable(tokens) -> per-position logits (logprobs / perplexity / embeddings)
+    scorer: Any = None                  # object with logprobs(ids) / embed(ids) (runtime.scorer.EngineScorer for GPU engines)
+    vocab_strings: Optional[List[str]] = None       # text of every token id, built on the first grammar-constrained request
     context_length: int = 4096
     classical: Any = None               # optional ClassicalServeState behind /v1/predict, /v1/explain
 
@@ -121,8 +138,10 @@ class AppState:
     def demo(cls) -> "AppState":
         """A self-contained state with a fake engine and a byte tokenizer (tests, smoke runs)."""
         from ..runtime.scheduler import FakeEngine
+        from ..runtime.scorer import EngineScorer
         from .tokenizer import ByteTokenizer
-        return cls(ServingEngine(FakeEngine(vocab=256)).start(), ByteTokenizer(256), RawTemplate(), "demo", None, compute_mode="cpu")
+        serving = ServingEngine(FakeEngine(vocab=256)).start()
+        return cls(serving, ByteTokenizer(256), RawTemplate(), "demo", None, compute_mode="cpu", scorer=EngineScorer(serving))
 
 
 def _finish_reason(r: Request) -> str:
@@ -155,11 +174,55 @@ def create_app(state: AppState) -> FastAPI:
     def stop_ids() -> List[int]:
         return [state.eos_token_id] if state.eos_token_id is not None else []
 
-    def submit(prompt_ids, max_tokens, temperature, top_k, top_p, on_token=None, on_finish=None) -> Request:
+    def vocab_strings() -> List[str]:
+        """Text of every token id (grammar masks test tokens as strings); built once per server."""
+        if state.vocab_strings is None:
+            tok = state.tokenizer
+            n = getattr(tok, "vocab_size", None) or len(getattr(tok, "vocab", []))
+            state.vocab_strings = [tok.decode([i]) for i in range(int(n))]
+        return state.vocab_strings
+
+    def controls_of(req) -> dict:
+        """Request-level sampling controls of an OpenAI-style body as ``Request`` fields: penalties, logit_bias, a grammar /
+        JSON-schema token mask and a stop-string check (the generation ends when a stop string appears in the decoded text)."""
+        extra: Dict[str, Any] = {}
+        for k in ("presence_penalty", "frequency_penalty"):
+            if getattr(req, k, 0.0):
+                extra[k] = float(getattr(req, k))
+        if getattr(req, "repetition_penalty", 1.0) not in (None, 1.0):
+            extra["repetition_penalty"] = float(req.repetition_penalty)
+        if getattr(req, "min_p", None):
+            extra["min_p"] = float(req.min_p)
+        if getattr(req, "logit_bias", None):
+            try:
+                extra["logit_bias"] = {int(k): float(v) for k, v in req.logit_bias.items()}
+            except ValueError:
+                raise HTTPException(400, "logit_bias keys must be token ids")
+        gtext, rf = getattr(req, "grammar", None), getattr(req, "response_format", None)
+        if gtext or (rf and rf.get("type") in ("json_object", "json_schema")):
+            from .grammar import Grammar, GrammarTokenMasker, grammar_from_json_schema
+            try:
+                if gtext:
+                    g = Grammar.from_gbnf(gtext)
+                else:
+                    schema = (rf.get("json_schema") or {}).get("schema", rf.get("json_schema")) if rf.get("type") == "json_schema" else {"type": "object"}
+                    g = grammar_from_json_schema(schema or {"type": "object"})
+            except Exception as e:
+                raise HTTPException(400, f"invalid grammar: {e}")
+            extra["token_masker"] = GrammarTokenMasker(g, vocab_strings(), state.eos_token_id)
+        stops = [s for s in (getattr(req, "stop", None) or []) if s]
+        if stops:
+            def stop_check(r: Request, stops=stops) -> bool:
+                text = state.tokenizer.decode(r.output[-64:])
+                return any(s in text for s in stops)
+            extra["stop_check"] = stop_check
+        return extra
+
+    def submit(prompt_ids, max_tokens, temperature, top_k, top_p, on_token=None, on_finish=None, extra: Optional[dict] = None) -> Request:
         if state.serving is None:
             raise HTTPException(503, "no model loaded")
         r = Request(prompt_ids, max_tokens=max_tokens, temperature=temperature, top_k=top_k, top_p=top_p, stop_token_ids=stop_ids(),
-                    on_token=on_token, on_finish=on_finish)
+                    on_token=on_token, on_finish=on_finish, **(extra or {}))
         try:
             state.serving.submit(r)
         except QueueFull:
@@ -170,11 +233,11 @@ def create_app(state: AppState) -> FastAPI:
             raise HTTPException(503, str(e))
         return r
 
-    async def run_blocking(prompt_ids, max_tokens, temperature, top_k, top_p) -> Request:
+    async def run_blocking(prompt_ids, max_tokens, temperature, top_k, top_p, extra: Optional[dict] = None) -> Request:
         loop = asyncio.get_running_loop()
         fut = loop.create_future()
         r = submit(prompt_ids, max_tokens, temperature, top_k, top_p,
-                   on_finish=lambda rq: loop.call_soon_threadsafe(lambda: fut.done() or fut.set_result(rq)))
+                   on_finish=lambda rq: loop.call_soon_threadsafe(lambda: fut.done() or fut.set_result(rq)), extra=extra)
         await fut
         record(r)
         if r.finish_reason == FinishReason.ERROR:
@@ -201,7 +264,8 @@ def create_app(state: AppState) -> FastAPI:
 
     def chat_params(req) -> tuple:
         t = 0.7 if req.temperature is None else req.temperature
-        return (req.max_tokens or 256, t, 1 if t == 0 else 40, 1.0 if req.top_p is None else req.top_p)
+        k = getattr(req, "top_k", None)
+        return (req.max_tokens or 256, t, 1 if t == 0 else (40 if k is None else int(k)), 1.0 if req.top_p is None else req.top_p)
 
     def audit(rid: str, kind: str, prompt_tokens: int, completion_tokens: int, latency: float) -> None:
         state.audit[rid] = {"request_id": rid, "endpoint": kind, "model": state.model_name, "prompt_tokens": prompt_tokens,
@@ -224,7 +288,9 @@ def create_app(state: AppState) -> FastAPI:
             dec = StreamDecoder(state.tokenizer)
             stops = set(stop_ids())
             r = submit(*r_holder["args"], on_token=lambda t: loop.call_soon_threadsafe(q.put_nowait, ("tok", t)),
-                       on_finish=lambda rq: loop.call_soon_threadsafe(q.put_nowait, ("end", rq)))
+                       on_finish=lambda rq: loop.call_soon_threadsafe(q.put_nowait, ("end", rq)), extra=r_holder.get("extra"))
+            stop_strs = r_holder.get("stops") or []
+            held = ""                                        # text not yet sent: a stop string may still be forming at its end
             if first_chunk is not None:
                 yield f"data: {json.dumps(first_chunk)}\n\n"
             try:
@@ -238,6 +304,16 @@ def create_app(state: AppState) -> FastAPI:
                         if val in stops:
                             continue
                         text = dec.push(val)
+                        if text and stop_strs:
+                            held += text
+                            cut = min((held.find(s_) for s_ in stop_strs if s_ in held), default=-1)
+                            if cut >= 0:                     # the stop string itself is never sent
+                                text, held = held[:cut], ""
+                                stop_strs = []
+                                r.cancelled = r.finish_reason is None
+                            else:
+                                keep = max(len(s_) for s_ in stop_strs) - 1
+                                text, held = (held[:-keep], held[-keep:]) if keep > 0 and len(held) > keep else ("", held) if keep > 0 else (held, "")
                         if text:
                             yield f"data: {json.dumps(make_chunk(val, text))}\n\n"
                     else:
@@ -246,6 +322,8 @@ def create_app(state: AppState) -> FastAPI:
                             yield f"data: {json.dumps({'error': val.error or 'generation failed'})}\n\n"
                         else:
                             tail = dec.flush()
+                            if r_holder.get("stops"):
+                                tail = apply_stops(held + tail, r_holder.get("stops")) if stop_strs else ""
                             if tail:
                                 yield f"data: {json.dumps(make_chunk(-1, tail))}\n\n"
                             yield f"data: {json.dumps(done_chunk(val))}\n\n"
@@ -355,10 +433,10 @@ def create_app(state: AppState) -> FastAPI:
         if req.stream:
             base = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": req.model}
             first = {**base, "choices": [{"index": 0, "delta": {"role": "assistant"}, "finish_reason": None}]}
-            return sse_stream({"args": (ids, *params)}, first,
+            return sse_stream({"args": (ids, *params), "extra": controls_of(req), "stops": req.stop}, first,
                               lambda _tid, text: {**base, "choices": [{"index": 0, "delta": {"content": text}, "finish_reason": None}]},
                               lambda r: {**base, "choices": [{"index": 0, "delta": {}, "finish_reason": _finish_reason(r)}]})
-        r = await run_blocking(ids, *params)
+        r = await run_blocking(ids, *params, extra=controls_of(req))
         text = apply_stops(text_of(r), req.stop)
         audit(rid, "chat.completions", len(ids), len(r.output), (r.finish_time or time.monotonic()) - r.arrival)
         return {"id": rid, "object": "chat.completion", "created": created, "model": req.model,
@@ -375,14 +453,13 @@ def create_app(state: AppState) -> FastAPI:
     async def completions(req: CompletionRequest):
         ids = encode(req.prompt)
         rid, created = f"cmpl-{uuid.uuid4().hex[:24]}", int(time.time())
-        t = 0.7 if req.temperature is None else req.temperature
-        params = (req.max_tokens or 256, t, 1 if t == 0 else 40, 1.0 if req.top_p is None else req.top_p)
+        params = chat_params(req)
         if req.stream:
             base = {"id": rid, "object": "text_completion", "created": created, "model": req.model}
-            return sse_stream({"args": (ids, *params)}, None,
+            return sse_stream({"args": (ids, *params), "extra": controls_of(req), "stops": req.stop}, None,
                               lambda _tid, text: {**base, "choices": [{"index": 0, "text": text, "finish_reason": None}]},
                               lambda r: {**base, "choices": [{"index": 0, "text": "", "finish_reason": _finish_reason(r)}]})
-        r = await run_blocking(ids, *params)
+        r = await run_blocking(ids, *params, extra=controls_of(req))
         audit(rid, "completions", len(ids), len(r.output), (r.finish_time or time.monotonic()) - r.arrival)
         return {"id": rid, "object": "text_completion", "created": created, "model": req.model,
                 "choices": [{"index": 0, "text": apply_stops(text_of(r), req.stop), "finish_reason": _finish_reason(r)}],

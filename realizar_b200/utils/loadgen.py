@@ -23,9 +23,12 @@ class LoadConfig:
     requests: int = 200
     rate_per_s: float = 20.0
     max_concurrency: int = 256
-    prompt_tokens: int = 64            # approximate: prompts are made of that many short words
+    prompt_tokens: int = 64            # approximate: prompts are made of that many short words (or exactly that many characters)
+    prompt_tokens_max: int = 0         # > prompt_tokens: every prompt draws its length uniformly from [prompt_tokens, prompt_tokens_max]
+    prompt_chars: bool = False         # prompt length counted in characters (byte-level tokenizers: one token per character)
     max_tokens: int = 32
     temperature: float = 0.0
+    top_p: float = 1.0
     model: str = "default"
     seed: int = 0
     timeout_s: float = 120.0
@@ -62,13 +65,22 @@ def summarize(traces: List[RequestTrace], wall_s: float) -> dict:
             "latency_ms": {"p50": _pct(lat, 50), "p95": _pct(lat, 95), "p99": _pct(lat, 99)}}
 
 
-def make_prompt(rng: random.Random, n_words: int) -> str:
+def make_prompt(rng: random.Random, n_words: int, chars: bool = False) -> str:
     words = ("the", "of", "and", "model", "token", "cache", "page", "head", "layer", "scale", "block", "warp", "tile", "core", "sum", "max")
+    if chars:
+        out = ""
+        while len(out) < n_words:
+            out += rng.choice(words) + " "
+        return out[:n_words]
     return " ".join(rng.choice(words) for _ in range(n_words))
 
 
+def prompt_length(rng: random.Random, cfg: "LoadConfig") -> int:
+    return rng.randint(cfg.prompt_tokens, cfg.prompt_tokens_max) if cfg.prompt_tokens_max > cfg.prompt_tokens else cfg.prompt_tokens
+
+
 def _body(cfg: LoadConfig, prompt: str) -> dict:
-    return {"model": cfg.model, "messages": [{"role": "user", "content": prompt}], "max_tokens": cfg.max_tokens, "temperature": cfg.temperature, "stream": True}
+    return {"model": cfg.model, "messages": [{"role": "user", "content": prompt}], "max_tokens": cfg.max_tokens, "temperature": cfg.temperature, "top_p": cfg.top_p, "stream": True}
 
 
 def _consume_sse_line(line: str, tr: RequestTrace) -> bool:
@@ -169,7 +181,7 @@ async def run_load_async(cfg: LoadConfig, url: Optional[str] = None, app=None) -
                 await _one_http(session, url.rstrip("/"), cfg, prompt, tr)
     try:
         for _ in range(cfg.requests):
-            tasks.append(asyncio.create_task(launch(make_prompt(rng, cfg.prompt_tokens))))
+            tasks.append(asyncio.create_task(launch(make_prompt(rng, prompt_length(rng, cfg), cfg.prompt_chars))))
             if cfg.rate_per_s > 0:
                 await asyncio.sleep(rng.expovariate(cfg.rate_per_s))        # Poisson arrivals
         await asyncio.gather(*tasks)

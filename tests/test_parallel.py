@@ -107,6 +107,51 @@ dist.destroy_process_group()
     assert r.returncode == 0, r.stderr[-2000:]
 
 
+def test_tensor_parallel_serving_proxy_two_gloo_ranks(tmp_path):
+    """Rank 0 runs the serving loop over a leader proxy, rank 1 follows: both (toy) engines must see the same calls with
+    the same arguments - slots, sampling parameters with penalties and logit_bias, prompt chunks, decode steps, token masks,
+    scoring passes - and rank 1 leaves its loop when the leader shuts down."""
+    script = tmp_path / "tp.py"
+    script.write_text("""
+import json, os, sys, torch, torch.distributed as dist
+sys.path.insert(0, %r)
+from realizar_b200.parallel.tp_serving import TpLeaderEngine, follower_loop
+from realizar_b200.runtime.scheduler import FakeEngine, Request, ServingEngine
+dist.init_process_group('gloo')
+rank = dist.get_rank()
+group = dist.new_group(backend='gloo')
+eng = FakeEngine(max_batch=2, vocab=50)
+if rank == 0:
+    lead = TpLeaderEngine(eng, group)
+    sv = ServingEngine(lead).start()
+    class Mask:
+        def __init__(self): self.n = 0
+        def mask(self): return [i in (7, 9) for i in range(50)]
+        def accept_token(self, t): self.n += 1; return True
+    r1 = sv.generate([1, 2, 3], max_tokens=4, temperature=0.7, top_k=5, presence_penalty=0.5, logit_bias={4: -3.0}, timeout=30)
+    r2 = sv.generate([10, 11], max_tokens=3, token_masker=Mask(), timeout=30)
+    sc = sv.call_on_engine(lambda e: e.score_tokens([5, 6, 7], want_embedding=True))
+    assert r1.output == [4, 5, 6, 7] and r2.output == [7, 7, 7] and len(sc['logprobs']) == 2, (r1.output, r2.output, sc)
+    sv.stop()
+    lead.shutdown(leave=False)
+else:
+    n = follower_loop(eng, group)
+    assert n > 0
+calls = [c for c in eng.calls]
+gathered = [None, None]
+dist.all_gather_object(gathered, json.dumps(calls))
+assert gathered[0] == gathered[1], (gathered[0][:400], gathered[1][:400])
+sp = getattr(eng, 'sampling_log', [])
+assert any(v.presence_penalty == 0.5 and v.logit_bias == {4: -3.0} and v.top_k == 5 and abs(v.temperature - 0.7) < 1e-9 for v in sp), sp
+dist.barrier()
+dist.destroy_process_group()
+""" % os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29549", str(script)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-3000:]
+
+
 def test_rank_failure_is_detected_by_the_survivor(tmp_path):
     """Failure drill on CPU ranks: rank 1 leaves between steps (no collective in flight); rank 0 learns of it
     through a heartbeat in the rendezvous store before its next collective, and a collective that is attempted

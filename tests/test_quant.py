@@ -124,3 +124,27 @@ def test_rejects_bad_shapes():
     with pytest.raises(ValueError):
         quant.dequantize(np.zeros(10, np.uint8), QType.Q4_K, (1, 256))
     assert quant.qtype_from_size(144 * 4, 2, 512) == QType.Q4_K
+
+
+@pytest.mark.parametrize("qt", [QType.Q4_0, QType.Q4_1, QType.Q5_0, QType.Q5_1, QType.Q8_0, QType.Q4_K, QType.Q5_K, QType.Q6_K])
+def test_simd_fused_dots_match_dequantised_reference(qt):
+    """The fused dequant-dot of every block type (AVX2, and AVX-512 VNNI where the host has it) against a float64 product
+    with the dequantised weights; the only difference allowed is the int8 quantisation of the activations."""
+    import ctypes
+    from realizar_b200._native import cpu_lib
+    lib = cpu_lib()
+    lib.rlz_cpu_dot_path.argtypes = [ctypes.c_int]
+    rng = np.random.default_rng(int(qt) + 100)
+    n, k = 37, 256 * 3
+    w = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+    q = quant.quantize(w, qt)
+    wd = quant.dequantize(q, qt, (n, k)).astype(np.float64)
+    for batch in (1, 3):
+        x = rng.standard_normal((batch, k)).astype(np.float32)
+        y = quant.matvec(q, qt, n, k, x if batch > 1 else x[0])
+        ref = x.astype(np.float64) @ wd.T
+        err = np.abs(np.asarray(y).reshape(batch, n) - ref).max() / np.abs(ref).max()
+        assert err < 0.02, (qt, batch, err)
+    assert lib.rlz_cpu_dot_path(int(qt)) in (0, 1, 2)
+    if lib.rlz_cpu_has_avx2():
+        assert lib.rlz_cpu_dot_path(int(qt)) >= 1          # no block type of the public surface is left on the scalar path

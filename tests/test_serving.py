@@ -242,4 +242,44 @@ def test_http_chat_completions_and_streaming(client):
     assert "realizar_requests_total" in m and "realizar_ttft_seconds_bucket" in m
     assert client.get("/v1/metrics").json()["requests_successful"] >= 3
     assert client.get("/metrics/dispatch").json()["total_dispatches"] >= 3
-    assert client.post("/v1/embeddings", json={"input": "x"}).status_code == 501
+
+
+def test_http_scoring_endpoints(client):
+    """/v1/logprobs, /v1/perplexity and /v1/embeddings run a scoring pass on the engine thread (here the toy engine, whose
+    successor token has probability 1/2)."""
+    import math
+    r = client.post("/v1/logprobs", json={"prompt": "abc"}).json()
+    assert r["tokens"] == [97, 98, 99] and r["token_logprobs"][0] is None
+    assert all(abs(x - math.log(0.5)) < 1e-9 for x in r["token_logprobs"][1:])
+    p = client.post("/v1/perplexity", json={"text": "abcd"}).json()
+    assert abs(p["perplexity"] - 2.0) < 1e-9 and p["num_tokens"] == 4
+    assert client.post("/v1/perplexity", json={"text": "a"}).status_code == 400
+    e = client.post("/v1/embeddings", json={"input": ["ab", "c"]}).json()
+    assert [d["embedding"] for d in e["data"]] == [[97.5, 2.0], [99.0, 1.0]] and e["usage"]["prompt_tokens"] == 3
+
+
+def test_http_stop_strings_penalties_and_grammar(client):
+    """Request-level controls reach the engine: stop strings end the generation (also mid-stream, and the stop string is
+    never sent), penalties and logit_bias arrive as sampling parameters, a GBNF grammar becomes per-step token masks."""
+    body = {"model": "demo", "messages": [{"role": "user", "content": "A"}], "max_tokens": 12, "temperature": 0}
+    r = client.post("/v1/chat/completions", json={**body, "stop": ["EF"]}).json()
+    assert r["choices"][0]["message"]["content"] == "BCD" and r["choices"][0]["finish_reason"] == "stop"
+    assert r["usage"]["completion_tokens"] <= 6                      # generation ended at the stop string, not at max_tokens
+    with client.stream("POST", "/v1/chat/completions", json={**body, "stop": ["EF"], "stream": True}) as resp:
+        events = [json.loads(l[6:]) for l in resp.iter_lines() if l.startswith("data: ") and l != "data: [DONE]"]
+    assert "".join(c["choices"][0]["delta"].get("content", "") for c in events if "choices" in c) == "BCD"
+    eng = client.app.state.rlz.serving.engine
+    client.post("/v1/chat/completions", json={**body, "max_tokens": 2, "presence_penalty": 0.5, "frequency_penalty": 0.25, "repetition_penalty": 1.3,
+                                              "logit_bias": {"66": -100}, "top_k": 7, "min_p": 0.05, "temperature": 0.8})
+    last = [c for c in eng.calls if c[0] == "sampling"][-1]
+    assert last[2] == 0.8
+    got = [v for v in eng.sampling_log if v.repetition_penalty == 1.3]
+    assert got and got[-1].presence_penalty == 0.5 and got[-1].frequency_penalty == 0.25 and got[-1].logit_bias == {66: -100.0} and got[-1].top_k == 7
+    assert client.post("/v1/chat/completions", json={**body, "logit_bias": {"x": 1}}).status_code == 400
+    # grammar: only the letters x / y may follow, so the toy engine (successor of its input) is overruled by the mask
+    r = client.post("/v1/chat/completions", json={**body, "max_tokens": 4, "grammar": 'root ::= [xy]+'}).json()
+    assert set(r["choices"][0]["message"]["content"]) <= set("xy") and len(r["choices"][0]["message"]["content"]) == 4
+    assert any(c[0] == "mask" for c in eng.calls)
+    assert client.post("/v1/chat/completions", json={**body, "grammar": "root ::= ("}).status_code == 400
+    r = client.post("/v1/completions", json={"prompt": "a", "max_tokens": 8, "temperature": 0, "stop": ["de"]}).json()
+    assert r["choices"][0]["text"] == "bc" and r["choices"][0]["finish_reason"] == "stop"
