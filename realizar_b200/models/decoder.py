@@ -423,9 +423,16 @@ class DecodePlan:
         self.kernel_launches = self.kernel_launches - n + 1
         return True
 
-    def run(self):
-        for t in self.thunks:
-            t()
+    def run(self, profiler=None):
+        """Issue the launches on the current stream.  With ``profiler`` (``utils.trace.BrickProfiler``) every launch is
+        bracketed by events under the name of its kind."""
+        if profiler is None:
+            for t in self.thunks:
+                t()
+            return
+        for t, rec in zip(self.thunks, self.records):
+            with profiler.brick(rec[0] if rec is not None else "other"):
+                t()
 
 
 def emit_head(plan: "DecodePlan", model: GpuModel, buf: StepBuffers, r0: int, batch: int, comm, greedy_only: bool, sm_count: int,

@@ -80,21 +80,36 @@ class Slot:
 class DecodeEngine:
     def __init__(self, weights: ModelWeights, config: Optional[EngineConfig] = None, device="cuda", comm=None,
                  tp_rank: int = 0, tp_size: int = 1):
-        self.cfg = config or EngineConfig()
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise RuntimeError("DecodeEngine runs on a CUDA device; use models.cpu_model.CpuModel on the CPU")
+        # launch policy of this device (grids, thresholds, environment overrides) in one place; an engine built without an explicit
+        # configuration takes its defaults from it
+        from .gpu_profile import GpuProfile
+        self.profile = GpuProfile.detect(self.device.index if self.device.index is not None else torch.cuda.current_device())
+        if not self.profile.supported:
+            raise RuntimeError(f"the CUDA kernels of this library are built for sm_100a; device '{self.profile.name}' is "
+                               f"sm_{self.profile.compute_capability[0]}{self.profile.compute_capability[1]}")
+        self.cfg = config or EngineConfig(**self.profile.engine_config_overrides())
         self.comm = comm
         self.model = GpuModel(weights, self.device, tp_rank, tp_size)
         self.mcfg = self.model.cfg
         m, c, dev = self.model, self.cfg, self.device
-        props = torch.cuda.get_device_properties(self.device)
-        self.sm_count = props.multi_processor_count
+        self.sm_count = self.profile.sm_count
         B = c.max_batch
         self.max_pages_per_seq = -(-c.max_seq_len // PAGE)
         self.num_pages = c.num_pages or B * self.max_pages_per_seq
         hd = self.mcfg.head_dim
         # [2 (k,v), layers, pages, kv_heads, PAGE, head_dim] bf16
+        from .memory import check_vram_sufficient
+        row = (hd + 16) if c.kv_dtype == "q8" else 2 * hd
+        kv_bytes = 2 * self.mcfg.num_layers * self.num_pages * m.kv_heads * PAGE * row
+        free_bytes, _total = torch.cuda.mem_get_info(self.device)
+        try:                                                 # the weights are on the device already: what is left must hold the cache
+            check_vram_sufficient(0, kv_bytes, free_bytes, self.mcfg.num_layers)
+        except MemoryError:
+            raise RuntimeError(f"KV cache of {kv_bytes / 2**30:.1f} GiB ({self.num_pages} pages) does not fit the {free_bytes / 2**30:.1f} GiB "
+                               f"left on {self.profile.name}: lower max_batch / max_seq_len / num_pages or use kv_dtype='q8'") from None
         self.kv = ops.kv_cache_alloc(self.mcfg.num_layers, self.num_pages, m.kv_heads, hd, dev, c.kv_dtype, PAGE)
         self.pages = PagedKvCache(self.num_pages, PAGE)
         self.splits = c.attn_splits or self._choose_splits(B)        # at the full batch; smaller buckets split the context further
@@ -157,12 +172,7 @@ class DecodeEngine:
 
     # -- configuration helpers --------------------------------------------------------------
     def _choose_splits(self, batch: int) -> int:
-        ctas_per_split = self.model.kv_heads * max(1, batch)
-        want = max(1, (2 * self.sm_count) // max(1, ctas_per_split))
-        s = 1
-        while s * 2 <= min(8, want):          # power of two up to the cluster size: splits merge through DSMEM
-            s *= 2
-        return s
+        return self.profile.attn_splits(self.model.kv_heads, batch)     # power of two up to the cluster size: splits merge through DSMEM
 
     def splits_for(self, bucket: int) -> int:
         """Context splits of the decode attention at this batch bucket: few sequences leave SMs idle unless each head's
@@ -281,6 +291,18 @@ class DecodeEngine:
         if code:
             raise ops.KernelError(f"a device-side check failed with status {code}: a bounded wait expired or an index left its range; "
                                   "results since the last check are not valid")
+
+    def profile_step(self, batch: int = 1, steps: int = 4) -> dict:
+        """Per-operation timing of the decode step at this batch: the plan is run launch by launch (no graph) with every launch
+        bracketed by CUDA events, ``steps`` times; returns ``{kind: {total_ms, count, avg_us, share}}`` sorted by share
+        (the brick profile of the reference's executor, src/cuda/executor/ profiler hooks)."""
+        from ..utils.trace import BrickProfiler
+        plan = self.plan(self.bucket_for(batch))
+        prof = BrickProfiler(cuda=True)
+        plan.run()                                           # warm-up (kernel attributes, first touches)
+        for _ in range(max(1, steps)):
+            plan.run(profiler=prof)
+        return prof.summary()
 
     def advance(self, batch: int) -> None:
         """Device-side feedback: sampled tokens become the next inputs, positions move on."""
@@ -722,4 +744,4 @@ class DecodeEngine:
 
     def memory_report(self) -> dict:
         return {"weights_bytes": self.model.weight_bytes(), "kv_bytes": self.kv.numel() * self.kv.element_size(), "kv_pages": self.num_pages,
-                "kv_utilization": self.pages.stats().utilization}
+                "kv_utilization": self.pages.stats().utilization, "device": self.profile.describe()}

@@ -171,6 +171,71 @@ def bench_attn(a):
             "l2_note": "KV %.0f MB %s L2" % (byts / 1e6, ">" if byts > 126e6 else "<=")}
 
 
+def bench_prefill(a):
+    """Causal prompt attention over the paged cache: ``--impl mma`` (16-query tiles, mma.sync) or ``tc`` (128-query tiles, tcgen05)."""
+    os.environ["RLZ_PREFILL_ATT"] = a.impl                  # read once by the launcher, before the first launch
+    from .. import ops
+    dev = torch.device("cuda")
+    H, Hkv, d, T = a.heads, a.kv_heads, a.head_dim, a.tokens
+    pages = -(-T // 16)
+    kc = (torch.randn(pages, Hkv, 16, d, device=dev) * 0.5).to(torch.bfloat16)
+    vc = (torch.randn(pages, Hkv, 16, d, device=dev) * 0.5).to(torch.bfloat16)
+    pt = torch.randperm(pages, device=dev).to(torch.int32)
+    qkv = torch.randn(T, (H + 2 * Hkv) * d, device=dev)
+    out = torch.empty(T, H * d, device=dev, dtype=torch.bfloat16)
+    ms = time_cuda(lambda: ops.attn_prefill(qkv, out, kc, vc, pt, T, 0, H, Hkv, d), a.iters)
+    flops = 4.0 * H * d * T * (T + 1) / 2                   # QK^T and PV over the causal half
+    pk = peaks()
+    return {"kernel": "attn_prefill_" + a.impl, "tokens": T, "heads": H, "kv_heads": Hkv, "head_dim": d, "ms": ms, "tflops": flops / ms / 1e9,
+            "frac_of_%s_bf16" % pk["source"]: flops / ms / 1e9 / pk["bf16_tflops"], "error": ops.attn_prefill_error()}
+
+
+def bench_small(a):
+    """The element-wise, norm, positional, cache-write and token-selection kernels at prompt-chunk / decode sizes, each timed
+    alone: GB/s against the copy bandwidth (bytes = what the kernel has to read and write once)."""
+    from .. import ops
+    dev = torch.device("cuda")
+    T, H, heads, d, V = a.tokens, a.hidden, a.heads, a.head_dim, a.vocab
+    x = torch.randn(T, H, device=dev)
+    xb = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
+    g, b = torch.rand(H, device=dev) + 0.5, torch.randn(H, device=dev) * 0.1
+    qkv = torch.randn(T, 3 * heads * d, device=dev)
+    pos = torch.arange(T, device=dev, dtype=torch.int32)
+    table = ops.make_rope_table(T, a.rope_dim, 1e4, dev)
+    pages = -(-T // 16)
+    kc = torch.zeros(pages, heads, 16, d, device=dev, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    rows = (pos // 16).to(torch.int32).contiguous()
+    gate, up = torch.randn(T, 4 * H, device=dev), torch.randn(T, 4 * H, device=dev)
+    act = torch.empty(T, 4 * H, device=dev, dtype=torch.bfloat16)
+    logits = torch.randn(a.batch, V, device=dev)
+    temp, topk = torch.full((a.batch,), 0.7, device=dev), torch.full((a.batch,), 40, device=dev, dtype=torch.int32)
+    topp, minp, uni = torch.full((a.batch,), 0.9, device=dev), torch.zeros(a.batch, device=dev), torch.rand(a.batch, device=dev)
+    hist = torch.randint(0, V, (a.batch, 64), device=dev, dtype=torch.int32)
+    ones, zeros = torch.full((a.batch,), 1.2, device=dev), torch.full((a.batch,), 0.1, device=dev)
+    bias, on = torch.zeros(a.batch, V, device=dev), torch.ones(a.batch, device=dev, dtype=torch.int32)
+    tgt = torch.randint(0, V, (a.batch,), device=dev, dtype=torch.int32)
+    cases = {
+        "norm_bf16 (LayerNorm -> bf16 operand)": (lambda: ops.norm_bf16(x, xb, g, b, ops.NORM_LAYER, 1e-5), T * H * 6),
+        "rope_ (q and k heads, table)": (lambda: ops.rope_(qkv, pos, 2 * heads, d, a.rope_dim, 2, 1e4, table=table), T * 2 * heads * a.rope_dim * 8),
+        "kv_append (bf16 pages)": (lambda: ops.kv_append(qkv[:, heads * d:], qkv[:, 2 * heads * d:], kc, vc, pos, rows, heads, d), T * 2 * heads * d * 6),
+        "swiglu_bf16 (silu(gate) * up -> bf16)": (lambda: ops.swiglu_bf16(gate, up, act, ops.ACT_SILU), T * 4 * H * 10),
+        "to_bf16": (lambda: ops.to_bf16(x, xb), T * H * 6),
+        "argmax (%d x %d)" % (a.batch, V): (lambda: ops.argmax(logits), a.batch * V * 4),
+        "sample top-k/top-p (%d x %d)" % (a.batch, V): (lambda: ops.sample(logits, temp, topk, topp, uni, minp), a.batch * V * 4),
+        "logit_controls (bias row + penalties)": (lambda: ops.logit_controls(logits, hist, ones, zeros, zeros, bias, on), a.batch * V * 12),
+        "logprob_parts (log-softmax pieces)": (lambda: ops.logprob_parts(logits, tgt), a.batch * V * 8),
+    }
+    pk = peaks()
+    out = {"kernel": "small", "tokens": T, "hidden": H, "batch": a.batch, "vocab": V, "results": {}}
+    for name, (fn, byts) in cases.items():
+        if a.only and a.only not in name:
+            continue
+        ms = time_cuda(fn, a.iters)
+        out["results"][name] = {"us": round(ms * 1e3, 2), "gbs": round(byts / ms / 1e6, 1), "frac_of_%s_hbm" % pk["source"]: round(byts / ms / 1e6 / pk["hbm_gbs"], 3)}
+    return out
+
+
 def bench_gemm(a):
     from ..ops import gemm as gemm_ops
     from ..quant import QType
@@ -237,6 +302,14 @@ def main(argv=None):
     t.add_argument("--heads", type=int, default=32); t.add_argument("--kv-heads", type=int, default=32); t.add_argument("--head-dim", type=int, default=80)
     t.add_argument("--ctx", type=int, default=4096); t.add_argument("--batch", type=int, default=8); t.add_argument("--splits", type=int, default=0)
     t.add_argument("--rope-dim", type=int, default=32); t.add_argument("--iters", type=int, default=10)
+    pf = sub.add_parser("prefill")
+    pf.add_argument("--impl", choices=["mma", "tc"], default="mma"); pf.add_argument("--tokens", type=int, default=512)
+    pf.add_argument("--heads", type=int, default=32); pf.add_argument("--kv-heads", type=int, default=32); pf.add_argument("--head-dim", type=int, default=80)
+    pf.add_argument("--iters", type=int, default=10)
+    sm = sub.add_parser("small")
+    sm.add_argument("--tokens", type=int, default=512); sm.add_argument("--hidden", type=int, default=2560); sm.add_argument("--heads", type=int, default=32)
+    sm.add_argument("--head-dim", type=int, default=80); sm.add_argument("--rope-dim", type=int, default=32); sm.add_argument("--vocab", type=int, default=51200)
+    sm.add_argument("--batch", type=int, default=64); sm.add_argument("--iters", type=int, default=10); sm.add_argument("--only", default="")
     m = sub.add_parser("gemm")
     m.add_argument("--qtype", default="Q4_K"); m.add_argument("--n", type=int, default=10240); m.add_argument("--k", type=int, default=2560)
     m.add_argument("--m", type=int, default=512); m.add_argument("--iters", type=int, default=10)
@@ -249,7 +322,7 @@ def main(argv=None):
     if a.pdl:
         from .. import ops
         ops.set_pdl(True)
-    res = {"gemv": bench_gemv, "attn": bench_attn, "gemm": bench_gemm}[a.cmd](a)
+    res = {"gemv": bench_gemv, "attn": bench_attn, "gemm": bench_gemm, "prefill": bench_prefill, "small": bench_small}[a.cmd](a)
     print(json.dumps(res))
     return 0
 

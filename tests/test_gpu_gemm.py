@@ -125,8 +125,8 @@ def test_gemm_all_reduce_push_and_reduce_two_emulated_ranks(cuda_device):
     assert float(torch.ones(4, device="cuda").sum()) == 4.0     # the context is still usable
 
 
-@pytest.mark.parametrize("m,k,splitk", [(40, 512, 1), (70, 512, 2), (300, 768, 1)])
-def test_gemm_two_shot_all_reduce_two_emulated_ranks(cuda_device, m, k, splitk):
+@pytest.mark.parametrize("m,k,splitk,world", [(40, 512, 1, 2), (70, 512, 2, 2), (300, 768, 1, 2), (70, 512, 2, 4), (5, 512, 1, 8), (300, 512, 1, 8)])
+def test_gemm_two_shot_all_reduce_two_emulated_ranks(cuda_device, m, k, splitk, world):
     """Two-shot all-reduce of a row-parallel GEMM with two ranks emulated on one GPU, one after the other: both GEMMs store
     their tiles into the inboxes of the row owners (ownership, tile flags), then each owner's reduce kernel sums them onto
     its residual rows, applies the following norm and writes the bf16 rows into both ranks' operand buffers.  The final wait
@@ -136,7 +136,7 @@ def test_gemm_two_shot_all_reduce_two_emulated_ranks(cuda_device, m, k, splitk):
     from realizar_b200 import ops
     from realizar_b200.ops import gemm as G
     from realizar_b200.ops import _signatures as S
-    n, world, splits, site, nsites = 384, 2, 2, 1, 4
+    n, splits, site, nsites = 384, 2, 1, 4
     own_rows = -(-m // world)
     own_cap, ntiles, mtiles = own_rows + 3, -(-n // 128), -(-m // 32) + 1
     ws = [_weight(n, k, QType.Q4_K if k % 256 == 0 else QType.BF16, 40 + r) for r in range(world)]
@@ -189,7 +189,7 @@ def test_gemm_two_shot_all_reduce_two_emulated_ranks(cuda_device, m, k, splitk):
     for q in range(world):                                    # fp32 rows and bf16 rows of BOTH owners arrived on every rank
         assert float((xres[q].cpu() - ref).abs().max() / ref.abs().max()) < 2e-2
         assert float((xb[q].float().cpu() - refb).abs().max() / refb.abs().max()) < 3e-2
-    assert torch.equal(xres[0], xres[1]) and torch.equal(xb[0], xb[1])
+    assert all(torch.equal(xres[0], xres[q]) and torch.equal(xb[0], xb[q]) for q in range(1, world))
     for q in range(world):                                    # every owned row published its tag to every rank
         got = ag[q].reshape(world, own_cap)
         for o in range(world):
@@ -205,9 +205,9 @@ def test_gemm_two_shot_all_reduce_two_emulated_ranks(cuda_device, m, k, splitk):
     assert int(status.item()) == 2004
     status.zero_()
     epoch.fill_(7)
-    ag[0].zero_()
-    ag[1].zero_()
-    reduce(1, push_x=False, to_xb=False, wait=True, limit=50)          # rank 1 publishes its own rows, rank 0's never arrive
+    for q in range(world):
+        ag[q].zero_()
+    reduce(1, push_x=False, to_xb=False, wait=True, limit=50)          # rank 1 publishes its own rows, the other ranks' never arrive
     assert int(status.item()) == 2005
     assert float(torch.ones(4, device="cuda").sum()) == 4.0     # the context is still usable
 
