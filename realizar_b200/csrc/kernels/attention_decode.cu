@@ -41,9 +41,8 @@ template <int GT, int MERGE, int HD>
 __global__ void __launch_bounds__(ATT_THREADS) attn_decode_mma_kernel(const __grid_constant__ AttnDecodeParams p) {
   __shared__ AttnSmem<GT, MERGE> sm;
   extern __shared__ __align__(128) uint8_t att_ring[];
-  pdl_launch_dependents();
-  pdl_wait();
-  attn_decode_body<GT, MERGE, 3, 0, 0, false, HD>(p, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, (int)threadIdx.x, sm, 0, att_ring);
+  pdl_launch_dependents();                                  // the body waits for the preceding kernel itself, after its K/V prefetch
+  attn_decode_body<GT, MERGE, 3, 0, 0, false, HD, true>(p, (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, (int)threadIdx.x, sm, 0, att_ring);
 }
 
 template <int GT, int MERGE, int HD>

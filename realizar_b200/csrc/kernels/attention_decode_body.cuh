@@ -137,7 +137,43 @@ template <int GT, int MERGE> struct AttnSmem {
 // (padded to HD * 2 + 16 bytes so that fragment loads are conflict-free) and computes S = Q K^T and O += P V of its stages
 // with mma.sync m16n8k16 (rows = the query heads of the group, padded to 16), about a seventh of the instructions per token
 // of the scalar path; the warps' partial results meet in the same merge as the other modes.
-template <int GT, int MERGE, int DEEP, int Q8, int TBO, bool SUB, int HD = 0>
+// Tensor-core mode: request the 32 token rows of iteration `it` into warp `warp`'s ring slot - whole pages with one bulk copy each
+// at head_dim 80, else one copy per K and V row (every lane its token's rows).
+template <int HD>
+__device__ __forceinline__ void att_mma_issue(const AttnDecodeParams& p, uint8_t* ring, unsigned long long* fb, int warp, int lane, int it, int start,
+                                              int end, bool pt_staged, const int* pt_s, const int32_t* pt, int kvh) {
+  constexpr bool PAGE_COPY = HD == 80;
+  constexpr int RS = PAGE_COPY ? 2 * HD : 2 * HD + 16, SLOT = 64 * RS;
+  uint8_t* slot = ring + (size_t)warp * SLOT;
+  const int tok0 = start + it * 32, nvalid = min(32, end - tok0);
+  if (PAGE_COPY) {
+    const int np = (nvalid + ATT_PAGE - 1) / ATT_PAGE;                 // whole pages: lanes 0..3 = (K, V) x (page 0, page 1)
+    if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(att_smem_u32(fb)), "r"((uint32_t)(np * 2 * ATT_PAGE * RS)) : "memory");
+    __syncwarp();
+    if (lane < 4 && (lane & 1) < np) {
+      const int tok = tok0 + (lane & 1) * ATT_PAGE;
+      const int page = pt_staged ? pt_s[(tok - start) / ATT_PAGE] : att_page(p, pt[tok / ATT_PAGE]);
+      const int64_t boff = ((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE * RS;
+      const uint8_t* src = (lane & 2 ? (const uint8_t*)p.v_cache : (const uint8_t*)p.k_cache) + boff;
+      att_bulk_g2s(slot + ((lane & 2 ? 32 : 0) + (lane & 1) * ATT_PAGE) * RS, src, ATT_PAGE * RS, fb);
+    }
+    return;
+  }
+  if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(att_smem_u32(fb)), "r"((uint32_t)(nvalid * 4 * HD)) : "memory");
+  __syncwarp();
+  if (lane < nvalid) {
+    const int tok = tok0 + lane;
+    const int page = pt_staged ? pt_s[(tok - start) / ATT_PAGE] : att_page(p, pt[tok / ATT_PAGE]);
+    const int64_t rowi = ((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE + (tok % ATT_PAGE);
+    att_bulk_g2s(slot + lane * RS, (const uint8_t*)p.k_cache + rowi * (2 * HD), 2 * HD, fb);
+    att_bulk_g2s(slot + (32 + lane) * RS, (const uint8_t*)p.v_cache + rowi * (2 * HD), 2 * HD, fb);
+  }
+}
+
+// WAITS: the body itself waits for the preceding kernel (programmatic dependent launch), after the work that does not depend on
+// it: in the tensor-core mode of a decode step the first K/V stage of every warp is requested before that wait - the cached
+// rows were written by earlier steps, only the new row comes from the preceding GEMV and it is patched in from shared memory.
+template <int GT, int MERGE, int DEEP, int Q8, int TBO, bool SUB, int HD = 0, bool WAITS = false>
 __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, const int bx, const int split, const int b, const int tid,
                                                  AttnSmem<GT, MERGE>& sm, const int bar, uint8_t* ring = nullptr) {
 #define ATT_SYNC() do { if (SUB) asm volatile("bar.sync %0, %1;" ::"r"(bar), "n"(ATT_THREADS) : "memory"); else __syncthreads(); } while (0)
@@ -154,9 +190,10 @@ __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, cons
   auto& pt_s = sm.pt_s; auto& qs_s = sm.qs_s; int& last_flag = sm.last_flag;
 
   const int pos = p.positions[b];
-  if (pos < 0) return;                                   // uniform over the cluster (same sequence)
+  if (pos < 0) { if constexpr (WAITS) pdl_wait(); return; }   // uniform over the cluster (same sequence); the grid still orders after its predecessor
   if (p.max_pages > 0 && pos / ATT_PAGE >= p.max_pages) {  // the position has run past the sequence's page-table row: touch nothing
     if (tid == 0) atomicExch(&g_attn_decode_error, 3301);
+    if constexpr (WAITS) pdl_wait();
     return;
   }
   if (PUSH) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");     // phase 1: "I have started"; waited on before the push
@@ -173,6 +210,19 @@ __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, cons
   const int npages = (max(0, end - start) + ATT_PAGE - 1) / ATT_PAGE;
   const bool pt_staged = npages <= ATT_PT_MAX;
   if (pt_staged && tid < npages) pt_s[tid] = att_page(p, pt[start / ATT_PAGE + tid]);
+  bool prefetched = false;
+  if constexpr (DEEP == 3 && WAITS) {
+    // rows appended by a kernel that runs right before this one (token-batch passes: no_append) must be waited for first
+    prefetched = !p.no_append;
+    if (tid == 0) {
+      for (int i = 0; i < ATT_RING; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(att_smem_u32(&sm.full[i])));
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    ATT_SYNC();                                            // barriers initialised, page-table entries staged
+    if (prefetched && warp < (max(0, end - start) + 31) / 32)
+      att_mma_issue<HD>(p, ring, &sm.full[warp], warp, lane, warp, start, end, pt_staged, pt_s, pt, kvh);
+    pdl_wait();
+  }
   const float* row = p.qkv + (int64_t)b * p.ld_qkv;
   for (int i = tid; i < gn * d; i += ATT_THREADS) {
     const int g = i / d, j = i - g * d;
@@ -277,38 +327,15 @@ __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, cons
     uint8_t* slot = ring + (size_t)warp * SLOT;
     unsigned long long* fb = &sm.full[warp];
     const int gq = lane >> 2, tq = lane & 3;                               // fragment coordinates: row group, thread in group
-    if (tid == 0) {
-      for (int i = 0; i < ATT_RING; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(att_smem_u32(&sm.full[i])));
-      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if constexpr (!WAITS) {
+      if (tid == 0) {
+        for (int i = 0; i < ATT_RING; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(att_smem_u32(&sm.full[i])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      }
+      ATT_SYNC();
     }
-    ATT_SYNC();
-    // request the 32 token rows of iteration `it` into this warp's slot: every lane copies the K and V row of its token
-    auto issue = [&](int it) {
-      const int tok0 = start + it * 32, nvalid = min(32, end - tok0);
-      if (PAGE_COPY) {
-        const int np = (nvalid + ATT_PAGE - 1) / ATT_PAGE;                 // whole pages: lanes 0..3 = (K, V) x (page 0, page 1)
-        if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(att_smem_u32(fb)), "r"((uint32_t)(np * 2 * ATT_PAGE * RS)) : "memory");
-        __syncwarp();
-        if (lane < 4 && (lane & 1) < np) {
-          const int tok = tok0 + (lane & 1) * ATT_PAGE;
-          const int page = pt_staged ? pt_s[(tok - start) / ATT_PAGE] : att_page(p, pt[tok / ATT_PAGE]);
-          const int64_t boff = ((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE * RS;
-          const uint8_t* src = (lane & 2 ? (const uint8_t*)p.v_cache : (const uint8_t*)p.k_cache) + boff;
-          att_bulk_g2s(slot + ((lane & 2 ? 32 : 0) + (lane & 1) * ATT_PAGE) * RS, src, ATT_PAGE * RS, fb);
-        }
-        return;
-      }
-      if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(att_smem_u32(fb)), "r"((uint32_t)(nvalid * 4 * HD)) : "memory");
-      __syncwarp();
-      if (lane < nvalid) {
-        const int tok = tok0 + lane;
-        const int page = pt_staged ? pt_s[(tok - start) / ATT_PAGE] : att_page(p, pt[tok / ATT_PAGE]);
-        const int64_t rowi = ((int64_t)page * p.n_kv_heads + kvh) * ATT_PAGE + (tok % ATT_PAGE);
-        att_bulk_g2s(slot + lane * RS, (const uint8_t*)p.k_cache + rowi * (2 * HD), 2 * HD, fb);
-        att_bulk_g2s(slot + (32 + lane) * RS, (const uint8_t*)p.v_cache + rowi * (2 * HD), 2 * HD, fb);
-      }
-    };
-    if (warp < iters) issue(warp);
+    auto issue = [&](int it) { att_mma_issue<HD>(p, ring, fb, warp, lane, it, start, end, pt_staged, pt_s, pt, kvh); };
+    if (!prefetched && warp < iters) issue(warp);
     // Q fragments (row = query head gq, pre-scaled): a0 = dims 2tq, 2tq+1 of a k step, a2 = the same + 8.  q is split into a
     // bf16 head and a bf16 remainder (two MMAs per tile) so that the scores keep fp32-like precision in q
     uint32_t qa[KS][2], qb[KS][2];
