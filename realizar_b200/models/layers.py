@@ -203,6 +203,30 @@ class Attention(torch.nn.Module):
         return self.o(out), (k, v)
 
 
+    def forward_streaming(self, x: torch.Tensor, cache, layer: int = 0) -> torch.Tensor:
+        """Token-by-token decoding over a ring-buffer cache (``runtime.streaming_kv.StreamingKVCache``): memory stays at
+        ``cache.window`` positions however long the stream runs; every new token attends to the retained sink positions and the
+        most recent ones, at their absolute positions.  With no sinks this equals ``forward`` with ``window = cache.window``.
+        ``x`` [T, dim]; returns [T, dim]."""
+        outs = []
+        for t in range(x.shape[0]):
+            q, k, v = self.project(x[t:t + 1])
+            q, k, v = q.view(1, self.heads, self.hd), k.view(1, self.kv_heads, self.hd), v.view(1, self.kv_heads, self.hd)
+            p = cache.length[layer]
+            pos = torch.tensor([p])
+            if self.rope is not None:
+                q, k = self.rope.apply(q, pos, p + 1), self.rope.apply(k, pos, p + 1)
+            cache.append(layer, k[0], v[0])
+            ks, vs, kpos = cache.get(layer)
+            rep = self.heads // self.kv_heads
+            kh, vh = ks.float().repeat_interleave(rep, 1).transpose(0, 1), vs.float().repeat_interleave(rep, 1).transpose(0, 1)
+            s = q.transpose(0, 1) @ kh.transpose(1, 2) * self.hd ** -0.5          # [heads, 1, retained]
+            if self.alibi is not None:
+                s = s - self.alibi.slopes[:, None, None] * (p - kpos)[None, None, :].float()
+            outs.append((torch.softmax(s, -1) @ vh).transpose(0, 1).reshape(1, -1))
+        return self.o(torch.cat(outs))
+
+
 def FusedQKVAttention(dim, heads, **kw):
     return Attention(dim, heads, fused_qkv=True, **kw)
 

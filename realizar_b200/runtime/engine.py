@@ -304,6 +304,30 @@ class DecodeEngine:
             plan.run(profiler=prof)
         return prof.summary()
 
+    def brick_report(self, batch: int = 1, steps: int = 4, efficiency: float = 0.5) -> dict:
+        """The decode step as compute bricks with roofline budgets: the weight-streaming launches against ``weight bytes /
+        (copy bandwidth x efficiency)``, attention against the cached K/V bytes of the open sequences, measured with
+        ``profile_step``; names the bottleneck (largest time above its budget).  Role of the reference's brick budgets and
+        bottleneck report (src/brick/mod.rs:47-442)."""
+        from ..utils.bricks import ComputeBrick, TokenBudget, TransformerLayerBrick
+        from ..utils.kernel_bench import peaks
+        bw = peaks()["hbm_gbs"]
+        prof = self.profile_step(batch, steps)
+        ctx = sum(max(0, s.position) for s in self.slots[:batch] if s.active)
+        kv_bytes = 2 * self.mcfg.num_layers * self.mcfg.num_kv_heads * self.mcfg.head_dim * ctx * (1 if self.cfg.kv_dtype == "q8" else 2)
+        nbytes = {"gemv": self.model.weight_bytes(), "gemm": self.model.weight_bytes(), "attn": kv_bytes}
+        bricks = []
+        for kind, st in prof.items():
+            b = ComputeBrick(kind, TokenBudget.from_bytes(max(1, nbytes.get(kind, 1)), bw, efficiency), bytes_moved=nbytes.get(kind, 0))
+            b.record(1e3 * st["total_ms"] / max(1, steps))
+            bricks.append(b)
+        layer = TransformerLayerBrick(bricks)
+        worst = layer.bottleneck()
+        return {"bandwidth_gbs": bw, "efficiency": efficiency, "step_us": layer.total_actual_us(), "budget_us": layer.total_budget_us(),
+                "bricks": {b.name: {"us_per_step": b.last_us, "budget_us": b.budget.us_per_token, "gbs": b.achieved_gbs(), "launches": prof[b.name]["count"] // max(1, steps)}
+                           for b in bricks},
+                "bottleneck": None if worst is None else {"brick": worst.brick, "gap": worst.gap, "share": worst.share}}
+
     def advance(self, batch: int) -> None:
         """Device-side feedback: sampled tokens become the next inputs, positions move on."""
         ops.advance_(self.buf.tokens[:batch], self.buf.sampled[:batch], self.buf.positions[:batch], limit=self.cfg.max_seq_len)

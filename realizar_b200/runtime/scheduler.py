@@ -256,6 +256,8 @@ class Scheduler:
         r.state, r.finish_reason, r.error = RequestState.FINISHED, reason, error
         r.finish_time = time.monotonic() if now is None else now
         self.stats["finished"] += 1
+        if getattr(self, "on_finished", None) is not None:   # the owner's per-request accounting
+            self.on_finished(r)
         if r.on_finish is not None:
             try:
                 r.on_finish(r)
@@ -303,6 +305,14 @@ class ServingEngine:
         self.last_error: Optional[str] = None
         self.step_times: Deque[float] = deque(maxlen=512)
         self._lock = threading.Lock()
+        from .batch_types import InferenceEventNotifier, InferenceMetrics
+        self.inference = InferenceMetrics()                  # per-request latency / token counters (reported by metrics())
+        self.notifier = InferenceEventNotifier()             # callbacks (request id, latency ms, tokens) at the end of every request
+        self.notifier.register(lambda _rid, ms, n: self.inference.record(ms, n))
+        self.sched.on_finished = self._request_finished
+
+    def _request_finished(self, r: "Request") -> None:
+        self.notifier.notify(r.id, 1e3 * (time.monotonic() - r.arrival), len(r.output))
 
     # -- public ---------------------------------------------------------------------------------
     def start(self) -> "ServingEngine":
@@ -332,24 +342,19 @@ class ServingEngine:
         KV snapshots: anything that needs the engine while requests are being served)."""
         if self.health != "ok":
             raise RuntimeError(f"engine is {self.health}: {self.last_error}")
-        done = threading.Event()
-        box: dict = {}
+        from .batch_types import AsyncGpuResult
+        res = AsyncGpuResult()
 
         def job(engine):
             try:
-                box["value"] = fn(engine)
+                res.set_result(fn(engine))
             except Exception as e:                           # delivered to the caller, the serving loop goes on
-                box["error"] = e
-            done.set()
+                res.set_error(e)
         if self._thread is None:                             # no worker thread (tests that drive step() themselves)
             job(self.engine)
         else:
             self._calls.put(job)
-        if not done.wait(timeout):
-            raise TimeoutError("engine call timed out")
-        if "error" in box:
-            raise box["error"]
-        return box.get("value")
+        return res.wait(timeout)                             # TimeoutError when the loop did not get to it in time
 
     def generate(self, prompt: Sequence[int], timeout: Optional[float] = None, **kw) -> Request:
         """Blocking convenience: submit and wait for completion."""
@@ -460,18 +465,21 @@ class ServingEngine:
         if (r.slot != 0 or r.temperature > 0 or r.token_masker is not None or r.logit_bias or r.repetition_penalty != 1.0
                 or r.presence_penalty or r.frequency_penalty or not getattr(eng, "gemm_ok", False)):
             return False
+        from .batch_types import SpeculativeBuffer
         from .speculative import verify_greedy
         k = min(self.spec_k, r.max_tokens - len(r.output) - 1, self.cfg.max_seq_len - r.total_len - 2)
         if k < 1:
             return False
         pos0 = eng.slots[0].position
-        last, drafts, feed = r.output[-1], [], r.output[-1]
+        last, feed, buf = r.output[-1], r.output[-1], SpeculativeBuffer(capacity=k)
         for _ in range(k):
             feed = eng.draft_step(0, int(feed), self.draft_layers)
-            drafts.append(int(feed))
+            buf.add_candidate(int(feed), 1.0)
+        drafts = [t for t, _ in buf.items]
         eng.rollback(0, pos0)
         nxt = eng.forward_tokens(0, [last] + drafts)
         v = verify_greedy(drafts, nxt)
+        assert buf.verify(nxt)[0] == v.accepted
         eng.rollback(0, pos0 + 1 + v.accepted)
         self.spec_stats["rounds"] += 1
         self.spec_stats["drafted"] += k
@@ -505,7 +513,9 @@ class ServingEngine:
     def metrics(self) -> dict:
         st = list(self.step_times)
         snap = self.sched.snapshot()
-        snap.update({"health": self.health, "avg_step_ms": 1e3 * sum(st) / len(st) if st else 0.0, "queue_depth": self._inbox.qsize() + snap["waiting"]})
+        snap.update({"health": self.health, "avg_step_ms": 1e3 * sum(st) / len(st) if st else 0.0, "queue_depth": self._inbox.qsize() + snap["waiting"],
+                     "requests_done": self.inference.total_inferences, "request_latency_ms_p50": self.inference.percentile(50),
+                     "request_latency_ms_p99": self.inference.percentile(99)})
         return snap
 
 

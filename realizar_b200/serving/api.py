@@ -16,6 +16,7 @@ import math
 import threading
 import time
 import uuid
+from collections import deque
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional
 
@@ -133,6 +134,8 @@ class AppState:
     vocab_strings: Optional[List[str]] = None       # text of every token id, built on the first grammar-constrained request
     context_length: int = 4096
     classical: Any = None               # optional ClassicalServeState behind /v1/predict, /v1/explain
+    route_latency: Dict[str, Any] = field(default_factory=dict)      # path -> LatencyHistogram of whole HTTP requests
+    spans: Any = field(default_factory=lambda: deque(maxlen=256))    # finished request spans, newest last (GET /v1/traces)
 
     @classmethod
     def demo(cls) -> "AppState":
@@ -152,6 +155,32 @@ def create_app(state: AppState) -> FastAPI:
     app = FastAPI(title="realizar-b200", version=__version__)
     app.add_middleware(CORSMiddleware, allow_origins=["*"], allow_methods=["*"], allow_headers=["*"])
     app.state.rlz = state
+
+    @app.middleware("http")
+    async def _trace(request: HttpRequest, call_next):
+        """W3C trace context in and out (``traceparent``), one span and one latency observation per HTTP request
+        (role of the reference's trace-context / span / latency-histogram types, src/observability/mod.rs:47-421)."""
+        from ..utils.observability import LatencyHistogram, Span, TraceContext
+        ctx = TraceContext.from_traceparent(request.headers.get("traceparent", "")) or TraceContext.new()
+        span = Span(f"{request.method} {request.url.path}", ctx)
+        try:
+            resp = await call_next(request)
+        except Exception:
+            state.spans.append(span.end(ok=False))
+            raise
+        span.set("http.status_code", resp.status_code).end(ok=resp.status_code < 500)
+        state.spans.append(span)
+        hist = state.route_latency.get(request.url.path)
+        if hist is None and len(state.route_latency) < 64:           # unknown paths (404 probes) must not grow the table without bound
+            hist = state.route_latency[request.url.path] = LatencyHistogram()
+        if hist is not None:
+            hist.observe(span.duration_ms)
+        resp.headers["traceparent"] = ctx.to_traceparent()
+        return resp
+
+    @app.get("/v1/traces")
+    async def traces(limit: int = 50):
+        return {"spans": [sp.to_otel() for sp in list(state.spans)[-max(1, min(limit, 256)):]]}
 
     @app.exception_handler(RequestValidationError)
     async def _validation(_req, exc: RequestValidationError):
@@ -357,6 +386,8 @@ def create_app(state: AppState) -> FastAPI:
         snap = state.metrics.snapshot()
         if state.serving is not None:
             snap["scheduler"] = state.serving.metrics()
+        snap["http_latency_ms"] = {path: {"count": h.total, "mean": round(h.mean_ms, 3), "p50_le": h.percentile(50), "p99_le": h.percentile(99)}
+                                   for path, h in state.route_latency.items()}
         return snap
 
     @app.get("/metrics/dispatch")

@@ -304,3 +304,19 @@ def test_engine_int8_kv_cache_tracks_bf16(cuda_device):
     for a, b in zip(res["bf16"][1][:3], res["q8"][1][:3]):
         assert _cos(a, b) > 0.995
     assert res["bf16"][0][:2] == res["q8"][0][:2]
+
+
+def test_profile_step_and_brick_report(cuda_device):
+    from realizar_b200.models.weights import synthetic_weights
+    from realizar_b200.runtime.engine import DecodeEngine, EngineConfig
+    w = synthetic_weights(small_phi2(), scheme="Q4_K_M", seed=1, std=0.05)
+    eng = DecodeEngine(w, EngineConfig(max_batch=2, max_seq_len=128, greedy_only=True))
+    eng.open_slot(0, 64)
+    eng.prefill(0, [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12])
+    prof = eng.profile_step(1, steps=2)
+    assert {"gemv", "attn"} <= set(prof) and abs(sum(v["share"] for v in prof.values()) - 1.0) < 1e-6
+    assert prof["attn"]["count"] == 2 * small_phi2().num_layers
+    rep = eng.brick_report(1, steps=2)
+    assert rep["bottleneck"]["brick"] in rep["bricks"] and rep["step_us"] > 0
+    assert rep["bricks"]["gemv"]["budget_us"] == pytest.approx(eng.model.weight_bytes() / (rep["bandwidth_gbs"] * 1e3 * 0.5))
+    assert rep["bricks"]["attn"]["launches"] == small_phi2().num_layers

@@ -409,3 +409,22 @@ def test_classical_http_endpoints():
         assert c.get("/v1/audit/none").status_code == 404
     finally:
         st.serving.stop()
+
+
+def test_attention_over_ring_buffer_cache_equals_sliding_window():
+    import torch
+    from realizar_b200.models.layers import Attention, RoPE
+    from realizar_b200.runtime.streaming_kv import StreamingKVCache
+    torch.manual_seed(0)
+    att = Attention(32, 4, kv_heads=2, rope=RoPE(8, 1e4), window=6)
+    x = torch.randn(20, 32)
+    with torch.no_grad():
+        full, _ = att(x)                                        # whole sequence at once, window mask
+        cache = StreamingKVCache(1, 6, 2, 8)
+        ring = att.forward_streaming(x, cache)                  # token by token, six positions of memory
+    assert cache.length[0] == 20 and cache.valid(0) == 6
+    assert torch.allclose(full, ring, atol=1e-5)
+    # with sink positions the first tokens stay visible: the result differs from the plain window once the ring has wrapped
+    with torch.no_grad():
+        sunk = att.forward_streaming(x, StreamingKVCache(1, 6, 2, 8, sinks=2))
+    assert torch.allclose(full[:6], sunk[:6], atol=1e-5) and not torch.allclose(full[10:], sunk[10:], atol=1e-4)

@@ -283,3 +283,25 @@ def test_http_stop_strings_penalties_and_grammar(client):
     assert client.post("/v1/chat/completions", json={**body, "grammar": "root ::= ("}).status_code == 400
     r = client.post("/v1/completions", json={"prompt": "a", "max_tokens": 8, "temperature": 0, "stop": ["de"]}).json()
     assert r["choices"][0]["text"] == "bc" and r["choices"][0]["finish_reason"] == "stop"
+
+
+def test_trace_context_is_propagated_and_requests_are_recorded():
+    from fastapi.testclient import TestClient
+    from realizar_b200.serving.api import AppState, create_app
+    state = AppState.demo()
+    try:
+        with TestClient(create_app(state)) as c:
+            tid = "4bf92f3577b34da6a3ce929d0e0e4736"
+            r = c.get("/health", headers={"traceparent": f"00-{tid}-00f067aa0ba902b7-01"})
+            assert r.status_code == 200 and r.headers["traceparent"].split("-")[1] == tid      # same trace, new span id
+            assert r.headers["traceparent"].split("-")[2] != "00f067aa0ba902b7"
+            r2 = c.get("/health")                                                             # no header: a new trace is started
+            assert len(r2.headers["traceparent"].split("-")[1]) == 32 and r2.headers["traceparent"].split("-")[1] != tid
+            spans = c.get("/v1/traces").json()["spans"]
+            assert spans[0]["traceId"] == tid and spans[0]["parentSpanId"] == "00f067aa0ba902b7" and spans[0]["name"] == "GET /health"
+            lat = c.get("/v1/metrics").json()["http_latency_ms"]
+            assert lat["/health"]["count"] == 2
+            sched = c.get("/v1/metrics").json()["scheduler"]
+            assert "requests_done" in sched
+    finally:
+        state.serving.stop()
