@@ -206,13 +206,78 @@ __global__ void page_rows_kernel(const int32_t* page_table, int64_t ld, const in
 }
 
 // bf16 producers for the tensor-core GEMM operands
+__device__ __forceinline__ uint2 pack_bf16x4(float a, float b, float c, float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  return make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
+
+// VEC: four columns per thread (16-byte loads, 8-byte stores); the launcher picks it when columns, leading dimensions and
+// base addresses allow
+template <bool VEC>
 __global__ void to_bf16_kernel(const float* src, __nv_bfloat16* dst, int64_t rows, int cols, int64_t ld_s, int64_t ld_d) {
   pdl_launch_dependents();
   pdl_wait();
+  if (VEC) {
+    const int c4 = cols >> 2;
+    const int64_t total = rows * c4;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+      const int64_t r = idx / c4; const int c = (int)(idx - r * c4) << 2;
+      const float4 v = *reinterpret_cast<const float4*>(src + r * ld_s + c);
+      *reinterpret_cast<uint2*>(dst + r * ld_d + c) = pack_bf16x4(v.x, v.y, v.z, v.w);
+    }
+    return;
+  }
   const int64_t total = rows * cols;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = idx / cols; const int c = (int)(idx - r * cols);
     dst[r * ld_d + c] = __float2bfloat16_rn(src[r * ld_s + c]);
+  }
+}
+
+// One pass over a row held in registers: up to NORM_REGV float4 per thread (rows up to 4 * NORM_REGV * blockDim columns), the
+// statistics from the registers (LayerNorm: mean, then the centred sum of squares), packed bf16x4 stores
+constexpr int NORM_REGV = 4;
+__global__ void __launch_bounds__(512) norm_bf16_vec_kernel(const float* x, const float* w, const float* b, __nv_bfloat16* y, int n, int64_t ld_x,
+                                                            int64_t ld_y, int norm_type, float eps) {
+  __shared__ float red[40];
+  pdl_launch_dependents();
+  pdl_wait();
+  const float4* xr = reinterpret_cast<const float4*>(x + (int64_t)blockIdx.x * ld_x);
+  const int n4 = n >> 2;
+  float4 v[NORM_REGV];
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < NORM_REGV; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    v[j] = i < n4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    s += norm_type == NORM_LAYER ? (v[j].x + v[j].y) + (v[j].z + v[j].w) : (v[j].x * v[j].x + v[j].y * v[j].y) + (v[j].z * v[j].z + v[j].w * v[j].w);
+  }
+  s = block_sum(s, red);
+  float mean = 0.f, rstd = 1.f;
+  if (norm_type == NORM_LAYER) {
+    mean = s / (float)n;
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NORM_REGV; ++j) {
+      if (threadIdx.x + j * blockDim.x < n4) {
+        const float a = v[j].x - mean, c = v[j].y - mean, d = v[j].z - mean, e = v[j].w - mean;
+        ss += (a * a + c * c) + (d * d + e * e);
+      }
+    }
+    rstd = rsqrtf(block_sum(ss, red) / (float)n + eps);
+  } else if (norm_type == NORM_RMS) {
+    rstd = rsqrtf(s / (float)n + eps);
+  }
+  uint2* yr = reinterpret_cast<uint2*>(y + (int64_t)blockIdx.x * ld_y);
+#pragma unroll
+  for (int j = 0; j < NORM_REGV; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    if (i < n4) {
+      float4 o = make_float4((v[j].x - mean) * rstd, (v[j].y - mean) * rstd, (v[j].z - mean) * rstd, (v[j].w - mean) * rstd);
+      if (w) { const float4 g = reinterpret_cast<const float4*>(w)[i]; o.x *= g.x; o.y *= g.y; o.z *= g.z; o.w *= g.w; }
+      if (b) { const float4 g = reinterpret_cast<const float4*>(b)[i]; o.x += g.x; o.y += g.y; o.z += g.z; o.w += g.w; }
+      yr[i] = pack_bf16x4(o.x, o.y, o.z, o.w);
+    }
   }
 }
 
@@ -242,10 +307,24 @@ __global__ void norm_bf16_kernel(const float* x, const float* w, const float* b,
   }
 }
 
+template <bool VEC>
 __global__ void swiglu_bf16_kernel(const float* gate, const float* up, __nv_bfloat16* y, int64_t rows, int cols, int64_t ld_g, int64_t ld_u,
                                    int64_t ld_y, int act) {
   pdl_launch_dependents();
   pdl_wait();
+  if (VEC) {
+    const int c4 = cols >> 2;
+    const int64_t total = rows * c4;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+      const int64_t r = idx / c4; const int c = (int)(idx - r * c4) << 2;
+      float4 v = *reinterpret_cast<const float4*>(gate + r * ld_g + c);
+      if (act == ACT_GELU) { v.x = gelu_tanh(v.x); v.y = gelu_tanh(v.y); v.z = gelu_tanh(v.z); v.w = gelu_tanh(v.w); }
+      else if (act == ACT_SILU) { v.x = silu(v.x); v.y = silu(v.y); v.z = silu(v.z); v.w = silu(v.w); }
+      if (up) { const float4 u = *reinterpret_cast<const float4*>(up + r * ld_u + c); v.x *= u.x; v.y *= u.y; v.z *= u.z; v.w *= u.w; }
+      *reinterpret_cast<uint2*>(y + r * ld_y + c) = pack_bf16x4(v.x, v.y, v.z, v.w);
+    }
+    return;
+  }
   const int64_t total = rows * cols;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = idx / cols; const int c = (int)(idx - r * cols);
@@ -275,21 +354,32 @@ extern "C" {
 using namespace rlz;
 
 static int ew_grid(long long total) { long long g = (total + 255) / 256; if (g > 148 * 8) g = 148 * 8; if (g < 1) g = 1; return (int)g; }
+static bool al16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+static bool al8(const void* p) { return ((uintptr_t)p & 7) == 0; }
 
 int rlz_to_bf16(const float* src, void* dst, long long rows, int cols, long long ld_s, long long ld_d, void* stream) {
-  return (int)launch(to_bf16_kernel, dim3(ew_grid(rows * cols)), dim3(256), 0, (cudaStream_t)stream, src, (__nv_bfloat16*)dst, (int64_t)rows, cols,
+  if (cols % 4 == 0 && ld_s % 4 == 0 && ld_d % 4 == 0 && al16(src) && al8(dst))
+    return (int)launch(to_bf16_kernel<true>, dim3(ew_grid(rows * cols / 4)), dim3(256), 0, (cudaStream_t)stream, src, (__nv_bfloat16*)dst,
+                       (int64_t)rows, cols, (int64_t)ld_s, (int64_t)ld_d);
+  return (int)launch(to_bf16_kernel<false>, dim3(ew_grid(rows * cols)), dim3(256), 0, (cudaStream_t)stream, src, (__nv_bfloat16*)dst, (int64_t)rows, cols,
                      (int64_t)ld_s, (int64_t)ld_d);
 }
 
 int rlz_norm_bf16(const float* x, const float* w, const float* b, void* y, int rows, int n, long long ld_x, long long ld_y, int norm_type,
                   float eps, void* stream) {
+  if (n % 4 == 0 && n <= 2048 * NORM_REGV && ld_x % 4 == 0 && ld_y % 4 == 0 && al16(x) && al8(y) && (!w || al16(w)) && (!b || al16(b)))
+    return (int)launch(norm_bf16_vec_kernel, dim3(rows), dim3(n <= 512 * NORM_REGV ? 128 : n <= 1024 * NORM_REGV ? 256 : 512), 0, (cudaStream_t)stream, x, w, b,
+                       (__nv_bfloat16*)y, n, (int64_t)ld_x, (int64_t)ld_y, norm_type, eps);
   return (int)launch(norm_bf16_kernel, dim3(rows), dim3(n >= 2048 ? 512 : 256), 0, (cudaStream_t)stream, x, w, b, (__nv_bfloat16*)y, n,
                      (int64_t)ld_x, (int64_t)ld_y, norm_type, eps);
 }
 
 int rlz_swiglu_bf16(const float* gate, const float* up, void* y, long long rows, int cols, long long ld_g, long long ld_u, long long ld_y,
                     int act, void* stream) {
-  return (int)launch(swiglu_bf16_kernel, dim3(ew_grid(rows * cols)), dim3(256), 0, (cudaStream_t)stream, gate, up, (__nv_bfloat16*)y,
+  if (cols % 4 == 0 && ld_g % 4 == 0 && ld_y % 4 == 0 && al16(gate) && al8(y) && (!up || (ld_u % 4 == 0 && al16(up))))
+    return (int)launch(swiglu_bf16_kernel<true>, dim3(ew_grid(rows * cols / 4)), dim3(256), 0, (cudaStream_t)stream, gate, up, (__nv_bfloat16*)y,
+                       (int64_t)rows, cols, (int64_t)ld_g, (int64_t)ld_u, (int64_t)ld_y, act);
+  return (int)launch(swiglu_bf16_kernel<false>, dim3(ew_grid(rows * cols)), dim3(256), 0, (cudaStream_t)stream, gate, up, (__nv_bfloat16*)y,
                      (int64_t)rows, cols, (int64_t)ld_g, (int64_t)ld_u, (int64_t)ld_y, act);
 }
 

@@ -177,7 +177,7 @@ class DecodeEngine:
     def splits_for(self, bucket: int) -> int:
         """Context splits of the decode attention at this batch bucket: few sequences leave SMs idle unless each head's
         context is cut into more pieces (an engine sized for 64 sequences still decodes a single one with 8 splits)."""
-        return self.cfg.attn_splits or self._choose_splits(bucket)
+        return self.cfg.attn_splits or int(os.environ.get("RLZ_ATTN_SPLITS", "0")) or self._choose_splits(bucket)
 
     def bucket_for(self, batch: int) -> int:
         for b in self.buckets:

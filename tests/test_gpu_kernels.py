@@ -451,3 +451,45 @@ def test_attn_decode_int8_kv(cuda_device, H, Hkv, d, splits):
         assert float((k_all[: L - 1] - hist_k[b]).abs().max()) <= float(hist_k[b].abs().amax(-1).max()) / 127 * 0.51 + 1e-6
         ref = _ref_attention(row[: H * d].reshape(H, d).cpu(), k_all.cpu(), v_all.cpu(), d ** -0.5).reshape(-1)
         assert _rel(out[b], ref) < 5e-3, (b, _rel(out[b], ref))
+
+
+@pytest.mark.parametrize("n", [2560, 4096, 72, 8192, 9000, 1001])
+@pytest.mark.parametrize("norm", ["layer", "rms"])
+def test_norm_bf16_vector_and_scalar_variants(cuda_device, n, norm):
+    """Rows that fit the register-resident 16-byte-vector kernel (n % 4 == 0, n <= 8192), longer rows and odd lengths
+    (scalar kernel), strided inputs: against an fp32 PyTorch computation rounded to bf16."""
+    from realizar_b200 import ops
+    torch.manual_seed(n)
+    T = 37
+    xfull = torch.randn(T, n + 8, device="cuda") * 3 + 0.5
+    x = xfull[:, :n] if n % 4 == 0 else xfull[:, 1:n + 1]          # odd sizes also start off the 16-byte grid
+    w, b = torch.rand(n, device="cuda") + 0.5, torch.randn(n, device="cuda") * 0.1
+    out = torch.empty(T, n, device="cuda", dtype=torch.bfloat16)
+    if norm == "layer":
+        ops.norm_bf16(x, out, w, b, ops.NORM_LAYER, 1e-5)
+        ref = torch.nn.functional.layer_norm(x.double(), (n,), w.double(), b.double(), 1e-5)
+    else:
+        ops.norm_bf16(x, out, w, None, ops.NORM_RMS, 1e-5)
+        ref = x.double() * torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + 1e-5) * w.double()
+    torch.cuda.synchronize()
+    err = (out.double() - ref).abs() / (ref.abs() + 1.0)
+    assert float(err.max()) < 6e-3, float(err.max())
+
+
+@pytest.mark.parametrize("cols,act,gated", [(10240, "gelu", False), (1024, "silu", True), (1002, "silu", True), (36, "gelu", False)])
+def test_swiglu_and_to_bf16_vector_and_scalar_variants(cuda_device, cols, act, gated):
+    from realizar_b200 import ops
+    torch.manual_seed(cols)
+    T = 19
+    gate, up = torch.randn(T, cols, device="cuda") * 2, torch.randn(T, cols, device="cuda")
+    out = torch.empty(T, cols, device="cuda", dtype=torch.bfloat16)
+    ops.swiglu_bf16(gate, up if gated else None, out, ops.ACT_SILU if act == "silu" else ops.ACT_GELU)
+    g = gate.double()
+    ref = torch.nn.functional.silu(g) if act == "silu" else torch.nn.functional.gelu(g, approximate="tanh")
+    if gated:
+        ref = ref * up.double()
+    assert float(((out.double() - ref).abs() / (ref.abs() + 1.0)).max()) < 6e-3
+    conv = ops.to_bf16(gate)
+    assert torch.equal(conv, gate.to(torch.bfloat16))
+    view = gate[:, 4:cols - 4] if cols % 4 == 0 else gate[:, 1:]
+    assert torch.equal(ops.to_bf16(view), view.to(torch.bfloat16))
