@@ -3,6 +3,7 @@
     python -m realizar_b200.utils.kernel_bench gemv --qtype Q4_K --n 200000 --k 2560 --batch 1
     python -m realizar_b200.utils.kernel_bench attn --heads 32 --kv-heads 32 --head-dim 80 --ctx 4096 --batch 8
     python -m realizar_b200.utils.kernel_bench gemm --qtype Q4_K --n 10240 --k 2560 --m 512
+    python -m realizar_b200.utils.kernel_bench step-trace --model phi-2 --ctx 600
 
 Each kernel is timed with CUDA events after warm-up.  Working sets are larger than the 126 MB
 L2 (or rotated over several copies) so the numbers are DRAM numbers.  The achieved rate is
@@ -286,6 +287,54 @@ def gemm_phase_trace(run) -> dict:
     return out
 
 
+def bench_step_trace(a):
+    """Phase trace of the GEMV launches INSIDE the captured decode step of a named model shape (batch 1): one launch at a time is
+    tagged, the step is replayed from its CUDA graph and the in-kernel time stamps of the tagged launch are read back.  Medians
+    over CTAs in microseconds: dependency wait, input staging, warp 0's rows, epilogue; ``span`` = first entry to last exit."""
+    import ctypes
+    from .. import ops
+    from ..models.config import named_config
+    from ..models.weights import synthetic_weights
+    from ..runtime.engine import DecodeEngine, EngineConfig
+    cfg = named_config(a.model)
+    dev = torch.device("cuda")
+    eng = DecodeEngine(synthetic_weights(cfg, scheme="Q4_K_M", seed=0, device=dev), EngineConfig(max_batch=1, max_seq_len=a.ctx + 64, greedy_only=True), device=dev)
+    eng.open_slot(0, a.ctx + 32)
+    eng.prefill(0, [int(t) for t in torch.randint(0, cfg.vocab_size, (a.ctx,))])
+    plan = eng.plan(1)
+    gemvs = [r[1] for r in plan.records if r and r[0] == "gemv"]
+    per_layer = (len(gemvs) - 1) // cfg.num_layers
+    lib, n = ops.lib(), 296
+    buf = (ctypes.c_ulonglong * (n * 8))()
+    out = {"kernel": "decode step phase trace", "model": a.model, "context": a.ctx, "gemv_launches": len(gemvs), "launches": {}}
+    picks = [(per_layer * a.layer + i, f"layer {a.layer} gemv {i}") for i in range(per_layer)] + [(len(gemvs) - 1, "lm_head")]
+    for which, name in picks:
+        if not ops.slab_eligible(gemvs[which]):
+            continue
+        for p in gemvs:
+            p._pad = 0
+        gemvs[which]._pad = 1
+        eng._graphs.clear()
+        eng.buf.positions[:1].fill_(a.ctx)
+        for _ in range(3):
+            eng.run_step(1)
+        torch.cuda.synchronize()
+        lib.rlz_gemv_slab_trace_read(buf, n, 1)
+        lib.rlz_gemv_slab_trace_enable(2)
+        eng.run_step(1)
+        torch.cuda.synchronize()
+        lib.rlz_gemv_slab_trace_enable(0)
+        lib.rlz_gemv_slab_trace_read(buf, n, 0)
+        t = np.frombuffer(buf, dtype=np.uint64).reshape(n, 8).astype(np.int64)
+        t = t[t[:, 0] > 0]
+        med = lambda i, j: round(float(np.median(t[:, j] - t[:, i])) / 1e3, 2)
+        out["launches"][name] = {"ctas": len(t), "wait": med(0, 1), "stage": med(1, 2), "rows_warp0": med(2, 3), "epilogue": med(6, 7),
+                                 "span": round(float(t[:, 7].max() - t[:, 0].min()) / 1e3, 2)}
+    for p in gemvs:
+        p._pad = 0
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--reps", type=int, default=1, help="back-to-back launches per timed region")
@@ -316,13 +365,15 @@ def main(argv=None):
     m.add_argument("--splitk", type=int, default=0, help="0 = chosen from the shape")
     m.add_argument("--trace", action="store_true", help="add the kernel's per-phase times (medians over CTAs)")
     m.add_argument("--wide", type=int, default=0, help="0 auto, 1 force 128-row CTAs, 2 force 256-row CTAs (m > 128)")
+    st = sub.add_parser("step-trace")
+    st.add_argument("--model", default="phi-2"); st.add_argument("--ctx", type=int, default=600); st.add_argument("--layer", type=int, default=20)
     a = ap.parse_args(argv)
     global REPS, GRAPH
     REPS, GRAPH = max(1, a.reps), a.graph
     if a.pdl:
         from .. import ops
         ops.set_pdl(True)
-    res = {"gemv": bench_gemv, "attn": bench_attn, "gemm": bench_gemm, "prefill": bench_prefill, "small": bench_small}[a.cmd](a)
+    res = {"gemv": bench_gemv, "attn": bench_attn, "gemm": bench_gemm, "prefill": bench_prefill, "small": bench_small, "step-trace": bench_step_trace}[a.cmd](a)
     print(json.dumps(res))
     return 0
 
