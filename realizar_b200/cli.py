@@ -53,7 +53,7 @@ def build_parser() -> argparse.ArgumentParser:
     for name in ("pull", "push"):
         q = sub.add_parser(name, help=f"{name} a model ({'needs a network' })"); q.add_argument("model")
     b = sub.add_parser("bench", help="kernel / engine benchmarks")
-    b.add_argument("suite", nargs="?", default=None, help="quantize | cpu_decode | tokenizer | cache | decode (GPU) | gemv | gemm | attn")
+    b.add_argument("suite", nargs="?", default=None, help="quantize | cpu_decode | cpu_generate | tokenizer | cache | decode (GPU) | gemv | gemm | attn")
     b.add_argument("--list", action="store_true"); b.add_argument("--output", "-o", default=None); b.add_argument("--model", default="tiny-llama")
     for name in ("bench-convoy", "bench-saturation"):
         q = sub.add_parser(name); q.add_argument("--model", default=None); q.add_argument("--output", "-o", default=None)
@@ -260,7 +260,7 @@ def cmd_registry_offline(a) -> int:
     return 2
 
 
-BENCH_SUITES = ("quantize", "cpu_decode", "tokenizer", "cache", "decode", "gemv", "gemm", "attn")
+BENCH_SUITES = ("quantize", "cpu_decode", "cpu_generate", "tokenizer", "cache", "decode", "gemv", "gemm", "attn")
 
 
 def run_bench_suite(suite: str, model: str = "tiny-llama") -> list:
@@ -288,6 +288,25 @@ def run_bench_suite(suite: str, model: str = "tiny-llama") -> list:
         s = DynamicSampler(10, 200).run(f)
         res.append(BenchResult(f"cpu_decode_{model}_ms_per_token", "ms", s))
         res.append(BenchResult(f"cpu_decode_{model}_tok_per_s", "tok/s", [1e3 / v for v in s], higher_is_better=True))
+    elif suite == "cpu_generate":
+        # the CPU headline configuration: Q4_K_M weights of the named shape, 128 prompt tokens then 128 greedy tokens
+        from .models.config import named_config
+        from .models.cpu_model import CpuModel
+        from .models.weights import synthetic_weights
+        cfg = named_config(model)
+        m = CpuModel(synthetic_weights(cfg, scheme="Q4_K_M", seed=0), 300)
+        prompt = [int(x) for x in np.random.default_rng(0).integers(0, cfg.vocab_size, 128)]
+        t0 = time.perf_counter()
+        for i, tok in enumerate(prompt):
+            lg = m.forward(tok, i)
+        t1 = time.perf_counter()
+        tok = int(np.argmax(lg))
+        for i in range(128):
+            lg = m.forward(tok, 128 + i)
+            tok = int(np.argmax(lg))
+        t2 = time.perf_counter()
+        res.append(BenchResult(f"cpu_generate_{model}_prompt_tok_per_s", "tok/s", [128 / (t1 - t0)], higher_is_better=True))
+        res.append(BenchResult(f"cpu_generate_{model}_decode_tok_per_s", "tok/s", [128 / (t2 - t1)], higher_is_better=True))
     elif suite == "tokenizer":
         from .serving.tokenizer import BPETokenizer, bytes_to_unicode
         b2u = bytes_to_unicode()
