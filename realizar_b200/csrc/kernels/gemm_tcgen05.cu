@@ -98,11 +98,44 @@ __device__ __forceinline__ void load_block(const uint8_t* blk, int g, int half, 
   }
 }
 
+template <int QT> struct IsLegacy { static constexpr bool value = QT == QT_Q4_0 || QT == QT_Q4_1 || QT == QT_Q5_0 || QT == QT_Q5_1 || QT == QT_Q8_0; };
+
+// 32-weight block types: one thread's half of a 64-column K step is exactly one block.  r[0] (and r[1] for Q8_0) = the code
+// bytes, r[2].x = d (and m) as two fp16, r[2].y = the 32 fifth bits.  Q4_0 / Q8_0 rows are planar on the device (all block
+// scales first, then the codes, both 16-byte aligned); the others keep their stored interleaved blocks, whose code bytes are
+// only 2- or 4-byte aligned.
 template <int QT>
-__device__ __forceinline__ void load_raw(const uint8_t* row, int k0, int half, RawW& w) {
+__device__ __forceinline__ void load_legacy(const uint8_t* row, int k, int k0, int half, RawW& w) {
+  const int b = (k0 >> 5) + half;
+  if (QT == QT_Q4_0 || QT == QT_Q8_0) {
+    const uint8_t* qs = row + dev_planar_qoff(k >> 5);
+    w.r[2].x = *(const uint16_t*)(row + 2 * b);
+    if (QT == QT_Q4_0) w.r[0] = __ldg((const uint4*)(qs + 16 * b));
+    else { w.r[0] = __ldg((const uint4*)(qs + 32 * b)); w.r[1] = __ldg((const uint4*)(qs + 32 * b + 16)); }
+  } else if (QT == QT_Q4_1) {
+    const uint32_t* blk = (const uint32_t*)(row + 20 * b);
+    w.r[2].x = blk[0];
+    w.r[0] = make_uint4(blk[1], blk[2], blk[3], blk[4]);
+  } else if (QT == QT_Q5_1) {
+    const uint32_t* blk = (const uint32_t*)(row + 24 * b);
+    w.r[2].x = blk[0]; w.r[2].y = blk[1];
+    w.r[0] = make_uint4(blk[2], blk[3], blk[4], blk[5]);
+  } else {                                                                  // Q5_0: 22-byte blocks, 2-byte aligned
+    const uint16_t* blk = (const uint16_t*)(row + 22 * b);
+    w.r[2].x = blk[0];
+    w.r[2].y = (uint32_t)blk[1] | ((uint32_t)blk[2] << 16);
+    w.r[0] = make_uint4((uint32_t)blk[3] | ((uint32_t)blk[4] << 16), (uint32_t)blk[5] | ((uint32_t)blk[6] << 16),
+                        (uint32_t)blk[7] | ((uint32_t)blk[8] << 16), (uint32_t)blk[9] | ((uint32_t)blk[10] << 16));
+  }
+}
+
+template <int QT>
+__device__ __forceinline__ void load_raw(const uint8_t* row, int k, int k0, int half, RawW& w) {
   const int sb = k0 >> 8, g = (k0 >> 6) & 3;
   if (QT == QT_Q4_K || QT == QT_Q5_K || QT == QT_Q6_K) {
     load_block<QT>(row + (int64_t)sb * BlockBytes<QT>::value, g, half, w);
+  } else if (IsLegacy<QT>::value) {
+    load_legacy<QT>(row, k, k0, half, w);
   } else {                                                                  // BF16 / F16: 32 elements = 64 bytes
     const uint4* src = (const uint4*)(row + (int64_t)(k0 + 32 * half) * 2);
 #pragma unroll
@@ -159,6 +192,38 @@ __device__ __forceinline__ void dequant_raw32(const RawW& w, int k0, int half, u
       const uint32_t s = w4 < 4 ? s0 : s1;
       out[2 * w4] = bf2_affine(__byte_perm(ws, 0, 0x4140) | MAGIC, MAGIC_OFF, s, 0u);
       out[2 * w4 + 1] = bf2_affine(__byte_perm(ws, 0, 0x4342) | MAGIC, MAGIC_OFF, s, 0u);
+    }
+  } else if (IsLegacy<QT>::value) {
+    // element e < 16 is the low nibble of code byte e, element 16 + e its high nibble (Q8_0: byte e is element e);
+    // value = d * (q - 8 | q - 16 | q) or d * q + m
+    const float d = h2f_alu(w.r[2].x & 0xFFFFu);
+    const float m = (QT == QT_Q4_1 || QT == QT_Q5_1) ? h2f_alu(w.r[2].x >> 16) : QT == QT_Q4_0 ? -8.f * d : QT == QT_Q5_0 ? -16.f * d : 0.f;
+    if (QT == QT_Q8_0) {
+      const uint32_t q[8] = {w.r[0].x, w.r[0].y, w.r[0].z, w.r[0].w, w.r[1].x, w.r[1].y, w.r[1].z, w.r[1].w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float a = (float)(int8_t)(q[i] & 0xFFu), b = (float)(int8_t)((q[i] >> 8) & 0xFFu);
+        const float c = (float)(int8_t)((q[i] >> 16) & 0xFFu), e = (float)(int8_t)(q[i] >> 24);
+        out[2 * i] = pack_bf16(d * a, d * b);
+        out[2 * i + 1] = pack_bf16(d * c, d * e);
+      }
+    } else {
+      const uint32_t q[4] = {w.r[0].x, w.r[0].y, w.r[0].z, w.r[0].w};
+      const uint32_t qh = w.r[2].y;
+      constexpr bool five = QT == QT_Q5_0 || QT == QT_Q5_1;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {                        // word i: code bytes 4i .. 4i+3
+        float lo[4], hi[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t byte = (q[i] >> (8 * j)) & 0xFFu;
+          uint32_t l = byte & 15u, h = byte >> 4;
+          if (five) { l |= ((qh >> (4 * i + j)) & 1u) << 4; h |= ((qh >> (16 + 4 * i + j)) & 1u) << 4; }
+          lo[j] = fmaf(d, (float)l, m); hi[j] = fmaf(d, (float)h, m);
+        }
+        out[2 * i] = pack_bf16(lo[0], lo[1]); out[2 * i + 1] = pack_bf16(lo[2], lo[3]);
+        out[8 + 2 * i] = pack_bf16(hi[0], hi[1]); out[8 + 2 * i + 1] = pack_bf16(hi[2], hi[3]);
+      }
     }
   } else if (QT == QT_BF16) {
 #pragma unroll
@@ -306,7 +371,7 @@ __global__ void __launch_bounds__(RT * GM_PRODUCERS + 96) gemm_kquant_tcgen05_ke
     RawW ring[PF];
 #pragma unroll
     for (int j = 0; j < PF; ++j)
-      if (j < nit) load_raw<QT>(wptr, (ks0 + j) * GM_KSTEP, half, ring[j]);
+      if (j < nit) load_raw<QT>(wptr, p.k, (ks0 + j) * GM_KSTEP, half, ring[j]);
     for (int it0 = 0; it0 < nit && ok; it0 += PF) {
 #pragma unroll
       for (int j = 0; j < PF; ++j) {
@@ -323,7 +388,7 @@ __global__ void __launch_bounds__(RT * GM_PRODUCERS + 96) gemm_kquant_tcgen05_ke
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] = 0u;
         }
-        if (it + PF < nit) load_raw<QT>(wptr, (ks0 + it + PF) * GM_KSTEP, half, ring[j]);   // refill the slot just consumed
+        if (it + PF < nit) load_raw<QT>(wptr, p.k, (ks0 + it + PF) * GM_KSTEP, half, ring[j]);   // refill the slot just consumed
         store_half_row_sw128(sm + s * STAGE, r, half, v);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic-proxy writes -> visible to the tensor core
         __syncwarp();
@@ -561,8 +626,20 @@ int launch_gemm(const GemmParams& p, cudaStream_t st) {
     case QT_Q5_K: return launch_gemm_q<NT, QT_Q5_K, RT>(p, st);
     case QT_Q6_K: return launch_gemm_q<NT, QT_Q6_K, RT>(p, st);
     case QT_BF16: return launch_gemm_q<NT, QT_BF16, RT>(p, st);
-    default: return launch_gemm_q<NT, QT_F16, RT>(p, st);
+    case QT_F16: return launch_gemm_q<NT, QT_F16, RT>(p, st);
+    default: break;
   }
+  if constexpr (RT == 1) {                                 // the 32-weight block types run 128-row CTAs only
+    switch (p.qtype) {
+      case QT_Q4_0: return launch_gemm_q<NT, QT_Q4_0, 1>(p, st);
+      case QT_Q4_1: return launch_gemm_q<NT, QT_Q4_1, 1>(p, st);
+      case QT_Q5_0: return launch_gemm_q<NT, QT_Q5_0, 1>(p, st);
+      case QT_Q5_1: return launch_gemm_q<NT, QT_Q5_1, 1>(p, st);
+      case QT_Q8_0: return launch_gemm_q<NT, QT_Q8_0, 1>(p, st);
+      default: break;
+    }
+  }
+  return -2;
 }
 
 }  // namespace rlz
@@ -596,7 +673,8 @@ int rlz_gemm_plan(const rlz::GemmParams* pp, int* nt, int* rows, int* splitk) {
   const long long tiles2 = (long long)((p.n + 255) / 256) * ((p.m + 255) / 256) * sk;
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const bool wide_fits = !(p.qtype == QT_Q5_K || p.qtype == QT_Q6_K);
+  const bool legacy = p.qtype == QT_Q4_0 || p.qtype == QT_Q4_1 || p.qtype == QT_Q5_0 || p.qtype == QT_Q5_1 || p.qtype == QT_Q8_0;
+  const bool wide_fits = !(p.qtype == QT_Q5_K || p.qtype == QT_Q6_K || legacy);
   const long long cost1 = ((tiles1 + sms - 1) / sms) * 840, cost2 = ((tiles2 + sms - 1) / sms) * 1100;
   if (wide_fits && (p._pad == 2 || (p._pad != 1 && cost2 < cost1))) *rows = 2 * GM_ROWS;
   return 0;
@@ -609,7 +687,8 @@ int rlz_gemm_kquant(const rlz::GemmParams* pp, void* stream) {
   using namespace rlz;
   GemmParams p = *pp;
   if (p.k % GM_KSTEP || p.m < 1 || p.n < 1) return -1;
-  if (!(p.qtype == QT_Q4_K || p.qtype == QT_Q5_K || p.qtype == QT_Q6_K || p.qtype == QT_BF16 || p.qtype == QT_F16)) return -2;
+  const bool legacy = p.qtype == QT_Q4_0 || p.qtype == QT_Q4_1 || p.qtype == QT_Q5_0 || p.qtype == QT_Q5_1 || p.qtype == QT_Q8_0;
+  if (!(p.qtype == QT_Q4_K || p.qtype == QT_Q5_K || p.qtype == QT_Q6_K || p.qtype == QT_BF16 || p.qtype == QT_F16 || legacy)) return -2;
   if ((p.qtype == QT_Q4_K || p.qtype == QT_Q5_K || p.qtype == QT_Q6_K) && p.k % 256) return -3;
   if (((uintptr_t)p.X & 15) || (p.ldx % 8) || ((uintptr_t)p.W & 15) || (p.w_stride & 15)) return -4;
   if (p.splitk < 1) p.splitk = 1;
@@ -639,7 +718,7 @@ int rlz_gemm_kquant(const rlz::GemmParams* pp, void* stream) {
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   // (256-row CTAs with the raw-block ring fit in shared memory for Q4_K blocks only)
-  const bool wide_fits = !(p.qtype == QT_Q5_K || p.qtype == QT_Q6_K);
+  const bool wide_fits = !(p.qtype == QT_Q5_K || p.qtype == QT_Q6_K || legacy);
   const long long cost1 = ((tiles1 + sms - 1) / sms) * 840, cost2 = ((tiles2 + sms - 1) / sms) * 1100;
   const bool wide = wide_fits && (p._pad == 2 || (p._pad != 1 && cost2 < cost1));
   return wide ? launch_gemm<256, 2>(p, st) : launch_gemm<256, 1>(p, st);

@@ -12,7 +12,8 @@ from . import _signatures as S
 from ..quant import QType
 
 GM_OUT_BF16, GM_RES_MUL = 1, 2
-GEMM_TYPES = (int(QType.Q4_K), int(QType.Q5_K), int(QType.Q6_K), int(QType.BF16), int(QType.F16))
+GEMM_TYPES = (int(QType.Q4_K), int(QType.Q5_K), int(QType.Q6_K), int(QType.BF16), int(QType.F16),
+              int(QType.Q4_0), int(QType.Q4_1), int(QType.Q5_0), int(QType.Q5_1), int(QType.Q8_0))     # 32-weight blocks: register-path producers
 
 
 def gemm_eligible(w: DeviceWeight) -> bool:

@@ -320,3 +320,33 @@ def test_profile_step_and_brick_report(cuda_device):
     assert rep["bottleneck"]["brick"] in rep["bricks"] and rep["step_us"] > 0
     assert rep["bricks"]["gemv"]["budget_us"] == pytest.approx(eng.model.weight_bytes() / (rep["bandwidth_gbs"] * 1e3 * 0.5))
     assert rep["bricks"]["attn"]["launches"] == small_phi2().num_layers
+
+
+@pytest.mark.parametrize("scheme", ["Q4_0", "Q8_0", "Q5_0", "Q4_1", "F16", "BF16"])
+def test_other_weight_types_run_prompts_on_the_tensor_core_path(cuda_device, scheme):
+    """Checkpoints in the 32-weight block types and dense 16-bit checkpoints: every projection is eligible for the tcgen05 GEMM,
+    so a prompt goes through the token-batch path (not token by token), and both paths agree with the fp32 oracle."""
+    from realizar_b200.models.reference import ReferenceDecoder
+    from realizar_b200.models.weights import synthetic_weights
+    from realizar_b200.runtime.engine import DecodeEngine, EngineConfig
+    from realizar_b200 import ops
+    cfg = _kq_llama()
+    w = synthetic_weights(cfg, scheme=scheme, seed=3, std=0.05)
+    toks = [int(t) for t in np.random.default_rng(1).integers(0, cfg.vocab_size, 45)]
+    eng = DecodeEngine(w, EngineConfig(max_batch=2, max_seq_len=128, greedy_only=True))
+    assert eng.gemm_ok
+    eng.open_slot(0, 96)
+    before = ops.launch_count()
+    eng.prefill(0, toks)
+    batched_launches = ops.launch_count() - before
+    lb = eng.logits_of_last_step(0).cpu().numpy()
+    eng.cfg.batched_prefill_min = 10 ** 9             # the same prompt token by token through the decode kernels
+    eng.open_slot(1, 96)
+    eng.prefill(1, toks)
+    assert batched_launches < len(toks)               # one pass over the 45 tokens, not 45 decode steps
+    ls = eng.logits_of_last_step(1).cpu().numpy()
+    want = ReferenceDecoder(w).forward(toks)[-1].numpy()
+    assert _cos(lb, want) > 0.99 and _cos(ls, want) > 0.99 and _cos(lb, ls) > 0.995
+    assert ops.device_error() == 0
+    out = eng.feed({0: int(lb.argmax())})
+    assert 0 <= int(out[0]) < cfg.vocab_size

@@ -16,6 +16,23 @@ def _weight(n, k, qt, seed):
     return ops.upload_weight(q, qt, n, k, "cuda"), torch.from_numpy(quant.dequantize(q, qt, (n, k)))
 
 
+@pytest.mark.parametrize("qt", [QType.Q4_0, QType.Q4_1, QType.Q5_0, QType.Q5_1, QType.Q8_0])
+@pytest.mark.parametrize("m,n,k,splitk", [(5, 128, 64, 1), (64, 200, 576, 1), (130, 384, 1024, 1), (300, 250, 2560, 1), (20, 256, 2048, 4)])
+def test_gemm_32_weight_block_types(cuda_device, qt, m, n, k, splitk):
+    """The 32-weight block types (planar Q4_0 / Q8_0 rows, interleaved Q4_1 / Q5_0 / Q5_1 blocks with 2- and 4-byte aligned
+    code bytes) on the tensor-core path, k a multiple of 64 only."""
+    from realizar_b200 import ops
+    from realizar_b200.ops import gemm
+    w, wd = _weight(n, k, qt, seed=m + n)
+    assert gemm.gemm_eligible(w)
+    x = torch.randn(m, k, device="cuda")
+    y = gemm.gemm(w, x, splitk=splitk)
+    assert ops.device_error() == 0
+    xr = x.to(torch.bfloat16).float().cpu()
+    ref = xr @ wd.to(torch.bfloat16).float().T
+    assert float((y.cpu() - ref).abs().max() / ref.abs().max()) < 2e-2
+
+
 @pytest.mark.parametrize("qt", [QType.Q4_K, QType.Q5_K, QType.Q6_K, QType.BF16, QType.F16])
 @pytest.mark.parametrize("m,n,k", [(5, 128, 256), (64, 200, 512), (130, 384, 1024), (33, 2560, 2560)])
 def test_gemm_matches_fp32(cuda_device, qt, m, n, k):
