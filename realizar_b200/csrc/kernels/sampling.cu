@@ -8,6 +8,7 @@
 // src/gguf/cuda/generate_2.rs:526-533); the sampling order (penalties -> temperature -> top-k
 // -> top-p) follows its CPU sampler (src/gguf/inference/fails.rs:92-336).
 #include "common.cuh"
+#include "gemv_params.h"
 #include <math.h>
 
 namespace rlz {
@@ -104,63 +105,79 @@ struct SampleParams {
   float* out_logprob;         // [B] or null: log-probability of the chosen token under the filtered distribution
 };
 
-__global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(const __grid_constant__ SampleParams p) {
-  __shared__ float sval[33]; __shared__ int sidx[33];
-  __shared__ unsigned hist[256];
-  __shared__ float cval[SAMP_MAX_CAND]; __shared__ int cidx[SAMP_MAX_CAND];
-  __shared__ float csum[SAMP_MAX_CAND];
-  __shared__ unsigned sh_prefix, sh_kk, sh_count, sh_ties;
-  __shared__ int sh_pick;
-  pdl_launch_dependents();
-  pdl_wait();
-  const int b = blockIdx.x, tid = threadIdx.x;
-  const float* row = p.logits + (int64_t)b * p.ld;
-  const int V = p.vocab;
-  const float temp = p.temperature[b];
-  int k = p.top_k[b];
+// Shared-memory state of one row's selection
+struct SampleSmem {
+  float sval[33]; int sidx[33];
+  unsigned hist[256];
+  float cval[SAMP_MAX_CAND]; int cidx[SAMP_MAX_CAND];
+  float csum[SAMP_MAX_CAND];
+  unsigned prefix, kk, count, ties;
+  int pick;
+};
 
-  float best = -INFINITY; int bi = 0x7fffffff;
-  for (int i = tid; i < V; i += SAMP_THREADS) { const float v = row[i]; if (v > best) { best = v; bi = i; } }
-  float vmax; int imax;
-  block_argmax(best, bi, sval, sidx, &vmax, &imax);
-  if (temp <= 0.f || k == 1) { if (tid == 0) { p.out[b] = imax; if (p.out_logprob) p.out_logprob[b] = 0.f; } return; }
-  if (k <= 0 || k > SAMP_MAX_CAND) k = SAMP_MAX_CAND;
-  if (k > V) k = V;
+// Where a row's values come from: the logits of a vocabulary slice (token id = position + offset)
+struct RowSrc {
+  const float* row; int off;
+  __device__ __forceinline__ float value(int i) const { return row[i]; }
+  __device__ __forceinline__ int token(int i) const { return i + off; }
+};
+// (the gathered candidate lists of a vocabulary-sharded head are the other source, see sample_merge_kernel)
 
-  // ---- exact k-th largest key by 4 x 8-bit radix select ------------------------------------
-  if (tid == 0) { sh_prefix = 0; sh_kk = (unsigned)k; }
+// Largest value of the row (ties: smallest token id), valid in all threads
+template <class Src>
+__device__ __forceinline__ void row_argmax(SampleSmem& S, const Src& src, int V, float* vmax, int* tmax) {
+  float best = -INFINITY; int bt = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += SAMP_THREADS) {
+    const float v = src.value(i); const int t = src.token(i);
+    if (v > best || (v == best && t < bt)) { best = v; bt = t; }
+  }
+  block_argmax(best, bt, S.sval, S.sidx, vmax, tmax);
+}
+
+// The k largest values of the row (exact k-th key by 4 x 8-bit radix select) into S.cval / S.cidx (token ids), unsorted, padded
+// with -inf up to SAMP_MAX_CAND; returns how many were taken
+template <class Src>
+__device__ __forceinline__ int select_topk(SampleSmem& S, const Src& src, int V, int k) {
+  const int tid = threadIdx.x;
+  if (tid == 0) { S.prefix = 0; S.kk = (unsigned)k; }
   for (int round = 0; round < 4; ++round) {
     const int shift = 24 - 8 * round;
-    if (tid < 256) hist[tid] = 0;
+    if (tid < 256) S.hist[tid] = 0;
     __syncthreads();
-    const unsigned prefix = sh_prefix, pmask = round == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
+    const unsigned prefix = S.prefix, pmask = round == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
     for (int i = tid; i < V; i += SAMP_THREADS) {
-      const uint32_t key = float_key(row[i]);
-      if ((key & pmask) == prefix) atomicAdd(&hist[(key >> shift) & 0xFFu], 1u);
+      const uint32_t key = float_key(src.value(i));
+      if ((key & pmask) == prefix) atomicAdd(&S.hist[(key >> shift) & 0xFFu], 1u);
     }
     __syncthreads();
     if (tid == 0) {
-      unsigned cum = 0, kk = sh_kk; int bin = 255;
-      for (; bin > 0; --bin) { if (cum + hist[bin] >= kk) break; cum += hist[bin]; }
-      sh_kk = kk - cum;                       // still needed from inside this bin
-      sh_prefix = prefix | ((unsigned)bin << shift);
+      unsigned cum = 0, kk = S.kk; int bin = 255;
+      for (; bin > 0; --bin) { if (cum + S.hist[bin] >= kk) break; cum += S.hist[bin]; }
+      S.kk = kk - cum;                        // still needed from inside this bin
+      S.prefix = prefix | ((unsigned)bin << shift);
     }
     __syncthreads();
   }
-  const uint32_t tkey = sh_prefix;            // key of the k-th largest logit
-  const unsigned ties_wanted = sh_kk;         // how many elements equal to it belong to the top k
-  if (tid == 0) { sh_count = 0; sh_ties = 0; }
-  for (int i = tid; i < SAMP_MAX_CAND; i += SAMP_THREADS) { cval[i] = -INFINITY; cidx[i] = 0x7fffffff; }
+  const uint32_t tkey = S.prefix;             // key of the k-th largest value
+  const unsigned ties_wanted = S.kk;          // how many elements equal to it belong to the top k
+  if (tid == 0) { S.count = 0; S.ties = 0; }
+  for (int i = tid; i < SAMP_MAX_CAND; i += SAMP_THREADS) { S.cval[i] = -INFINITY; S.cidx[i] = 0x7fffffff; }
   __syncthreads();
   for (int i = tid; i < V; i += SAMP_THREADS) {
-    const float v = row[i]; const uint32_t key = float_key(v);
+    const float v = src.value(i); const uint32_t key = float_key(v);
     bool take = key > tkey;
-    if (key == tkey) take = atomicAdd(&sh_ties, 1u) < ties_wanted;
-    if (take) { const unsigned slot = atomicAdd(&sh_count, 1u); if (slot < SAMP_MAX_CAND) { cval[slot] = v; cidx[slot] = i; } }
+    if (key == tkey) take = atomicAdd(&S.ties, 1u) < ties_wanted;
+    if (take) { const unsigned slot = atomicAdd(&S.count, 1u); if (slot < SAMP_MAX_CAND) { S.cval[slot] = v; S.cidx[slot] = src.token(i); } }
   }
   __syncthreads();
+  return (int)min(S.count, (unsigned)SAMP_MAX_CAND);
+}
 
-  // ---- bitonic sort: value descending, index ascending --------------------------------------
+// Candidates in S.cval / S.cidx (n valid): sort by (value descending, token id ascending), softmax with temperature relative to
+// vmax, min-p / top-p filtering, inverse-CDF draw with p.uniform[b]; writes p.out[b]
+__device__ __forceinline__ void sort_and_draw(SampleSmem& S, const SampleParams& p, int b, int n, float vmax, float temp) {
+  const int tid = threadIdx.x;
+  float* cval = S.cval; int* cidx = S.cidx; float* csum = S.csum;
   for (int size = 2; size <= SAMP_MAX_CAND; size <<= 1) {
     for (int stride = size >> 1; stride > 0; stride >>= 1) {
       const int i = tid, j = i ^ stride;
@@ -173,9 +190,6 @@ __global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(const __grid_const
       __syncthreads();
     }
   }
-
-  // ---- softmax over candidates, min-p / top-p filtering, inverse-CDF draw --------------------
-  const int n = (int)min(sh_count, (unsigned)SAMP_MAX_CAND);
   const float inv_t = 1.f / temp;
   float pr = tid < n ? __expf((cval[tid] - vmax) * inv_t) : 0.f;
   if (p.min_p && p.min_p[b] > 0.f && pr < p.min_p[b]) pr = 0.f;      // relative to the top probability (= 1 here)
@@ -189,29 +203,139 @@ __global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(const __grid_const
   }
   const float total = csum[SAMP_MAX_CAND - 1];
   const float top_p = p.top_p[b];
-  if (tid == 0) sh_pick = n - 1;
+  if (tid == 0) S.pick = n - 1;
   __syncthreads();
   // nucleus: smallest prefix whose mass reaches top_p * total
   float kept = total;
   if (top_p < 1.f) {
     const float need = top_p * total;
     const bool here = csum[tid] >= need && (tid == 0 || csum[tid - 1] < need);
-    if (here) sh_pick = tid;
+    if (here) S.pick = tid;
     __syncthreads();
-    kept = csum[sh_pick];
+    kept = csum[S.pick];
     __syncthreads();
   }
-  const int last = top_p < 1.f ? sh_pick : n - 1;
+  const int last = top_p < 1.f ? S.pick : n - 1;
   const float target = p.uniform[b] * kept;
-  if (tid == 0) sh_pick = last;
+  if (tid == 0) S.pick = last;
   __syncthreads();
-  if (tid <= last && csum[tid] > target && (tid == 0 || csum[tid - 1] <= target)) sh_pick = tid;
+  if (tid <= last && csum[tid] > target && (tid == 0 || csum[tid - 1] <= target)) S.pick = tid;
   __syncthreads();
   if (tid == 0) {
-    const int c = sh_pick;
+    const int c = S.pick;
     p.out[b] = cidx[c];
     if (p.out_logprob) { const float pc = c == 0 ? csum[0] : csum[c] - csum[c - 1]; p.out_logprob[b] = logf(fmaxf(pc, 1e-30f) / kept); }
   }
+}
+
+__device__ __forceinline__ int clamp_k(int k, int V) {
+  if (k <= 0 || k > SAMP_MAX_CAND) k = SAMP_MAX_CAND;
+  return k > V ? V : k;
+}
+
+__global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(const __grid_constant__ SampleParams p) {
+  __shared__ SampleSmem S;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x;
+  const RowSrc src{p.logits + (int64_t)b * p.ld, 0};
+  const float temp = p.temperature[b];
+  const int k = p.top_k[b];
+  float vmax; int tmax;
+  row_argmax(S, src, p.vocab, &vmax, &tmax);
+  if (temp <= 0.f || k == 1) { if (threadIdx.x == 0) { p.out[b] = tmax; if (p.out_logprob) p.out_logprob[b] = 0.f; } return; }
+  const int n = select_topk(S, src, p.vocab, clamp_k(k, p.vocab));
+  sort_and_draw(S, p, b, n, vmax, temp);
+}
+
+// ---- vocabulary-sharded heads: per-rank candidates, exchange over peer memory, identical draw on every rank -----------------
+// Every rank selects the top-k of ITS vocabulary slice (the global top-k is contained in the union of the local ones), stores
+// the (value, token id) pairs into every rank's inbox and publishes one flag word per (rank, row): (epoch << 11) | count.  The
+// second kernel waits (bounded) for the world's flags of its row and runs the same selection and draw over the gathered
+// candidates; with the same uniform number every rank picks the same token.  Replaces an all-gather of the whole vocabulary row.
+struct ShardSample {
+  uint2* inbox[GEMV_AR_MAX_RANKS];       // rank r's candidate inbox: [parity 2][world][batch_cap][K] pairs
+  uint32_t* flags[GEMV_AR_MAX_RANKS];    // rank r's flags: [parity 2][world][batch_cap]
+  const uint32_t* epoch; int32_t* status;
+  int64_t spin_limit;
+  int32_t rank, world, batch_cap, K;     // K <= SAMP_MAX_CAND pairs reserved per (rank, row)
+  int32_t index_offset, _pad;            // first token id of this rank's slice
+};
+
+// one row's candidate lists as they lie in an inbox: writer r's list starts r * stride pairs on, its first cnt[r] pairs are valid
+struct Gathered {
+  const uint2* base; const int* cnt; int K; int64_t stride;
+  __device__ __forceinline__ float value(int i) const { const int r = i / K, j = i - r * K; return j < cnt[r] ? __uint_as_float(base[r * stride + j].x) : -INFINITY; }
+  __device__ __forceinline__ int token(int i) const { const int r = i / K, j = i - r * K; return j < cnt[r] ? (int)base[r * stride + j].y : 0x7fffffff; }
+};
+
+__global__ void __launch_bounds__(SAMP_THREADS) sample_push_kernel(const __grid_constant__ SampleParams p, const __grid_constant__ ShardSample c) {
+  __shared__ SampleSmem S;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x, tid = threadIdx.x;
+  const RowSrc src{p.logits + (int64_t)b * p.ld, c.index_offset};
+  const float temp = p.temperature[b];
+  int k = p.top_k[b];
+  int n;
+  if (temp <= 0.f || k == 1) {                             // greedy rows exchange one candidate
+    float vmax; int tmax;
+    row_argmax(S, src, p.vocab, &vmax, &tmax);
+    if (tid == 0) { S.cval[0] = vmax; S.cidx[0] = tmax; }
+    __syncthreads();
+    n = 1;
+  } else {
+    k = clamp_k(k, p.vocab);
+    n = select_topk(S, src, p.vocab, k > c.K ? c.K : k);
+  }
+  const uint32_t epoch = *c.epoch;
+  const int64_t slot = ((int64_t)(epoch & 1u) * c.world + c.rank) * c.batch_cap + b;
+  for (int q = 0; q < c.world; ++q) {
+    uint2* dst = c.inbox[q] + slot * c.K;
+    for (int i = tid; i < n; i += SAMP_THREADS) dst[i] = make_uint2(__float_as_uint(S.cval[i]), (uint32_t)S.cidx[i]);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < c.world) {
+    const uint32_t word = ((epoch & 0x1FFFFFu) << 11) | (uint32_t)n;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(c.flags[tid] + slot), "r"(word) : "memory");
+  }
+}
+
+__global__ void __launch_bounds__(SAMP_THREADS) sample_merge_kernel(const __grid_constant__ SampleParams p, const __grid_constant__ ShardSample c) {
+  __shared__ SampleSmem S;
+  __shared__ int cnt[GEMV_AR_MAX_RANKS];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x, tid = threadIdx.x;
+  const uint32_t epoch = *c.epoch;
+  const int64_t base = (int64_t)(epoch & 1u) * c.world * c.batch_cap;
+  if (tid < c.world) {                                     // one poller per writer; a wait that runs out leaves that writer's list empty
+    const uint32_t* f = c.flags[c.rank] + base + (int64_t)tid * c.batch_cap + b;
+    int got = -1;
+    for (int64_t spins = 0; spins <= c.spin_limit; ++spins) {
+      uint32_t v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+      if ((v >> 11) == (epoch & 0x1FFFFFu)) { got = (int)(v & 0x7FFu); break; }
+    }
+    if (got < 0) { atomicExch(c.status, 2006); got = 0; }
+    cnt[tid] = got > c.K ? c.K : got;
+  }
+  __syncthreads();
+  // row b of every writer, as one [world][K] array: the writers' slots of a row are batch_cap * K pairs apart
+  const uint2* mine = c.inbox[c.rank] + (base + b) * c.K;
+  const Gathered src{mine, cnt, c.K, (int64_t)c.batch_cap * c.K};
+  const int V = c.world * c.K;
+  const float temp = p.temperature[b];
+  const int k = p.top_k[b];
+  float vmax; int tmax;
+  row_argmax(S, src, V, &vmax, &tmax);
+  if (temp <= 0.f || k == 1) { if (tid == 0) { p.out[b] = tmax; if (p.out_logprob) p.out_logprob[b] = 0.f; } return; }
+  int total = 0;
+  for (int r = 0; r < c.world; ++r) total += cnt[r];
+  int kk = clamp_k(k, total < 1 ? 1 : total);
+  if (kk > c.K) kk = c.K;                                  // beyond K per rank the union of the lists is no longer the global top
+  const int n = select_topk(S, src, V, kk);
+  sort_and_draw(S, p, b, n, vmax, temp);
 }
 
 // logits[b, tok] adjusted for every distinct token in history[b, :] (entries < 0 are padding):
@@ -349,5 +473,17 @@ int rlz_penalties(float* logits, long long ld, int vocab, int batch, const int32
 }
 
 int rlz_sizeof_sample_params() { return (int)sizeof(rlz::SampleParams); }
+int rlz_sizeof_shard_sample() { return (int)sizeof(rlz::ShardSample); }
+
+// Vocabulary-sharded sampling, first half: p.logits / p.vocab describe this rank's slice; candidates go to every rank's inbox.
+int rlz_sample_push(const SampleParams* p, const ShardSample* c, void* stream) {
+  if (p->batch < 1 || p->batch > c->batch_cap || c->K < 1 || c->K > SAMP_MAX_CAND || c->world < 1 || c->world > GEMV_AR_MAX_RANKS) return -1;
+  return (int)launch(sample_push_kernel, dim3(p->batch), dim3(SAMP_THREADS), 0, (cudaStream_t)stream, *p, *c);
+}
+// Second half: the draw over the gathered candidates; p.logits is not read.
+int rlz_sample_merge(const SampleParams* p, const ShardSample* c, void* stream) {
+  if (p->batch < 1 || p->batch > c->batch_cap || c->K < 1 || c->K > SAMP_MAX_CAND || c->world < 1 || c->world > GEMV_AR_MAX_RANKS) return -1;
+  return (int)launch(sample_merge_kernel, dim3(p->batch), dim3(SAMP_THREADS), 0, (cudaStream_t)stream, *p, *c);
+}
 
 }  // extern "C"

@@ -457,14 +457,15 @@ def emit_select(plan: "DecodePlan", model: GpuModel, buf: StepBuffers, r0: int, 
     fused = tp and getattr(comm, "fused", False)
     rows = slice(r0, r0 + batch)
 
-    def controls(logits_rows):
-        """History update and per-sequence logit controls ahead of the sampling kernel (sampling plans only)."""
+    def controls(logits_rows, v0: int = 0, vn: int = V):
+        """History update and per-sequence logit controls ahead of the sampling kernel (sampling plans only); ``v0`` / ``vn``:
+        the vocabulary slice that ``logits_rows`` holds."""
         if buf.history is None:
             return 0
         def run():
             ops.history_push(buf.history[rows], buf.tokens[rows], buf.positions[rows], batch)
-            ops.logit_controls(logits_rows, buf.history[rows], buf.repetition[rows], buf.presence[rows], buf.frequency[rows], buf.bias[rows],
-                               buf.bias_on[rows], vocab=V)
+            ops.logit_controls(logits_rows, buf.history[rows], buf.repetition[rows], buf.presence[rows], buf.frequency[rows],
+                               buf.bias[rows, v0:v0 + vn], buf.bias_on[rows], index_offset=v0, vocab=vn)
         plan.add(run, launches=2)
         return 2
     if tp and greedy_only:
@@ -472,6 +473,15 @@ def emit_select(plan: "DecodePlan", model: GpuModel, buf: StepBuffers, r0: int, 
             ops.argmax(buf.logits[rows], out=buf.local_idx[rows], out_val=buf.local_val[rows], index_offset=model.vocab_start, vocab=model.vocab_local)
             comm.select_greedy(buf.local_val[rows], buf.local_idx[rows], buf.sampled[rows], batch)
         plan.add(pick, launches=2 if fused else 1)
+    elif fused and getattr(comm, "sbuf", None) is not None and os.environ.get("RLZ_SHARDED_SAMPLING", "1") != "0":
+        # every rank selects the candidates of its vocabulary slice, the lists are exchanged over peer memory and every rank
+        # draws the same token from the merged list: no rank ever holds the whole vocabulary row
+        sp_loc = ops.build_sample_params(buf.logits[rows], buf.temperature[rows], buf.top_k[rows], buf.top_p[rows], buf.uniform[rows],
+                                         buf.sampled[rows], buf.min_p[rows], vocab=model.vocab_local)
+        desc = comm.shard_sample_desc(model.vocab_start)
+        plan.keep += [sp_loc, desc]
+        controls(buf.logits[rows], model.vocab_start, model.vocab_local)
+        plan.add(lambda: comm.sample_sharded(sp_loc, desc), launches=2)
     elif tp:
         sp_full = ops.build_sample_params(buf.logits_full[rows], buf.temperature[rows], buf.top_k[rows], buf.top_p[rows], buf.uniform[rows],
                                           buf.sampled[rows], buf.min_p[rows], vocab=V)

@@ -70,6 +70,12 @@ class SampleParams(Structure):
                 ("out_logprob", c_void_p)]
 
 
+class ShardSample(Structure):
+    _fields_ = [("inbox", c_void_p * AR_MAX_RANKS), ("flags", c_void_p * AR_MAX_RANKS), ("epoch", c_void_p), ("status", c_void_p),
+                ("spin_limit", c_int64), ("rank", c_int32), ("world", c_int32), ("batch_cap", c_int32), ("K", c_int32),
+                ("index_offset", c_int32), ("_pad", c_int32)]
+
+
 class GemmParams(Structure):
     _fields_ = [("W", c_void_p), ("w_stride", c_int64), ("qtype", c_int32), ("n", c_int32), ("k", c_int32), ("m", c_int32),
                 ("X", c_void_p), ("ldx", c_int64), ("Y", c_void_p), ("ldy", c_int64), ("bias", c_void_p), ("residual", c_void_p),
@@ -165,6 +171,8 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_page_rows.argtypes = [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_void_p]
     lib.rlz_argmax.argtypes = [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
     lib.rlz_sample.argtypes = [POINTER(SampleParams), c_void_p]
+    lib.rlz_sample_push.argtypes = [POINTER(SampleParams), POINTER(ShardSample), c_void_p]
+    lib.rlz_sample_merge.argtypes = [POINTER(SampleParams), POINTER(ShardSample), c_void_p]
     lib.rlz_history_push.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p]
     lib.rlz_logit_controls.argtypes = [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
                                        c_void_p, c_void_p]

@@ -89,8 +89,28 @@ def main(argv=None) -> int:
         t0 = t.clone()
         dist.broadcast(t0, 0)
         ok &= bool((t == t0).all())                          # every rank generated the same tokens
-        comm.close()
+        # non-greedy sampling: candidates of the vocabulary slices exchanged over peer memory (fused) against the gathered row
+        eng.close()
         del eng
+        torch.cuda.synchronize()
+        dist.barrier()
+        sampled = {}
+        for sharded in (("1", "0") if mode == "fused" else ("0",)):
+            os.environ["RLZ_SHARDED_SAMPLING"] = sharded
+            eng2 = DecodeEngine(w, EngineConfig(max_batch=2, max_seq_len=256, cuda_graphs=bool(a.graphs), greedy_only=False, seed=11), device=dev,
+                                comm=comm, tp_rank=rank, tp_size=world)
+            sampled[sharded] = eng2.generate(prompt, SamplingParams(max_tokens=a.tokens, temperature=0.8, top_k=50, top_p=0.9))
+            st = torch.tensor(sampled[sharded], device=dev)
+            st0 = st.clone()
+            dist.broadcast(st0, 0)
+            ok &= bool((st == st0).all()) and (comm.check_status() if hasattr(comm, "check_status") else 0) == 0
+            eng2.close()
+            del eng2
+        os.environ.pop("RLZ_SHARDED_SAMPLING", None)
+        results[mode]["sampled"] = sampled
+        if len(sampled) == 2:
+            ok &= sampled["1"] == sampled["0"]
+        comm.close()
         torch.cuda.synchronize()
     modes = list(results)
     if len(modes) == 2:

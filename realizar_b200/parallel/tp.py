@@ -148,6 +148,9 @@ class FusedTpComm(NcclTpComm):
         self._off_cand = n_sites * self._inbox_site
         cand_inbox = 2 * w * max_batch * 2 * 8
         total = (self._off_cand + cand_inbox + 255) // 256 * 256
+        if self.buf is not None:                           # a second engine on the same communicator: the first one's buffers go
+            self.buf.close()
+        self._cand = None
         self.buf = SymmetricBuffer(total, self.rank, w, self.group)
         self.n_sites = n_sites
 
@@ -259,6 +262,33 @@ class FusedTpComm(NcclTpComm):
         c.site, c.nsites, c.norm, c.push_x, c.wait_ag, c.eps = site, self.ts_sites, norm, 1 if push_x else 0, 1 if wait else 0, eps
         ops.check(ops.lib().rlz_rs_reduce(ctypes.byref(c), ops.stream_ptr()), "rs_reduce")
 
+    # -- sampling with a vocabulary-sharded head: per-rank candidates, exchange over peer memory, same draw everywhere -------
+    def allocate_sample(self, max_batch: int, k: int = 1024) -> None:
+        """Symmetric memory for the candidate exchange of non-greedy sampling: per (parity, writer rank, sequence) ``k``
+        {value, token id} pairs and one flag word."""
+        w = self.world
+        self.sm_k, self.sm_batch = k, max_batch
+        pairs = 2 * w * max_batch * k * 8
+        self._sm_off_flags = (pairs + 255) // 256 * 256
+        if getattr(self, "sbuf", None) is not None:
+            self.sbuf.close()
+        self.sbuf = SymmetricBuffer(self._sm_off_flags + (2 * w * max_batch * 4 + 255) // 256 * 256, self.rank, w, self.group)
+
+    def shard_sample_desc(self, index_offset: int) -> "S.ShardSample":
+        c = S.ShardSample()
+        for r in range(self.world):
+            c.inbox[r] = self.sbuf.ptrs[r]
+            c.flags[r] = self.sbuf.ptrs[r] + self._sm_off_flags
+        c.epoch, c.status, c.spin_limit = self.epoch.data_ptr(), self.status.data_ptr(), self.spin_limit
+        c.rank, c.world, c.batch_cap, c.K, c.index_offset = self.rank, self.world, self.sm_batch, self.sm_k, index_offset
+        return c
+
+    def sample_sharded(self, sp_local: "S.SampleParams", desc: "S.ShardSample") -> None:
+        """``sp_local`` describes this rank's logits slice; the chosen token ids (identical on every rank) go to ``sp_local.out``."""
+        lib = ops.lib()
+        ops.check(lib.rlz_sample_push(ctypes.byref(sp_local), ctypes.byref(desc), ops.stream_ptr()), "sample_push")
+        ops.check(lib.rlz_sample_merge(ctypes.byref(sp_local), ctypes.byref(desc), ops.stream_ptr()), "sample_merge")
+
     def begin_step(self) -> None:
         ops.check(ops.lib().rlz_epoch_bump(self.epoch.data_ptr(), ops.stream_ptr()), "epoch_bump")
 
@@ -292,6 +322,9 @@ class FusedTpComm(NcclTpComm):
         if getattr(self, "gbuf", None) is not None:
             self.gbuf.close()
             self.gbuf = None
+        if getattr(self, "sbuf", None) is not None:
+            self.sbuf.close()
+            self.sbuf = None
         if getattr(self, "tsbuf", None) is not None:
             self.ts_x = self.ts_xb = None
             self.tsbuf.close()

@@ -142,6 +142,8 @@ class DecodeEngine:
             chunks_max = -(-B // 4)
             per_layer = 1 if self.mcfg.parallel_residual else 2
             comm.allocate(self.mcfg.num_layers * per_layer * chunks_max, self.mcfg.hidden_dim, max_batch=B)
+            if not c.greedy_only:
+                comm.allocate_sample(B)                    # candidate exchange of vocabulary-sharded sampling
         self.slots = [Slot() for _ in range(B)]
         self._slot_bias: Dict[int, dict] = {}
         self._bias_live: Dict[int, bool] = {}

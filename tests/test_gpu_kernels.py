@@ -493,3 +493,53 @@ def test_swiglu_and_to_bf16_vector_and_scalar_variants(cuda_device, cols, act, g
     assert torch.equal(conv, gate.to(torch.bfloat16))
     view = gate[:, 4:cols - 4] if cols % 4 == 0 else gate[:, 1:]
     assert torch.equal(ops.to_bf16(view), view.to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("world,K", [(2, 1024), (4, 1024), (8, 256)])
+def test_sharded_sampling_emulated_ranks_match_full_row_sampler(cuda_device, world, K):
+    """Vocabulary-sharded sampling: every emulated rank pushes the candidates of its slice (one launch per rank, none of them
+    waits), then every rank merges; each must pick exactly what the one-kernel sampler picks on the whole row."""
+    import ctypes
+    from realizar_b200 import ops
+    from realizar_b200.ops import _signatures as S
+    torch.manual_seed(world)
+    B, V = 6, 5003
+    vl = -(-V // world)
+    logits = torch.randn(B, V, device="cuda") * 3
+    temperature = torch.tensor([0.7, 0.0, 1.0, 0.9, 1.3, 0.8], device="cuda")
+    top_k = torch.tensor([40, 0, 1, 0, 2000, 200], device="cuda", dtype=torch.int32)
+    top_p = torch.tensor([0.9, 1.0, 1.0, 0.5, 1.0, 0.95], device="cuda")
+    min_p = torch.tensor([0.0, 0.0, 0.0, 0.0, 0.01, 0.0], device="cuda")
+    for trial in range(3):
+        uniform = torch.rand(B, device="cuda")
+        want = ops.sample(logits, temperature, top_k, top_p, uniform, min_p)
+        if K < 1024:                                        # a narrower exchange caps every row's candidate count at K
+            want = ops.sample(logits, temperature, torch.where((top_k <= 0) | (top_k > K), torch.full_like(top_k, K), top_k), top_p, uniform, min_p)
+        inbox = [torch.zeros(2 * world * B * K, 2, device="cuda", dtype=torch.int32) for _ in range(world)]
+        flags = [torch.zeros(2 * world * B, device="cuda", dtype=torch.int32) for _ in range(world)]
+        epoch = torch.full((1,), 5 + trial, device="cuda", dtype=torch.int32)
+        status = torch.zeros(1, device="cuda", dtype=torch.int32)
+        outs = [torch.full((B,), -1, device="cuda", dtype=torch.int32) for _ in range(world)]
+        descs, sps = [], []
+        for r in range(world):
+            c = S.ShardSample()
+            for q in range(world):
+                c.inbox[q], c.flags[q] = inbox[q].data_ptr(), flags[q].data_ptr()
+            c.epoch, c.status, c.spin_limit = epoch.data_ptr(), status.data_ptr(), 1000
+            c.rank, c.world, c.batch_cap, c.K, c.index_offset = r, world, B, K, r * vl
+            n_local = max(0, min(V, (r + 1) * vl) - r * vl)
+            sp = ops.build_sample_params(logits[:, r * vl:], temperature, top_k, top_p, uniform, outs[r], min_p, vocab=n_local)
+            descs.append(c); sps.append(sp)
+        for r in range(world):
+            ops.check(ops.lib().rlz_sample_push(ctypes.byref(sps[r]), ctypes.byref(descs[r]), ops.stream_ptr()), "push")
+        for r in range(world):
+            ops.check(ops.lib().rlz_sample_merge(ctypes.byref(sps[r]), ctypes.byref(descs[r]), ops.stream_ptr()), "merge")
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        for r in range(world):
+            assert torch.equal(outs[r], want), (r, outs[r].tolist(), want.tolist())
+    # a list that never arrives: the wait runs out, the status word says so, the draw uses what is there
+    flags[0].zero_()
+    ops.check(ops.lib().rlz_sample_merge(ctypes.byref(sps[0]), ctypes.byref(descs[0]), ops.stream_ptr()), "merge")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 2006
