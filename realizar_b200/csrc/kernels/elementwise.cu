@@ -13,6 +13,12 @@
 
 namespace rlz {
 
+// Index guards.  Indices that come from DEVICE data (token ids, positions, page ids) are checked where they are used, in every
+// build: the access is skipped and a code is recorded (3401 token id outside the vocabulary, 3402 page id outside the cache,
+// 3403 position outside the page-table row).  Indices that come from the host are validated by the launchers instead.
+__device__ int g_index_error = 0;
+__device__ __forceinline__ void index_error(int code) { atomicCAS(&g_index_error, 0, code); }
+
 // out[t, :] = dequant(table[tokens[t], :]) (+ pos_table[positions[t], :]).  One CTA per token.
 __global__ void embed_kernel(const uint8_t* table, int qtype, int64_t row_bytes, int hidden, const int32_t* tokens,
                              const float* pos_table, const int32_t* positions, float* out, int64_t ld_out, int vocab) {
@@ -21,7 +27,11 @@ __global__ void embed_kernel(const uint8_t* table, int qtype, int64_t row_bytes,
   const int t = blockIdx.x;
   const int tok = tokens[t];
   float* o = out + (int64_t)t * ld_out;
-  if (tok < 0 || tok >= vocab) { for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = 0.f; return; }
+  if (tok < 0 || tok >= vocab) {                         // negative ids mark idle rows (zeros, silently); ids past the table are an error
+    if (threadIdx.x == 0 && tok >= vocab) index_error(3401);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = 0.f;
+    return;
+  }
   const uint8_t* row = table + (int64_t)tok * row_bytes;
   const int be = qtype_block_elems(qtype), bb = qtype_block_bytes(qtype);
   if (be == 1) {
@@ -140,13 +150,14 @@ __global__ void elementwise_kernel(const float* a, const float* b, const float* 
 
 // Append T rows of k / v ([T, n_kv_heads, d] f32, row stride ld) to the paged bf16 cache.
 __global__ void kv_append_kernel(const float* k, const float* v, int64_t ld, __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
-                                 const int32_t* positions, const int32_t* page_rows, int n_kv_heads, int d, int page) {
+                                 const int32_t* positions, const int32_t* page_rows, int n_kv_heads, int d, int page, int num_pages) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   if (pos < 0) return;
   const int pg = page_rows[t];                     // physical page holding position `pos`
+  if (num_pages > 0 && (unsigned)pg >= (unsigned)num_pages) { if (threadIdx.x == 0) index_error(3402); return; }
   const int slot = pos % page;
   const float* kr = k + (int64_t)t * ld;
   const float* vr = v + (int64_t)t * ld;
@@ -174,13 +185,14 @@ __global__ void kv_append_kernel(const float* k, const float* v, int64_t ld, __n
 
 // int8 cache rows (head_dim codes, then the fp32 scale max|x| / 127 of the row): one warp per (token, kv head) and tensor
 __global__ void kv_append_q8_kernel(const float* k, const float* v, int64_t ld, uint8_t* k_cache, uint8_t* v_cache, const int32_t* positions,
-                                    const int32_t* page_rows, int n_kv_heads, int d, int page) {
+                                    const int32_t* page_rows, int n_kv_heads, int d, int page, int num_pages) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int pos = positions[t];
   if (pos < 0) return;
   const int pg = page_rows[t], slot = pos % page;
+  if (num_pages > 0 && (unsigned)pg >= (unsigned)num_pages) { if (threadIdx.x == 0) index_error(3402); return; }
   const int rowb = d + 16;
   for (int job = warp; job < 2 * n_kv_heads; job += nw) {
     const int h = job >> 1;
@@ -202,6 +214,7 @@ __global__ void page_rows_kernel(const int32_t* page_table, int64_t ld, const in
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int pos = positions[i];
+  if (pos >= 0 && pos / page >= ld) { index_error(3403); out[i] = -1; return; }      // -1: the append that follows skips the row (3402)
   out[i] = pos >= 0 ? page_table[(int64_t)i * ld + pos / page] : 0;
 }
 
@@ -422,15 +435,23 @@ int rlz_elementwise(const float* a, const float* b, const float* bias, const flo
 }
 
 int rlz_kv_append_q8(const float* k, const float* v, long long ld, void* k_cache, void* v_cache, const int32_t* positions,
-                     const int32_t* page_rows, int n_tokens, int n_kv_heads, int d, int page, void* stream) {
+                     const int32_t* page_rows, int n_tokens, int n_kv_heads, int d, int page, int num_pages, void* stream) {
   return (int)launch(kv_append_q8_kernel, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, k, v, (int64_t)ld, (uint8_t*)k_cache,
-                     (uint8_t*)v_cache, positions, page_rows, n_kv_heads, d, page);
+                     (uint8_t*)v_cache, positions, page_rows, n_kv_heads, d, page, num_pages);
 }
 
 int rlz_kv_append(const float* k, const float* v, long long ld, void* k_cache, void* v_cache, const int32_t* positions,
-                  const int32_t* page_rows, int n_tokens, int n_kv_heads, int d, int page, void* stream) {
+                  const int32_t* page_rows, int n_tokens, int n_kv_heads, int d, int page, int num_pages, void* stream) {
   return (int)launch(kv_append_kernel, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, k, v, (int64_t)ld, (__nv_bfloat16*)k_cache,
-                     (__nv_bfloat16*)v_cache, positions, page_rows, n_kv_heads, d, page);
+                     (__nv_bfloat16*)v_cache, positions, page_rows, n_kv_heads, d, page, num_pages);
+}
+
+// 0 / first code recorded by an index guard of this file (3401-3403)
+int rlz_index_error(int clear) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, rlz::g_index_error, sizeof(int)) != cudaSuccess) return -1;
+  if (clear && v) { int z = 0; cudaMemcpyToSymbol(rlz::g_index_error, &z, sizeof(int)); }
+  return v;
 }
 
 int rlz_page_rows(const int32_t* page_table, long long ld, const int32_t* positions, int32_t* out, int n, int page, void* stream) {

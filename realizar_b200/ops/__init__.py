@@ -234,7 +234,7 @@ def device_error(clear: bool = True) -> int:
     """Error code recorded by a kernel whose bounded wait expired (0 = none)."""
     c = 1 if clear else 0
     return (int(lib().rlz_device_error(c)) or int(lib().rlz_gemv_slab_error(c)) or int(lib().rlz_gemm_error(c))
-            or int(lib().rlz_attn_decode_error(c)) or int(lib().rlz_attn_prefill_error(c)))
+            or int(lib().rlz_attn_decode_error(c)) or int(lib().rlz_attn_prefill_error(c)) or int(lib().rlz_index_error(c)))
 
 
 def gemv(w: DeviceWeight, x: torch.Tensor, bias=None, act=ACT_NONE, residual=None, norm=NORM_NONE, norm_w=None, norm_b=None,
@@ -405,7 +405,7 @@ def kv_append(k, v, k_cache, v_cache, positions, page_rows, n_kv_heads, d, page=
     """Write the rows of ``k`` / ``v`` at their positions into the paged cache (bf16 rows, or int8 rows with a per-row scale)."""
     fn = lib().rlz_kv_append_q8 if k_cache.dtype in (torch.uint8, torch.int8) else lib().rlz_kv_append
     check(fn(k.data_ptr(), v.data_ptr(), k.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(),
-                              page_rows.data_ptr(), k.shape[0], n_kv_heads, d, page, stream_ptr()), "kv_append")
+             page_rows.data_ptr(), k.shape[0], n_kv_heads, d, page, k_cache.shape[0], stream_ptr()), "kv_append")
 
 
 def page_rows(page_table: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n: int, page: int) -> None:

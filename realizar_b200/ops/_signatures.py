@@ -158,7 +158,7 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_rope.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_int, c_int, c_float, c_void_p, c_int, c_void_p]
     lib.rlz_elementwise.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_longlong,
                                     c_longlong, c_int, c_int, c_void_p]
-    lib.rlz_kv_append.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+    lib.rlz_kv_append.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
     lib.rlz_kv_append_q8.argtypes = lib.rlz_kv_append.argtypes
     lib.rlz_to_bf16.argtypes = [c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_longlong, c_void_p]
     lib.rlz_norm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_float, c_void_p]

@@ -49,6 +49,7 @@ class EngineConfig:
     prefix_cache: bool = False             # share full KV pages between prompts with a common prefix
     parity_gate: bool = False              # at load: GPU vs CPU logits on the BOS token must agree (cosine >= 0.99)
     kv_dtype: str = "bf16"                 # "q8": int8 KV rows with a per-(token, head) scale (half the cache memory)
+    canaries: bool = False                 # guard bands around every step buffer, inspected by check_health() (also RLZ_CANARIES=1)
     batch_buckets: Sequence[int] = ()      # graph buckets; default powers of two up to max_batch
     seed: int = 0
 
@@ -117,7 +118,18 @@ class DecodeEngine:
         o_k = max(L.o.k for L in m.layers)
         d_k = max(L.down.k for L in m.layers)
         y1_w = (m.act_col0 + d_k + 256) if self.mcfg.parallel_residual else qkv_w
-        z = lambda *s, dt=torch.float32: torch.zeros(*s, device=dev, dtype=dt)
+        # step buffers: plain zeros, or (canaries) tensors with guard bands on both sides that check_health() inspects
+        self.guards = None
+        if c.canaries or os.environ.get("RLZ_CANARIES", "0") != "0":
+            from .memory import GuardBands
+            self.guards = GuardBands(dev)
+        _n = [0]
+
+        def z(*s, dt=torch.float32):
+            if self.guards is None:
+                return torch.zeros(*s, device=dev, dtype=dt)
+            _n[0] += 1
+            return self.guards.zeros(*s, dtype=dt, name=f"step buffer {_n[0]} {tuple(s)} {str(dt).split('.')[-1]}")
         self.buckets = sorted(set(c.batch_buckets or [b for b in (1, 2, 4, 8, 16, 32, 64, 128) if b < B] + [B]))
         part, ctr = ops.attn_decode_scratch(max(b * self.splits_for(b) for b in self.buckets), m.heads, 1, hd, dev)
         # tokens and positions are the two rows of one buffer (and of one pinned host buffer), so a step uploads both with one copy
@@ -293,6 +305,10 @@ class DecodeEngine:
         if code:
             raise ops.KernelError(f"a device-side check failed with status {code}: a bounded wait expired or an index left its range; "
                                   "results since the last check are not valid")
+        if self.guards is not None:
+            bad = self.guards.check()
+            if bad:
+                raise ops.KernelError("guard bands overwritten next to: " + "; ".join(bad))
 
     def profile_step(self, batch: int = 1, steps: int = 4) -> dict:
         """Per-operation timing of the decode step at this batch: the plan is run launch by launch (no graph) with every launch

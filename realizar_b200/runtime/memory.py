@@ -220,3 +220,39 @@ class HybridScheduler:
             return ComputeBackend.CPU
         gpu_cost = elements / self.gpu_speedup * (1.0 if operands_on_device else 1.0 + self.pcie_cost_factor)
         return ComputeBackend.GPU if gpu_cost < elements else ComputeBackend.CPU
+
+
+class GuardBands:
+    """Allocator of zero-initialised tensors with canary bands: ``BAND`` bytes of a fixed pattern before and after every
+    tensor (the tail up to the next 256-byte boundary included).  ``check()`` names the tensors whose bands changed: a kernel
+    wrote outside the buffer it was given.  The engine allocates its step buffers through this when ``canaries`` is set and
+    checks the bands in ``check_health()``.  Host-side stand-in for the guard pages a memory checker would give."""
+    BAND = 256
+    PATTERN = 0xA5
+
+    def __init__(self, device="cpu"):
+        self.device = torch.device(device)
+        self.entries: List[tuple] = []                     # (name, raw uint8 tensor, payload bytes)
+
+    def zeros(self, *shape, dtype=torch.float32, name: str = "") -> torch.Tensor:
+        n = 1
+        for d in shape:
+            n *= int(d)
+        nbytes = n * torch.empty(0, dtype=dtype).element_size()
+        padded = (nbytes + 255) // 256 * 256
+        raw = torch.full((2 * self.BAND + padded,), self.PATTERN, dtype=torch.uint8, device=self.device)
+        raw[self.BAND: self.BAND + nbytes] = 0
+        self.entries.append((name or f"buffer{len(self.entries)}", raw, nbytes))
+        return raw[self.BAND: self.BAND + nbytes].view(dtype).view(*shape)
+
+    def check(self) -> List[str]:
+        """Names of the tensors with an overwritten band (one reduction per tensor; synchronises)."""
+        bad = []
+        for name, raw, nbytes in self.entries:
+            front, back = raw[: self.BAND], raw[self.BAND + nbytes:]
+            if bool((front != self.PATTERN).any()) or bool((back != self.PATTERN).any()):
+                bad.append(name)
+        return bad
+
+    def bytes_reserved(self) -> int:
+        return sum(int(raw.numel()) for _, raw, _ in self.entries)

@@ -53,6 +53,53 @@ def check_block_layouts() -> List[str]:
     return bad
 
 
+def parse_ptxas_report(text: str) -> List[dict]:
+    """Entries of a ptxas ``-v`` report: mangled name, kernel base name, registers, barriers, spill bytes, stack, static smem."""
+    import re
+    out = []
+    pat = re.compile(r"Compiling entry function '(\S+)' for 'sm_100a'\n.*?\n\s+(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads\n"
+                     r".*?Used (\d+) registers(?:, used (\d+) barriers)?(?:, \d+ bytes cumulative stack size)?(?:, (\d+) bytes smem)?")
+    for m in pat.finditer(text):
+        name = m.group(1)
+        b = re.search(r"_ZN3rlz(\d+)", name)
+        base = name
+        if b:
+            i = b.end()
+            base = name[i:i + int(b.group(1))]
+        out.append({"name": name, "kernel": base, "stack": int(m.group(2)), "spill_stores": int(m.group(3)), "spill_loads": int(m.group(4)),
+                    "registers": int(m.group(5)), "barriers": int(m.group(6) or 0), "static_smem": int(m.group(7) or 0)})
+    return out
+
+
+def check_kernel_parity(report_dir=None) -> List[str]:
+    """Hold the compiled kernels to ``contracts/kernel_parity.yaml``.  Returns the violations; raises FileNotFoundError when the
+    build's resource reports are not there (nothing built in this tree yet)."""
+    report_dir = Path(report_dir) if report_dir else Path(__file__).resolve().parents[1] / "_lib" / "obj"
+    bad, cache = [], {}
+    for fam in load("kernel_parity")["families"]:
+        path = report_dir / f"{fam['file']}.ptxas.txt"
+        if fam["file"] not in cache:
+            if not path.exists():
+                raise FileNotFoundError(path)
+            cache[fam["file"]] = parse_ptxas_report(path.read_text())
+        ks = [e for e in cache[fam["file"]] if e["kernel"] == fam["kernel"]]
+        tag = fam["kernel"]
+        if len(ks) < fam.get("min_instantiations", 1):
+            bad.append(f"{tag}: {len(ks)} instantiations, contract wants at least {fam.get('min_instantiations', 1)}")
+            continue
+        worst = max(e["registers"] for e in ks)
+        if worst > fam["max_registers"]:
+            bad.append(f"{tag}: {worst} registers > {fam['max_registers']}")
+        spill = max(e["spill_stores"] for e in ks)
+        if spill > fam.get("max_spill_bytes", 0):
+            bad.append(f"{tag}: {spill} bytes of spill stores > {fam.get('max_spill_bytes', 0)}")
+        if fam.get("same_static_smem") and len({e["static_smem"] for e in ks}) != 1:
+            bad.append(f"{tag}: variants differ in static shared memory {sorted({e['static_smem'] for e in ks})}")
+        if fam.get("same_barriers") and len({e["barriers"] for e in ks}) != 1:
+            bad.append(f"{tag}: variants differ in barrier count {sorted({e['barriers'] for e in ks})}")
+    return bad
+
+
 def required_tensors(fused_qkv: bool, gated: bool, parallel_residual: bool, layers: int) -> List[str]:
     doc = load("model_load")
     per = list(doc["required_per_layer"]["fused_qkv" if fused_qkv else "separate_qkv"])

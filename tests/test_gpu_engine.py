@@ -350,3 +350,44 @@ def test_other_weight_types_run_prompts_on_the_tensor_core_path(cuda_device, sch
     assert ops.device_error() == 0
     out = eng.feed({0: int(lb.argmax())})
     assert 0 <= int(out[0]) < cfg.vocab_size
+
+
+def test_canaries_and_index_guards(cuda_device):
+    """Guard bands around the step buffers stay intact over prompt passes and decode steps and a damaged band is reported; device
+    indices outside their range are skipped and recorded (no access is made with them)."""
+    from realizar_b200 import ops
+    from realizar_b200.models.weights import synthetic_weights
+    from realizar_b200.runtime.engine import DecodeEngine, EngineConfig, SamplingParams
+    w = synthetic_weights(_kq_llama(), seed=2, std=0.05)
+    eng = DecodeEngine(w, EngineConfig(max_batch=4, max_seq_len=128, canaries=True))
+    assert eng.guards is not None and len(eng.guards.entries) > 10
+    eng.generate([(5 * i + 1) % 500 for i in range(40)], SamplingParams(max_tokens=12, temperature=0.8, top_k=20))
+    eng.generate([1, 2, 3], SamplingParams(max_tokens=4))
+    eng.check_health()                                       # nothing wrote outside its buffer
+    name, raw, nbytes = eng.guards.entries[3]
+    raw[eng.guards.BAND + nbytes + 5] = 0                    # damage one band from the host
+    with pytest.raises(ops.KernelError, match="guard bands"):
+        eng.check_health()
+    raw[eng.guards.BAND + nbytes + 5] = eng.guards.PATTERN
+    eng.check_health()
+    # index guards
+    assert ops.device_error() == 0
+    H, V = 64, 100
+    table = torch.randn(V, H, device="cuda")
+    out = torch.full((3, H), 7.0, device="cuda")
+    toks = torch.tensor([5, 1000, -2], device="cuda", dtype=torch.int32)
+    ops.embed(table.view(torch.uint8).reshape(V, -1), 0, H * 4, H, V, toks, out, None, None)
+    torch.cuda.synchronize()
+    assert torch.equal(out[0], table[5]) and float(out[1:].abs().sum()) == 0 and ops.device_error() == 3401       # (-2 marks an idle row: zeros, no error)
+    kc = torch.zeros(4, 2, 16, 8, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    kv = torch.randn(2, 2 * 8, device="cuda")
+    pos = torch.tensor([3, 20], device="cuda", dtype=torch.int32)
+    ops.kv_append(kv, kv, kc, vc, pos, torch.tensor([1, 9], device="cuda", dtype=torch.int32), 2, 8)     # page 9 of a 4-page cache
+    torch.cuda.synchronize()
+    assert float(kc[1].abs().sum()) > 0 and ops.device_error() == 3402
+    pt = torch.zeros(2, 3, device="cuda", dtype=torch.int32)
+    rows = torch.zeros(2, device="cuda", dtype=torch.int32)
+    ops.page_rows(pt, torch.tensor([10, 100], device="cuda", dtype=torch.int32), rows, 2, 16)            # position 100 needs page-table column 6 of 3
+    torch.cuda.synchronize()
+    assert rows.tolist() == [0, -1] and ops.device_error() == 3403

@@ -222,3 +222,19 @@ def test_step_program_builder_packs_ops_and_rejects_bad_programs():
         b2.add_attn(a)
     with pytest.raises(ValueError):
         StepProgramBuilder(StubLib(), dev, 1, 8, 148).add_attn(S.AttnDecodeParams(n_heads=8, n_kv_heads=1, splits=1, batch=1))
+
+
+def test_guard_bands_name_the_overwritten_buffer():
+    import torch
+    from realizar_b200.runtime.memory import GuardBands
+    g = GuardBands("cpu")
+    a = g.zeros(5, 7, name="a")
+    b = g.zeros(33, dtype=torch.int32, name="b")
+    assert a.shape == (5, 7) and float(a.abs().sum()) == 0 and b.dtype == torch.int32
+    a.fill_(3.0); b.fill_(-1)                                # writes inside the tensors leave the bands alone
+    assert g.check() == []
+    raw_b = g.entries[1][1]
+    raw_b[GuardBands.BAND + 33 * 4] = 0                      # one byte past the end of b
+    assert g.check() == ["b"]
+    g.entries[0][1][GuardBands.BAND - 1] = 1                 # one byte before a
+    assert g.check() == ["a", "b"] and g.bytes_reserved() >= 2 * 2 * GuardBands.BAND + 5 * 7 * 4 + 33 * 4
