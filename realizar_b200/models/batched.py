@@ -99,7 +99,7 @@ class BatchedForward:
             return self.x[:T]
         x = self.forward(T, self.pt_row, shared_table=True, pos0=pos0, pos0_dev=self.positions)
         seen = self._chunk_seen[T] = self._chunk_seen.get(T, 0) + 1
-        if self.chunk_graphs and len(self._chunk_graphs) < 16 and (T == self.T or seen >= 2):
+        if self.chunk_graphs and not self.model.streaming and len(self._chunk_graphs) < 16 and (T == self.T or seen >= 2):
             torch.cuda.synchronize(self.model.device)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
@@ -189,7 +189,9 @@ class BatchedForward:
         ops.embed(m.embed_table, m.embed_qtype, m.embed_row_bytes, H, cfg.vocab_size, self.tokens[:T], self.x, m.pos_table, self.positions)
         self.launches_per_pass += 1
         ts = self.two_shot
+        order = list(range(len(m.layers)))
         for l, L in enumerate(m.layers):
+            m.acquire_layer(l)                                 # streamed layers: wait for the copy into their buffer (no-op otherwise)
             nxt = m.layers[l + 1] if l + 1 < len(m.layers) else None
             next_attn_norm = (norm_t, nxt.attn_norm_w, nxt.attn_norm_b) if nxt is not None else None
             if not ts or l == 0:                               # two-shot: the previous layer's reduce wrote this layer's operand
@@ -263,4 +265,5 @@ class BatchedForward:
                     self._two_shot(L.down, self.act_b[:T, : L.down.k], T, L.down_b, None, next_attn_norm, final=nxt is None)
                 else:
                     self._row_parallel(L.down, self.act_b[:T, : L.down.k], T, L.down_b)
+            m.release_layer(l, m.prefetch_after(order, l) if m.streaming else None)
         return x

@@ -21,7 +21,7 @@ from __future__ import annotations
 import logging
 import os
 from dataclasses import dataclass, field
-from typing import Callable, List, Optional, Sequence
+from typing import Callable, Dict, List, Optional, Sequence
 
 import numpy as np
 import torch
@@ -135,9 +135,13 @@ def make_rope_table(cfg, device, max_positions: Optional[int] = None) -> torch.T
 class GpuModel:
     """Weights of one (shard of a) decoder on one GPU."""
 
-    def __init__(self, weights: ModelWeights, device="cuda", tp_rank: int = 0, tp_size: int = 1):
+    def __init__(self, weights: ModelWeights, device="cuda", tp_rank: int = 0, tp_size: int = 1, resident_layers: Optional[int] = None):
+        """``resident_layers``: keep only the first that many layers' matrices on the device; the others stay in pinned host
+        memory and are streamed through two device buffers while the model runs (models larger than the device)."""
         cfg = weights.config
         self.cfg = cfg
+        self.streamed_from = cfg.num_layers                  # first layer whose matrices are streamed (= num_layers: none)
+        self._stream: Dict[int, dict] = {}
         self.device = torch.device(device)
         self.tp_rank, self.tp_size = tp_rank, tp_size
         if cfg.num_heads % tp_size or cfg.num_kv_heads % tp_size or cfg.intermediate_dim % tp_size:
@@ -228,6 +232,92 @@ class GpuModel:
             ub = _f32(g("ffn_up.bias"), dev)
             L.up_b = ub[i0:i1].contiguous() if ub is not None else None
             self.layers.append(L)
+            if resident_layers is not None and l >= max(0, resident_layers):
+                self._offload_layer(l, L)
+        if self._stream:
+            self._finish_streaming()
+
+    # -- layer streaming: matrices of the later layers live in pinned host memory ------------------------------------------
+    # (role of the reference's streaming plan and layer prefetcher, src/cuda/streaming.rs:36-219)
+    @staticmethod
+    def _layer_mats(L) -> list:
+        """The distinct device matrices of a layer (Q, K, V count once when they are row ranges of one matrix)."""
+        base = [L.qkv] if L.qkv is not None else [L.q, L.k, L.v]
+        return [w for w in base + [L.o, L.gate, L.up, L.down] if w is not None]
+
+    def _offload_layer(self, l: int, L) -> None:
+        mats = self._layer_mats(L)
+        off, spans = 0, []
+        for w in mats:
+            spans.append((off, w.data.shape[0], w.data.shape[1]))
+            off += (w.data.numel() + 255) // 256 * 256
+        host = torch.empty(off, dtype=torch.uint8, pin_memory=True)
+        for w, (o, n, stride) in zip(mats, spans):
+            host[o:o + n * stride].copy_(w.data.reshape(-1))
+        qkv_rows = (L.q.n, L.k.n, L.v.n) if L.qkv is not None else None
+        for w in mats + ([L.q, L.k, L.v] if L.qkv is not None else []):
+            w.data = None                                    # the device copy goes; views are re-created over the stream buffers
+        self._stream[l] = {"host": host, "spans": spans, "bytes": off, "qkv_rows": qkv_rows}
+        self.streamed_from = min(self.streamed_from, l)
+
+    def _finish_streaming(self) -> None:
+        dev = self.device
+        size = max(st["bytes"] for st in self._stream.values())
+        self._slots = [torch.empty(size, dtype=torch.uint8, device=dev) for _ in range(2)]
+        self._slot_layer = [-1, -1]
+        self._side = torch.cuda.Stream(dev)
+        self._ready = [torch.cuda.Event(), torch.cuda.Event()]
+        self._freed = [torch.cuda.Event(), torch.cuda.Event()]
+        self._freed_valid = [False, False]
+        self.stream_copies = 0
+        for l, st in self._stream.items():
+            L, buf = self.layers[l], self._slots[(l - self.streamed_from) & 1]
+            for w, (o, n, stride) in zip(self._layer_mats(L), st["spans"]):
+                w.data = buf[o:o + n * stride].view(n, stride)
+            if st["qkv_rows"] is not None:
+                r1, r2, r3 = st["qkv_rows"][0], st["qkv_rows"][0] + st["qkv_rows"][1], sum(st["qkv_rows"])
+                L.q, L.k, L.v = L.qkv.rows(0, r1), L.qkv.rows(r1, r2), L.qkv.rows(r2, r3)
+
+    @property
+    def streaming(self) -> bool:
+        return bool(self._stream)
+
+    def _issue_copy(self, l: int) -> None:
+        slot, st = (l - self.streamed_from) & 1, self._stream[l]
+        with torch.cuda.stream(self._side):
+            if self._freed_valid[slot]:
+                self._side.wait_event(self._freed[slot])     # the layer that used this buffer last has been consumed
+            self._slots[slot][:st["bytes"]].copy_(st["host"], non_blocking=True)
+            self._ready[slot].record(self._side)
+        self._slot_layer[slot] = l
+        self.stream_copies += 1
+
+    def acquire_layer(self, l: int) -> None:
+        """Before the first launch of layer ``l``: its matrices are (being) copied into their buffer; the current stream waits."""
+        if l < self.streamed_from or not self._stream:
+            return
+        slot = (l - self.streamed_from) & 1
+        if self._slot_layer[slot] != l:
+            self._issue_copy(l)
+        torch.cuda.current_stream(self.device).wait_event(self._ready[slot])
+
+    def release_layer(self, l: int, prefetch: Optional[int] = None) -> None:
+        """After the last launch of layer ``l``: its buffer may be refilled; ``prefetch`` names the layer to start copying into it."""
+        if l < self.streamed_from or not self._stream:
+            return
+        slot = (l - self.streamed_from) & 1
+        self._freed[slot].record(torch.cuda.current_stream(self.device))
+        self._freed_valid[slot] = True
+        if prefetch is not None and prefetch != l and prefetch >= self.streamed_from and ((prefetch - self.streamed_from) & 1) == slot:
+            self._issue_copy(prefetch)
+
+    def prefetch_after(self, order: Sequence[int], i: int) -> Optional[int]:
+        """The layer to prefetch when ``order[i]`` is done, for a pass that visits the layers in ``order``: the streamed layer two
+        places on (the next one already sits in the other buffer), wrapping to the start of the next pass."""
+        s = [l for l in order if l >= self.streamed_from]
+        if len(s) <= 2 or order[i] not in s:
+            return None
+        return s[(s.index(order[i]) + 2) % len(s)]
 
     def weight_bytes(self) -> int:
         tot = self.lm_head.nbytes
@@ -576,10 +666,13 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
         if tp and not use_ar:
             plan.add(lambda: reduce_into_x(buf.partial_out[:batch]), launches=1)
 
+    order = [l for l in range(len(model.layers)) if layer_subset is None or l in layer_subset]
     for l, L in enumerate(model.layers):
         if layer_subset is not None and l not in layer_subset:
             continue
         kc, vc = k_cache[l], v_cache[l]
+        if model.streaming and l >= model.streamed_from:     # streamed layer: wait for its matrices (stream operations, no launch)
+            plan.add(lambda l=l: model.acquire_layer(l), launches=0)
         for c0, cb in chunks:
             x = buf.x[c0:]
             xin = VecIn(x, H, ld=buf.x.stride(0), norm=norm_t, norm_w=L.attn_norm_w, norm_b=L.attn_norm_b, eps=cfg.eps)
@@ -625,6 +718,8 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
                 plan.add_gemv_auto([xin], [mat], buf.act[c0:, L.down_in_off:], cb, buf.act.stride(0), target_ctas=target)
             row_parallel(lambda c0: [VecIn(buf.act[c0:], L.down.k, ld=buf.act.stride(0), pre=buf.act_q if handoff(L) else None)],
                          lambda res: MatOut([(L.down, 0)], bias=L.down_b, residual=res))
+        if model.streaming and l >= model.streamed_from:
+            plan.add(lambda l=l, nxt=model.prefetch_after(order, order.index(l)): model.release_layer(l, nxt), launches=0)
 
     emit_head(plan, model, buf, 0, batch, comm, greedy_only, sm_count, target_ctas=target if p_occ else None)
     plan.ar_sites = site[0]

@@ -13,6 +13,7 @@ src/cuda/executor/layers/forward_graphed_decode.rs:18-211) and with its batched 
 """
 from __future__ import annotations
 
+import dataclasses
 import logging
 import os
 from dataclasses import dataclass, field
@@ -49,6 +50,7 @@ class EngineConfig:
     prefix_cache: bool = False             # share full KV pages between prompts with a common prefix
     parity_gate: bool = False              # at load: GPU vs CPU logits on the BOS token must agree (cosine >= 0.99)
     kv_dtype: str = "bf16"                 # "q8": int8 KV rows with a per-(token, head) scale (half the cache memory)
+    resident_layers: Optional[int] = None  # layers whose matrices stay on the device; None = all if they fit, else as many as fit (the rest is streamed)
     canaries: bool = False                 # guard bands around every step buffer, inspected by check_health() (also RLZ_CANARIES=1)
     batch_buckets: Sequence[int] = ()      # graph buckets; default powers of two up to max_batch
     seed: int = 0
@@ -93,7 +95,27 @@ class DecodeEngine:
                                f"sm_{self.profile.compute_capability[0]}{self.profile.compute_capability[1]}")
         self.cfg = config or EngineConfig(**self.profile.engine_config_overrides())
         self.comm = comm
-        self.model = GpuModel(weights, self.device, tp_rank, tp_size)
+        resident = self.cfg.resident_layers
+        if resident is None:
+            # does the model fit next to its KV cache?  If not, keep as many layers resident as fit and stream the others from
+            # pinned host memory through two device buffers (the plan of the reference's src/cuda/streaming.rs:36-219)
+            from .memory import StreamingMode, check_vram_sufficient
+            wc, c0 = weights.config, self.cfg
+            pages = c0.num_pages or c0.max_batch * -(-c0.max_seq_len // PAGE)
+            rowb = (wc.head_dim + 16) if c0.kv_dtype == "q8" else 2 * wc.head_dim
+            kv_est = 2 * wc.num_layers * pages * (wc.num_kv_heads // max(1, tp_size)) * PAGE * rowb
+            free_bytes, _t = torch.cuda.mem_get_info(self.device)
+            try:
+                plan = check_vram_sufficient(weights.total_bytes() // max(1, tp_size), kv_est, free_bytes, wc.num_layers)
+            except MemoryError as e:
+                raise RuntimeError(f"model does not fit on {self.profile.name} even with layer streaming: {e}") from None
+            if plan.mode == StreamingMode.LAYER_STREAMING:
+                resident = plan.resident_layers
+                log.warning("weights + KV cache exceed the free device memory: %d of %d layers resident, the rest streamed from host memory",
+                            resident, wc.num_layers)
+        self.model = GpuModel(weights, self.device, tp_rank, tp_size, resident_layers=resident)
+        if self.model.streaming:                             # copies on a side stream between launches: no captured graphs
+            self.cfg = dataclasses.replace(self.cfg, cuda_graphs=False, persistent_step=False)
         self.mcfg = self.model.cfg
         m, c, dev = self.model, self.cfg, self.device
         self.sm_count = self.profile.sm_count

@@ -391,3 +391,35 @@ def test_canaries_and_index_guards(cuda_device):
     ops.page_rows(pt, torch.tensor([10, 100], device="cuda", dtype=torch.int32), rows, 2, 16)            # position 100 needs page-table column 6 of 3
     torch.cuda.synchronize()
     assert rows.tolist() == [0, -1] and ops.device_error() == 3403
+
+
+@pytest.mark.parametrize("which", ["llama", "phi2"])
+def test_layer_streaming_matches_resident_engine(cuda_device, which):
+    """Only the first layer's matrices stay on the device; the other four are streamed from pinned host memory through two
+    buffers (prompt pass on the tensor-core path, decode steps on the GEMV path, a layer-skipping draft step): same tokens and
+    logits as the engine that keeps everything resident."""
+    import dataclasses
+    from realizar_b200.models.weights import synthetic_weights
+    from realizar_b200.runtime.engine import DecodeEngine, EngineConfig, SamplingParams
+    cfg = dataclasses.replace(_kq_llama() if which == "llama" else small_phi2(), num_layers=5)
+    w = synthetic_weights(cfg, seed=4, std=0.05)
+    prompt = [int(t) for t in np.random.default_rng(2).integers(0, cfg.vocab_size, 37)]
+    outs, logits = [], []
+    for resident in (None, 1):
+        eng = DecodeEngine(w, EngineConfig(max_batch=2, max_seq_len=128, greedy_only=True, resident_layers=resident))
+        assert eng.model.streaming == (resident is not None)
+        outs.append(eng.generate(prompt, SamplingParams(max_tokens=10)))
+        eng.open_slot(0, 64)
+        eng.prefill(0, prompt[:9])
+        eng.draft_step(0, 5, (0, 2, 4))                     # a pass over a subset of the layers
+        eng.feed({0: 7})
+        logits.append(eng.logits_of_last_step(0).float().cpu().numpy())
+        eng.check_health()
+        if resident is not None:
+            assert eng.model.stream_copies > 4 * 10          # the four streamed layers were copied in every pass
+            assert not eng.cfg.cuda_graphs
+        eng.close()
+        del eng
+        torch.cuda.synchronize()
+    assert outs[0] == outs[1], outs
+    assert _cos(logits[0], logits[1]) > 0.9999
