@@ -466,7 +466,8 @@ def create_app(state: AppState) -> FastAPI:
             first = {**base, "choices": [{"index": 0, "delta": {"role": "assistant"}, "finish_reason": None}]}
             return sse_stream({"args": (ids, *params), "extra": controls_of(req), "stops": req.stop}, first,
                               lambda _tid, text: {**base, "choices": [{"index": 0, "delta": {"content": text}, "finish_reason": None}]},
-                              lambda r: {**base, "choices": [{"index": 0, "delta": {}, "finish_reason": _finish_reason(r)}]})
+                              lambda r: {**base, "choices": [{"index": 0, "delta": {}, "finish_reason": _finish_reason(r)}],
+                                         "usage": {"prompt_tokens": len(ids), "completion_tokens": len(r.output), "total_tokens": len(ids) + len(r.output)}})
         r = await run_blocking(ids, *params, extra=controls_of(req))
         text = apply_stops(text_of(r), req.stop)
         audit(rid, "chat.completions", len(ids), len(r.output), (r.finish_time or time.monotonic()) - r.arrival)

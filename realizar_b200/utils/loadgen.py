@@ -40,7 +40,8 @@ class RequestTrace:
     first_token: Optional[float] = None
     token_times: List[float] = field(default_factory=list)
     end: Optional[float] = None
-    tokens: int = 0
+    tokens: int = 0                       # streamed content events
+    generated: Optional[int] = None       # tokens generated according to the server's final usage record
     error: Optional[str] = None
 
     @property
@@ -57,9 +58,9 @@ def summarize(traces: List[RequestTrace], wall_s: float) -> dict:
     ttft = [1e3 * t.ttft for t in ok if t.ttft is not None]
     itl = [1e3 * d for t in ok for d in np.diff(t.token_times)]
     lat = [1e3 * (t.end - t.start) for t in ok]
-    toks = sum(t.tokens for t in ok)
+    toks = sum(t.generated if t.generated is not None else t.tokens for t in ok)      # generated tokens; events when the server sends no usage
     return {"requests": len(traces), "completed": len(ok), "errors": len(traces) - len(ok), "wall_s": wall_s,
-            "req_per_s": len(ok) / wall_s if wall_s else 0.0, "tok_per_s": toks / wall_s if wall_s else 0.0, "tokens": toks,
+            "req_per_s": len(ok) / wall_s if wall_s else 0.0, "tok_per_s": toks / wall_s if wall_s else 0.0, "tokens": toks, "events": sum(t.tokens for t in ok),
             "ttft_ms": {"p50": _pct(ttft, 50), "p95": _pct(ttft, 95), "p99": _pct(ttft, 99)},
             "itl_ms": {"p50": _pct(itl, 50), "p95": _pct(itl, 95), "p99": _pct(itl, 99)},
             "latency_ms": {"p50": _pct(lat, 50), "p95": _pct(lat, 95), "p99": _pct(lat, 99)}}
@@ -97,6 +98,8 @@ def _consume_sse_line(line: str, tr: RequestTrace) -> bool:
     if "error" in obj:
         tr.error = str(obj["error"])
         return True
+    if isinstance(obj.get("usage"), dict) and "completion_tokens" in obj["usage"]:
+        tr.generated = int(obj["usage"]["completion_tokens"])          # the server's own count (events can carry several tokens)
     ch = (obj.get("choices") or [{}])[0]
     if (ch.get("delta") or {}).get("content"):
         now = time.perf_counter()
