@@ -498,7 +498,8 @@ int rlz_attn_prefill_error(int clear) {
 // 1 when the tensor-core prefill kernel has an instantiation for this head size
 int rlz_attn_prefill_supported(int head_dim) { return head_dim == 64 || head_dim == 80 || head_dim == 96 || head_dim == 128; }
 
-int rlz_attn_prefill(const rlz::AttnPrefillParams* pp, void* stream) {
+// impl: -1 = the default choice (or RLZ_PREFILL_ATT), 0 = tcgen05 kernel, 1 = mma.sync kernel (bf16 caches only)
+int rlz_attn_prefill_impl(const rlz::AttnPrefillParams* pp, void* stream, int impl) {
   using namespace rlz;
   const AttnPrefillParams& p = *pp;
   if (p.n_tokens < 1 || p.n_kv_heads < 1 || p.n_heads % p.n_kv_heads || p.pos0 < 0 || p.window < 0) return -2;
@@ -509,7 +510,9 @@ int rlz_attn_prefill(const rlz::AttnPrefillParams* pp, void* stream) {
   static const int impl_env = [] { const char* e = getenv("RLZ_PREFILL_ATT"); return !e ? -1 : (e[0] == 'm' ? 1 : 0); }();
   // default: mma where whole pages can be copied (head_dim 80: TTFT of a 512-token Phi-2-shaped prompt 8.0 vs 9.1 ms); with
   // row-by-row copies (head_dim 128, 1024-token Llama-3-8B-shaped prompt) the two measured the same (35.9 vs 35.2 ms)
-  const bool use_mma = !p.kv_q8 && (impl_env < 0 ? p.head_dim == 80 : impl_env == 1);
+  const int want = impl >= 0 ? impl : impl_env;
+  if (want == 1 && p.kv_q8) return -5;
+  const bool use_mma = !p.kv_q8 && (want < 0 ? p.head_dim == 80 : want == 1);
   if (use_mma) {
     switch (p.head_dim) {
       case 64: return launch_prefill_mma<64>(p, st);
@@ -527,6 +530,8 @@ int rlz_attn_prefill(const rlz::AttnPrefillParams* pp, void* stream) {
     default: return -1;
   }
 }
+
+int rlz_attn_prefill(const rlz::AttnPrefillParams* pp, void* stream) { return rlz_attn_prefill_impl(pp, stream, -1); }
 
 int rlz_sizeof_attn_prefill_params() { return (int)sizeof(rlz::AttnPrefillParams); }
 

@@ -99,7 +99,14 @@ class LLM:
         self.cfg = self.weights.config
         self.tokenizer = build_tokenizer(self.weights)
         self.template = build_template(self.weights, self.path.stem)
-        self.used_gpu = torch.cuda.is_available() if use_gpu is None else bool(use_gpu)
+        if use_gpu is None:
+            # automatic choice: the GPU when there is one, unless the model is so small that moving it there costs more than
+            # running it here (the hybrid dispatch heuristic; weights count as operands that are not on the device yet)
+            from .runtime.memory import ComputeBackend, HybridScheduler
+            pick = HybridScheduler(gpu_available=torch.cuda.is_available()).choose(self.weights.total_bytes())
+            self.used_gpu = pick == ComputeBackend.GPU
+        else:
+            self.used_gpu = bool(use_gpu)
         self.max_seq_len = min(max_seq_len, self.cfg.context_length)
         if self.used_gpu:
             from .runtime.engine import DecodeEngine, EngineConfig

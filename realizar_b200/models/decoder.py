@@ -251,7 +251,8 @@ class GpuModel:
         for w in mats:
             spans.append((off, w.data.shape[0], w.data.shape[1]))
             off += (w.data.numel() + 255) // 256 * 256
-        host = torch.empty(off, dtype=torch.uint8, pin_memory=True)
+        from ..runtime.memory import PinnedHostBuffer
+        host = PinnedHostBuffer(off).tensor                  # page-locked when the host allows it (copies then overlap with compute)
         for w, (o, n, stride) in zip(mats, spans):
             host[o:o + n * stride].copy_(w.data.reshape(-1))
         qkv_rows = (L.q.n, L.k.n, L.v.n) if L.qkv is not None else None

@@ -302,10 +302,11 @@ def attn_prefill_supported(head_dim: int) -> bool:
 
 def attn_prefill(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor, n_tokens: int,
                  pos0: int, n_heads: int, n_kv_heads: int, head_dim: int, q_off: int = 0, window: int = 0,
-                 pos0_dev: Optional[torch.Tensor] = None) -> None:
+                 pos0_dev: Optional[torch.Tensor] = None, impl: Optional[str] = None) -> None:
     """Causal attention of chunk rows ``pos0 .. pos0+n_tokens-1`` of one sequence over its paged cache
     (tensor-core kernel; the chunk's own K/V rows must already be in the cache).  With ``pos0_dev`` (an int32 device
-    tensor) the position of row 0 is read on the device, so a captured launch serves every chunk position."""
+    tensor) the position of row 0 is read on the device, so a captured launch serves every chunk position.
+    ``impl``: "tc" (128-query tiles on tcgen05) or "mma" (16-query tiles on mma.sync); None = the launcher's choice."""
     p = S.AttnPrefillParams()
     p.qkv, p.out, p.k_cache, p.v_cache, p.page_table = qkv.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), page_table.data_ptr()
     p.ld_qkv, p.ld_out = qkv.stride(0), out.stride(0)
@@ -314,7 +315,7 @@ def attn_prefill(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_
     p.kv_q8 = 1 if k_cache.dtype in (torch.uint8, torch.int8) else 0
     p.out_bf16 = 1 if out.dtype == torch.bfloat16 else 0          # bf16: written as the operand of the output-projection GEMM
     p.pos0_ptr = ptr(pos0_dev)
-    check(lib().rlz_attn_prefill(ctypes.byref(p), stream_ptr()), "attn_prefill")
+    check(lib().rlz_attn_prefill_impl(ctypes.byref(p), stream_ptr(), {None: -1, "tc": 0, "mma": 1}[impl]), "attn_prefill")
 
 
 def attn_prefill_error(clear: bool = True) -> int:

@@ -164,6 +164,7 @@ def declare(lib: ctypes.CDLL) -> None:
     lib.rlz_norm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_float, c_void_p]
     lib.rlz_swiglu_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_longlong, c_longlong, c_int, c_void_p]
     lib.rlz_attn_prefill.argtypes = [POINTER(AttnPrefillParams), c_void_p]
+    lib.rlz_attn_prefill_impl.argtypes = [POINTER(AttnPrefillParams), c_void_p, c_int]
     lib.rlz_attn_prefill_supported.argtypes = [c_int]
     lib.rlz_attn_prefill_error.argtypes = [c_int]
     lib.rlz_ll_reduce.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p]

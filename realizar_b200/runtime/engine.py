@@ -19,6 +19,7 @@ import os
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from .. import ops
@@ -184,14 +185,18 @@ class DecodeEngine:
         self._plans: Dict[int, DecodePlan] = {}
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self._gen = torch.Generator(device=dev).manual_seed(c.seed)
-        # pinned staging for the streaming loop
-        self._h_tok_pos = torch.zeros(2, B, dtype=torch.int32).pin_memory()
+        # pinned staging for the streaming loop (page-locked where the host allows it, pageable otherwise) and a pool for the
+        # large transient device buffers of scoring passes
+        from .memory import GpuMemoryPool, PinnedHostBuffer
+        self.pool = GpuMemoryPool(dev, max_pooled_bytes=1 << 30)
+        pinned = lambda *shape: PinnedHostBuffer(4 * int(np.prod(shape))).view(torch.int32, int(np.prod(shape))).zero_().view(*shape)
+        self._h_tok_pos = pinned(2, B)
         self._h_tok_pos[1].fill_(-1)
         self._h_tokens, self._h_positions = self._h_tok_pos[0], self._h_tok_pos[1]
         self._d_tok_pos = tok_pos
         self._np_tokens, self._np_positions = self._h_tokens.numpy(), self._h_positions.numpy()     # cheap scalar writes
-        self._h_sampled = torch.zeros(B, dtype=torch.int32).pin_memory()
-        self._h_table = torch.zeros(B, self.max_pages_per_seq, dtype=torch.int32).pin_memory()
+        self._h_sampled = pinned(B)
+        self._h_table = pinned(B, self.max_pages_per_seq)
         self._next_seq = 0
         self.pdl = c.pdl
         ops.set_pdl(self.pdl)
@@ -663,8 +668,8 @@ class DecodeEngine:
         norm_t = ops.NORM_LAYER if cfg.uses_layernorm else ops.NORM_RMS
         tp = m.tp_size > 1
         vloc = m.vocab_local if tp else cfg.vocab_size
-        if getattr(self, "_score_logits", None) is None:
-            self._score_logits = torch.empty(bf.T, vloc, device=self.device, dtype=torch.float32)
+        raw_logits = self.pool.acquire(bf.T * vloc * 4)      # chunk rows x vocabulary slice, fp32: back to the pool when the pass ends
+        self._score_logits = raw_logits[: bf.T * vloc * 4].view(torch.float32).view(bf.T, vloc)
         toks = torch.as_tensor(list(tokens), dtype=torch.int32)
         lps: List[float] = []
         tops: List[list] = []
@@ -706,6 +711,8 @@ class DecodeEngine:
             self.check_health()
         finally:
             self.close_slot(slot)
+            self._score_logits = None
+            self.pool.release(raw_logits)
         out = {"logprobs": lps, "num_tokens": n}
         if lps:
             nll = -sum(lps) / len(lps)
@@ -808,4 +815,6 @@ class DecodeEngine:
 
     def memory_report(self) -> dict:
         return {"weights_bytes": self.model.weight_bytes(), "kv_bytes": self.kv.numel() * self.kv.element_size(), "kv_pages": self.num_pages,
-                "kv_utilization": self.pages.stats().utilization, "device": self.profile.describe()}
+                "kv_utilization": self.pages.stats().utilization, "device": self.profile.describe(),
+                "pool": {"hits": self.pool.stats.hits, "misses": self.pool.stats.misses, "bytes_pooled": self.pool.stats.bytes_pooled},
+                "streamed_layers": len(self.model.layers) - self.model.streamed_from}

@@ -164,7 +164,10 @@ def check_vram_sufficient(weight_bytes: int, kv_bytes: int, free_bytes: int, num
 class LayerStreamer:
     """Double-buffered prefetch: while layer ``i`` computes from one buffer, layer ``i+1`` is copied
     into the other on a side stream.  ``copy(layer, buffer_index)`` and ``compute(layer, buffer_index)``
-    are supplied by the caller; with CUDA the copies run on their own stream and events order them."""
+    are supplied by the caller; with CUDA the copies run on their own stream and events order them.
+    Stand-alone form of the schedule for callers that own their layers (``examples/stream_layers.py``); the engine's launch
+    plans are built ahead of time, so ``models.decoder.GpuModel`` applies the same schedule through ``acquire_layer`` /
+    ``release_layer`` hooks inside the plan."""
 
     def __init__(self, num_layers: int, copy: Callable[[int, int], None], compute: Callable[[int, int], None], use_cuda: Optional[bool] = None):
         self.n, self.copy, self.compute = num_layers, copy, compute

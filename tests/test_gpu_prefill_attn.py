@@ -23,9 +23,10 @@ def _reference(q, k, v, pos0, window):
     return (torch.softmax(s, -1) @ vh).permute(1, 0, 2)
 
 
+@pytest.mark.parametrize("impl", ["tc", "mma"])            # both kernels at every head size, whatever the launcher would pick
 @pytest.mark.parametrize("d,H,Hkv", [(64, 8, 2), (80, 4, 4), (128, 8, 1), (96, 2, 2)])
 @pytest.mark.parametrize("T,pos0,window", [(40, 0, 0), (128, 0, 0), (300, 37, 0), (200, 150, 64)])
-def test_flash_prefill_matches_reference(cuda_device, d, H, Hkv, T, pos0, window):
+def test_flash_prefill_matches_reference(cuda_device, d, H, Hkv, T, pos0, window, impl):
     from realizar_b200 import ops
     assert ops.attn_prefill_supported(d)
     dev = cuda_device
@@ -46,7 +47,7 @@ def test_flash_prefill_matches_reference(cuda_device, d, H, Hkv, T, pos0, window
     qkv = torch.zeros(T, ld)
     qkv[:, 8:8 + H * d] = q.reshape(T, -1)
     out = torch.full((T, H * d + 4), float("nan"), device=dev)
-    ops.attn_prefill(qkv.to(dev), out, kc.to(dev), vc.to(dev), perm.to(dev), T, pos0, H, Hkv, d, q_off=8, window=window)
+    ops.attn_prefill(qkv.to(dev), out, kc.to(dev), vc.to(dev), perm.to(dev), T, pos0, H, Hkv, d, q_off=8, window=window, impl=impl)
     torch.cuda.synchronize()
     assert ops.attn_prefill_error() == 0
     # the kernel sees bf16 q / k / v: give the reference the same rounded inputs
