@@ -297,10 +297,21 @@ def bench_step_trace(a):
     from ..models.weights import synthetic_weights
     from ..runtime.engine import DecodeEngine, EngineConfig
     cfg = named_config(a.model)
-    dev = torch.device("cuda")
-    eng = DecodeEngine(synthetic_weights(cfg, scheme="Q4_K_M", seed=0, device=dev), EngineConfig(max_batch=1, max_seq_len=a.ctx + 64, greedy_only=True), device=dev)
+    # under torch.distributed.run the step is the tensor-parallel one: the epilogue of the row-parallel launches then holds
+    # the in-kernel all-reduce (push to every peer, poll the own inbox), and the trace shows what it costs
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    comm = None
+    if world > 1:
+        import torch.distributed as dist
+        from ..parallel.tp import make_tp_comm
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+        comm = make_tp_comm(rank, world, torch.device("cuda", torch.cuda.current_device()), mode="fused")
+    dev = torch.device("cuda", torch.cuda.current_device())
+    eng = DecodeEngine(synthetic_weights(cfg, scheme="Q4_K_M", seed=0, device=dev), EngineConfig(max_batch=1, max_seq_len=a.ctx + 64, greedy_only=True),
+                       device=dev, comm=comm, tp_rank=rank, tp_size=world)
     eng.open_slot(0, a.ctx + 32)
-    eng.prefill(0, [int(t) for t in torch.randint(0, cfg.vocab_size, (a.ctx,))])
+    eng.prefill(0, [int(t) for t in torch.randint(0, cfg.vocab_size, (a.ctx,), generator=torch.Generator().manual_seed(0))])   # same prompt on every rank
     plan = eng.plan(1)
     gemvs = [r[1] for r in plan.records if r and r[0] == "gemv"]
     per_layer = (len(gemvs) - 1) // cfg.num_layers
@@ -329,9 +340,20 @@ def bench_step_trace(a):
         t = t[t[:, 0] > 0]
         med = lambda i, j: round(float(np.median(t[:, j] - t[:, i])) / 1e3, 2)
         out["launches"][name] = {"ctas": len(t), "wait": med(0, 1), "stage": med(1, 2), "rows_warp0": med(2, 3), "epilogue": med(6, 7),
+                                 "epilogue_p90": round(float(np.percentile(t[:, 7] - t[:, 6], 90)) / 1e3, 2),
                                  "span": round(float(t[:, 7].max() - t[:, 0].min()) / 1e3, 2)}
     for p in gemvs:
         p._pad = 0
+    out["world"] = world
+    if world > 1:
+        import torch.distributed as dist
+        eng.close()
+        comm.close()
+        torch.cuda.synchronize()
+        dist.barrier()
+        dist.destroy_process_group()
+        if rank != 0:
+            return None
     return out
 
 
@@ -374,7 +396,8 @@ def main(argv=None):
         from .. import ops
         ops.set_pdl(True)
     res = {"gemv": bench_gemv, "attn": bench_attn, "gemm": bench_gemm, "prefill": bench_prefill, "small": bench_small, "step-trace": bench_step_trace}[a.cmd](a)
-    print(json.dumps(res))
+    if res is not None:
+        print(json.dumps(res))
     return 0
 
 
