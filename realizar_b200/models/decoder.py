@@ -625,7 +625,8 @@ def build_decode_plan(model: GpuModel, buf: StepBuffers, k_cache: torch.Tensor, 
     # batch 1, one GPU: the launch that produces the MLP activation also writes it as the int8 block that the down-projection
     # launch stages, so all of that launch's CTAs copy 1.9 bytes per value instead of reading 4 and quantising
     def handoff(L) -> bool:
-        return (batch == 1 and not tp and buf.act_q is not None and os.environ.get("RLZ_ACT_HANDOFF", "1") != "0" and _is_fast(L.down)
+        # (tensor parallel: only when this rank's activation slice starts on a block boundary of the down projection's shard)
+        return (batch == 1 and (not tp or L.down_in_off == 0) and buf.act_q is not None and os.environ.get("RLZ_ACT_HANDOFF", "1") != "0" and _is_fast(L.down)
                 and _is_fast(L.up) and (L.gate is None or _is_fast(L.gate)) and L.down.k % 128 == 0 and L.up.n == L.down.k
                 and buf.act_q.numel() >= ops.act_block_bytes(L.down.k))
     overlap_up = cfg.parallel_residual and len(chunks) == 1 and os.environ.get("RLZ_OVERLAP_UP", "0") == "1"   # measured slower than the single chain; opt-in

@@ -167,7 +167,7 @@ class DecodeEngine:
             attn_partial=part, attn_counters=ctr,
             local_val=z(B) if tp_size > 1 else None, local_idx=z(B, dt=torch.int32) if tp_size > 1 else None,
             logits_full=z(B, self.mcfg.vocab_size) if (tp_size > 1 and not c.greedy_only) else None,
-            act_q=z(ops.act_block_bytes((d_k + 127) // 128 * 128), dt=torch.uint8) if tp_size == 1 else None)
+            act_q=z(ops.act_block_bytes((d_k + 127) // 128 * 128), dt=torch.uint8))
         if not c.greedy_only:                              # sampling plans carry per-sequence logit controls
             b = self.buf
             b.history = torch.full((B, HISTORY_WINDOW), -1, device=dev, dtype=torch.int32)
