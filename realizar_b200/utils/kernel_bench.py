@@ -4,6 +4,7 @@
     python -m realizar_b200.utils.kernel_bench attn --heads 32 --kv-heads 32 --head-dim 80 --ctx 4096 --batch 8
     python -m realizar_b200.utils.kernel_bench gemm --qtype Q4_K --n 10240 --k 2560 --m 512
     python -m realizar_b200.utils.kernel_bench step-trace --model phi-2 --ctx 600
+    python -m realizar_b200.utils.kernel_bench step-profile --model phi-2 --ctx 600
 
 Each kernel is timed with CUDA events after warm-up.  Working sets are larger than the 126 MB
 L2 (or rotated over several copies) so the numbers are DRAM numbers.  The achieved rate is
@@ -357,6 +358,33 @@ def bench_step_trace(a):
     return out
 
 
+def bench_step_profile(a):
+    """Per-launch CUDA-event times of the decode step of a named model shape, launch by launch without a graph (so without the
+    overlap that programmatic dependent launch gives the captured step), plus the same step replayed from its graph, and the
+    roofline budgets of the weight-streaming and attention launches."""
+    from ..models.config import named_config
+    from ..models.weights import synthetic_weights
+    from ..runtime.engine import DecodeEngine, EngineConfig
+    cfg = named_config(a.model)
+    dev = torch.device("cuda")
+    eng = DecodeEngine(synthetic_weights(cfg, scheme="Q4_K_M", seed=0, device=dev), EngineConfig(max_batch=max(a.batch, a.max_batch), max_seq_len=a.ctx + 192, greedy_only=True), device=dev)
+    g = torch.Generator().manual_seed(0)
+    for slot in range(a.batch):
+        eng.open_slot(slot, a.ctx + 160)
+        eng.prefill(slot, [int(t) for t in torch.randint(0, cfg.vocab_size, (a.ctx,), generator=g)])
+    eng.buf.positions[:a.batch].fill_(a.ctx)
+    rep = eng.brick_report(a.batch, steps=8)
+    prof = eng.profile_step(a.batch, steps=8)
+    for _ in range(3):
+        eng.run_step(a.batch)
+    eng.buf.positions[:a.batch].fill_(a.ctx)               # (rows whose position is -1 are idle: attention would skip them)
+    ms = time_cuda(lambda: eng.run_step(a.batch), 20)
+    return {"kernel": "decode step profile", "model": a.model, "batch": a.batch, "context": a.ctx, "graph_replay_us": round(1e3 * ms, 1),
+            "eager_sum_us": round(rep["step_us"], 1), "launches": {k: {"per_step": v["count"] // 8, "avg_us": round(v["avg_us"], 2), "share": round(v["share"], 3)} for k, v in prof.items()},
+            "budgets": {k: {"budget_us": round(v["budget_us"], 1), "gbs": None if v["gbs"] is None else round(v["gbs"], 1)} for k, v in rep["bricks"].items()},
+            "bottleneck": rep["bottleneck"]}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--reps", type=int, default=1, help="back-to-back launches per timed region")
@@ -389,13 +417,16 @@ def main(argv=None):
     m.add_argument("--wide", type=int, default=0, help="0 auto, 1 force 128-row CTAs, 2 force 256-row CTAs (m > 128)")
     st = sub.add_parser("step-trace")
     st.add_argument("--model", default="phi-2"); st.add_argument("--ctx", type=int, default=600); st.add_argument("--layer", type=int, default=20)
+    sp = sub.add_parser("step-profile")
+    sp.add_argument("--model", default="phi-2"); sp.add_argument("--ctx", type=int, default=600); sp.add_argument("--batch", type=int, default=1)
+    sp.add_argument("--max-batch", type=int, default=1, help="slots the engine is built for (buffer sizes)")
     a = ap.parse_args(argv)
     global REPS, GRAPH
     REPS, GRAPH = max(1, a.reps), a.graph
     if a.pdl:
         from .. import ops
         ops.set_pdl(True)
-    res = {"gemv": bench_gemv, "attn": bench_attn, "gemm": bench_gemm, "prefill": bench_prefill, "small": bench_small, "step-trace": bench_step_trace}[a.cmd](a)
+    res = {"gemv": bench_gemv, "attn": bench_attn, "gemm": bench_gemm, "prefill": bench_prefill, "small": bench_small, "step-trace": bench_step_trace, "step-profile": bench_step_profile}[a.cmd](a)
     if res is not None:
         print(json.dumps(res))
     return 0
