@@ -47,12 +47,17 @@ def nvcc_path() -> str | None:
     return None
 
 
-def build_cpu(verbose: bool = False) -> Path:
+def build_cpu(verbose: bool = False, sanitize: str | None = None) -> Path:
+    """``sanitize``: "address" (AddressSanitizer + UndefinedBehaviorSanitizer) or "thread" builds a second library,
+    ``librlz_cpu_asan.so`` / ``librlz_cpu_tsan.so``, that a process loads instead of the regular one through ``RLZ_CPU_LIB``
+    (with the sanitizer runtime preloaded: ``LD_PRELOAD=$(gcc -print-file-name=libasan.so)``)."""
     LIB.mkdir(exist_ok=True)
-    out = LIB / "librlz_cpu.so"
+    out = LIB / {None: "librlz_cpu.so", "address": "librlz_cpu_asan.so", "thread": "librlz_cpu_tsan.so"}[sanitize]
     srcs = [CSRC / s for s in CPU_SOURCES if (CSRC / s).exists()]
     if _newer(srcs + _headers(), out):
-        cmd = ["g++", "-O3", "-std=c++17", "-shared", "-fPIC", "-pthread", "-fno-math-errno",
+        flags = ["-O3"] if sanitize is None else ["-O1", "-g", "-fno-omit-frame-pointer",
+                                                   "-fsanitize=address,undefined" if sanitize == "address" else "-fsanitize=thread"]
+        cmd = ["g++", *flags, "-std=c++17", "-shared", "-fPIC", "-pthread", "-fno-math-errno",
                "-o", str(out)] + [str(s) for s in srcs]
         if verbose:
             print(" ".join(cmd))

@@ -20,7 +20,9 @@ def cpu_lib() -> ctypes.CDLL:
     with _lock:
         if _cpu is None:
             path = _build.LIB / "librlz_cpu.so"
-            if not path.exists() or os.environ.get("RLZ_REBUILD"):
+            if os.environ.get("RLZ_CPU_LIB"):                # another flavour of the library (sanitizer builds)
+                path = _build.Path(os.environ["RLZ_CPU_LIB"])
+            elif not path.exists() or os.environ.get("RLZ_REBUILD"):
                 path = _build.build_cpu()
             lib = ctypes.CDLL(str(path))
             lib.rlz_block_elems.argtypes = [c_int]

@@ -27,6 +27,7 @@ from ..models.batched import BatchedForward, gemm_capable
 from ..models.decoder import DecodePlan, GpuModel, StepBuffers, build_decode_plan, emit_head, emit_select
 from ..ops import gemm as G
 from ..models.weights import ModelWeights
+from ..utils.trace import nvtx_range
 from .paged_kv import PagedKvCache
 
 log = logging.getLogger("realizar_b200.engine")
@@ -311,13 +312,14 @@ class DecodeEngine:
             if self.steps_run % 256 == 0:
                 plan.program.check()
             return
-        if self.cfg.cuda_graphs:
-            g = self._graphs.get(bucket)
-            if g is None:
-                g = self._graphs[bucket] = self._capture(bucket)
-            g.replay()
-        else:
-            self.plan(bucket).run()
+        with nvtx_range("decode step"):                     # (a no-op unless RLZ_NVTX=1)
+            if self.cfg.cuda_graphs:
+                g = self._graphs.get(bucket)
+                if g is None:
+                    g = self._graphs[bucket] = self._capture(bucket)
+                g.replay()
+            else:
+                self.plan(bucket).run()
         self.steps_run += 1
         if self.steps_run % self.health_check_every == 0:
             self.check_health()

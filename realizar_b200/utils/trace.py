@@ -10,6 +10,7 @@ Reference parity: ``InferenceTracer`` (src/inference_trace/mod.rs:30-448), ``Bri
 from __future__ import annotations
 
 import json
+import os
 import time
 from contextlib import contextmanager
 from dataclasses import asdict, dataclass, field
@@ -113,9 +114,27 @@ def first_divergence(diffs: List[TraceDiff]) -> Optional[TraceDiff]:
     return next((d for d in diffs if not d.ok), None)
 
 
+@contextmanager
+def nvtx_range(name: str):
+    """An NVTX range around a piece of host code that launches GPU work, when ``RLZ_NVTX=1`` and a CUDA device is present
+    (timeline tools group the launches under it); otherwise nothing."""
+    on = os.environ.get("RLZ_NVTX", "0") != "0"
+    if on:
+        import torch
+        on = torch.cuda.is_available()
+    if on:
+        torch.cuda.nvtx.range_push(name)
+    try:
+        yield
+    finally:
+        if on:
+            torch.cuda.nvtx.range_pop()
+
+
 class BrickProfiler:
     """Accumulates per-brick timings.  On a CUDA device the bricks are bracketed with events on the
-    current stream and resolved at ``summary()`` (no synchronisation inside the hot loop)."""
+    current stream and resolved at ``summary()`` (no synchronisation inside the hot loop); with ``RLZ_NVTX=1`` every brick is
+    also an NVTX range."""
 
     def __init__(self, cuda: Optional[bool] = None):
         import torch
@@ -130,7 +149,8 @@ class BrickProfiler:
             import torch
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            yield
+            with nvtx_range(name):
+                yield
             e1.record()
             self._pending.append((name, e0, e1))
         else:
