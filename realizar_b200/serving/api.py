@@ -134,6 +134,7 @@ class AppState:
     vocab_strings: Optional[List[str]] = None       # text of every token id, built on the first grammar-constrained request
     context_length: int = 4096
     classical: Any = None               # optional ClassicalServeState behind /v1/predict, /v1/explain
+    fanouts: Dict[Any, Any] = field(default_factory=dict)             # event loop -> TokenFanout (engine thread -> stream queues)
     route_latency: Dict[str, Any] = field(default_factory=dict)      # path -> LatencyHistogram of whole HTTP requests
     spans: Any = field(default_factory=lambda: deque(maxlen=256))    # finished request spans, newest last (GET /v1/traces)
 
@@ -145,6 +146,34 @@ class AppState:
         from .tokenizer import ByteTokenizer
         serving = ServingEngine(FakeEngine(vocab=256)).start()
         return cls(serving, ByteTokenizer(256), RawTemplate(), "demo", None, compute_mode="cpu", scorer=EngineScorer(serving))
+
+
+class TokenFanout:
+    """Delivery of engine-thread events (tokens, request ends) to the per-stream asyncio queues with ONE event-loop wake-up per
+    burst instead of one per token: the engine thread appends to a list and schedules a drain only when none is pending, the
+    drain (on the loop thread) moves everything posted so far into the queues.  At 256 streams a decode step posts 256 tokens;
+    256 ``call_soon_threadsafe`` calls mean 256 writes to the loop's wake-up pipe and as many lock hand-overs."""
+
+    def __init__(self, loop: "asyncio.AbstractEventLoop"):
+        self.loop = loop
+        self._items: List[tuple] = []
+        self._lock = threading.Lock()
+        self._scheduled = False
+
+    def post(self, q: "asyncio.Queue", item) -> None:
+        with self._lock:
+            self._items.append((q, item))
+            if self._scheduled:
+                return
+            self._scheduled = True
+        self.loop.call_soon_threadsafe(self._drain)
+
+    def _drain(self) -> None:
+        with self._lock:
+            items, self._items = self._items, []
+            self._scheduled = False
+        for q, item in items:
+            q.put_nowait(item)
 
 
 def _finish_reason(r: Request) -> str:
@@ -313,11 +342,14 @@ def create_app(state: AppState) -> FastAPI:
         """Server-sent events fed by the engine thread through an asyncio queue."""
         async def gen():
             loop = asyncio.get_running_loop()
+            fan = state.fanouts.get(loop)
+            if fan is None:
+                fan = state.fanouts[loop] = TokenFanout(loop)
             q: asyncio.Queue = asyncio.Queue()
             dec = StreamDecoder(state.tokenizer)
             stops = set(stop_ids())
-            r = submit(*r_holder["args"], on_token=lambda t: loop.call_soon_threadsafe(q.put_nowait, ("tok", t)),
-                       on_finish=lambda rq: loop.call_soon_threadsafe(q.put_nowait, ("end", rq)), extra=r_holder.get("extra"))
+            r = submit(*r_holder["args"], on_token=lambda t: fan.post(q, ("tok", t)),
+                       on_finish=lambda rq: fan.post(q, ("end", rq)), extra=r_holder.get("extra"))
             stop_strs = r_holder.get("stops") or []
             held = ""                                        # text not yet sent: a stop string may still be forming at its end
             if first_chunk is not None:
@@ -330,9 +362,19 @@ def create_app(state: AppState) -> FastAPI:
                         yield ": keep-alive\n\n"
                         continue
                     if kind == "tok":
-                        if val in stops:
-                            continue
-                        text = dec.push(val)
+                        # tokens that piled up while this stream waited for the loop go out as ONE event: under load the
+                        # per-event cost (JSON, HTTP framing, a socket write) is what limits the server, not the tokens
+                        text, pending_end = ("" if val in stops else dec.push(val)), None
+                        while not q.empty():
+                            k2, v2 = q.get_nowait()
+                            if k2 != "tok":
+                                pending_end = (k2, v2)
+                                break
+                            if v2 not in stops:
+                                text += dec.push(v2)
+                                val = v2
+                        if pending_end is not None:
+                            q.put_nowait(pending_end)          # (nothing can follow a request's end: order is kept)
                         if text and stop_strs:
                             held += text
                             cut = min((held.find(s_) for s_ in stop_strs if s_ in held), default=-1)
