@@ -297,8 +297,7 @@ def run_bench_suite(suite: str, model: str = "tiny-llama") -> list:
         m = CpuModel(synthetic_weights(cfg, scheme="Q4_K_M", seed=0), 300)
         prompt = [int(x) for x in np.random.default_rng(0).integers(0, cfg.vocab_size, 128)]
         t0 = time.perf_counter()
-        for i, tok in enumerate(prompt):
-            lg = m.forward(tok, i)
+        lg = m.prefill(prompt)                               # chunks of 32 tokens: one batched product per projection and chunk
         t1 = time.perf_counter()
         tok = int(np.argmax(lg))
         for i in range(128):

@@ -208,6 +208,120 @@ int forward(Model& m, int token, int pos, float* logits_out) {
   return 0;
 }
 
+// ---- prompt chunks: T consecutive tokens of one sequence in one pass --------------------------------------------------------
+// Every projection runs as ONE batched matrix-vector product (each weight row is read once and multiplied with the T quantised
+// activation rows), attention runs per (token, head) over the cache up to the token's own position, and only the last token
+// goes through the output matrix.  Row by row the arithmetic is the same as in forward(), so the logits of the last token are
+// bit-identical to a token-by-token prompt.  (Role of the reference's batched CPU prefill: append_kv / advance_by,
+// src/gguf/runtime.rs:123-298.)
+struct ChunkCtx { Model* m; int layer, pos0, T; const float* q; float* att; float* scores; };
+
+void attn_chunk(int64_t j0, int64_t j1, void* vp) {
+  ChunkCtx* a = (ChunkCtx*)vp; Model& m = *a->m; const Config& c = m.cfg;
+  const int kv_dim = c.n_kv_heads * c.head_dim, group = c.n_heads / c.n_kv_heads, qd = c.n_heads * c.head_dim;
+  const float scale = 1.f / sqrtf((float)c.head_dim);
+  const float* kc = m.kcache.data() + (size_t)a->layer * c.max_seq * kv_dim;
+  const float* vc = m.vcache.data() + (size_t)a->layer * c.max_seq * kv_dim;
+  for (int64_t j = j0; j < j1; ++j) {                      // job = (token, head)
+    const int t = (int)(j / c.n_heads), h = (int)(j % c.n_heads), len = a->pos0 + t + 1, kvh = h / group;
+    const float* qh = a->q + (size_t)t * qd + (size_t)h * c.head_dim;
+    float* sc = a->scores + (size_t)j * c.max_seq; float mx = -INFINITY;
+    for (int u = 0; u < len; ++u) {
+      const float* kr = kc + (size_t)u * kv_dim + kvh * c.head_dim; float s = 0;
+      for (int i = 0; i < c.head_dim; ++i) s += qh[i] * kr[i];
+      sc[u] = s * scale; mx = std::max(mx, sc[u]);
+    }
+    float sum = 0; for (int u = 0; u < len; ++u) { sc[u] = expf(sc[u] - mx); sum += sc[u]; }
+    float* o = a->att + (size_t)t * qd + (size_t)h * c.head_dim; for (int i = 0; i < c.head_dim; ++i) o[i] = 0;
+    for (int u = 0; u < len; ++u) {
+      const float* vr = vc + (size_t)u * kv_dim + kvh * c.head_dim; const float p = sc[u] / sum;
+      for (int i = 0; i < c.head_dim; ++i) o[i] += p * vr[i];
+    }
+  }
+}
+
+void linear_rows(const Tensor& w, const Tensor& b, const float* x, float* y, int T, std::vector<float>& bbuf) {
+  rlz_matvec(w.qtype, w.data, x, y, w.n, w.k, T);
+  if (b.ok()) {
+    if ((int64_t)bbuf.size() != w.n) vec_from(b, bbuf);
+    for (int t = 0; t < T; ++t) for (int64_t i = 0; i < w.n; ++i) y[(size_t)t * w.n + i] += bbuf[i];
+  }
+}
+
+int forward_chunk(Model& m, const int* tokens, int T, int pos0, float* logits_out) {
+  const Config& c = m.cfg; Runtime& rt = g_rt[&m];
+  if (T < 1 || pos0 < 0 || pos0 + T > c.max_seq) return -1;
+  const int H = c.hidden, qd = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim, I = c.intermediate;
+  std::vector<float> x((size_t)T * H), h((size_t)T * H), q((size_t)T * qd), k((size_t)T * kvd), v((size_t)T * kvd), qkv, att((size_t)T * qd),
+      tmp((size_t)T * H), up((size_t)T * I), gate, act((size_t)T * I), ffn((size_t)T * H), scores((size_t)T * c.n_heads * c.max_seq), row(H);
+  for (int t = 0; t < T; ++t) {
+    if (tokens[t] < 0 || tokens[t] >= c.vocab) return -1;
+    const int64_t rb = rlz_row_bytes(m.tok_embd.qtype, H); if (rb < 0) return -2;
+    rlz_dequantize(m.tok_embd.qtype, m.tok_embd.data + (int64_t)tokens[t] * rb, x.data() + (size_t)t * H, H);
+    if (m.pos_embd.ok()) {
+      const int64_t pb = rlz_row_bytes(m.pos_embd.qtype, H);
+      rlz_dequantize(m.pos_embd.qtype, m.pos_embd.data + (int64_t)(pos0 + t) * pb, row.data(), H);
+      for (int i = 0; i < H; ++i) x[(size_t)t * H + i] += row[i];
+    }
+  }
+  if (c.gated_ffn) gate.resize((size_t)T * I);
+  m.trace.assign(c.n_layers, 0.f);
+  for (int l = 0; l < c.n_layers; ++l) {
+    Layer& L = m.layers[l];
+    for (int t = 0; t < T; ++t) norm(c, x.data() + (size_t)t * H, h.data() + (size_t)t * H, H, L.attn_norm_w, L.attn_norm_b, rt.attn_nc[l].w, rt.attn_nc[l].b);
+    if (L.qkv_w.ok()) {
+      qkv.resize((size_t)T * (qd + 2 * kvd));
+      linear_rows(L.qkv_w, L.qkv_b, h.data(), qkv.data(), T, rt.qkv_b[l]);
+      for (int t = 0; t < T; ++t) {
+        const float* r = qkv.data() + (size_t)t * (qd + 2 * kvd);
+        std::copy(r, r + qd, q.begin() + (size_t)t * qd);
+        std::copy(r + qd, r + qd + kvd, k.begin() + (size_t)t * kvd);
+        std::copy(r + qd + kvd, r + qd + 2 * kvd, v.begin() + (size_t)t * kvd);
+      }
+    } else {
+      linear_rows(L.q_w, L.q_b, h.data(), q.data(), T, rt.q_b[l]);
+      linear_rows(L.k_w, L.k_b, h.data(), k.data(), T, rt.k_b[l]);
+      linear_rows(L.v_w, L.v_b, h.data(), v.data(), T, rt.v_b[l]);
+    }
+    if (L.q_norm_w.ok() && rt.qn[l].empty()) vec_from(L.q_norm_w, rt.qn[l]);
+    if (L.k_norm_w.ok() && rt.kn[l].empty()) vec_from(L.k_norm_w, rt.kn[l]);
+    for (int t = 0; t < T; ++t) {
+      float* qt = q.data() + (size_t)t * qd; float* kt = k.data() + (size_t)t * kvd;
+      if (L.q_norm_w.ok()) head_rmsnorm(c, qt, c.n_heads, rt.qn[l]);
+      if (L.k_norm_w.ok()) head_rmsnorm(c, kt, c.n_kv_heads, rt.kn[l]);
+      rope(c, qt, c.n_heads, pos0 + t); rope(c, kt, c.n_kv_heads, pos0 + t);
+      std::copy(kt, kt + kvd, m.kcache.begin() + ((size_t)l * c.max_seq + pos0 + t) * kvd);
+      std::copy(v.begin() + (size_t)t * kvd, v.begin() + (size_t)(t + 1) * kvd, m.vcache.begin() + ((size_t)l * c.max_seq + pos0 + t) * kvd);
+    }
+    ChunkCtx actx{&m, l, pos0, T, q.data(), att.data(), scores.data()};
+    rlz_parallel_for((int64_t)T * c.n_heads, 1, attn_chunk, &actx);
+    linear_rows(L.o_w, L.o_b, att.data(), tmp.data(), T, rt.o_b[l]);
+    if (!c.parallel_residual) {
+      for (size_t i = 0; i < (size_t)T * H; ++i) x[i] += tmp[i];
+      for (int t = 0; t < T; ++t) norm(c, x.data() + (size_t)t * H, h.data() + (size_t)t * H, H, L.ffn_norm_w, L.ffn_norm_b, rt.ffn_nc[l].w, rt.ffn_nc[l].b);
+    }
+    if (c.gated_ffn) {
+      linear_rows(L.gate_w, L.gate_b, h.data(), gate.data(), T, rt.gate_b[l]);
+      linear_rows(L.up_w, L.up_b, h.data(), up.data(), T, rt.up_b[l]);
+      for (size_t i = 0; i < (size_t)T * I; ++i) act[i] = silu(gate[i]) * up[i];
+    } else {
+      linear_rows(L.up_w, L.up_b, h.data(), up.data(), T, rt.up_b[l]);
+      for (size_t i = 0; i < (size_t)T * I; ++i) act[i] = gelu_tanh(up[i]);
+    }
+    linear_rows(L.down_w, L.down_b, act.data(), ffn.data(), T, rt.down_b[l]);
+    if (c.parallel_residual) for (size_t i = 0; i < (size_t)T * H; ++i) x[i] += tmp[i] + ffn[i];
+    else for (size_t i = 0; i < (size_t)T * H; ++i) x[i] += ffn[i];
+    double ss = 0; const float* last = x.data() + (size_t)(T - 1) * H; for (int i = 0; i < H; ++i) ss += (double)last[i] * last[i];
+    m.trace[l] = (float)sqrt(ss);
+  }
+  // only the last token needs logits
+  std::copy(x.begin() + (size_t)(T - 1) * H, x.end(), m.x.begin());
+  norm(c, m.x.data(), m.h.data(), H, m.out_norm_w, m.out_norm_b, rt.out_nc.w, rt.out_nc.b);
+  linear(m.out_w, m.out_b, m.h.data(), m.logits.data(), rt.out_b);
+  if (logits_out) std::copy(m.logits.begin(), m.logits.end(), logits_out);
+  return 0;
+}
+
 }  // namespace
 
 extern "C" {
@@ -271,15 +385,29 @@ int rlz_cpu_model_validate(void* mp) {
 
 int rlz_cpu_forward(void* mp, int token, int pos, float* logits_out) { return forward(*(Model*)mp, token, pos, logits_out); }
 
+// Prompt tokens `tokens[0..n)` at positions pos0.. in chunks of up to `chunk` tokens (each projection one batched product per
+// chunk); `logits_out` receives the logits after the last token.
+int rlz_cpu_prefill(void* mp, const int* tokens, int n, int pos0, int chunk, float* logits_out) {
+  Model& m = *(Model*)mp;
+  if (n < 1) return -1;
+  if (chunk < 1) chunk = 32;
+  for (int i = 0; i < n; i += chunk) {
+    const int T = std::min(chunk, n - i);
+    const int rc = forward_chunk(m, tokens + i, T, pos0 + i, i + T >= n ? logits_out : nullptr);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
 int rlz_cpu_layer_trace(void* mp, float* out) { Model& m = *(Model*)mp; std::copy(m.trace.begin(), m.trace.end(), out); return (int)m.trace.size(); }
 
-// Greedy generation: token-by-token prefill then n_gen argmax decode steps.
+// Greedy generation: the prompt in chunks of 32 tokens, then n_gen argmax decode steps.
 // timings[0] = prefill seconds, timings[1] = decode seconds.  Returns tokens generated.
 int rlz_cpu_generate_greedy(void* mp, const int* prompt, int n_prompt, int n_gen, int eos, int* out, double* timings) {
   Model& m = *(Model*)mp; const Config& c = m.cfg;
   if (n_prompt <= 0 || n_prompt + n_gen > c.max_seq) return -1;
   auto t0 = std::chrono::steady_clock::now();
-  for (int i = 0; i < n_prompt; ++i) if (forward(m, prompt[i], i, nullptr)) return -2;
+  if (rlz_cpu_prefill(mp, prompt, n_prompt, 0, 32, nullptr)) return -2;
   auto t1 = std::chrono::steady_clock::now();
   int produced = 0;
   for (int g = 0; g < n_gen; ++g) {

@@ -637,9 +637,42 @@ float dot_q4k_q8k_vnni(const uint8_t* w, const Q8K* a, int nb) {
       summ += m0 * (a[i].bsums[4 * j] + a[i].bsums[4 * j + 1]) + m1 * (a[i].bsums[4 * j + 2] + a[i].bsums[4 * j + 3]);
       q += 32; q8 += 64;
     }
-    sumf += d * (float)_mm512_reduce_add_epi32(acc) - dmin * (float)summ;
+    sumf = fmaf(-dmin, (float)summ, fmaf(d, (float)_mm512_reduce_add_epi32(acc), sumf));      // (explicit: the x4 form must round alike)
   }
   return sumf;
+}
+// The same dot for FOUR activation rows against one weight row: the weight's nibbles are unpacked and its sub-block scales
+// broadcast once, then multiplied with each activation (prompt chunks: every weight row meets many activation rows).  Per row
+// the integer sums and the order of the float operations equal dot_q4k_q8k_vnni, so the results are bit-identical to it.
+__attribute__((target("avx512f,avx512bw,avx512vl,avx512vnni")))
+void dot_q4k_q8k_vnni_x4(const uint8_t* w, const Q8K* a, int64_t a_stride, int nb, float* out) {
+  const __m256i m4 = _mm256_set1_epi8(0xF);
+  float sumf[4] = {0, 0, 0, 0};
+  for (int i = 0; i < nb; ++i, w += 144) {
+    const float dw = half_bits_to_float(load_u16(w)), dminw = half_bits_to_float(load_u16(w + 2));
+    const uint8_t* q = w + 16;
+    __m512i acc[4] = {_mm512_setzero_si512(), _mm512_setzero_si512(), _mm512_setzero_si512(), _mm512_setzero_si512()};
+    int summ[4] = {0, 0, 0, 0};
+    for (int j = 0; j < 4; ++j) {
+      uint8_t sc0, m0, sc1, m1; get_scale_min_k4(2 * j, w + 4, &sc0, &m0); get_scale_min_k4(2 * j + 1, w + 4, &sc1, &m1);
+      const __m256i qb = _mm256_loadu_si256((const __m256i*)q);
+      const __m512i wv = _mm512_inserti64x4(_mm512_castsi256_si512(_mm256_and_si256(qb, m4)), _mm256_and_si256(_mm256_srli_epi16(qb, 4), m4), 1);
+      const __m512i scv = _mm512_inserti64x4(_mm512_castsi256_si512(_mm256_set1_epi32(sc0)), _mm256_set1_epi32(sc1), 1);
+      for (int b = 0; b < 4; ++b) {
+        const Q8K& ab = a[(int64_t)b * a_stride + i];
+        const __m512i p = _mm512_dpbusd_epi32(_mm512_setzero_si512(), wv, _mm512_loadu_si512((const void*)(ab.qs + 64 * j)));
+        acc[b] = _mm512_add_epi32(acc[b], _mm512_mullo_epi32(p, scv));
+        summ[b] += m0 * (ab.bsums[4 * j] + ab.bsums[4 * j + 1]) + m1 * (ab.bsums[4 * j + 2] + ab.bsums[4 * j + 3]);
+      }
+      q += 32;
+    }
+    for (int b = 0; b < 4; ++b) {
+      const float ad = a[(int64_t)b * a_stride + i].d;
+      const float d = dw * ad, dmin = dminw * ad;
+      sumf[b] = fmaf(-dmin, (float)summ[b], fmaf(d, (float)_mm512_reduce_add_epi32(acc[b]), sumf[b]));
+    }
+  }
+  for (int b = 0; b < 4; ++b) out[b] = sumf[b];
 }
 // Q6_K: per 128-weight half, four 32-byte operands; (q - 32) . a = q . a - 32 * sum(a), the sums come from the Q8_K block sums
 __attribute__((target("avx512f,avx512bw,avx512vl,avx512vnni")))
@@ -840,8 +873,17 @@ int rlz_matvec(int qtype, const void* W, const float* x, float* y, int64_t n, in
     pool().run([&](int) {
       for (;;) {
         int64_t r0 = next.fetch_add(32); if (r0 >= n) break;
-        for (int64_t r = r0; r < std::min(n, r0 + 32); ++r)
-          for (int64_t b = 0; b < batch; ++b) y[b * n + r] = dot_kquant(qtype, w + r * rb, act.data() + b * nb, nb);
+        for (int64_t r = r0; r < std::min(n, r0 + 32); ++r) {
+          int64_t b = 0;
+#if RLZ_X86
+          if (qtype == QT_Q4_K && has_vnni512())             // four activation rows per pass over the weight row
+            for (; b + 4 <= batch; b += 4) {
+              float o[4]; dot_q4k_q8k_vnni_x4(w + r * rb, act.data() + b * nb, nb, nb, o);
+              for (int t = 0; t < 4; ++t) y[(b + t) * n + r] = o[t];
+            }
+#endif
+          for (; b < batch; ++b) y[b * n + r] = dot_kquant(qtype, w + r * rb, act.data() + b * nb, nb);
+        }
       }
     });
     return 0;

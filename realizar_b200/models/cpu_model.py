@@ -60,10 +60,15 @@ class CpuModel:
         cpu_lib().rlz_cpu_layer_trace(self._h, out.ctypes.data_as(ctypes.c_void_p))
         return out
 
-    def prefill(self, tokens: Sequence[int]) -> np.ndarray:
-        logits = None
-        for i, t in enumerate(tokens):
-            logits = self.forward(t, i)
+    def prefill(self, tokens: Sequence[int], pos0: int = 0, chunk: int = 32) -> np.ndarray:
+        """Run prompt tokens at positions ``pos0 ..`` in chunks of ``chunk`` tokens (every projection one batched product per
+        chunk, the output matrix only for the last token); returns the logits after the last token.  ``chunk=1`` is the
+        token-by-token path; both give the same logits bit for bit."""
+        p = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32))
+        logits = np.empty(self.cfg.vocab_size, dtype=np.float32)
+        rc = cpu_lib().rlz_cpu_prefill(self._h, p.ctypes.data_as(ctypes.c_void_p), len(p), int(pos0), int(chunk), logits.ctypes.data_as(ctypes.c_void_p))
+        if rc:
+            raise ValueError(f"prefill failed (rc={rc}): {len(p)} tokens at position {pos0}, max_seq={self.max_seq}")
         return logits
 
     def generate_greedy(self, prompt: Sequence[int], n_gen: int, eos: Optional[int] = None):

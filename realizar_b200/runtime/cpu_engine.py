@@ -55,10 +55,8 @@ class CpuSlotEngine:
 
     def prefill(self, slot: int, tokens: Sequence[int]) -> int:
         m = self.models[slot]
-        logits = None
-        for t in tokens:
-            logits = m.forward(int(t), self.pos[slot])
-            self.pos[slot] += 1
+        logits = m.prefill([int(t) for t in tokens], pos0=self.pos[slot])     # chunks of 32 tokens per batched pass
+        self.pos[slot] += len(tokens)
         self.history[slot].extend(int(t) for t in tokens)
         return self._pick(slot, logits)
 
