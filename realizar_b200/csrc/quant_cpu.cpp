@@ -45,6 +45,7 @@ class Pool {
   // run fn(worker_index) on every worker (including the caller as worker 0)
   void run(const std::function<void(int)>& fn) {
     if (n_ == 1) { fn(0); return; }
+    std::lock_guard<std::mutex> one_caller(run_mu_);      // callers on different threads take turns (the hand-over state is single)
     {
       std::lock_guard<std::mutex> l(mu_);
       fn_ = &fn;
@@ -84,7 +85,7 @@ class Pool {
   }
   int n_;
   std::vector<std::thread> workers_;
-  std::mutex mu_;
+  std::mutex mu_, run_mu_;
   std::condition_variable cv_;
   const std::function<void(int)>* fn_ = nullptr;
   std::atomic<int> pending_{0}, sleepers_{0};

@@ -82,3 +82,23 @@ def test_host_library_under_address_and_ub_sanitizers():
     tail = (r.stdout + r.stderr)[-3000:]
     assert r.returncode == 0 and "SANITIZED-OK" in r.stdout, tail
     assert "ERROR: AddressSanitizer" not in r.stderr and "runtime error:" not in r.stderr, tail
+
+
+def test_thread_pool_under_thread_sanitizer(tmp_path):
+    """The host library's spin-then-sleep thread pool under ThreadSanitizer, driven by a small C++ program (no interpreter in
+    the process): three caller threads issue batched products and parallel loops at once; every result must equal the
+    single-caller one and the sanitizer must stay silent."""
+    if not _runtime("libtsan.so"):
+        pytest.skip("no ThreadSanitizer runtime with this compiler")
+    csrc = os.path.join(ROOT, "realizar_b200", "csrc")
+    exe = str(tmp_path / "pool_stress")
+    build = subprocess.run(["g++", "-O1", "-g", "-fsanitize=thread", "-std=c++17", "-pthread", "-fno-math-errno", "-I", csrc, "-o", exe,
+                            os.path.join(ROOT, "tests", "native", "pool_stress.cpp"), os.path.join(csrc, "quant_cpu.cpp")],
+                           capture_output=True, text=True, timeout=600)
+    if build.returncode != 0:
+        pytest.skip("the ThreadSanitizer build of the stress program does not link here: " + build.stderr[-300:])
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=600, env=dict(os.environ, TSAN_OPTIONS="halt_on_error=1 exitcode=66"))
+    if "FATAL: ThreadSanitizer" in r.stderr and "unexpected memory mapping" in r.stderr:
+        pytest.skip("ThreadSanitizer cannot map its shadow memory in this environment")
+    assert r.returncode == 0 and "POOL-STRESS OK" in r.stdout, (r.stdout + r.stderr)[-2000:]
+    assert "ThreadSanitizer" not in r.stderr, r.stderr[-2000:]
