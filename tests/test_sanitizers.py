@@ -55,6 +55,33 @@ EXERCISE = textwrap.dedent("""
         except Exception:
             rejected += 1
     assert rejected >= 8
+    # APR v2 container: build one (plain and LZ4-compressed), parse it back, then truncated and corrupted copies
+    from realizar_b200.formats import apr as A
+    for comp in (None, "lz4"):
+        bld = A.AprBuilder({"architecture": "llama", "hidden_size": 64, "vocab_size": 10}, compression=comp)
+        bld.add_tensor_raw("model.embed_tokens.weight", (10, 64), 0, rng.standard_normal((10, 64)).astype(np.float32))
+        bld.add_tensor_raw("model.norm.weight", (64,), 0, np.ones(64, np.float32))
+        ab = bld.build()
+        am = A.AprModel.from_bytes(ab)
+        assert am.tensor_data("model.norm.weight").size == 64 * 4
+        for cut in (0, 7, 31, 64, len(ab) // 2, len(ab) - 3):
+            try:
+                A.AprModel.from_bytes(ab[:cut])
+            except Exception:
+                rejected += 1
+        for _ in range(30):
+            b = bytearray(ab)
+            for i in rng.integers(0, len(b), 12):
+                b[i] = int(rng.integers(0, 256))
+            try:
+                m2 = A.AprModel.from_bytes(bytes(b))
+                for nm in ("model.embed_tokens.weight", "model.norm.weight"):
+                    try:
+                        m2.tensor_data(nm)
+                    except Exception:
+                        pass
+            except Exception:
+                rejected += 1
     print("SANITIZED-OK", rejected)
 """) % ROOT
 
