@@ -51,6 +51,7 @@ def cpu_lib() -> ctypes.CDLL:
             lib.rlz_cpu_model_set_tensor.argtypes = [c_void_p, c_char_p, c_int, c_void_p, c_int64, c_int64]
             lib.rlz_cpu_model_validate.argtypes = [c_void_p]
             lib.rlz_cpu_forward.argtypes = [c_void_p, c_int, c_int, c_void_p]
+            lib.rlz_cpu_forward_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
             lib.rlz_cpu_prefill.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
             lib.rlz_cpu_layer_trace.argtypes = [c_void_p, c_void_p]
             lib.rlz_cpu_generate_greedy.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]

@@ -322,6 +322,110 @@ int forward_chunk(Model& m, const int* tokens, int T, int pos0, float* logits_ou
   return 0;
 }
 
+// ---- one decode step for several sequences in lock-step --------------------------------------------------------------------
+// Row r is sequence `ms[r]` (its own KV cache) fed token `tokens[r]` at position `pos[r]`; all sequences share the weights of
+// ms[0] (the handles were bound to the same tensors).  Every projection, the output matrix included, is ONE batched product over
+// the R rows, so a step reads the weights once whatever the number of sequences; attention runs per (row, head) on the row's own
+// cache.  Row by row the arithmetic equals forward().
+struct RowsCtx { Model** ms; const int* pos; int layer, R; const float* q; float* att; float* scores; };
+
+void attn_rows(int64_t j0, int64_t j1, void* vp) {
+  RowsCtx* a = (RowsCtx*)vp; const Config& c = a->ms[0]->cfg;
+  const int kv_dim = c.n_kv_heads * c.head_dim, group = c.n_heads / c.n_kv_heads, qd = c.n_heads * c.head_dim;
+  const float scale = 1.f / sqrtf((float)c.head_dim);
+  for (int64_t j = j0; j < j1; ++j) {
+    const int r = (int)(j / c.n_heads), h = (int)(j % c.n_heads), len = a->pos[r] + 1, kvh = h / group;
+    Model& m = *a->ms[r];
+    const float* kc = m.kcache.data() + (size_t)a->layer * c.max_seq * kv_dim;
+    const float* vc = m.vcache.data() + (size_t)a->layer * c.max_seq * kv_dim;
+    const float* qh = a->q + (size_t)r * qd + (size_t)h * c.head_dim;
+    float* sc = a->scores + (size_t)j * c.max_seq; float mx = -INFINITY;
+    for (int u = 0; u < len; ++u) {
+      const float* kr = kc + (size_t)u * kv_dim + kvh * c.head_dim; float s = 0;
+      for (int i = 0; i < c.head_dim; ++i) s += qh[i] * kr[i];
+      sc[u] = s * scale; mx = std::max(mx, sc[u]);
+    }
+    float sum = 0; for (int u = 0; u < len; ++u) { sc[u] = expf(sc[u] - mx); sum += sc[u]; }
+    float* o = a->att + (size_t)r * qd + (size_t)h * c.head_dim; for (int i = 0; i < c.head_dim; ++i) o[i] = 0;
+    for (int u = 0; u < len; ++u) {
+      const float* vr = vc + (size_t)u * kv_dim + kvh * c.head_dim; const float p = sc[u] / sum;
+      for (int i = 0; i < c.head_dim; ++i) o[i] += p * vr[i];
+    }
+  }
+}
+
+int forward_rows(Model** ms, const int* tokens, const int* pos, int R, float* logits_out) {
+  Model& m = *ms[0]; const Config& c = m.cfg; Runtime& rt = g_rt[&m];
+  if (R < 1) return -1;
+  for (int r = 0; r < R; ++r) {
+    const Config& cr = ms[r]->cfg;
+    if (cr.hidden != c.hidden || cr.n_layers != c.n_layers || cr.max_seq != c.max_seq || cr.vocab != c.vocab) return -4;
+    if (pos[r] < 0 || pos[r] >= c.max_seq || tokens[r] < 0 || tokens[r] >= c.vocab) return -1;
+  }
+  const int H = c.hidden, qd = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim, I = c.intermediate;
+  std::vector<float> x((size_t)R * H), h((size_t)R * H), q((size_t)R * qd), k((size_t)R * kvd), v((size_t)R * kvd), qkv, att((size_t)R * qd),
+      tmp((size_t)R * H), up((size_t)R * I), gate, act((size_t)R * I), ffn((size_t)R * H), scores((size_t)R * c.n_heads * c.max_seq), row(H);
+  for (int r = 0; r < R; ++r) {
+    const int64_t rb = rlz_row_bytes(m.tok_embd.qtype, H); if (rb < 0) return -2;
+    rlz_dequantize(m.tok_embd.qtype, m.tok_embd.data + (int64_t)tokens[r] * rb, x.data() + (size_t)r * H, H);
+    if (m.pos_embd.ok()) {
+      const int64_t pb = rlz_row_bytes(m.pos_embd.qtype, H);
+      rlz_dequantize(m.pos_embd.qtype, m.pos_embd.data + (int64_t)pos[r] * pb, row.data(), H);
+      for (int i = 0; i < H; ++i) x[(size_t)r * H + i] += row[i];
+    }
+  }
+  if (c.gated_ffn) gate.resize((size_t)R * I);
+  for (int l = 0; l < c.n_layers; ++l) {
+    Layer& L = m.layers[l];
+    for (int r = 0; r < R; ++r) norm(c, x.data() + (size_t)r * H, h.data() + (size_t)r * H, H, L.attn_norm_w, L.attn_norm_b, rt.attn_nc[l].w, rt.attn_nc[l].b);
+    if (L.qkv_w.ok()) {
+      qkv.resize((size_t)R * (qd + 2 * kvd));
+      linear_rows(L.qkv_w, L.qkv_b, h.data(), qkv.data(), R, rt.qkv_b[l]);
+      for (int r = 0; r < R; ++r) {
+        const float* s0 = qkv.data() + (size_t)r * (qd + 2 * kvd);
+        std::copy(s0, s0 + qd, q.begin() + (size_t)r * qd);
+        std::copy(s0 + qd, s0 + qd + kvd, k.begin() + (size_t)r * kvd);
+        std::copy(s0 + qd + kvd, s0 + qd + 2 * kvd, v.begin() + (size_t)r * kvd);
+      }
+    } else {
+      linear_rows(L.q_w, L.q_b, h.data(), q.data(), R, rt.q_b[l]);
+      linear_rows(L.k_w, L.k_b, h.data(), k.data(), R, rt.k_b[l]);
+      linear_rows(L.v_w, L.v_b, h.data(), v.data(), R, rt.v_b[l]);
+    }
+    if (L.q_norm_w.ok() && rt.qn[l].empty()) vec_from(L.q_norm_w, rt.qn[l]);
+    if (L.k_norm_w.ok() && rt.kn[l].empty()) vec_from(L.k_norm_w, rt.kn[l]);
+    for (int r = 0; r < R; ++r) {
+      float* qt = q.data() + (size_t)r * qd; float* kt = k.data() + (size_t)r * kvd; Model& mr = *ms[r];
+      if (L.q_norm_w.ok()) head_rmsnorm(c, qt, c.n_heads, rt.qn[l]);
+      if (L.k_norm_w.ok()) head_rmsnorm(c, kt, c.n_kv_heads, rt.kn[l]);
+      rope(c, qt, c.n_heads, pos[r]); rope(c, kt, c.n_kv_heads, pos[r]);
+      std::copy(kt, kt + kvd, mr.kcache.begin() + ((size_t)l * c.max_seq + pos[r]) * kvd);
+      std::copy(v.begin() + (size_t)r * kvd, v.begin() + (size_t)(r + 1) * kvd, mr.vcache.begin() + ((size_t)l * c.max_seq + pos[r]) * kvd);
+    }
+    RowsCtx actx{ms, pos, l, R, q.data(), att.data(), scores.data()};
+    rlz_parallel_for((int64_t)R * c.n_heads, 1, attn_rows, &actx);
+    linear_rows(L.o_w, L.o_b, att.data(), tmp.data(), R, rt.o_b[l]);
+    if (!c.parallel_residual) {
+      for (size_t i = 0; i < (size_t)R * H; ++i) x[i] += tmp[i];
+      for (int r = 0; r < R; ++r) norm(c, x.data() + (size_t)r * H, h.data() + (size_t)r * H, H, L.ffn_norm_w, L.ffn_norm_b, rt.ffn_nc[l].w, rt.ffn_nc[l].b);
+    }
+    if (c.gated_ffn) {
+      linear_rows(L.gate_w, L.gate_b, h.data(), gate.data(), R, rt.gate_b[l]);
+      linear_rows(L.up_w, L.up_b, h.data(), up.data(), R, rt.up_b[l]);
+      for (size_t i = 0; i < (size_t)R * I; ++i) act[i] = silu(gate[i]) * up[i];
+    } else {
+      linear_rows(L.up_w, L.up_b, h.data(), up.data(), R, rt.up_b[l]);
+      for (size_t i = 0; i < (size_t)R * I; ++i) act[i] = gelu_tanh(up[i]);
+    }
+    linear_rows(L.down_w, L.down_b, act.data(), ffn.data(), R, rt.down_b[l]);
+    if (c.parallel_residual) for (size_t i = 0; i < (size_t)R * H; ++i) x[i] += tmp[i] + ffn[i];
+    else for (size_t i = 0; i < (size_t)R * H; ++i) x[i] += ffn[i];
+  }
+  for (int r = 0; r < R; ++r) norm(c, x.data() + (size_t)r * H, h.data() + (size_t)r * H, H, m.out_norm_w, m.out_norm_b, rt.out_nc.w, rt.out_nc.b);
+  linear_rows(m.out_w, m.out_b, h.data(), logits_out, R, rt.out_b);      // [R, vocab]
+  return 0;
+}
+
 }  // namespace
 
 extern "C" {
@@ -397,6 +501,15 @@ int rlz_cpu_prefill(void* mp, const int* tokens, int n, int pos0, int chunk, flo
     if (rc) return rc;
   }
   return 0;
+}
+
+// One decode step for `n` sequences in lock-step: handle i is fed tokens[i] at positions[i]; logits_out is [n, vocab].
+// The handles must have been bound to the same weight tensors (the weights of handle 0 are used for all rows).
+int rlz_cpu_forward_rows(void** handles, const int* tokens, const int* positions, int n, float* logits_out) {
+  if (n < 1 || n > 64) return -1;
+  Model* ms[64];
+  for (int i = 0; i < n; ++i) { ms[i] = (Model*)handles[i]; if (!ms[i]) return -1; for (int j = 0; j < i; ++j) if (ms[j] == ms[i]) return -5; }
+  return forward_rows(ms, tokens, positions, n, logits_out);
 }
 
 int rlz_cpu_layer_trace(void* mp, float* out) { Model& m = *(Model*)mp; std::copy(m.trace.begin(), m.trace.end(), out); return (int)m.trace.size(); }

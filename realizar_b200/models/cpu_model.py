@@ -55,6 +55,22 @@ class CpuModel:
             raise ValueError(f"forward failed (rc={rc}): token={token} pos={pos} max_seq={self.max_seq}")
         return logits
 
+    @staticmethod
+    def forward_rows(models: Sequence["CpuModel"], tokens: Sequence[int], positions: Sequence[int]) -> np.ndarray:
+        """One decode step for several sequences in lock-step (``models[i]`` is fed ``tokens[i]`` at ``positions[i]``; every model
+        keeps its own KV cache, all were built from the same weights): every projection is one batched product, so the step reads
+        the weights once for all sequences.  Returns logits ``[len(models), vocab]``; row by row they equal ``forward``."""
+        n = len(models)
+        handles = (ctypes.c_void_p * n)(*[m._h for m in models])
+        tk = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32))
+        ps = np.ascontiguousarray(np.asarray(positions, dtype=np.int32))
+        logits = np.empty((n, models[0].cfg.vocab_size), dtype=np.float32)
+        rc = cpu_lib().rlz_cpu_forward_rows(handles, tk.ctypes.data_as(ctypes.c_void_p), ps.ctypes.data_as(ctypes.c_void_p), n,
+                                            logits.ctypes.data_as(ctypes.c_void_p))
+        if rc:
+            raise ValueError(f"forward_rows failed (rc={rc})")
+        return logits
+
     def layer_trace(self) -> np.ndarray:
         out = np.empty(self.cfg.num_layers, dtype=np.float32)
         cpu_lib().rlz_cpu_layer_trace(self._h, out.ctypes.data_as(ctypes.c_void_p))

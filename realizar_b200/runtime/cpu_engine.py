@@ -62,9 +62,13 @@ class CpuSlotEngine:
 
     def feed(self, slot_tokens: Dict[int, int]) -> List[int]:
         out = [0] * self.cfg.max_batch
-        for s, t in slot_tokens.items():
-            logits = self.models[s].forward(int(t), self.pos[s])
+        slots = sorted(slot_tokens)
+        if len(slots) > 1:                                   # lock-step: the weights are read once for all running sequences
+            rows = CpuModel.forward_rows([self.models[s] for s in slots], [int(slot_tokens[s]) for s in slots], [self.pos[s] for s in slots])
+        else:
+            rows = [self.models[s].forward(int(slot_tokens[s]), self.pos[s]) for s in slots]
+        for s, logits in zip(slots, rows):
             self.pos[s] += 1
-            self.history[s].append(int(t))
+            self.history[s].append(int(slot_tokens[s]))
             out[s] = self._pick(s, logits)
         return out

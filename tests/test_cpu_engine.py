@@ -79,3 +79,40 @@ def test_chunked_prompt_pass_is_bit_identical_to_token_by_token():
         assert np.array_equal(serial.forward(5, 45), chunked.forward(5, 45)), name
         with pytest.raises(ValueError):
             chunked.prefill([1] * 200)                         # past max_seq
+
+
+def test_lock_step_decode_of_several_sequences_equals_separate_steps():
+    """One batched step for three sequences (own KV caches, different lengths) against three single steps: same logits bit
+    for bit over several steps; the CPU slot engine uses the lock-step path whenever more than one stream decodes."""
+    import numpy as np
+    from realizar_b200.models.config import named_config
+    from realizar_b200.models.cpu_model import CpuModel
+    from realizar_b200.models.weights import synthetic_weights
+    from realizar_b200.runtime.cpu_engine import CpuEngineConfig, CpuSlotEngine
+    from realizar_b200.runtime.engine import SamplingParams
+    for name in ("tiny-llama", "tiny-phi2"):
+        w = synthetic_weights(named_config(name), scheme="Q4_K_M", seed=0)
+        ms, ref = [CpuModel(w, 64) for _ in range(3)], [CpuModel(w, 64) for _ in range(3)]
+        prompts = [[1, 2, 3, 4, 5], [9, 8, 7], [4, 4, 4, 4, 4, 4, 4]]
+        for m, r, p in zip(ms, ref, prompts):
+            m.prefill(p); r.prefill(p)
+        toks, pos = [11, 12, 13], [len(p) for p in prompts]
+        for _ in range(3):
+            lg = CpuModel.forward_rows(ms, toks, pos)
+            lr = np.stack([r.forward(t, p) for r, t, p in zip(ref, toks, pos)])
+            assert np.array_equal(lg, lr), name
+            toks, pos = [int(a.argmax()) for a in lg], [p + 1 for p in pos]
+        with pytest.raises(ValueError):
+            CpuModel.forward_rows([ms[0], ms[0]], [1, 2], [0, 0])      # the same handle twice
+    eng = CpuSlotEngine(w, CpuEngineConfig(max_batch=3, max_seq_len=64))
+    solo = CpuSlotEngine(w, CpuEngineConfig(max_batch=1, max_seq_len=64))
+    firsts = {}
+    for s, p in enumerate(prompts):
+        eng.open_slot(s, 32); eng.set_sampling(s, SamplingParams(max_tokens=4))
+        firsts[s] = eng.prefill(s, p)
+    out = eng.feed(dict(firsts))
+    for s, p in enumerate(prompts):
+        solo.open_slot(0, 32); solo.set_sampling(0, SamplingParams(max_tokens=4))
+        f = solo.prefill(0, p)
+        assert f == firsts[s] and solo.feed({0: f})[0] == out[s]
+        solo.close_slot(0)
