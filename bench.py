@@ -102,8 +102,9 @@ class ClockSampler(threading.Thread):
 def reference_arm(args):
     # The reference is a Rust crate (no setup.py / pyproject.toml, no cargo toolchain or vendored crates
     # in this image), so installing it with pip fails and there is nothing to run.
-    print(json.dumps({"impl": "reference", "unavailable": "reference is a Rust crate: pip install fails (neither setup.py nor "
-                      "pyproject.toml), no cargo/rustc and its trueno* crates are not vendored", "n_gpus": args.gpus}))
+    if int(os.environ.get("RANK", "0")) == 0:               # one line per job, also when every rank of a multi-GPU launch gets here
+        print(json.dumps({"impl": "reference", "unavailable": "reference is a Rust crate: pip install fails (neither setup.py nor "
+                          "pyproject.toml), no cargo/rustc and its trueno* crates are not vendored", "n_gpus": args.gpus}))
     return 0
 
 
