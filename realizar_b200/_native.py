@@ -32,6 +32,7 @@ def cpu_lib() -> ctypes.CDLL:
             lib.rlz_quantize.argtypes = [c_int, c_void_p, c_void_p, c_int64, c_int64]
             lib.rlz_dequantize.argtypes = [c_int, c_void_p, c_void_p, c_int64]
             lib.rlz_matvec.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]
+            lib.rlz_matvec_multi.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64]
             lib.rlz_gguf_open_buffer.argtypes = [c_void_p, c_uint64, c_char_p, c_int]
             lib.rlz_gguf_open_buffer.restype = c_void_p
             lib.rlz_gguf_open_file.argtypes = [c_char_p, c_char_p, c_int]

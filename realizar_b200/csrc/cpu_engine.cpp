@@ -21,6 +21,7 @@ using namespace rlz;
 
 extern "C" {
 int rlz_matvec(int qtype, const void* W, const float* x, float* y, int64_t n, int64_t k, int64_t batch);
+int rlz_matvec_multi(int nmat, const int* qtypes, const void* const* Ws, const int64_t* ns, int64_t k, const float* x, float* const* ys, int64_t batch);
 int rlz_dequantize(int qtype, const void* src, float* dst, int64_t n);
 int64_t rlz_row_bytes(int qtype, int64_t k);
 void rlz_parallel_for(int64_t n, int64_t chunk, void (*fn)(int64_t, int64_t, void*), void* ctx);
@@ -85,6 +86,23 @@ void linear(const Tensor& w, const Tensor& b, const float* x, float* y, std::vec
   if (b.ok()) {
     if ((int64_t)bbuf.size() != w.n) vec_from(b, bbuf);
     for (int64_t i = 0; i < w.n; ++i) y[i] += bbuf[i];
+  }
+}
+
+// Up to three projections of the same input in one parallel region (falls back to one region each when their block types need
+// different activation formats); biases are added afterwards.  T rows of x ([T, k]) give T rows per output ([T, n]).
+struct Proj { const Tensor* w; const Tensor* b; float* y; std::vector<float>* bbuf; };
+void linear_group(Proj* ps, int np, const float* x, int T) {
+  int qts[4]; const void* Ws[4]; int64_t ns[4]; float* ys[4];
+  for (int i = 0; i < np; ++i) { qts[i] = ps[i].w->qtype; Ws[i] = ps[i].w->data; ns[i] = ps[i].w->n; ys[i] = ps[i].y; }
+  bool same_k = true; for (int i = 1; i < np; ++i) same_k &= ps[i].w->k == ps[0].w->k;
+  if (!same_k || np < 2 || rlz_matvec_multi(np, qts, Ws, ns, ps[0].w->k, x, ys, T) != 0)
+    for (int i = 0; i < np; ++i) rlz_matvec(qts[i], Ws[i], x, ys[i], ns[i], ps[i].w->k, T);
+  for (int i = 0; i < np; ++i) {
+    const Tensor& b = *ps[i].b;
+    if (!b.ok()) continue;
+    if ((int64_t)ps[i].bbuf->size() != ns[i]) vec_from(b, *ps[i].bbuf);
+    for (int t = 0; t < T; ++t) for (int64_t j = 0; j < ns[i]; ++j) ys[i][(size_t)t * ns[i] + j] += (*ps[i].bbuf)[j];
   }
 }
 
@@ -169,9 +187,8 @@ int forward(Model& m, int token, int pos, float* logits_out) {
       std::copy(m.qkv.begin() + qd, m.qkv.begin() + qd + kvd, m.k.begin());
       std::copy(m.qkv.begin() + qd + kvd, m.qkv.begin() + qd + 2 * kvd, m.v.begin());
     } else {
-      linear(L.q_w, L.q_b, m.h.data(), m.q.data(), rt.q_b[l]);
-      linear(L.k_w, L.k_b, m.h.data(), m.k.data(), rt.k_b[l]);
-      linear(L.v_w, L.v_b, m.h.data(), m.v.data(), rt.v_b[l]);
+      Proj qkv3[3] = {{&L.q_w, &L.q_b, m.q.data(), &rt.q_b[l]}, {&L.k_w, &L.k_b, m.k.data(), &rt.k_b[l]}, {&L.v_w, &L.v_b, m.v.data(), &rt.v_b[l]}};
+      linear_group(qkv3, 3, m.h.data(), 1);
     }
     if (L.q_norm_w.ok()) { if (rt.qn[l].empty()) vec_from(L.q_norm_w, rt.qn[l]); head_rmsnorm(c, m.q.data(), c.n_heads, rt.qn[l]); }
     if (L.k_norm_w.ok()) { if (rt.kn[l].empty()) vec_from(L.k_norm_w, rt.kn[l]); head_rmsnorm(c, m.k.data(), c.n_kv_heads, rt.kn[l]); }
@@ -189,8 +206,8 @@ int forward(Model& m, int token, int pos, float* logits_out) {
       ffn_in = m.h.data();
     }
     if (c.gated_ffn) {
-      linear(L.gate_w, L.gate_b, ffn_in, m.gate.data(), rt.gate_b[l]);
-      linear(L.up_w, L.up_b, ffn_in, m.up.data(), rt.up_b[l]);
+      Proj gu[2] = {{&L.gate_w, &L.gate_b, m.gate.data(), &rt.gate_b[l]}, {&L.up_w, &L.up_b, m.up.data(), &rt.up_b[l]}};
+      linear_group(gu, 2, ffn_in, 1);
       for (int i = 0; i < c.intermediate; ++i) m.act[i] = silu(m.gate[i]) * m.up[i];
     } else {
       linear(L.up_w, L.up_b, ffn_in, m.up.data(), rt.up_b[l]);
@@ -279,9 +296,8 @@ int forward_chunk(Model& m, const int* tokens, int T, int pos0, float* logits_ou
         std::copy(r + qd + kvd, r + qd + 2 * kvd, v.begin() + (size_t)t * kvd);
       }
     } else {
-      linear_rows(L.q_w, L.q_b, h.data(), q.data(), T, rt.q_b[l]);
-      linear_rows(L.k_w, L.k_b, h.data(), k.data(), T, rt.k_b[l]);
-      linear_rows(L.v_w, L.v_b, h.data(), v.data(), T, rt.v_b[l]);
+      Proj qkv3[3] = {{&L.q_w, &L.q_b, q.data(), &rt.q_b[l]}, {&L.k_w, &L.k_b, k.data(), &rt.k_b[l]}, {&L.v_w, &L.v_b, v.data(), &rt.v_b[l]}};
+      linear_group(qkv3, 3, h.data(), T);
     }
     if (L.q_norm_w.ok() && rt.qn[l].empty()) vec_from(L.q_norm_w, rt.qn[l]);
     if (L.k_norm_w.ok() && rt.kn[l].empty()) vec_from(L.k_norm_w, rt.kn[l]);
@@ -301,8 +317,8 @@ int forward_chunk(Model& m, const int* tokens, int T, int pos0, float* logits_ou
       for (int t = 0; t < T; ++t) norm(c, x.data() + (size_t)t * H, h.data() + (size_t)t * H, H, L.ffn_norm_w, L.ffn_norm_b, rt.ffn_nc[l].w, rt.ffn_nc[l].b);
     }
     if (c.gated_ffn) {
-      linear_rows(L.gate_w, L.gate_b, h.data(), gate.data(), T, rt.gate_b[l]);
-      linear_rows(L.up_w, L.up_b, h.data(), up.data(), T, rt.up_b[l]);
+      Proj gu[2] = {{&L.gate_w, &L.gate_b, gate.data(), &rt.gate_b[l]}, {&L.up_w, &L.up_b, up.data(), &rt.up_b[l]}};
+      linear_group(gu, 2, h.data(), T);
       for (size_t i = 0; i < (size_t)T * I; ++i) act[i] = silu(gate[i]) * up[i];
     } else {
       linear_rows(L.up_w, L.up_b, h.data(), up.data(), T, rt.up_b[l]);
@@ -388,9 +404,8 @@ int forward_rows(Model** ms, const int* tokens, const int* pos, int R, float* lo
         std::copy(s0 + qd + kvd, s0 + qd + 2 * kvd, v.begin() + (size_t)r * kvd);
       }
     } else {
-      linear_rows(L.q_w, L.q_b, h.data(), q.data(), R, rt.q_b[l]);
-      linear_rows(L.k_w, L.k_b, h.data(), k.data(), R, rt.k_b[l]);
-      linear_rows(L.v_w, L.v_b, h.data(), v.data(), R, rt.v_b[l]);
+      Proj qkv3[3] = {{&L.q_w, &L.q_b, q.data(), &rt.q_b[l]}, {&L.k_w, &L.k_b, k.data(), &rt.k_b[l]}, {&L.v_w, &L.v_b, v.data(), &rt.v_b[l]}};
+      linear_group(qkv3, 3, h.data(), R);
     }
     if (L.q_norm_w.ok() && rt.qn[l].empty()) vec_from(L.q_norm_w, rt.qn[l]);
     if (L.k_norm_w.ok() && rt.kn[l].empty()) vec_from(L.k_norm_w, rt.kn[l]);
@@ -410,8 +425,8 @@ int forward_rows(Model** ms, const int* tokens, const int* pos, int R, float* lo
       for (int r = 0; r < R; ++r) norm(c, x.data() + (size_t)r * H, h.data() + (size_t)r * H, H, L.ffn_norm_w, L.ffn_norm_b, rt.ffn_nc[l].w, rt.ffn_nc[l].b);
     }
     if (c.gated_ffn) {
-      linear_rows(L.gate_w, L.gate_b, h.data(), gate.data(), R, rt.gate_b[l]);
-      linear_rows(L.up_w, L.up_b, h.data(), up.data(), R, rt.up_b[l]);
+      Proj gu[2] = {{&L.gate_w, &L.gate_b, gate.data(), &rt.gate_b[l]}, {&L.up_w, &L.up_b, up.data(), &rt.up_b[l]}};
+      linear_group(gu, 2, h.data(), R);
       for (size_t i = 0; i < (size_t)R * I; ++i) act[i] = silu(gate[i]) * up[i];
     } else {
       linear_rows(L.up_w, L.up_b, h.data(), up.data(), R, rt.up_b[l]);

@@ -903,6 +903,42 @@ int rlz_matvec(int qtype, const void* W, const float* x, float* y, int64_t n, in
   return 0;
 }
 
+// Several weight matrices with the same input (Q / K / V, gate / up): the activation rows are quantised once and the rows of all
+// matrices are spread over the pool in ONE parallel region (a decode step of a small model is bounded by the number of such
+// regions, not by their arithmetic).  All matrices must take the same activation format (all K-quants or all 32-weight block
+// types); returns -2 otherwise and the caller falls back to one call per matrix.  Row by row the results equal rlz_matvec.
+int rlz_matvec_multi(int nmat, const int* qtypes, const void* const* Ws, const int64_t* ns, int64_t k, const float* x, float* const* ys, int64_t batch) {
+  if (nmat < 1 || nmat > 4) return -1;
+  bool kq = is_kquant(qtypes[0]);
+  int64_t rbs[4], starts[5] = {0, 0, 0, 0, 0};
+  for (int m = 0; m < nmat; ++m) {
+    const int qt = qtypes[m];
+    if (qt == QT_F32 || qt == QT_F16 || qt == QT_BF16 || is_kquant(qt) != kq) return -2;
+    rbs[m] = rlz_row_bytes(qt, k);
+    if (rbs[m] < 0) return -1;
+    starts[m + 1] = starts[m] + ns[m];
+  }
+  const int64_t total = starts[nmat];
+  const int nb = (int)(kq ? k / 256 : k / 32);
+  std::vector<Q8K> actk; std::vector<Q80A> actl;
+  if (kq) { actk.resize((size_t)nb * batch); for (int64_t b = 0; b < batch; ++b) quantize_q8_k(x + b * k, actk.data() + b * nb, k); }
+  else { actl.resize((size_t)nb * batch); for (int64_t b = 0; b < batch; ++b) quantize_q8_0_act(x + b * k, actl.data() + b * nb, k); }
+  std::atomic<int64_t> next{0};
+  pool().run([&](int) {
+    for (;;) {
+      int64_t g0 = next.fetch_add(32); if (g0 >= total) break;
+      for (int64_t g = g0; g < std::min(total, g0 + 32); ++g) {
+        int m = 0; while (g >= starts[m + 1]) ++m;
+        const int64_t r = g - starts[m], n = ns[m];
+        const uint8_t* wr = (const uint8_t*)Ws[m] + r * rbs[m];
+        for (int64_t b = 0; b < batch; ++b)
+          ys[m][b * n + r] = kq ? dot_kquant(qtypes[m], wr, actk.data() + b * nb, nb) : dot_legacy_q8_0(qtypes[m], wr, actl.data() + b * nb, nb);
+      }
+    }
+  });
+  return 0;
+}
+
 // run fn over [0,n) in parallel chunks (exposed for the CPU engine in this library)
 void rlz_parallel_for(int64_t n, int64_t chunk, void (*fn)(int64_t, int64_t, void*), void* ctx) {
   std::atomic<int64_t> next{0};

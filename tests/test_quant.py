@@ -148,3 +148,27 @@ def test_simd_fused_dots_match_dequantised_reference(qt):
     assert lib.rlz_cpu_dot_path(int(qt)) in (0, 1, 2)
     if lib.rlz_cpu_has_avx2():
         assert lib.rlz_cpu_dot_path(int(qt)) >= 1          # no block type of the public surface is left on the scalar path
+
+
+def test_multi_matrix_product_equals_separate_products():
+    """Several matrices with one input in one parallel region (Q / K / V, gate / up in the CPU decoder): bit-identical to one call
+    per matrix; matrices whose block types need different activation formats are refused (-2) so the caller falls back."""
+    import ctypes
+    from realizar_b200._native import cpu_lib
+    lib, rng = cpu_lib(), np.random.default_rng(0)
+    for types, k, want in (((QType.Q5_0, QType.Q5_0, QType.Q8_0), 896, 0), ((QType.Q4_K, QType.Q6_K), 512, 0), ((QType.Q4_K, QType.Q8_0), 512, -2)):
+        ns, B = [64, 20, 33][:len(types)], 3
+        x = rng.standard_normal((B, k)).astype(np.float32)
+        qs, ys, refs = [], [], []
+        for qt, n in zip(types, ns):
+            q = np.ascontiguousarray(np.frombuffer(quant.quantize((rng.standard_normal((n, k)) * 0.1).astype(np.float32), qt), np.uint8))
+            qs.append(q); ys.append(np.zeros((B, n), np.float32))
+            r = np.zeros((B, n), np.float32)
+            assert lib.rlz_matvec(int(qt), q.ctypes.data, x.ctypes.data, r.ctypes.data, n, k, B) == 0
+            refs.append(r)
+        m = len(types)
+        rc = lib.rlz_matvec_multi(m, (ctypes.c_int * m)(*[int(t) for t in types]), (ctypes.c_void_p * m)(*[q.ctypes.data for q in qs]),
+                                  (ctypes.c_int64 * m)(*ns), k, x.ctypes.data, (ctypes.c_void_p * m)(*[y.ctypes.data for y in ys]), B)
+        assert rc == want
+        if rc == 0:
+            assert all(np.array_equal(a, b) for a, b in zip(ys, refs))
