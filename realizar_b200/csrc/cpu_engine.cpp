@@ -106,14 +106,24 @@ void linear_group(Proj* ps, int np, const float* x, int T) {
   }
 }
 
-void rope(const Config& c, float* v, int n_heads, int pos) {
+// (cos, sin) of every rotary pair at one position: computed once per token and shared by all layers and heads
+void rope_table(const Config& c, int pos, std::vector<float>& cs) {
+  const int rd = c.rope_dim, half = rd / 2;
+  cs.resize(rd > 0 ? (size_t)2 * half : 0);
+  for (int i = 0; i < half; ++i) {
+    const float freq = powf(c.rope_theta, -2.f * i / rd);
+    const float ang = pos * freq;
+    cs[2 * i] = cosf(ang); cs[2 * i + 1] = sinf(ang);
+  }
+}
+
+void rope(const Config& c, float* v, int n_heads, const std::vector<float>& cs_tab) {
   const int rd = c.rope_dim; if (rd <= 0) return;
   const int half = rd / 2;
   for (int h = 0; h < n_heads; ++h) {
     float* p = v + (size_t)h * c.head_dim;
     for (int i = 0; i < half; ++i) {
-      const float freq = powf(c.rope_theta, -2.f * i / rd);
-      const float ang = pos * freq, cs = cosf(ang), sn = sinf(ang);
+      const float cs = cs_tab[2 * i], sn = cs_tab[2 * i + 1];
       const int i0 = c.rope_type == 2 ? i : 2 * i, i1 = c.rope_type == 2 ? i + half : 2 * i + 1;
       const float a = p[i0], b = p[i1];
       p[i0] = a * cs - b * sn; p[i1] = a * sn + b * cs;
@@ -178,6 +188,7 @@ int forward(Model& m, int token, int pos, float* logits_out) {
     for (int i = 0; i < H; ++i) m.x[i] += m.tmp[i];
   }
   m.trace.assign(c.n_layers, 0.f);
+  std::vector<float> cs_tab; rope_table(c, pos, cs_tab);
   for (int l = 0; l < c.n_layers; ++l) {
     Layer& L = m.layers[l];
     norm(c, m.x.data(), m.h.data(), H, L.attn_norm_w, L.attn_norm_b, rt.attn_nc[l].w, rt.attn_nc[l].b);
@@ -192,7 +203,7 @@ int forward(Model& m, int token, int pos, float* logits_out) {
     }
     if (L.q_norm_w.ok()) { if (rt.qn[l].empty()) vec_from(L.q_norm_w, rt.qn[l]); head_rmsnorm(c, m.q.data(), c.n_heads, rt.qn[l]); }
     if (L.k_norm_w.ok()) { if (rt.kn[l].empty()) vec_from(L.k_norm_w, rt.kn[l]); head_rmsnorm(c, m.k.data(), c.n_kv_heads, rt.kn[l]); }
-    rope(c, m.q.data(), c.n_heads, pos); rope(c, m.k.data(), c.n_kv_heads, pos);
+    rope(c, m.q.data(), c.n_heads, cs_tab); rope(c, m.k.data(), c.n_kv_heads, cs_tab);
     std::copy(m.k.begin(), m.k.begin() + kvd, m.kcache.begin() + ((size_t)l * c.max_seq + pos) * kvd);
     std::copy(m.v.begin(), m.v.begin() + kvd, m.vcache.begin() + ((size_t)l * c.max_seq + pos) * kvd);
     AttnCtx actx{&m, l, pos};
@@ -282,6 +293,8 @@ int forward_chunk(Model& m, const int* tokens, int T, int pos0, float* logits_ou
     }
   }
   if (c.gated_ffn) gate.resize((size_t)T * I);
+  std::vector<std::vector<float>> cs_tabs(T);
+  for (int t = 0; t < T; ++t) rope_table(c, pos0 + t, cs_tabs[t]);
   m.trace.assign(c.n_layers, 0.f);
   for (int l = 0; l < c.n_layers; ++l) {
     Layer& L = m.layers[l];
@@ -305,7 +318,7 @@ int forward_chunk(Model& m, const int* tokens, int T, int pos0, float* logits_ou
       float* qt = q.data() + (size_t)t * qd; float* kt = k.data() + (size_t)t * kvd;
       if (L.q_norm_w.ok()) head_rmsnorm(c, qt, c.n_heads, rt.qn[l]);
       if (L.k_norm_w.ok()) head_rmsnorm(c, kt, c.n_kv_heads, rt.kn[l]);
-      rope(c, qt, c.n_heads, pos0 + t); rope(c, kt, c.n_kv_heads, pos0 + t);
+      rope(c, qt, c.n_heads, cs_tabs[t]); rope(c, kt, c.n_kv_heads, cs_tabs[t]);
       std::copy(kt, kt + kvd, m.kcache.begin() + ((size_t)l * c.max_seq + pos0 + t) * kvd);
       std::copy(v.begin() + (size_t)t * kvd, v.begin() + (size_t)(t + 1) * kvd, m.vcache.begin() + ((size_t)l * c.max_seq + pos0 + t) * kvd);
     }
@@ -391,6 +404,8 @@ int forward_rows(Model** ms, const int* tokens, const int* pos, int R, float* lo
     }
   }
   if (c.gated_ffn) gate.resize((size_t)R * I);
+  std::vector<std::vector<float>> cs_tabs(R);
+  for (int r = 0; r < R; ++r) rope_table(c, pos[r], cs_tabs[r]);
   for (int l = 0; l < c.n_layers; ++l) {
     Layer& L = m.layers[l];
     for (int r = 0; r < R; ++r) norm(c, x.data() + (size_t)r * H, h.data() + (size_t)r * H, H, L.attn_norm_w, L.attn_norm_b, rt.attn_nc[l].w, rt.attn_nc[l].b);
@@ -413,7 +428,7 @@ int forward_rows(Model** ms, const int* tokens, const int* pos, int R, float* lo
       float* qt = q.data() + (size_t)r * qd; float* kt = k.data() + (size_t)r * kvd; Model& mr = *ms[r];
       if (L.q_norm_w.ok()) head_rmsnorm(c, qt, c.n_heads, rt.qn[l]);
       if (L.k_norm_w.ok()) head_rmsnorm(c, kt, c.n_kv_heads, rt.kn[l]);
-      rope(c, qt, c.n_heads, pos[r]); rope(c, kt, c.n_kv_heads, pos[r]);
+      rope(c, qt, c.n_heads, cs_tabs[r]); rope(c, kt, c.n_kv_heads, cs_tabs[r]);
       std::copy(kt, kt + kvd, mr.kcache.begin() + ((size_t)l * c.max_seq + pos[r]) * kvd);
       std::copy(v.begin() + (size_t)r * kvd, v.begin() + (size_t)(r + 1) * kvd, mr.vcache.begin() + ((size_t)l * c.max_seq + pos[r]) * kvd);
     }
