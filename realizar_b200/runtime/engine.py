@@ -800,6 +800,22 @@ class DecodeEngine:
         self.kv[:, :, idx] = snap["kv"].to(self.device, non_blocking=True)
         s.position = snap["position"]
 
+    def reset(self) -> None:
+        """Back to the post-load state after a failed step: probe the device (a lost context makes the synchronise raise, and
+        then nothing in this process can use the GPU again), close every open sequence, clear the device-side status words and
+        mark every row idle.  Weights, captured graphs and launch plans stay: they do not depend on sequence state."""
+        torch.cuda.synchronize(self.device)                  # raises when the context is poisoned
+        for slot, s in enumerate(self.slots):
+            if s.active:
+                self.close_slot(slot)
+        ops.device_error(clear=True)
+        if self.comm is not None and hasattr(self.comm, "check_status"):
+            self.comm.check_status()
+        self._h_tok_pos[1].fill_(-1)
+        self.buf.positions.fill_(-1)
+        self.steps_run = 0
+        torch.cuda.synchronize(self.device)
+
     def close(self) -> None:
         """Release the captured graphs and launch plans (they hold kernels, buffers and, under tensor parallelism, work of the
         process group's communicator) and wait for the device.  Call before ``torch.distributed.destroy_process_group()``:

@@ -510,6 +510,40 @@ class ServingEngine:
                     self.sched.finish(r, FinishReason.ERROR, error=repr(e))
                 return
 
+    def recover(self) -> bool:
+        """After the loop latched unhealthy: probe the engine and, when it still answers, bring the server back.  Everything
+        that was in flight has already been failed; ``engine.reset()`` returns the engine to its post-load state (no open
+        sequences, error words cleared) and must raise when the device context itself is lost - then the process has to be
+        restarted and the latch stays.  Returns True when serving again.  (Role of the reference's poisoned-context detection
+        and pool reset, src/cuda/executor/mod.rs:60-118.)"""
+        if self.health == "ok":
+            return True
+        if self._thread is not None and self._thread.is_alive():
+            return False                                     # the loop has not finished failing its requests yet
+        try:
+            reset = getattr(self.engine, "reset", None)
+            if reset is None:
+                raise RuntimeError("the engine cannot be reset in place")
+            reset()
+        except Exception as e:                               # context lost (or no reset path): stay latched
+            self.last_error = f"recovery failed: {e!r}"
+            return False
+        self.sched = Scheduler(self.cfg, total_pages=getattr(self.engine, "num_pages", None))
+        self.sched.on_finished = self._request_finished
+        while not self._inbox.empty():                       # requests that slipped in between the failure and the latch
+            try:
+                r = self._inbox.get_nowait()
+                r.error, r.state, r.finish_reason = "engine was reset", RequestState.FINISHED, FinishReason.ERROR
+                if r.on_finish:
+                    r.on_finish(r)
+            except queue.Empty:
+                break
+        self.health, self.last_error = "ok", None
+        self._thread = None
+        self._stop.clear()
+        self.start()
+        return True
+
     def metrics(self) -> dict:
         st = list(self.step_times)
         snap = self.sched.snapshot()
@@ -557,6 +591,13 @@ class FakeEngine:
 
     def free_slots(self):
         return [i for i in range(self.cfg.max_batch) if i not in self.open]
+
+    def reset(self) -> None:
+        """Back to the post-load state (``fail_after`` counts from here again; ``context_lost`` makes the probe fail)."""
+        if getattr(self, "context_lost", False):
+            raise RuntimeError("device context lost")
+        self.open.clear()
+        self.steps = 0
 
     def score_tokens(self, tokens, want_embedding=False, top_k=0):
         """Scores of the toy model: the successor (t + 1) % vocab has probability 1/2."""

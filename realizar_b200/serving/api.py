@@ -626,6 +626,17 @@ def create_app(state: AppState) -> FastAPI:
         r = await run_blocking(encode("warm up"), 4, 0.0, 1, 1.0)
         return {"status": "ok", "tokens": len(r.output), "seconds": time.monotonic() - t0}
 
+    @app.post("/v1/gpu/reset")
+    async def gpu_reset():
+        """Bring a server back whose engine loop stopped after a failed step (health "unhealthy"): the engine is probed and
+        reset in place; 503 when the device context is lost and the process has to be restarted."""
+        if state.serving is None:
+            raise HTTPException(503, "no model loaded")
+        ok = await asyncio.get_running_loop().run_in_executor(None, state.serving.recover)
+        if not ok:
+            raise HTTPException(503, f"engine cannot be recovered in place: {state.serving.last_error}")
+        return {"status": "ok", "health": state.serving.health}
+
     return app
 
 

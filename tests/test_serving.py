@@ -305,3 +305,43 @@ def test_trace_context_is_propagated_and_requests_are_recorded():
             assert "requests_done" in sched
     finally:
         state.serving.stop()
+
+
+def test_recovery_after_a_failed_step_and_refusal_when_the_context_is_lost():
+    """The engine raises in the middle of serving: requests in flight fail, /health turns unhealthy; POST /v1/gpu/reset resets the
+    engine in place and the server answers again; when the reset probe itself fails (device context lost) the latch stays."""
+    from fastapi.testclient import TestClient
+    from realizar_b200.runtime.scheduler import FakeEngine, ServingEngine
+    from realizar_b200.serving.api import AppState, create_app
+    from realizar_b200.serving.chat_template import RawTemplate
+    from realizar_b200.serving.tokenizer import ByteTokenizer
+    eng = FakeEngine(vocab=256, fail_after=3)
+    serving = ServingEngine(eng).start()
+    state = AppState(serving, ByteTokenizer(256), RawTemplate(), "demo", None, compute_mode="cpu")
+    try:
+        with TestClient(create_app(state)) as c:
+            r = c.post("/generate", json={"prompt": "abc", "max_tokens": 20})
+            assert r.status_code == 500
+            for _ in range(100):
+                if serving.health != "ok":
+                    break
+                time.sleep(0.01)
+            assert c.get("/health").status_code == 503
+            eng.fail_after = None
+            assert c.post("/v1/gpu/reset").json() == {"status": "ok", "health": "ok"}
+            assert c.get("/health").status_code == 200
+            ok = c.post("/generate", json={"prompt": "abc", "max_tokens": 5})
+            assert ok.status_code == 200 and ok.json()["num_generated"] == 5
+            # second failure, and this time the device does not answer the probe
+            eng.fail_after, eng.steps = 1, 0
+            assert c.post("/generate", json={"prompt": "abc", "max_tokens": 20}).status_code == 500
+            for _ in range(100):
+                if serving.health != "ok" and not serving._thread.is_alive():
+                    break
+                time.sleep(0.01)
+            eng.context_lost = True
+            r = c.post("/v1/gpu/reset")
+            assert r.status_code == 503 and "context lost" in r.json()["detail"]
+            assert c.get("/health").status_code == 503
+    finally:
+        serving.stop()
