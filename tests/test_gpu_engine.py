@@ -423,3 +423,19 @@ def test_layer_streaming_matches_resident_engine(cuda_device, which):
         torch.cuda.synchronize()
     assert outs[0] == outs[1], outs
     assert _cos(logits[0], logits[1]) > 0.9999
+
+
+def test_engine_reset_returns_to_the_post_load_state(cuda_device):
+    from realizar_b200.models.weights import synthetic_weights
+    from realizar_b200.runtime.engine import DecodeEngine, EngineConfig, SamplingParams
+    w = synthetic_weights(_kq_llama(), seed=2, std=0.05)
+    eng = DecodeEngine(w, EngineConfig(max_batch=2, max_seq_len=128, greedy_only=True))
+    first = eng.generate([1, 2, 3, 4, 5, 6, 7, 8, 9], SamplingParams(max_tokens=6))
+    eng.open_slot(0, 64); eng.open_slot(1, 64)
+    eng.prefill(0, [5, 6, 7]); eng.prefill(1, [9] * 20)
+    used = eng.pages.stats().utilization
+    assert used > 0 and len(eng.free_slots()) == 0
+    eng.reset()
+    assert len(eng.free_slots()) == 2 and eng.pages.stats().utilization == 0
+    assert int(eng.buf.positions.max()) == -1
+    assert eng.generate([1, 2, 3, 4, 5, 6, 7, 8, 9], SamplingParams(max_tokens=6)) == first
