@@ -15,11 +15,15 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence
 
+import logging
+
 import numpy as np
 import torch
 import torch.distributed as dist
 
-OP_STOP, OP_OPEN, OP_CLOSE, OP_SAMPLING, OP_PREFILL, OP_FEED, OP_SCORE, OP_MASK, OP_DRAFT, OP_FORWARD, OP_ROLLBACK = range(11)
+log = logging.getLogger("realizar_b200.tp_serving")
+
+OP_STOP, OP_OPEN, OP_CLOSE, OP_SAMPLING, OP_PREFILL, OP_FEED, OP_SCORE, OP_MASK, OP_DRAFT, OP_FORWARD, OP_ROLLBACK, OP_RESET = range(12)
 
 
 class _Channel:
@@ -135,6 +139,12 @@ class TpLeaderEngine:
         self.chan.send(OP_ROLLBACK, slot, [position])
         self.engine.rollback(slot, position)
 
+    def reset(self) -> None:
+        """After a failed step: every rank returns its engine to the post-load state (the followers ignore the commands that
+        were sent between their failure and this one, see ``follower_loop``).  Raises when this rank's device does not answer."""
+        self.chan.send(OP_RESET)
+        self.engine.reset()
+
     def shutdown(self, leave: bool = True) -> None:
         """Release the followers (they leave ``follower_loop``).  With ``leave`` (servers) this rank then takes its engine
         and the process group down in order - captured graphs first, then the peer-memory mappings, then the group - as the
@@ -156,35 +166,52 @@ def leave_group(engine, comm) -> None:
 
 
 def follower_loop(engine, group) -> int:
-    """Execute rank 0's engine calls until it sends the stop command.  Returns the number of calls executed."""
-    chan, n = _Channel(group), 0
+    """Execute rank 0's engine calls until it sends the stop command.  Returns the number of calls executed.
+    A call that raises here (the same status word or CUDA error that stops rank 0's loop) does not end the follower: it stops
+    executing commands - the sequence state is no longer in step with rank 0 - until rank 0 sends the reset command, resets its
+    engine and goes on; if the reset itself raises, the device is lost and the exception ends this rank."""
+    chan, n, failed = _Channel(group), 0, None
     while True:
         op, slot, ints, floats = chan.recv()
         if op == OP_STOP:
             return n
+        if op == OP_RESET:
+            engine.reset()
+            failed = None
+            continue
+        if failed is not None:
+            continue
         n += 1
-        if op == OP_OPEN:
-            engine.open_slot(slot, ints[0])
-        elif op == OP_CLOSE:
-            engine.close_slot(slot)
-        elif op == OP_SAMPLING:
-            engine.set_sampling(slot, _sampling_from_wire(ints, floats))
-        elif op == OP_MASK:
-            engine.set_token_mask(slot, None if ints[0] == 0 else np.unpackbits(np.asarray(ints[2:], dtype=np.uint8))[: ints[1]].astype(bool))
-        elif op == OP_PREFILL:
-            engine.prefill(slot, ints)
-        elif op == OP_FEED:
-            engine.feed({ints[i]: ints[i + 1] for i in range(0, len(ints), 2)})
-        elif op == OP_SCORE:
-            engine.score_tokens(ints, want_embedding=bool(slot))
-        elif op == OP_DRAFT:
-            engine.draft_step(slot, ints[0], ints[1:])
-        elif op == OP_FORWARD:
-            engine.forward_tokens(slot, ints)
-        elif op == OP_ROLLBACK:
-            engine.rollback(slot, ints[0])
-        else:
-            raise RuntimeError(f"unknown tensor-parallel serving command {op}")
+        try:
+            _execute(engine, op, slot, ints, floats)
+        except Exception as e:                              # noqa: BLE001 - reported, then wait for the reset
+            failed = repr(e)
+            log.error("tensor-parallel follower: engine call %d failed (%s); waiting for a reset", op, failed)
+
+
+def _execute(engine, op, slot, ints, floats) -> None:
+    if op == OP_OPEN:
+        engine.open_slot(slot, ints[0])
+    elif op == OP_CLOSE:
+        engine.close_slot(slot)
+    elif op == OP_SAMPLING:
+        engine.set_sampling(slot, _sampling_from_wire(ints, floats))
+    elif op == OP_MASK:
+        engine.set_token_mask(slot, None if ints[0] == 0 else np.unpackbits(np.asarray(ints[2:], dtype=np.uint8))[: ints[1]].astype(bool))
+    elif op == OP_PREFILL:
+        engine.prefill(slot, ints)
+    elif op == OP_FEED:
+        engine.feed({ints[i]: ints[i + 1] for i in range(0, len(ints), 2)})
+    elif op == OP_SCORE:
+        engine.score_tokens(ints, want_embedding=bool(slot))
+    elif op == OP_DRAFT:
+        engine.draft_step(slot, ints[0], ints[1:])
+    elif op == OP_FORWARD:
+        engine.forward_tokens(slot, ints)
+    elif op == OP_ROLLBACK:
+        engine.rollback(slot, ints[0])
+    else:
+        raise RuntimeError(f"unknown tensor-parallel serving command {op}")
 
 
 def init_tp(mode: str = "fused"):

@@ -120,7 +120,7 @@ from realizar_b200.runtime.scheduler import FakeEngine, Request, ServingEngine
 dist.init_process_group('gloo')
 rank = dist.get_rank()
 group = dist.new_group(backend='gloo')
-eng = FakeEngine(max_batch=2, vocab=50)
+eng = FakeEngine(max_batch=2, vocab=50, fail_after=7)      # the 8th decode step fails on EVERY rank (same call sequence everywhere)
 if rank == 0:
     lead = TpLeaderEngine(eng, group)
     sv = ServingEngine(lead).start()
@@ -132,6 +132,20 @@ if rank == 0:
     r2 = sv.generate([10, 11], max_tokens=3, token_masker=Mask(), timeout=30)
     sc = sv.call_on_engine(lambda e: e.score_tokens([5, 6, 7], want_embedding=True))
     assert r1.output == [4, 5, 6, 7] and r2.output == [7, 7, 7] and len(sc['logprobs']) == 2, (r1.output, r2.output, sc)
+    # a step that fails on every rank (same call sequence, same counter): the loop latches, the followers stop executing,
+    # the reset command brings all ranks back in step and serving goes on
+    import time
+    assert eng.steps == 5
+    bad = sv.generate([1, 2, 3], max_tokens=8, timeout=30)
+    assert bad.error is not None
+    for _ in range(200):
+        if sv.health != 'ok' and not sv._thread.is_alive():
+            break
+        time.sleep(0.01)
+    assert sv.health == 'unhealthy'
+    assert sv.recover() and sv.health == 'ok'
+    r3 = sv.generate([20, 21], max_tokens=3, timeout=30)
+    assert r3.output == [22, 23, 24], r3.output
     sv.stop()
     lead.shutdown(leave=False)
 else:
