@@ -402,12 +402,14 @@ void quantize_q8_k(const float* x, Q8K* y, int64_t k) {
   }
 }
 
-struct Q80A { float d; int8_t qs[32]; };
+struct Q80A { float d; int32_t sum; int8_t qs[32]; };     // sum of the 32 codes: the offset term of the unsigned weight types
 void quantize_q8_0_act(const float* x, Q80A* y, int64_t k) {
   for (int64_t i = 0; i < k / 32; ++i) {
     float amax = 0; for (int j = 0; j < 32; ++j) amax = std::max(amax, fabsf(x[i * 32 + j]));
     const float d = amax / 127.f, id = d ? 1.f / d : 0.f;
-    y[i].d = d; for (int j = 0; j < 32; ++j) y[i].qs[j] = (int8_t)nearest_int(x[i * 32 + j] * id);
+    int sum = 0;
+    y[i].d = d; for (int j = 0; j < 32; ++j) { y[i].qs[j] = (int8_t)nearest_int(x[i * 32 + j] * id); sum += y[i].qs[j]; }
+    y[i].sum = sum;
   }
 }
 
@@ -616,6 +618,51 @@ float dot_legacy_q8_0_avx2(int qtype, const uint8_t* w, const Q80A* a, int nb) {
   return hsum8(acc) + extra;
 }
 
+// 32-weight block types with VNNI (256-bit form): one dpbusd per block replaces the maddubs / madd pair, the fifth bits of
+// Q5_0 / Q5_1 come from a byte mask register loaded with the 32 bits themselves, and the constant offset of the unsigned codes
+// (8 for Q4_0, 16 for Q5_0) is applied through the activation block's code sum instead of a second product.
+__attribute__((target("avx512f,avx512bw,avx512vl,avx512vnni,avx2,fma")))
+float dot_legacy_q8_0_vnni(int qtype, const uint8_t* w, const Q80A* a, int nb) {
+  const __m256i bit5 = _mm256_set1_epi8(0x10);
+  __m256 acc = _mm256_setzero_ps();
+  float extra = 0.f;
+  const int bb = qtype_block_bytes(qtype);
+  for (int i = 0; i < nb; ++i, w += bb) {
+    const __m256i av = _mm256_loadu_si256((const __m256i*)a[i].qs);
+    const float da = half_bits_to_float(load_u16(w)) * a[i].d;
+    __m256i p;
+    switch (qtype) {
+      case QT_Q8_0: {
+        const __m256i q = _mm256_loadu_si256((const __m256i*)(w + 2));
+        p = _mm256_dpbusd_epi32(_mm256_setzero_si256(), _mm256_sign_epi8(q, q), _mm256_sign_epi8(av, q));
+        break; }
+      case QT_Q4_0:
+        p = _mm256_dpbusd_epi32(_mm256_setzero_si256(), nibbles32(w + 2), av);
+        extra = fmaf(-8.f * da, (float)a[i].sum, extra);
+        break;
+      case QT_Q5_0: {
+        const __mmask32 k5 = (__mmask32)((uint32_t)w[2] | ((uint32_t)w[3] << 8) | ((uint32_t)w[4] << 16) | ((uint32_t)w[5] << 24));
+        p = _mm256_dpbusd_epi32(_mm256_setzero_si256(), _mm256_or_si256(nibbles32(w + 6), _mm256_maskz_mov_epi8(k5, bit5)), av);
+        extra = fmaf(-16.f * da, (float)a[i].sum, extra);
+        break; }
+      case QT_Q4_1: case QT_Q5_1: {
+        const float m = half_bits_to_float(load_u16(w + 2));
+        __m256i q;
+        if (qtype == QT_Q4_1) q = nibbles32(w + 4);
+        else {
+          const __mmask32 k5 = (__mmask32)((uint32_t)w[4] | ((uint32_t)w[5] << 8) | ((uint32_t)w[6] << 16) | ((uint32_t)w[7] << 24));
+          q = _mm256_or_si256(nibbles32(w + 8), _mm256_maskz_mov_epi8(k5, bit5));
+        }
+        p = _mm256_dpbusd_epi32(_mm256_setzero_si256(), q, av);
+        extra = fmaf(m * a[i].d, (float)a[i].sum, extra);
+        break; }
+      default: return 0.f;
+    }
+    acc = _mm256_fmadd_ps(_mm256_set1_ps(da), _mm256_cvtepi32_ps(p), acc);
+  }
+  return hsum8(acc) + extra;
+}
+
 // ---- AVX-512 VNNI: one dpbusd does the byte products and their 4-wise sums ----------------------------------------------
 // Q4_K: the 64 activation bytes of a group of two sub-blocks are contiguous, so one 512-bit operand holds the low nibbles
 // (sub-block 2j) in its lower half and the high nibbles (2j + 1) in its upper half; the two sub-block scales sit in the
@@ -719,8 +766,10 @@ bool has_vnni512() { return false; }
 float dot_legacy_q8_0(int qtype, const uint8_t* w, const Q80A* a, int nb) {
   // legacy 32-element blocks against Q8_0-quantised activations
 #if RLZ_X86
-  if (has_avx2() && (qtype == QT_Q8_0 || qtype == QT_Q4_0 || qtype == QT_Q5_0 || qtype == QT_Q4_1 || qtype == QT_Q5_1))
-    return dot_legacy_q8_0_avx2(qtype, w, a, nb);
+  if (qtype == QT_Q8_0 || qtype == QT_Q4_0 || qtype == QT_Q5_0 || qtype == QT_Q4_1 || qtype == QT_Q5_1) {
+    if (has_vnni512()) return dot_legacy_q8_0_vnni(qtype, w, a, nb);
+    if (has_avx2()) return dot_legacy_q8_0_avx2(qtype, w, a, nb);
+  }
 #endif
   float sumf = 0; const int bb = qtype_block_bytes(qtype);
   for (int i = 0; i < nb; ++i, w += bb) {
@@ -785,7 +834,8 @@ int rlz_cpu_has_avx512_vnni() { return has_vnni512() ? 1 : 0; }
 int rlz_cpu_dot_path(int qtype) {
   switch (qtype) {
     case QT_Q4_K: case QT_Q6_K: return has_vnni512() ? 2 : has_avx2() ? 1 : 0;
-    case QT_Q5_K: case QT_Q8_0: case QT_Q4_0: case QT_Q5_0: case QT_Q4_1: case QT_Q5_1: return has_avx2() ? 1 : 0;
+    case QT_Q8_0: case QT_Q4_0: case QT_Q5_0: case QT_Q4_1: case QT_Q5_1: return has_vnni512() ? 2 : has_avx2() ? 1 : 0;
+    case QT_Q5_K: return has_avx2() ? 1 : 0;
     default: return 0;
   }
 }
