@@ -238,3 +238,16 @@ def test_guard_bands_name_the_overwritten_buffer():
     assert g.check() == ["b"]
     g.entries[0][1][GuardBands.BAND - 1] = 1                 # one byte before a
     assert g.check() == ["a", "b"] and g.bytes_reserved() >= 2 * 2 * GuardBands.BAND + 5 * 7 * 4 + 33 * 4
+
+
+def test_layer_streaming_prefetch_order():
+    """Which layer a streamed model starts copying when a layer is done: two places on in the pass's order (the next one already
+    sits in the other buffer), wrapping into the next pass; nothing when at most two layers are streamed."""
+    from realizar_b200.models.decoder import GpuModel
+    m = object.__new__(GpuModel)
+    m.streamed_from = 2
+    order = list(range(7))                                   # layers 2..6 are streamed
+    assert [m.prefetch_after(order, i) for i in range(7)] == [None, None, 4, 5, 6, 2, 3]
+    assert [m.prefetch_after([0, 2, 4, 6], i) for i in range(4)] == [None, 6, 2, 4]          # a layer-skipping draft pass
+    m.streamed_from = 5
+    assert [m.prefetch_after(order, i) for i in range(7)] == [None] * 7                      # two streamed layers stay put

@@ -345,3 +345,33 @@ def test_recovery_after_a_failed_step_and_refusal_when_the_context_is_lost():
             assert c.get("/health").status_code == 503
     finally:
         serving.stop()
+
+
+def test_token_fanout_coalesces_wakeups_and_keeps_order():
+    """Many posts from another thread between two runs of the event loop arrive through ONE scheduled drain, in order."""
+    import asyncio
+    from realizar_b200.serving.api import TokenFanout
+
+    async def main():
+        loop = asyncio.get_running_loop()
+        fan = TokenFanout(loop)
+        q1, q2 = asyncio.Queue(), asyncio.Queue()
+        calls = []
+        orig = loop.call_soon_threadsafe
+        loop.call_soon_threadsafe = lambda *a, **k: (calls.append(1), orig(*a, **k))[1]
+
+        def producer():
+            for i in range(100):
+                fan.post(q1 if i % 2 == 0 else q2, ("tok", i))
+            fan.post(q1, ("end", None))
+        t = threading.Thread(target=producer)
+        t.start()
+        t.join()                                             # the loop has not run in between: everything is pending
+        got1 = [await q1.get() for _ in range(51)]
+        got2 = [await q2.get() for _ in range(50)]
+        assert [v for _, v in got1[:-1]] == list(range(0, 100, 2)) and got1[-1] == ("end", None)
+        assert [v for _, v in got2] == list(range(1, 100, 2))
+        assert len(calls) == 1                               # one wake-up for 101 posts
+        fan.post(q2, ("tok", 7))                             # and the next burst schedules its own
+        assert await q2.get() == ("tok", 7) and len(calls) == 2
+    asyncio.run(main())
