@@ -106,6 +106,9 @@ def test_cli_bench_compare_list_viz(tmp_path, capsys, monkeypatch):
     assert cli.main(["viz", f1]) == 0 and "p99" in capsys.readouterr().out
     assert cli.main(["bench", "--list"]) == 0
     assert cli.main(["bench", "cache", "-o", str(tmp_path / "c.json")]) == 0
+    assert cli.main(["bench", "cpu_generate", "--model", "tiny-llama", "-o", str(tmp_path / "g.json")]) == 0       # 128 + 128 tokens on the CPU engine
+    names = [r["name"] for r in json.loads((tmp_path / "g.json").read_text())["results"]] if (tmp_path / "g.json").exists() else []
+    assert any("decode_tok_per_s" in n for n in names) and any("prompt_tok_per_s" in n for n in names), names
     assert "paged_kv_open_reserve_close_64x512" in benchlib.load_results(str(tmp_path / "c.json"))
 
 
